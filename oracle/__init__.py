@@ -1,0 +1,254 @@
+"""CPU oracle for the fused glue ops: TEST INFRASTRUCTURE, not product code.
+
+ctypes front of oracle/cam_oracle.c (the C restatement of the reference's HIP glue kernels, one IEEE operation per
+statement) plus the float64 references the reference's own tests use. Imported only by tests/, __graft_entry__.smoke() and
+bench.py's CPU-baseline legs; the package caminus_b200 never imports it.
+
+Every function takes and returns numpy arrays. Row-parallel work is split over host threads here (ctypes releases the GIL
+for the duration of a call; the C side is single-threaded); `threads=1` gives the scalar port.
+"""
+import ctypes
+import os
+import subprocess
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+
+_DIR = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_DIR, 'libcam_oracle.so')
+_lib = None
+
+
+def build(force=False):
+    """compile cam_oracle.c with the Makefile beside it (gcc only)"""
+    src = os.path.join(_DIR, 'cam_oracle.c')
+    if force or not os.path.isfile(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.run(['make', '-C', _DIR, '-B'], check=True, stdout=subprocess.DEVNULL)
+    return _SO
+
+
+def _has_fma():
+    try:
+        return ' fma ' in open('/proc/cpuinfo').read()
+    except OSError:
+        return True
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        if not _has_fma():   # a library built for x86-64-v3 would trap here: rebuild without -march
+            subprocess.run(['gcc', '-O2', '-fPIC', '-shared', '-ffp-contract=off', '-fno-fast-math', '-std=gnu11', '-o', _SO,
+                            os.path.join(_DIR, 'cam_oracle.c'), '-lm'], check=True)
+        L = ctypes.CDLL(_SO)
+        L.orc_expf.restype = ctypes.c_float; L.orc_expf.argtypes = [ctypes.c_float]
+        L.orc_silu.restype = ctypes.c_float; L.orc_silu.argtypes = [ctypes.c_float]
+        L.orc_rsqrt.restype = ctypes.c_float; L.orc_rsqrt.argtypes = [ctypes.c_float]
+        L.orc_powi.restype = ctypes.c_float; L.orc_powi.argtypes = [ctypes.c_float, ctypes.c_int]
+        L.orc_sincos.restype = None
+        L.orc_sincos.argtypes = [ctypes.c_float, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float)]
+        _lib = L
+    return _lib
+
+
+def default_threads():
+    return len(os.sched_getaffinity(0)) if hasattr(os, 'sched_getaffinity') else (os.cpu_count() or 1)
+
+
+P, I, L_, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
+
+
+def _p(a, off=0):
+    return P(0) if a is None else P(a.ctypes.data + off)
+
+
+def _chunks(n, threads):
+    threads = max(1, min(int(threads), n))
+    edges = [n * i // threads for i in range(threads + 1)]
+    return [(a, b) for a, b in zip(edges[:-1], edges[1:]) if b > a]
+
+
+def _run(n, threads, fn):
+    """fn(a, b) on row ranges [a, b) covering [0, n)"""
+    ch = _chunks(n, threads)
+    if len(ch) <= 1:
+        for a, b in ch: fn(a, b)
+        return
+    with ThreadPoolExecutor(len(ch)) as ex:
+        list(ex.map(lambda ab: fn(*ab), ch))
+
+
+def _c(a, dt):
+    a = np.ascontiguousarray(a, dtype=dt)
+    return a
+
+
+# ---- scalar sequences -------------------------------------------------------------------------------------------------
+def expf(a): return float(lib().orc_expf(F(float(a))))
+def silu(x): return float(lib().orc_silu(F(float(x))))
+def rsqrt(v): return float(lib().orc_rsqrt(F(float(v))))
+def powi(b, e): return float(lib().orc_powi(F(float(b)), I(int(e))))
+
+
+def sincos(theta):
+    s, c = F(), F()
+    lib().orc_sincos(F(float(theta)), ctypes.byref(s), ctypes.byref(c))
+    return s.value, c.value
+
+
+# ---- ops --------------------------------------------------------------------------------------------------------------
+def q4k_get_rows(W, rb, vocab, toks, N, threads=None):
+    """W: uint8 table (vocab rows of rb bytes of Q4_K blocks); toks int32 [n] -> float32 [n, N]"""
+    W = _c(W, np.uint8).reshape(-1); toks = _c(toks, np.int32).reshape(-1); n = toks.size
+    x = np.empty((n, N), np.float32)
+    f = lib().orc_q4k_get_rows
+    _run(n, threads or default_threads(),
+         lambda a, b: f(_p(W), I(rb), I(vocab), _p(toks, 4 * a), _p(x, 4 * a * N), I(b - a), I(N)))
+    return x
+
+
+def add_rms16(x, nw, eps, d=None, w=None, S=0, want_h=True, threads=None):
+    """q3p_add_rms16: returns (x updated, h or None, h16 as float16)"""
+    x = _c(x, np.float32).copy(); n, N = x.shape
+    d = None if d is None else _c(d, np.float32); w = None if w is None else _c(w, np.float32); nw = _c(nw, np.float32)
+    h = np.empty((n, N), np.float32) if want_h else None; h16 = np.empty((n, N), np.uint16)
+    f = lib().orc_add_rms16
+    _run(n, threads or default_threads(),
+         lambda a, b: f(_p(x, 4 * a * N), _p(d, 4 * a * S * N), _p(w, 4 * a * S), I(S), _p(nw), F(eps), _p(h, 4 * a * N),
+                        _p(h16, 2 * a * N), I(b - a), I(N)))
+    return x, h, h16.view(np.float16)
+
+
+def add_rms16_q35(x, nw, eps, d=None, threads=None):
+    x = _c(x, np.float32).copy(); n, N = x.shape
+    d = None if d is None else _c(d, np.float32); nw = _c(nw, np.float32)
+    h = np.empty((n, N), np.float32); h16 = np.empty((n, N), np.uint16)
+    f = lib().orc_add_rms16_q35
+    _run(n, threads or default_threads(),
+         lambda a, b: f(_p(x, 4 * a * N), _p(d, 4 * a * N), _p(nw), F(eps), _p(h, 4 * a * N), _p(h16, 2 * a * N), I(b - a), I(N)))
+    return x, h, h16.view(np.float16)
+
+
+def add_rms_f16(x16, nw, eps, d16=None, threads=None):
+    """fp16-storage form: returns (x updated float16, h16 float16)"""
+    x = _c(x16, np.float16).copy(); n, N = x.shape
+    d = None if d16 is None else _c(d16, np.float16); nw = _c(nw, np.float32)
+    h16 = np.empty((n, N), np.uint16)
+    f = lib().orc_add_rms_f16
+    _run(n, threads or default_threads(),
+         lambda a, b: f(_p(x, 2 * a * N), _p(d, 2 * a * N), _p(nw), F(eps), _p(h16, 2 * a * N), I(b - a), I(N)))
+    return x, h16.view(np.float16)
+
+
+def rms_partial_f16(x16, d16=None, threads=None):
+    x = _c(x16, np.float16); n, Ns = x.shape
+    d = None if d16 is None else _c(d16, np.float16)
+    ss = np.empty(n, np.float32)
+    f = lib().orc_rms_partial_f16
+    _run(n, threads or default_threads(), lambda a, b: f(_p(x, 2 * a * Ns), _p(d, 2 * a * Ns), _p(ss, 4 * a), I(b - a), I(Ns)))
+    return ss
+
+
+def rms_apply_f16(x16, tot, nw, eps, Nfull, d16=None, threads=None):
+    x = _c(x16, np.float16).copy(); n, Ns = x.shape
+    d = None if d16 is None else _c(d16, np.float16); nw = _c(nw, np.float32); tot = _c(tot, np.float32)
+    h16 = np.empty((n, Ns), np.uint16)
+    f = lib().orc_rms_apply_f16
+    _run(n, threads or default_threads(),
+         lambda a, b: f(_p(x, 2 * a * Ns), _p(d, 2 * a * Ns), _p(tot, 4 * a), _p(nw), F(eps), _p(h16, 2 * a * Ns), I(b - a),
+                        I(Ns), I(Nfull)))
+    return x, h16.view(np.float16)
+
+
+def swiglu16(g, u, threads=None):
+    g = _c(g, np.float32).reshape(-1); u = _c(u, np.float32).reshape(-1); n = g.size
+    y = np.empty(n, np.uint16); f = lib().orc_swiglu16
+    _run(n, threads or default_threads(), lambda a, b: f(_p(g, 4 * a), _p(u, 4 * a), _p(y, 2 * a), L_(b - a)))
+    return y.view(np.float16)
+
+
+def silu_mul(g, u, threads=None):
+    g = _c(g, np.float32).reshape(-1); u = _c(u, np.float32).reshape(-1); n = g.size
+    h = np.empty(n, np.float32); f = lib().orc_silu_mul
+    _run(n, threads or default_threads(), lambda a, b: f(_p(g, 4 * a), _p(u, 4 * a), _p(h, 4 * a), L_(b - a)))
+    return h
+
+
+def _blocks(n, threads, fn):
+    """split n values at multiples of 32"""
+    nb = (n + 31) // 32
+    _run(nb, threads, lambda a, b: fn(a * 32, min(b * 32, n)))
+
+
+def q8_1(x, sum_order=0, threads=None):
+    """gg_quantize_q8_1: float32 [n] -> uint8 [ceil(n / 32) * 36]"""
+    x = _c(x, np.float32).reshape(-1); n = x.size
+    y = np.empty((n + 31) // 32 * 36, np.uint8); f = lib().orc_q8_1
+    _blocks(n, threads or default_threads(), lambda a, b: f(_p(x, 4 * a), _p(y, a // 32 * 36), L_(b - a), I(sum_order)))
+    return y
+
+
+def swiglu_q8_1(g, u, sum_order=0, threads=None):
+    """silu(g) * u quantised to Q8_1; g, u both float32 or both float16"""
+    f16 = g.dtype == np.float16
+    dt, es = (np.float16, 2) if f16 else (np.float32, 4)
+    g = _c(g, dt).reshape(-1); u = _c(u, dt).reshape(-1); n = g.size
+    y = np.empty((n + 31) // 32 * 36, np.uint8)
+    f = lib().orc_swiglu_q8_1_f16 if f16 else lib().orc_swiglu_q8_1
+    _blocks(n, threads or default_threads(),
+            lambda a, b: f(_p(g, es * a), _p(u, es * a), _p(y, a // 32 * 36), L_(b - a), I(sum_order)))
+    return y
+
+
+def swiglu_f32_from_f16(g, u, threads=None):
+    g = _c(g, np.float16).reshape(-1); u = _c(u, np.float16).reshape(-1); n = g.size
+    h = np.empty(n, np.float32); f = lib().orc_swiglu_f32_from_f16
+    _run(n, threads or default_threads(), lambda a, b: f(_p(g, 2 * a), _p(u, 2 * a), _p(h, 4 * a), L_(b - a)))
+    return h
+
+
+def qk_rope(qkv, ldq, nh, nkv, par, pos0, cache, n, yarn=False, threads=None):
+    """q3p_qk_rope: qkv float32 [n * ldq]; cache float16 (flat; rows of 2 nkv 128) is copied and updated.
+    Returns (q16 float16 [n, nh, 128], cache)"""
+    qkv = _c(qkv, np.float32).reshape(-1); par = _c(par, np.float32); cache = _c(cache, np.float16).reshape(-1).copy()
+    q16 = np.empty((n, nh, 128), np.uint16); f = lib().orc_qk_rope
+    _run(n, threads or default_threads(),
+         lambda a, b: f(_p(qkv, 4 * a * ldq), I(ldq), I(nh), I(nkv), _p(par), I(pos0 + a), _p(q16, 2 * a * nh * 128), _p(cache),
+                        I(b - a), I(int(yarn))))
+    return q16.view(np.float16), cache
+
+
+def qk_rope_f16(q, k, par, pos0, yarn=False, threads=None):
+    """fp16 q [n, nh, 128], k [n, nkv, 128] -> (q out, k out) float16"""
+    q = _c(q, np.float16); k = _c(k, np.float16); par = _c(par, np.float32)
+    n, nh, _ = q.shape; nkv = k.shape[1]
+    qo = np.empty(q.shape, np.uint16); ko = np.empty(k.shape, np.uint16); f = lib().orc_qk_rope_f16
+    _run(n, threads or default_threads(),
+         lambda a, b: f(_p(q, 2 * a * nh * 128), _p(k, 2 * a * nkv * 128), I(nh), I(nkv), _p(par), I(pos0 + a),
+                        _p(qo, 2 * a * nh * 128), _p(ko, 2 * a * nkv * 128), I(b - a), I(int(yarn))))
+    return qo.view(np.float16), ko.view(np.float16)
+
+
+# ---- float64 references, as the reference's tests state them ----------------------------------------------------------------
+def rms_f64(x, nw, eps):
+    """tests/prefill/test_q3m_ops.py:160-161: x / sqrt(mean(x^2) + eps) * nw in float64"""
+    x = np.asarray(x, np.float64)
+    return x / np.sqrt((x * x).mean(-1, keepdims=True) + eps) * np.asarray(nw, np.float64)
+
+
+def norm_rope_f64(x, w, theta, eps, mscale=1.0):
+    """tests/engine/test_q3m_yarn_rope.py:102-108: float64 norm + NeoX RoPE of rows x [..., 128] with the angles theta [64]
+    (the caller passes the kernel's fp32 angles, or float64 ones for the looser test_q3m_ops.py:204-208 form)"""
+    x = np.asarray(x, np.float64)
+    y = x / np.sqrt((x * x).mean(-1, keepdims=True) + eps) * np.asarray(w, np.float64)
+    th = np.asarray(theta, np.float64)
+    c, s = np.cos(th) * mscale, np.sin(th) * mscale
+    return np.concatenate([y[..., :64] * c - y[..., 64:] * s, y[..., 64:] * c + y[..., :64] * s], -1)
+
+
+def q8_split(q8):
+    """tests/engine/golden_util.py:92-98: Q8_1 bytes -> (d float16 [nb], s float16 [nb], qs int8 [nb, 32])"""
+    b = np.asarray(q8, np.uint8).reshape(-1, 36)
+    return (b[:, 0:2].copy().view(np.float16).reshape(-1), b[:, 2:4].copy().view(np.float16).reshape(-1),
+            b[:, 4:].copy().view(np.int8))

@@ -1,0 +1,371 @@
+/* CPU oracle for the fused glue ops: TEST INFRASTRUCTURE, not product code.
+ *
+ * A plain-C restatement, statement by statement and in the same order of floating-point operations, of the reference's
+ * (jdominick05/caminus) HIP glue kernels. Only the test-suite, the smoke check and the benchmark's CPU-baseline leg may
+ * call it; the shipped library never links or loads it.
+ *
+ * Every operation below is an IEEE-754 binary32/binary64 operation with round-to-nearest-even (compile with
+ * -ffp-contract=off, no fast-math): products and sums are rounded one by one, fused multiply-adds appear exactly where the
+ * reference writes fma. The four library calls the reference leaves to AMD's device library (expf, rsqrtf, powf,
+ * cosf/sinf) have no portable bit pattern, so they are replaced by explicit sequences of IEEE operations, defined once here
+ * (orc_expf, orc_rsqrt, orc_powi, orc_sincos) and restated with the same operations in the CUDA kernels: the CUDA path
+ * is held bit-for-bit to this file, and this file is held to the reference's own CPU code (own_dequant.q4_k, q8_host,
+ * the float64 norm / RoPE references of its tests) by tests/test_oracle_pins.py and the fixtures in tests/golden/.
+ *
+ * Thread mapping restated from the reference: a workgroup of 256 threads = 8 waves of 32; a wave sum is the xor butterfly
+ * with partners 16, 8, 4, 2, 1 (kernels/q3m_prefill.hip:351-355); the workgroup total is the wave partials added in wave
+ * order from 0.0f (kernels/q3m_prefill.hip:405-406).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+#include <stddef.h>
+
+typedef _Float16 f16;
+
+static inline uint32_t f2u(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+static inline float u2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+static inline float h2f(uint16_t h) { f16 v; memcpy(&v, &h, 2); return (float)v; }           /* exact */
+static inline uint16_t f2h(float f) { f16 v = (f16)f; uint16_t h; memcpy(&h, &v, 2); return h; } /* RNE */
+
+/* ---- the four explicit sequences ------------------------------------------------------------------------------------ */
+
+/* exp(a), a clamped to [-87, 88]: n = rint(a log2 e) by the 1.5 * 2^23 constant, r = a - n ln2 in two fma steps,
+ * a degree-6 polynomial in fma form, then n added to the exponent field. Relative error below 1 ulp on the clamped range. */
+float orc_expf(float a) {
+    a = fminf(fmaxf(a, -87.0f), 88.0f);
+    const float t = fmaf(a, 0x1.715476p+0f, 12582912.0f);
+    const float n = t - 12582912.0f;
+    float r = fmaf(n, -0x1.62e430p-1f, a);
+    r = fmaf(n, 0x1.05c610p-29f, r);
+    float p = 0x1.687b46p-10f;
+    p = fmaf(p, r, 0x1.123bdcp-7f);
+    p = fmaf(p, r, 0x1.555b5cp-5f);
+    p = fmaf(p, r, 0x1.55548ep-3f);
+    p = fmaf(p, r, 0x1.fffff8p-2f);
+    p = fmaf(p, r, 1.0f);
+    p = fmaf(p, r, 1.0f);
+    return u2f(f2u(p) + (f2u(t) << 23));
+}
+
+/* the reference's gg_silu, x / (1 + expf(-x)) (kernels/k3_gguf_ops.h:53), on orc_expf; the division is IEEE */
+float orc_silu(float x) { return x / (1.0f + orc_expf(-x)); }
+
+/* 1 / sqrt(v): IEEE square root, then IEEE division (stands for rsqrtf) */
+float orc_rsqrt(float v) { return 1.0f / sqrtf(v); }
+
+/* base^e for an integer e >= 0: binary exponentiation in binary64, rounded once to binary32 (stands for powf(base, (float)e)) */
+float orc_powi(float base, int e) {
+    double b = (double)base, p = 1.0;
+    while (e) { if (e & 1) p = p * b; b = b * b; e >>= 1; }
+    return (float)p;
+}
+
+/* sin and cos of theta (|theta| < 2^22): n = rint(theta 2/pi), r = theta - n pi/2 in three fma steps, polynomials on
+ * [-pi/4, pi/4], quadrant from n's two low bits. Absolute error below 2 ulp of 1. */
+void orc_sincos(float theta, float * sn, float * cs) {
+    const float t = fmaf(theta, 0x1.45f306p-1f, 12582912.0f);
+    const float n = t - 12582912.0f;
+    const uint32_t q = f2u(t) & 3u;
+    float r = fmaf(n, -0x1.921fb6p+0f, theta);
+    r = fmaf(n, 0x1.777a5cp-25f, r);
+    r = fmaf(n, 0x1.ee59dap-50f, r);
+    const float z = r * r;
+    float ps = -0x1.99518cp-13f;
+    ps = fmaf(ps, z, 0x1.11076ep-7f);
+    ps = fmaf(ps, z, -0x1.555546p-3f);
+    const float s = fmaf(r * z, ps, r);
+    float pc = 0x1.994222p-16f;
+    pc = fmaf(pc, z, -0x1.6c08c4p-10f);
+    pc = fmaf(pc, z, 0x1.55553ep-5f);
+    pc = fmaf(pc, z, -0.5f);
+    const float c = fmaf(z, pc, 1.0f);
+    const float s0 = (q & 1u) ? c : s, c0 = (q & 1u) ? s : c;
+    *sn = (q & 2u) ? -s0 : s0;
+    *cs = ((q + 1u) & 2u) ? -c0 : c0;
+}
+
+/* ---- wave / workgroup sums ------------------------------------------------------------------------------------------ */
+
+/* v[32] -> every lane's butterfly total (partners 16, 8, 4, 2, 1); returns lane 0's (all lanes hold the same bits) */
+static float wave_sum(const float * v) {
+    float a[32], b[32];
+    memcpy(a, v, sizeof a);
+    for (int o = 16; o > 0; o >>= 1) {
+        for (int l = 0; l < 32; l++) b[l] = a[l] + a[l ^ o];
+        memcpy(a, b, sizeof a);
+    }
+    return a[0];
+}
+static float wave_max(const float * v) {
+    float m = v[0];
+    for (int l = 1; l < 32; l++) m = fmaxf(m, v[l]);   /* max is exact: any order gives the butterfly's bits */
+    return m;
+}
+
+/* ---- Q4_K embedding rows (kernels/q3m_prefill.hip:362-380; host form python/caminus/own_dequant.py:19-37) ---------------- */
+void orc_q4k_get_rows(const uint8_t * W, int rb, int vocab, const int32_t * toks, float * x, int n, int N) {
+    for (int t = 0; t < n; t++) {
+        int tok = toks[t]; tok = tok < 0 ? 0 : tok; tok = tok > vocab - 1 ? vocab - 1 : tok;
+        const uint8_t * row = W + (size_t)tok * rb;
+        float * xr = x + (size_t)t * N;
+        for (int i = 0; i < N; i++) {
+            const uint8_t * blk = row + (size_t)(i >> 8) * 144;
+            const int j = i & 255, sb = j >> 5, l = j & 31, is = sb >> 1, hi = sb & 1;
+            const uint8_t * s = blk + 4;
+            const uint32_t sc = sb < 4 ? (s[sb] & 63u) : ((s[sb + 4] & 0xfu) | ((uint32_t)(s[sb - 4] >> 6) << 4));
+            const uint32_t m = sb < 4 ? (s[sb + 4] & 63u) : ((uint32_t)(s[sb + 4] >> 4) | ((uint32_t)(s[sb] >> 6) << 4));
+            const float d = h2f((uint16_t)(blk[0] | (blk[1] << 8)));
+            const float dm = h2f((uint16_t)(blk[2] | (blk[3] << 8)));
+            const float q = (float)((blk[16 + is * 32 + l] >> (4 * hi)) & 15);
+            const float a = d * (float)sc, b = a * q, c = dm * (float)m;
+            xr[i] = b - c;
+        }
+    }
+}
+
+/* ---- residual add + RMSNorm ----------------------------------------------------------------------------------------- */
+
+/* one row of N = 256 NI values already added (xs): thread tid's chain over tid + 256 j, the 8 wave sums in order */
+static float row_ss(const float * xs, int N) {
+    float part[8];
+    for (int wv = 0; wv < 8; wv++) {
+        float v[32];
+        for (int l = 0; l < 32; l++) {
+            const int tid = wv * 32 + l;
+            float ss = 0.0f;
+            for (int i = tid; i < N; i += 256) ss = fmaf(xs[i], xs[i], ss);
+            v[l] = ss;
+        }
+        part[wv] = wave_sum(v);
+    }
+    float tot = 0.0f;
+    for (int q = 0; q < 8; q++) tot += part[q];
+    return tot;
+}
+
+/* q3p_add_rms16 (kernels/q3m_prefill.hip:382-415): x [n][N] += sum over slots (d [n][S][N], w [n][S] or null);
+ * h (nullable) and h16 = the normed row. */
+void orc_add_rms16(float * x, const float * d, const float * w, int S, const float * nw, float eps, float * h, uint16_t * h16,
+                   int n, int N) {
+    for (int t = 0; t < n; t++) {
+        float * xr = x + (size_t)t * N;
+        const float * dr = d ? d + (size_t)t * S * N : NULL;
+        const float * wr = w ? w + (size_t)t * S : NULL;
+        for (int i = 0; i < N; i++) {
+            float acc = 0.0f;
+            for (int sl = 0; sl < S; sl++) acc = wr ? fmaf(wr[sl], dr[(size_t)sl * N + i], acc) : acc + dr[(size_t)sl * N + i];
+            if (S > 0) xr[i] = xr[i] + acc;
+        }
+        const float tot = row_ss(xr, N);
+        const float scale = orc_rsqrt(tot / (float)N + eps);
+        for (int i = 0; i < N; i++) {
+            const float v = (xr[i] * scale) * nw[i];
+            if (h) h[(size_t)t * N + i] = v;
+            h16[(size_t)t * N + i] = f2h(v);
+        }
+    }
+}
+
+/* q35p_add_rms16 (kernels/q35_prefill.hip:628-660): x += d (d nullable), any N = 256 NI; h always written */
+void orc_add_rms16_q35(float * x, const float * d, const float * nw, float eps, float * h, uint16_t * h16, int n, int N) {
+    for (int t = 0; t < n; t++) {
+        float * xr = x + (size_t)t * N;
+        if (d) for (int i = 0; i < N; i++) xr[i] = xr[i] + d[(size_t)t * N + i];
+        const float tot = row_ss(xr, N);
+        const float scale = orc_rsqrt(tot / (float)N + eps);
+        for (int i = 0; i < N; i++) {
+            const float v = (xr[i] * scale) * nw[i];
+            h[(size_t)t * N + i] = v;
+            h16[(size_t)t * N + i] = f2h(v);
+        }
+    }
+}
+
+/* the fp16-storage form of the same statements (the benchmark's per-layer config): xs = (float)x + (float)d in fp32,
+ * x = fp16(xs) stored, the norm taken over the unrounded xs, h16 = fp16((xs scale) nw) */
+void orc_add_rms_f16(uint16_t * x, const uint16_t * d, const float * nw, float eps, uint16_t * h16, int n, int N) {
+    for (int t = 0; t < n; t++) {
+        float xs[N];
+        uint16_t * xr = x + (size_t)t * N;
+        for (int i = 0; i < N; i++) {
+            xs[i] = h2f(xr[i]);
+            if (d) { xs[i] = xs[i] + h2f(d[(size_t)t * N + i]); xr[i] = f2h(xs[i]); }
+        }
+        const float tot = row_ss(xs, N);
+        const float scale = orc_rsqrt(tot / (float)N + eps);
+        for (int i = 0; i < N; i++) h16[(size_t)t * N + i] = f2h((xs[i] * scale) * nw[i]);
+    }
+}
+
+/* tensor-parallel form (no reference counterpart: the reference replicates its norms): this rank holds a column shard
+ * x [n][Ns] of rows of Nfull. Kernel 1: the shard's partial sum of squares of xs = x + d with the same thread mapping on
+ * its Ns columns, nothing stored. Kernel 2, after the partials were summed over ranks: x = fp16(xs), h16 = the normed shard. */
+void orc_rms_partial_f16(const uint16_t * x, const uint16_t * d, float * ss, int n, int Ns) {
+    for (int t = 0; t < n; t++) {
+        float xs[Ns];
+        for (int i = 0; i < Ns; i++) {
+            xs[i] = h2f(x[(size_t)t * Ns + i]);
+            if (d) xs[i] = xs[i] + h2f(d[(size_t)t * Ns + i]);
+        }
+        ss[t] = row_ss(xs, Ns);
+    }
+}
+void orc_rms_apply_f16(uint16_t * x, const uint16_t * d, const float * tot, const float * nw, float eps, uint16_t * h16,
+                       int n, int Ns, int Nfull) {
+    for (int t = 0; t < n; t++) {
+        const float scale = orc_rsqrt(tot[t] / (float)Nfull + eps);
+        for (int i = 0; i < Ns; i++) {
+            float xs = h2f(x[(size_t)t * Ns + i]);
+            if (d) { xs = xs + h2f(d[(size_t)t * Ns + i]); x[(size_t)t * Ns + i] = f2h(xs); }
+            h16[(size_t)t * Ns + i] = f2h((xs * scale) * nw[i]);
+        }
+    }
+}
+
+/* ---- SwiGLU and Q8_1 ------------------------------------------------------------------------------------------------ */
+
+/* q3p_swiglu (kernels/q3m_prefill.hip:515-518): y = fp16(silu(g) u) */
+void orc_swiglu16(const float * g, const float * u, uint16_t * y, long n) {
+    for (long i = 0; i < n; i++) y[i] = f2h(orc_silu(g[i]) * u[i]);
+}
+/* gg_silu_mul (kernels/k3_gguf.hip:74-77): h = silu(g) u in fp32 */
+void orc_silu_mul(const float * g, const float * u, float * h, long n) {
+    for (long i = 0; i < n; i++) h[i] = orc_silu(g[i]) * u[i];
+}
+
+/* one block of 32 values -> 36 bytes: fp16 d, fp16 sum, int8 qs[32].
+ * quantize_q8_1_lane as the reference restates it in q8_lane (kernels/k3_gguf_ops.h:145-153): amax and sum by the wave
+ * butterfly, d = amax / 127.0f, q = amax == 0 ? 0 : roundf(x / d) (true division; halves away from zero).
+ * sum_order 0: the lane butterfly (gg_op_q8_1, kernels/k3_gguf_ops.h:55-77). sum_order 1: aq_fill's order, 8 lanes of a
+ * float4 each: (e0 + e1) + (e2 + e3) per lane, then partners 4, 2, 1 (kernels/k3_gguf_ops.h:83-120); d and the codes are
+ * the same in both ("d = amax / 127 and q = roundf(x / d) per element exactly as quantize_q8_1_lane").
+ * A value that is not finite gives code 0 (the reference leaves that conversion undefined). */
+static void q8_1_block(const float * xi, uint8_t * out, int sum_order) {
+    float a[32];
+    for (int l = 0; l < 32; l++) a[l] = fabsf(xi[l]);
+    const float amax = wave_max(a);
+    float sum;
+    if (sum_order == 0) sum = wave_sum(xi);
+    else {
+        float p[8], q[8];
+        for (int l = 0; l < 8; l++) p[l] = (xi[4 * l] + xi[4 * l + 1]) + (xi[4 * l + 2] + xi[4 * l + 3]);
+        for (int m = 4; m >= 1; m >>= 1) {
+            for (int l = 0; l < 8; l++) q[l] = p[l] + p[l ^ m];
+            memcpy(p, q, sizeof p);
+        }
+        sum = p[0];
+    }
+    const float d = amax / 127.0f;
+    const uint16_t hd = f2h(d), hs = f2h(sum);
+    memcpy(out, &hd, 2); memcpy(out + 2, &hs, 2);
+    for (int l = 0; l < 32; l++) {
+        int8_t q = 0;
+        if (amax != 0.0f) {
+            const float v = xi[l] / d;
+            if (fabsf(v) < 127.5f) q = (int8_t)roundf(v);   /* (false for NaN; a finite block never exceeds 127.00002) */
+        }
+        out[4 + l] = (uint8_t)q;
+    }
+}
+
+/* gg_quantize_q8_1 (kernels/k3_gguf.hip:29-36): n values, blocks of 32, values past n are 0 */
+void orc_q8_1(const float * x, uint8_t * y, long n, int sum_order) {
+    const long nb = (n + 31) / 32;
+    for (long b = 0; b < nb; b++) {
+        float xi[32];
+        for (int l = 0; l < 32; l++) { const long i = b * 32 + l; xi[l] = i < n ? x[i] : 0.0f; }
+        q8_1_block(xi, y + b * 36, sum_order);
+    }
+}
+/* gg_op_q8_1 work = 2 (kernels/k3_gguf_ops.h:70-72): xi = silu(x) * mul, then the block quantiser */
+void orc_swiglu_q8_1(const float * g, const float * u, uint8_t * y, long n, int sum_order) {
+    const long nb = (n + 31) / 32;
+    for (long b = 0; b < nb; b++) {
+        float xi[32];
+        for (int l = 0; l < 32; l++) { const long i = b * 32 + l; xi[l] = i < n ? orc_silu(g[i]) * u[i] : 0.0f; }
+        q8_1_block(xi, y + b * 36, sum_order);
+    }
+}
+/* the same with fp16 gate / up (converted exactly to fp32 first) */
+void orc_swiglu_q8_1_f16(const uint16_t * g, const uint16_t * u, uint8_t * y, long n, int sum_order) {
+    const long nb = (n + 31) / 32;
+    for (long b = 0; b < nb; b++) {
+        float xi[32];
+        for (int l = 0; l < 32; l++) { const long i = b * 32 + l; xi[l] = i < n ? orc_silu(h2f(g[i])) * h2f(u[i]) : 0.0f; }
+        q8_1_block(xi, y + b * 36, sum_order);
+    }
+}
+/* the fp32 products the quantiser saw (for the reference's flip rule, tests/engine/golden_util.py:132-173) */
+void orc_swiglu_f32_from_f16(const uint16_t * g, const uint16_t * u, float * h, long n) {
+    for (long i = 0; i < n; i++) h[i] = orc_silu(h2f(g[i])) * h2f(u[i]);
+}
+
+/* ---- q/k RMSNorm + NeoX RoPE ---------------------------------------------------------------------------------------- */
+
+/* one head of 128 (kernels/q3m_prefill.hip:552-590): ss = x x per dim, four wave sums in order, scale = rsqrt(tot / 128 +
+ * eps), y1 = (scale x) w, pairs (j, j + 64): fma(x0, c, -(x1 s)) and fma(x1, c, x0 s) */
+static void head_norm_rope(const float * x, const float * wn, float eps, const float * rc, const float * rs, float * y) {
+    float part[4], sq[128], y1[128];
+    for (int i = 0; i < 128; i++) sq[i] = x[i] * x[i];
+    for (int wv = 0; wv < 4; wv++) part[wv] = wave_sum(sq + 32 * wv);
+    float tot = 0.0f;
+    for (int q = 0; q < 4; q++) tot += part[q];
+    const float scale = orc_rsqrt(tot / 128.0f + eps);
+    for (int i = 0; i < 128; i++) y1[i] = (scale * x[i]) * wn[i];
+    for (int j = 0; j < 64; j++) {
+        const float c = rc[j], sn = rs[j], x0 = y1[j], x1 = y1[j + 64];
+        y[j] = fmaf(x0, c, -(x1 * sn));
+        y[j + 64] = fmaf(x1, c, x0 * sn);
+    }
+}
+/* cos / sin of a position: plain (theta = (float)pos powf(theta_scale, j), kernels/q3m_prefill.hip:565) or the YaRN table
+ * (theta = (float)pos freq[j], both times mscale, kernels/q3m_prefill.hip:560-563) */
+static void pos_table(const float * par, int pos, int yarn, float * rc, float * rs) {
+    for (int j = 0; j < 64; j++) {
+        float s, c;
+        if (yarn) { orc_sincos((float)pos * par[258 + j], &s, &c); rc[j] = c * par[322]; rs[j] = s * par[322]; }
+        else { orc_sincos((float)pos * orc_powi(par[256], j), &s, &c); rc[j] = c; rs[j] = s; }
+    }
+}
+
+/* q3p_qk_rope (kernels/q3m_prefill.hip:520-591, the F16 cache form): qkv fp32 [n][ldq] = q | k | v; q16 [n][nh][128];
+ * cache row pos = K [nkv][128] | V [nkv][128] fp16. par = q_norm[128] | k_norm[128] | theta_scale | eps (| freq[64] | mscale) */
+void orc_qk_rope(const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, uint16_t * q16, uint16_t * cache,
+                 int n, int yarn) {
+    const size_t M = (size_t)nkv * 128;
+    for (int t = 0; t < n; t++) {
+        const int pos = pos0 + t;
+        float rc[64], rs[64], y[128];
+        pos_table(par, pos, yarn, rc, rs);
+        const float * row = qkv + (size_t)t * ldq;
+        uint16_t * cw = cache + (size_t)pos * 2 * M;
+        for (int hy = 0; hy < nh + nkv; hy++) {
+            const int isq = hy < nh, g = hy - nh;
+            const float * x = isq ? row + (size_t)hy * 128 : row + (size_t)nh * 128 + (size_t)g * 128;
+            head_norm_rope(x, isq ? par : par + 128, par[257], rc, rs, y);
+            uint16_t * o = isq ? q16 + ((size_t)t * nh + hy) * 128 : cw + (size_t)g * 128;
+            for (int i = 0; i < 128; i++) o[i] = f2h(y[i]);
+            if (!isq) for (int i = 0; i < 128; i++) cw[M + (size_t)g * 128 + i] = f2h(row[(size_t)nh * 128 + M + (size_t)g * 128 + i]);
+        }
+    }
+}
+/* the same statements on fp16 q [n][nh][128] and k [n][nkv][128] (converted exactly to fp32), fp16 out (may alias in) */
+void orc_qk_rope_f16(const uint16_t * q, const uint16_t * k, int nh, int nkv, const float * par, int pos0, uint16_t * qo,
+                     uint16_t * ko, int n, int yarn) {
+    for (int t = 0; t < n; t++) {
+        float rc[64], rs[64], x[128], y[128];
+        pos_table(par, pos0 + t, yarn, rc, rs);
+        for (int hy = 0; hy < nh + nkv; hy++) {
+            const int isq = hy < nh;
+            const size_t off = isq ? ((size_t)t * nh + hy) * 128 : ((size_t)t * nkv + (hy - nh)) * 128;
+            const uint16_t * in = isq ? q + off : k + off;
+            uint16_t * o = isq ? qo + off : ko + off;
+            for (int i = 0; i < 128; i++) x[i] = h2f(in[i]);
+            head_norm_rope(x, isq ? par : par + 128, par[257], rc, rs, y);
+            for (int i = 0; i < 128; i++) o[i] = f2h(y[i]);
+        }
+    }
+}
+
+int orc_version(void) { return 1; }
