@@ -1,0 +1,279 @@
+"""Benchmark of the per-layer glue path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--ops]
+
+A step is one pass of the per-layer glue over one batch of token rows (Qwen3-32B shape, fp16 storage): residual add +
+RMSNorm (hidden 5120) -> q/k RMSNorm + NeoX RoPE (64 q + 8 kv heads of 128) -> SwiGLU + Q8_1 (intermediate 25600), three
+launches. Every rank (one process per GPU; torchrun for N > 1) processes T = 65536 rows of its own: rows are independent,
+so there is no data-path collective and the scaling is weak. `value` = rows of all ranks / the slowest rank's device time
+with inputs resident in HBM; `e2e` = the same through the host-buffer call (pinned host inputs copied in, outputs copied
+back, inside the timed region). `roofline` is for the dominant kernel (SwiGLU + Q8_1) from CUDA events recorded around it in
+the timed steps. `cpu_baseline` is the CPU oracle on a bounded sample of rows on this box's host cores.
+--impl reference times the CPU implementation alone. --ops adds one line per single-op config to stderr-free JSON key "ops".
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path: sys.path.insert(0, ROOT)
+
+import numpy as np   # noqa: E402
+
+T_PER_GPU, HIDDEN, NH, NKV, INTER = 65536, 5120, 64, 8, 25600
+BYTES_PER_TOKEN = {'add_rms_f16': 4 * HIDDEN * 2, 'qk_rope_f16': (NH + NKV) * 128 * 2 * 2, 'swiglu_q8_1_f16': 2 * INTER * 2 + INTER // 32 * 36}
+METRIC = 'per-layer glue throughput (residual add + RMSNorm -> q/k norm + RoPE -> SwiGLU + Q8_1), tokens/s'
+
+
+def peaks():
+    p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.isfile(p):
+        try: return float(json.load(open(p))['hbm_gbs']), 'measured'
+        except Exception: pass
+    return 6650.0, 'fallback'
+
+
+class Clocks:
+    """samples nvidia-smi during the timed region"""
+    Q = 'index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,' \
+        'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap'
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile('w', suffix='.csv', delete=False); self.path = f.name
+            self.proc = subprocess.Popen(['nvidia-smi', f'--id={self.index}', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits', '-lms', '100'],
+                                         stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None: return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try: self.proc.wait(timeout=5)
+        except Exception: self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            c = [v.strip() for v in line.split(',')]
+            if len(c) < 9: continue
+            try: sm.append(float(c[1])); mx.append(float(c[2]))
+            except ValueError: continue
+            for name, v in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), c[5:9]):
+                if v.lower().startswith('active'): reasons.add(name)
+        try: os.unlink(self.path)
+        except OSError: pass
+        if not sm: return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['no samples']}
+        return {'sm_mhz': float(np.median(sm)), 'sm_max_mhz': float(max(mx)), 'reasons': sorted(reasons), 'samples': len(sm)}
+
+
+def cpu_layer_glue(sample, threads):
+    """the CPU oracle over `sample` rows of the same workload: seconds for one pass"""
+    import oracle
+    from caminus_b200 import synth
+    x0, r0, w = synth.add_rms_inputs(sample, HIDDEN, dtype=np.float16)
+    q0, k0 = synth.qk_inputs(sample, NH, NKV); g0, u0 = synth.swiglu_inputs(sample, INTER); par = synth.rope_par()
+    oracle.add_rms_f16(x0[:8], w, 1e-6, r0[:8], threads=1)     # (library load, page-in)
+    t0 = time.perf_counter()
+    oracle.add_rms_f16(x0, w, 1e-6, r0, threads=threads)
+    oracle.qk_rope_f16(q0, k0, par, 0, threads=threads)
+    oracle.swiglu_q8_1(g0.reshape(-1), u0.reshape(-1), sum_order=1, threads=threads)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank):
+    """the reference arm: the path's CPU implementation (the C restatement of the reference's kernels: its HIP sources do not
+    compile for a CPU) on this box's host cores, all threads, a bounded sample of the workload per step"""
+    if rank != 0: return
+    import oracle
+    oracle.build()
+    threads = oracle.default_threads()
+    sample = 256
+    for _ in range(args.warmup): cpu_layer_glue(sample, threads)
+    ts = [cpu_layer_glue(sample, threads) for _ in range(args.steps)]
+    sec = float(np.mean(ts)); val = sample / sec
+    print(json.dumps({
+        'impl': 'reference', 'metric': METRIC, 'value': val, 'unit': 'tokens/s', 'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup,
+        'ms_per_step': sec * 1e3, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': f'per-layer glue, Qwen3-32B shape (BASELINE config 5): hidden {HIDDEN}, {NH} q + {NKV} kv heads x 128, '
+                               f'intermediate {INTER}, fp16 storage', 'rows_per_step': sample},
+        'cpu_baseline': {'value': val, 'unit': 'tokens/s', 'cores': threads, 'kind': 'port',
+                         'sample': f'{sample} token rows per step through all three ops (the C oracle, rows split over {threads} host threads)'},
+        'e2e': {'value': val, 'unit': 'tokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0}), flush=True)
+
+
+def single_op_lines(torch, dev, peak):
+    """device-resident GB/s of the single-op configs 1-4 (median of 20 event-timed launches; buffers rotated where a
+    config's data would fit in L2)"""
+    from caminus_b200 import glue, synth
+    from caminus_b200.engine import gguf
+    from caminus_b200.prefill import q3m_ops
+    O = q3m_ops.Ops(dev)
+    out = {}
+
+    def timed(fn, reps=20, rot=1):
+        for i in range(3): fn(i % rot)
+        torch.cuda.synchronize(dev)
+        ts = []
+        for i in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(i % rot); b.record(); b.synchronize(); ts.append(a.elapsed_time(b) * 1e-3)
+        return float(np.median(ts)), float(np.min(ts))
+
+    def line(name, nbytes, sec, units, unit):
+        med, mn = sec
+        out[name] = {'bytes': nbytes, 'us_median': med * 1e6, 'us_min': mn * 1e6, 'gbs': nbytes / med / 1e9, 'frac_of_peak': nbytes / med / 1e9 / peak,
+                     'frac_of_8tbs': nbytes / med / 8e12, unit: units / med}
+
+    g = torch.Generator(device=dev); g.manual_seed(0)
+    # config 1: add + RMSNorm fp32, hidden 2048: T = 1 (latency) and a T sweep
+    for T in (1, 4096, 65536):
+        rot = 8 if T <= 4096 else 1
+        xs = [torch.randn(T, 2048, device=dev, generator=g) for _ in range(rot)]; d = torch.randn(T, 2048, device=dev, generator=g)
+        nw = 1 + 0.05 * torch.randn(2048, device=dev, generator=g); h = torch.empty(T, 2048, device=dev); h16 = torch.empty(T, 2048, dtype=torch.float16, device=dev)
+        sec = timed(lambda i: O.add_rms16(xs[i], nw, 1e-6, h16, T, 2048, d=d, S=1, h=h), reps=200 if T == 1 else 20, rot=rot)
+        line(f'add_rms16_f32_h2048_T{T}', T * (4 * 8192 + 4096) + 8192, sec, T, 'tokens_per_s')
+        del xs, d, h, h16
+    # config 2: q/k norm + RoPE fp16, T = 4096, 32 + 4 heads (75 MB: 4 rotating copies)
+    T = 4096
+    qs = [torch.randn(T, 32, 128, device=dev, generator=g).half() for _ in range(4)]; ks = [torch.randn(T, 4, 128, device=dev, generator=g).half() for _ in range(4)]
+    par = torch.from_numpy(synth.rope_par()).to(dev)
+    line('qk_rope_f16_T4096', T * 36 * 128 * 4 + 1032, timed(lambda i: glue.qk_rope_f16(qs[i], ks[i], par, 0), rot=4), T, 'tokens_per_s')
+    del qs, ks
+    # config 3: SwiGLU + Q8_1, T = 8192, I = 25600
+    T = 8192
+    gt = (torch.randn(T * INTER, device=dev, generator=g) * 1.5).half(); up = (torch.randn(T * INTER, device=dev, generator=g) * 1.5).half()
+    yq = torch.empty(T * INTER // 32 * 36, dtype=torch.uint8, device=dev)
+    line('swiglu_q8_1_f16_T8192', T * BYTES_PER_TOKEN['swiglu_q8_1_f16'], timed(lambda i: gguf.swiglu_q8_1(gt, up, yq)), T, 'tokens_per_s')
+    del gt, up, yq
+    # config 4: Q4_K rows, vocab 151936 x 2048, 16384 ids (output 134 MB: 2 rotating outputs)
+    vocab, N, n = 151936, 2048, 16384
+    W = torch.randint(0, 256, (vocab, 8, 144), device=dev, dtype=torch.uint8, generator=g)
+    W[:, :, 0:4] = (torch.randn(vocab, 8, 2, device=dev, generator=g) * 1e-3).abs().half().view(torch.uint8).view(vocab, 8, 4)
+    toks = torch.randint(0, vocab, (n,), device=dev, dtype=torch.int32, generator=g)
+    xo = [torch.empty(n, N, device=dev) for _ in range(2)]
+    line('q4k_get_rows_16384x2048', n * (4 + 1152 + 8192), timed(lambda i: O.emb(W.view(-1), 1152, vocab, toks, xo[i], n, N), rot=2), n, 'rows_per_s')
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1); ap.add_argument('--steps', type=int, default=20); ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--rows', type=int, default=T_PER_GPU, help='token rows per GPU (the configured workload is 65536)')
+    ap.add_argument('--ops', action='store_true', help='also time the single-op configs 1-4 on rank 0')
+    ap.add_argument('--cpu-sample', type=int, default=512)
+    ap.add_argument('--e2e-rows', type=int, default=16384, help='token rows per GPU of the host-buffer leg (pinned host memory: 209 KB per row)')
+    args = ap.parse_args()
+    rank, world, local = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1)), int(os.environ.get('LOCAL_RANK', 0))
+    if args.impl == 'reference': return run_reference(args, rank)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from caminus_b200 import glue, lib
+    lib.load()
+    dev = torch.device(f'cuda:{local}'); torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group('nccl', device_id=dev)
+    T = args.rows
+    gen = torch.Generator(device=dev); gen.manual_seed(1000 + rank)
+    rn = lambda *s, scale=1.0: (torch.randn(*s, device=dev, generator=gen) * scale).half()
+    x = rn(T, HIDDEN); resid = rn(T, HIDDEN); q = rn(T, NH, 128); k = rn(T, NKV, 128)
+    gate = torch.empty(T, INTER, dtype=torch.float16, device=dev); up = torch.empty(T, INTER, dtype=torch.float16, device=dev)
+    for a in range(0, T, 8192): gate[a:a + 8192] = rn(min(8192, T - a), INTER, scale=1.5); up[a:a + 8192] = rn(min(8192, T - a), INTER, scale=1.5)
+    from caminus_b200 import synth
+    nw = (1 + 0.05 * torch.randn(HIDDEN, device=dev, generator=gen)).float(); par = torch.from_numpy(synth.rope_par()).to(dev)
+    h16 = torch.empty_like(x); yq = torch.empty(T * INTER // 32 * 36, dtype=torch.uint8, device=dev)
+
+    def step(ev=None):      # x, q, k are updated in place, as the path does: the next step runs on this step's rows (still finite)
+        if ev: ev[0].record()
+        glue.add_rms_f16(x, nw, 1e-6, h16=h16, d=resid)
+        if ev: ev[1].record()
+        glue.qk_rope_f16(q, k, par, 0)
+        if ev: ev[2].record()
+        glue.swiglu_q8_1(gate.view(-1), up.view(-1), yq)
+        if ev: ev[3].record()
+
+    def barrier():
+        if world > 1: torch.distributed.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup): step()
+    barrier()
+    clocks = Clocks(local); clocks.start()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    barrier()
+    for i in range(args.steps): step(evs[i])
+    barrier()
+    clk = clocks.stop()
+    # device time of exactly K steps: first step's first event to the last step's last; per-kernel times from the events between
+    per = np.array([[e[j].elapsed_time(e[j + 1]) for j in range(3)] for e in evs]) * 1e-3     # [steps, 3] seconds
+    total = evs[0][0].elapsed_time(evs[-1][3]) * 1e-3
+    if world > 1:
+        t = torch.tensor([total], device=dev, dtype=torch.float64); torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX); total = float(t.item())
+    ms_per_step = total / args.steps * 1e3
+    value = T * world / (total / args.steps)
+
+    # end to end through host buffers (pinned): inputs copied in, the three launches, outputs copied back, every step
+    from caminus_b200 import host
+    Te = min(T, args.e2e_rows)
+    Hrun = host.HostLayerGlue(Te, HIDDEN, NH, NKV, INTER, nw, par, dev)
+    Hrun.fill_from(x, resid, q, k, gate, up)
+    del gate, up, yq, h16, x, q, k, resid
+    torch.cuda.empty_cache()
+    for _ in range(2): Hrun.run()
+    barrier()
+    e2e_steps = max(2, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps): Hrun.run()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev, dtype=torch.float64); torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX); e2e_s = float(t.item())
+
+    if rank == 0:
+        peak, which = peaks()
+        names = ['add_rms_f16', 'qk_rope_f16', 'swiglu_q8_1_f16']
+        med = np.median(per, 0)
+        kern = {n: {'us': float(med[i] * 1e6), 'gbs': T * BYTES_PER_TOKEN[n] / float(med[i]) / 1e9,
+                    'frac': T * BYTES_PER_TOKEN[n] / float(med[i]) / 1e9 / peak} for i, n in enumerate(names)}
+        dom = 'swiglu_q8_1_f16'
+        ach = T * BYTES_PER_TOKEN[dom] / float(per[:, 2].mean()) / 1e9
+        import oracle
+        threads = oracle.default_threads()
+        cs = cpu_layer_glue(args.cpu_sample, threads)
+        line = {
+            'metric': METRIC, 'value': value, 'unit': 'tokens/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
+            'ms_per_step': ms_per_step, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
+            'data': 'synthetic',
+            'config': {'workload': f'per-layer glue, Qwen3-32B shape (BASELINE config 5): T = {T} token rows per GPU, hidden {HIDDEN}, {NH} q + {NKV} kv '
+                                   f'heads x 128, intermediate {INTER}, fp16 storage, fp32 arithmetic', 'rows_per_gpu': T,
+                       'parallelism': f'token rows x {world} (no collective)', 'l2': 'inputs (13.7 GB per step) larger than L2',
+                       'bytes_per_token': sum(BYTES_PER_TOKEN.values())},
+            'clocks': clk,
+            'e2e': {'value': Te * world / e2e_s, 'unit': 'tokens/s', 'rows_per_gpu': Te, 'h2d_bytes_per_step': Hrun.h2d_bytes, 'd2h_bytes_per_step': Hrun.d2h_bytes,
+                    'ms_per_step': e2e_s * 1e3},
+            'gpu_launches': 3 * args.steps,
+            'roofline': {'bound': 'hbm', 'kernel': 'q8_1_kernel<fp16, swiglu> (SwiGLU + Q8_1)', 'achieved': ach, 'peak': peak, 'unit': 'GB/s',
+                         'frac': ach / peak, 'peak_source': which, 'frac_of_8tbs': ach / 8000.0, 'traffic': None},
+            'kernels': kern,
+            'hbm_gbs_all_three': T * sum(BYTES_PER_TOKEN.values()) / (total / args.steps) / 1e9,
+            'cpu_baseline': {'value': args.cpu_sample / cs, 'unit': 'tokens/s', 'cores': threads, 'kind': 'port',
+                             'sample': f'{args.cpu_sample} token rows through all three ops (the C oracle, rows split over {threads} host threads)'},
+        }
+        if args.ops: line['ops'] = single_op_lines(torch, dev, peak)
+        print(json.dumps(line), flush=True)
+    if world > 1: torch.distributed.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

@@ -1,0 +1,33 @@
+// Library-wide entry points of the C ABI and the per-device cache of the multiprocessor count.
+#include "cam_common.cuh"
+
+#include <mutex>
+
+int cam_sm_count() {
+    static std::mutex mu;
+    static int count[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::lock_guard<std::mutex> lock(mu);
+    if (count[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v < 1) v = 148;
+        count[dev] = v;
+    }
+    return count[dev];
+}
+
+// The ABI's version: bumped when an entry's parameters change.
+extern "C" int cam_abi_version(void) { return 1; }
+
+// Text of an entry's return value: 0 ok, negative = an argument refusal of this library, positive = a cudaError_t.
+extern "C" const char * cam_error_string(int code) {
+    switch (code) {
+        case CAM_OK: return "ok";
+        case CAM_ERR_ARG: return "invalid argument (a count, a size or a null pointer the entry does not take)";
+        case CAM_ERR_ALIGN: return "a pointer or stride is not aligned for 128-bit access";
+        case CAM_ERR_SHAPE: return "a row length, head layout or position range outside what the kernels are built for";
+        case CAM_ERR_CAPACITY: return "more than a fixed-size buffer of the library holds";
+        default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
+    }
+}

@@ -1,0 +1,322 @@
+// Residual add + RMSNorm (the reference's q3p_add_rms16, kernels/q3m_prefill.hip:382-415, = own_op_add_rms16,
+// kernels/k3_own_ops.h:305-383; q35p_add_rms16, kernels/q35_prefill.hip:628-660, = q35_op_add_rms16,
+// kernels/k3_q35_ops.h:88-130), an fp16-storage form of the same statements, and a tensor-parallel pair.
+//
+// The reference runs one workgroup of 256 threads per row: thread tid owns elements tid + 256 j, sums their squares in an
+// fma chain over j, the 8 waves reduce by the xor butterfly (partners 16, 8, 4, 2, 1) and the 8 wave sums are added in
+// order. Here ONE WARP owns a row and every lane stands for 8 of the reference's threads, with 128-bit accesses:
+//   fp32 rows: lane l reads float4 chunks at 4l + 128 m; accumulator (c, m & 1) is reference thread v = 4l + c + 128 (m & 1),
+//              whose chain runs over j = m >> 1 in order. v's wave is (l >> 3) + 4 (m & 1), its wave lane 4 (l & 7) + c:
+//              butterfly partners 16, 8, 4 are lanes l ^ 4, l ^ 2, l ^ 1; partners 2 and 1 are inside the lane.
+//   fp16 rows: lane l reads 8 halves at 8l + 256 m; accumulator c is thread v = 8l + c, chain over j = m; wave l >> 2, wave
+//              lane 8 (l & 3) + c: partners 16, 8 are lanes l ^ 2, l ^ 1; partners 4, 2, 1 are inside the lane.
+// Adding in that order reproduces the reference's sum of squares bit for bit (addition is commutative, so both partners of
+// a butterfly step hold the same bits), without a block-wide barrier.
+#include "cam_common.cuh"
+
+namespace {
+
+// ---- the reference's reduction on this file's two layouts ------------------------------------------------------------------
+// fp32 layout: a[c + 4 b] (c < 4, b < 2). Returns the workgroup total (every lane).
+CAM_DEV float ref_total_f32(float (&a)[8], int lane) {
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1)
+#pragma unroll
+        for (int k = 0; k < 8; k++) a[k] = fadd(a[k], __shfl_xor_sync(CAM_FULL, a[k], o));
+    float P[2];
+#pragma unroll
+    for (int b = 0; b < 2; b++) {
+        const float t0 = fadd(a[4 * b + 0], a[4 * b + 2]), t1 = fadd(a[4 * b + 1], a[4 * b + 3]);   // partner 2
+        P[b] = fadd(t0, t1);                                                                        // partner 1
+    }
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) tot = fadd(tot, __shfl_sync(CAM_FULL, P[w >> 2], 8 * (w & 3)));    // wave w: lanes 8 (w & 3) .., b = w >> 2
+    return tot;
+}
+// fp16 layout: a[c] (c < 8)
+CAM_DEV float ref_total_f16(float (&a)[8], int lane) {
+#pragma unroll
+    for (int o = 2; o > 0; o >>= 1)
+#pragma unroll
+        for (int k = 0; k < 8; k++) a[k] = fadd(a[k], __shfl_xor_sync(CAM_FULL, a[k], o));
+    const float u0 = fadd(a[0], a[4]), u1 = fadd(a[1], a[5]), u2 = fadd(a[2], a[6]), u3 = fadd(a[3], a[7]);   // partner 4
+    const float P = fadd(fadd(u0, u2), fadd(u1, u3));                                                           // partners 2, 1
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) tot = fadd(tot, __shfl_sync(CAM_FULL, P, 4 * w));
+    return tot;
+}
+
+// ---- fp32 rows ----------------------------------------------------------------------------------------------------------
+// CH > 0: N = 128 CH, the row stays in registers. CH = 0: any N (a multiple of 256), the row is read again from memory.
+// Q35: x = x + d (one addend). Otherwise the weighted slots of q3p_add_rms16: acc from 0 in slot order.
+constexpr int RMS_WARPS = 4;
+
+CAM_DEV float4 slot_add(float4 xv, const float * __restrict__ dr, const float * __restrict__ wr, int S, int N, int i, bool q35) {
+    if (q35) {
+        const float4 dv = __ldg(reinterpret_cast<const float4 *>(dr + i));
+        return make_float4(fadd(xv.x, dv.x), fadd(xv.y, dv.y), fadd(xv.z, dv.z), fadd(xv.w, dv.w));
+    }
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int sl = 0; sl < S; sl++) {
+        const float4 dv = __ldg(reinterpret_cast<const float4 *>(dr + (size_t)sl * N + i));
+        if (wr) {
+            const float w = __ldg(wr + sl);
+            acc = make_float4(ffma(w, dv.x, acc.x), ffma(w, dv.y, acc.y), ffma(w, dv.z, acc.z), ffma(w, dv.w, acc.w));
+        } else acc = make_float4(fadd(acc.x, dv.x), fadd(acc.y, dv.y), fadd(acc.z, dv.z), fadd(acc.w, dv.w));
+    }
+    return make_float4(fadd(xv.x, acc.x), fadd(xv.y, acc.y), fadd(xv.z, acc.z), fadd(xv.w, acc.w));
+}
+
+CAM_DEV void norm_store(float4 xv, float scale, const float * __restrict__ nw, float * hr, uint16_t * h16r, int i) {
+    const float4 wv = __ldg(reinterpret_cast<const float4 *>(nw + i));
+    const float4 v = make_float4(fmul(fmul(xv.x, scale), wv.x), fmul(fmul(xv.y, scale), wv.y), fmul(fmul(xv.z, scale), wv.z),
+                                 fmul(fmul(xv.w, scale), wv.w));
+    if (hr) __stcs(reinterpret_cast<float4 *>(hr + i), v);
+    st64_stream(h16r + i, make_uint2(f2_to_h2(v.x, v.y), f2_to_h2(v.z, v.w)));
+}
+
+template <int CH>
+__global__ void __launch_bounds__(RMS_WARPS * 32) add_rms_f32_kernel(float * __restrict__ x, const float * __restrict__ d,
+                                                                     const float * __restrict__ w, int S, const float * __restrict__ nw,
+                                                                     float eps, float * __restrict__ h, uint16_t * __restrict__ h16,
+                                                                     int N, int n, int q35) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nch = CH > 0 ? CH : N >> 7;
+    const bool add = q35 ? d != nullptr : S > 0;
+    for (int t = blockIdx.x * RMS_WARPS + warp; t < n; t += gridDim.x * RMS_WARPS) {
+        float * xr = x + (size_t)t * N;
+        const float * dr = d ? d + (size_t)t * (q35 ? 1 : S) * N : nullptr;
+        const float * wr = w ? w + (size_t)t * S : nullptr;
+        float * hr = h ? h + (size_t)t * N : nullptr;
+        uint16_t * h16r = h16 + (size_t)t * N;
+        float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        if (CH > 0) {
+            float4 xv[CH > 0 ? CH : 1];
+#pragma unroll
+            for (int m = 0; m < CH; m++) xv[m] = *reinterpret_cast<const float4 *>(xr + 4 * lane + 128 * m);
+            if (add) {
+#pragma unroll
+                for (int m = 0; m < CH; m++) {
+                    xv[m] = slot_add(xv[m], dr, wr, S, N, 4 * lane + 128 * m, q35);
+                    *reinterpret_cast<float4 *>(xr + 4 * lane + 128 * m) = xv[m];
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < CH; m++) {
+                const int b = 4 * (m & 1);
+                a[b + 0] = ffma(xv[m].x, xv[m].x, a[b + 0]); a[b + 1] = ffma(xv[m].y, xv[m].y, a[b + 1]);
+                a[b + 2] = ffma(xv[m].z, xv[m].z, a[b + 2]); a[b + 3] = ffma(xv[m].w, xv[m].w, a[b + 3]);
+            }
+            const float tot = ref_total_f32(a, lane);
+            const float scale = cam_rsqrt(fadd(fdiv(tot, (float)N), eps));
+#pragma unroll
+            for (int m = 0; m < CH; m++) norm_store(xv[m], scale, nw, hr, h16r, 4 * lane + 128 * m);
+        } else {
+            for (int m = 0; m < nch; m += 2) {                 // (N is a multiple of 256: chunks come in pairs b = 0, 1)
+#pragma unroll
+                for (int b = 0; b < 2; b++) {
+                    const int i = 4 * lane + 128 * (m + b);
+                    float4 xv = *reinterpret_cast<const float4 *>(xr + i);
+                    if (add) { xv = slot_add(xv, dr, wr, S, N, i, q35); *reinterpret_cast<float4 *>(xr + i) = xv; }
+                    a[4 * b + 0] = ffma(xv.x, xv.x, a[4 * b + 0]); a[4 * b + 1] = ffma(xv.y, xv.y, a[4 * b + 1]);
+                    a[4 * b + 2] = ffma(xv.z, xv.z, a[4 * b + 2]); a[4 * b + 3] = ffma(xv.w, xv.w, a[4 * b + 3]);
+                }
+            }
+            const float tot = ref_total_f32(a, lane);
+            const float scale = cam_rsqrt(fadd(fdiv(tot, (float)N), eps));
+            for (int m = 0; m < nch; m++) {      // (each lane reads back what it wrote itself)
+                const int i = 4 * lane + 128 * m;
+                norm_store(*reinterpret_cast<const float4 *>(xr + i), scale, nw, hr, h16r, i);
+            }
+        }
+    }
+}
+
+// ---- fp16 rows, staged through shared memory with cp.async ------------------------------------------------------------------
+// Each warp keeps STAGES rows (x and d, 2 N bytes each) in flight in its own slice of shared memory; a lane copies exactly
+// the 16-byte chunks it will read back, so waiting on its own copy groups is the only synchronisation. The row is read
+// twice from shared memory (sum of squares, then normalise) and never twice from HBM.
+// MODE 0: x = fp16(xs) stored, h16 = fp16((xs scale) nw)   (xs = (float)x + (float)d in fp32, the norm over the unrounded xs)
+// MODE 1: the tensor-parallel partial: ss[t] = this shard's sum of squares of xs, nothing else stored
+// MODE 2: the tensor-parallel apply: as MODE 0 with the row total read from tot[t] and divided by Nfull
+constexpr int F16_STAGES = 2;
+
+CAM_DEV void load8(const uint4 v, float (&f)[8]) {
+    const float2 a = h2_to_f2(v.x), b = h2_to_f2(v.y), c = h2_to_f2(v.z), e = h2_to_f2(v.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = e.x; f[7] = e.y;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(128) add_rms_f16_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d,
+                                                          const float * __restrict__ nw, float eps, uint16_t * __restrict__ h16,
+                                                          float * __restrict__ ss, const float * __restrict__ tot_in, int N, int Nfull,
+                                                          int n, int warps) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nch = (N + 255) >> 8;                             // 16-byte chunks per lane per row and tensor (the last may be
+    const int nd = d ? 2 : 1;                                   // short when N is not a multiple of 256: lanes past N add +0)
+    const size_t half_bytes = (size_t)nch * 512;                // one tensor's row in a stage
+    const size_t stage_bytes = (size_t)nd * half_bytes;
+    unsigned char * mine = smem + (size_t)warp * F16_STAGES * stage_bytes;
+    const int stride = gridDim.x * warps;
+    const int t0 = blockIdx.x * warps + warp;
+
+    auto issue = [&](int t, int st) {
+        if (t < n) {
+            unsigned char * sx = mine + (size_t)st * stage_bytes;
+            const uint16_t * xr = x + (size_t)t * N;
+            for (int m = 0; m < nch; m++)
+                if (8 * lane + 256 * m < N) cp_async16(sx + (size_t)(m * 32 + lane) * 16, xr + 8 * lane + 256 * m);
+            if (d) {
+                const uint16_t * dr = d + (size_t)t * N;
+                for (int m = 0; m < nch; m++)
+                    if (8 * lane + 256 * m < N) cp_async16(sx + half_bytes + (size_t)(m * 32 + lane) * 16, dr + 8 * lane + 256 * m);
+            }
+        }
+        cp_async_commit();
+    };
+
+    issue(t0, 0);
+    int st = 0;
+    for (int t = t0; t < n; t += stride, st ^= 1) {
+        issue(t + stride, st ^ 1);
+        cp_async_wait<1>();                                     // this row's group has landed (the next may still fly)
+        const unsigned char * sx = mine + (size_t)st * stage_bytes;
+        const unsigned char * sd = sx + half_bytes;
+        float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        float tot;
+        if (MODE != 2) {
+#pragma unroll 4
+            for (int m = 0; m < nch; m++) {
+                if (8 * lane + 256 * m >= N) break;
+                float xs[8];
+                load8(*reinterpret_cast<const uint4 *>(sx + (size_t)(m * 32 + lane) * 16), xs);
+                if (d) {
+                    float dv[8];
+                    load8(*reinterpret_cast<const uint4 *>(sd + (size_t)(m * 32 + lane) * 16), dv);
+#pragma unroll
+                    for (int c = 0; c < 8; c++) xs[c] = fadd(xs[c], dv[c]);
+                }
+#pragma unroll
+                for (int c = 0; c < 8; c++) a[c] = ffma(xs[c], xs[c], a[c]);
+            }
+            tot = ref_total_f16(a, lane);
+        } else tot = __ldg(tot_in + t);
+        if (MODE == 1) {
+            if (lane == 0) ss[t] = tot;
+        } else {
+            const float scale = cam_rsqrt(fadd(fdiv(tot, (float)(MODE == 2 ? Nfull : N)), eps));
+            uint16_t * xr = x + (size_t)t * N;
+            uint16_t * hr = h16 + (size_t)t * N;
+#pragma unroll 2
+            for (int m = 0; m < nch; m++) {
+                const int i = 8 * lane + 256 * m;
+                if (i >= N) break;
+                float xs[8];
+                load8(*reinterpret_cast<const uint4 *>(sx + (size_t)(m * 32 + lane) * 16), xs);
+                if (d) {
+                    float dv[8];
+                    load8(*reinterpret_cast<const uint4 *>(sd + (size_t)(m * 32 + lane) * 16), dv);
+#pragma unroll
+                    for (int c = 0; c < 8; c++) xs[c] = fadd(xs[c], dv[c]);
+                    st128(xr + i, make_uint4(f2_to_h2(xs[0], xs[1]), f2_to_h2(xs[2], xs[3]), f2_to_h2(xs[4], xs[5]), f2_to_h2(xs[6], xs[7])));
+                }
+                const float4 w0 = __ldg(reinterpret_cast<const float4 *>(nw + i)), w1 = __ldg(reinterpret_cast<const float4 *>(nw + i + 4));
+                float v[8];
+                v[0] = fmul(fmul(xs[0], scale), w0.x); v[1] = fmul(fmul(xs[1], scale), w0.y);
+                v[2] = fmul(fmul(xs[2], scale), w0.z); v[3] = fmul(fmul(xs[3], scale), w0.w);
+                v[4] = fmul(fmul(xs[4], scale), w1.x); v[5] = fmul(fmul(xs[5], scale), w1.y);
+                v[6] = fmul(fmul(xs[6], scale), w1.z); v[7] = fmul(fmul(xs[7], scale), w1.w);
+                st128_stream(hr + i, make_uint4(f2_to_h2(v[0], v[1]), f2_to_h2(v[2], v[3]), f2_to_h2(v[4], v[5]), f2_to_h2(v[6], v[7])));
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
+template <int MODE>
+int launch_f16(uint16_t * x, const uint16_t * d, const float * nw, float eps, uint16_t * h16, float * ss, const float * tot, int N,
+               int Nfull, int n, cudaStream_t stream) {
+    if (n == 0) return CAM_OK;
+    const size_t per_warp = (size_t)F16_STAGES * (d ? 2 : 1) * ((N + 255) >> 8) * 512;
+    int warps = 4;
+    while (warps > 1 && per_warp * warps > 200 * 1024) warps >>= 1;
+    const size_t smem = per_warp * warps;
+    if (smem > 227 * 1024) return CAM_ERR_SHAPE;
+    const cudaError_t e = cudaFuncSetAttribute(add_rms_f16_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    int per_sm = (int)((227 * 1024) / (smem + 1024));           // (1 KB per resident block is the system's)
+    per_sm = per_sm < 1 ? 1 : per_sm > 8 ? 8 : per_sm;
+    const long cap = (long)cam_sm_count() * per_sm;
+    const long want = ((long)n + warps - 1) / warps;
+    const int grid = (int)(want < cap ? want : cap);
+    add_rms_f16_kernel<MODE><<<grid, warps * 32, smem, stream>>>(x, d, nw, eps, h16, ss, tot, N, Nfull, n, warps);
+    return (int)cudaGetLastError();
+}
+
+int launch_f32(float * x, const float * d, const float * w, int S, const float * nw, float eps, float * h, uint16_t * h16, int N, int n,
+               int q35, cudaStream_t stream) {
+    if (n == 0) return CAM_OK;
+    const long cap = (long)cam_sm_count() * 4;
+    const long want = ((long)n + RMS_WARPS - 1) / RMS_WARPS;
+    const int grid = (int)(want < cap ? want : cap);
+#define CAM_RMS_CASE(CHV) \
+    case CHV: add_rms_f32_kernel<CHV><<<grid, RMS_WARPS * 32, 0, stream>>>(x, d, w, S, nw, eps, h, h16, N, n, q35); break;
+    switch (N <= 2048 ? N >> 7 : 0) {
+        CAM_RMS_CASE(2) CAM_RMS_CASE(4) CAM_RMS_CASE(6) CAM_RMS_CASE(8) CAM_RMS_CASE(10) CAM_RMS_CASE(12) CAM_RMS_CASE(14) CAM_RMS_CASE(16)
+        default: add_rms_f32_kernel<0><<<grid, RMS_WARPS * 32, 0, stream>>>(x, d, w, S, nw, eps, h, h16, N, n, q35); break;
+    }
+#undef CAM_RMS_CASE
+    return (int)cudaGetLastError();
+}
+
+}   // namespace
+
+// q3p_add_rms16: x [n][N] += sum over S slots of w[t][s] d[t][s][:] (w null: plain sums; d null or S = 0: no add);
+// h (nullable) fp32 and h16 fp16 = (x rsqrt(mean x^2 + eps)) nw. n is the reference's grid.x.
+// Reference: kernels/q3m_prefill.hip:385-387; wrapper python/caminus/prefill/q3m_ops.py:89-92.
+extern "C" int q3p_add_rms16(int n, float * x, const float * d, const float * w, int S, const float * nw, float eps, float * h,
+                             void * h16, int N, void * stream) {
+    if (n < 0 || N < 256 || (N & 255) || N > 2048 || S < 0 || !x || !nw || !h16 || (S > 0 && !d)) return CAM_ERR_ARG;
+    if (!cam_aligned16(x) || !cam_aligned16(nw) || (d && !cam_aligned16(d)) || (h && !cam_aligned16(h)) ||
+        (reinterpret_cast<uintptr_t>(h16) & 7u) || (w && (reinterpret_cast<uintptr_t>(w) & 3u))) return CAM_ERR_ALIGN;
+    return launch_f32(x, d, w, S, nw, eps, h, (uint16_t *)h16, N, n, 0, (cudaStream_t)stream);
+}
+
+// q35p_add_rms16: x [n][N] += d (d nullable), any N = 256 NI <= 65536; h and h16 always written.
+// Reference: kernels/q35_prefill.hip:636-638; wrapper python/caminus/prefill/q35own.py:135-140.
+extern "C" int q35p_add_rms16(int n, float * x, const float * d, const float * nw, float eps, float * h, void * h16, int N,
+                              void * stream) {
+    if (n < 0 || N < 256 || (N & 255) || N > 65536 || !x || !nw || !h || !h16) return CAM_ERR_ARG;
+    if (!cam_aligned16(x) || !cam_aligned16(nw) || (d && !cam_aligned16(d)) || !cam_aligned16(h) ||
+        (reinterpret_cast<uintptr_t>(h16) & 7u)) return CAM_ERR_ALIGN;
+    return launch_f32(x, d, nullptr, 0, nw, eps, h, (uint16_t *)h16, N, n, 1, (cudaStream_t)stream);
+}
+
+// cam_add_rms_f16: the same statements on fp16 storage: x [n][N] fp16 (updated in place when d is given), d fp16 (nullable),
+// h16 fp16 out. N a multiple of 256. No counterpart kernel in the reference (its glue takes fp32 activations); the
+// arithmetic is q35p_add_rms16's (kernels/q35_prefill.hip:636-660) between an exact fp16 load and a rounded fp16 store.
+extern "C" int cam_add_rms_f16(int n, void * x, const void * d, const float * nw, float eps, void * h16, int N, void * stream) {
+    if (n < 0 || N < 256 || (N & 255) || N > 65536 || !x || !nw || !h16) return CAM_ERR_ARG;
+    if (!cam_aligned16(x) || !cam_aligned16(nw) || (d && !cam_aligned16(d)) || !cam_aligned16(h16)) return CAM_ERR_ALIGN;
+    return launch_f16<0>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, nullptr, nullptr, N, N, n, (cudaStream_t)stream);
+}
+
+// Tensor-parallel RMSNorm (hidden dimension sharded over ranks; no counterpart in the reference, which replicates its norms).
+// Ns (this rank's columns) is a multiple of 8.
+// cam_rms_partial_f16: ss [n] fp32 = this shard's sum of squares of xs = x + d over its Ns columns (nothing else written).
+// After the caller summed ss over the ranks (an all-reduce of n floats):
+// cam_rms_apply_f16: x = fp16(xs) (when d is given), h16 = fp16((xs rsqrt(tot / Nfull + eps)) nw_shard).
+extern "C" int cam_rms_partial_f16(int n, const void * x, const void * d, float * ss, int Ns, void * stream) {
+    if (n < 0 || Ns < 8 || (Ns & 7) || !x || !ss) return CAM_ERR_ARG;
+    if (!cam_aligned16(x) || (d && !cam_aligned16(d)) || (reinterpret_cast<uintptr_t>(ss) & 3u)) return CAM_ERR_ALIGN;
+    return launch_f16<1>((uint16_t *)x, (const uint16_t *)d, nullptr, 0.0f, nullptr, ss, nullptr, Ns, Ns, n, (cudaStream_t)stream);
+}
+extern "C" int cam_rms_apply_f16(int n, void * x, const void * d, const float * tot, const float * nw, float eps, void * h16, int Ns,
+                                 int Nfull, void * stream) {
+    if (n < 0 || Ns < 8 || (Ns & 7) || Nfull < Ns || !x || !tot || !nw || !h16) return CAM_ERR_ARG;
+    if (!cam_aligned16(x) || (d && !cam_aligned16(d)) || !cam_aligned16(nw) || !cam_aligned16(h16)) return CAM_ERR_ALIGN;
+    return launch_f16<2>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, nullptr, tot, Ns, Nfull, n, (cudaStream_t)stream);
+}

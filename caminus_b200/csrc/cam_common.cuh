@@ -1,0 +1,107 @@
+// Shared device helpers of the glue kernels (sm_100a).
+//
+// Arithmetic rule of this library: every value a kernel stores is produced by IEEE-754 operations with round-to-nearest
+// (the __f*_rn intrinsics are never contracted or reassociated by the compiler; the translation units are also built
+// with -fmad=false), so a result does not depend on the approximate special-function unit and can be restated
+// operation by operation on a CPU. The reference leaves expf, rsqrtf, powf and cosf / sinf to its device library;
+// here they are the explicit sequences cam_expf, cam_rsqrt, cam_powi and cam_sincos below.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define CAM_DEV __device__ __forceinline__
+#define CAM_FULL 0xffffffffu
+
+// ---- argument refusals of the C entry points (negative; CUDA errors are returned as their positive cudaError_t) --------
+#define CAM_OK 0
+#define CAM_ERR_ARG (-1)        // a count, size or null pointer the entry does not take
+#define CAM_ERR_ALIGN (-2)      // a pointer or stride that is not 16-byte aligned
+#define CAM_ERR_SHAPE (-3)      // a row length or head layout outside what the kernels are built for
+#define CAM_ERR_CAPACITY (-4)   // more than a fixed-size buffer of the library holds
+
+CAM_DEV float fmul(float a, float b) { return __fmul_rn(a, b); }
+CAM_DEV float fadd(float a, float b) { return __fadd_rn(a, b); }
+CAM_DEV float fsub(float a, float b) { return __fsub_rn(a, b); }
+CAM_DEV float ffma(float a, float b, float c) { return __fmaf_rn(a, b, c); }
+CAM_DEV float fdiv(float a, float b) { return __fdiv_rn(a, b); }
+
+// exp(a), a clamped to [-87, 88]: n = rint(a log2 e) through the 1.5 * 2^23 constant, r = a - n ln 2 in two fma steps,
+// a degree-6 polynomial, n added to the exponent field.
+CAM_DEV float cam_expf(float a) {
+    a = fminf(fmaxf(a, -87.0f), 88.0f);
+    const float t = ffma(a, 0x1.715476p+0f, 12582912.0f);
+    const float n = fsub(t, 12582912.0f);
+    float r = ffma(n, -0x1.62e430p-1f, a);
+    r = ffma(n, 0x1.05c610p-29f, r);
+    float p = 0x1.687b46p-10f;
+    p = ffma(p, r, 0x1.123bdcp-7f);
+    p = ffma(p, r, 0x1.555b5cp-5f);
+    p = ffma(p, r, 0x1.55548ep-3f);
+    p = ffma(p, r, 0x1.fffff8p-2f);
+    p = ffma(p, r, 1.0f);
+    p = ffma(p, r, 1.0f);
+    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+}
+// the reference's gg_silu, x / (1 + expf(-x)) (kernels/k3_gguf_ops.h:53), with an IEEE division
+CAM_DEV float cam_silu(float x) { return fdiv(x, fadd(1.0f, cam_expf(-x))); }
+// 1 / sqrt(v): IEEE square root then IEEE division
+CAM_DEV float cam_rsqrt(float v) { return fdiv(1.0f, __fsqrt_rn(v)); }
+// base^e (integer e >= 0) by binary exponentiation in binary64, rounded once to binary32
+CAM_DEV float cam_powi(float base, int e) {
+    double b = (double)base, p = 1.0;
+    while (e) { if (e & 1) p = __dmul_rn(p, b); b = __dmul_rn(b, b); e >>= 1; }
+    return __double2float_rn(p);
+}
+// sin, cos of theta (|theta| < 2^22): n = rint(theta 2/pi), r = theta - n pi/2 in three fma steps, polynomials on
+// [-pi/4, pi/4], quadrant from n's two low bits
+CAM_DEV void cam_sincos(float theta, float & sn, float & cs) {
+    const float t = ffma(theta, 0x1.45f306p-1f, 12582912.0f);
+    const float n = fsub(t, 12582912.0f);
+    const uint32_t q = __float_as_uint(t) & 3u;
+    float r = ffma(n, -0x1.921fb6p+0f, theta);
+    r = ffma(n, 0x1.777a5cp-25f, r);
+    r = ffma(n, 0x1.ee59dap-50f, r);
+    const float z = fmul(r, r);
+    float ps = -0x1.99518cp-13f;
+    ps = ffma(ps, z, 0x1.11076ep-7f);
+    ps = ffma(ps, z, -0x1.555546p-3f);
+    const float s = ffma(fmul(r, z), ps, r);
+    float pc = 0x1.994222p-16f;
+    pc = ffma(pc, z, -0x1.6c08c4p-10f);
+    pc = ffma(pc, z, 0x1.55553ep-5f);
+    pc = ffma(pc, z, -0.5f);
+    const float c = ffma(z, pc, 1.0f);
+    const float s0 = (q & 1u) ? c : s, c0 = (q & 1u) ? s : c;
+    sn = (q & 2u) ? -s0 : s0;
+    cs = ((q + 1u) & 2u) ? -c0 : c0;
+}
+
+// ---- fp16 <-> fp32 (the widening is exact; the narrowing rounds to nearest even) --------------------------------------------
+CAM_DEV float2 h2_to_f2(uint32_t v) { return __half22float2(*reinterpret_cast<const __half2 *>(&v)); }
+CAM_DEV uint32_t f2_to_h2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+CAM_DEV uint16_t f_to_h(float a) { return __half_as_ushort(__float2half_rn(a)); }
+
+// ---- 128-bit global accesses ------------------------------------------------------------------------------------------
+CAM_DEV uint4 ldg128(const void * p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }          // read-only data
+CAM_DEV uint4 ld128(const void * p) { return *reinterpret_cast<const uint4 *>(p); }                 // data this kernel also writes
+CAM_DEV void st128(void * p, uint4 v) { *reinterpret_cast<uint4 *>(p) = v; }
+CAM_DEV void st64(void * p, uint2 v) { *reinterpret_cast<uint2 *>(p) = v; }
+CAM_DEV void st128_stream(void * p, uint4 v) { __stcs(reinterpret_cast<uint4 *>(p), v); }           // written once, not re-read here
+CAM_DEV void st64_stream(void * p, uint2 v) { __stcs(reinterpret_cast<uint2 *>(p), v); }
+
+// ---- cp.async (16 bytes per thread, L2 only) with commit / wait groups --------------------------------------------------------
+CAM_DEV void cp_async16(void * smem, const void * gmem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+CAM_DEV void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> CAM_DEV void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+static inline bool cam_aligned16(const void * p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// multiprocessors of the current device (cached per device)
+int cam_sm_count();

@@ -1,0 +1,184 @@
+// SwiGLU and the Q8_1 activation quantiser, fused and unfused.
+//
+// Reference statements: gg_silu(x) = x / (1 + expf(-x)) (kernels/k3_gguf_ops.h:53); the tape op gg_op_q8_1 with work = 2,
+// xi = gg_silu(x) * mul then quantize_q8_1_lane (kernels/k3_gguf_ops.h:55-77), restated in-tree as q8_lane
+// (kernels/k3_gguf_ops.h:145-153): amax = max |xi| and sum over the block of 32, d = amax / 127.0f, q = amax == 0 ? 0 :
+// roundf(xi / d) with a true division, block = { half d, half sum, int8 qs[32] } = 36 bytes. Unfused forms: q3p_swiglu
+// (kernels/q3m_prefill.hip:515-518), gg_silu_mul (kernels/k3_gguf.hip:74-77), gg_quantize_q8_1 (kernels/k3_gguf.hip:29-36).
+//
+// Mapping: a thread owns 8 consecutive values (one 16-byte load of fp16 gate and up, or two of fp32), 4 adjacent lanes own a
+// block. amax is order-free; the block sum follows the order of the reference's 8-lane quantiser aq_fill
+// (kernels/k3_gguf_ops.h:83-120): (e0 + e1) + (e2 + e3) per group of four, then partners 4, 2, 1 over the 8 groups. A lane
+// holds groups 2q and 2q + 1 (q its place in the quad): partner 4 is lane q ^ 2, partner 2 is lane q ^ 1, partner 1 is the
+// lane's other group. d and the codes are quantize_q8_1_lane's bits whatever the order.
+// A block's 36 bytes are written as 4-byte words: the quad's lanes write 8 codes each, lane 0 also (d, sum).
+#include "cam_common.cuh"
+
+namespace {
+
+constexpr int Q8_THREADS = 256;
+
+template <typename T> struct Load8;
+template <> struct Load8<float> {
+    static CAM_DEV void get(const float * p, float (&f)[8]) {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(p)), b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+    static CAM_DEV float one(const float * p) { return __ldg(p); }
+};
+template <> struct Load8<uint16_t> {
+    static CAM_DEV void get(const uint16_t * p, float (&f)[8]) {
+        const uint4 v = ldg128(p);
+        const float2 a = h2_to_f2(v.x), b = h2_to_f2(v.y), c = h2_to_f2(v.z), e = h2_to_f2(v.w);
+        f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = e.x; f[7] = e.y;
+    }
+    static CAM_DEV float one(const uint16_t * p) { return __half2float(__ushort_as_half(__ldg(p))); }
+};
+
+CAM_DEV int q8_code(float x, float d, float amax) {
+    const float v = fdiv(x, d);
+    return (amax != 0.0f && fabsf(v) < 127.5f) ? __float2int_rn(roundf(v)) : 0;   // (false for a NaN: code 0)
+}
+
+// SWIGLU: xi = silu(g) u; else xi = g. Full blocks [0, nb).
+template <typename T, bool SWIGLU>
+__global__ void __launch_bounds__(Q8_THREADS) q8_1_kernel(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y,
+                                                          long nb) {
+    const int lane = threadIdx.x & 31, q = lane & 3;
+    const long ngroups = nb * 4;
+    const long stride = (long)gridDim.x * Q8_THREADS;
+    for (long base = (long)blockIdx.x * Q8_THREADS + (threadIdx.x & ~31); base < ngroups; base += stride) {
+        const long gi = base + lane;
+        const bool on = gi < ngroups;
+        float h[8];
+        if (on) {
+            Load8<T>::get(g + gi * 8, h);
+            if (SWIGLU) {
+                float uv[8];
+                Load8<T>::get(u + gi * 8, uv);
+#pragma unroll
+                for (int k = 0; k < 8; k++) h[k] = fmul(cam_silu(h[k]), uv[k]);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; k++) h[k] = 0.0f;
+        }
+        float amax = fabsf(h[0]);
+#pragma unroll
+        for (int k = 1; k < 8; k++) amax = fmaxf(amax, fabsf(h[k]));
+        amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 2));
+        float sa = fadd(fadd(h[0], h[1]), fadd(h[2], h[3])), sb = fadd(fadd(h[4], h[5]), fadd(h[6], h[7]));
+        sa = fadd(sa, __shfl_xor_sync(CAM_FULL, sa, 2)); sb = fadd(sb, __shfl_xor_sync(CAM_FULL, sb, 2));   // partner 4
+        sa = fadd(sa, __shfl_xor_sync(CAM_FULL, sa, 1)); sb = fadd(sb, __shfl_xor_sync(CAM_FULL, sb, 1));   // partner 2
+        const float sum = fadd(sa, sb);                                                                     // partner 1
+        const float d = fdiv(amax, 127.0f);
+        uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            w0 |= (uint32_t)(q8_code(h[k], d, amax) & 0xff) << (8 * k);
+            w1 |= (uint32_t)(q8_code(h[4 + k], d, amax) & 0xff) << (8 * k);
+        }
+        if (on) {
+            uint32_t * o = reinterpret_cast<uint32_t *>(y + (gi >> 2) * 36);
+            if (q == 0) __stcs(o, f2_to_h2(d, sum));
+            __stcs(o + 1 + 2 * q, w0);
+            __stcs(o + 2 + 2 * q, w1);
+        }
+    }
+}
+
+// the last, partial block (n % 32 values, the rest 0): one warp, one lane per value
+template <typename T, bool SWIGLU>
+__global__ void __launch_bounds__(32) q8_1_tail_kernel(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y,
+                                                       long first, int rem) {
+    const int lane = threadIdx.x;
+    float x = 0.0f;
+    if (lane < rem) {
+        x = Load8<T>::one(g + first + lane);
+        if (SWIGLU) x = fmul(cam_silu(x), Load8<T>::one(u + first + lane));
+    }
+    float amax = fabsf(x);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, o));
+    float s = fadd(x, __shfl_xor_sync(CAM_FULL, x, 1));      // e0 + e1 | e2 + e3
+    s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 2));            // (e0 + e1) + (e2 + e3): the group's sum
+    s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 16));           // partners 4, 2, 1 of the 8 groups
+    s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 8));
+    s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 4));
+    const float d = fdiv(amax, 127.0f);
+    uint8_t * o = y + (first >> 5) * 36;
+    o[4 + lane] = (uint8_t)q8_code(x, d, amax);
+    if (lane == 0) *reinterpret_cast<uint32_t *>(o) = f2_to_h2(d, s);
+}
+
+template <typename T, bool SWIGLU>
+int launch_q8(const T * g, const T * u, void * y, long n, cudaStream_t stream) {
+    if (n < 0 || !g || !y || (SWIGLU && !u)) return CAM_ERR_ARG;
+    if (n == 0) return CAM_OK;
+    if (!cam_aligned16(g) || (SWIGLU && !cam_aligned16(u)) || (reinterpret_cast<uintptr_t>(y) & 3u)) return CAM_ERR_ALIGN;
+    const long nb = n >> 5;
+    if (nb > 0) {
+        const long want = (nb * 4 + Q8_THREADS - 1) / Q8_THREADS;
+        const long cap = (long)cam_sm_count() * 8;
+        q8_1_kernel<T, SWIGLU><<<(int)(want < cap ? want : cap), Q8_THREADS, 0, stream>>>(g, u, (uint8_t *)y, nb);
+    }
+    if (n & 31) q8_1_tail_kernel<T, SWIGLU><<<1, 32, 0, stream>>>(g, u, (uint8_t *)y, nb << 5, (int)(n & 31));
+    return (int)cudaGetLastError();
+}
+
+// y = silu(g) u elementwise: fp16 (q3p_swiglu) or fp32 (gg_silu_mul) out
+template <bool HALF_OUT>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const float * __restrict__ g, const float * __restrict__ u, void * __restrict__ y,
+                                                       long n, int vec) {
+    const long stride = (long)gridDim.x * 256;
+    const long n4 = vec ? n >> 2 : 0;
+    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n4; i += stride) {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(g) + i), b = __ldg(reinterpret_cast<const float4 *>(u) + i);
+        const float4 v = make_float4(fmul(cam_silu(a.x), b.x), fmul(cam_silu(a.y), b.y), fmul(cam_silu(a.z), b.z), fmul(cam_silu(a.w), b.w));
+        if (HALF_OUT) st64_stream(reinterpret_cast<uint16_t *>(y) + 4 * i, make_uint2(f2_to_h2(v.x, v.y), f2_to_h2(v.z, v.w)));
+        else __stcs(reinterpret_cast<float4 *>(y) + i, v);
+    }
+    for (long i = 4 * n4 + (long)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+        const float v = fmul(cam_silu(__ldg(g + i)), __ldg(u + i));
+        if (HALF_OUT) reinterpret_cast<uint16_t *>(y)[i] = f_to_h(v);
+        else reinterpret_cast<float *>(y)[i] = v;
+    }
+}
+
+template <bool HALF_OUT>
+int launch_silu_mul(const float * g, const float * u, void * y, long n, cudaStream_t stream) {
+    if (n < 0 || !g || !u || !y) return CAM_ERR_ARG;
+    if (n == 0) return CAM_OK;
+    const int vec = cam_aligned16(g) && cam_aligned16(u) && cam_aligned16(y);
+    const long want = ((vec ? (n + 3) / 4 : n) + 255) / 256;
+    const long cap = (long)cam_sm_count() * 8;
+    silu_mul_kernel<HALF_OUT><<<(int)(want < cap ? want : cap), 256, 0, stream>>>(g, u, y, n, vec);
+    return (int)cudaGetLastError();
+}
+
+}   // namespace
+
+// q3p_swiglu: y16[i] = fp16(silu(g[i]) u[i]), i < n. Reference: kernels/q3m_prefill.hip:516-518; python/caminus/prefill/q3m_ops.py:106-107.
+extern "C" int q3p_swiglu(const float * g, const float * u, void * y16, int n, void * stream) {
+    return launch_silu_mul<true>(g, u, y16, n, (cudaStream_t)stream);
+}
+// gg_silu_mul: h[i] = silu(g[i]) u[i] in fp32. Reference: kernels/k3_gguf.hip:74-77; python/caminus/engine/gguf.py:57-61.
+extern "C" int gg_silu_mul(const float * g, const float * u, float * h, int n, void * stream) {
+    return launch_silu_mul<false>(g, u, h, n, (cudaStream_t)stream);
+}
+// gg_quantize_q8_1: n fp32 values -> ceil(n / 32) blocks of 36 bytes; values past n quantise as 0. (The reference's launch
+// also writes whole blocks of zeros up to the next multiple of 8 blocks; this entry writes exactly ceil(n / 32).)
+// Reference: kernels/k3_gguf.hip:29-36; python/caminus/engine/gguf.py:39-46.
+extern "C" int gg_quantize_q8_1(const float * x, void * y, int n, void * stream) {
+    return launch_q8<float, false>(x, nullptr, y, n, (cudaStream_t)stream);
+}
+// gg_swiglu_q8_1: Q8_1 blocks of silu(x[i]) mul[i]: the tape op OP_GG_Q8_1 with work = 2 as one launch.
+// Reference: kernels/k3_gguf_ops.h:55-77 (semantics); python/caminus/engine/k3.py:649-659 (Engine.gg_q8_1(x, yq, mul=u)).
+extern "C" int gg_swiglu_q8_1(const float * x, const float * mul, void * y, long n, void * stream) {
+    return launch_q8<float, true>(x, mul, y, n, (cudaStream_t)stream);
+}
+// the same with fp16 gate and up (widened exactly to fp32 before the same statements)
+extern "C" int gg_swiglu_q8_1_f16(const void * g, const void * u, void * y, long n, void * stream) {
+    return launch_q8<uint16_t, true>((const uint16_t *)g, (const uint16_t *)u, y, n, (cudaStream_t)stream);
+}

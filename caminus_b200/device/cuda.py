@@ -1,0 +1,88 @@
+"""Launch the B200 glue kernels with the reference's loader interface.
+
+The reference loads a gfx1100 code object per module and launches `extern "C"` kernels through hipModuleLaunchKernel:
+    Module(name).<kernel>(grid, block, *args, shmem=0, stream=None)
+(python/caminus/device/hip.py:77-123), each argument a torch tensor (passed as its device pointer) or a ctypes scalar.
+This module gives the same two classes over libcaminus_b200.so, so the reference's op wrappers run on CUDA tensors by
+assigning `caminus.device.hip.Module = caminus_b200.device.cuda.Module` (and the by-name imports of its wrappers).
+
+What changes under the call: the AMD block shape is dropped (the kernels choose their own launch shape); where the
+reference carries a row or head count only in the launch grid, it is read from `grid` and passed as the C entry's leading
+argument; the module name selects the build variant the reference bakes into separate code objects (the YaRN RoPE).
+Errors: an unknown module raises FileNotFoundError as a missing code object does; a refused argument ValueError; a
+launch failure RuntimeError('CUDA error ...') (the reference: RuntimeError('HIP error ...'), device/hip.py:35-37).
+"""
+import ctypes
+
+from .. import lib as _lib
+
+# caminus.prefill.graph's recorder hook of the reference (device/hip.py:12-14): an object with intercept(...) / launched(...)
+RECORD = None
+LOADED = []    # module names this process asked for, in order (the reference's LOADED, device/hip.py:16)
+
+# kernel -> (C entry, how many leading counts come from the launch grid)
+_Q3M = {'q3p_emb': ('q3p_emb', 1), 'q3p_add_rms16': ('q3p_add_rms16', 1), 'q3p_swiglu': ('q3p_swiglu', 0),
+        'q3p_qk_rope': ('q3p_qk_rope', 1)}
+MODULES = {
+    'q3m_prefill': _Q3M,
+    'q3m_prefill_yarn': dict(_Q3M, q3p_qk_rope=('q3p_qk_rope_yarn', 1)),
+    'q35_prefill': {'q35p_add_rms16': ('q35p_add_rms16', 1)},
+    'k3_gguf': {'gg_quantize_q8_1': ('gg_quantize_q8_1', 0), 'gg_silu_mul': ('gg_silu_mul', 0)},
+    'k3_gguf_gsq': {'gg_quantize_q8_1': ('gg_quantize_q8_1', 0), 'gg_silu_mul': ('gg_silu_mul', 0)},
+}
+
+
+def check(err):
+    _lib.check(err)
+
+
+def _current_stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _arg(a):
+    if hasattr(a, 'data_ptr'):
+        if getattr(a, 'is_cuda', True) is False: raise ValueError('caminus_b200: a kernel argument is a CPU tensor')
+        return ctypes.c_void_p(a.data_ptr())
+    return a
+
+
+class Kernel:
+    def __init__(self, module, name, entry, ngrid):
+        self.module, self.name, self.entry, self.ngrid = module, name, entry, ngrid
+        self.fn = getattr(_lib.load(), entry)
+
+    def __call__(self, grid, block, *args, shmem=0, stream=None):
+        """args: torch tensors (passed as device pointers) or ctypes scalars (c_int, c_float, c_void_p(0) for null)"""
+        vals = [_arg(a) for a in args]
+        grid = (tuple(grid) + (1, 1))[:3]
+        s = _current_stream() if stream is None else stream
+        r = RECORD
+        if r is not None and r.intercept(self, grid, block, vals, shmem, s): return
+        if self.name == 'q3p_qk_rope':   # grid.y is the reference's nh + nkv: it must agree with the kernel's own arguments
+            nh, nkv = int(getattr(vals[2], 'value', vals[2])), int(getattr(vals[3], 'value', vals[3]))
+            if grid[1] != nh + nkv: raise ValueError(f'q3p_qk_rope: grid.y {grid[1]} is not nh + nkv = {nh + nkv}')
+        lead = [ctypes.c_int(int(grid[i])) for i in range(self.ngrid)]
+        _lib.check(self.fn(*lead, *vals, ctypes.c_void_p(s)), self.name)
+        if r is not None: r.launched(self, grid, block, vals, shmem, s)
+
+
+class Module:
+    """one of the reference's code objects by name, served by the entries of libcaminus_b200.so"""
+
+    def __init__(self, name):
+        if name not in MODULES:
+            raise FileNotFoundError(f'caminus_b200: no kernels for the code object {name!r} (have {", ".join(sorted(MODULES))}); '
+                                    f'library {_lib.path()}')
+        _lib.load()
+        self._name, self._fns = name, {}
+        if name not in LOADED: LOADED.append(name)
+
+    def __getattr__(self, name):
+        if name.startswith('_'): raise AttributeError(name)
+        if name not in self._fns:
+            spec = MODULES[self._name].get(name)
+            if spec is None: raise RuntimeError(f'CUDA error: the code object {self._name} has no kernel {name}')
+            self._fns[name] = Kernel(self._name, name, *spec)
+        return self._fns[name]

@@ -1,0 +1,48 @@
+"""Q8_1 activation quantiser and SwiGLU, with the reference's host functions (python/caminus/engine/gguf.py:39-61) plus the
+fused form the decode tape builds with Engine.gg_q8_1(x, yq, mul=u) (python/caminus/engine/k3.py:649-659)."""
+import ctypes
+
+import torch
+
+from ..device.cuda import Module
+from .. import lib as _lib
+
+Q8_1_BYTES = 36          # block_q8_1: half d, half sum, 32 int8
+_mod = {}
+
+
+def _m(module='k3_gguf'):
+    key = (torch.cuda.current_device(), module)
+    if key not in _mod: _mod[key] = Module(module)
+    return _mod[key]
+
+
+def quantize_q8_1(x):
+    """x fp32 [n] (cuda) -> q8_1 blocks (uint8 [ceil(n / 32) * 36]); values past n quantize as 0"""
+    n = x.numel(); nb = (n + 31) // 32
+    y = torch.empty(nb * Q8_1_BYTES, dtype=torch.uint8, device=x.device)
+    _m().gg_quantize_q8_1(((nb * 32 + 255) // 256,), (256,), x.contiguous(), y, ctypes.c_int(n))
+    return y
+
+
+def silu_mul(g, u):
+    """h = silu(g) * u in fp32"""
+    n = g.numel(); h = torch.empty_like(g)
+    _m('k3_gguf_gsq').gg_silu_mul(((n + 255) // 256,), (256,), g.contiguous(), u.contiguous(), h, ctypes.c_int(n))
+    return h
+
+
+def swiglu_q8_1(g, u, yq=None):
+    """q8_1 blocks of silu(g) * u in one launch; g, u both fp32 or both fp16 (cuda), same numel"""
+    if g.dtype != u.dtype or g.dtype not in (torch.float32, torch.float16) or g.numel() != u.numel() or g.device != u.device:
+        raise ValueError(f'swiglu_q8_1: gate {g.dtype} [{g.numel()}] and up {u.dtype} [{u.numel()}] (both fp32 or both fp16, one size)')
+    if not (g.is_contiguous() and u.is_contiguous()): raise ValueError('swiglu_q8_1: gate and up must be contiguous')
+    n = g.numel(); nb = (n + 31) // 32
+    if yq is None: yq = torch.empty(nb * Q8_1_BYTES, dtype=torch.uint8, device=g.device)
+    elif yq.dtype != torch.uint8 or yq.numel() < nb * Q8_1_BYTES or not yq.is_contiguous():
+        raise ValueError(f'swiglu_q8_1: yq needs {nb * Q8_1_BYTES} contiguous uint8')
+    fn = _lib.load().gg_swiglu_q8_1_f16 if g.dtype == torch.float16 else _lib.load().gg_swiglu_q8_1
+    with torch.cuda.device(g.device):
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(fn(g.data_ptr(), u.data_ptr(), yq.data_ptr(), n, s), 'gg_swiglu_q8_1')
+    return yq

@@ -1,0 +1,62 @@
+"""The glue part of the reference's launch wrappers for Qwen3-30B-A3B's batched prefill
+(python/caminus/prefill/q3m_ops.py:61-139: Ops.emb / add_rms16 / swiglu / qk_rope), same names, argument meaning and
+refusals, over the B200 kernels. The GEMM, router and attention methods of the reference's class are not part of this
+library (contractions and the scheduler are outside its path)."""
+import ctypes
+
+import torch
+
+from ..device import cuda as hip
+from ..engine import k3
+
+I, F = ctypes.c_int, ctypes.c_float
+NULL = ctypes.c_void_p(0)
+YARN_MODULE = {False: 'q3m_prefill_yarn'}
+YARN_PAR = 2 * 128 + 2 + k3.YARN_TABLE_FLOATS      # q_norm | k_norm | theta_scale, eps | freq [64] | mscale
+
+
+class Ops:
+    def __init__(self, dev, module='q3m_prefill', q8=False, yarn=False):
+        """yarn: the long-context mode: qk_rope reads the YaRN table after eps in par (YARN_PAR floats)"""
+        self.dev = torch.device(dev) if not isinstance(dev, torch.device) else dev
+        self.module, self.q8, self.yarn = module, bool(q8), bool(yarn)
+        if self.q8: raise ValueError('q3m Ops: the Q8_0 KV cache form is not built in this library')
+        if self.yarn and module != 'q3m_prefill': raise ValueError(f'q3m Ops: the long-context mode runs with q3m_prefill only (not {module})')
+        with torch.cuda.device(self.dev):
+            self.mod = hip.Module(module)
+            self.ropemod = hip.Module(YARN_MODULE[False]) if self.yarn else self.mod
+
+    # -- the glue ----------------------------------------------------------------------------------------------------------
+    def emb(self, W, rb, vocab, toks, x, n, N):
+        with torch.cuda.device(self.dev):
+            self.mod.q3p_emb((n,), (256,), W, I(rb), I(vocab), toks, x, I(N))
+
+    def add_rms16(self, x, nw, eps, h16, n, N, d=None, w=None, S=0, h=None):
+        if N % 256 or N > 2048: raise ValueError(f'q3m add_rms16: N {N} (a multiple of 256, <= 2048)')
+        with torch.cuda.device(self.dev):
+            self.mod.q3p_add_rms16((n,), (256,), x, NULL if d is None else d, NULL if w is None else w, I(S), nw, F(eps),
+                                   NULL if h is None else h, h16, I(N))
+
+    def swiglu(self, g, u, y16, n):
+        with torch.cuda.device(self.dev):
+            self.mod.q3p_swiglu((min(-(-n // 256), 4096),), (256,), g, u, y16, I(n))
+
+    def _span(self, what, cache, pos0, n, nkv, rows):
+        """positions pos0 .. pos0 + n - 1 must be among the cache's first `rows` positions (2 * nkv * 128 fp16 per row; None:
+        every row of the allocation), else k3.ContextBoundsError and nothing is launched"""
+        if n < 1 or nkv < 1: raise ValueError(f'q3m {what}: n {n}, nkv {nkv}')
+        if cache.dtype != torch.float16: raise ValueError(f'q3m {what}: a F16 prefill needs a {torch.float16} cache, not {cache.dtype}')
+        alloc = k3.kv_rows(cache, nkv * 128, False)
+        if rows is not None and not 0 <= int(rows) <= alloc: raise ValueError(f'q3m {what}: rows {rows} of a cache of {alloc}')
+        k3.check_span(pos0, n, alloc if rows is None else int(rows), what=f'q3m {what}')
+
+    def qk_rope(self, qkv, ldq, nh, nkv, par, pos0, q16, cache, n, rows=None, err=None):
+        self._span('qk_rope', cache, pos0, n, nkv, rows)
+        if ldq < (nh + 2 * nkv) * 128 or qkv.numel() < (n - 1) * ldq + (nh + 2 * nkv) * 128 or q16.numel() < n * nh * 128:
+            raise ValueError(f'q3m qk_rope: {n} tokens need qkv rows of {(nh + 2 * nkv) * 128} (stride {ldq}) and {n * nh * 128} q16')
+        if par.dtype != torch.float32 or par.numel() < (YARN_PAR if self.yarn else 2 * 128 + 2):
+            raise ValueError(f'q3m qk_rope: par needs {YARN_PAR if self.yarn else 2 * 128 + 2} fp32 values'
+                             f'{" (q_norm | k_norm | theta_scale, eps | the YaRN table)" if self.yarn else ""}, not {par.numel()} {par.dtype}')
+        if err is not None: raise ValueError('q3m qk_rope: err is the Q8 cache\'s word')
+        with torch.cuda.device(self.dev):
+            self.ropemod.q3p_qk_rope((n, nh + nkv), (128,), qkv, I(ldq), I(nh), I(nkv), par, I(pos0), q16, cache)

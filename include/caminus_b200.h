@@ -1,0 +1,105 @@
+/* caminus_b200: C ABI of the B200 (sm_100a) glue kernels: libcaminus_b200.so.
+ *
+ * Each entry replaces one `extern "C" __global__` kernel of the reference (jdominick05/caminus, HIP for gfx1100) and
+ * takes that kernel's parameters in the reference's order, device pointers as plain pointers. Where the reference conveys
+ * a row or head count only through the launch grid, the count is the explicit leading argument here. The last argument
+ * is the CUDA stream (a cudaStream_t passed as void *, 0 = the default stream). Nothing here allocates device memory;
+ * every buffer is the caller's and must stay alive until the stream has run the launch.
+ *
+ * Return value: 0 = launched; negative = the arguments were refused and nothing was launched (CAM_ERR_*);
+ * positive = a cudaError_t from the launch. cam_error_string() gives the text of any of them.
+ *
+ * Alignment: pointers to row data must be 16-byte aligned and row strides multiples of 16 bytes (128-bit accesses);
+ * an entry returns CAM_ERR_ALIGN otherwise. fp16 buffers are IEEE binary16 passed as void *.
+ *
+ * Arithmetic: every stored value is produced by IEEE-754 round-to-nearest operations in the order of the reference's
+ * statements (including its wave-butterfly summation order). expf, rsqrtf, powf and cosf / sinf of the reference's device
+ * library are explicit sequences of IEEE operations (csrc/cam_common.cuh), so results are reproducible bit for bit on a CPU.
+ */
+#ifndef CAMINUS_B200_H
+#define CAMINUS_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CAM_OK 0
+#define CAM_ERR_ARG (-1)
+#define CAM_ERR_ALIGN (-2)
+#define CAM_ERR_SHAPE (-3)
+#define CAM_ERR_CAPACITY (-4)
+
+/* Library. Replaces the loader half of runtime/rt.h:55-70 (rt::Module::load / fn / launch) and the error text of
+ * python/caminus/device/hip.py:35-37. */
+int cam_abi_version(void);
+const char * cam_error_string(int code);
+
+/* Q4_K embedding rows: x [n][N] fp32 = rows toks[i], clamped to [0, vocab), of the raw-block table W (rb bytes per row,
+ * 144-byte super-blocks of 256 values). Bitwise the host decoder own_dequant.q4_k.
+ * Replaces q3p_emb, kernels/q3m_prefill.hip:364-365 (n = grid.x); wrapper python/caminus/prefill/q3m_ops.py:86-87. */
+int q3p_emb(int n, const void * W, int rb, int vocab, const int * toks, float * x, int N, void * stream);
+
+/* Residual add + RMSNorm, Qwen3-MoE form: x [n][N] += sum over S slots of w[t][s] * d[t][s][:] (w null: plain sums; S = 0:
+ * no add); h (nullable) fp32 and h16 fp16 = (x * rsqrt(mean(x^2) + eps)) * nw. N a multiple of 256, <= 2048.
+ * Replaces q3p_add_rms16, kernels/q3m_prefill.hip:385-387 (n = grid.x); wrapper python/caminus/prefill/q3m_ops.py:89-92. */
+int q3p_add_rms16(int n, float * x, const float * d, const float * w, int S, const float * nw, float eps, float * h, void * h16,
+                  int N, void * stream);
+
+/* Residual add + RMSNorm, dense form: x [n][N] += d (d nullable); h fp32 and h16 fp16 always written; N = 256 k <= 65536.
+ * Replaces q35p_add_rms16, kernels/q35_prefill.hip:636-638 (n = grid.x); wrapper python/caminus/prefill/q35own.py:135-140. */
+int q35p_add_rms16(int n, float * x, const float * d, const float * nw, float eps, float * h, void * h16, int N, void * stream);
+
+/* The same statements on fp16 storage: x [n][N] fp16 (updated in place when d is given), d fp16 (nullable), h16 fp16.
+ * xs = (float)x + (float)d; x = fp16(xs); h16 = fp16((xs * rsqrt(mean(xs^2) + eps)) * nw).
+ * No kernel of this signature in the reference (its glue takes fp32 activations); arithmetic of
+ * kernels/q35_prefill.hip:636-660 between an exact fp16 load and a rounded fp16 store. */
+int cam_add_rms_f16(int n, void * x, const void * d, const float * nw, float eps, void * h16, int N, void * stream);
+
+/* Tensor-parallel RMSNorm, hidden dimension sharded (Ns columns of Nfull on this rank, Ns a multiple of 8).
+ * partial: ss [n] fp32 = this shard's sum of squares of xs = x + d (d nullable); nothing else is written.
+ * apply (after ss was summed over the ranks into tot): x = fp16(xs) when d is given; h16 = fp16((xs * rsqrt(tot / Nfull +
+ * eps)) * nw_shard). No counterpart in the reference, which replicates its norms on both cards
+ * (python/caminus/engine/q3moe_tp.py:18-20). */
+int cam_rms_partial_f16(int n, const void * x, const void * d, float * ss, int Ns, void * stream);
+int cam_rms_apply_f16(int n, void * x, const void * d, const float * tot, const float * nw, float eps, void * h16, int Ns,
+                      int Nfull, void * stream);
+
+/* y16[i] = fp16(silu(g[i]) * u[i]), i < n.
+ * Replaces q3p_swiglu, kernels/q3m_prefill.hip:516-518; wrapper python/caminus/prefill/q3m_ops.py:106-107. */
+int q3p_swiglu(const float * g, const float * u, void * y16, int n, void * stream);
+
+/* h[i] = silu(g[i]) * u[i] in fp32.
+ * Replaces gg_silu_mul, kernels/k3_gguf.hip:74-77; wrapper python/caminus/engine/gguf.py:57-61. */
+int gg_silu_mul(const float * g, const float * u, float * h, int n, void * stream);
+
+/* Q8_1 quantiser: n fp32 values -> ceil(n / 32) blocks of 36 bytes { fp16 d = amax / 127, fp16 sum, int8 qs[32] }; values
+ * past n quantise as 0. Writes exactly ceil(n / 32) blocks (the reference's launch pads to a multiple of 8 blocks).
+ * Replaces gg_quantize_q8_1, kernels/k3_gguf.hip:29-36; wrapper python/caminus/engine/gguf.py:39-46. */
+int gg_quantize_q8_1(const float * x, void * y, int n, void * stream);
+
+/* SwiGLU fused with the Q8_1 quantiser: blocks of silu(x[i]) * mul[i]. One launch for the reference's tape op OP_GG_Q8_1 with
+ * work = 2 (kernels/k3_gguf_ops.h:55-77; built by Engine.gg_q8_1(x, yq, mul=u), python/caminus/engine/k3.py:649-659).
+ * The _f16 form takes fp16 gate and up (widened exactly to fp32 first). */
+int gg_swiglu_q8_1(const float * x, const float * mul, void * y, long n, void * stream);
+int gg_swiglu_q8_1_f16(const void * g, const void * u, void * y, long n, void * stream);
+
+/* Per-head q/k RMSNorm + NeoX RoPE. qkv fp32 [n][ldq] = q (nh heads of 128) | k (nkv) | v (nkv); q16 fp16 [n][nh][128];
+ * cache fp16: row pos0 + t = K [nkv][128] | V [nkv][128] (V copied). par = q_norm[128] | k_norm[128] | theta_scale | eps
+ * (the _yarn entry, the reference's q3m_prefill_yarn object: then freq[64] | mscale). The caller checks that rows
+ * pos0 .. pos0 + n - 1 exist in the cache (the reference's wrapper does); pos0 + n <= 2^22.
+ * Replaces q3p_qk_rope, kernels/q3m_prefill.hip:537-538 (n = grid.x, nh + nkv = grid.y); wrapper
+ * python/caminus/prefill/q3m_ops.py:122-139. */
+int q3p_qk_rope(int n, const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, void * q16, void * cache,
+                void * stream);
+int q3p_qk_rope_yarn(int n, const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, void * q16, void * cache,
+                     void * stream);
+
+/* The same statements on fp16 q [n][nh][128] and k [n][nkv][128], fp16 out (qo / ko may alias q / k); yarn as above.
+ * No kernel of this signature in the reference; arithmetic of kernels/q3m_prefill.hip:552-590. */
+int cam_qk_rope_f16(int n, const void * q, const void * k, int nh, int nkv, const float * par, int pos0, void * qo, void * ko,
+                    int yarn, void * stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,288 @@
+"""Parity of the CUDA path (called through the C ABI / the reference-shaped wrappers) with the CPU oracle on the same
+seeded inputs: bit for bit for every stored byte, plus the reference's own tolerance against float64 where it states one."""
+import ctypes
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip('torch')
+pytestmark = pytest.mark.gpu
+
+import oracle   # noqa: E402
+from caminus_b200 import glue, synth   # noqa: E402
+from caminus_b200.engine import gguf, k3   # noqa: E402
+from caminus_b200.prefill import q3m_ops, q35own   # noqa: E402
+
+DEV = 'cuda:0'
+
+
+def cu(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def bits(a):
+    a = a.detach().cpu().numpy() if torch.is_tensor(a) else np.asarray(a)
+    return a.view({2: np.uint16, 4: np.uint32, 1: np.uint8}[a.dtype.itemsize]).reshape(-1)
+
+
+def same(a, b):
+    return np.array_equal(bits(a), bits(b))
+
+
+def ulp16(v):
+    return np.abs(np.spacing(np.abs(v).astype(np.float16))).astype(np.float64)
+
+
+@pytest.fixture(scope='module')
+def O():
+    return q3m_ops.Ops(DEV)
+
+
+# ---- Q4_K embedding rows ------------------------------------------------------------------------------------------------
+def test_emb_golden_bitwise(O, golden):
+    f = golden('q4k_rows')
+    W = f['W']; vocab = int(f['vocab']); rb = W.shape[1] * 144; N = W.shape[1] * 256; toks = f['toks']
+    x = torch.zeros(len(toks), N, device=DEV)
+    O.emb(cu(W.reshape(-1)), rb, vocab, cu(toks), x, len(toks), N)
+    assert same(x, f['want'])                                       # the reference decoder's bits, ids clamped
+
+
+@pytest.mark.parametrize('n,vocab,N', [(1, 7, 256), (33, 1000, 2048), (16384, 151936, 2048), (257, 300, 5120)])
+def test_emb_vs_oracle(O, n, vocab, N):
+    W = synth.q4k_table(vocab, N, seed=1); toks = synth.token_ids(n, vocab, seed=1)
+    if n > 8: toks[:4] = [-1, vocab, vocab - 1, 0]
+    x = torch.full((n, N), float('nan'), device=DEV)
+    O.emb(cu(W.reshape(-1)), N // 256 * 144, vocab, cu(toks), x, n, N)
+    assert same(x, oracle.q4k_get_rows(W, N // 256 * 144, vocab, toks, N))
+
+
+# ---- residual add + RMSNorm ---------------------------------------------------------------------------------------------
+def test_add_rms16_golden(O, golden):
+    f = golden('add_rms')
+    x0, dd, ww, nw = f['x0'], f['dd'], f['ww'], f['nw']; n, D = x0.shape
+    x = cu(x0); h = torch.zeros(n, D, device=DEV); h16 = torch.zeros(n, D, dtype=torch.float16, device=DEV)
+    O.add_rms16(x, cu(nw), 1e-6, h16, n, D, d=cu(dd), w=cu(ww), S=8, h=h)
+    xo, ho, h16o = oracle.add_rms16(x0, nw, 1e-6, d=dd, w=ww, S=8)
+    assert same(x, xo) and same(h, ho) and same(h16, h16o)
+    rel = lambda a, b: float(np.abs(a - b).max() / np.sqrt((b ** 2).mean()))
+    assert rel(x.cpu().numpy(), f['xr']) < 1e-6 and rel(h.cpu().numpy(), f['hr']) < 2e-6        # tests/prefill/test_q3m_ops.py:162
+    assert rel(h16.float().cpu().numpy(), f['hr']) < 2e-3
+    # BASELINE config 1: T = 1, hidden 2048, one added row
+    x = cu(f['x1']); h = torch.zeros(1, 2048, device=DEV); h16 = torch.zeros(1, 2048, dtype=torch.float16, device=DEV)
+    O.add_rms16(x, cu(f['w1']), 1e-6, h16, 1, 2048, d=cu(f['r1']), S=1, h=h)
+    xo, ho, h16o = oracle.add_rms16(f['x1'], f['w1'], 1e-6, d=f['r1'].reshape(1, 1, -1), S=1)
+    assert same(x, xo) and same(h, ho) and same(h16, h16o)
+    assert np.abs(h.cpu().numpy() - f['h1']).max() <= 1e-5 * np.abs(f['h1']).max()
+
+
+@pytest.mark.parametrize('N', [256, 512, 768, 1024, 1280, 1536, 1792, 2048])
+@pytest.mark.parametrize('S,weighted', [(0, False), (1, False), (3, True)])
+def test_add_rms16_shapes(O, N, S, weighted):
+    g = np.random.default_rng(N + S)
+    n = 37
+    x0 = (g.standard_normal((n, N)) * 3).astype(np.float32); nw = (g.random(N) + 0.5).astype(np.float32)
+    dd = g.standard_normal((n, max(S, 1), N)).astype(np.float32) if S else None
+    ww = g.random((n, S)).astype(np.float32) if weighted else None
+    x = cu(x0); h16 = torch.zeros(n, N, dtype=torch.float16, device=DEV); h = torch.zeros(n, N, device=DEV)
+    O.add_rms16(x, cu(nw), 1e-6, h16, n, N, d=None if dd is None else cu(dd), w=None if ww is None else cu(ww), S=S, h=h)
+    xo, ho, h16o = oracle.add_rms16(x0, nw, 1e-6, d=dd, w=ww, S=S)
+    assert same(x, xo) and same(h, ho) and same(h16, h16o)
+    # h omitted: the same h16
+    x = cu(x0); h16b = torch.zeros(n, N, dtype=torch.float16, device=DEV)
+    O.add_rms16(x, cu(nw), 1e-6, h16b, n, N, d=None if dd is None else cu(dd), w=None if ww is None else cu(ww), S=S)
+    assert same(h16b, h16o)
+
+
+@pytest.mark.parametrize('N', [256, 2048, 2560, 5120, 8192, 65536])
+@pytest.mark.parametrize('add', [True, False])
+def test_add_rms16_q35(N, add):
+    Q = q35own.Ops(DEV)
+    g = np.random.default_rng(N)
+    n = 9 if N > 8192 else 133
+    x0 = (g.standard_normal((n, N)) * 3).astype(np.float32); nw = (g.random(N) + 0.5).astype(np.float32)
+    dd = g.standard_normal((n, N)).astype(np.float32) if add else None
+    x = cu(x0); h = torch.zeros(n, N, device=DEV); h16 = torch.zeros(n, N, dtype=torch.float16, device=DEV)
+    Q.add_rms16(x, cu(nw), 1e-6, h16, n, N, d=None if dd is None else cu(dd), h=h)
+    xo, ho, h16o = oracle.add_rms16_q35(x0, nw, 1e-6, d=dd)
+    assert same(x, xo) and same(h, ho) and same(h16, h16o)
+    with pytest.raises(ValueError): Q.add_rms16(x, cu(nw), 1e-6, h16, n, N)          # h is required (q35own.py:139)
+
+
+@pytest.mark.parametrize('T,N', [(1, 2048), (5, 256), (777, 5120), (4096, 5120), (64, 8192), (3, 28672)])
+@pytest.mark.parametrize('add', [True, False])
+def test_add_rms_f16(T, N, add):
+    x0, r0, w = synth.add_rms_inputs(T, N, seed=T, dtype=np.float16)
+    x = cu(x0); h16 = torch.zeros(T, N, dtype=torch.float16, device=DEV)
+    glue.add_rms_f16(x, cu(w), 1e-6, h16=h16, d=cu(r0) if add else None)
+    xo, ho = oracle.add_rms_f16(x0, w, 1e-6, r0 if add else None)
+    assert same(x, xo) and same(h16, ho)
+    s = x0.astype(np.float64) + (r0.astype(np.float64) if add else 0)
+    ref = oracle.rms_f64(s, w, 1e-6)
+    assert (np.abs(h16.float().cpu().numpy() - ref) <= 2 * ulp16(ref) + 1e-5 * np.abs(ref).max()).all()   # 2 fp16 ulp / 1e-5
+
+
+# ---- SwiGLU and Q8_1 ------------------------------------------------------------------------------------------------------
+def test_q8_1_golden(golden):
+    f = golden('q8_1')
+    for x, dk, qk in ((f['x'], 'd16', 'q'), (f['x'][:int(f['n_odd'])], 'd16_odd', 'q_odd')):
+        y = gguf.quantize_q8_1(cu(x))
+        d, s, q = oracle.q8_split(y.cpu().numpy())
+        assert np.array_equal(q, f[qk]) and same(d, f[dk])                       # 0 mismatches (tests/engine/test_gguf_mv.py:33-45)
+        assert same(y, oracle.q8_1(x, sum_order=1))                              # every byte, the block sums included
+
+
+@pytest.mark.parametrize('dtype', [np.float16, np.float32])
+@pytest.mark.parametrize('n', [32, 64, 31, 1, 8 * 25600, 1000003])
+def test_swiglu_q8_1_vs_oracle(dtype, n):
+    g, u = synth.swiglu_inputs(1, n, seed=n, dtype=dtype)
+    g = g.reshape(-1); u = u.reshape(-1)
+    if n >= 64: g[:8] = np.array([30, -30, 0, -0.0, 1e-3, -88, 88, 3], dtype); u[32:64] = 0   # silu extremes; an all-zero block
+    y = gguf.swiglu_q8_1(cu(g), cu(u))
+    assert same(y, oracle.swiglu_q8_1(g, u, sum_order=1))
+    d, s, q = oracle.q8_split(y.cpu().numpy())
+    d0, s0, q0 = oracle.q8_split(oracle.swiglu_q8_1(g, u, sum_order=0))        # the lane-butterfly sum order: d, codes identical,
+    assert np.array_equal(q, q0) and same(d, d0)                                 # the sums within one fp16 ulp
+    assert (np.abs(s.astype(np.float64) - s0.astype(np.float64)) <= ulp16(s0.astype(np.float64)) + 1e-6).all()
+
+
+def test_swiglu_golden_reference_host_path(golden):
+    """against the reference's host path (numpy float32 silu, q8_host): the flip rule of tests/engine/golden_util.py:132-173"""
+    f = golden('swiglu')
+    y = gguf.swiglu_q8_1(cu(f['gate']), cu(f['up']))
+    d, s, q = oracle.q8_split(y.cpu().numpy())
+    dq = q.astype(np.int32) - f['q'].astype(np.int32)
+    assert np.abs(dq).max() <= 1 and (dq != 0).mean() < 1e-3
+    assert np.abs(d.view(np.int16).astype(np.int32) - f['d16'].view(np.int16).astype(np.int32)).max() <= 1
+    y16 = torch.zeros(5000, dtype=torch.float16, device=DEV)
+    q3m_ops.Ops(DEV).swiglu(cu(f['gg']), cu(f['uu']), y16, 5000)
+    assert np.abs(y16.float().cpu().numpy() - f['sr']).max() <= np.abs(f['sr']).max() * 2.0 ** -10    # test_q3m_ops.py:184-187
+    assert same(y16, oracle.swiglu16(f['gg'], f['uu']))
+    assert same(gguf.silu_mul(cu(f['gg']), cu(f['uu'])), oracle.silu_mul(f['gg'], f['uu']))
+
+
+def test_swiglu_q8_1_full_size_config():
+    """BASELINE config 3 (T = 8192, I = 25600): the whole output against the oracle on a strided sample of rows, and
+    size-independent properties of all of it: |q| <= 127, d >= 0, |x - d q| <= d / 2 up to fp16 rounding of d."""
+    T, I = 8192, 25600
+    g, u = synth.swiglu_inputs(T, I, seed=0)
+    gd, ud = cu(g), cu(u)
+    y = gguf.swiglu_q8_1(gd.reshape(-1), ud.reshape(-1))
+    yb = y.view(T, I // 32, 36)
+    rows = np.arange(0, T, 61)
+    want = oracle.swiglu_q8_1(g[rows].reshape(-1), u[rows].reshape(-1), sum_order=1).reshape(len(rows), I // 32, 36)
+    assert np.array_equal(yb[torch.from_numpy(rows).to(DEV)].cpu().numpy(), want)
+    qs = yb[:, :, 4:].contiguous().view(torch.int8)
+    assert int(qs.min()) >= -127 and int(qs.max()) <= 127
+    d = yb[:, :, 0:2].contiguous().view(torch.float16).float().squeeze(-1)
+    assert bool((d >= 0).all()) and bool((qs.abs().amax(-1) == 127)[d > 0].all())      # the largest value of a block codes to 127
+    y2 = gguf.swiglu_q8_1(gd.reshape(-1), ud.reshape(-1))
+    assert torch.equal(y, y2)                                                          # run to run identical
+
+
+# ---- q/k RMSNorm + RoPE -----------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize('yarn', [False, True])
+def test_qk_rope_golden(golden, yarn):
+    f = golden('qk_rope')
+    pos, nh, nkv, par, qkv = f['pos'], int(f['nh']), int(f['nkv']), f['par'], f['qkv']
+    M = nkv * 128; ldq = nh * 128 + 2 * M
+    R = q3m_ops.Ops(DEV, yarn=yarn)
+    pd = cu(par if yarn else par[:258])
+    for i, p in enumerate(int(v) for v in pos):
+        if p >= 5000: continue
+        cache0 = (np.random.default_rng(p).standard_normal((p + 3) * 2 * M) * 1.5).astype(np.float16)
+        cache = cu(cache0); q16 = torch.zeros(1, nh, 128, dtype=torch.float16, device=DEV)
+        R.qk_rope(cu(qkv[i]), ldq, nh, nkv, pd, p, q16, cache, 1)
+        qo, co = oracle.qk_rope(qkv[i], ldq, nh, nkv, par, p, cache0, 1, yarn=yarn)
+        assert same(q16, qo) and same(cache, co)                       # K | V row written, every other row untouched
+        ref = f['q_yarn' if yarn else 'q_plain'][i]
+        bound = ulp16(ref) + 1e-5 * np.abs(ref).max() + (0 if yarn else 2.0 ** -23 * p * np.abs(ref).max())
+        assert (np.abs(q16[0].float().cpu().numpy() - ref) <= bound).all()     # tests/engine/test_q3m_yarn_rope.py:132-135
+
+
+@pytest.mark.parametrize('n,nh,nkv,pos0', [(75, 32, 4, 1000), (1, 32, 4, 0), (130, 64, 8, 7), (19, 5, 1, 3), (40, 16, 2, 131000)])
+def test_qk_rope_chunk(O, n, nh, nkv, pos0):
+    """a chunk at pos0 as tests/prefill/test_q3m_ops.py:189-217 runs it, with a padded row stride"""
+    g = np.random.default_rng(n); M = nkv * 128; ldq = nh * 128 + 2 * M + 64; rows = 9 if pos0 > 100000 else pos0 + n + 2
+    base = pos0 if pos0 > 100000 else 0
+    par = synth.rope_par(seed=n)
+    qkv = (g.standard_normal((n, ldq)) * 3).astype(np.float32)
+    cache0 = (g.standard_normal((rows if base == 0 else n + 2) * 2 * M) * 1.5).astype(np.float16)
+    if base:   # a cache this large is not needed: check the positions with the fp16 entry instead
+        q = qkv[:, :nh * 128].astype(np.float16).reshape(n, nh, 128); k = qkv[:, nh * 128:nh * 128 + M].astype(np.float16).reshape(n, nkv, 128)
+        qo, ko = glue.qk_rope_f16(cu(q), cu(k), cu(par), pos0, qo=torch.zeros(n, nh, 128, dtype=torch.float16, device=DEV),
+                                  ko=torch.zeros(n, nkv, 128, dtype=torch.float16, device=DEV))
+        qr, kr = oracle.qk_rope_f16(q, k, par, pos0)
+        assert same(qo, qr) and same(ko, kr)
+        return
+    cache = cu(cache0); q16 = torch.zeros(n, nh, 128, dtype=torch.float16, device=DEV)
+    O.qk_rope(cu(qkv.reshape(-1)), ldq, nh, nkv, cu(par), pos0, q16, cache, n)
+    qo, co = oracle.qk_rope(qkv.reshape(-1), ldq, nh, nkv, par, pos0, cache0, n)
+    assert same(q16, qo) and same(cache, co)
+    assert np.array_equal(cache.cpu().numpy()[:pos0 * 2 * M], cache0[:pos0 * 2 * M])                 # rows below the chunk untouched
+    assert np.array_equal(cache.cpu().numpy().reshape(-1, 2, M)[pos0:pos0 + n, 1], qkv[:, nh * 128 + M:nh * 128 + 2 * M].astype(np.float16))
+
+
+@pytest.mark.parametrize('yarn', [False, True])
+def test_qk_rope_f16_config(yarn):
+    """BASELINE config 2: T = 4096, 32 q + 4 kv heads, positions 0 .. 4095; in place and out of place"""
+    T, nh, nkv = 4096, 32, 4
+    q, k = synth.qk_inputs(T, nh, nkv, seed=0)
+    par = synth.rope_par(seed=0, yarn_table=synth.yarn_table() if yarn else None)
+    qr, kr = oracle.qk_rope_f16(q, k, par, 0, yarn=yarn)
+    qd, kd = cu(q), cu(k)
+    qo, ko = glue.qk_rope_f16(qd, kd, cu(par), 0, qo=torch.empty_like(qd), ko=torch.empty_like(kd), yarn=yarn)
+    assert same(qo, qr) and same(ko, kr) and same(qd, q)
+    glue.qk_rope_f16(qd, kd, cu(par), 0, yarn=yarn)
+    assert same(qd, qr) and same(kd, kr)
+    # float64 on the kernel's fp32 angle: 1 fp16 ulp + 1e-5 max (tests/engine/test_q3m_yarn_rope.py:132-135), sampled tokens
+    for t in (0, 1, 63, 64, 1000, 4095):
+        fr = par[258:322] if yarn else np.array([oracle.powi(par[256], j) for j in range(64)], np.float32)
+        th = (np.float32(t) * fr).astype(np.float64)
+        ref = oracle.norm_rope_f64(q[t], par[:128], th, 1e-6, float(par[322]) if yarn else 1.0)
+        assert (np.abs(qr[t].astype(np.float64) - ref) <= ulp16(ref) + 1e-5 * np.abs(ref).max()).all()
+
+
+def test_qk_rope_refusals(O):
+    """a span outside the cache: refused on the host, nothing launched, buffers keep their bytes (test_q3m_ops.py:241-257)"""
+    nh, nkv, n = 32, 4, 75; M = nkv * 128; ctx = 1075
+    par = cu(synth.rope_par()); qkv = torch.randn(n * (nh * 128 + 2 * M), device=DEV)
+    cache = torch.randn(ctx * 2 * M, device=DEV).half(); q16 = torch.zeros(n, nh, 128, dtype=torch.float16, device=DEV)
+    keep = (cache.clone(), q16.clone())
+    for fn in (lambda: O.qk_rope(qkv, nh * 128 + 2 * M, nh, nkv, par, -1, q16, cache, n),
+               lambda: O.qk_rope(qkv, nh * 128 + 2 * M, nh, nkv, par, ctx - n + 1, q16, cache, n),
+               lambda: O.qk_rope(qkv, nh * 128 + 2 * M, nh, nkv, par, ctx - 64 - n + 1, q16, cache, n, rows=ctx - 64),
+               lambda: O.qk_rope(qkv, nh * 128 + 2 * M, nh, nkv, par, 1000.5, q16, cache, n)):
+        with pytest.raises(k3.ContextBoundsError): fn()
+    torch.cuda.synchronize()
+    assert torch.equal(cache, keep[0]) and torch.equal(q16, keep[1])
+    with pytest.raises(ValueError): O.qk_rope(qkv, nh * 128, nh, nkv, par, 0, q16, cache, n)              # row stride too short
+    with pytest.raises(ValueError): O.qk_rope(qkv, nh * 128 + 2 * M, nh, nkv, par[:200], 0, q16, cache, n)
+
+
+# ---- the loader interface -----------------------------------------------------------------------------------------------
+def test_module_interface():
+    from caminus_b200.device import cuda as hip
+    with pytest.raises(FileNotFoundError): hip.Module('no_such_object')
+    m = hip.Module('q3m_prefill')
+    with pytest.raises(RuntimeError): m.q3p_attn
+    x = torch.zeros(4, 256, device=DEV)
+    with pytest.raises(ValueError):   # a misaligned row pointer is refused, nothing is launched
+        m.q3p_emb((1,), (256,), torch.zeros(144, dtype=torch.uint8, device=DEV), ctypes.c_int(144), ctypes.c_int(1),
+                  torch.zeros(1, dtype=torch.int32, device=DEV), x.view(-1)[1:], ctypes.c_int(256))
+    with pytest.raises(ValueError):   # grid.y must be nh + nkv
+        m.q3p_qk_rope((1, 5), (128,), x, ctypes.c_int(768), ctypes.c_int(2), ctypes.c_int(2), x, ctypes.c_int(0), x, x)
+    assert 'q3m_prefill' in hip.LOADED
+
+
+def test_layer_glue_sequence():
+    """the per-layer order of BASELINE config 5 at a small T: each op's bytes are the oracle's"""
+    T, N, nh, nkv, I = 96, 5120, 64, 8, 25600
+    x0, r0, w = synth.add_rms_inputs(T, N, seed=5, dtype=np.float16)
+    q0, k0 = synth.qk_inputs(T, nh, nkv, seed=5); g0, u0 = synth.swiglu_inputs(T, I, seed=5); par = synth.rope_par(seed=5)
+    L = glue.LayerGlue(cu(w), cu(par))
+    x, q, k = cu(x0), cu(q0), cu(k0)
+    h16 = torch.empty_like(x); yq = torch.empty(T * I // 32 * 36, dtype=torch.uint8, device=DEV)
+    L(x, cu(r0), q, k, cu(g0), cu(u0), h16, yq, pos0=11)
+    xo, ho = oracle.add_rms_f16(x0, w, 1e-6, r0); qo, ko = oracle.qk_rope_f16(q0, k0, par, 11)
+    assert same(x, xo) and same(h16, ho) and same(q, qo) and same(k, ko)
+    assert same(yq, oracle.swiglu_q8_1(g0.reshape(-1), u0.reshape(-1), sum_order=1))
