@@ -152,14 +152,21 @@ template <int MODE>
 __global__ void __launch_bounds__(128) add_rms_f16_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d,
                                                           const float * __restrict__ nw, float eps, uint16_t * __restrict__ h16,
                                                           float * __restrict__ ss, const float * __restrict__ tot_in, int N, int Nfull,
-                                                          int n, int warps) {
+                                                          int n, int warps, int nw_smem) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nch = (N + 255) >> 8;                             // 16-byte chunks per lane per row and tensor (the last may be
     const int nd = d ? 2 : 1;                                   // short when N is not a multiple of 256: lanes past N add +0)
     const size_t half_bytes = (size_t)nch * 512;                // one tensor's row in a stage
     const size_t stage_bytes = (size_t)nd * half_bytes;
-    unsigned char * mine = smem + (size_t)warp * F16_STAGES * stage_bytes;
+    // the norm weights, staged once per block in front of the row stages when they fit (nw_smem floats; 0: read from global)
+    float * snw = reinterpret_cast<float *>(smem);
+    if (MODE != 1 && nw_smem) {
+        for (int i = threadIdx.x; i < N; i += blockDim.x) snw[i] = __ldg(nw + i);
+        __syncthreads();
+    }
+    const float * wsrc = (MODE != 1 && nw_smem) ? snw : nw;
+    unsigned char * mine = smem + (size_t)nw_smem * 4 + (size_t)warp * F16_STAGES * stage_bytes;
     const int stride = gridDim.x * warps;
     const int t0 = blockIdx.x * warps + warp;
 
@@ -223,7 +230,7 @@ __global__ void __launch_bounds__(128) add_rms_f16_kernel(uint16_t * __restrict_
                     for (int c = 0; c < 8; c++) xs[c] = fadd(xs[c], dv[c]);
                     st128(xr + i, make_uint4(f2_to_h2(xs[0], xs[1]), f2_to_h2(xs[2], xs[3]), f2_to_h2(xs[4], xs[5]), f2_to_h2(xs[6], xs[7])));
                 }
-                const float4 w0 = __ldg(reinterpret_cast<const float4 *>(nw + i)), w1 = __ldg(reinterpret_cast<const float4 *>(nw + i + 4));
+                const float4 w0 = *reinterpret_cast<const float4 *>(wsrc + i), w1 = *reinterpret_cast<const float4 *>(wsrc + i + 4);
                 float v[8];
                 v[0] = fmul(fmul(xs[0], scale), w0.x); v[1] = fmul(fmul(xs[1], scale), w0.y);
                 v[2] = fmul(fmul(xs[2], scale), w0.z); v[3] = fmul(fmul(xs[3], scale), w0.w);
@@ -241,32 +248,32 @@ int launch_f16(uint16_t * x, const uint16_t * d, const float * nw, float eps, ui
                int Nfull, int n, cudaStream_t stream) {
     if (n == 0) return CAM_OK;
     const size_t per_warp = (size_t)F16_STAGES * (d ? 2 : 1) * ((N + 255) >> 8) * 512;
+    const size_t budget = 226 * 1024;
+    int nw_smem = (MODE != 1 && (size_t)N * 4 + per_warp <= budget) ? N : 0;
     int warps = 4;
-    while (warps > 1 && per_warp * warps > 200 * 1024) warps >>= 1;
-    const size_t smem = per_warp * warps;
-    if (smem > 227 * 1024) return CAM_ERR_SHAPE;
+    while (warps > 1 && (size_t)nw_smem * 4 + per_warp * warps > budget) warps >>= 1;
+    if (n < 4 * warps) nw_smem = 0;                               // (a handful of rows: staging the weights costs more than it saves)
+    const size_t smem = (size_t)nw_smem * 4 + per_warp * warps;
+    if (smem > budget) return CAM_ERR_SHAPE;
     const cudaError_t e = cudaFuncSetAttribute(add_rms_f16_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
-    int per_sm = (int)((227 * 1024) / (smem + 1024));           // (1 KB per resident block is the system's)
-    per_sm = per_sm < 1 ? 1 : per_sm > 8 ? 8 : per_sm;
-    const long cap = (long)cam_sm_count() * per_sm;
-    const long want = ((long)n + warps - 1) / warps;
-    const int grid = (int)(want < cap ? want : cap);
-    add_rms_f16_kernel<MODE><<<grid, warps * 32, smem, stream>>>(x, d, nw, eps, h16, ss, tot, N, Nfull, n, warps);
+    const int grid = cam_resident_grid(add_rms_f16_kernel<MODE>, warps * 32, smem, ((long)n + warps - 1) / warps);
+    add_rms_f16_kernel<MODE><<<grid, warps * 32, smem, stream>>>(x, d, nw, eps, h16, ss, tot, N, Nfull, n, warps, nw_smem);
     return (int)cudaGetLastError();
 }
 
 int launch_f32(float * x, const float * d, const float * w, int S, const float * nw, float eps, float * h, uint16_t * h16, int N, int n,
                int q35, cudaStream_t stream) {
     if (n == 0) return CAM_OK;
-    const long cap = (long)cam_sm_count() * 4;
     const long want = ((long)n + RMS_WARPS - 1) / RMS_WARPS;
-    const int grid = (int)(want < cap ? want : cap);
-#define CAM_RMS_CASE(CHV) \
-    case CHV: add_rms_f32_kernel<CHV><<<grid, RMS_WARPS * 32, 0, stream>>>(x, d, w, S, nw, eps, h, h16, N, n, q35); break;
+#define CAM_RMS_CASE(CHV)                                                                                              \
+    case CHV:                                                                                                          \
+        add_rms_f32_kernel<CHV><<<cam_resident_grid(add_rms_f32_kernel<CHV>, RMS_WARPS * 32, 0, want), RMS_WARPS * 32, 0, stream>>>( \
+            x, d, w, S, nw, eps, h, h16, N, n, q35);                                                                   \
+        break;
     switch (N <= 2048 ? N >> 7 : 0) {
         CAM_RMS_CASE(2) CAM_RMS_CASE(4) CAM_RMS_CASE(6) CAM_RMS_CASE(8) CAM_RMS_CASE(10) CAM_RMS_CASE(12) CAM_RMS_CASE(14) CAM_RMS_CASE(16)
-        default: add_rms_f32_kernel<0><<<grid, RMS_WARPS * 32, 0, stream>>>(x, d, w, S, nw, eps, h, h16, N, n, q35); break;
+        CAM_RMS_CASE(0)
     }
 #undef CAM_RMS_CASE
     return (int)cudaGetLastError();

@@ -105,3 +105,13 @@ static inline bool cam_aligned16(const void * p) { return (reinterpret_cast<uint
 
 // multiprocessors of the current device (cached per device)
 int cam_sm_count();
+
+// A persistent grid: as many blocks as the device holds at once (so that no block waits for another to finish), capped by
+// the work. `want` = blocks that would each get one unit of work.
+template <typename K>
+static inline int cam_resident_grid(K kernel, int threads, size_t smem, long want) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+    const long cap = (long)cam_sm_count() * per_sm;
+    return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
+}

@@ -62,8 +62,7 @@ extern "C" int q3p_emb(int n, const void * W, int rb, int vocab, const int * tok
     if (!cam_aligned16(W) || (rb & 15) || !cam_aligned16(x) || (reinterpret_cast<uintptr_t>(toks) & 3u)) return CAM_ERR_ALIGN;
     const long total = (long)n * (N >> 8);
     const long want = (total + EMB_WARPS - 1) / EMB_WARPS;
-    const long cap = (long)cam_sm_count() * 8;           // 8 resident blocks of 256 threads per multiprocessor
-    const int grid = (int)(want < cap ? want : cap);
+    const int grid = cam_resident_grid(emb_q4k_kernel, EMB_WARPS * 32, 0, want);
     emb_q4k_kernel<<<grid, EMB_WARPS * 32, 0, (cudaStream_t)stream>>>((const uint8_t *)W, rb, vocab, toks, x, N, n);
     return (int)cudaGetLastError();
 }

@@ -177,12 +177,7 @@ int launch_rope(const RopeArgs & A, cudaStream_t stream) {
     const cudaError_t e = cudaFuncSetAttribute(qk_rope_kernel<T, CACHE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
     const int warps = pick_warps(H);
-    int per_sm = (int)((227 * 1024) / (smem + 1024));
-    const int by_threads = 2048 / (warps * 32);
-    per_sm = per_sm > by_threads ? by_threads : per_sm;
-    per_sm = per_sm < 1 ? 1 : per_sm;
-    const long cap = (long)cam_sm_count() * per_sm;
-    const int grid = (int)((long)A.n < cap ? (long)A.n : cap);
+    const int grid = cam_resident_grid(qk_rope_kernel<T, CACHE>, warps * 32, smem, A.n);
     qk_rope_kernel<T, CACHE><<<grid, warps * 32, smem, stream>>>(A);
     return (int)cudaGetLastError();
 }

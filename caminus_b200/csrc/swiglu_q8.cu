@@ -88,6 +88,104 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_1_kernel(const T * __restrict__
     }
 }
 
+// ---- the fused SwiGLU + Q8_1 kernel: a fast pass with proof margins, exact recomputation where a margin is not met --------
+//
+// The exact statements (cam_silu: a 12-operation exp, two IEEE divisions per value) cost about twice the instructions the
+// memory system leaves time for. The fast pass therefore evaluates h^ = g * rcp(1 + ex2(-g log2 e)) * u on the
+// special-function unit and quantises with a reciprocal, which is NOT bit-reproducible by itself. It is used only where it
+// provably gives the exact statements' bytes. With h the exact value of an element, |h^ - h| <= EPS |h|, EPS = 1.35e-6,
+// whenever g >= -8: against the true value the fast pass is within 1.02e-6 (the rounding of ex2's argument, 6e-8 |g|, and
+// ex2.approx's 2^-22, both scaled by e / (1 + e) <= 1; the rounding of 1 + e; rcp.approx's 2^-23; two products) and the exact
+// sequence within 3.2e-7 (2.2 ulp measured over the whole range, and its product). From that:
+//   d:     d^ = amax^ / 127 is within 1.53e-6 (< 26 fp32 ulps) of the exact fp32 d. If d^'s low 13 bits are more than 40 away
+//          from the fp16 rounding tie (0x1000) and d^ is in fp16's normal range, fp16(d^) = fp16(d): the stored scale is exact.
+//   codes: t^ = h^ / d^ is within 3.06e-6 |t| <= 3.9e-4 of the exact fp32 quotient. If t^ is more than 4.5e-4 away from every
+//          half-integer, round-to-nearest of t^ is the exact code (roundf of the exact quotient): no tie and no boundary
+//          lies between them.
+// A block (32 values) where any of this fails: some g < -8, a quotient within 4.5e-4 of a rounding boundary, d^ near an fp16
+// tie or outside [6.2e-5, 6e4), a sum that is not finite (NaN or infinite input): is recomputed by the whole warp with
+// the exact statements, one lane per value. About 4 % of the blocks of Gaussian inputs take that path.
+// The stored scale d and the 32 codes are therefore always the exact statements' bytes. The block sum of a block on the
+// fast pass is the fp16 rounding of the same-order sum of the h^: it can differ from the exact statements' sum by one fp16
+// ulp (or by 1.6e-6 sum |h| when the values cancel). The reference reports that field and does not gate it
+// (tests/engine/golden_util.py:145-146); the strict kernel above gives its exact bytes too.
+CAM_DEV float ex2_approx(float a) { float r; asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
+CAM_DEV float rcp_approx(float a) { float r; asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
+
+template <typename T>
+__global__ void __launch_bounds__(Q8_THREADS) swiglu_q8_fast_kernel(const T * __restrict__ g, const T * __restrict__ u,
+                                                                    uint8_t * __restrict__ y, long nb) {
+    const int lane = threadIdx.x & 31, q = lane & 3;
+    const long ngroups = nb * 4;
+    const long stride = (long)gridDim.x * Q8_THREADS;
+    for (long base = (long)blockIdx.x * Q8_THREADS + (threadIdx.x & ~31); base < ngroups; base += stride) {
+        const long gi = base + lane;
+        const bool on = gi < ngroups;
+        float gv[8], uv[8], h[8];
+        if (on) { Load8<T>::get(g + gi * 8, gv); Load8<T>::get(u + gi * 8, uv); }
+        else {
+#pragma unroll
+            for (int k = 0; k < 8; k++) { gv[k] = 0.0f; uv[k] = 0.0f; }
+        }
+        float gmin = gv[0], amax = 0.0f;
+#pragma unroll
+        for (int k = 1; k < 8; k++) gmin = fminf(gmin, gv[k]);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const float e = ex2_approx(fmul(gv[k], -0x1.715476p+0f));
+            h[k] = fmul(fmul(gv[k], rcp_approx(fadd(1.0f, e))), uv[k]);
+            amax = fmaxf(amax, fabsf(h[k]));
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 2));
+        float sa = fadd(fadd(h[0], h[1]), fadd(h[2], h[3])), sb = fadd(fadd(h[4], h[5]), fadd(h[6], h[7]));
+        sa = fadd(sa, __shfl_xor_sync(CAM_FULL, sa, 2)); sb = fadd(sb, __shfl_xor_sync(CAM_FULL, sb, 2));
+        sa = fadd(sa, __shfl_xor_sync(CAM_FULL, sa, 1)); sb = fadd(sb, __shfl_xor_sync(CAM_FULL, sb, 1));
+        const float sum = fadd(sa, sb);
+        const float d = fmul(amax, 0x1.020408p-7f);                         // amax / 127 within 1.2e-7
+        const float inv = rcp_approx(d);
+        const int low = (int)(__float_as_uint(d) & 0x1fffu) - 0x1000;
+        bool redo = !(gmin >= -8.0f) || !(d >= 6.2e-5f && d < 6.0e4f) || (low >= -40 && low <= 40) || !(fabsf(sum) < 3.0e38f);
+        float fmax_ = 0.0f;
+        uint32_t v[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const float t = ffma(h[k], inv, 12582912.0f);                    // the quotient rounded to an integer (ties to even)
+            const float f = ffma(h[k], inv, -fsub(t, 12582912.0f));          // its distance from that integer
+            fmax_ = fmaxf(fmax_, fabsf(f));
+            v[k] = __float_as_uint(t);                                       // the integer sits in the low mantissa bits
+        }
+        redo = redo || !(fmax_ < 0.49955f);
+        const uint32_t mask = __ballot_sync(CAM_FULL, redo && on);
+        const uint32_t quad = (mask | (mask >> 1) | (mask >> 2) | (mask >> 3)) & 0x11111111u;   // bit 4 j: block j of this warp
+        if (on && !((quad >> (lane & ~3)) & 1u)) {
+            const uint32_t w0 = __byte_perm(__byte_perm(v[0], v[1], 0x0040), __byte_perm(v[2], v[3], 0x0040), 0x5410);
+            const uint32_t w1 = __byte_perm(__byte_perm(v[4], v[5], 0x0040), __byte_perm(v[6], v[7], 0x0040), 0x5410);
+            uint32_t * o = reinterpret_cast<uint32_t *>(y + (gi >> 2) * 36);
+            if (q == 0) __stcs(o, f2_to_h2(d, sum));
+            __stcs(o + 1 + 2 * q, w0);
+            __stcs(o + 2 + 2 * q, w1);
+        }
+        // exact recomputation of the flagged blocks: the whole warp, one lane per value (uniform: quad is the same in every lane)
+        for (uint32_t m = quad; m; m &= m - 1) {
+            const long blk = (base >> 2) + ((__ffs(m) - 1) >> 2);
+            const float x = fmul(cam_silu(Load8<T>::one(g + blk * 32 + lane)), Load8<T>::one(u + blk * 32 + lane));
+            float am = fabsf(x);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(CAM_FULL, am, o));
+            float s = fadd(x, __shfl_xor_sync(CAM_FULL, x, 1));
+            s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 2));
+            s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 16));
+            s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 8));
+            s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 4));
+            const float de = fdiv(am, 127.0f);
+            uint8_t * o = y + blk * 36;
+            o[4 + lane] = (uint8_t)q8_code(x, de, am);
+            if (lane == 0) *reinterpret_cast<uint32_t *>(o) = f2_to_h2(de, s);
+        }
+    }
+}
+
 // the last, partial block (n % 32 values, the rest 0): one warp, one lane per value
 template <typename T, bool SWIGLU>
 __global__ void __launch_bounds__(32) q8_1_tail_kernel(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y,
@@ -112,7 +210,8 @@ __global__ void __launch_bounds__(32) q8_1_tail_kernel(const T * __restrict__ g,
     if (lane == 0) *reinterpret_cast<uint32_t *>(o) = f2_to_h2(d, s);
 }
 
-template <typename T, bool SWIGLU>
+// FAST: the two-pass fused kernel (SwiGLU only); otherwise the exact statements for every value
+template <typename T, bool SWIGLU, bool FAST = false>
 int launch_q8(const T * g, const T * u, void * y, long n, cudaStream_t stream) {
     if (n < 0 || !g || !y || (SWIGLU && !u)) return CAM_ERR_ARG;
     if (n == 0) return CAM_OK;
@@ -120,8 +219,8 @@ int launch_q8(const T * g, const T * u, void * y, long n, cudaStream_t stream) {
     const long nb = n >> 5;
     if (nb > 0) {
         const long want = (nb * 4 + Q8_THREADS - 1) / Q8_THREADS;
-        const long cap = (long)cam_sm_count() * 8;
-        q8_1_kernel<T, SWIGLU><<<(int)(want < cap ? want : cap), Q8_THREADS, 0, stream>>>(g, u, (uint8_t *)y, nb);
+        if (FAST) swiglu_q8_fast_kernel<T><<<cam_resident_grid(swiglu_q8_fast_kernel<T>, Q8_THREADS, 0, want), Q8_THREADS, 0, stream>>>(g, u, (uint8_t *)y, nb);
+        else q8_1_kernel<T, SWIGLU><<<cam_resident_grid(q8_1_kernel<T, SWIGLU>, Q8_THREADS, 0, want), Q8_THREADS, 0, stream>>>(g, u, (uint8_t *)y, nb);
     }
     if (n & 31) q8_1_tail_kernel<T, SWIGLU><<<1, 32, 0, stream>>>(g, u, (uint8_t *)y, nb << 5, (int)(n & 31));
     return (int)cudaGetLastError();
@@ -152,8 +251,7 @@ int launch_silu_mul(const float * g, const float * u, void * y, long n, cudaStre
     if (n == 0) return CAM_OK;
     const int vec = cam_aligned16(g) && cam_aligned16(u) && cam_aligned16(y);
     const long want = ((vec ? (n + 3) / 4 : n) + 255) / 256;
-    const long cap = (long)cam_sm_count() * 8;
-    silu_mul_kernel<HALF_OUT><<<(int)(want < cap ? want : cap), 256, 0, stream>>>(g, u, y, n, vec);
+    silu_mul_kernel<HALF_OUT><<<cam_resident_grid(silu_mul_kernel<HALF_OUT>, 256, 0, want), 256, 0, stream>>>(g, u, y, n, vec);
     return (int)cudaGetLastError();
 }
 
@@ -176,9 +274,17 @@ extern "C" int gg_quantize_q8_1(const float * x, void * y, int n, void * stream)
 // gg_swiglu_q8_1: Q8_1 blocks of silu(x[i]) mul[i]: the tape op OP_GG_Q8_1 with work = 2 as one launch.
 // Reference: kernels/k3_gguf_ops.h:55-77 (semantics); python/caminus/engine/k3.py:649-659 (Engine.gg_q8_1(x, yq, mul=u)).
 extern "C" int gg_swiglu_q8_1(const float * x, const float * mul, void * y, long n, void * stream) {
-    return launch_q8<float, true>(x, mul, y, n, (cudaStream_t)stream);
+    return launch_q8<float, true, true>(x, mul, y, n, (cudaStream_t)stream);
 }
 // the same with fp16 gate and up (widened exactly to fp32 before the same statements)
 extern "C" int gg_swiglu_q8_1_f16(const void * g, const void * u, void * y, long n, void * stream) {
+    return launch_q8<uint16_t, true, true>((const uint16_t *)g, (const uint16_t *)u, y, n, (cudaStream_t)stream);
+}
+// The strict forms: every value through the exact statements, so the block sums are the exact statements' bytes as well as
+// d and the codes (which the entries above already guarantee). About half the throughput.
+extern "C" int gg_swiglu_q8_1_strict(const float * x, const float * mul, void * y, long n, void * stream) {
+    return launch_q8<float, true>(x, mul, y, n, (cudaStream_t)stream);
+}
+extern "C" int gg_swiglu_q8_1_f16_strict(const void * g, const void * u, void * y, long n, void * stream) {
     return launch_q8<uint16_t, true>((const uint16_t *)g, (const uint16_t *)u, y, n, (cudaStream_t)stream);
 }

@@ -26,6 +26,8 @@ SIGNATURES = {
     'gg_quantize_q8_1': [P, P, I, P],
     'gg_swiglu_q8_1': [P, P, P, L, P],
     'gg_swiglu_q8_1_f16': [P, P, P, L, P],
+    'gg_swiglu_q8_1_strict': [P, P, P, L, P],
+    'gg_swiglu_q8_1_f16_strict': [P, P, P, L, P],
     'q3p_qk_rope': [I, P, I, I, I, P, I, P, P, P],
     'q3p_qk_rope_yarn': [I, P, I, I, I, P, I, P, P, P],
     'cam_qk_rope_f16': [I, P, P, I, I, P, I, P, P, I, P],

@@ -79,9 +79,15 @@ int gg_quantize_q8_1(const float * x, void * y, int n, void * stream);
 
 /* SwiGLU fused with the Q8_1 quantiser: blocks of silu(x[i]) * mul[i]. One launch for the reference's tape op OP_GG_Q8_1 with
  * work = 2 (kernels/k3_gguf_ops.h:55-77; built by Engine.gg_q8_1(x, yq, mul=u), python/caminus/engine/k3.py:649-659).
- * The _f16 form takes fp16 gate and up (widened exactly to fp32 first). */
+ * The _f16 form takes fp16 gate and up (widened exactly to fp32 first).
+ * d and the 32 codes of every block are the bytes of the exact statements (a fast pass is used only where that is proven,
+ * the rest is recomputed exactly: csrc/swiglu_q8.cu). The block sum may differ from the exact statements' by one fp16 ulp; the
+ * reference reports that field and does not gate it (tests/engine/golden_util.py:145-146). The _strict forms run the exact
+ * statements for every value (the sums are exact too) at about half the throughput. */
 int gg_swiglu_q8_1(const float * x, const float * mul, void * y, long n, void * stream);
 int gg_swiglu_q8_1_f16(const void * g, const void * u, void * y, long n, void * stream);
+int gg_swiglu_q8_1_strict(const float * x, const float * mul, void * y, long n, void * stream);
+int gg_swiglu_q8_1_f16_strict(const void * g, const void * u, void * y, long n, void * stream);
 
 /* Per-head q/k RMSNorm + NeoX RoPE. qkv fp32 [n][ldq] = q (nh heads of 128) | k (nkv) | v (nkv); q16 fp16 [n][nh][128];
  * cache fp16: row pos0 + t = K [nkv][128] | V [nkv][128] (V copied). par = q_norm[128] | k_norm[128] | theta_scale | eps

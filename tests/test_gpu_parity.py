@@ -131,18 +131,54 @@ def test_q8_1_golden(golden):
         assert same(y, oracle.q8_1(x, sum_order=1))                              # every byte, the block sums included
 
 
+def sums_close(y, want, h):
+    """the block sums of the fast pass: within one fp16 ulp of the exact statements' sum, or 2e-6 sum |h| when the values cancel"""
+    _, s, _ = oracle.q8_split(y); _, s0, _ = oracle.q8_split(want)
+    n = h.size; hp = np.zeros((n + 31) // 32 * 32); hp[:n] = np.abs(h.astype(np.float64))
+    tol = ulp16(s0.astype(np.float64)) + 2e-6 * hp.reshape(-1, 32).sum(1)
+    return bool((np.abs(s.astype(np.float64) - s0.astype(np.float64)) <= tol).all())
+
+
 @pytest.mark.parametrize('dtype', [np.float16, np.float32])
 @pytest.mark.parametrize('n', [32, 64, 31, 1, 8 * 25600, 1000003])
 def test_swiglu_q8_1_vs_oracle(dtype, n):
     g, u = synth.swiglu_inputs(1, n, seed=n, dtype=dtype)
     g = g.reshape(-1); u = u.reshape(-1)
     if n >= 64: g[:8] = np.array([30, -30, 0, -0.0, 1e-3, -88, 88, 3], dtype); u[32:64] = 0   # silu extremes; an all-zero block
-    y = gguf.swiglu_q8_1(cu(g), cu(u))
-    assert same(y, oracle.swiglu_q8_1(g, u, sum_order=1))
-    d, s, q = oracle.q8_split(y.cpu().numpy())
+    want = oracle.swiglu_q8_1(g, u, sum_order=1)
+    ys = gguf.swiglu_q8_1(cu(g), cu(u), strict=True)
+    assert same(ys, want)                                                        # strict: every byte
+    y = gguf.swiglu_q8_1(cu(g), cu(u)).cpu().numpy()
+    d, s, q = oracle.q8_split(y); d1, s1, q1 = oracle.q8_split(want)
+    assert np.array_equal(q, q1) and same(d, d1)                                 # the fused kernel: d and codes exact, always
+    h = oracle.swiglu_f32_from_f16(g, u) if dtype == np.float16 else oracle.silu_mul(g, u)
+    assert sums_close(y, want, h)
     d0, s0, q0 = oracle.q8_split(oracle.swiglu_q8_1(g, u, sum_order=0))        # the lane-butterfly sum order: d, codes identical,
     assert np.array_equal(q, q0) and same(d, d0)                                 # the sums within one fp16 ulp
-    assert (np.abs(s.astype(np.float64) - s0.astype(np.float64)) <= ulp16(s0.astype(np.float64)) + 1e-6).all()
+    assert (np.abs(s1.astype(np.float64) - s0.astype(np.float64)) <= ulp16(s0.astype(np.float64)) + 1e-6).all()
+
+
+@pytest.mark.parametrize('kind', ['wide_gate', 'outliers', 'tiny', 'huge', 'negative_gate', 'nonfinite', 'ties'])
+def test_swiglu_q8_1_hard_inputs(kind):
+    """inputs that stress the fast pass's margins: the fused kernel's d and codes stay the exact statements' bytes"""
+    g_ = np.random.default_rng(sum(map(ord, kind)))
+    n = 1 << 20
+    gate = (g_.standard_normal(n) * 1.5).astype(np.float32); up = (g_.standard_normal(n) * 1.5).astype(np.float32)
+    if kind == 'wide_gate': gate *= 4                                            # tests/prefill/test_q3m_ops.py:184
+    if kind == 'outliers': m = g_.random(n) < 0.002; gate[m] *= 30; up[m] *= 30   # tests/prefill/test_prefill_glue.py:125-128
+    if kind == 'tiny': gate *= 1e-3; up *= 1e-4
+    if kind == 'huge': up *= 1e3
+    if kind == 'negative_gate': gate = -np.abs(gate) * 3
+    if kind == 'ties': gate = np.round(gate * 2) / 2; up = np.round(up * 4) / 4   # few distinct values: exact .5 quotients occur
+    gate = gate.astype(np.float16); up = up.astype(np.float16)
+    if kind == 'nonfinite':
+        gate[5] = np.inf; up[100] = np.nan; gate[200] = -np.inf; up[300] = np.inf; gate[400] = np.nan
+    want = oracle.swiglu_q8_1(gate, up, sum_order=1)
+    y = gguf.swiglu_q8_1(cu(gate), cu(up)).cpu().numpy()
+    d, s, q = oracle.q8_split(y); d1, s1, q1 = oracle.q8_split(want)
+    ok = ~(np.isnan(d1.astype(np.float32)))                                      # (a NaN scale has no fixed bit pattern)
+    assert np.array_equal(q, q1) and np.array_equal(d.view(np.uint16)[ok], d1.view(np.uint16)[ok]) and np.isnan(d.astype(np.float32)[~ok]).all()
+    if kind != 'nonfinite': assert sums_close(y, want, oracle.swiglu_f32_from_f16(gate, up))
 
 
 def test_swiglu_golden_reference_host_path(golden):
@@ -167,10 +203,15 @@ def test_swiglu_q8_1_full_size_config():
     g, u = synth.swiglu_inputs(T, I, seed=0)
     gd, ud = cu(g), cu(u)
     y = gguf.swiglu_q8_1(gd.reshape(-1), ud.reshape(-1))
-    yb = y.view(T, I // 32, 36)
+    ystrict = gguf.swiglu_q8_1(gd.reshape(-1), ud.reshape(-1), strict=True)
+    yb, ysb = y.view(T, I // 32, 36), ystrict.view(T, I // 32, 36)
     rows = np.arange(0, T, 61)
     want = oracle.swiglu_q8_1(g[rows].reshape(-1), u[rows].reshape(-1), sum_order=1).reshape(len(rows), I // 32, 36)
-    assert np.array_equal(yb[torch.from_numpy(rows).to(DEV)].cpu().numpy(), want)
+    assert np.array_equal(ysb[torch.from_numpy(rows).to(DEV)].cpu().numpy(), want)     # the exact statements: the oracle's bytes
+    # the fused kernel against the exact statements over ALL 6.5 M blocks: d and the 32 codes identical, sums within one fp16 ulp
+    assert torch.equal(yb[:, :, 0:2], ysb[:, :, 0:2]) and torch.equal(yb[:, :, 4:], ysb[:, :, 4:])
+    sf, ss_ = yb[:, :, 2:4].contiguous().view(torch.float16).float(), ysb[:, :, 2:4].contiguous().view(torch.float16).float()
+    assert bool(((sf - ss_).abs() <= ss_.abs() * 2.0 ** -10 + 1e-3).all())
     qs = yb[:, :, 4:].contiguous().view(torch.int8)
     assert int(qs.min()) >= -127 and int(qs.max()) <= 127
     d = yb[:, :, 0:2].contiguous().view(torch.float16).float().squeeze(-1)
@@ -285,4 +326,5 @@ def test_layer_glue_sequence():
     L(x, cu(r0), q, k, cu(g0), cu(u0), h16, yq, pos0=11)
     xo, ho = oracle.add_rms_f16(x0, w, 1e-6, r0); qo, ko = oracle.qk_rope_f16(q0, k0, par, 11)
     assert same(x, xo) and same(h16, ho) and same(q, qo) and same(k, ko)
-    assert same(yq, oracle.swiglu_q8_1(g0.reshape(-1), u0.reshape(-1), sum_order=1))
+    d, s, q_ = oracle.q8_split(yq.cpu().numpy()); d1, s1, q1 = oracle.q8_split(oracle.swiglu_q8_1(g0.reshape(-1), u0.reshape(-1), sum_order=1))
+    assert same(d, d1) and np.array_equal(q_, q1)
