@@ -171,6 +171,8 @@ def main():
     ap.add_argument('--rows', type=int, default=T_PER_GPU, help='token rows per GPU (the configured workload is 65536)')
     ap.add_argument('--ops', action='store_true', help='also time the single-op configs 1-4 on rank 0')
     ap.add_argument('--cpu-sample', type=int, default=512)
+    ap.add_argument('--skip-e2e', action='store_true', help='leave out the host-buffer leg (profiling runs)')
+    ap.add_argument('--skip-cpu', action='store_true', help='leave out the CPU baseline leg (profiling runs)')
     ap.add_argument('--e2e-rows', type=int, default=16384, help='token rows per GPU of the host-buffer leg (pinned host memory: 209 KB per row)')
     args = ap.parse_args()
     rank, world, local = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1)), int(os.environ.get('LOCAL_RANK', 0))
@@ -226,19 +228,23 @@ def main():
     # end to end through host buffers (pinned): inputs copied in, the three launches, outputs copied back, every step
     from caminus_b200 import host
     Te = min(T, args.e2e_rows)
-    Hrun = host.HostLayerGlue(Te, HIDDEN, NH, NKV, INTER, nw, par, dev)
-    Hrun.fill_from(x, resid, q, k, gate, up)
-    del gate, up, yq, h16, x, q, k, resid
-    torch.cuda.empty_cache()
-    for _ in range(2): Hrun.run()
-    barrier()
-    e2e_steps = max(2, min(args.steps, 5))
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps): Hrun.run()
-    barrier()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_s], device=dev, dtype=torch.float64); torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX); e2e_s = float(t.item())
+    e2e = None
+    if not args.skip_e2e:
+        Hrun = host.HostLayerGlue(Te, HIDDEN, NH, NKV, INTER, nw, par, dev)
+        Hrun.fill_from(x, resid, q, k, gate, up)
+        del gate, up, yq, h16, x, q, k, resid
+        torch.cuda.empty_cache()
+        for _ in range(2): Hrun.run()
+        barrier()
+        e2e_steps = max(2, min(args.steps, 5))
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps): Hrun.run()
+        barrier()
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
+        if world > 1:
+            t = torch.tensor([e2e_s], device=dev, dtype=torch.float64); torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX); e2e_s = float(t.item())
+        e2e = {'value': Te * world / e2e_s, 'unit': 'tokens/s', 'rows_per_gpu': Te, 'h2d_bytes_per_step': Hrun.h2d_bytes,
+               'd2h_bytes_per_step': Hrun.d2h_bytes, 'ms_per_step': e2e_s * 1e3}
 
     if rank == 0:
         peak, which = peaks()
@@ -248,9 +254,13 @@ def main():
                     'frac': T * BYTES_PER_TOKEN[n] / float(med[i]) / 1e9 / peak} for i, n in enumerate(names)}
         dom = 'swiglu_q8_1_f16'
         ach = T * BYTES_PER_TOKEN[dom] / float(per[:, 2].mean()) / 1e9
-        import oracle
-        threads = oracle.default_threads()
-        cs = cpu_layer_glue(args.cpu_sample, threads)
+        cpu = None
+        if not args.skip_cpu:
+            import oracle
+            threads = oracle.default_threads()
+            cs = cpu_layer_glue(args.cpu_sample, threads)
+            cpu = {'value': args.cpu_sample / cs, 'unit': 'tokens/s', 'cores': threads, 'kind': 'port',
+                   'sample': f'{args.cpu_sample} token rows through all three ops (the C oracle, rows split over {threads} host threads)'}
         line = {
             'metric': METRIC, 'value': value, 'unit': 'tokens/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
             'ms_per_step': ms_per_step, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
@@ -260,15 +270,13 @@ def main():
                        'parallelism': f'token rows x {world} (no collective)', 'l2': 'inputs (13.7 GB per step) larger than L2',
                        'bytes_per_token': sum(BYTES_PER_TOKEN.values())},
             'clocks': clk,
-            'e2e': {'value': Te * world / e2e_s, 'unit': 'tokens/s', 'rows_per_gpu': Te, 'h2d_bytes_per_step': Hrun.h2d_bytes, 'd2h_bytes_per_step': Hrun.d2h_bytes,
-                    'ms_per_step': e2e_s * 1e3},
+            'e2e': e2e,
             'gpu_launches': 3 * args.steps,
-            'roofline': {'bound': 'hbm', 'kernel': 'q8_1_kernel<fp16, swiglu> (SwiGLU + Q8_1)', 'achieved': ach, 'peak': peak, 'unit': 'GB/s',
+            'roofline': {'bound': 'hbm', 'kernel': 'swiglu_q8_fast_kernel<fp16> (SwiGLU + Q8_1)', 'achieved': ach, 'peak': peak, 'unit': 'GB/s',
                          'frac': ach / peak, 'peak_source': which, 'frac_of_8tbs': ach / 8000.0, 'traffic': None},
             'kernels': kern,
             'hbm_gbs_all_three': T * sum(BYTES_PER_TOKEN.values()) / (total / args.steps) / 1e9,
-            'cpu_baseline': {'value': args.cpu_sample / cs, 'unit': 'tokens/s', 'cores': threads, 'kind': 'port',
-                             'sample': f'{args.cpu_sample} token rows through all three ops (the C oracle, rows split over {threads} host threads)'},
+            'cpu_baseline': cpu,
         }
         if args.ops: line['ops'] = single_op_lines(torch, dev, peak)
         print(json.dumps(line), flush=True)
