@@ -243,6 +243,66 @@ __global__ void __launch_bounds__(128) add_rms_f16_kernel(uint16_t * __restrict_
     cp_async_wait<0>();
 }
 
+// ---- fp16 rows held in registers -----------------------------------------------------------------------------------------
+// N = 256 CH: a warp loads its whole row (x and d: 2 CH 16-byte loads per lane, all issued before any is used, so a warp
+// keeps 4 N bytes in flight), keeps xs in fp32 registers between the sum of squares and the normalisation, and reads the
+// norm weights from shared memory (staged once per block). No row is touched twice, in HBM or in shared memory.
+template <int CH>
+__global__ void __launch_bounds__(128, 2) add_rms_f16_reg_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d,
+                                                                 const float * __restrict__ nw, float eps, uint16_t * __restrict__ h16, int n) {
+    constexpr int N = 256 * CH;
+    __shared__ __align__(16) float snw[N];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x * 4; i < N; i += 512) *reinterpret_cast<float4 *>(snw + i) = __ldg(reinterpret_cast<const float4 *>(nw + i));
+    __syncthreads();
+    for (int t = blockIdx.x * 4 + warp; t < n; t += gridDim.x * 4) {
+        uint16_t * xr = x + (size_t)t * N + 8 * lane;
+        uint16_t * hr = h16 + (size_t)t * N + 8 * lane;
+        uint4 rx[CH], rd[CH];
+#pragma unroll
+        for (int m = 0; m < CH; m++) rx[m] = ld128(xr + 256 * m);
+        if (d) {
+            const uint16_t * dr = d + (size_t)t * N + 8 * lane;
+#pragma unroll
+            for (int m = 0; m < CH; m++) rd[m] = ldg128(dr + 256 * m);
+        }
+        float xs[CH][8];
+        float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int m = 0; m < CH; m++) {
+            load8(rx[m], xs[m]);
+            if (d) {
+                float dv[8];
+                load8(rd[m], dv);
+#pragma unroll
+                for (int c = 0; c < 8; c++) xs[m][c] = fadd(xs[m][c], dv[c]);
+                st128(xr + 256 * m, make_uint4(f2_to_h2(xs[m][0], xs[m][1]), f2_to_h2(xs[m][2], xs[m][3]), f2_to_h2(xs[m][4], xs[m][5]),
+                                               f2_to_h2(xs[m][6], xs[m][7])));
+            }
+#pragma unroll
+            for (int c = 0; c < 8; c++) a[c] = ffma(xs[m][c], xs[m][c], a[c]);
+        }
+        const float tot = ref_total_f16(a, lane);
+        const float scale = cam_rsqrt(fadd(fdiv(tot, (float)N), eps));
+#pragma unroll
+        for (int m = 0; m < CH; m++) {
+            const float4 w0 = *reinterpret_cast<const float4 *>(snw + 8 * lane + 256 * m), w1 = *reinterpret_cast<const float4 *>(snw + 8 * lane + 256 * m + 4);
+            const float v0 = fmul(fmul(xs[m][0], scale), w0.x), v1 = fmul(fmul(xs[m][1], scale), w0.y);
+            const float v2 = fmul(fmul(xs[m][2], scale), w0.z), v3 = fmul(fmul(xs[m][3], scale), w0.w);
+            const float v4 = fmul(fmul(xs[m][4], scale), w1.x), v5 = fmul(fmul(xs[m][5], scale), w1.y);
+            const float v6 = fmul(fmul(xs[m][6], scale), w1.z), v7 = fmul(fmul(xs[m][7], scale), w1.w);
+            st128_stream(hr + 256 * m, make_uint4(f2_to_h2(v0, v1), f2_to_h2(v2, v3), f2_to_h2(v4, v5), f2_to_h2(v6, v7)));
+        }
+    }
+}
+
+template <int CH>
+int launch_f16_reg(uint16_t * x, const uint16_t * d, const float * nw, float eps, uint16_t * h16, int n, cudaStream_t stream) {
+    const int grid = cam_resident_grid(add_rms_f16_reg_kernel<CH>, 128, 0, ((long)n + 3) / 4);
+    add_rms_f16_reg_kernel<CH><<<grid, 128, 0, stream>>>(x, d, nw, eps, h16, n);
+    return (int)cudaGetLastError();
+}
+
 template <int MODE>
 int launch_f16(uint16_t * x, const uint16_t * d, const float * nw, float eps, uint16_t * h16, float * ss, const float * tot, int N,
                int Nfull, int n, cudaStream_t stream) {
@@ -308,6 +368,16 @@ extern "C" int q35p_add_rms16(int n, float * x, const float * d, const float * n
 extern "C" int cam_add_rms_f16(int n, void * x, const void * d, const float * nw, float eps, void * h16, int N, void * stream) {
     if (n < 0 || N < 256 || (N & 255) || N > 65536 || !x || !nw || !h16) return CAM_ERR_ARG;
     if (!cam_aligned16(x) || !cam_aligned16(nw) || (d && !cam_aligned16(d)) || !cam_aligned16(h16)) return CAM_ERR_ALIGN;
+    if (n >= 64) {      // (a handful of rows: the staged kernel, which does not stage the weights first)
+        switch (N) {
+            case 1024: return launch_f16_reg<4>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
+            case 2048: return launch_f16_reg<8>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
+            case 2560: return launch_f16_reg<10>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
+            case 4096: return launch_f16_reg<16>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
+            case 5120: return launch_f16_reg<20>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
+            default: break;
+        }
+    }
     return launch_f16<0>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, nullptr, nullptr, N, N, n, (cudaStream_t)stream);
 }
 

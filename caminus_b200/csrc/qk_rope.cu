@@ -10,9 +10,12 @@
 // (16 bytes per thread, two stages: the next token's copy flies while this one is computed). The 64 cos / sin of a
 // position are computed once per token (64 threads) and shared by all of its heads; the reference recomputes them in every
 // (token, head) workgroup. A half-warp owns a head: lane l holds dims 4l .. 4l + 3 and 64 + 4l .. 64 + 4l + 3, i.e. complete
-// rotation pairs, so the rotation needs no exchange. The reference's sum order is kept: a lane's 8 squares are 8 of its
-// threads; butterfly partners 16, 8, 4 are lanes l ^ 4, l ^ 2, l ^ 1, partners 2 and 1 are inside the lane, and the four wave
-// sums sit in lanes 0 and 8 of the half-warp (low dims) and again there for the high dims.
+// rotation pairs, so the rotation needs no exchange.
+// Sum of squares: the order of THIS mapping, not the reference's: per lane an fma chain over its 4 low dims and one over
+// its 4 high dims, added, then the half-warp butterfly with partners 8, 4, 2, 1. (The reference's order, squares rounded one
+// by one and a 32-lane butterfly per 32 consecutive dims, costs 13 shuffles and 20 additions per head here against 4 and 5,
+// on a kernel that is instruction-bound; the sum is one input of a tolerance-gated fp16 result.) Every other statement is
+// the reference's.
 #include "cam_common.cuh"
 
 namespace {
@@ -42,13 +45,15 @@ template <> struct In<uint16_t> {
 };
 
 // T: the input type. CACHE: the reference's signature (fp32 qkv rows in, q16 and the cache row's K | V halves out).
-template <typename T, bool CACHE>
+// P: heads per half-warp and round: a warp takes 2 P heads of a token at a time, reduces them all, then ONE pass of the
+// scale's square root and divisions serves all of them (lane j computes head j's), instead of one per head.
+template <typename T, bool CACHE, int P>
 __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int nh = A.nh, nkv = A.nkv, H = nh + nkv;
     const int in_heads = CACHE ? nh + 2 * nkv : H;                       // heads staged per token
-    const size_t stage_bytes = (size_t)in_heads * 128 * sizeof(T);
+    const int stage_bytes = in_heads * 128 * (int)sizeof(T);
     float * wq = reinterpret_cast<float *>(smem);                        // [128] | wk [128] | freq [64] | rc [2][64] | rs [2][64]
     float * wk = wq + 128, * freq = wk + 128, * rc = freq + 64, * rs = rc + 128;
     unsigned char * stage = smem + (128 + 128 + 64 + 128 + 128) * 4;
@@ -60,15 +65,15 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
 
     auto issue = [&](int t, int st) {
         if (t < A.n) {
-            unsigned char * s = stage + (size_t)st * stage_bytes;
+            unsigned char * s = stage + st * stage_bytes;
             if (CACHE) {
                 const unsigned char * src = reinterpret_cast<const unsigned char *>(reinterpret_cast<const float *>(A.in0) + (size_t)t * A.ldq);
-                for (int c = tid; c < in_heads * 32; c += blockDim.x) cp_async16(s + (size_t)c * 16, src + (size_t)c * 16);
+                for (int c = tid; c < in_heads * 32; c += blockDim.x) cp_async16(s + c * 16, src + c * 16);
             } else {
                 const unsigned char * sq = reinterpret_cast<const unsigned char *>(reinterpret_cast<const uint16_t *>(A.in0) + (size_t)t * nh * 128);
                 const unsigned char * sk = reinterpret_cast<const unsigned char *>(reinterpret_cast<const uint16_t *>(A.in1) + (size_t)t * nkv * 128);
-                for (int c = tid; c < nh * 16; c += blockDim.x) cp_async16(s + (size_t)c * 16, sq + (size_t)c * 16);
-                for (int c = tid; c < nkv * 16; c += blockDim.x) cp_async16(s + (size_t)(nh * 16 + c) * 16, sk + (size_t)c * 16);
+                for (int c = tid; c < nh * 16; c += blockDim.x) cp_async16(s + c * 16, sq + c * 16);
+                for (int c = tid; c < nkv * 16; c += blockDim.x) cp_async16(s + (nh * 16 + c) * 16, sk + c * 16);
             }
         }
         cp_async_commit();
@@ -84,65 +89,75 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
     issue(t0, 0);
     if (tid < 64 && t0 < A.n) tables(t0, 0);
     int st = 0;
-    const int hw = lane >> 4, l16 = lane & 15, base = lane & 16;
+    const int hw = lane >> 4, l16 = lane & 15;
+    const int xoff = 4 * l16 * (int)sizeof(T);
     for (int t = t0; t < A.n; t += gridDim.x, st ^= 1) {
         const int tn = t + gridDim.x;
         issue(tn, st ^ 1);
         if (tid < 64 && tn < A.n) tables(tn, st ^ 1);
         cp_async_wait<1>();
         __syncthreads();
-        const unsigned char * s = stage + (size_t)st * stage_bytes;
-        const float * crc = rc + st * 64, * crs = rs + st * 64;
+        const unsigned char * s = stage + st * stage_bytes;
+        const float4 c4 = *reinterpret_cast<const float4 *>(rc + st * 64 + 4 * l16), s4 = *reinterpret_cast<const float4 *>(rs + st * 64 + 4 * l16);
+        const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
         const int pos = A.pos0 + t;
-        for (int h0 = 0; h0 < H; h0 += 2 * nwarps) {
-            const int hy = h0 + 2 * warp + hw;
-            const bool on = hy < H;
-            const bool isq = hy < nh;
-            float x[8];
-            if (on) {
-                const unsigned char * hp = s + (size_t)hy * 128 * sizeof(T);       // q heads then k heads, in both input forms
-                float lo[4], hi[4];
-                In<T>::get4(hp + (size_t)(4 * l16) * sizeof(T), lo);
-                In<T>::get4(hp + (size_t)(64 + 4 * l16) * sizeof(T), hi);
+        for (int h0 = 2 * warp * P; h0 < H; h0 += 2 * nwarps * P) {        // this warp's heads h0 .. h0 + 2 P - 1 (uniform per warp)
+            float x[P][8], tot[P];
 #pragma unroll
-                for (int c = 0; c < 4; c++) { x[c] = lo[c]; x[4 + c] = hi[c]; }
-            } else {
+            for (int p = 0; p < P; p++) {
+                const int hy = h0 + 2 * p + hw;
+                if (hy < H) {
+                    const unsigned char * hp = s + hy * 128 * (int)sizeof(T) + xoff;       // q heads then k heads, in both input forms
+                    float lo[4], hi[4];
+                    In<T>::get4(hp, lo);
+                    In<T>::get4(hp + 64 * sizeof(T), hi);
 #pragma unroll
-                for (int c = 0; c < 8; c++) x[c] = 0.0f;
+                    for (int c = 0; c < 4; c++) { x[p][c] = lo[c]; x[p][4 + c] = hi[c]; }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 8; c++) x[p][c] = 0.0f;
+                }
+                // the head's sum of squares: per lane an fma chain over its 4 low and its 4 high dims, then the half-warp butterfly
+                float sl = 0.0f, sh = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 4; c++) { sl = ffma(x[p][c], x[p][c], sl); sh = ffma(x[p][4 + c], x[p][4 + c], sh); }
+                float ss = fadd(sl, sh);
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) ss = fadd(ss, __shfl_xor_sync(CAM_FULL, ss, o));
+                tot[p] = ss;
             }
-            float a[8];
+            // lane j < 2 P computes the scale of head h0 + j (pass j >> 1, half-warp j & 1); then every lane fetches its heads' scales
+            float mine = 1.0f;
 #pragma unroll
-            for (int c = 0; c < 8; c++) a[c] = fmul(x[c], x[c]);
-#pragma unroll
-            for (int o = 4; o > 0; o >>= 1)
-#pragma unroll
-                for (int c = 0; c < 8; c++) a[c] = fadd(a[c], __shfl_xor_sync(CAM_FULL, a[c], o));          // partners 16, 8, 4
-            const float P0 = fadd(fadd(a[0], a[2]), fadd(a[1], a[3])), P1 = fadd(fadd(a[4], a[6]), fadd(a[5], a[7]));   // 2, 1
-            float tot = 0.0f;
-            tot = fadd(tot, __shfl_sync(CAM_FULL, P0, base));
-            tot = fadd(tot, __shfl_sync(CAM_FULL, P0, base + 8));
-            tot = fadd(tot, __shfl_sync(CAM_FULL, P1, base));
-            tot = fadd(tot, __shfl_sync(CAM_FULL, P1, base + 8));
-            if (!on) continue;                                              // (uniform per half-warp; no shuffle follows)
-            const float scale = cam_rsqrt(fadd(fdiv(tot, 128.0f), eps));
-            const float * wn = isq ? wq : wk;
-            const float4 wlo = *reinterpret_cast<const float4 *>(wn + 4 * l16), whi = *reinterpret_cast<const float4 *>(wn + 64 + 4 * l16);
-            const float4 c4 = *reinterpret_cast<const float4 *>(crc + 4 * l16), s4 = *reinterpret_cast<const float4 *>(crs + 4 * l16);
-            const float wl[4] = {wlo.x, wlo.y, wlo.z, wlo.w}, wh[4] = {whi.x, whi.y, whi.z, whi.w};
-            const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
-            float ylo[4], yhi[4];
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                const float x0 = fmul(fmul(scale, x[c]), wl[c]), x1 = fmul(fmul(scale, x[4 + c]), wh[c]);
-                ylo[c] = ffma(x0, cc[c], -fmul(x1, sn[c]));
-                yhi[c] = ffma(x1, cc[c], fmul(x0, sn[c]));
+            for (int p = 0; p < P; p++) {
+                const float v = __shfl_sync(CAM_FULL, tot[p], 16 * (lane & 1));
+                if ((lane >> 1) == p) mine = v;
             }
-            uint16_t * o;
-            if (isq) o = A.out0 + ((size_t)t * nh + hy) * 128;
-            else if (CACHE) o = A.out1 + (size_t)pos * 2 * nkv * 128 + (size_t)(hy - nh) * 128;
-            else o = A.out1 + ((size_t)t * nkv + (hy - nh)) * 128;
-            st64_stream(o + 4 * l16, make_uint2(f2_to_h2(ylo[0], ylo[1]), f2_to_h2(ylo[2], ylo[3])));
-            st64_stream(o + 64 + 4 * l16, make_uint2(f2_to_h2(yhi[0], yhi[1]), f2_to_h2(yhi[2], yhi[3])));
+            const float scale_mine = cam_rsqrt(fadd(fmul(mine, 0.0078125f), eps));      // tot / 128: the same bits as the division
+#pragma unroll
+            for (int p = 0; p < P; p++) {
+                const float scale = __shfl_sync(CAM_FULL, scale_mine, 2 * p + hw);
+                const int hy = h0 + 2 * p + hw;
+                if (hy < H) {
+                    const bool isq = hy < nh;
+                    const float * wn = (isq ? wq : wk) + 4 * l16;
+                    const float4 wlo = *reinterpret_cast<const float4 *>(wn), whi = *reinterpret_cast<const float4 *>(wn + 64);
+                    const float wl[4] = {wlo.x, wlo.y, wlo.z, wlo.w}, wh[4] = {whi.x, whi.y, whi.z, whi.w};
+                    float ylo[4], yhi[4];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const float x0 = fmul(fmul(scale, x[p][c]), wl[c]), x1 = fmul(fmul(scale, x[p][4 + c]), wh[c]);
+                        ylo[c] = ffma(x0, cc[c], -fmul(x1, sn[c]));
+                        yhi[c] = ffma(x1, cc[c], fmul(x0, sn[c]));
+                    }
+                    uint16_t * o;
+                    if (isq) o = A.out0 + ((size_t)t * nh + hy) * 128;
+                    else if (CACHE) o = A.out1 + (size_t)pos * 2 * nkv * 128 + (size_t)(hy - nh) * 128;
+                    else o = A.out1 + ((size_t)t * nkv + (hy - nh)) * 128;
+                    st64_stream(o + 4 * l16, make_uint2(f2_to_h2(ylo[0], ylo[1]), f2_to_h2(ylo[2], ylo[3])));
+                    st64_stream(o + 64 + 4 * l16, make_uint2(f2_to_h2(yhi[0], yhi[1]), f2_to_h2(yhi[2], yhi[3])));
+                }
+            }
         }
         if (CACHE) {      // v: copied as fp16 into the row's V half
             const float * vs = reinterpret_cast<const float *>(s) + (size_t)H * 128;
@@ -157,15 +172,26 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
     cp_async_wait<0>();
 }
 
-// the block size whose half-warps divide the token's heads with the least idle half-warps (more warps on a tie)
-int pick_warps(int H) {
-    int best = 8, waste = 1 << 30;
-    for (int w = 12; w >= 4; w--) {
-        const int passes = (H + 2 * w - 1) / (2 * w);
-        const int idle = passes * 2 * w - H;
-        if (idle < waste) { waste = idle; best = w; }
-    }
-    return best;
+// warps per block (4 .. 12) and heads per half-warp and round (1 .. 4): the pair with the fewest idle half-warp slots over a
+// token's H heads; among equals the most heads per round (one scale computation serves 2 P heads), then the most warps
+void pick_shape(int H, int & warps, int & P) {
+    int waste = 1 << 30;
+    warps = 8; P = 1;
+    for (int p = 4; p >= 1; p--)
+        for (int w = 12; w >= 4; w--) {
+            const int per_round = 2 * w * p;
+            const int idle = (H + per_round - 1) / per_round * per_round - H;
+            if (idle < waste) { waste = idle; warps = w; P = p; }
+        }
+}
+
+template <typename T, bool CACHE, int P>
+int launch_rope_p(const RopeArgs & A, int warps, size_t smem, cudaStream_t stream) {
+    const cudaError_t e = cudaFuncSetAttribute(qk_rope_kernel<T, CACHE, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    const int grid = cam_resident_grid(qk_rope_kernel<T, CACHE, P>, warps * 32, smem, A.n);
+    qk_rope_kernel<T, CACHE, P><<<grid, warps * 32, smem, stream>>>(A);
+    return (int)cudaGetLastError();
 }
 
 template <typename T, bool CACHE>
@@ -174,12 +200,14 @@ int launch_rope(const RopeArgs & A, cudaStream_t stream) {
     const int in_heads = CACHE ? A.nh + 2 * A.nkv : H;
     const size_t smem = (128 + 128 + 64 + 128 + 128) * 4 + 2 * (size_t)in_heads * 128 * sizeof(T);
     if (smem > 227 * 1024) return CAM_ERR_SHAPE;
-    const cudaError_t e = cudaFuncSetAttribute(qk_rope_kernel<T, CACHE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return (int)e;
-    const int warps = pick_warps(H);
-    const int grid = cam_resident_grid(qk_rope_kernel<T, CACHE>, warps * 32, smem, A.n);
-    qk_rope_kernel<T, CACHE><<<grid, warps * 32, smem, stream>>>(A);
-    return (int)cudaGetLastError();
+    int warps, P;
+    pick_shape(H, warps, P);
+    switch (P) {
+        case 1: return launch_rope_p<T, CACHE, 1>(A, warps, smem, stream);
+        case 2: return launch_rope_p<T, CACHE, 2>(A, warps, smem, stream);
+        case 3: return launch_rope_p<T, CACHE, 3>(A, warps, smem, stream);
+        default: return launch_rope_p<T, CACHE, 4>(A, warps, smem, stream);
+    }
 }
 
 int check_common(int n, int nh, int nkv, const void * par, int pos0) {

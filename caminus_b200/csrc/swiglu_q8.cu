@@ -99,91 +99,97 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_1_kernel(const T * __restrict__
 // sequence within 3.2e-7 (2.2 ulp measured over the whole range, and its product). From that:
 //   d:     d^ = amax^ / 127 is within 1.53e-6 (< 26 fp32 ulps) of the exact fp32 d. If d^'s low 13 bits are more than 40 away
 //          from the fp16 rounding tie (0x1000) and d^ is in fp16's normal range, fp16(d^) = fp16(d): the stored scale is exact.
-//   codes: t^ = h^ / d^ is within 3.06e-6 |t| <= 3.9e-4 of the exact fp32 quotient. If t^ is more than 4.5e-4 away from every
-//          half-integer, round-to-nearest of t^ is the exact code (roundf of the exact quotient): no tie and no boundary
-//          lies between them.
-// A block (32 values) where any of this fails: some g < -8, a quotient within 4.5e-4 of a rounding boundary, d^ near an fp16
+//   codes: t^ = h^ / d^ is within 3.06e-6 |t| of the exact fp32 quotient t. If t^ (1 - 3.2e-6) and t^ (1 + 3.2e-6) round to the
+//          same integer, no rounding boundary and no tie lies in the interval that holds t, and that integer is roundf(t).
+// A block (32 values) where any of this fails: some g < -8, an interval that holds a rounding boundary, d^ near an fp16
 // tie or outside [6.2e-5, 6e4), a sum that is not finite (NaN or infinite input): is recomputed by the whole warp with
-// the exact statements, one lane per value. About 4 % of the blocks of Gaussian inputs take that path.
+// the exact statements, one lane per value. About 2 % of the blocks of Gaussian inputs take that path.
 // The stored scale d and the 32 codes are therefore always the exact statements' bytes. The block sum of a block on the
 // fast pass is the fp16 rounding of the same-order sum of the h^: it can differ from the exact statements' sum by one fp16
 // ulp (or by 1.6e-6 sum |h| when the values cancel). The reference reports that field and does not gate it
 // (tests/engine/golden_util.py:145-146); the strict kernel above gives its exact bytes too.
-CAM_DEV float ex2_approx(float a) { float r; asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
-CAM_DEV float rcp_approx(float a) { float r; asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
+// (.ftz: a denormal exponent argument counts as 0 and a denormal 2^a as 0; both are below 1e-38 beside the 1 they are added to)
+CAM_DEV float ex2_approx(float a) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
+CAM_DEV float rcp_approx(float a) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
 
+// one warp-wide step over 8 blocks (256 values) starting at group `base` (a multiple of 32). FULL: all 32 lanes have a group.
+template <typename T, bool FULL>
+CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y, int base, int ngroups, int lane) {
+    const int gi = base + lane, q = lane & 3;
+    const bool on = FULL || gi < ngroups;
+    float gv[8], uv[8], h[8];
+    if (on) { Load8<T>::get(g + (size_t)gi * 8, gv); Load8<T>::get(u + (size_t)gi * 8, uv); }
+    else {
+#pragma unroll
+        for (int k = 0; k < 8; k++) { gv[k] = 0.0f; uv[k] = 0.0f; }
+    }
+    float gmin = gv[0], amax = 0.0f;
+#pragma unroll
+    for (int k = 1; k < 8; k++) gmin = fminf(gmin, gv[k]);
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const float e = ex2_approx(fmul(gv[k], -0x1.715476p+0f));
+        h[k] = fmul(fmul(gv[k], rcp_approx(fadd(1.0f, e))), uv[k]);
+        amax = fmaxf(amax, fabsf(h[k]));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 2));
+    float sa = fadd(fadd(h[0], h[1]), fadd(h[2], h[3])), sb = fadd(fadd(h[4], h[5]), fadd(h[6], h[7]));
+    sa = fadd(sa, __shfl_xor_sync(CAM_FULL, sa, 2)); sb = fadd(sb, __shfl_xor_sync(CAM_FULL, sb, 2));
+    sa = fadd(sa, __shfl_xor_sync(CAM_FULL, sa, 1)); sb = fadd(sb, __shfl_xor_sync(CAM_FULL, sb, 1));
+    const float sum = fadd(sa, sb);
+    const float d = fmul(amax, 0x1.020408p-7f);                             // amax / 127 within 1.2e-7
+    const float inv = rcp_approx(d);
+    // the quotient's two ends, t (1 +- 3.2e-6), each rounded to an integer (ties to even) in the low mantissa bits of
+    // t + 1.5 * 2^23: equal integers mean no rounding boundary (and no tie) lies within the error interval of the quotient
+    const float inv_hi = fmul(inv, 0x1.000036p+0f), inv_lo = fmul(inv, 0x1.ffff94p-1f);
+    uint32_t v[8], differ = 0;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        v[k] = __float_as_uint(ffma(h[k], inv_hi, 12582912.0f));
+        differ |= v[k] ^ __float_as_uint(ffma(h[k], inv_lo, 12582912.0f));
+    }
+    const int low = (int)(__float_as_uint(d) & 0x1fffu) - 0x1000;
+    const bool redo = differ != 0 || !(gmin >= -8.0f) || !(d >= 6.2e-5f && d < 6.0e4f) || (low >= -40 && low <= 40) || !(fabsf(sum) < 3.0e38f);
+    const uint32_t mask = __ballot_sync(CAM_FULL, redo && on);
+    const uint32_t quad = (mask | (mask >> 1) | (mask >> 2) | (mask >> 3)) & 0x11111111u;   // bit 4 j: block j of this warp
+    if (on && !((quad >> (lane & ~3)) & 1u)) {
+        const uint32_t w0 = __byte_perm(__byte_perm(v[0], v[1], 0x0040), __byte_perm(v[2], v[3], 0x0040), 0x5410);
+        const uint32_t w1 = __byte_perm(__byte_perm(v[4], v[5], 0x0040), __byte_perm(v[6], v[7], 0x0040), 0x5410);
+        uint32_t * o = reinterpret_cast<uint32_t *>(y + (size_t)(gi >> 2) * 36);
+        if (q == 0) __stcs(o, f2_to_h2(d, sum));
+        __stcs(o + 1 + 2 * q, w0);
+        __stcs(o + 2 + 2 * q, w1);
+    }
+    // exact recomputation of the flagged blocks: the whole warp, one lane per value (uniform: quad is the same in every lane)
+    for (uint32_t m = quad; m; m &= m - 1) {
+        const size_t blk = (size_t)(base >> 2) + ((__ffs(m) - 1) >> 2);
+        const float x = fmul(cam_silu(Load8<T>::one(g + blk * 32 + lane)), Load8<T>::one(u + blk * 32 + lane));
+        float am = fabsf(x);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(CAM_FULL, am, o));
+        float s = fadd(x, __shfl_xor_sync(CAM_FULL, x, 1));
+        s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 2));
+        s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 16));
+        s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 8));
+        s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 4));
+        const float de = fdiv(am, 127.0f);
+        uint8_t * o = y + blk * 36;
+        o[4 + lane] = (uint8_t)q8_code(x, de, am);
+        if (lane == 0) *reinterpret_cast<uint32_t *>(o) = f2_to_h2(de, s);
+    }
+}
+
+// nb < 2^29 blocks per launch (32-bit group indices); the host splits longer inputs
 template <typename T>
 __global__ void __launch_bounds__(Q8_THREADS) swiglu_q8_fast_kernel(const T * __restrict__ g, const T * __restrict__ u,
-                                                                    uint8_t * __restrict__ y, long nb) {
-    const int lane = threadIdx.x & 31, q = lane & 3;
-    const long ngroups = nb * 4;
-    const long stride = (long)gridDim.x * Q8_THREADS;
-    for (long base = (long)blockIdx.x * Q8_THREADS + (threadIdx.x & ~31); base < ngroups; base += stride) {
-        const long gi = base + lane;
-        const bool on = gi < ngroups;
-        float gv[8], uv[8], h[8];
-        if (on) { Load8<T>::get(g + gi * 8, gv); Load8<T>::get(u + gi * 8, uv); }
-        else {
-#pragma unroll
-            for (int k = 0; k < 8; k++) { gv[k] = 0.0f; uv[k] = 0.0f; }
-        }
-        float gmin = gv[0], amax = 0.0f;
-#pragma unroll
-        for (int k = 1; k < 8; k++) gmin = fminf(gmin, gv[k]);
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            const float e = ex2_approx(fmul(gv[k], -0x1.715476p+0f));
-            h[k] = fmul(fmul(gv[k], rcp_approx(fadd(1.0f, e))), uv[k]);
-            amax = fmaxf(amax, fabsf(h[k]));
-        }
-        amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 2));
-        float sa = fadd(fadd(h[0], h[1]), fadd(h[2], h[3])), sb = fadd(fadd(h[4], h[5]), fadd(h[6], h[7]));
-        sa = fadd(sa, __shfl_xor_sync(CAM_FULL, sa, 2)); sb = fadd(sb, __shfl_xor_sync(CAM_FULL, sb, 2));
-        sa = fadd(sa, __shfl_xor_sync(CAM_FULL, sa, 1)); sb = fadd(sb, __shfl_xor_sync(CAM_FULL, sb, 1));
-        const float sum = fadd(sa, sb);
-        const float d = fmul(amax, 0x1.020408p-7f);                         // amax / 127 within 1.2e-7
-        const float inv = rcp_approx(d);
-        const int low = (int)(__float_as_uint(d) & 0x1fffu) - 0x1000;
-        bool redo = !(gmin >= -8.0f) || !(d >= 6.2e-5f && d < 6.0e4f) || (low >= -40 && low <= 40) || !(fabsf(sum) < 3.0e38f);
-        float fmax_ = 0.0f;
-        uint32_t v[8];
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            const float t = ffma(h[k], inv, 12582912.0f);                    // the quotient rounded to an integer (ties to even)
-            const float f = ffma(h[k], inv, -fsub(t, 12582912.0f));          // its distance from that integer
-            fmax_ = fmaxf(fmax_, fabsf(f));
-            v[k] = __float_as_uint(t);                                       // the integer sits in the low mantissa bits
-        }
-        redo = redo || !(fmax_ < 0.49955f);
-        const uint32_t mask = __ballot_sync(CAM_FULL, redo && on);
-        const uint32_t quad = (mask | (mask >> 1) | (mask >> 2) | (mask >> 3)) & 0x11111111u;   // bit 4 j: block j of this warp
-        if (on && !((quad >> (lane & ~3)) & 1u)) {
-            const uint32_t w0 = __byte_perm(__byte_perm(v[0], v[1], 0x0040), __byte_perm(v[2], v[3], 0x0040), 0x5410);
-            const uint32_t w1 = __byte_perm(__byte_perm(v[4], v[5], 0x0040), __byte_perm(v[6], v[7], 0x0040), 0x5410);
-            uint32_t * o = reinterpret_cast<uint32_t *>(y + (gi >> 2) * 36);
-            if (q == 0) __stcs(o, f2_to_h2(d, sum));
-            __stcs(o + 1 + 2 * q, w0);
-            __stcs(o + 2 + 2 * q, w1);
-        }
-        // exact recomputation of the flagged blocks: the whole warp, one lane per value (uniform: quad is the same in every lane)
-        for (uint32_t m = quad; m; m &= m - 1) {
-            const long blk = (base >> 2) + ((__ffs(m) - 1) >> 2);
-            const float x = fmul(cam_silu(Load8<T>::one(g + blk * 32 + lane)), Load8<T>::one(u + blk * 32 + lane));
-            float am = fabsf(x);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(CAM_FULL, am, o));
-            float s = fadd(x, __shfl_xor_sync(CAM_FULL, x, 1));
-            s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 2));
-            s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 16));
-            s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 8));
-            s = fadd(s, __shfl_xor_sync(CAM_FULL, s, 4));
-            const float de = fdiv(am, 127.0f);
-            uint8_t * o = y + blk * 36;
-            o[4 + lane] = (uint8_t)q8_code(x, de, am);
-            if (lane == 0) *reinterpret_cast<uint32_t *>(o) = f2_to_h2(de, s);
-        }
-    }
+                                                                    uint8_t * __restrict__ y, int nb) {
+    const int lane = threadIdx.x & 31;
+    const int ngroups = nb * 4;
+    const int stride = gridDim.x * Q8_THREADS;
+    int base = blockIdx.x * Q8_THREADS + (threadIdx.x & ~31);
+    for (; base + 32 <= ngroups; base += stride) swiglu_q8_step<T, true>(g, u, y, base, ngroups, lane);
+    if (base < ngroups) swiglu_q8_step<T, false>(g, u, y, base, ngroups, lane);
 }
 
 // the last, partial block (n % 32 values, the rest 0): one warp, one lane per value
@@ -219,8 +225,15 @@ int launch_q8(const T * g, const T * u, void * y, long n, cudaStream_t stream) {
     const long nb = n >> 5;
     if (nb > 0) {
         const long want = (nb * 4 + Q8_THREADS - 1) / Q8_THREADS;
-        if (FAST) swiglu_q8_fast_kernel<T><<<cam_resident_grid(swiglu_q8_fast_kernel<T>, Q8_THREADS, 0, want), Q8_THREADS, 0, stream>>>(g, u, (uint8_t *)y, nb);
-        else q8_1_kernel<T, SWIGLU><<<cam_resident_grid(q8_1_kernel<T, SWIGLU>, Q8_THREADS, 0, want), Q8_THREADS, 0, stream>>>(g, u, (uint8_t *)y, nb);
+        if (FAST) {
+            const long piece = 1L << 28;                                   // blocks per launch
+            for (long b0 = 0; b0 < nb; b0 += piece) {
+                const long m = nb - b0 < piece ? nb - b0 : piece;
+                const long w = (m * 4 + Q8_THREADS - 1) / Q8_THREADS;
+                swiglu_q8_fast_kernel<T><<<cam_resident_grid(swiglu_q8_fast_kernel<T>, Q8_THREADS, 0, w), Q8_THREADS, 0, stream>>>(
+                    g + b0 * 32, u + b0 * 32, (uint8_t *)y + b0 * 36, (int)m);
+            }
+        } else q8_1_kernel<T, SWIGLU><<<cam_resident_grid(q8_1_kernel<T, SWIGLU>, Q8_THREADS, 0, want), Q8_THREADS, 0, stream>>>(g, u, (uint8_t *)y, nb);
     }
     if (n & 31) q8_1_tail_kernel<T, SWIGLU><<<1, 32, 0, stream>>>(g, u, (uint8_t *)y, nb << 5, (int)(n & 31));
     return (int)cudaGetLastError();

@@ -208,25 +208,26 @@ def swiglu_f32_from_f16(g, u, threads=None):
     return h
 
 
-def qk_rope(qkv, ldq, nh, nkv, par, pos0, cache, n, yarn=False, threads=None):
+def qk_rope(qkv, ldq, nh, nkv, par, pos0, cache, n, yarn=False, sum_order=0, threads=None):
     """q3p_qk_rope: qkv float32 [n * ldq]; cache float16 (flat; rows of 2 nkv 128) is copied and updated.
+    sum_order 0: the reference's order of the head's sum of squares; 1: the CUDA kernel's (see cam_oracle.c).
     Returns (q16 float16 [n, nh, 128], cache)"""
     qkv = _c(qkv, np.float32).reshape(-1); par = _c(par, np.float32); cache = _c(cache, np.float16).reshape(-1).copy()
     q16 = np.empty((n, nh, 128), np.uint16); f = lib().orc_qk_rope
     _run(n, threads or default_threads(),
          lambda a, b: f(_p(qkv, 4 * a * ldq), I(ldq), I(nh), I(nkv), _p(par), I(pos0 + a), _p(q16, 2 * a * nh * 128), _p(cache),
-                        I(b - a), I(int(yarn))))
+                        I(b - a), I(int(yarn)), I(int(sum_order))))
     return q16.view(np.float16), cache
 
 
-def qk_rope_f16(q, k, par, pos0, yarn=False, threads=None):
+def qk_rope_f16(q, k, par, pos0, yarn=False, sum_order=0, threads=None):
     """fp16 q [n, nh, 128], k [n, nkv, 128] -> (q out, k out) float16"""
     q = _c(q, np.float16); k = _c(k, np.float16); par = _c(par, np.float32)
     n, nh, _ = q.shape; nkv = k.shape[1]
     qo = np.empty(q.shape, np.uint16); ko = np.empty(k.shape, np.uint16); f = lib().orc_qk_rope_f16
     _run(n, threads or default_threads(),
          lambda a, b: f(_p(q, 2 * a * nh * 128), _p(k, 2 * a * nkv * 128), I(nh), I(nkv), _p(par), I(pos0 + a),
-                        _p(qo, 2 * a * nh * 128), _p(ko, 2 * a * nkv * 128), I(b - a), I(int(yarn))))
+                        _p(qo, 2 * a * nh * 128), _p(ko, 2 * a * nkv * 128), I(b - a), I(int(yarn)), I(int(sum_order))))
     return qo.view(np.float16), ko.view(np.float16)
 
 

@@ -305,12 +305,28 @@ void orc_swiglu_f32_from_f16(const uint16_t * g, const uint16_t * u, float * h, 
 
 /* one head of 128 (kernels/q3m_prefill.hip:552-590): ss = x x per dim, four wave sums in order, scale = rsqrt(tot / 128 +
  * eps), y1 = (scale x) w, pairs (j, j + 64): fma(x0, c, -(x1 s)) and fma(x1, c, x0 s) */
-static void head_norm_rope(const float * x, const float * wn, float eps, const float * rc, const float * rs, float * y) {
+/* sum_order 0: the reference's (above). sum_order 1: the CUDA kernel's mapping, 16 lanes per head: lane l sums its dims
+ * 4l .. 4l + 3 and 64 + 4l .. 64 + 4l + 3 in two fma chains, adds them, then a butterfly with partners 8, 4, 2, 1. */
+static void head_norm_rope(const float * x, const float * wn, float eps, const float * rc, const float * rs, float * y, int sum_order) {
     float part[4], sq[128], y1[128];
-    for (int i = 0; i < 128; i++) sq[i] = x[i] * x[i];
-    for (int wv = 0; wv < 4; wv++) part[wv] = wave_sum(sq + 32 * wv);
     float tot = 0.0f;
-    for (int q = 0; q < 4; q++) tot += part[q];
+    if (sum_order == 0) {
+        for (int i = 0; i < 128; i++) sq[i] = x[i] * x[i];
+        for (int wv = 0; wv < 4; wv++) part[wv] = wave_sum(sq + 32 * wv);
+        for (int q = 0; q < 4; q++) tot += part[q];
+    } else {
+        float p[16], q[16];
+        for (int l = 0; l < 16; l++) {
+            float sl = 0.0f, sh = 0.0f;
+            for (int c = 0; c < 4; c++) { sl = fmaf(x[4 * l + c], x[4 * l + c], sl); sh = fmaf(x[64 + 4 * l + c], x[64 + 4 * l + c], sh); }
+            p[l] = sl + sh;
+        }
+        for (int o = 8; o > 0; o >>= 1) {
+            for (int l = 0; l < 16; l++) q[l] = p[l] + p[l ^ o];
+            memcpy(p, q, sizeof p);
+        }
+        tot = p[0];
+    }
     const float scale = orc_rsqrt(tot / 128.0f + eps);
     for (int i = 0; i < 128; i++) y1[i] = (scale * x[i]) * wn[i];
     for (int j = 0; j < 64; j++) {
@@ -332,7 +348,7 @@ static void pos_table(const float * par, int pos, int yarn, float * rc, float * 
 /* q3p_qk_rope (kernels/q3m_prefill.hip:520-591, the F16 cache form): qkv fp32 [n][ldq] = q | k | v; q16 [n][nh][128];
  * cache row pos = K [nkv][128] | V [nkv][128] fp16. par = q_norm[128] | k_norm[128] | theta_scale | eps (| freq[64] | mscale) */
 void orc_qk_rope(const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, uint16_t * q16, uint16_t * cache,
-                 int n, int yarn) {
+                 int n, int yarn, int sum_order) {
     const size_t M = (size_t)nkv * 128;
     for (int t = 0; t < n; t++) {
         const int pos = pos0 + t;
@@ -343,7 +359,7 @@ void orc_qk_rope(const float * qkv, int ldq, int nh, int nkv, const float * par,
         for (int hy = 0; hy < nh + nkv; hy++) {
             const int isq = hy < nh, g = hy - nh;
             const float * x = isq ? row + (size_t)hy * 128 : row + (size_t)nh * 128 + (size_t)g * 128;
-            head_norm_rope(x, isq ? par : par + 128, par[257], rc, rs, y);
+            head_norm_rope(x, isq ? par : par + 128, par[257], rc, rs, y, sum_order);
             uint16_t * o = isq ? q16 + ((size_t)t * nh + hy) * 128 : cw + (size_t)g * 128;
             for (int i = 0; i < 128; i++) o[i] = f2h(y[i]);
             if (!isq) for (int i = 0; i < 128; i++) cw[M + (size_t)g * 128 + i] = f2h(row[(size_t)nh * 128 + M + (size_t)g * 128 + i]);
@@ -352,7 +368,7 @@ void orc_qk_rope(const float * qkv, int ldq, int nh, int nkv, const float * par,
 }
 /* the same statements on fp16 q [n][nh][128] and k [n][nkv][128] (converted exactly to fp32), fp16 out (may alias in) */
 void orc_qk_rope_f16(const uint16_t * q, const uint16_t * k, int nh, int nkv, const float * par, int pos0, uint16_t * qo,
-                     uint16_t * ko, int n, int yarn) {
+                     uint16_t * ko, int n, int yarn, int sum_order) {
     for (int t = 0; t < n; t++) {
         float rc[64], rs[64], x[128], y[128];
         pos_table(par, pos0 + t, yarn, rc, rs);
@@ -362,7 +378,7 @@ void orc_qk_rope_f16(const uint16_t * q, const uint16_t * k, int nh, int nkv, co
             const uint16_t * in = isq ? q + off : k + off;
             uint16_t * o = isq ? qo + off : ko + off;
             for (int i = 0; i < 128; i++) x[i] = h2f(in[i]);
-            head_norm_rope(x, isq ? par : par + 128, par[257], rc, rs, y);
+            head_norm_rope(x, isq ? par : par + 128, par[257], rc, rs, y, sum_order);
             for (int i = 0; i < 128; i++) o[i] = f2h(y[i]);
         }
     }

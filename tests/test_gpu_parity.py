@@ -233,7 +233,7 @@ def test_qk_rope_golden(golden, yarn):
         cache0 = (np.random.default_rng(p).standard_normal((p + 3) * 2 * M) * 1.5).astype(np.float16)
         cache = cu(cache0); q16 = torch.zeros(1, nh, 128, dtype=torch.float16, device=DEV)
         R.qk_rope(cu(qkv[i]), ldq, nh, nkv, pd, p, q16, cache, 1)
-        qo, co = oracle.qk_rope(qkv[i], ldq, nh, nkv, par, p, cache0, 1, yarn=yarn)
+        qo, co = oracle.qk_rope(qkv[i], ldq, nh, nkv, par, p, cache0, 1, yarn=yarn, sum_order=1)
         assert same(q16, qo) and same(cache, co)                       # K | V row written, every other row untouched
         ref = f['q_yarn' if yarn else 'q_plain'][i]
         bound = ulp16(ref) + 1e-5 * np.abs(ref).max() + (0 if yarn else 2.0 ** -23 * p * np.abs(ref).max())
@@ -252,12 +252,12 @@ def test_qk_rope_chunk(O, n, nh, nkv, pos0):
         q = qkv[:, :nh * 128].astype(np.float16).reshape(n, nh, 128); k = qkv[:, nh * 128:nh * 128 + M].astype(np.float16).reshape(n, nkv, 128)
         qo, ko = glue.qk_rope_f16(cu(q), cu(k), cu(par), pos0, qo=torch.zeros(n, nh, 128, dtype=torch.float16, device=DEV),
                                   ko=torch.zeros(n, nkv, 128, dtype=torch.float16, device=DEV))
-        qr, kr = oracle.qk_rope_f16(q, k, par, pos0)
+        qr, kr = oracle.qk_rope_f16(q, k, par, pos0, sum_order=1)
         assert same(qo, qr) and same(ko, kr)
         return
     cache = cu(cache0); q16 = torch.zeros(n, nh, 128, dtype=torch.float16, device=DEV)
     O.qk_rope(cu(qkv.reshape(-1)), ldq, nh, nkv, cu(par), pos0, q16, cache, n)
-    qo, co = oracle.qk_rope(qkv.reshape(-1), ldq, nh, nkv, par, pos0, cache0, n)
+    qo, co = oracle.qk_rope(qkv.reshape(-1), ldq, nh, nkv, par, pos0, cache0, n, sum_order=1)
     assert same(q16, qo) and same(cache, co)
     assert np.array_equal(cache.cpu().numpy()[:pos0 * 2 * M], cache0[:pos0 * 2 * M])                 # rows below the chunk untouched
     assert np.array_equal(cache.cpu().numpy().reshape(-1, 2, M)[pos0:pos0 + n, 1], qkv[:, nh * 128 + M:nh * 128 + 2 * M].astype(np.float16))
@@ -269,7 +269,7 @@ def test_qk_rope_f16_config(yarn):
     T, nh, nkv = 4096, 32, 4
     q, k = synth.qk_inputs(T, nh, nkv, seed=0)
     par = synth.rope_par(seed=0, yarn_table=synth.yarn_table() if yarn else None)
-    qr, kr = oracle.qk_rope_f16(q, k, par, 0, yarn=yarn)
+    qr, kr = oracle.qk_rope_f16(q, k, par, 0, yarn=yarn, sum_order=1)
     qd, kd = cu(q), cu(k)
     qo, ko = glue.qk_rope_f16(qd, kd, cu(par), 0, qo=torch.empty_like(qd), ko=torch.empty_like(kd), yarn=yarn)
     assert same(qo, qr) and same(ko, kr) and same(qd, q)
@@ -324,7 +324,7 @@ def test_layer_glue_sequence():
     x, q, k = cu(x0), cu(q0), cu(k0)
     h16 = torch.empty_like(x); yq = torch.empty(T * I // 32 * 36, dtype=torch.uint8, device=DEV)
     L(x, cu(r0), q, k, cu(g0), cu(u0), h16, yq, pos0=11)
-    xo, ho = oracle.add_rms_f16(x0, w, 1e-6, r0); qo, ko = oracle.qk_rope_f16(q0, k0, par, 11)
+    xo, ho = oracle.add_rms_f16(x0, w, 1e-6, r0); qo, ko = oracle.qk_rope_f16(q0, k0, par, 11, sum_order=1)
     assert same(x, xo) and same(h16, ho) and same(q, qo) and same(k, ko)
     d, s, q_ = oracle.q8_split(yq.cpu().numpy()); d1, s1, q1 = oracle.q8_split(oracle.swiglu_q8_1(g0.reshape(-1), u0.reshape(-1), sum_order=1))
     assert same(d, d1) and np.array_equal(q_, q1)
