@@ -119,14 +119,34 @@ def single_op_lines(torch, dev, peak):
     O = q3m_ops.Ops(dev)
     out = {}
 
-    def timed(fn, reps=20, rot=1):
+    def timed(fn, reps=9, rot=1, inner=10):
+        """per-launch seconds: `inner` launches back to back between two events (the queue never runs dry, as inside a model's
+        layer loop), median and minimum over `reps` such batches"""
         for i in range(3): fn(i % rot)
         torch.cuda.synchronize(dev)
         ts = []
-        for i in range(reps):
+        for r in range(reps):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(); fn(i % rot); b.record(); b.synchronize(); ts.append(a.elapsed_time(b) * 1e-3)
+            a.record()
+            for i in range(inner): fn((r * inner + i) % rot)
+            b.record(); b.synchronize(); ts.append(a.elapsed_time(b) * 1e-3 / inner)
         return float(np.median(ts)), float(np.min(ts))
+
+    def graphed(fn, launches=200):
+        """per-launch seconds of `launches` launches captured in one CUDA graph (no host launch cost between them)"""
+        try:
+            st = torch.cuda.Stream(dev)
+            with torch.cuda.stream(st):
+                fn(0); st.synchronize()
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=st):
+                    for i in range(launches): fn(i)
+                gr.replay(); st.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(st); gr.replay(); b.record(st); b.synchronize()
+            return a.elapsed_time(b) * 1e-3 / launches
+        except Exception as e:     # (capture refused: report why, keep the bench alive)
+            return f'{type(e).__name__}: {e}'[:160]
 
     def line(name, nbytes, sec, units, unit):
         med, mn = sec
@@ -139,8 +159,11 @@ def single_op_lines(torch, dev, peak):
         rot = 8 if T <= 4096 else 1
         xs = [torch.randn(T, 2048, device=dev, generator=g) for _ in range(rot)]; d = torch.randn(T, 2048, device=dev, generator=g)
         nw = 1 + 0.05 * torch.randn(2048, device=dev, generator=g); h = torch.empty(T, 2048, device=dev); h16 = torch.empty(T, 2048, dtype=torch.float16, device=dev)
-        sec = timed(lambda i: O.add_rms16(xs[i], nw, 1e-6, h16, T, 2048, d=d, S=1, h=h), reps=200 if T == 1 else 20, rot=rot)
+        sec = timed(lambda i: O.add_rms16(xs[i], nw, 1e-6, h16, T, 2048, d=d, S=1, h=h), rot=rot, inner=100 if T == 1 else 10)
         line(f'add_rms16_f32_h2048_T{T}', T * (4 * 8192 + 4096) + 8192, sec, T, 'tokens_per_s')
+        if T == 1:
+            gs = graphed(lambda i: O.add_rms16(xs[i % rot], nw, 1e-6, h16, T, 2048, d=d, S=1, h=h))
+            out[f'add_rms16_f32_h2048_T{T}']['us_in_cuda_graph'] = gs * 1e6 if isinstance(gs, float) else gs
         del xs, d, h, h16
     # config 2: q/k norm + RoPE fp16, T = 4096, 32 + 4 heads (75 MB: 4 rotating copies)
     T = 4096

@@ -37,15 +37,18 @@ __global__ void __launch_bounds__(EMB_WARPS * 32) emb_q4k_kernel(const uint8_t *
         const uint32_t sc1 = (s_hi & 0xfu) | ((s_lo >> 6) << 4), m1 = (s_hi >> 4) | ((s_mid >> 6) << 4);
         const float dl0 = fmul(dd.x, (float)sc0), ml0 = fmul(dd.y, (float)m0);
         const float dl1 = fmul(dd.x, (float)sc1), ml1 = fmul(dd.y, (float)m1);
+        // nibble c of a word as a float: its byte is placed under the exponent of 2^23 (one byte permute), then 2^23 is
+        // subtracted: exact for 0 .. 15, and two operations instead of shift, mask and convert
+        const uint32_t n0 = (w0 >> nib) & 0x0f0f0f0fu, n1 = (w1 >> nib) & 0x0f0f0f0fu;
         float4 y0, y1;
-        y0.x = fsub(fmul(dl0, (float)((w0 >> nib) & 15u)), ml0);
-        y0.y = fsub(fmul(dl0, (float)((w0 >> (8 + nib)) & 15u)), ml0);
-        y0.z = fsub(fmul(dl0, (float)((w0 >> (16 + nib)) & 15u)), ml0);
-        y0.w = fsub(fmul(dl0, (float)((w0 >> (24 + nib)) & 15u)), ml0);
-        y1.x = fsub(fmul(dl1, (float)((w1 >> nib) & 15u)), ml1);
-        y1.y = fsub(fmul(dl1, (float)((w1 >> (8 + nib)) & 15u)), ml1);
-        y1.z = fsub(fmul(dl1, (float)((w1 >> (16 + nib)) & 15u)), ml1);
-        y1.w = fsub(fmul(dl1, (float)((w1 >> (24 + nib)) & 15u)), ml1);
+        y0.x = fsub(fmul(dl0, fsub(__uint_as_float(__byte_perm(n0, 0x4b000000u, 0x7440)), 8388608.0f)), ml0);
+        y0.y = fsub(fmul(dl0, fsub(__uint_as_float(__byte_perm(n0, 0x4b000000u, 0x7441)), 8388608.0f)), ml0);
+        y0.z = fsub(fmul(dl0, fsub(__uint_as_float(__byte_perm(n0, 0x4b000000u, 0x7442)), 8388608.0f)), ml0);
+        y0.w = fsub(fmul(dl0, fsub(__uint_as_float(__byte_perm(n0, 0x4b000000u, 0x7443)), 8388608.0f)), ml0);
+        y1.x = fsub(fmul(dl1, fsub(__uint_as_float(__byte_perm(n1, 0x4b000000u, 0x7440)), 8388608.0f)), ml1);
+        y1.y = fsub(fmul(dl1, fsub(__uint_as_float(__byte_perm(n1, 0x4b000000u, 0x7441)), 8388608.0f)), ml1);
+        y1.z = fsub(fmul(dl1, fsub(__uint_as_float(__byte_perm(n1, 0x4b000000u, 0x7442)), 8388608.0f)), ml1);
+        y1.w = fsub(fmul(dl1, fsub(__uint_as_float(__byte_perm(n1, 0x4b000000u, 0x7443)), 8388608.0f)), ml1);
         float * o = x + (size_t)t * N + (size_t)b * 256 + 4 * lane;
         __stcs(reinterpret_cast<float4 *>(o), y0);
         __stcs(reinterpret_cast<float4 *>(o + 128), y1);

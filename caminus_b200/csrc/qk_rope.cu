@@ -7,7 +7,7 @@
 // out[j] = fma(y1[j], c, -(y1[j + 64] s)), out[j + 64] = fma(y1[j + 64], c, y1[j] s); stored as fp16.
 //
 // Mapping: one thread block per token, looping over tokens. The token's heads are brought into shared memory with cp.async
-// (16 bytes per thread, two stages: the next token's copy flies while this one is computed). The 64 cos / sin of a
+// (16 bytes per thread, three stages: the next two tokens' copies fly while this one is computed). The 64 cos / sin of a
 // position are computed once per token (64 threads) and shared by all of its heads; the reference recomputes them in every
 // (token, head) workgroup. A half-warp owns a head: lane l holds dims 4l .. 4l + 3 and 64 + 4l .. 64 + 4l + 3, i.e. complete
 // rotation pairs, so the rotation needs no exchange.
@@ -17,6 +17,9 @@
 // on a kernel that is instruction-bound; the sum is one input of a tolerance-gated fp16 result.) Every other statement is
 // the reference's.
 #include "cam_common.cuh"
+
+#include <cstdio>
+#include <cstdlib>
 
 namespace {
 
@@ -47,16 +50,21 @@ template <> struct In<uint16_t> {
 // T: the input type. CACHE: the reference's signature (fp32 qkv rows in, q16 and the cache row's K | V halves out).
 // P: heads per half-warp and round: a warp takes 2 P heads of a token at a time, reduces them all, then ONE pass of the
 // scale's square root and divisions serves all of them (lane j computes head j's), instead of one per head.
-template <typename T, bool CACHE, int P>
+// ONE: the block's warps cover the token's heads in exactly one round (H = 2 P warps): no head loop and no bounds tests, and
+// everything that depends only on the head (offsets in the stage and in the output, the weight row) is computed before
+// the token loop.
+constexpr int ROPE_STAGES = 3;        // tokens in flight per block: two copies fly while one token is computed
+
+template <typename T, bool CACHE, int P, bool ONE>
 __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int nh = A.nh, nkv = A.nkv, H = nh + nkv;
     const int in_heads = CACHE ? nh + 2 * nkv : H;                       // heads staged per token
     const int stage_bytes = in_heads * 128 * (int)sizeof(T);
-    float * wq = reinterpret_cast<float *>(smem);                        // [128] | wk [128] | freq [64] | rc [2][64] | rs [2][64]
-    float * wk = wq + 128, * freq = wk + 128, * rc = freq + 64, * rs = rc + 128;
-    unsigned char * stage = smem + (128 + 128 + 64 + 128 + 128) * 4;
+    float * wq = reinterpret_cast<float *>(smem);                        // [128] | wk [128] | freq [64] | rc [S][64] | rs [S][64]
+    float * wk = wq + 128, * freq = wk + 128, * rc = freq + 64, * rs = rc + 64 * ROPE_STAGES;
+    unsigned char * stage = smem + (128 + 128 + 64 + 2 * 64 * ROPE_STAGES) * 4;
     const float eps = __ldg(A.par + 257);
 
     if (tid < 128) { wq[tid] = __ldg(A.par + tid); wk[tid] = __ldg(A.par + 128 + tid); }
@@ -85,29 +93,47 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
         rs[buf * 64 + tid] = A.yarn ? fmul(sn, mscale) : sn;
     };
 
-    const int t0 = blockIdx.x;
-    issue(t0, 0);
-    if (tid < 64 && t0 < A.n) tables(t0, 0);
-    int st = 0;
     const int hw = lane >> 4, l16 = lane & 15;
     const int xoff = 4 * l16 * (int)sizeof(T);
-    for (int t = t0; t < A.n; t += gridDim.x, st ^= 1) {
-        const int tn = t + gridDim.x;
-        issue(tn, st ^ 1);
-        if (tid < 64 && tn < A.n) tables(tn, st ^ 1);
-        cp_async_wait<1>();
+    // head-only quantities of the ONE form (head hy_p = 2 (warp P + p) + hw)
+    int soff[P], ooff[P];
+    const float * wrow[P];
+    bool isq_[P];
+#pragma unroll
+    for (int p = 0; p < P; p++) {
+        const int hy = 2 * (warp * P + p) + hw;
+        isq_[p] = hy < nh;
+        soff[p] = hy * 128 * (int)sizeof(T) + xoff;
+        ooff[p] = (isq_[p] ? hy : hy - nh) * 128 + 4 * l16;
+        wrow[p] = (isq_[p] ? wq : wk) + 4 * l16;
+    }
+
+    const int t0 = blockIdx.x, g = gridDim.x;
+#pragma unroll
+    for (int k = 0; k < ROPE_STAGES - 1; k++) {
+        issue(t0 + k * g, k);
+        if (tid < 64 && t0 + k * g < A.n) tables(t0 + k * g, k);
+    }
+    int st = 0;
+    for (int t = t0; t < A.n; t += g, st = st + 1 == ROPE_STAGES ? 0 : st + 1) {
+        const int tn = t + (ROPE_STAGES - 1) * g, sn_ = st == 0 ? ROPE_STAGES - 1 : st - 1;      // the stage freed by the previous token
+        issue(tn, sn_);
+        if (tid < 64 && tn < A.n) tables(tn, sn_);
+        cp_async_wait<ROPE_STAGES - 1>();
         __syncthreads();
         const unsigned char * s = stage + st * stage_bytes;
         const float4 c4 = *reinterpret_cast<const float4 *>(rc + st * 64 + 4 * l16), s4 = *reinterpret_cast<const float4 *>(rs + st * 64 + 4 * l16);
         const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
         const int pos = A.pos0 + t;
-        for (int h0 = 2 * warp * P; h0 < H; h0 += 2 * nwarps * P) {        // this warp's heads h0 .. h0 + 2 P - 1 (uniform per warp)
+        uint16_t * const qbase = A.out0 + (size_t)t * nh * 128;
+        uint16_t * const kbase = CACHE ? A.out1 + (size_t)pos * 2 * nkv * 128 : A.out1 + (size_t)t * nkv * 128;
+        for (int h0 = 2 * warp * P; h0 < H; h0 += 2 * nwarps * P) {        // this warp's heads h0 .. h0 + 2 P - 1 (ONE: a single round)
             float x[P][8], tot[P];
 #pragma unroll
             for (int p = 0; p < P; p++) {
                 const int hy = h0 + 2 * p + hw;
-                if (hy < H) {
-                    const unsigned char * hp = s + hy * 128 * (int)sizeof(T) + xoff;       // q heads then k heads, in both input forms
+                if (ONE || hy < H) {
+                    const unsigned char * hp = ONE ? s + soff[p] : s + hy * 128 * (int)sizeof(T) + xoff;   // q heads then k heads
                     float lo[4], hi[4];
                     In<T>::get4(hp, lo);
                     In<T>::get4(hp + 64 * sizeof(T), hi);
@@ -138,9 +164,9 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
             for (int p = 0; p < P; p++) {
                 const float scale = __shfl_sync(CAM_FULL, scale_mine, 2 * p + hw);
                 const int hy = h0 + 2 * p + hw;
-                if (hy < H) {
-                    const bool isq = hy < nh;
-                    const float * wn = (isq ? wq : wk) + 4 * l16;
+                if (ONE || hy < H) {
+                    const bool isq = ONE ? isq_[p] : hy < nh;
+                    const float * wn = ONE ? wrow[p] : (isq ? wq : wk) + 4 * l16;
                     const float4 wlo = *reinterpret_cast<const float4 *>(wn), whi = *reinterpret_cast<const float4 *>(wn + 64);
                     const float wl[4] = {wlo.x, wlo.y, wlo.z, wlo.w}, wh[4] = {whi.x, whi.y, whi.z, whi.w};
                     float ylo[4], yhi[4];
@@ -150,18 +176,15 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
                         ylo[c] = ffma(x0, cc[c], -fmul(x1, sn[c]));
                         yhi[c] = ffma(x1, cc[c], fmul(x0, sn[c]));
                     }
-                    uint16_t * o;
-                    if (isq) o = A.out0 + ((size_t)t * nh + hy) * 128;
-                    else if (CACHE) o = A.out1 + (size_t)pos * 2 * nkv * 128 + (size_t)(hy - nh) * 128;
-                    else o = A.out1 + ((size_t)t * nkv + (hy - nh)) * 128;
-                    st64_stream(o + 4 * l16, make_uint2(f2_to_h2(ylo[0], ylo[1]), f2_to_h2(ylo[2], ylo[3])));
-                    st64_stream(o + 64 + 4 * l16, make_uint2(f2_to_h2(yhi[0], yhi[1]), f2_to_h2(yhi[2], yhi[3])));
+                    uint16_t * o = (isq ? qbase : kbase) + (ONE ? ooff[p] : (isq ? hy : hy - nh) * 128 + 4 * l16);
+                    st64_stream(o, make_uint2(f2_to_h2(ylo[0], ylo[1]), f2_to_h2(ylo[2], ylo[3])));
+                    st64_stream(o + 64, make_uint2(f2_to_h2(yhi[0], yhi[1]), f2_to_h2(yhi[2], yhi[3])));
                 }
             }
         }
         if (CACHE) {      // v: copied as fp16 into the row's V half
             const float * vs = reinterpret_cast<const float *>(s) + (size_t)H * 128;
-            uint16_t * vo = A.out1 + (size_t)pos * 2 * nkv * 128 + (size_t)nkv * 128;
+            uint16_t * vo = kbase + (size_t)nkv * 128;
             for (int c = tid; c < nkv * 32; c += blockDim.x) {
                 const float4 v = *reinterpret_cast<const float4 *>(vs + 4 * c);
                 st64_stream(vo + 4 * c, make_uint2(f2_to_h2(v.x, v.y), f2_to_h2(v.z, v.w)));
@@ -175,6 +198,10 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
 // warps per block (4 .. 12) and heads per half-warp and round (1 .. 4): the pair with the fewest idle half-warp slots over a
 // token's H heads; among equals the most heads per round (one scale computation serves 2 P heads), then the most warps
 void pick_shape(int H, int & warps, int & P) {
+    if (const char * e = getenv("CAMINUS_B200_ROPE_SHAPE")) {      // "warps,P": overrides the choice (tuning)
+        int w = 0, p = 0;
+        if (sscanf(e, "%d,%d", &w, &p) == 2 && w >= 4 && w <= 12 && p >= 1 && p <= 4) { warps = w; P = p; return; }
+    }
     int waste = 1 << 30;
     warps = 8; P = 1;
     for (int p = 4; p >= 1; p--)
@@ -185,12 +212,12 @@ void pick_shape(int H, int & warps, int & P) {
         }
 }
 
-template <typename T, bool CACHE, int P>
+template <typename T, bool CACHE, int P, bool ONE>
 int launch_rope_p(const RopeArgs & A, int warps, size_t smem, cudaStream_t stream) {
-    const cudaError_t e = cudaFuncSetAttribute(qk_rope_kernel<T, CACHE, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    const cudaError_t e = cudaFuncSetAttribute(qk_rope_kernel<T, CACHE, P, ONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
-    const int grid = cam_resident_grid(qk_rope_kernel<T, CACHE, P>, warps * 32, smem, A.n);
-    qk_rope_kernel<T, CACHE, P><<<grid, warps * 32, smem, stream>>>(A);
+    const int grid = cam_resident_grid(qk_rope_kernel<T, CACHE, P, ONE>, warps * 32, smem, A.n);
+    qk_rope_kernel<T, CACHE, P, ONE><<<grid, warps * 32, smem, stream>>>(A);
     return (int)cudaGetLastError();
 }
 
@@ -198,16 +225,18 @@ template <typename T, bool CACHE>
 int launch_rope(const RopeArgs & A, cudaStream_t stream) {
     const int H = A.nh + A.nkv;
     const int in_heads = CACHE ? A.nh + 2 * A.nkv : H;
-    const size_t smem = (128 + 128 + 64 + 128 + 128) * 4 + 2 * (size_t)in_heads * 128 * sizeof(T);
+    const size_t smem = (128 + 128 + 64 + 2 * 64 * ROPE_STAGES) * 4 + ROPE_STAGES * (size_t)in_heads * 128 * sizeof(T);
     if (smem > 227 * 1024) return CAM_ERR_SHAPE;
     int warps, P;
     pick_shape(H, warps, P);
+    const bool one = H == 2 * warps * P;
+#define CAM_ROPE_CASE(PV) \
+    case PV: return one ? launch_rope_p<T, CACHE, PV, true>(A, warps, smem, stream) : launch_rope_p<T, CACHE, PV, false>(A, warps, smem, stream);
     switch (P) {
-        case 1: return launch_rope_p<T, CACHE, 1>(A, warps, smem, stream);
-        case 2: return launch_rope_p<T, CACHE, 2>(A, warps, smem, stream);
-        case 3: return launch_rope_p<T, CACHE, 3>(A, warps, smem, stream);
-        default: return launch_rope_p<T, CACHE, 4>(A, warps, smem, stream);
+        CAM_ROPE_CASE(1) CAM_ROPE_CASE(2) CAM_ROPE_CASE(3)
+        default: return one ? launch_rope_p<T, CACHE, 4, true>(A, warps, smem, stream) : launch_rope_p<T, CACHE, 4, false>(A, warps, smem, stream);
     }
+#undef CAM_ROPE_CASE
 }
 
 int check_common(int n, int nh, int nkv, const void * par, int pos0) {
