@@ -53,24 +53,21 @@ CAM_DEV float ref_total_f16(float (&a)[8], int lane) {
 // Q35: x = x + d (one addend). Otherwise the weighted slots of q3p_add_rms16: acc from 0 in slot order.
 constexpr int RMS_WARPS = 4;
 
+CAM_DEV float4 add4(float4 a, float4 b) { return make_float4(fadd(a.x, b.x), fadd(a.y, b.y), fadd(a.z, b.z), fadd(a.w, b.w)); }
+CAM_DEV float4 fma4(float w, float4 d, float4 acc) { return make_float4(ffma(w, d.x, acc.x), ffma(w, d.y, acc.y), ffma(w, d.z, acc.z), ffma(w, d.w, acc.w)); }
+
+// the generic-N path's per-chunk addend (one chunk at a time)
 CAM_DEV float4 slot_add(float4 xv, const float * __restrict__ dr, const float * __restrict__ wr, int S, int N, int i, bool q35) {
-    if (q35) {
-        const float4 dv = __ldg(reinterpret_cast<const float4 *>(dr + i));
-        return make_float4(fadd(xv.x, dv.x), fadd(xv.y, dv.y), fadd(xv.z, dv.z), fadd(xv.w, dv.w));
-    }
+    if (q35) return add4(xv, __ldg(reinterpret_cast<const float4 *>(dr + i)));
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     for (int sl = 0; sl < S; sl++) {
         const float4 dv = __ldg(reinterpret_cast<const float4 *>(dr + (size_t)sl * N + i));
-        if (wr) {
-            const float w = __ldg(wr + sl);
-            acc = make_float4(ffma(w, dv.x, acc.x), ffma(w, dv.y, acc.y), ffma(w, dv.z, acc.z), ffma(w, dv.w, acc.w));
-        } else acc = make_float4(fadd(acc.x, dv.x), fadd(acc.y, dv.y), fadd(acc.z, dv.z), fadd(acc.w, dv.w));
+        acc = wr ? fma4(__ldg(wr + sl), dv, acc) : add4(acc, dv);
     }
-    return make_float4(fadd(xv.x, acc.x), fadd(xv.y, acc.y), fadd(xv.z, acc.z), fadd(xv.w, acc.w));
+    return add4(xv, acc);
 }
 
-CAM_DEV void norm_store(float4 xv, float scale, const float * __restrict__ nw, float * hr, uint16_t * h16r, int i) {
-    const float4 wv = __ldg(reinterpret_cast<const float4 *>(nw + i));
+CAM_DEV void norm_store(float4 xv, float scale, float4 wv, float * hr, uint16_t * h16r, int i) {
     const float4 v = make_float4(fmul(fmul(xv.x, scale), wv.x), fmul(fmul(xv.y, scale), wv.y), fmul(fmul(xv.z, scale), wv.z),
                                  fmul(fmul(xv.w, scale), wv.w));
     if (hr) __stcs(reinterpret_cast<float4 *>(hr + i), v);
@@ -82,9 +79,14 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) add_rms_f32_kernel(float * __r
                                                                      const float * __restrict__ w, int S, const float * __restrict__ nw,
                                                                      float eps, float * __restrict__ h, uint16_t * __restrict__ h16,
                                                                      int N, int n, int q35) {
+    __shared__ __align__(16) float snw[CH > 0 ? 128 * CH : 4];          // the norm weights, staged once per block (CH > 0)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nch = CH > 0 ? CH : N >> 7;
     const bool add = q35 ? d != nullptr : S > 0;
+    if (CH > 0) {
+        for (int i = threadIdx.x * 4; i < 128 * CH; i += RMS_WARPS * 128) *reinterpret_cast<float4 *>(snw + i) = __ldg(reinterpret_cast<const float4 *>(nw + i));
+        __syncthreads();
+    }
     for (int t = blockIdx.x * RMS_WARPS + warp; t < n; t += gridDim.x * RMS_WARPS) {
         float * xr = x + (size_t)t * N;
         const float * dr = d ? d + (size_t)t * (q35 ? 1 : S) * N : nullptr;
@@ -93,15 +95,39 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) add_rms_f32_kernel(float * __r
         uint16_t * h16r = h16 + (size_t)t * N;
         float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
         if (CH > 0) {
+            // every load of a phase is issued before any of its values is used: a warp keeps the whole row in flight
             float4 xv[CH > 0 ? CH : 1];
 #pragma unroll
             for (int m = 0; m < CH; m++) xv[m] = *reinterpret_cast<const float4 *>(xr + 4 * lane + 128 * m);
             if (add) {
+                if (q35 || (S == 1 && !wr)) {        // one addend: x + d (q35p), x + (0 + d) (q3p's accumulator from 0)
+                    float4 dv[CH > 0 ? CH : 1];
 #pragma unroll
-                for (int m = 0; m < CH; m++) {
-                    xv[m] = slot_add(xv[m], dr, wr, S, N, 4 * lane + 128 * m, q35);
-                    *reinterpret_cast<float4 *>(xr + 4 * lane + 128 * m) = xv[m];
+                    for (int m = 0; m < CH; m++) dv[m] = __ldg(reinterpret_cast<const float4 *>(dr + 4 * lane + 128 * m));
+#pragma unroll
+                    for (int m = 0; m < CH; m++) xv[m] = add4(xv[m], q35 ? dv[m] : add4(make_float4(0.0f, 0.0f, 0.0f, 0.0f), dv[m]));
+                } else {                             // the slots in order, each slot's row loaded whole
+                    float4 acc[CH > 0 ? CH : 1];
+#pragma unroll
+                    for (int m = 0; m < CH; m++) acc[m] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    for (int sl = 0; sl < S; sl++) {
+                        float4 dv[CH > 0 ? CH : 1];
+#pragma unroll
+                        for (int m = 0; m < CH; m++) dv[m] = __ldg(reinterpret_cast<const float4 *>(dr + (size_t)sl * N + 4 * lane + 128 * m));
+                        if (wr) {
+                            const float ws = __ldg(wr + sl);
+#pragma unroll
+                            for (int m = 0; m < CH; m++) acc[m] = fma4(ws, dv[m], acc[m]);
+                        } else {
+#pragma unroll
+                            for (int m = 0; m < CH; m++) acc[m] = add4(acc[m], dv[m]);
+                        }
+                    }
+#pragma unroll
+                    for (int m = 0; m < CH; m++) xv[m] = add4(xv[m], acc[m]);
                 }
+#pragma unroll
+                for (int m = 0; m < CH; m++) *reinterpret_cast<float4 *>(xr + 4 * lane + 128 * m) = xv[m];
             }
 #pragma unroll
             for (int m = 0; m < CH; m++) {
@@ -112,7 +138,8 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) add_rms_f32_kernel(float * __r
             const float tot = ref_total_f32(a, lane);
             const float scale = cam_rsqrt(fadd(fdiv(tot, (float)N), eps));
 #pragma unroll
-            for (int m = 0; m < CH; m++) norm_store(xv[m], scale, nw, hr, h16r, 4 * lane + 128 * m);
+            for (int m = 0; m < CH; m++)
+                norm_store(xv[m], scale, *reinterpret_cast<const float4 *>(snw + 4 * lane + 128 * m), hr, h16r, 4 * lane + 128 * m);
         } else {
             for (int m = 0; m < nch; m += 2) {                 // (N is a multiple of 256: chunks come in pairs b = 0, 1)
 #pragma unroll
@@ -128,10 +155,63 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) add_rms_f32_kernel(float * __r
             const float scale = cam_rsqrt(fadd(fdiv(tot, (float)N), eps));
             for (int m = 0; m < nch; m++) {      // (each lane reads back what it wrote itself)
                 const int i = 4 * lane + 128 * m;
-                norm_store(*reinterpret_cast<const float4 *>(xr + i), scale, nw, hr, h16r, i);
+                norm_store(*reinterpret_cast<const float4 *>(xr + i), scale, __ldg(reinterpret_cast<const float4 *>(nw + i)), hr, h16r, i);
             }
         }
     }
+}
+
+// A few rows (decode: T = 1): one block of 256 threads per row with the reference's own mapping (thread tid owns
+// tid + 256 j), so that a row's loads are spread over 8 warps and its latency is one trip to memory, not sixteen
+// loads deep in one warp. N <= 2048.
+__global__ void __launch_bounds__(256) add_rms_f32_row_kernel(float * __restrict__ x, const float * __restrict__ d, const float * __restrict__ w,
+                                                              int S, const float * __restrict__ nw, float eps, float * __restrict__ h,
+                                                              uint16_t * __restrict__ h16, int N, int q35) {
+    __shared__ float part[8];
+    const int tid = threadIdx.x, lane = tid & 31, wave = tid >> 5, NI = N >> 8, t = blockIdx.x;
+    float * xr = x + (size_t)t * N;
+    const float * dr = d ? d + (size_t)t * (q35 ? 1 : S) * N : nullptr;
+    const float * wr = w ? w + (size_t)t * S : nullptr;
+    const bool add = q35 ? d != nullptr : S > 0;
+    float xv[8], wv[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+        if (j < NI) { xv[j] = xr[tid + 256 * j]; wv[j] = __ldg(nw + tid + 256 * j); }
+    if (add) {
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (j < NI) {
+                if (q35) xv[j] = fadd(xv[j], __ldg(dr + tid + 256 * j));
+                else {
+                    float acc = 0.0f;
+                    for (int sl = 0; sl < S; sl++) {
+                        const float dv = __ldg(dr + (size_t)sl * N + tid + 256 * j);
+                        acc = wr ? ffma(__ldg(wr + sl), dv, acc) : fadd(acc, dv);
+                    }
+                    xv[j] = fadd(xv[j], acc);
+                }
+                xr[tid + 256 * j] = xv[j];
+            }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+        if (j < NI) ss = ffma(xv[j], xv[j], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss = fadd(ss, __shfl_xor_sync(CAM_FULL, ss, o));
+    if (lane == 0) part[wave] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int q = 0; q < 8; q++) tot = fadd(tot, part[q]);
+    const float scale = cam_rsqrt(fadd(fdiv(tot, (float)N), eps));
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+        if (j < NI) {
+            const float v = fmul(fmul(xv[j], scale), wv[j]);
+            if (h) h[(size_t)t * N + tid + 256 * j] = v;
+            h16[(size_t)t * N + tid + 256 * j] = f_to_h(v);
+        }
 }
 
 // ---- fp16 rows, staged through shared memory with cp.async ------------------------------------------------------------------
@@ -325,6 +405,10 @@ int launch_f16(uint16_t * x, const uint16_t * d, const float * nw, float eps, ui
 int launch_f32(float * x, const float * d, const float * w, int S, const float * nw, float eps, float * h, uint16_t * h16, int N, int n,
                int q35, cudaStream_t stream) {
     if (n == 0) return CAM_OK;
+    if (N <= 2048 && n <= 2 * cam_sm_count()) {      // a few rows: a block per row
+        add_rms_f32_row_kernel<<<n, 256, 0, stream>>>(x, d, w, S, nw, eps, h, h16, N, q35);
+        return (int)cudaGetLastError();
+    }
     const long want = ((long)n + RMS_WARPS - 1) / RMS_WARPS;
 #define CAM_RMS_CASE(CHV)                                                                                              \
     case CHV:                                                                                                          \

@@ -36,9 +36,15 @@ def check(err):
     _lib.check(err)
 
 
+_torch = None
+
+
 def _current_stream():
-    import torch
-    return torch.cuda.current_stream().cuda_stream
+    global _torch
+    if _torch is None:
+        import torch
+        _torch = torch
+    return _torch.cuda.current_stream().cuda_stream
 
 
 def _arg(a):

@@ -15,6 +15,20 @@ YARN_MODULE = {False: 'q3m_prefill_yarn'}
 YARN_PAR = 2 * 128 + 2 + k3.YARN_TABLE_FLOATS      # q_norm | k_norm | theta_scale, eps | freq [64] | mscale
 
 
+class _On:
+    """`with _On(dev):` makes dev the current device for a launch; free when it already is (the common case)"""
+    __slots__ = ('dev', 'ctx')
+
+    def __init__(self, dev): self.dev, self.ctx = dev, None
+
+    def __enter__(self):
+        if self.dev.index is not None and torch.cuda.current_device() != self.dev.index:
+            self.ctx = torch.cuda.device(self.dev); self.ctx.__enter__()
+
+    def __exit__(self, *a):
+        if self.ctx is not None: self.ctx.__exit__(*a); self.ctx = None
+
+
 class Ops:
     def __init__(self, dev, module='q3m_prefill', q8=False, yarn=False):
         """yarn: the long-context mode: qk_rope reads the YaRN table after eps in par (YARN_PAR floats)"""
@@ -28,17 +42,17 @@ class Ops:
 
     # -- the glue ----------------------------------------------------------------------------------------------------------
     def emb(self, W, rb, vocab, toks, x, n, N):
-        with torch.cuda.device(self.dev):
+        with _On(self.dev):
             self.mod.q3p_emb((n,), (256,), W, I(rb), I(vocab), toks, x, I(N))
 
     def add_rms16(self, x, nw, eps, h16, n, N, d=None, w=None, S=0, h=None):
         if N % 256 or N > 2048: raise ValueError(f'q3m add_rms16: N {N} (a multiple of 256, <= 2048)')
-        with torch.cuda.device(self.dev):
+        with _On(self.dev):
             self.mod.q3p_add_rms16((n,), (256,), x, NULL if d is None else d, NULL if w is None else w, I(S), nw, F(eps),
                                    NULL if h is None else h, h16, I(N))
 
     def swiglu(self, g, u, y16, n):
-        with torch.cuda.device(self.dev):
+        with _On(self.dev):
             self.mod.q3p_swiglu((min(-(-n // 256), 4096),), (256,), g, u, y16, I(n))
 
     def _span(self, what, cache, pos0, n, nkv, rows):
@@ -58,5 +72,5 @@ class Ops:
             raise ValueError(f'q3m qk_rope: par needs {YARN_PAR if self.yarn else 2 * 128 + 2} fp32 values'
                              f'{" (q_norm | k_norm | theta_scale, eps | the YaRN table)" if self.yarn else ""}, not {par.numel()} {par.dtype}')
         if err is not None: raise ValueError('q3m qk_rope: err is the Q8 cache\'s word')
-        with torch.cuda.device(self.dev):
+        with _On(self.dev):
             self.ropemod.q3p_qk_rope((n, nh + nkv), (128,), qkv, I(ldq), I(nh), I(nkv), par, I(pos0), q16, cache)

@@ -328,3 +328,48 @@ def test_layer_glue_sequence():
     assert same(x, xo) and same(h16, ho) and same(q, qo) and same(k, ko)
     d, s, q_ = oracle.q8_split(yq.cpu().numpy()); d1, s1, q1 = oracle.q8_split(oracle.swiglu_q8_1(g0.reshape(-1), u0.reshape(-1), sum_order=1))
     assert same(d, d1) and np.array_equal(q_, q1)
+
+
+# ---- tensor-parallel RMSNorm (hidden sharded) ---------------------------------------------------------------------------------
+@pytest.mark.parametrize('T,N,G', [(300, 5120, 8), (64, 2048, 2), (1000, 5120, 4)])
+@pytest.mark.parametrize('add', [True, False])
+def test_tp_rmsnorm_pieces(T, N, G, add):
+    """the two kernels of the hidden-sharded norm on the G column shards of one row batch (all on this GPU): each shard's
+    partial and its apply are the oracle's bytes; the whole agrees with the unsharded kernel within 1e-5 relative (the
+    order of the sum over shards differs from the unsharded row sum)"""
+    from caminus_b200 import dist as D
+    x0, r0, w = synth.add_rms_inputs(T, N, seed=T + G, dtype=np.float16)
+    parts, shards = [], []
+    for r in range(G):
+        a, b = D.col_shard(N, r, G)
+        xs = np.ascontiguousarray(x0[:, a:b]); rs = np.ascontiguousarray(r0[:, a:b]) if add else None
+        norm = D.TPRmsNorm(cu(w[a:b]), N, 1e-6, all_reduce=lambda t: None)
+        ss = norm.partial(cu(xs), cu(rs) if add else None).clone()
+        assert same(ss, oracle.rms_partial_f16(xs, rs))
+        parts.append(ss); shards.append((a, b, xs, rs, norm))
+    tot = torch.zeros(T, device=DEV)
+    for ss in parts: tot += ss                                       # rank order, as a ring all-reduce would not guarantee
+    full_x, full_h = oracle.add_rms_f16(x0, w, 1e-6, r0 if add else None)
+    for a, b, xs, rs, norm in shards:
+        xd = cu(xs)
+        h16 = norm.apply(xd, tot, d=cu(rs) if add else None)
+        xo, ho = oracle.rms_apply_f16(xs, tot.cpu().numpy(), w[a:b], 1e-6, N, rs)
+        assert same(xd, xo) and same(h16, ho)
+        assert same(xd, full_x[:, a:b].copy())                       # the residual update does not depend on the sharding
+        ref = full_h[:, a:b].astype(np.float64)
+        assert (np.abs(h16.float().cpu().numpy() - ref) <= ulp16(ref) + 1e-5 * np.abs(ref).max()).all()
+
+
+def test_add_rms16_single_row_kernel_and_many_rows_agree(O):
+    """n <= 2 x multiprocessors takes the block-per-row kernel, more rows the warp-per-row kernel: the same bytes"""
+    g = np.random.default_rng(9); N = 2048; n = 700
+    x0 = (g.standard_normal((n, N)) * 3).astype(np.float32); dd = g.standard_normal((n, 2, N)).astype(np.float32)
+    ww = g.random((n, 2)).astype(np.float32); nw = (g.random(N) + 0.5).astype(np.float32)
+    outs = []
+    for rows in (n, 5):
+        x = cu(x0[:rows]); h = torch.zeros(rows, N, device=DEV); h16 = torch.zeros(rows, N, dtype=torch.float16, device=DEV)
+        O.add_rms16(x, cu(nw), 1e-6, h16, rows, N, d=cu(dd[:rows]), w=cu(ww[:rows]), S=2, h=h)
+        outs.append((x.cpu().numpy(), h.cpu().numpy(), h16.cpu().numpy()))
+    for a, b in zip(outs[0], outs[1]): assert same(a[:5], b)
+    xo, ho, h16o = oracle.add_rms16(x0[:5], nw, 1e-6, d=dd[:5], w=ww[:5], S=2)
+    assert same(outs[1][0], xo) and same(outs[1][1], ho) and same(outs[1][2], h16o)
