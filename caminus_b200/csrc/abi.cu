@@ -1,7 +1,9 @@
 // Library-wide entry points of the C ABI and the per-device cache of the multiprocessor count.
 #include "cam_common.cuh"
 
+#include <map>
 #include <mutex>
+#include <tuple>
 
 int cam_sm_count() {
     static std::mutex mu;
@@ -15,6 +17,21 @@ int cam_sm_count() {
         count[dev] = v;
     }
     return count[dev];
+}
+
+int cam_blocks_per_sm(const void * kernel, int threads, size_t smem) {
+    static std::mutex mu;
+    static std::map<std::tuple<int, const void *, int, size_t>, int> cache;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const auto key = std::make_tuple(dev, kernel, threads, smem);
+    std::lock_guard<std::mutex> lock(mu);
+    const auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+    cache[key] = per_sm;
+    return per_sm;
 }
 
 // The ABI's version: bumped when an entry's parameters change.

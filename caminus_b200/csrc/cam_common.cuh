@@ -108,10 +108,12 @@ int cam_sm_count();
 
 // A persistent grid: as many blocks as the device holds at once (so that no block waits for another to finish), capped by
 // the work. `want` = blocks that would each get one unit of work.
+// resident blocks per multiprocessor of a kernel at a block size and dynamic shared-memory size (cached per device)
+int cam_blocks_per_sm(const void * kernel, int threads, size_t smem);
+
 template <typename K>
 static inline int cam_resident_grid(K kernel, int threads, size_t smem, long want) {
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+    const int per_sm = cam_blocks_per_sm(reinterpret_cast<const void *>(kernel), threads, smem);
     const long cap = (long)cam_sm_count() * per_sm;
     return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
 }
