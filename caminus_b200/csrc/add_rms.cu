@@ -14,6 +14,8 @@
 // a butterfly step hold the same bits), without a block-wide barrier.
 #include "cam_common.cuh"
 
+#include <mutex>
+
 namespace {
 
 // ---- the reference's reduction on this file's two layouts ------------------------------------------------------------------
@@ -480,4 +482,55 @@ extern "C" int cam_rms_apply_f16(int n, void * x, const void * d, const float * 
     if (n < 0 || Ns < 8 || (Ns & 7) || Nfull < Ns || !x || !tot || !nw || !h16) return CAM_ERR_ARG;
     if (!cam_aligned16(x) || (d && !cam_aligned16(d)) || !cam_aligned16(nw) || !cam_aligned16(h16)) return CAM_ERR_ALIGN;
     return launch_f16<2>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, nullptr, tot, Ns, Nfull, n, (cudaStream_t)stream);
+}
+
+// ---- the two-kernel norm with its intermediate in the library's own static memory ------------------------------------------------
+// The partial / apply pair above hands the per-row sums of squares from the first kernel to the second through a
+// buffer the caller allocates. Some callers cannot allocate: a plugin that an engine hands fixed buffers sized at
+// start-up and forbids from touching the allocator (the reference's own rule for its wrappers: "nothing here allocates"),
+// or a process whose device memory is already fully carved up, where one more cudaMalloc fails or forces a synchronisation.
+// For them the sums live in this file-scope array, which every device that loads the library holds until it exits
+// (CAM_STATIC_ROWS floats = 256 KB).
+#define CAM_STATIC_ROWS 65536
+static __device__ __align__(256) float cam_static_ss[CAM_STATIC_ROWS];
+
+// The array's device address on the current device. In host code the name `cam_static_ss` is only a handle for the runtime,
+// not a device pointer: the address comes from cudaGetSymbolAddress, asked once per device with that device current.
+static int static_ss_address(float ** out) {
+    static std::mutex mu;
+    static float * addr[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return CAM_ERR_ARG;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[dev]) {
+        void * p = nullptr;
+        e = cudaGetSymbolAddress(&p, cam_static_ss);
+        if (e != cudaSuccess) return (int)e;
+        addr[dev] = static_cast<float *>(p);
+    }
+    *out = addr[dev];
+    return CAM_OK;
+}
+
+// cam_rms_norm_f16_static: x [n][N] fp16 (updated in place to fp16(x + d) when d is given), d fp16 (nullable), nw fp32 [N],
+// h16 fp16 [n][N] = the normed rows; N a multiple of 8; n <= 65536 rows per call (CAM_ERR_CAPACITY beyond: split the batch).
+// The same two launches and the same bytes as cam_rms_partial_f16 followed by cam_rms_apply_f16 with Ns = Nfull = N, with the
+// row sums in the library's static array instead of a caller's buffer. Calls no cudaMalloc / cudaFree and no allocating
+// routine. The first call on a device looks up the array's address (cudaGetSymbolAddress): make that first call outside any
+// stream capture. Every call on a device uses the same array and the array keeps the last call's sums: nothing in it has
+// to start at zero (the first kernel overwrites rows 0 .. n - 1 before the second reads them), but two calls whose kernels
+// can overlap on the GPU (different streams without an ordering between them) race on it: order them.
+extern "C" int cam_rms_norm_f16_static(int n, void * x, const void * d, const float * nw, float eps, void * h16, int N, void * stream) {
+    if (n < 0 || N < 8 || (N & 7) || !x || !nw || !h16) return CAM_ERR_ARG;
+    if (n > CAM_STATIC_ROWS) return CAM_ERR_CAPACITY;
+    if (!cam_aligned16(x) || (d && !cam_aligned16(d)) || !cam_aligned16(nw) || !cam_aligned16(h16)) return CAM_ERR_ALIGN;
+    if (n == 0) return CAM_OK;
+    float * ss = nullptr;
+    int r = static_ss_address(&ss);
+    if (r != CAM_OK) return r;
+    r = launch_f16<1>((uint16_t *)x, (const uint16_t *)d, nullptr, 0.0f, nullptr, ss, nullptr, N, N, n, (cudaStream_t)stream);
+    if (r != CAM_OK) return r;
+    return launch_f16<2>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, nullptr, ss, N, N, n, (cudaStream_t)stream);
 }

@@ -21,6 +21,7 @@ SIGNATURES = {
     'cam_add_rms_f16': [I, P, P, P, F, P, I, P],
     'cam_rms_partial_f16': [I, P, P, P, I, P],
     'cam_rms_apply_f16': [I, P, P, P, P, F, P, I, I, P],
+    'cam_rms_norm_f16_static': [I, P, P, P, F, P, I, P],
     'q3p_swiglu': [P, P, P, I, P],
     'gg_silu_mul': [P, P, P, I, P],
     'gg_quantize_q8_1': [P, P, I, P],

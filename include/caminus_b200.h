@@ -64,6 +64,16 @@ int cam_rms_partial_f16(int n, const void * x, const void * d, float * ss, int N
 int cam_rms_apply_f16(int n, void * x, const void * d, const float * tot, const float * nw, float eps, void * h16, int Ns,
                       int Nfull, void * stream);
 
+/* The partial / apply pair above as ONE call that allocates nothing: the per-row sums of squares that pass from the first
+ * kernel to the second live in a static device array inside the library (65536 floats, 256 KB per device that loads it)
+ * instead of a caller's buffer. For callers that must not allocate device memory: a plugin working in buffers its engine
+ * sized at start-up, or a process whose device memory is already fully handed out. x [n][N] fp16 (updated in place when d is
+ * given), d fp16 (nullable), nw fp32 [N], h16 fp16 [n][N]; N a multiple of 8; same bytes as the pair with Ns = Nfull = N.
+ * n > 65536 returns CAM_ERR_CAPACITY (split the batch). The first call on a device resolves the array's address: make it
+ * before any stream capture. All calls on a device share the array: calls that can overlap on the GPU race; order them.
+ * This entry has no counterpart in the reference. */
+int cam_rms_norm_f16_static(int n, void * x, const void * d, const float * nw, float eps, void * h16, int N, void * stream);
+
 /* y16[i] = fp16(silu(g[i]) * u[i]), i < n.
  * Replaces q3p_swiglu, kernels/q3m_prefill.hip:516-518; wrapper python/caminus/prefill/q3m_ops.py:106-107. */
 int q3p_swiglu(const float * g, const float * u, void * y16, int n, void * stream);
