@@ -249,6 +249,25 @@ def main():
     value = T * world / (total / args.steps)
 
     # end to end through host buffers (pinned): inputs copied in, the three launches, outputs copied back, every step
+    # the hidden-sharded RMSNorm (N > 1 only): this rank's hidden / N columns of all T rows, partial -> NCCL all-reduce of [T] fp32 -> apply
+    tp = None
+    if world > 1 and HIDDEN % (8 * world) == 0:
+        from caminus_b200 import dist as D
+        Ns = HIDDEN // world
+        xs = rn(T, Ns); ds = rn(T, Ns); hs = torch.empty_like(xs)
+        norm = D.TPRmsNorm(nw[:Ns].contiguous(), HIDDEN, 1e-6)
+        for _ in range(3): norm(xs, ds, hs)
+        barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record()
+        for _ in range(args.steps): norm(xs, ds, hs)
+        ev[1].record(); barrier()
+        tps = ev[0].elapsed_time(ev[1]) * 1e-3 / args.steps
+        t = torch.tensor([tps], device=dev, dtype=torch.float64); torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX); tps = float(t.item())
+        tp = {'us_per_step': tps * 1e6, 'tokens_per_s': T / tps, 'hbm_gbs_per_gpu': T * 4 * Ns * 2 / tps / 1e9,
+              'nvlink_bytes_per_rank': T * 4, 'note': f'hidden {HIDDEN} in {world} shards of {Ns}; every rank holds all {T} rows'}
+        del xs, ds, hs
+
     from caminus_b200 import host
     Te = min(T, args.e2e_rows)
     e2e = None
@@ -300,6 +319,7 @@ def main():
             'kernels': kern,
             'hbm_gbs_all_three': T * sum(BYTES_PER_TOKEN.values()) / (total / args.steps) / 1e9,
             'cpu_baseline': cpu,
+            'tp_rmsnorm': tp,
         }
         if args.ops: line['ops'] = single_op_lines(torch, dev, peak)
         print(json.dumps(line), flush=True)
