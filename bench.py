@@ -39,24 +39,55 @@ def peaks():
 
 
 class Clocks:
-    """samples nvidia-smi during the timed region"""
+    """samples the SM clock and the throttle reasons of one GPU during the timed region: NVML polled every 2 ms from a
+    thread (reads only), or `nvidia-smi -lms 20` when the NVML binding is missing"""
     Q = 'index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,' \
         'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap'
+    BITS = {'hw_slowdown': 0x8, 'hw_thermal_slowdown': 0x40, 'sw_thermal_slowdown': 0x20, 'sw_power_cap': 0x4}
 
     def __init__(self, index):
-        self.index, self.proc, self.path = index, None, None
+        self.index, self.proc, self.path, self.thread, self.stop_flag = index, None, None, None, False
+        self.sm, self.reasons, self.max_mhz = [], set(), None
+
+    def _poll(self, nv, h):
+        while not self.stop_flag:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                r = int(nv.nvmlDeviceGetCurrentClocksEventReasons(h)) if hasattr(nv, 'nvmlDeviceGetCurrentClocksEventReasons') \
+                    else int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                for name, bit in self.BITS.items():
+                    if r & bit: self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self):
         try:
+            import pynvml as nv
+            nv.nvmlInit()
+            vis = os.environ.get('CUDA_VISIBLE_DEVICES')
+            idx = int(vis.split(',')[self.index]) if vis and all(v.strip().isdigit() for v in vis.split(',')) else self.index
+            h = nv.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll, args=(nv, h), daemon=True); self.thread.start()
+            return
+        except Exception:
+            self.thread = None
+        try:
             f = tempfile.NamedTemporaryFile('w', suffix='.csv', delete=False); self.path = f.name
-            self.proc = subprocess.Popen(['nvidia-smi', f'--id={self.index}', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits', '-lms', '100'],
+            self.proc = subprocess.Popen(['nvidia-smi', f'--id={self.index}', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits', '-lms', '20'],
                                          stdout=f, stderr=subprocess.DEVNULL)
+            time.sleep(0.5)     # (the tool needs a moment before its first sample)
         except Exception:
             self.proc = None
 
     def stop(self):
+        if self.thread is not None:
+            self.stop_flag = True; self.thread.join(1.0)
+            if not self.sm: return {'sm_mhz': None, 'sm_max_mhz': self.max_mhz, 'reasons': ['no samples']}
+            return {'sm_mhz': float(np.median(self.sm)), 'sm_max_mhz': self.max_mhz, 'reasons': sorted(self.reasons), 'samples': len(self.sm), 'via': 'nvml'}
         if self.proc is None: return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try: self.proc.wait(timeout=5)
         except Exception: self.proc.kill()
@@ -71,7 +102,7 @@ class Clocks:
         try: os.unlink(self.path)
         except OSError: pass
         if not sm: return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['no samples']}
-        return {'sm_mhz': float(np.median(sm)), 'sm_max_mhz': float(max(mx)), 'reasons': sorted(reasons), 'samples': len(sm)}
+        return {'sm_mhz': float(np.median(sm)), 'sm_max_mhz': float(max(mx)), 'reasons': sorted(reasons), 'samples': len(sm), 'via': 'nvidia-smi'}
 
 
 def cpu_layer_glue(sample, threads):
