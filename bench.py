@@ -27,6 +27,10 @@ import numpy as np   # noqa: E402
 
 T_PER_GPU, HIDDEN, NH, NKV, INTER = 65536, 5120, 64, 8, 25600
 BYTES_PER_TOKEN = {'add_rms_f16': 4 * HIDDEN * 2, 'qk_rope_f16': (NH + NKV) * 128 * 2 * 2, 'swiglu_q8_1_f16': 2 * INTER * 2 + INTER // 32 * 36}
+# DRAM bytes per token row of the dominant kernel, from one ncu capture at T = 8192 (profiles/swiglu_q8_fast_kernel_T8192_I25600.md:
+# dram__bytes_read.sum + dram__bytes_write.sum = 838.95 + 217.91 MB); the traffic grows in proportion to the rows, so a launch
+# of T rows is scaled from it
+SWIGLU_DRAM_BYTES_PER_TOKEN = (838_954_496 + 217_908_736) / 8192
 METRIC = 'per-layer glue throughput (residual add + RMSNorm -> q/k norm + RoPE -> SwiGLU + Q8_1), tokens/s'
 
 
@@ -346,7 +350,8 @@ def main():
             'e2e': e2e,
             'gpu_launches': 3 * args.steps,
             'roofline': {'bound': 'hbm', 'kernel': 'swiglu_q8_fast_kernel<fp16> (SwiGLU + Q8_1)', 'achieved': ach, 'peak': peak, 'unit': 'GB/s',
-                         'frac': ach / peak, 'peak_source': which, 'frac_of_8tbs': ach / 8000.0, 'traffic': None},
+                         'frac': ach / peak, 'peak_source': which, 'frac_of_8tbs': ach / 8000.0, 'traffic': SWIGLU_DRAM_BYTES_PER_TOKEN * T,
+                         'traffic_note': 'bytes per launch, scaled by rows from an ncu capture at T = 8192', 'algorithmic_bytes': T * BYTES_PER_TOKEN[dom]},
             'kernels': kern,
             'hbm_gbs_all_three': T * sum(BYTES_PER_TOKEN.values()) / (total / args.steps) / 1e9,
             'cpu_baseline': cpu,
