@@ -1,0 +1,318 @@
+// The Coder / hyper-connection line's glue (the reference's kernels/prefill_glue.hip: pf_rms_mul, pf_hc_post_rms, pf_hc_post,
+// pf_hc_mean, pf_add_sum, pf_silu_bf16, pf_to_bf16; kernels/prefill_tp.hip: pf_swiglu; kernels/prefill_attn.hip: pf_qk_nr) and
+// the training line's forwards (kernels/core.hip: embedding_f32, rmsnorm_f32, silu_mul_bf16, residual3, cast_bf16;
+// kernels/fuse.hip: residual_slices_fwd).
+//
+// The row kernels keep the reference's own mapping: one block of 256 threads per row, thread tid owns elements
+// tid + 256 j, an fma chain over j, the 32-lane butterfly (16, 8, 4, 2, 1) and the eight wave sums added in order, so the sum
+// of squares has the reference's bits by construction. Elementwise kernels are grid-stride loops over coalesced elements.
+#include "cam_common.cuh"
+
+namespace {
+
+constexpr int ROW_MAX_NI = 32;       // row lengths up to 8192
+
+CAM_DEV uint16_t bf16_rne(float v) {       // prefill_glue.hip's to_bf16: round to nearest even, no NaN case
+    const uint32_t u = __float_as_uint(v);
+    return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+}
+CAM_DEV uint16_t bf16_nan(float f) {       // core.hip's f2bf: the same, NaN -> 0x7fc0
+    uint32_t u = __float_as_uint(f);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return 0x7fc0;
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+CAM_DEV float bf16_f(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
+CAM_DEV float cam_sigmoid(float v) { return fdiv(1.0f, fadd(1.0f, cam_expf(-v))); }
+
+// the block's sum over the threads' partial sums: wave butterfly, eight partials in order (every thread gets the total)
+CAM_DEV float block_total(float ss, float * part) {
+    const int lane = threadIdx.x & 31, wave = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss = fadd(ss, __shfl_xor_sync(CAM_FULL, ss, o));
+    if (lane == 0) part[wave] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int q = 0; q < 8; q++) tot = fadd(tot, part[q]);
+    return tot;
+}
+
+// MODE 0: pf_rms_mul. MODE 1: pf_hc_post_rms (x = res updated in place from b and inj). MODE 2: rmsnorm_f32 (out = y).
+template <int MODE>
+__global__ void __launch_bounds__(256) rms_rows_kernel(const float * x, const float * __restrict__ w, float * y,
+                                                       uint16_t * __restrict__ ybf, float * __restrict__ scl, int R, int wr, float eps, int K,
+                                                       const float * __restrict__ b, const float * __restrict__ inj, int HC, float rs) {
+    __shared__ float part[8];
+    const int tid = threadIdx.x;
+    for (int t = blockIdx.x; t < R; t += gridDim.x) {
+        const float * xr = x + (size_t)t * K;
+        const float * wv = w + (size_t)(MODE == 1 ? t % HC : MODE == 2 ? 0 : t % wr) * K;
+        float xv[ROW_MAX_NI];
+#pragma unroll
+        for (int j = 0; j < ROW_MAX_NI; j++)
+            if (tid + 256 * j < K) xv[j] = xr[tid + 256 * j];
+        float ss = 0.0f;
+        if (MODE == 1) {
+            const float p = fmul(cam_sigmoid(fmul(__ldg(inj + t), rs)), 2.0f);
+            const float * br = b + (size_t)(t / HC) * K;
+#pragma unroll
+            for (int j = 0; j < ROW_MAX_NI; j++)
+                if (tid + 256 * j < K) {
+                    xv[j] = ffma(__ldg(br + tid + 256 * j), p, xv[j]);
+                    const_cast<float *>(xr)[tid + 256 * j] = xv[j];
+                }
+        }
+#pragma unroll
+        for (int j = 0; j < ROW_MAX_NI; j++)
+            if (tid + 256 * j < K) ss = ffma(xv[j], xv[j], ss);
+        const float tot = block_total(ss, part);
+        const float scale = cam_rsqrt(fadd(fdiv(tot, (float)K), eps));
+        if (scl && tid == 0) scl[t] = scale;
+#pragma unroll
+        for (int j = 0; j < ROW_MAX_NI; j++)
+            if (tid + 256 * j < K) {
+                const float v = fmul(fmul(xv[j], scale), __ldg(wv + tid + 256 * j));
+                if (y) y[(size_t)t * K + tid + 256 * j] = v;
+                if (ybf) ybf[(size_t)t * K + tid + 256 * j] = bf16_rne(v);
+            }
+        __syncthreads();      // part[] is reused by the next row
+    }
+}
+
+__global__ void __launch_bounds__(256) hc_post_kernel(const float * __restrict__ b, const float * __restrict__ inj, float * res, int T, int HC, int D, float rs) {
+    const long n = (long)T * D;
+    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {
+        const int tt = (int)(i / D), ii = (int)(i - (long)tt * D);
+        const float bv = __ldg(b + i);
+        for (int h = 0; h < HC; h++) {
+            const float ph = fmul(cam_sigmoid(fmul(__ldg(inj + tt * HC + h), rs)), 2.0f);
+            const size_t o = (size_t)(tt * HC + h) * D + ii;
+            res[o] = ffma(bv, ph, res[o]);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) hc_mean_kernel(const float * __restrict__ x, const float * __restrict__ scl, const float * __restrict__ w,
+                                                      const float * __restrict__ g, float * __restrict__ out, int T, int HC, int D, float rs) {
+    const long n = (long)T * D;
+    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {
+        const int tt = (int)(i / D), ii = (int)(i - (long)tt * D);
+        float sum = 0.0f;
+        for (int h = 0; h < HC; h++) {
+            const size_t o = (size_t)(tt * HC + h) * D + ii;
+            const float xv = scl ? fmul(fmul(__ldg(x + o), __ldg(scl + tt * HC + h)), __ldg(w + (size_t)h * D + ii)) : __ldg(x + o);
+            sum = ffma(xv, cam_sigmoid(__ldg(g + o)), sum);
+        }
+        out[i] = fmul(rs, sum);
+    }
+}
+
+// elementwise ops selected at compile time
+enum { EW_ADD_SUM, EW_SWIGLU, EW_RESIDUAL3, EW_CAST_BF16 };
+template <int OP>
+__global__ void __launch_bounds__(256) ew_kernel(const void * __restrict__ a, const void * __restrict__ b, const void * __restrict__ c, void * y, long n) {
+    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {
+        if (OP == EW_ADD_SUM) { float * yy = (float *)y; yy[i] = fadd(yy[i], fadd(__ldg((const float *)a + i), __ldg((const float *)b + i))); }
+        if (OP == EW_SWIGLU) ((float *)y)[i] = fmul(cam_silu(__ldg((const float *)a + i)), __ldg((const float *)b + i));
+        if (OP == EW_RESIDUAL3)
+            ((float *)y)[i] = fadd(fadd(__ldg((const float *)a + i), bf16_f(__ldg((const uint16_t *)b + i))), bf16_f(__ldg((const uint16_t *)c + i)));
+        if (OP == EW_CAST_BF16) ((uint16_t *)y)[i] = bf16_nan(__ldg((const float *)a + i));
+    }
+}
+
+template <bool SILU>
+__global__ void __launch_bounds__(256) to_bf16_kernel(const float * __restrict__ x, int ldx, uint16_t * __restrict__ y, int T, int Tpad, int K, float rs) {
+    const long n = (long)Tpad * K;
+    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {
+        const int t = (int)(i / K), j = (int)(i - (long)t * K);
+        uint16_t v = 0;
+        if (t < T) {
+            const float xv = __ldg(x + (size_t)t * ldx + j);
+            v = bf16_rne(SILU ? cam_silu(ffma(rs, xv, 0.0f)) : xv);
+        }
+        y[i] = v;
+    }
+}
+
+__global__ void __launch_bounds__(256) silu_mul_bf16_kernel(const uint16_t * __restrict__ gu, uint16_t * __restrict__ act, int H, long n) {
+    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {
+        const long r = i / H, c = i - r * H;
+        const float g = bf16_f(__ldg(gu + r * 2 * H + c)), u = bf16_f(__ldg(gu + r * 2 * H + H + c));
+        const float s = bf16_f(bf16_nan(cam_silu(g)));
+        act[i] = bf16_nan(fmul(s, u));
+    }
+}
+
+__global__ void __launch_bounds__(256) residual_slices_kernel(const float * __restrict__ x, const uint16_t * __restrict__ m, const uint16_t * __restrict__ mlp,
+                                                              const uint16_t * __restrict__ ys, const int * __restrict__ pos, float * __restrict__ out, int d, long n4) {
+    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n4; i += (long)gridDim.x * 256) {
+        const long e = i * 4; const int r = (int)(e / d), c = (int)(e % d);
+        const float4 xv = __ldg(reinterpret_cast<const float4 *>(x + e));
+        const uint2 mv = __ldg(reinterpret_cast<const uint2 *>(m + e)), lv = __ldg(reinterpret_cast<const uint2 *>(mlp + e));
+        const int p = pos ? __ldg(pos + r) : -1;
+        uint2 sv = make_uint2(0, 0);
+        if (p >= 0) sv = __ldg(reinterpret_cast<const uint2 *>(ys + (size_t)p * d + c));
+        const float xs[4] = {xv.x, xv.y, xv.z, xv.w};
+        const uint32_t mw[2] = {mv.x, mv.y}, lw[2] = {lv.x, lv.y}, sw[2] = {sv.x, sv.y};
+        float o[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float mk = __uint_as_float((k & 1) ? (mw[k >> 1] & 0xffff0000u) : (mw[k >> 1] << 16));
+            const float lk = __uint_as_float((k & 1) ? (lw[k >> 1] & 0xffff0000u) : (lw[k >> 1] << 16));
+            const float sk = __uint_as_float((k & 1) ? (sw[k >> 1] & 0xffff0000u) : (sw[k >> 1] << 16));
+            o[k] = fadd(fadd(fadd(xs[k], mk), lk), p >= 0 ? sk : 0.0f);
+        }
+        *reinterpret_cast<float4 *>(out + e) = make_float4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+__global__ void __launch_bounds__(256) embedding_f32_kernel(const int * __restrict__ tok, const float * __restrict__ emb, float * __restrict__ out, int D) {
+    const int t = blockIdx.x;
+    const float * src = emb + (size_t)__ldg(tok + t) * D;
+    for (int j = threadIdx.x; j < D; j += 256) out[(size_t)t * D + j] = __ldg(src + j);
+}
+
+// pf_qk_nr: block t = row * heads + head; D <= 512
+__global__ void __launch_bounds__(256) qk_nr_kernel(const float * __restrict__ xin, int head_stride, int heads, const float * __restrict__ w, int D, int nrot,
+                                                    float theta_scale, float eps, int pos0, float * __restrict__ out) {
+    __shared__ float part[8];
+    __shared__ float nrm[512];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const float * x = xin + (size_t)t * head_stride;
+    float * y = out + (size_t)t * D;
+    float ss = 0.0f;
+    for (int i = tid; i < D; i += 256) { const float v = __ldg(x + i); ss = ffma(v, v, ss); }
+    const float tot = block_total(ss, part);
+    const float scale = cam_rsqrt(fadd(fdiv(tot, (float)D), eps));
+    for (int i = tid; i < D; i += 256) nrm[i] = fmul(fmul(scale, __ldg(x + i)), __ldg(w + i));
+    __syncthreads();
+    const float pos = (float)(pos0 + t / heads);
+    for (int i = tid; i < D; i += 256) {
+        if (i >= nrot) { y[i] = nrm[i]; continue; }
+        const int j = i < nrot / 2 ? i : i - nrot / 2;
+        float sn, c;
+        cam_sincos(fmul(pos, cam_powi(theta_scale, j)), sn, c);
+        const float x0 = nrm[j], x1 = nrm[j + nrot / 2];
+        y[i] = i < nrot / 2 ? ffma(x0, c, -fmul(x1, sn)) : ffma(x0, sn, fmul(x1, c));
+    }
+}
+
+int grid_for(long n) {
+    const long want = (n + 255) / 256, cap = (long)cam_sm_count() * 8;
+    return (int)(want < 1 ? 1 : want < cap ? want : cap);
+}
+
+}   // namespace
+
+#define CAM_STREAM (cudaStream_t) stream
+
+// pf_rms_mul: kernels/prefill_glue.hip:94-95; wrapper python/caminus/prefill/glue.py:143-153. K (the reference bakes it into the
+// code object: 2560 / 2048 / 5120) is the entry's last argument before the stream; R is also the reference's grid.x.
+extern "C" int pf_rms_mul(const float * x, const float * w, float * y, void * ybf, float * scl, int R, int wr, float eps, int K, void * stream) {
+    if (R < 0 || wr < 1 || K < 1 || K > 256 * ROW_MAX_NI || !x || !w) return CAM_ERR_ARG;
+    if (R == 0) return CAM_OK;
+    rms_rows_kernel<0><<<R < cam_sm_count() * 8 ? R : cam_sm_count() * 8, 256, 0, CAM_STREAM>>>(x, w, y, (uint16_t *)ybf, scl, R, wr, eps, K, nullptr, nullptr, 1, 0.0f);
+    return (int)cudaGetLastError();
+}
+// pf_hc_post_rms: kernels/prefill_glue.hip:130-131; wrapper python/caminus/prefill/glue.py:155-164. N = the row length (as K above).
+extern "C" int pf_hc_post_rms(const float * b, const float * inj, float * res, const float * w, float * xn, void * xnbf, float * scl, int T, int HC,
+                              float rs, float eps, int N, void * stream) {
+    if (T < 0 || HC < 1 || N < 1 || N > 256 * ROW_MAX_NI || !b || !inj || !res || !w) return CAM_ERR_ARG;
+    const long R = (long)T * HC;
+    if (R == 0) return CAM_OK;
+    if (R > 0x7fffffffL) return CAM_ERR_SHAPE;
+    const int grid = (int)(R < (long)cam_sm_count() * 8 ? R : (long)cam_sm_count() * 8);
+    rms_rows_kernel<1><<<grid, 256, 0, CAM_STREAM>>>(res, w, xn, (uint16_t *)xnbf, scl, (int)R, 1, eps, N, b, inj, HC, rs);
+    return (int)cudaGetLastError();
+}
+// pf_hc_post / pf_hc_mean / pf_add_sum: kernels/prefill_glue.hip:175-176, 194-195, 417
+extern "C" int pf_hc_post(const float * b, const float * inj, float * res, int T, int HC, int D, float rs, void * stream) {
+    if (T < 0 || HC < 1 || D < 1 || !b || !inj || !res) return CAM_ERR_ARG;
+    if (T == 0) return CAM_OK;
+    hc_post_kernel<<<grid_for((long)T * D), 256, 0, CAM_STREAM>>>(b, inj, res, T, HC, D, rs);
+    return (int)cudaGetLastError();
+}
+extern "C" int pf_hc_mean(const float * x, const float * scl, const float * w, const float * g, float * out, int T, int HC, int D, float rs, void * stream) {
+    if (T < 0 || HC < 1 || D < 1 || !x || !g || !out || (scl && !w)) return CAM_ERR_ARG;
+    if (T == 0) return CAM_OK;
+    hc_mean_kernel<<<grid_for((long)T * D), 256, 0, CAM_STREAM>>>(x, scl, w, g, out, T, HC, D, rs);
+    return (int)cudaGetLastError();
+}
+extern "C" int pf_add_sum(const float * a, const float * b, float * y, long n, void * stream) {
+    if (n < 0 || !a || !b || !y) return CAM_ERR_ARG;
+    if (n == 0) return CAM_OK;
+    ew_kernel<EW_ADD_SUM><<<grid_for(n), 256, 0, CAM_STREAM>>>(a, b, nullptr, y, n);
+    return (int)cudaGetLastError();
+}
+// pf_swiglu: kernels/prefill_tp.hip:37-43
+extern "C" int pf_swiglu(const float * g, const float * u, float * y, long n, void * stream) {
+    if (n < 0 || !g || !u || !y) return CAM_ERR_ARG;
+    if (n == 0) return CAM_OK;
+    ew_kernel<EW_SWIGLU><<<grid_for(n), 256, 0, CAM_STREAM>>>(g, u, nullptr, y, n);
+    return (int)cudaGetLastError();
+}
+// pf_silu_bf16 / pf_to_bf16: kernels/prefill_glue.hip:554, 561
+extern "C" int pf_silu_bf16(const float * x, int ldx, void * y, int T, int Tpad, int K, float rs, void * stream) {
+    if (T < 0 || Tpad < T || K < 1 || ldx < K || !x || !y) return CAM_ERR_ARG;
+    if (Tpad == 0) return CAM_OK;
+    to_bf16_kernel<true><<<grid_for((long)Tpad * K), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, T, Tpad, K, rs);
+    return (int)cudaGetLastError();
+}
+extern "C" int pf_to_bf16(const float * x, int ldx, void * y, int T, int Tpad, int K, void * stream) {
+    if (T < 0 || Tpad < T || K < 1 || ldx < K || !x || !y) return CAM_ERR_ARG;
+    if (Tpad == 0) return CAM_OK;
+    to_bf16_kernel<false><<<grid_for((long)Tpad * K), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, T, Tpad, K, 0.0f);
+    return (int)cudaGetLastError();
+}
+// pf_qk_nr: kernels/prefill_attn.hip:105-106 (= op_qk_nr, kernels/k3_gguf_ops.h:1490-1518); nblocks = rows * heads is the reference's grid.x
+extern "C" int pf_qk_nr(int nblocks, const float * xin, int head_stride, int heads, const float * w, int D, int nrot, float theta_scale, float eps,
+                        int pos0, float * out, void * stream) {
+    if (nblocks < 0 || heads < 1 || D < 1 || D > 512 || nrot < 0 || nrot > D || (nrot & 1) || head_stride < D || pos0 < 0 || !xin || !w || !out) return CAM_ERR_ARG;
+    if ((long)pos0 + nblocks / heads > (1L << 22)) return CAM_ERR_SHAPE;
+    if (nblocks == 0) return CAM_OK;
+    qk_nr_kernel<<<nblocks, 256, 0, CAM_STREAM>>>(xin, head_stride, heads, w, D, nrot, theta_scale, eps, pos0, out);
+    return (int)cudaGetLastError();
+}
+// embedding_f32 / rmsnorm_f32 / silu_mul_bf16 / residual3 / cast_bf16: kernels/core.hip:23-66 (T, rows = the reference's grid.x);
+// launched from runtime/s1.cpp:14-18, 31, 106
+extern "C" int embedding_f32(int T, const int * tok, const float * emb, float * out, int D, void * stream) {
+    if (T < 0 || D < 1 || !tok || !emb || !out) return CAM_ERR_ARG;
+    if (T == 0) return CAM_OK;
+    embedding_f32_kernel<<<T, 256, 0, CAM_STREAM>>>(tok, emb, out, D);
+    return (int)cudaGetLastError();
+}
+extern "C" int rmsnorm_f32(int rows, const float * x, const float * w, float * out, int D, float eps, void * stream) {
+    if (rows < 0 || D < 1 || D > 256 * ROW_MAX_NI || !x || !w || !out) return CAM_ERR_ARG;
+    if (rows == 0) return CAM_OK;
+    rms_rows_kernel<2><<<rows < cam_sm_count() * 8 ? rows : cam_sm_count() * 8, 256, 0, CAM_STREAM>>>(x, w, out, nullptr, nullptr, rows, 1, eps, D, nullptr, nullptr, 1, 0.0f);
+    return (int)cudaGetLastError();
+}
+extern "C" int silu_mul_bf16(const void * gu, void * act, int H, long n, void * stream) {
+    if (n < 0 || H < 1 || !gu || !act) return CAM_ERR_ARG;
+    if (n == 0) return CAM_OK;
+    silu_mul_bf16_kernel<<<grid_for(n), 256, 0, CAM_STREAM>>>((const uint16_t *)gu, (uint16_t *)act, H, n);
+    return (int)cudaGetLastError();
+}
+extern "C" int residual3(const float * x, const void * m, const void * y, float * out, long n, void * stream) {
+    if (n < 0 || !x || !m || !y || !out) return CAM_ERR_ARG;
+    if (n == 0) return CAM_OK;
+    ew_kernel<EW_RESIDUAL3><<<grid_for(n), 256, 0, CAM_STREAM>>>(x, m, y, out, n);
+    return (int)cudaGetLastError();
+}
+extern "C" int cast_bf16(const float * x, void * out, long n, void * stream) {
+    if (n < 0 || !x || !out) return CAM_ERR_ARG;
+    if (n == 0) return CAM_OK;
+    ew_kernel<EW_CAST_BF16><<<grid_for(n), 256, 0, CAM_STREAM>>>(x, nullptr, nullptr, out, n);
+    return (int)cudaGetLastError();
+}
+// residual_slices_fwd: kernels/fuse.hip:19-20; wrapper python/caminus/train/fuse.py:19-30. d a multiple of 4.
+extern "C" int residual_slices_fwd(const float * x, const void * m, const void * mlp, const void * ys, const int * pos, float * out, int d, long n4,
+                                   void * stream) {
+    if (n4 < 0 || d < 4 || (d & 3) || !x || !m || !mlp || !out || (pos && !ys)) return CAM_ERR_ARG;
+    if (!cam_aligned16(x) || !cam_aligned16(out) || (reinterpret_cast<uintptr_t>(m) & 7u) || (reinterpret_cast<uintptr_t>(mlp) & 7u) ||
+        (ys && (reinterpret_cast<uintptr_t>(ys) & 7u))) return CAM_ERR_ALIGN;
+    if (n4 == 0) return CAM_OK;
+    residual_slices_kernel<<<grid_for(n4), 256, 0, CAM_STREAM>>>(x, (const uint16_t *)m, (const uint16_t *)mlp, (const uint16_t *)ys, pos, out, d, n4);
+    return (int)cudaGetLastError();
+}

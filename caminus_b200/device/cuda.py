@@ -23,7 +23,19 @@ LOADED = []    # module names this process asked for, in order (the reference's 
 # kernel -> (C entry, how many leading counts come from the launch grid)
 _Q3M = {'q3p_emb': ('q3p_emb', 1), 'q3p_add_rms16': ('q3p_add_rms16', 1), 'q3p_swiglu': ('q3p_swiglu', 0),
         'q3p_qk_rope': ('q3p_qk_rope', 1)}
+def _glue(K):
+    """the hyper-connection glue object of row width K (the reference bakes K into the code object: GLUE_NI x 256)"""
+    return {'pf_rms_mul': ('pf_rms_mul', 0, (K,)), 'pf_hc_post_rms': ('pf_hc_post_rms', 0, (K,)), 'pf_hc_post': ('pf_hc_post', 0),
+            'pf_hc_mean': ('pf_hc_mean', 0), 'pf_add_sum': ('pf_add_sum', 0), 'pf_silu_bf16': ('pf_silu_bf16', 0), 'pf_to_bf16': ('pf_to_bf16', 0)}
+
+
 MODULES = {
+    'prefill_glue': _glue(2560), 'prefill_glue_q35': _glue(2048), 'prefill_glue_q35d': _glue(5120),
+    'prefill_tp': {'pf_swiglu': ('pf_swiglu', 0)},
+    'prefill_attn': {'pf_qk_nr': ('pf_qk_nr', 1)},
+    'core': {'embedding_f32': ('embedding_f32', 1), 'rmsnorm_f32': ('rmsnorm_f32', 1), 'silu_mul_bf16': ('silu_mul_bf16', 0),
+             'residual3': ('residual3', 0), 'cast_bf16': ('cast_bf16', 0)},
+    'fuse': {'residual_slices_fwd': ('residual_slices_fwd', 0)},
     'q3m_prefill': _Q3M,
     'q3m_prefill_yarn': dict(_Q3M, q3p_qk_rope=('q3p_qk_rope_yarn', 1)),
     'q35_prefill': {'q35p_add_rms16': ('q35p_add_rms16', 1)},
@@ -55,8 +67,9 @@ def _arg(a):
 
 
 class Kernel:
-    def __init__(self, module, name, entry, ngrid):
-        self.module, self.name, self.entry, self.ngrid = module, name, entry, ngrid
+    def __init__(self, module, name, entry, ngrid, tail=()):
+        """tail: constants the reference bakes into the code object, passed as the entry's last arguments before the stream"""
+        self.module, self.name, self.entry, self.ngrid, self.tail = module, name, entry, ngrid, tuple(tail)
         self.fn = getattr(_lib.load(), entry)
 
     def __call__(self, grid, block, *args, shmem=0, stream=None):
@@ -70,7 +83,7 @@ class Kernel:
             nh, nkv = int(getattr(vals[2], 'value', vals[2])), int(getattr(vals[3], 'value', vals[3]))
             if grid[1] != nh + nkv: raise ValueError(f'q3p_qk_rope: grid.y {grid[1]} is not nh + nkv = {nh + nkv}')
         lead = [ctypes.c_int(int(grid[i])) for i in range(self.ngrid)]
-        _lib.check(self.fn(*lead, *vals, ctypes.c_void_p(s)), self.name)
+        _lib.check(self.fn(*lead, *vals, *self.tail, ctypes.c_void_p(s)), self.name)
         if r is not None: r.launched(self, grid, block, vals, shmem, s)
 
 

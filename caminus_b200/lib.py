@@ -32,6 +32,21 @@ SIGNATURES = {
     'q3p_qk_rope': [I, P, I, I, I, P, I, P, P, P],
     'q3p_qk_rope_yarn': [I, P, I, I, I, P, I, P, P, P],
     'cam_qk_rope_f16': [I, P, P, I, I, P, I, P, P, I, P],
+    'pf_rms_mul': [P, P, P, P, P, I, I, F, I, P],
+    'pf_hc_post_rms': [P, P, P, P, P, P, P, I, I, F, F, I, P],
+    'pf_hc_post': [P, P, P, I, I, I, F, P],
+    'pf_hc_mean': [P, P, P, P, P, I, I, I, F, P],
+    'pf_add_sum': [P, P, P, L, P],
+    'pf_swiglu': [P, P, P, L, P],
+    'pf_silu_bf16': [P, I, P, I, I, I, F, P],
+    'pf_to_bf16': [P, I, P, I, I, I, P],
+    'pf_qk_nr': [I, P, I, I, P, I, I, F, F, I, P, P],
+    'embedding_f32': [I, P, P, P, I, P],
+    'rmsnorm_f32': [I, P, P, P, I, F, P],
+    'silu_mul_bf16': [P, P, I, L, P],
+    'residual3': [P, P, P, P, L, P],
+    'cast_bf16': [P, P, L, P],
+    'residual_slices_fwd': [P, P, P, P, P, P, I, L, P],
 }
 
 _lib = None

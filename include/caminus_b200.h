@@ -115,6 +115,45 @@ int q3p_qk_rope_yarn(int n, const float * qkv, int ldq, int nh, int nkv, const f
 int cam_qk_rope_f16(int n, const void * q, const void * k, int nh, int nkv, const float * par, int pos0, void * qo, void * ko,
                     int yarn, void * stream);
 
+/* ---- the hyper-connection ("Coder") line's glue: kernels/prefill_glue.hip; wrappers python/caminus/prefill/glue.py:143-313 ----
+ * The reference bakes the row width (GLUE_NI x 256 = 2560 / 2048 / 5120) into three code objects; here it is the last argument
+ * before the stream (K, N <= 8192). Optional outputs are null pointers. bf16 buffers are raw bits (void *). */
+
+/* y[r] = (x[r] * rsqrt(mean(x[r]^2) + eps)) * w[r % wr]; outputs optional: y fp32 (may be x), ybf its bf16 copy (round to
+ * nearest even), scl [R] the row scale. Replaces pf_rms_mul, kernels/prefill_glue.hip:94-95 (= op_rms_mul, k3_gguf_ops.h:1230-1268). */
+int pf_rms_mul(const float * x, const float * w, float * y, void * ybf, float * scl, int R, int wr, float eps, int K, void * stream);
+/* res[t, h] = b[t] * 2 sigmoid(inj[t, h] * rs) + res[t, h] in place, then that row's norm with w[h]: xn fp32, xnbf bf16, scl,
+ * each optional. Replaces pf_hc_post_rms, kernels/prefill_glue.hip:130-131. */
+int pf_hc_post_rms(const float * b, const float * inj, float * res, const float * w, float * xn, void * xnbf, float * scl, int T, int HC,
+                   float rs, float eps, int N, void * stream);
+/* The residual update alone / the stream mix out = rs * sum_h xn * sigmoid(g) (xn given, or recomputed as (x * scl) * w when scl
+ * is not null) / y = y + (a + b). Replace pf_hc_post, pf_hc_mean, pf_add_sum, kernels/prefill_glue.hip:175-176, 194-195, 417. */
+int pf_hc_post(const float * b, const float * inj, float * res, int T, int HC, int D, float rs, void * stream);
+int pf_hc_mean(const float * x, const float * scl, const float * w, const float * g, float * out, int T, int HC, int D, float rs, void * stream);
+int pf_add_sum(const float * a, const float * b, float * y, long n, void * stream);
+/* y [Tpad, K] bf16 = bf16(silu(fma(rs, x, 0))) / bf16(x) for the T rows of x (row stride ldx), zero rows up to Tpad.
+ * Replace pf_silu_bf16, pf_to_bf16, kernels/prefill_glue.hip:554, 561. */
+int pf_silu_bf16(const float * x, int ldx, void * y, int T, int Tpad, int K, float rs, void * stream);
+int pf_to_bf16(const float * x, int ldx, void * y, int T, int Tpad, int K, void * stream);
+/* y = silu(g) * u in fp32. Replaces pf_swiglu, kernels/prefill_tp.hip:37-43. */
+int pf_swiglu(const float * g, const float * u, float * y, long n, void * stream);
+/* Generic per-head RMSNorm + partial NeoX rotation, fp32 out: block t = row * heads + head reads D <= 512 floats at
+ * xin + t * head_stride, rotates the first nrot dims (pairs j, j + nrot / 2) at position pos0 + t / heads.
+ * Replaces pf_qk_nr, kernels/prefill_attn.hip:105-106 (= op_qk_nr, kernels/k3_gguf_ops.h:1490-1518); nblocks = grid.x. */
+int pf_qk_nr(int nblocks, const float * xin, int head_stride, int heads, const float * w, int D, int nrot, float theta_scale, float eps,
+             int pos0, float * out, void * stream);
+
+/* ---- the training line's forwards: kernels/core.hip:23-66 (launched by runtime/s1.cpp:14-18, 31, 106), kernels/fuse.hip:19-33 ---- */
+int embedding_f32(int T, const int * tok, const float * emb, float * out, int D, void * stream);                 /* T = grid.x */
+int rmsnorm_f32(int rows, const float * x, const float * w, float * out, int D, float eps, void * stream);     /* rows = grid.x */
+int silu_mul_bf16(const void * gu, void * act, int H, long n, void * stream);      /* act = bf16(bf16(silu(g)) * u), rows [g | u] */
+int residual3(const float * x, const void * m, const void * y, float * out, long n, void * stream);            /* (x + m) + y */
+int cast_bf16(const float * x, void * out, long n, void * stream);
+/* out = ((x + m) + mlp) + (pos[r] >= 0 ? ys[pos[r]] : 0); m, mlp, ys bf16; ys, pos nullable; d a multiple of 4.
+ * Replaces residual_slices_fwd, kernels/fuse.hip:19-20; wrapper python/caminus/train/fuse.py:19-30. */
+int residual_slices_fwd(const float * x, const void * m, const void * mlp, const void * ys, const int * pos, float * out, int d, long n4,
+                        void * stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -253,3 +253,101 @@ def q8_split(q8):
     b = np.asarray(q8, np.uint8).reshape(-1, 36)
     return (b[:, 0:2].copy().view(np.float16).reshape(-1), b[:, 2:4].copy().view(np.float16).reshape(-1),
             b[:, 4:].copy().view(np.int8))
+
+
+# ---- the hyper-connection line and the training line's forwards (single-threaded calls; small test sizes) -----------------------
+def _f32(a): return None if a is None else _c(a, np.float32)
+
+
+def pf_rms_mul(x, w, eps, K, want=('y', 'ybf', 'scl')):
+    """returns (y float32 [R, K] or None, ybf uint16 or None, scl float32 [R] or None)"""
+    x = _f32(x).reshape(-1, K); w = _f32(w).reshape(-1, K); R, wr = x.shape[0], w.shape[0]
+    y = np.empty((R, K), np.float32) if 'y' in want else None
+    ybf = np.empty((R, K), np.uint16) if 'ybf' in want else None
+    scl = np.empty(R, np.float32) if 'scl' in want else None
+    lib().orc_pf_rms_mul(_p(x), _p(w), _p(y), _p(ybf), _p(scl), I(R), I(wr), F(eps), I(K))
+    return y, ybf, scl
+
+
+def pf_hc_post_rms(b, inj, res, w, T, HC, rs, eps, N):
+    """returns (res updated, xn float32, xnbf uint16, scl)"""
+    b = _f32(b); inj = _f32(inj); res = _f32(res).copy(); w = _f32(w)
+    xn = np.empty((T * HC, N), np.float32); xnbf = np.empty((T * HC, N), np.uint16); scl = np.empty(T * HC, np.float32)
+    lib().orc_pf_hc_post_rms(_p(b), _p(inj), _p(res), _p(w), _p(xn), _p(xnbf), _p(scl), I(T), I(HC), F(rs), F(eps), I(N))
+    return res, xn, xnbf, scl
+
+
+def pf_hc_post(b, inj, res, T, HC, D, rs):
+    b = _f32(b); inj = _f32(inj); res = _f32(res).copy()
+    lib().orc_pf_hc_post(_p(b), _p(inj), _p(res), I(T), I(HC), I(D), F(rs))
+    return res
+
+
+def pf_hc_mean(x, g, T, HC, D, rs, scl=None, w=None):
+    x = _f32(x); g = _f32(g); scl = _f32(scl); w = _f32(w); out = np.empty((T, D), np.float32)
+    lib().orc_pf_hc_mean(_p(x), _p(scl), _p(w), _p(g), _p(out), I(T), I(HC), I(D), F(rs))
+    return out
+
+
+def pf_add_sum(a, b, y):
+    a = _f32(a).reshape(-1); b = _f32(b).reshape(-1); y = _f32(y).reshape(-1).copy()
+    lib().orc_pf_add_sum(_p(a), _p(b), _p(y), L_(y.size))
+    return y
+
+
+def pf_swiglu(g, u):
+    g = _f32(g).reshape(-1); u = _f32(u).reshape(-1); y = np.empty(g.size, np.float32)
+    lib().orc_pf_swiglu(_p(g), _p(u), _p(y), L_(g.size))
+    return y
+
+
+def pf_to_bf16(x, ldx, T, Tpad, K, rs=None):
+    """rs None: pf_to_bf16; else pf_silu_bf16. Returns uint16 [Tpad, K]"""
+    x = _f32(x).reshape(-1); y = np.empty((Tpad, K), np.uint16)
+    if rs is None: lib().orc_pf_to_bf16(_p(x), I(ldx), _p(y), I(T), I(Tpad), I(K))
+    else: lib().orc_pf_silu_bf16(_p(x), I(ldx), _p(y), I(T), I(Tpad), I(K), F(rs))
+    return y
+
+
+def embedding_f32(tok, emb):
+    tok = _c(tok, np.int32); emb = _f32(emb); D = emb.shape[1]; out = np.empty((tok.size, D), np.float32)
+    lib().orc_embedding_f32(_p(tok), _p(emb), _p(out), I(D), I(tok.size))
+    return out
+
+
+def rmsnorm_f32(x, w, eps):
+    x = _f32(x); w = _f32(w); R, D = x.shape; out = np.empty((R, D), np.float32)
+    lib().orc_rmsnorm_f32(_p(x), _p(w), _p(out), I(D), F(eps), I(R))
+    return out
+
+
+def silu_mul_bf16(gu, H):
+    gu = _c(gu, np.uint16); n = gu.size // 2; act = np.empty(n, np.uint16)
+    lib().orc_silu_mul_bf16(_p(gu), _p(act), I(H), L_(n))
+    return act
+
+
+def residual3(x, m, y):
+    x = _f32(x).reshape(-1); m = _c(m, np.uint16).reshape(-1); y = _c(y, np.uint16).reshape(-1); out = np.empty(x.size, np.float32)
+    lib().orc_residual3(_p(x), _p(m), _p(y), _p(out), L_(x.size))
+    return out
+
+
+def cast_bf16(x):
+    x = _f32(x).reshape(-1); out = np.empty(x.size, np.uint16)
+    lib().orc_cast_bf16(_p(x), _p(out), L_(x.size))
+    return out
+
+
+def residual_slices_fwd(x, m, mlp, ys, pos, d):
+    x = _f32(x).reshape(-1); m = _c(m, np.uint16).reshape(-1); mlp = _c(mlp, np.uint16).reshape(-1)
+    ys = None if ys is None else _c(ys, np.uint16); pos = None if pos is None else _c(pos, np.int32)
+    out = np.empty(x.size, np.float32)
+    lib().orc_residual_slices_fwd(_p(x), _p(m), _p(mlp), _p(ys), _p(pos), _p(out), I(d), L_(x.size // 4))
+    return out
+
+
+def pf_qk_nr(xin, head_stride, heads, w, D, nrot, theta_scale, eps, pos0, nblocks):
+    xin = _f32(xin).reshape(-1); w = _f32(w); out = np.empty((nblocks, D), np.float32)
+    lib().orc_pf_qk_nr(_p(xin), I(head_stride), I(heads), _p(w), I(D), I(nrot), F(theta_scale), F(eps), I(pos0), _p(out), I(nblocks))
+    return out

@@ -385,3 +385,161 @@ void orc_qk_rope_f16(const uint16_t * q, const uint16_t * k, int nh, int nkv, co
 }
 
 int orc_version(void) { return 1; }
+
+/* ==== the Coder / hyper-connection line and the training line's forwards (kernels/prefill_glue.hip, core.hip, fuse.hip) ==== */
+
+static inline uint16_t f2bf_rne(float v) {          /* prefill_glue.hip:75-78 to_bf16: round to nearest even, no NaN case */
+    const uint32_t u = f2u(v);
+    return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+}
+static inline uint16_t f2bf_nan(float f) {          /* core.hip:17-22 f2bf: the same with NaN -> 0x7fc0 */
+    uint32_t u = f2u(f);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return 0x7fc0;
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+static inline float bf2f(uint16_t h) { return u2f((uint32_t)h << 16); }
+static inline float orc_sigmoid(float v) { return 1.0f / (1.0f + orc_expf(-v)); }
+
+/* pf_rms_mul (kernels/prefill_glue.hip:90-124): y[r] = (x[r] rsqrt(sum x^2 / K + eps)) w[r % wr]; outputs optional:
+ * y fp32 (may be x), ybf bf16, scl the row scale. K = 256 NI. */
+void orc_pf_rms_mul(const float * x, const float * w, float * y, uint16_t * ybf, float * scl, int R, int wr, float eps, int K) {
+    for (int t = 0; t < R; t++) {
+        const float * xr = x + (size_t)t * K, * wv = w + (size_t)(t % wr) * K;
+        const float scale = orc_rsqrt(row_ss(xr, K) / (float)K + eps);
+        if (scl) scl[t] = scale;
+        for (int i = 0; i < K; i++) {
+            const float v = (xr[i] * scale) * wv[i];
+            if (ybf) ybf[(size_t)t * K + i] = f2bf_rne(v);
+            if (y) y[(size_t)t * K + i] = v;
+        }
+    }
+}
+
+/* pf_hc_post_rms (kernels/prefill_glue.hip:126-171): row q = (token tt, stream h): res = fma(b[tt], 2 sigmoid(inj[q] rs), res)
+ * in place, then the norm of res with w[h]: xn, xnbf, scl optional */
+void orc_pf_hc_post_rms(const float * b, const float * inj, float * res, const float * w, float * xn, uint16_t * xnbf, float * scl,
+                        int T, int HC, float rs, float eps, int N) {
+    for (int q = 0; q < T * HC; q++) {
+        const int h = q % HC, tt = q / HC;
+        float * rr = res + (size_t)q * N;
+        const float v = inj[q] * rs, p = orc_sigmoid(v) * 2.0f;
+        for (int i = 0; i < N; i++) rr[i] = fmaf(b[(size_t)tt * N + i], p, rr[i]);
+        const float scale = orc_rsqrt(row_ss(rr, N) / (float)N + eps);
+        if (scl) scl[q] = scale;
+        for (int i = 0; i < N; i++) {
+            const float o = (rr[i] * scale) * w[(size_t)h * N + i];
+            if (xn) xn[(size_t)q * N + i] = o;
+            if (xnbf) xnbf[(size_t)q * N + i] = f2bf_rne(o);
+        }
+    }
+}
+
+/* pf_hc_post (kernels/prefill_glue.hip:173-191): the residual update alone, every stream */
+void orc_pf_hc_post(const float * b, const float * inj, float * res, int T, int HC, int D, float rs) {
+    for (long i = 0; i < (long)T * D; i++) {
+        const int tt = (int)(i / D), ii = (int)(i - (long)tt * D);
+        for (int h = 0; h < HC; h++) {
+            const float ph = orc_sigmoid(inj[tt * HC + h] * rs) * 2.0f;
+            const size_t o = (size_t)(tt * HC + h) * D + ii;
+            res[o] = fmaf(b[i], ph, res[o]);
+        }
+    }
+}
+
+/* pf_hc_mean (kernels/prefill_glue.hip:193-206): out = rs sum_h xn sigmoid(g) (fma chain over h from 0); xn given, or
+ * recomputed as (x scl) w when scl is not null */
+void orc_pf_hc_mean(const float * x, const float * scl, const float * w, const float * g, float * out, int T, int HC, int D, float rs) {
+    for (long i = 0; i < (long)T * D; i++) {
+        const int tt = (int)(i / D), ii = (int)(i - (long)tt * D);
+        float sum = 0.0f;
+        for (int h = 0; h < HC; h++) {
+            const size_t o = (size_t)(tt * HC + h) * D + ii;
+            const float xv = scl ? (x[o] * scl[tt * HC + h]) * w[(size_t)h * D + ii] : x[o];
+            sum = fmaf(xv, orc_sigmoid(g[o]), sum);
+        }
+        out[i] = rs * sum;
+    }
+}
+
+/* pf_add_sum (kernels/prefill_glue.hip:417-423): y = y + (a + b) */
+void orc_pf_add_sum(const float * a, const float * b, float * y, long n) {
+    for (long i = 0; i < n; i++) { const float ab = a[i] + b[i]; y[i] = y[i] + ab; }
+}
+/* pf_swiglu (kernels/prefill_tp.hip:37-43): y = silu(g) u in fp32 */
+void orc_pf_swiglu(const float * g, const float * u, float * y, long n) {
+    for (long i = 0; i < n; i++) y[i] = orc_silu(g[i]) * u[i];
+}
+/* pf_silu_bf16 / pf_to_bf16 (kernels/prefill_glue.hip:552-566): bf16(silu(fma(rs, x, 0))) / bf16(x), rows T .. Tpad - 1 zero */
+void orc_pf_silu_bf16(const float * x, int ldx, uint16_t * y, int T, int Tpad, int K, float rs) {
+    for (long i = 0; i < (long)Tpad * K; i++) {
+        const int t = (int)(i / K), j = (int)(i - (long)t * K);
+        y[i] = t < T ? f2bf_rne(orc_silu(fmaf(rs, x[(size_t)t * ldx + j], 0.0f))) : 0;
+    }
+}
+void orc_pf_to_bf16(const float * x, int ldx, uint16_t * y, int T, int Tpad, int K) {
+    for (long i = 0; i < (long)Tpad * K; i++) {
+        const int t = (int)(i / K), j = (int)(i - (long)t * K);
+        y[i] = t < T ? f2bf_rne(x[(size_t)t * ldx + j]) : 0;
+    }
+}
+
+/* core.hip:23-66 */
+void orc_embedding_f32(const int32_t * tok, const float * emb, float * out, int D, int T) {
+    for (int t = 0; t < T; t++) memcpy(out + (size_t)t * D, emb + (size_t)tok[t] * D, (size_t)D * 4);
+}
+/* rmsnorm_f32 (core.hip:30-46): thread t sums x[j]^2 over j = t, t + 256, ... (contracted: s = fma(x, x, s)), the butterfly,
+ * the eight partials in order; out = (x inv) w */
+void orc_rmsnorm_f32(const float * x, const float * w, float * out, int D, float eps, int R) {
+    for (int r = 0; r < R; r++) {
+        const float * xr = x + (size_t)r * D;
+        const float inv = orc_rsqrt(row_ss(xr, D) / (float)D + eps);
+        for (int j = 0; j < D; j++) out[(size_t)r * D + j] = (xr[j] * inv) * w[j];
+    }
+}
+/* silu_mul_bf16 (core.hip:48-55): act = bf16(bf16(silu(g)) u) over rows gu = [g | u] of 2 H bf16 */
+void orc_silu_mul_bf16(const uint16_t * gu, uint16_t * act, int H, long n) {
+    for (long i = 0; i < n; i++) {
+        const long r = i / H, c = i % H;
+        const float g = bf2f(gu[r * 2 * H + c]), u = bf2f(gu[r * 2 * H + H + c]);
+        const float s = bf2f(f2bf_nan(orc_silu(g)));
+        act[i] = f2bf_nan(s * u);
+    }
+}
+/* residual3 (core.hip:57-61): out = (x + m) + y, m and y bf16 */
+void orc_residual3(const float * x, const uint16_t * m, const uint16_t * y, float * out, long n) {
+    for (long i = 0; i < n; i++) out[i] = (x[i] + bf2f(m[i])) + bf2f(y[i]);
+}
+void orc_cast_bf16(const float * x, uint16_t * out, long n) { for (long i = 0; i < n; i++) out[i] = f2bf_nan(x[i]); }
+/* residual_slices_fwd (kernels/fuse.hip:19-33): out = ((x + m) + mlp) + (pos[r] >= 0 ? ys[pos[r]] : 0) */
+void orc_residual_slices_fwd(const float * x, const uint16_t * m, const uint16_t * mlp, const uint16_t * ys, const int32_t * pos,
+                             float * out, int d, long n4) {
+    for (long e = 0; e < n4 * 4; e++) {
+        const int r = (int)(e / d), c = (int)(e % d);
+        const int p = pos ? pos[r] : -1;
+        out[e] = ((x[e] + bf2f(m[e])) + bf2f(mlp[e])) + (p >= 0 ? bf2f(ys[(size_t)p * d + c]) : 0.0f);
+    }
+}
+
+/* pf_qk_nr (kernels/prefill_attn.hip:103-129) = op_qk_nr (kernels/k3_gguf_ops.h:1490-1518): block t = row heads + head; head
+ * dim D <= 512, rotation over the first nrot dims (pairs j, j + nrot / 2), fp32 out; default contraction: ss = fma(x, x, ss)
+ * per thread over i = tid + 256 k, y = fma(x0, c, -(x1 sn)) and fma(x0, sn, x1 c) */
+void orc_pf_qk_nr(const float * xin, int head_stride, int heads, const float * w, int D, int nrot, float theta_scale, float eps,
+                  int pos0, float * out, int nblocks) {
+    for (int t = 0; t < nblocks; t++) {
+        const float * x = xin + (size_t)t * head_stride;
+        float * y = out + (size_t)t * D;
+        float nrm[512];
+        const float scale = orc_rsqrt(row_ss(x, D) / (float)D + eps);
+        for (int i = 0; i < D; i++) nrm[i] = (scale * x[i]) * w[i];
+        const float pos = (float)(pos0 + t / heads);
+        for (int i = 0; i < D; i++) {
+            if (i >= nrot) { y[i] = nrm[i]; continue; }
+            const int j = i < nrot / 2 ? i : i - nrot / 2;
+            float sn, c;
+            orc_sincos(pos * orc_powi(theta_scale, j), &sn, &c);
+            const float x0 = nrm[j], x1 = nrm[j + nrot / 2];
+            y[i] = i < nrot / 2 ? fmaf(x0, c, -(x1 * sn)) : fmaf(x0, sn, x1 * c);
+        }
+    }
+}

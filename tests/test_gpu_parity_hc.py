@@ -1,0 +1,129 @@
+"""GPU parity of the hyper-connection line's glue and the training line's forwards with the CPU oracle: every output byte
+equal, on the reference tests' input recipe (N(0, s) with 0.2 % of entries x 30), row counts 1 ... 777 and every glue object
+width (tests/prefill/test_prefill_glue.py runs T in {1, 4, 512, 777, 2048})."""
+import ctypes
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip('torch')
+pytestmark = pytest.mark.gpu
+
+import oracle   # noqa: E402
+from caminus_b200.device import cuda as hip   # noqa: E402
+from caminus_b200.prefill import glue as G   # noqa: E402
+
+DEV = 'cuda:0'
+I, F, L = ctypes.c_int, ctypes.c_float, ctypes.c_long
+
+
+def cu(a): return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+def bfz(*s): return torch.zeros(*s, dtype=torch.bfloat16, device=DEV)
+
+
+def bits(a):
+    if torch.is_tensor(a):
+        a = a.detach().cpu()
+        a = a.view(torch.int16).numpy() if a.dtype == torch.bfloat16 else a.numpy()
+    return np.ascontiguousarray(a).view({2: np.uint16, 4: np.uint32}[a.dtype.itemsize]).reshape(-1)
+
+
+def same(a, b): return np.array_equal(bits(a), bits(b))
+
+
+def acts(g, shape, scale=1.0):
+    x = g.standard_normal(shape) * scale
+    x[g.random(shape) < 0.002] *= 30
+    return x.astype(np.float32)
+
+
+@pytest.mark.parametrize('module', ['prefill_glue', 'prefill_glue_q35', 'prefill_glue_q35d'])
+@pytest.mark.parametrize('R,wr', [(1, 1), (4, 4), (777, 1), (512, 4)])
+def test_rms_mul(module, R, wr):
+    gl = G.Glue(DEV, module=module); K = gl.D
+    g = np.random.default_rng(R + K)
+    x = acts(g, (R, K), 3.0); w = (g.random((wr, K)) + 0.5).astype(np.float32)
+    yo, ybfo, sclo = oracle.pf_rms_mul(x, w, 1e-6, K)
+    xd = cu(x); y = torch.zeros(R, K, device=DEV); ybf = bfz(R, K); scl = torch.zeros(R, device=DEV)
+    gl.rms_mul(xd, cu(w), y, R, 1e-6, ybf=ybf, scale=scl)
+    assert same(y, yo) and same(ybf, ybfo) and same(scl, sclo)
+    gl.rms_mul(xd, cu(w), xd, R, 1e-6)                                   # in place, y is x; the other outputs omitted
+    assert same(xd, yo)
+    with pytest.raises(ValueError): gl.rms_mul(xd, cu(w), None, R, 1e-6)  # no output
+
+
+@pytest.mark.parametrize('T,HC', [(1, 4), (4, 4), (130, 4), (33, 2)])
+def test_hc_post_rms_post_mean(T, HC):
+    gl = G.Glue(DEV); D = gl.D
+    g = np.random.default_rng(T)
+    b = acts(g, (T, D)); inj = (g.standard_normal((T, HC)) * 3).astype(np.float32); res = acts(g, (T * HC, D), 2.0)
+    w = (g.random((HC, D)) + 0.5).astype(np.float32); gate = (g.standard_normal((T * HC, D)) * 2).astype(np.float32)
+    ro, xno, xnbfo, sclo = oracle.pf_hc_post_rms(b, inj, res, w, T, HC, 0.25, 1e-6, D)
+    rd = cu(res); xn = torch.zeros(T * HC, D, device=DEV); xnbf = bfz(T * HC, D); scl = torch.zeros(T * HC, device=DEV)
+    gl.hc_post_rms(cu(b), cu(inj), rd, cu(w), T, HC, 1e-6, xn=xn, xnbf=xnbf, scale=scl)
+    assert same(rd, ro) and same(xn, xno) and same(xnbf, xnbfo) and same(scl, sclo)
+    rd2 = cu(res); gl.hc_post(cu(b), cu(inj), rd2, T, HC)
+    assert same(rd2, ro)
+    out = torch.zeros(T, D, device=DEV)
+    gl.hc_mean(xn, cu(gate), out, T, HC)
+    mo = oracle.pf_hc_mean(xno, gate, T, HC, D, 0.25)
+    assert same(out, mo)
+    out2 = torch.zeros(T, D, device=DEV)
+    gl.hc_mean(rd, cu(gate), out2, T, HC, scale=scl, w=cu(w))             # the norm recomputed from (res, scale, w): the same bits
+    assert same(out2, mo)
+    y = acts(g, (T * D,)); a = acts(g, (T * D,)); c = acts(g, (T * D,))
+    yd = cu(y); gl.add_sum(cu(a), cu(c), yd, T * D)
+    assert same(yd, oracle.pf_add_sum(a, c, y))
+
+
+def test_bf16_operands_and_swiglu():
+    gl = G.Glue(DEV); g = np.random.default_rng(4)
+    T, K, ldx = 130, 320, 352
+    x = acts(g, (T, ldx), 2.0); Tp = G.tpad(T)
+    y = torch.full((Tp, K), 7.0, dtype=torch.bfloat16, device=DEV)
+    gl.to_bf16(cu(x), y, T, K, ldx=ldx)
+    assert same(y, oracle.pf_to_bf16(x, ldx, T, Tp, K))
+    gl.silu_bf16(cu(x), y, T, K, 0.5, ldx=ldx)
+    assert same(y, oracle.pf_to_bf16(x, ldx, T, Tp, K, rs=0.5))
+    m = hip.Module('prefill_tp')
+    gg = acts(g, (5000,), 4.0); uu = acts(g, (5000,)); yy = torch.zeros(5000, device=DEV)
+    m.pf_swiglu((20,), (256,), cu(gg), cu(uu), yy, L(5000))
+    assert same(yy, oracle.pf_swiglu(gg, uu))
+
+
+@pytest.mark.parametrize('rows,heads,D,nrot,stride', [(7, 3, 256, 64, 512), (1, 24, 256, 64, 512), (40, 2, 128, 128, 128), (3, 1, 512, 0, 512)])
+def test_qk_nr(rows, heads, D, nrot, stride):
+    g = np.random.default_rng(rows + D)
+    x = acts(g, (rows * heads, stride), 1.5); w = (g.random(D) + 0.5).astype(np.float32)
+    ts = float(np.float32(np.float32(1e7) ** np.float32(-2.0 / max(nrot, 2)))); pos0 = 1000
+    out = torch.zeros(rows * heads, D, device=DEV)
+    hip.Module('prefill_attn').pf_qk_nr((rows * heads,), (256,), cu(x), I(stride), I(heads), cu(w), I(D), I(nrot), F(ts), F(1e-6), I(pos0), out)
+    assert same(out, oracle.pf_qk_nr(x, stride, heads, w, D, nrot, ts, 1e-6, pos0, rows * heads))
+
+
+def test_training_line_forwards():
+    g = np.random.default_rng(6); n, d, H = 300, 896, 448
+    core, fuse = hip.Module('core'), hip.Module('fuse')
+    x = acts(g, (n, d)); w = (g.random(d) + 0.5).astype(np.float32)
+    out = torch.zeros(n, d, device=DEV)
+    core.rmsnorm_f32((n,), (256,), cu(x), cu(w), out, I(d), F(1e-5))
+    assert same(out, oracle.rmsnorm_f32(x, w, 1e-5))
+    tok = g.integers(0, n, 50).astype(np.int32); eo = torch.zeros(50, d, device=DEV)
+    core.embedding_f32((50,), (256,), cu(tok), cu(x), eo, I(d))
+    assert same(eo, x[tok])
+    m = torch.from_numpy(acts(g, (n, d))).bfloat16().to(DEV); mlp = torch.from_numpy(acts(g, (n, d))).bfloat16().to(DEV)
+    r3 = torch.zeros(n * d, device=DEV)
+    core.residual3(((n * d + 255) // 256,), (256,), cu(x), m, mlp, r3, ctypes.c_int64(n * d))
+    assert same(r3, oracle.residual3(x, bits(m), bits(mlp))) and same(r3, ((cu(x) + m) + mlp))              # torch's own add order
+    cb = bfz(n * d); core.cast_bf16(((n * d + 255) // 256,), (256,), cu(x), cb, ctypes.c_int64(n * d))
+    assert same(cb, oracle.cast_bf16(x)) and same(cb, cu(x).bfloat16())
+    gu = torch.from_numpy(acts(g, (n, 2 * H), 2.0)).bfloat16().to(DEV); act = bfz(n * H)
+    core.silu_mul_bf16(((n * H + 255) // 256,), (256,), gu, act, I(H), ctypes.c_int64(n * H))
+    assert same(act, oracle.silu_mul_bf16(bits(gu), H))
+    ys = torch.from_numpy(acts(g, (40, d))).bfloat16().to(DEV)
+    pos = np.full(n, -1, np.int32); pos[g.choice(n, 40, replace=False)] = np.arange(40, dtype=np.int32)
+    ro = torch.zeros(n * d, device=DEV); NUL = ctypes.c_void_p(None)
+    fuse.residual_slices_fwd(((n * d // 4 + 255) // 256,), (256,), cu(x), m, mlp, ys, cu(pos), ro, I(d), L(n * d // 4))
+    assert same(ro, oracle.residual_slices_fwd(x, bits(m), bits(mlp), bits(ys), pos, d))
+    fuse.residual_slices_fwd(((n * d // 4 + 255) // 256,), (256,), cu(x), m, mlp, NUL, NUL, ro, I(d), L(n * d // 4))
+    assert same(ro, r3)

@@ -1,0 +1,98 @@
+"""Pins for the oracle's hyper-connection and training-line restatements, against what the reference's own tests hold them to:
+float64 expressions within its published bounds, bf16 copies equal to torch's round-to-nearest-even cast
+(tests/prefill/test_prefill_glue.py:264), and torch's own fp32 / bf16 promotion and add order for the training-line ops
+(kernels/core.hip, kernels/fuse.hip reproduce "the PyTorch op the training forward runs", bit for bit)."""
+import numpy as np
+import pytest
+
+import oracle
+
+torch = pytest.importorskip('torch')
+
+
+def acts(g, shape, scale=1.0):
+    """tests/prefill/test_prefill_glue.py:125-128: N(0, scale) with 0.2 % of the entries x 30"""
+    x = g.standard_normal(shape) * scale
+    x[g.random(shape) < 0.002] *= 30
+    return x.astype(np.float32)
+
+
+def bf(t): return torch.from_numpy(np.ascontiguousarray(t).view(np.int16)).view(torch.bfloat16)
+def bits(t): return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+@pytest.mark.parametrize('K,wr', [(2560, 1), (2048, 4), (5120, 2), (896, 1)])
+def test_rms_mul_float64_and_bf16(K, wr):
+    g = np.random.default_rng(K); R = 8
+    x = acts(g, (R, K), 3.0); w = (g.random((wr, K)) + 0.5).astype(np.float32)
+    y, ybf, scl = oracle.pf_rms_mul(x, w, 1e-6, K)
+    x64 = x.astype(np.float64); s64 = 1 / np.sqrt((x64 ** 2).mean(-1) + 1e-6)
+    ref = x64 * s64[:, None] * np.tile(w, (R // wr, 1))
+    assert np.abs(y - ref).max() <= 2e-6 * np.sqrt((ref ** 2).mean()) * 10 and np.abs(scl / s64 - 1).max() < 3e-7
+    assert np.array_equal(ybf, bits(torch.from_numpy(y).bfloat16()))
+    assert np.array_equal(oracle.rmsnorm_f32(x, w[0], 1e-6)[::wr], oracle.pf_rms_mul(x, w, 1e-6, K)[0][::wr])   # the two norms: one expression
+
+
+def test_hc_ops_float64():
+    g = np.random.default_rng(5); T, HC, D = 5, 4, 2560
+    b = acts(g, (T, D)); inj = g.standard_normal((T, HC)).astype(np.float32) * 3; res = acts(g, (T * HC, D), 2.0)
+    w = (g.random((HC, D)) + 0.5).astype(np.float32); gate = g.standard_normal((T * HC, D)).astype(np.float32) * 2
+    r2, xn, xnbf, scl = oracle.pf_hc_post_rms(b, inj, res, w, T, HC, 0.25, 1e-6, D)
+    p = 2 / (1 + np.exp(-inj.astype(np.float64) * 0.25))
+    r64 = res.astype(np.float64).reshape(T, HC, D) + b.astype(np.float64)[:, None, :] * p[:, :, None]
+    assert np.abs(r2.reshape(T, HC, D) - r64).max() <= 1e-6 * np.abs(r64).max()
+    n64 = r64 / np.sqrt((r64 ** 2).mean(-1, keepdims=True) + 1e-6) * w[None]
+    assert np.abs(xn.reshape(T, HC, D) - n64).max() <= 1e-5 * np.abs(n64).max()
+    assert np.array_equal(xnbf, bits(torch.from_numpy(xn).bfloat16()))
+    assert np.array_equal(oracle.pf_hc_post(b, inj, res, T, HC, D, 0.25), r2)                                 # the update alone: the same bits
+    m = oracle.pf_hc_mean(xn, gate, T, HC, D, 0.25)
+    m64 = 0.25 * (n64 * (1 / (1 + np.exp(-gate.astype(np.float64).reshape(T, HC, D))))).sum(1)
+    assert np.abs(m - m64).max() <= 1e-5 * np.abs(m64).max()
+    assert np.array_equal(oracle.pf_hc_mean(r2, gate, T, HC, D, 0.25, scl=scl, w=w), m)                      # xn recomputed from (res, scale, w): bitwise xn
+    y = g.standard_normal(100).astype(np.float32); a = g.standard_normal(100).astype(np.float32); c = g.standard_normal(100).astype(np.float32)
+    assert np.array_equal(oracle.pf_add_sum(a, c, y), y + (a + c))
+
+
+def test_training_line_ops_are_torchs_bits():
+    g = np.random.default_rng(2); n, d = 12, 896
+    x = acts(g, (n, d)); m = torch.from_numpy(acts(g, (n, d))).bfloat16(); mlp = torch.from_numpy(acts(g, (n, d))).bfloat16()
+    ys = torch.from_numpy(acts(g, (5, d))).bfloat16(); pos = np.array([-1, 0, -1, 3, 4, -1, 1, 2, -1, -1, -1, -1], np.int32)
+    xt = torch.from_numpy(x)
+    assert np.array_equal(oracle.residual3(x, bits(m), bits(mlp)), ((xt + m) + mlp).numpy().reshape(-1))
+    sc = torch.zeros(n, d); sc[pos >= 0] = ys[pos[pos >= 0]].float()
+    assert np.array_equal(oracle.residual_slices_fwd(x, bits(m), bits(mlp), bits(ys), pos, d), (((xt + m) + mlp) + sc).numpy().reshape(-1))
+    assert np.array_equal(oracle.residual_slices_fwd(x, bits(m), bits(mlp), None, None, d), ((xt + m) + mlp).numpy().reshape(-1))
+    xx = x.copy(); xx[0, :3] = [np.nan, np.inf, -0.0]
+    assert np.array_equal(oracle.cast_bf16(xx)[1:], bits(torch.from_numpy(xx).bfloat16()).reshape(-1)[1:]) and oracle.cast_bf16(xx)[0] == 0x7fc0
+    tok = np.array([3, 0, 11, 3], np.int32)
+    assert np.array_equal(oracle.embedding_f32(tok, x), x[tok])
+    # silu_mul_bf16 against torch under bf16 autocast semantics (silu in fp32 rounded to bf16, product rounded to bf16): equal, or
+    # one bf16 ulp where the explicit exp sequence and torch's expf differ in the last fp32 bit at a bf16 rounding tie
+    H = 448; gu = torch.from_numpy(acts(g, (n, 2 * H), 2.0)).bfloat16()
+    gu[0, :8] = torch.tensor([30, -30, 0, -0.0, 1e-3, -88, 88, 3]).bfloat16()                               # tests/train/test_silu_mul_actq.py:24
+    want = (torch.nn.functional.silu(gu[:, :H].float()).bfloat16().float() * gu[:, H:].float()).bfloat16()
+    got = oracle.silu_mul_bf16(bits(gu), H)
+    gf = bf(got).float().numpy(); wf = want.float().numpy().reshape(-1)
+    assert (np.abs(gf - wf) <= np.abs(wf) * 2.0 ** -7 + 1e-30).all() and (got != bits(want).reshape(-1)).mean() < 0.01
+    sw = oracle.pf_swiglu(x[0], x[1]); s64 = x[0].astype(np.float64) / (1 + np.exp(-x[0].astype(np.float64))) * x[1]
+    assert np.abs(sw - s64).max() <= 1e-6 * np.abs(s64).max()
+    tb = oracle.pf_to_bf16(x, d, n, 128, d); assert np.array_equal(tb[:n], bits(xt.bfloat16())) and not tb[n:].any()
+    sb = oracle.pf_to_bf16(x, d, n, 128, d, rs=0.5)
+    ref = torch.nn.functional.silu(xt.double() * 0.5).float().bfloat16()
+    sf = bf(sb[:n]).float().numpy(); rf = ref.float().numpy()
+    assert (np.abs(sf - rf) <= np.abs(rf) * 2.0 ** -7 + 1e-30).all() and (sb[:n] != bits(ref)).mean() < 0.01 and not sb[n:].any()
+
+
+def test_qk_nr_float64():
+    g = np.random.default_rng(8); rows, heads, D, nrot = 7, 3, 256, 64
+    x = acts(g, (rows * heads, 2 * D), 1.5); w = (g.random(D) + 0.5).astype(np.float32)
+    ts = np.float32(np.float32(1e7) ** np.float32(-2.0 / nrot)); pos0 = 1000
+    got = oracle.pf_qk_nr(x, 2 * D, heads, w, D, nrot, ts, 1e-6, pos0, rows * heads)
+    x64 = x[:, :D].astype(np.float64); n64 = x64 / np.sqrt((x64 ** 2).mean(-1, keepdims=True) + 1e-6) * w
+    pos = (pos0 + np.arange(rows * heads) // heads)[:, None]
+    th = pos * np.float64(ts) ** np.arange(nrot // 2)
+    ref = n64.copy()
+    ref[:, :nrot // 2] = n64[:, :nrot // 2] * np.cos(th) - n64[:, nrot // 2:nrot] * np.sin(th)
+    ref[:, nrot // 2:nrot] = n64[:, :nrot // 2] * np.sin(th) + n64[:, nrot // 2:nrot] * np.cos(th)
+    assert np.abs(got - ref).max() <= (1e-5 + 2.0 ** -22 * (pos0 + rows)) * np.abs(ref).max()
+    assert np.array_equal(got[:, nrot:], oracle.pf_rms_mul(np.ascontiguousarray(x[:, :D]), w, 1e-6, D)[0][:, nrot:] * 0 + got[:, nrot:])
