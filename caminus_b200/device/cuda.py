@@ -38,6 +38,8 @@ MODULES = {
     'fuse': {'residual_slices_fwd': ('residual_slices_fwd', 0)},
     'q3m_prefill': _Q3M,
     'q3m_prefill_yarn': dict(_Q3M, q3p_qk_rope=('q3p_qk_rope_yarn', 1)),
+    'q3m_prefill_kvq8': {'q3p_qk_rope_q8': ('q3p_qk_rope_q8', 1)},
+    'q3m_prefill_kvq8_yarn': {'q3p_qk_rope_q8': ('q3p_qk_rope_q8_yarn', 1)},
     'q35_prefill': {'q35p_add_rms16': ('q35p_add_rms16', 1)},
     'k3_gguf': {'gg_quantize_q8_1': ('gg_quantize_q8_1', 0), 'gg_silu_mul': ('gg_silu_mul', 0)},
     'k3_gguf_gsq': {'gg_quantize_q8_1': ('gg_quantize_q8_1', 0), 'gg_silu_mul': ('gg_silu_mul', 0)},
@@ -79,9 +81,9 @@ class Kernel:
         s = _current_stream() if stream is None else stream
         r = RECORD
         if r is not None and r.intercept(self, grid, block, vals, shmem, s): return
-        if self.name == 'q3p_qk_rope':   # grid.y is the reference's nh + nkv: it must agree with the kernel's own arguments
+        if self.name in ('q3p_qk_rope', 'q3p_qk_rope_q8'):   # grid.y is the reference's nh + nkv: it must agree with the kernel's own arguments
             nh, nkv = int(getattr(vals[2], 'value', vals[2])), int(getattr(vals[3], 'value', vals[3]))
-            if grid[1] != nh + nkv: raise ValueError(f'q3p_qk_rope: grid.y {grid[1]} is not nh + nkv = {nh + nkv}')
+            if grid[1] != nh + nkv: raise ValueError(f'{self.name}: grid.y {grid[1]} is not nh + nkv = {nh + nkv}')
         lead = [ctypes.c_int(int(grid[i])) for i in range(self.ngrid)]
         _lib.check(self.fn(*lead, *vals, *self.tail, ctypes.c_void_p(s)), self.name)
         if r is not None: r.launched(self, grid, block, vals, shmem, s)

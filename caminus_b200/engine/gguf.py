@@ -47,3 +47,27 @@ def swiglu_q8_1(g, u, yq=None, strict=False):
         s = torch.cuda.current_stream().cuda_stream
         _lib.check(fn(g.data_ptr(), u.data_ptr(), yq.data_ptr(), n, s), 'gg_swiglu_q8_1')
     return yq
+
+
+MMQ_BLOCK_BYTES = 144     # block_q8_1_mmq: 16 bytes of scales + 128 int8
+MMQ_LAYOUTS = {'D4': 0, 'DS4': 1}
+
+
+def quantize_mmq_q8_1(x, layout='D4', u=None, y=None, kvalid=None):
+    """rows of x [rows, K] (cuda; fp32, or fp16 with u) -> Q8_1 in the MMQ layout, uint8 [ceil(K / 128), rows, 144].
+    u given: the blocks of silu(x) * u (the fused gate / up epilogue's bytes). kvalid: values per row that count (default K)"""
+    if x.dim() != 2 or x.stride(1) != 1 or x.dtype not in (torch.float32, torch.float16): raise ValueError('quantize_mmq_q8_1: x must be [rows, K] fp32 / fp16')
+    if u is None and x.dtype != torch.float32: raise ValueError('quantize_mmq_q8_1: plain quantisation takes fp32')
+    if u is not None and (u.shape != x.shape or u.dtype != x.dtype or u.stride() != x.stride()): raise ValueError('quantize_mmq_q8_1: u must match x')
+    if layout not in MMQ_LAYOUTS: raise ValueError(f'quantize_mmq_q8_1: layout {layout!r} ({sorted(MMQ_LAYOUTS)})')
+    rows, K = x.shape; kvalid = K if kvalid is None else int(kvalid); Kpad = (K + 127) // 128 * 128
+    if y is None: y = torch.empty(Kpad // 128, rows, MMQ_BLOCK_BYTES, dtype=torch.uint8, device=x.device)
+    elif y.dtype != torch.uint8 or y.numel() < Kpad // 128 * rows * MMQ_BLOCK_BYTES or not y.is_contiguous(): raise ValueError('quantize_mmq_q8_1: y too small')
+    L = _lib.load()
+    with torch.cuda.device(x.device):
+        s = torch.cuda.current_stream().cuda_stream
+        if u is None: r = L.cam_quantize_mmq_q8_1(x.data_ptr(), y.data_ptr(), kvalid, Kpad, x.stride(0), rows, MMQ_LAYOUTS[layout], s)
+        elif x.dtype == torch.float16: r = L.cam_swiglu_mmq_q8_1_f16(x.data_ptr(), u.data_ptr(), y.data_ptr(), kvalid, Kpad, x.stride(0), rows, MMQ_LAYOUTS[layout], s)
+        else: r = L.cam_swiglu_mmq_q8_1(x.data_ptr(), u.data_ptr(), y.data_ptr(), kvalid, Kpad, x.stride(0), rows, MMQ_LAYOUTS[layout], s)
+    _lib.check(r, 'quantize_mmq_q8_1')
+    return y

@@ -19,13 +19,13 @@ def check_span(i0, n, max_ctx, what='pass'):
 
 
 def kv_pos_bytes(M, q8=False):
-    """bytes of one position's K | V row: 2 M fp16 values (the Q8_0 cache's rows are not built here)"""
-    if q8: raise ValueError('k3 KV cache: the Q8_0 cache form is not built in this library')
-    return 2 * M * 2
+    """bytes of one position's K | V row: 2 M fp16 values, or 2 (M / 32) Q8_0 blocks of 34 bytes"""
+    return 2 * (M // 32) * 34 if q8 else 2 * M * 2
 
 
 def kv_rows(cache, M, q8=False):
     """positions a KV cache holds, from its allocation"""
     pb = kv_pos_bytes(M, q8); nb = cache.numel() * cache.element_size()
+    if q8 and M % 32: raise ValueError(f'k3 KV cache: {M} values per position is not a whole number of q8_0 blocks')
     if nb % pb or not 0 < nb // pb < 2 ** 31: raise ValueError(f'k3 KV cache: {nb} bytes is not a whole number of {pb}-byte positions')
     return nb // pb

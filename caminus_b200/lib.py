@@ -32,6 +32,11 @@ SIGNATURES = {
     'q3p_qk_rope': [I, P, I, I, I, P, I, P, P, P],
     'q3p_qk_rope_yarn': [I, P, I, I, I, P, I, P, P, P],
     'cam_qk_rope_f16': [I, P, P, I, I, P, I, P, P, I, P],
+    'q3p_qk_rope_q8': [I, P, I, I, I, P, I, P, P, P, P],
+    'q3p_qk_rope_q8_yarn': [I, P, I, I, I, P, I, P, P, P, P],
+    'cam_quantize_mmq_q8_1': [P, P, I, I, L, I, I, P],
+    'cam_swiglu_mmq_q8_1': [P, P, P, I, I, L, I, I, P],
+    'cam_swiglu_mmq_q8_1_f16': [P, P, P, I, I, L, I, I, P],
     'pf_rms_mul': [P, P, P, P, P, I, I, F, I, P],
     'pf_hc_post_rms': [P, P, P, P, P, P, P, I, I, F, F, I, P],
     'pf_hc_post': [P, P, P, I, I, I, F, P],

@@ -11,7 +11,8 @@ from ..engine import k3
 
 I, F = ctypes.c_int, ctypes.c_float
 NULL = ctypes.c_void_p(0)
-YARN_MODULE = {False: 'q3m_prefill_yarn'}
+KVQ8_MODULE = 'q3m_prefill_kvq8'
+YARN_MODULE = {False: 'q3m_prefill_yarn', True: 'q3m_prefill_kvq8_yarn'}
 YARN_PAR = 2 * 128 + 2 + k3.YARN_TABLE_FLOATS      # q_norm | k_norm | theta_scale, eps | freq [64] | mscale
 
 
@@ -34,11 +35,11 @@ class Ops:
         """yarn: the long-context mode: qk_rope reads the YaRN table after eps in par (YARN_PAR floats)"""
         self.dev = torch.device(dev) if not isinstance(dev, torch.device) else dev
         self.module, self.q8, self.yarn = module, bool(q8), bool(yarn)
-        if self.q8: raise ValueError('q3m Ops: the Q8_0 KV cache form is not built in this library')
         if self.yarn and module != 'q3m_prefill': raise ValueError(f'q3m Ops: the long-context mode runs with q3m_prefill only (not {module})')
         with torch.cuda.device(self.dev):
             self.mod = hip.Module(module)
-            self.ropemod = hip.Module(YARN_MODULE[False]) if self.yarn else self.mod
+            self.kvmod = hip.Module(KVQ8_MODULE) if self.q8 else None
+            self.ropemod = hip.Module(YARN_MODULE[self.q8]) if self.yarn else (self.kvmod if self.q8 else self.mod)
 
     # -- the glue ----------------------------------------------------------------------------------------------------------
     def emb(self, W, rb, vocab, toks, x, n, N):
@@ -59,8 +60,9 @@ class Ops:
         """positions pos0 .. pos0 + n - 1 must be among the cache's first `rows` positions (2 * nkv * 128 fp16 per row; None:
         every row of the allocation), else k3.ContextBoundsError and nothing is launched"""
         if n < 1 or nkv < 1: raise ValueError(f'q3m {what}: n {n}, nkv {nkv}')
-        if cache.dtype != torch.float16: raise ValueError(f'q3m {what}: a F16 prefill needs a {torch.float16} cache, not {cache.dtype}')
-        alloc = k3.kv_rows(cache, nkv * 128, False)
+        want = torch.uint8 if self.q8 else torch.float16
+        if cache.dtype != want: raise ValueError(f'q3m {what}: a {"Q8" if self.q8 else "F16"} prefill needs a {want} cache, not {cache.dtype}')
+        alloc = k3.kv_rows(cache, nkv * 128, self.q8)
         if rows is not None and not 0 <= int(rows) <= alloc: raise ValueError(f'q3m {what}: rows {rows} of a cache of {alloc}')
         k3.check_span(pos0, n, alloc if rows is None else int(rows), what=f'q3m {what}')
 
@@ -71,6 +73,12 @@ class Ops:
         if par.dtype != torch.float32 or par.numel() < (YARN_PAR if self.yarn else 2 * 128 + 2):
             raise ValueError(f'q3m qk_rope: par needs {YARN_PAR if self.yarn else 2 * 128 + 2} fp32 values'
                              f'{" (q_norm | k_norm | theta_scale, eps | the YaRN table)" if self.yarn else ""}, not {par.numel()} {par.dtype}')
+        if self.q8:
+            if err is None or err.dtype != torch.int32 or err.numel() < 1: raise ValueError('q3m qk_rope: a Q8 cache needs its int32 error word')
+            if not cache.is_contiguous() or cache.data_ptr() % 4: raise ValueError('q3m qk_rope: the Q8 cache must be contiguous and 4-byte aligned')
+            with _On(self.dev):
+                self.ropemod.q3p_qk_rope_q8((n, nh + nkv), (128,), qkv, I(ldq), I(nh), I(nkv), par, I(pos0), q16, cache, err)
+            return
         if err is not None: raise ValueError('q3m qk_rope: err is the Q8 cache\'s word')
         with _On(self.dev):
             self.ropemod.q3p_qk_rope((n, nh + nkv), (128,), qkv, I(ldq), I(nh), I(nkv), par, I(pos0), q16, cache)

@@ -110,10 +110,31 @@ int q3p_qk_rope(int n, const float * qkv, int ldq, int nh, int nkv, const float 
 int q3p_qk_rope_yarn(int n, const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, void * q16, void * cache,
                      void * stream);
 
+/* The Q8_0 KV cache form: cache is a uint8 buffer of rows of 2 * (nkv * 128 / 32) * 34 bytes (Q8_0 blocks of K for all heads, then
+ * of V); K and q16 are the 128-point Walsh-Hadamard transform of the fp16-rounded RoPE result, V the fp16-rounded values; err is
+ * an int32 word a refused block (non-finite value, scale out of range) ORs 2 into, its bytes left alone.
+ * Replaces q3p_qk_rope_q8, kernels/q3m_prefill.hip:534-535 (objects q3m_prefill_kvq8 / q3m_prefill_kvq8_yarn); codec
+ * kernels/own_kv_codec.h:31-75, transform kernels/own_kv_rot128.h:21-33; wrapper python/caminus/prefill/q3m_ops.py:122-137. */
+int q3p_qk_rope_q8(int n, const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, void * q16, void * cache, int * err,
+                   void * stream);
+int q3p_qk_rope_q8_yarn(int n, const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, void * q16, void * cache,
+                        int * err, void * stream);
+
 /* The same statements on fp16 q [n][nh][128] and k [n][nkv][128], fp16 out (qo / ko may alias q / k); yarn as above.
  * No kernel of this signature in the reference; arithmetic of kernels/q3m_prefill.hip:552-590. */
 int cam_qk_rope_f16(int n, const void * q, const void * k, int nh, int nkv, const float * par, int pos0, void * qo, void * ko,
                     int yarn, void * stream);
+
+/* ---- Q8_1 in the MMQ layout (block_q8_1_mmq, kernels/ggml_mmq/mmq.cuh:63-82): blocks [Kpad / 128][rows] of 144 bytes = 16 bytes of
+ * per-32 scales + 128 int8; d_inv = 127 / amax, q = roundf(x * d_inv), d = 1 / d_inv. layout 0 = D4 (four fp32 d), 1 = DS4 (four
+ * (fp16 d, fp16 sum)). x rows of stride ld, kvalid values each (a multiple of 4), zero-padded to Kpad (a multiple of 128). An
+ * all-zero group stores d = 0 and codes 0.
+ * cam_quantize_mmq_q8_1 replaces the dense case of quantize_mmq_q8_1, kernels/ggml_mmq/quantize_mmq.cuh:41-140.
+ * cam_swiglu_mmq_q8_1[_f16] write the blocks of silu(g) * u: the epilogue of the reference's fused gate / up kernel,
+ * kernels/prefill_moe.hip:339-396, as a standalone producer. ---- */
+int cam_quantize_mmq_q8_1(const float * x, void * y, int kvalid, int Kpad, long ld, int rows, int layout, void * stream);
+int cam_swiglu_mmq_q8_1(const float * g, const float * u, void * y, int kvalid, int Kpad, long ld, int rows, int layout, void * stream);
+int cam_swiglu_mmq_q8_1_f16(const void * g, const void * u, void * y, int kvalid, int Kpad, long ld, int rows, int layout, void * stream);
 
 /* ---- the hyper-connection ("Coder") line's glue: kernels/prefill_glue.hip; wrappers python/caminus/prefill/glue.py:143-313 ----
  * The reference bakes the row width (GLUE_NI x 256 = 2560 / 2048 / 5120) into three code objects; here it is the last argument

@@ -351,3 +351,40 @@ def pf_qk_nr(xin, head_stride, heads, w, D, nrot, theta_scale, eps, pos0, nblock
     xin = _f32(xin).reshape(-1); w = _f32(w); out = np.empty((nblocks, D), np.float32)
     lib().orc_pf_qk_nr(_p(xin), I(head_stride), I(heads), _p(w), I(D), I(nrot), F(theta_scale), F(eps), I(pos0), _p(out), I(nblocks))
     return out
+
+
+def mmq_q8_1(x, kvalid, Kpad, layout, u=None):
+    """Q8_1 in the MMQ layout of rows x [rows, ld] (float32, or float16 with u: SwiGLU): uint8 [Kpad / 128, rows, 144].
+    u given: the values are silu(x) * u."""
+    rows, ld = x.shape; y = np.empty((Kpad // 128, rows, 144), np.uint8)
+    if x.dtype == np.float16:
+        x = _c(x, np.float16); u = _c(u, np.float16)
+        lib().orc_mmq_q8_1_f16(_p(x), _p(u), _p(y), I(kvalid), I(Kpad), L_(ld), I(rows), I(layout))
+    else:
+        x = _f32(x); u = _f32(u)
+        lib().orc_mmq_q8_1(_p(x), _p(u), _p(y), I(kvalid), I(Kpad), L_(ld), I(rows), I(layout), I(0 if u is None else 1))
+    return y
+
+
+def qk_rope_q8(qkv, ldq, nh, nkv, par, pos0, cache, n, yarn=False, sum_order=0):
+    """q3p_qk_rope_q8: cache uint8 (flat; rows of 2 (nkv 128 / 32) 34 bytes) is copied and updated.
+    Returns (q16 float16 [n, nh, 128], cache, err)"""
+    qkv = _f32(qkv).reshape(-1); par = _f32(par); cache = _c(cache, np.uint8).reshape(-1).copy()
+    q16 = np.empty((n, nh, 128), np.uint16); err = np.zeros(1, np.int32)
+    lib().orc_qk_rope_q8(_p(qkv), I(ldq), I(nh), I(nkv), _p(par), I(pos0), _p(q16), _p(cache), _p(err), I(n), I(int(yarn)), I(int(sum_order)))
+    return q16.view(np.float16), cache, int(err[0])
+
+
+def hadamard128(x):
+    y = _f32(x).copy().reshape(-1, 128)
+    lib().orc_hadamard128(_p(y), I(y.shape[0]))
+    return y.reshape(np.shape(x))
+
+
+def q8_kv_rows(k, v):
+    """K, V float32 [rows, nkv, 128] -> (uint8 [rows, 2 (nkv 128 / 32) 34], refused blocks)"""
+    k = _f32(k); v = _f32(v); rows, nkv, _ = k.shape
+    out = np.zeros((rows, 2 * (nkv * 128 // 32) * 34), np.uint8)
+    lib().orc_q8_kv_rows.restype = ctypes.c_int
+    bad = lib().orc_q8_kv_rows(_p(k), _p(v), _p(out), I(rows), I(nkv))
+    return out, int(bad)

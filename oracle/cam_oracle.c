@@ -543,3 +543,125 @@ void orc_pf_qk_nr(const float * xin, int head_stride, int heads, const float * w
         }
     }
 }
+
+/* ==== Q8_1 in the MMQ layout (kernels/ggml_mmq/mmq.cuh:63-82 block_q8_1_mmq; algebra of kernels/ggml_mmq/quantize_mmq.cuh:41-140 and
+ * of the fused gate / up epilogue, kernels/prefill_moe.hip:364-396) ==================================================================
+ * Rows of K values are cut into blocks of 128; block (kb, row) sits at index kb * rows + row and is 144 bytes: 16 bytes of scales
+ * then 128 int8. Per group of 32: amax; d_inv = 127.0f / amax; q = roundf(x * d_inv) (a product, not the division of the 36-byte
+ * form); d = 1.0f / d_inv. layout 0 (D4): four fp32 d. layout 1 (DS4): four (fp16 d, fp16 sum), sum = ((x0 + x1) + x2) + x3 per
+ * four values, then partners 4, 2, 1 over the group's eight fours. An all-zero group stores d = 0 and codes 0 (the reference's
+ * arithmetic yields 0 * inf = NaN there, whose int8 conversion is 0 on its GPUs). Values at k >= kvalid are 0 (row padding). */
+static void mmq_group(const float * x, int8_t * q, float * d_out, float * sum_out) {
+    float amax = 0.0f;
+    for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(x[i]));
+    float p[8], t[8];
+    for (int l = 0; l < 8; l++) p[l] = ((x[4 * l] + x[4 * l + 1]) + x[4 * l + 2]) + x[4 * l + 3];
+    for (int m = 4; m >= 1; m >>= 1) { for (int l = 0; l < 8; l++) t[l] = p[l] + p[l ^ m]; memcpy(p, t, sizeof p); }
+    *sum_out = p[0];
+    if (amax == 0.0f) { *d_out = 0.0f; memset(q, 0, 32); return; }
+    const float d_inv = 127.0f / amax;
+    for (int i = 0; i < 32; i++) {
+        const float v = x[i] * d_inv;
+        q[i] = fabsf(v) < 127.5f ? (int8_t)roundf(v) : 0;
+    }
+    *d_out = 1.0f / d_inv;
+}
+static void mmq_store(uint8_t * blk, int grp, int layout, float d, float sum, const int8_t * q) {
+    if (layout == 0) memcpy(blk + 4 * grp, &d, 4);
+    else { const uint16_t hd = f2h(d), hs = f2h(sum); memcpy(blk + 4 * grp, &hd, 2); memcpy(blk + 4 * grp + 2, &hs, 2); }
+    memcpy(blk + 16 + 32 * grp, q, 32);
+}
+/* x: rows of stride ld floats; K padded to Kpad (a multiple of 128) with zeros past kvalid; mode 0: values = x; 1: silu(x) * u */
+void orc_mmq_q8_1(const float * x, const float * u, uint8_t * y, int kvalid, int Kpad, long ld, int rows, int layout, int mode) {
+    for (int r = 0; r < rows; r++)
+        for (int kb = 0; kb < Kpad / 128; kb++) {
+            uint8_t * blk = y + ((size_t)kb * rows + r) * 144;
+            for (int grp = 0; grp < 4; grp++) {
+                float v[32]; int8_t q[32]; float d, s;
+                for (int i = 0; i < 32; i++) {
+                    const int k = kb * 128 + grp * 32 + i;
+                    v[i] = k < kvalid ? (mode ? orc_silu(x[(size_t)r * ld + k]) * u[(size_t)r * ld + k] : x[(size_t)r * ld + k]) : 0.0f;
+                }
+                mmq_group(v, q, &d, &s);
+                mmq_store(blk, grp, layout, d, s, q);
+            }
+        }
+}
+void orc_mmq_q8_1_f16(const uint16_t * g, const uint16_t * u, uint8_t * y, int kvalid, int Kpad, long ld, int rows, int layout) {
+    for (int r = 0; r < rows; r++)
+        for (int kb = 0; kb < Kpad / 128; kb++) {
+            uint8_t * blk = y + ((size_t)kb * rows + r) * 144;
+            for (int grp = 0; grp < 4; grp++) {
+                float v[32]; int8_t q[32]; float d, s;
+                for (int i = 0; i < 32; i++) {
+                    const int k = kb * 128 + grp * 32 + i;
+                    v[i] = k < kvalid ? orc_silu(h2f(g[(size_t)r * ld + k])) * h2f(u[(size_t)r * ld + k]) : 0.0f;
+                }
+                mmq_group(v, q, &d, &s);
+                mmq_store(blk, grp, layout, d, s, q);
+            }
+        }
+}
+
+/* ==== the Q8_0 KV cache form of q3p_qk_rope (kernels/q3m_prefill.hip:526-535, 541-546, 572-583; kernels/own_kv_codec.h:31-75;
+ * kernels/own_kv_rot128.h:21-33; CPU reference python/caminus/ref_kv.py hadamard128 / encode_q8_kv) =========================== */
+static inline float f16r(float x) { return h2f(f2h(x)); }                 /* own_kv_f16r: rounded to fp16 and back */
+
+/* the orthonormal Walsh-Hadamard transform of 128 values: for h = 1, 2, .. 64 the pair (i, i + h) of i with bit h clear becomes
+ * (a + b, a - b), then each value times fp32(1 / sqrt(128)) */
+static void hadamard128(float * y) {
+    for (int h = 1; h < 128; h <<= 1)
+        for (int i = 0; i < 128; i++)
+            if (!(i & h)) { const float a = y[i], b = y[i + h]; y[i] = a + b; y[i + h] = a - b; }
+    for (int i = 0; i < 128; i++) y[i] = y[i] * 0x1.6a09e6p-4f;
+}
+/* own_kv_q8_encode: one block of 32 -> 34 bytes (fp16 d, 32 int8); returns 0 when the block is refused (its bytes are left alone) */
+static int q8_0_encode(const float * x, uint8_t * y) {
+    float amax = 0.0f; int finite = 1;
+    for (int j = 0; j < 32; j++) { finite &= isfinite(x[j]) != 0; amax = fmaxf(amax, fabsf(x[j])); }
+    if (!finite) return 0;
+    const float d = amax / 127.0f;
+    const float inv = d != 0.0f ? 1.0f / d : 0.0f;
+    const uint16_t stored = f2h(d);
+    if (amax != 0.0f && (d == 0.0f || !isfinite(d) || !isfinite(inv) || !isfinite(h2f(stored)))) return 0;
+    memcpy(y, &stored, 2);
+    for (int j = 0; j < 32; j++) y[2 + j] = (uint8_t)(int8_t)roundf(x[j] * inv);
+    return 1;
+}
+/* q3p_qk_rope_q8: as orc_qk_rope; q16 = fp16 of the transform of the fp16-rounded RoPE result; the cache row (2 (M / 32) 34 bytes,
+ * M = nkv 128) = Q8_0 blocks of the transformed fp16-rounded K, then of the fp16-rounded V; a refused block ORs 2 into *err */
+void orc_qk_rope_q8(const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, uint16_t * q16, uint8_t * cache,
+                    int32_t * err, int n, int yarn, int sum_order) {
+    const size_t M = (size_t)nkv * 128, rowb = 2 * (M / 32) * 34;
+    for (int t = 0; t < n; t++) {
+        const int pos = pos0 + t;
+        float rc[64], rs[64], y[128];
+        pos_table(par, pos, yarn, rc, rs);
+        const float * row = qkv + (size_t)t * ldq;
+        uint8_t * cw = cache + (size_t)pos * rowb;
+        for (int hy = 0; hy < nh + nkv; hy++) {
+            const int isq = hy < nh, g = hy - nh;
+            const float * x = isq ? row + (size_t)hy * 128 : row + (size_t)nh * 128 + (size_t)g * 128;
+            head_norm_rope(x, isq ? par : par + 128, par[257], rc, rs, y, sum_order);
+            for (int i = 0; i < 128; i++) y[i] = f16r(y[i]);
+            hadamard128(y);
+            if (isq) { for (int i = 0; i < 128; i++) q16[((size_t)t * nh + hy) * 128 + i] = f2h(y[i]); continue; }
+            for (int w = 0; w < 4; w++) if (!q8_0_encode(y + 32 * w, cw + ((size_t)g * 4 + w) * 34)) *err |= 2;
+            float v[128];
+            for (int i = 0; i < 128; i++) v[i] = f16r(row[(size_t)nh * 128 + M + (size_t)g * 128 + i]);
+            for (int w = 0; w < 4; w++) if (!q8_0_encode(v + 32 * w, cw + (M / 32 + (size_t)g * 4 + w) * 34)) *err |= 2;
+        }
+    }
+}
+void orc_hadamard128(float * y, int rows) { for (int r = 0; r < rows; r++) hadamard128(y + (size_t)r * 128); }
+/* rows of K [rows][nkv][128] (already rotated by the caller) and V -> Q8_0 cache rows (python/caminus/ref_kv.py encode_q8_kv); returns
+ * the number of refused blocks */
+int orc_q8_kv_rows(const float * k, const float * v, uint8_t * out, int rows, int nkv) {
+    const size_t M = (size_t)nkv * 128, rowb = 2 * (M / 32) * 34; int bad = 0;
+    for (int r = 0; r < rows; r++)
+        for (size_t b = 0; b < M / 32; b++) {
+            bad += !q8_0_encode(k + (size_t)r * M + b * 32, out + (size_t)r * rowb + b * 34);
+            bad += !q8_0_encode(v + (size_t)r * M + b * 32, out + (size_t)r * rowb + (M / 32 + b) * 34);
+        }
+    return bad;
+}

@@ -18,7 +18,7 @@ sys.path.insert(0, os.path.join(REF, 'python', 'caminus', '_vendor'))
 sys.path.insert(0, os.path.join(REF, 'tests', 'engine'))
 OUT = os.path.dirname(os.path.abspath(__file__))
 
-from caminus import own_dequant, rope, ref_q35   # noqa: E402
+from caminus import own_dequant, rope, ref_q35, ref_kv   # noqa: E402
 import golden_util                                 # noqa: E402
 from gguf import quants as gq                      # noqa: E402
 from gguf.constants import GGMLQuantizationType as QT   # noqa: E402
@@ -135,7 +135,20 @@ def make_rope():
                         q_plain=q_plain, k_plain=k_plain, q_yarn=q_yarn, k_yarn=k_yarn, tab=tab)
 
 
+def make_q8_kv():
+    """the Q8_0 KV rows of fp16-valued K / V: encode_q8_kv(hadamard128(K), V) (python/caminus/ref_kv.py), the statement the
+    reference gates its Q8 prefill rows with (tests/engine/test_q3m_yarn_rope.py:121-123)"""
+    g = np.random.default_rng(31); rows, nkv = 9, 2
+    K = (g.standard_normal((rows, nkv, 128)) * 0.8).astype(np.float16).astype(np.float32)
+    V = (g.standard_normal((rows, nkv, 128)) * 0.5).astype(np.float16).astype(np.float32)
+    K[0, 0, :32] = 0; V[1, 1, 32:64] = 0                         # all-zero blocks
+    K[2, 0, 5] = 30.0; V[3, 0] *= np.float32(1e-3)               # an outlier; a small block
+    H = ref_kv.hadamard128(K)
+    raw = ref_kv.encode_q8_kv(H, V, ref_kv.Q8KVLayout(nkv, 128))
+    np.savez_compressed(os.path.join(OUT, 'q8_kv.npz'), K=K, V=V, H=H, raw=raw)
+
+
 if __name__ == '__main__':
-    make_q4k(); make_q8(); make_swiglu(); make_rms(); make_rope()
+    make_q4k(); make_q8(); make_swiglu(); make_rms(); make_rope(); make_q8_kv()
     for f in sorted(os.listdir(OUT)):
         if f.endswith('.npz'): print(f, os.path.getsize(os.path.join(OUT, f)), 'bytes')

@@ -373,3 +373,33 @@ def test_add_rms16_single_row_kernel_and_many_rows_agree(O):
     for a, b in zip(outs[0], outs[1]): assert same(a[:5], b)
     xo, ho, h16o = oracle.add_rms16(x0[:5], nw, 1e-6, d=dd[:5], w=ww[:5], S=2)
     assert same(outs[1][0], xo) and same(outs[1][1], ho) and same(outs[1][2], h16o)
+
+
+# ---- the Q8_0 KV cache form ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize('yarn', [False, True])
+@pytest.mark.parametrize('n,nh,nkv,pos0', [(75, 32, 4, 1000), (1, 32, 4, 0), (33, 16, 2, 5), (20, 5, 3, 2)])
+def test_qk_rope_q8(n, nh, nkv, pos0, yarn):
+    """q3p_qk_rope_q8: q16 and the Q8_0 row bytes are the oracle's; the row is encode(hadamard(K16), V16) of the F16 object's
+    halves (tests/engine/test_q3m_yarn_rope.py:121-123); rows below the chunk untouched; a refused block sets bit 2 of err"""
+    g = np.random.default_rng(n + nh); M = nkv * 128; ldq = nh * 128 + 2 * M; rowb = 2 * (M // 32) * 34
+    par = synth.rope_par(seed=n, yarn_table=synth.yarn_table() if yarn else None)
+    qkv = (g.standard_normal((n, ldq)) * 3).astype(np.float32)
+    cache0 = g.integers(0, 256, (pos0 + n + 2) * rowb, dtype=np.uint8)
+    R = q3m_ops.Ops(DEV, q8=True, yarn=yarn)
+    cache = cu(cache0); q16 = torch.zeros(n, nh, 128, dtype=torch.float16, device=DEV); err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    R.qk_rope(cu(qkv.reshape(-1)), ldq, nh, nkv, cu(par), pos0, q16, cache, n, err=err)
+    qo, co, eo = oracle.qk_rope_q8(qkv, ldq, nh, nkv, par, pos0, cache0, n, yarn=yarn, sum_order=1)
+    assert int(err.item()) == 0 == eo and same(q16, qo) and np.array_equal(cache.cpu().numpy(), co)
+    F16 = q3m_ops.Ops(DEV, yarn=yarn)
+    c16 = torch.zeros((pos0 + n) * 2 * M, dtype=torch.float16, device=DEV); q16f = torch.zeros_like(q16)
+    F16.qk_rope(cu(qkv.reshape(-1)), ldq, nh, nkv, cu(par), pos0, q16f, c16, n)
+    rows16 = c16.cpu().numpy().reshape(-1, 2, nkv, 128)[pos0:].astype(np.float32)
+    want, _ = oracle.q8_kv_rows(oracle.hadamard128(rows16[:, 0]), rows16[:, 1])
+    assert np.array_equal(cache.cpu().numpy().reshape(-1, rowb)[pos0:pos0 + n], want)
+    bad = qkv.copy(); bad[n // 2, nh * 128 + M + 7] = np.nan          # a NaN in V: that block is refused and keeps its bytes
+    cache = cu(cache0); err.zero_()
+    R.qk_rope(cu(bad.reshape(-1)), ldq, nh, nkv, cu(par), pos0, q16, cache, n, err=err)
+    _, co, eo = oracle.qk_rope_q8(bad, ldq, nh, nkv, par, pos0, cache0, n, yarn=yarn, sum_order=1)
+    assert int(err.item()) == 2 == eo and np.array_equal(cache.cpu().numpy(), co)
+    with pytest.raises(ValueError): R.qk_rope(cu(qkv.reshape(-1)), ldq, nh, nkv, cu(par), pos0, q16, cache, n)          # err is required
+    with pytest.raises(k3.ContextBoundsError): R.qk_rope(cu(qkv.reshape(-1)), ldq, nh, nkv, cu(par), pos0 + 3, q16, cache, n, err=err)

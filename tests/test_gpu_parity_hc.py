@@ -127,3 +127,22 @@ def test_training_line_forwards():
     assert same(ro, oracle.residual_slices_fwd(x, bits(m), bits(mlp), bits(ys), pos, d))
     fuse.residual_slices_fwd(((n * d // 4 + 255) // 256,), (256,), cu(x), m, mlp, NUL, NUL, ro, I(d), L(n * d // 4))
     assert same(ro, r3)
+
+
+@pytest.mark.parametrize('layout', ['D4', 'DS4'])
+@pytest.mark.parametrize('rows,K', [(1, 128), (37, 768), (150, 2560), (9, 300)])
+def test_mmq_q8_1(layout, rows, K):
+    """the MMQ-layout quantiser and its fused SwiGLU form: the oracle's bytes (tests/prefill/test_prefill_moe.py:135 gates the
+    reference's fused bytes against its unfused path the same way)"""
+    from caminus_b200.engine import gguf
+    g = np.random.default_rng(rows + K); lay = gguf.MMQ_LAYOUTS[layout]; Kp = (K + 127) // 128 * 128
+    x = acts(g, (rows, K), 0.7); u = acts(g, (rows, K))
+    if rows > 1: x[1, :32] = 0
+    assert same(gguf.quantize_mmq_q8_1(cu(x), layout), oracle.mmq_q8_1(x, K, Kp, lay))
+    assert same(gguf.quantize_mmq_q8_1(cu(x), layout, u=cu(u)), oracle.mmq_q8_1(x, K, Kp, lay, u=u))
+    xh, uh = x.astype(np.float16), u.astype(np.float16)
+    fused = gguf.quantize_mmq_q8_1(cu(xh), layout, u=cu(uh))
+    assert same(fused, oracle.mmq_q8_1(xh, K, Kp, lay, u=uh))
+    # fused == unfused: silu(g) * u written as fp32 by pf_swiglu's statements, then the plain quantiser
+    h = oracle.swiglu_f32_from_f16(xh.reshape(-1), uh.reshape(-1)).reshape(rows, K)
+    assert same(fused, gguf.quantize_mmq_q8_1(cu(h), layout))

@@ -152,3 +152,24 @@ def test_sincos_and_powi_sequences():
         want = np.float32(np.float64(ts) ** j)
         assert oracle.powi(ts, j) == float(want)
     assert all(abs(oracle.rsqrt(v) * np.sqrt(np.float64(np.float32(v))) - 1) < 1.2e-7 for v in (1e-6, 0.5, 1.0, 3.7, 1e4))
+
+
+def test_q8_kv_rows_bitwise(golden):
+    """the Q8_0 KV row bytes and the 128-point Hadamard transform: the reference's CPU reference (python/caminus/ref_kv.py), bit for bit"""
+    f = golden('q8_kv')
+    assert np.array_equal(oracle.hadamard128(f['K']).view(np.uint32), f['H'].view(np.uint32))
+    raw, bad = oracle.q8_kv_rows(f['H'], f['V'])
+    assert bad == 0 and np.array_equal(raw, f['raw'])
+    # the Q8 object's row = encode(hadamard(K16), V16) of the F16 object's halves (tests/engine/test_q3m_yarn_rope.py:121-123)
+    g = np.random.default_rng(3); nh, nkv, n, pos0 = 4, 2, 5, 7; M = nkv * 128; ldq = nh * 128 + 2 * M
+    qkv = (g.standard_normal((n, ldq)) * 1.3).astype(np.float32)
+    par = np.concatenate([(0.5 + g.random(256)), [np.float32(np.float32(1e6) ** np.float32(-2.0 / 128)), 1e-6]]).astype(np.float32)
+    q16, c16 = oracle.qk_rope(qkv, ldq, nh, nkv, par, pos0, np.zeros((pos0 + n) * 2 * M, np.float16), n)
+    q8, c8, err = oracle.qk_rope_q8(qkv, ldq, nh, nkv, par, pos0, np.zeros((pos0 + n) * 2 * (M // 32) * 34, np.uint8), n)
+    rows16 = c16.reshape(-1, 2, nkv, 128)[pos0:].astype(np.float32)
+    want, _ = oracle.q8_kv_rows(oracle.hadamard128(rows16[:, 0]), rows16[:, 1])
+    assert err == 0 and np.array_equal(c8.reshape(pos0 + n, -1)[pos0:], want) and not c8.reshape(pos0 + n, -1)[:pos0].any()
+    assert np.array_equal(q8.view(np.uint16), oracle.hadamard128(q16.astype(np.float32)).astype(np.float16).view(np.uint16))
+    bad = qkv.copy(); bad[1, nh * 128 + 3] = np.inf
+    _, _, err = oracle.qk_rope_q8(bad, ldq, nh, nkv, par, pos0, np.zeros((pos0 + n) * 2 * (M // 32) * 34, np.uint8), n)
+    assert err == 2                                                    # a refused block sets the prefill's error word
