@@ -37,6 +37,12 @@ SIGNATURES = {
     'cam_quantize_mmq_q8_1': [P, P, I, I, L, I, I, P],
     'cam_swiglu_mmq_q8_1': [P, P, P, I, I, L, I, I, P],
     'cam_swiglu_mmq_q8_1_f16': [P, P, P, I, I, L, I, I, P],
+    'actq_fwd_bf16': [I, P, P, P, I, F, I, P],
+    'actq_fwd_f32': [I, P, P, P, I, F, I, P],
+    'actq_fwd_codes_bf16': [I, P, P, P, P, I, F, I, P],
+    'actq_fwd_codes_f32': [I, P, P, P, P, I, F, I, P],
+    'silu_mul_actq_fwd': [I, P, I, I, P, P, P, F, I, P],
+    'block_entry_fwd': [I, P, P, P, I, F, P, P, P, P, P, I, F, I, P],
     'pf_rms_mul': [P, P, P, P, P, I, I, F, I, P],
     'pf_hc_post_rms': [P, P, P, P, P, P, P, I, I, F, F, I, P],
     'pf_hc_post': [P, P, P, I, I, I, F, P],

@@ -175,6 +175,21 @@ int cast_bf16(const float * x, void * out, long n, void * stream);
 int residual_slices_fwd(const float * x, const void * m, const void * mlp, const void * ys, const int * pos, float * out, int d, long n4,
                         void * stream);
 
+/* ---- the training line's activation quantiser, forward: kernels/actq.hip:96-132, 247-274, 307-326; wrappers
+ * python/caminus/train/actq.py:22-169. Per row of K (a multiple of 128, <= 8192): u = bf16(FWHT128(bf16(src)) * bf16(1 / sqrt(128)));
+ * s = max(amax * clip / qmax, 1e-8); q = clamp(rint(u / s), -qmax - 1, qmax), qmax <= 7; y = bf16(q * s) (bf16 [M][K], nullable when
+ * codes are written), s [M], codes = the int4 codes packed two per byte along K (nullable). M = the reference's grid.x. ---- */
+int actq_fwd_bf16(int M, const void * x, void * y, float * s, int K, float clip, int qmax, void * stream);
+int actq_fwd_f32(int M, const float * x, void * y, float * s, int K, float clip, int qmax, void * stream);
+int actq_fwd_codes_bf16(int M, const void * x, void * y, float * s, void * codes, int K, float clip, int qmax, void * stream);
+int actq_fwd_codes_f32(int M, const float * x, void * y, float * s, void * codes, int K, float clip, int qmax, void * stream);
+/* the source is the MLP activation bf16(bf16(silu(g)) * u) of rows gu = [g | u] (bf16, row stride ld), never materialised */
+int silu_mul_actq_fwd(int M, const void * gu, int ld, int F, void * y, float * s, void * codes, float clip, int qmax, void * stream);
+/* the source is RMSNorm(x) = (x * rstd) * nw, never materialised; rstd_out [M]; nab <= 16 gate projections
+ * ab[j] = bf16(sum_k bf16(h_k) * wab[j][k]) (wab bf16 [nab][d], ab bf16 [M][nab]; both null when nab = 0) */
+int block_entry_fwd(int M, const float * x, const float * nw, const void * wab, int nab, float eps, void * y, float * s, void * codes,
+                    void * ab, float * rstd_out, int d, float clip, int qmax, void * stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -388,3 +388,27 @@ def q8_kv_rows(k, v):
     lib().orc_q8_kv_rows.restype = ctypes.c_int
     bad = lib().orc_q8_kv_rows(_p(k), _p(v), _p(out), I(rows), I(nkv))
     return out, int(bad)
+
+
+def actq_fwd(x, clip, qmax):
+    """x [M, K] float32, or uint16 (bf16 bits) -> (y uint16 [M, K], s float32 [M], codes uint16 [M, K / 4])"""
+    is_bf = x.dtype == np.uint16; x = _c(x, np.uint16 if is_bf else np.float32); M, K = x.shape
+    y = np.empty((M, K), np.uint16); s = np.empty(M, np.float32); codes = np.empty((M, K // 4), np.uint16)
+    lib().orc_actq_fwd(_p(x), I(int(is_bf)), _p(y), _p(s), _p(codes), I(M), I(K), F(clip), I(qmax))
+    return y, s, codes
+
+
+def silu_mul_actq_fwd(gu, Fw, clip, qmax):
+    gu = _c(gu, np.uint16); M, ld = gu.shape
+    y = np.empty((M, Fw), np.uint16); s = np.empty(M, np.float32); codes = np.empty((M, Fw // 4), np.uint16)
+    lib().orc_silu_mul_actq_fwd(_p(gu), I(ld), I(Fw), _p(y), _p(s), _p(codes), I(M), F(clip), I(qmax))
+    return y, s, codes
+
+
+def block_entry_fwd(x, nw, wab, eps, clip, qmax):
+    x = _f32(x); nw = _f32(nw); M, d = x.shape; nab = 0 if wab is None else wab.shape[0]
+    wab = None if wab is None else _c(wab, np.uint16)
+    y = np.empty((M, d), np.uint16); s = np.empty(M, np.float32); codes = np.empty((M, d // 4), np.uint16)
+    ab = np.empty((M, nab), np.uint16); rstd = np.empty(M, np.float32)
+    lib().orc_block_entry_fwd(_p(x), _p(nw), _p(wab), I(nab), F(eps), _p(y), _p(s), _p(codes), _p(ab), _p(rstd), I(M), I(d), F(clip), I(qmax))
+    return y, s, codes, ab, rstd

@@ -665,3 +665,99 @@ int orc_q8_kv_rows(const float * k, const float * v, uint8_t * out, int rows, in
         }
     return bad;
 }
+
+/* ==== the training line's activation quantiser (kernels/actq.hip:40-132, 225-274, 307-326) =========================================
+ * Per row of K (a multiple of 128, <= 8192), one workgroup of 8 waves; wave w takes chunks w, w + 8, ...; lane l of a chunk holds
+ * elements 4l .. 4l + 3. u = bf16(FWHT128(bf16(src)) * bf16(1 / sqrt(128))); amax by wave butterfly then lds[0], lds[1], .. in order;
+ * s = max(amax * clip / qmax, 1e-8); q = clamp(rint(u / s), -qmax - 1, qmax); y = bf16(q s); codes packed four per 16 bits. */
+static inline float rbf(float f) { return bf2f(f2bf_nan(f)); }
+static void fwht128(float * v) {      /* v[128]: lane l = v[4l .. 4l + 3]: stages 1, 2 inside the lane, 4 .. 64 across lanes (kernels/actq.hip:40-53) */
+    for (int l = 0; l < 32; l++) {
+        float * p = v + 4 * l; float a = p[0], b = p[1]; p[0] = a + b; p[1] = a - b;
+        a = p[2]; b = p[3]; p[2] = a + b; p[3] = a - b;
+        a = p[0]; b = p[2]; p[0] = a + b; p[2] = a - b;
+        a = p[1]; b = p[3]; p[1] = a + b; p[3] = a - b;
+    }
+    for (int m = 1; m < 32; m <<= 1) {
+        float t[128];
+        for (int l = 0; l < 32; l++) for (int e = 0; e < 4; e++) {
+            const float own = v[4 * l + e], pr = v[4 * (l ^ m) + e];
+            t[4 * l + e] = (l & m) ? (pr - own) : (own + pr);
+        }
+        memcpy(v, t, sizeof t);
+    }
+}
+/* src: K values of one row already in fp32 (before the bf16 rounding of the input) */
+static void actq_row(const float * src, uint16_t * y, float * s_out, int K, float clip, int qmax, uint16_t * codes) {
+    const int nch = K / 128;
+    float u[8192]; float wmax[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int ch = 0; ch < nch; ch++) {
+        float * c = u + 128 * ch;
+        for (int i = 0; i < 128; i++) c[i] = rbf(src[128 * ch + i]);
+        fwht128(c);
+        for (int i = 0; i < 128; i++) { c[i] = rbf(c[i] * 0.08837890625f); wmax[ch % 8] = fmaxf(wmax[ch % 8], fabsf(c[i])); }
+    }
+    float amax = wmax[0];
+    for (int w = 1; w < 8; w++) amax = fmaxf(amax, wmax[w]);
+    const float s = fmaxf(amax * clip / (float)qmax, 1e-8f);
+    if (s_out) *s_out = s;
+    for (int ch = 0; ch < nch; ch++) for (int l = 0; l < 32; l++) {
+        uint32_t pk = 0;
+        for (int e = 0; e < 4; e++) {
+            const int k = ch * 128 + l * 4 + e;
+            const float q = fminf(fmaxf(rintf(u[k] / s), (float)(-qmax - 1)), (float)qmax);
+            if (y) y[k] = f2bf_nan(q * s);
+            pk |= ((uint32_t)(int)q & 0xFu) << (4 * e);
+        }
+        if (codes) codes[ch * 32 + l] = (uint16_t)pk;
+    }
+}
+/* actq_fwd[_codes]_{bf16,f32} (kernels/actq.hip:315-326): x [M][K] bf16 (is_bf16) or fp32 */
+void orc_actq_fwd(const void * x, int is_bf16, uint16_t * y, float * s, uint16_t * codes, int M, int K, float clip, int qmax) {
+    for (int r = 0; r < M; r++) {
+        float src[8192];
+        for (int k = 0; k < K; k++) src[k] = is_bf16 ? bf2f(((const uint16_t *)x)[(size_t)r * K + k]) : ((const float *)x)[(size_t)r * K + k];
+        actq_row(src, y ? y + (size_t)r * K : NULL, s ? s + r : NULL, K, clip, qmax, codes ? codes + (size_t)r * (K / 4) : NULL);
+    }
+}
+/* silu_mul_actq_fwd (kernels/actq.hip:307-310, SiluMulSrc :89-95): the source is bf16(bf16(silu(g)) u) of gu rows [g | u], stride ld */
+void orc_silu_mul_actq_fwd(const uint16_t * gu, int ld, int F, uint16_t * y, float * s, uint16_t * codes, int M, float clip, int qmax) {
+    for (int r = 0; r < M; r++) {
+        float src[8192]; const uint16_t * row = gu + (size_t)r * ld;
+        for (int k = 0; k < F; k++) src[k] = rbf(rbf(orc_silu(bf2f(row[k]))) * bf2f(row[F + k]));
+        actq_row(src, y ? y + (size_t)r * F : NULL, s ? s + r : NULL, F, clip, qmax, codes ? codes + (size_t)r * (F / 4) : NULL);
+    }
+}
+/* the workgroup sum of actq.hip (wave butterfly, then lds[0] + lds[1] + ..): thread t's partial over k = t, t + 256, .. */
+static float block_sum_of(const float * part256) {
+    float lds[8];
+    for (int w = 0; w < 8; w++) lds[w] = wave_sum(part256 + 32 * w);
+    float r = lds[0];
+    for (int w = 1; w < 8; w++) r = r + lds[w];
+    return r;
+}
+/* block_entry_fwd (kernels/actq.hip:247-274): rstd = rsqrt(mean(x^2) + eps); the quantiser's source is x rstd w; nab gate
+ * projections ab[j] = bf16(sum_k bf16(h_k) wab[j][k]) */
+void orc_block_entry_fwd(const float * x, const float * nw, const uint16_t * wab, int nab, float eps, uint16_t * y, float * s,
+                         uint16_t * codes, uint16_t * ab, float * rstd_out, int M, int d, float clip, int qmax) {
+    for (int r = 0; r < M; r++) {
+        const float * xr = x + (size_t)r * d;
+        float part[256];
+        for (int t = 0; t < 256; t++) { float ss = 0.f; for (int k = t; k < d; k += 256) ss = fmaf(xr[k], xr[k], ss); part[t] = ss; }
+        const float rstd = orc_rsqrt(block_sum_of(part) / (float)d + eps);
+        rstd_out[r] = rstd;
+        float src[8192];
+        for (int k = 0; k < d; k++) src[k] = xr[k] * rstd * nw[k];
+        actq_row(src, y ? y + (size_t)r * d : NULL, s ? s + r : NULL, d, clip, qmax, codes ? codes + (size_t)r * (d / 4) : NULL);
+        for (int j = 0; j < nab; j++) {
+            for (int t = 0; t < 256; t++) {
+                float acc = 0.f;
+                for (int k = t; k < d; k += 256) acc = fmaf(rbf(xr[k] * rstd * nw[k]), bf2f(wab[(size_t)j * d + k]), acc);
+                part[t] = acc;
+            }
+            float lds[8]; for (int w = 0; w < 8; w++) lds[w] = wave_sum(part + 32 * w);
+            float v = 0.f; for (int w = 0; w < 8; w++) v += lds[w];
+            ab[(size_t)r * nab + j] = f2bf_nan(v);
+        }
+    }
+}

@@ -146,3 +146,31 @@ def test_mmq_q8_1(layout, rows, K):
     # fused == unfused: silu(g) * u written as fp32 by pf_swiglu's statements, then the plain quantiser
     h = oracle.swiglu_f32_from_f16(xh.reshape(-1), uh.reshape(-1)).reshape(rows, K)
     assert same(fused, gguf.quantize_mmq_q8_1(cu(h), layout))
+
+
+@pytest.mark.parametrize('M,K', [(1, 128), (37, 896), (300, 1024), (5, 8192)])
+def test_actq_family(M, K):
+    """actq_fwd_*, silu_mul_actq_fwd, block_entry_fwd: values, scales and packed codes are the oracle's bytes; silu extremes and a
+    row-strided view as tests/train/test_silu_mul_actq.py:21-47"""
+    from caminus_b200.train import actq as A
+    g = np.random.default_rng(M + K)
+    x = acts(g, (M, K), 2.0)
+    for xin in (cu(x), cu(x).bfloat16()):
+        y, c, s = A.actq_codes(xin, 4, 1.0)
+        ref = x if xin.dtype == torch.float32 else bits(xin).reshape(M, K)
+        yo, so, co = oracle.actq_fwd(ref, 1.0, 7)
+        assert same(y, yo) and same(s, so) and np.array_equal(c.cpu().numpy().view(np.uint16).reshape(-1), co.reshape(-1))
+        assert same(A.actq(xin, 4, 1.0), yo)
+    wide = torch.from_numpy(acts(g, (M, 2 * K + 64), 2.0)).bfloat16().to(DEV)
+    wide[0, :8] = torch.tensor([30, -30, 0, -0.0, 1e-3, -88, 88, 3]).bfloat16()
+    gu = wide[:, :2 * K]                                              # a row-strided view
+    y, c, s = A.silu_mul_actq(gu, 4, 0.9)
+    yo, so, co = oracle.silu_mul_actq_fwd(bits(wide.cpu()).reshape(M, -1), K, 0.9, 7)
+    assert same(y, yo) and same(s, so) and np.array_equal(c.cpu().numpy().view(np.uint16).reshape(-1), co.reshape(-1))
+    if K <= 1024:
+        nw = (g.random(K) + 0.5).astype(np.float32); wab = torch.from_numpy(acts(g, (6, K), 0.05)).bfloat16().to(DEV)
+        for w_ in (wab, None):
+            y, c, s, ab, rstd = A.block_entry(cu(x), cu(nw), w_, 1e-6, 4, 1.0)
+            yo, so, co, abo, ro = oracle.block_entry_fwd(x, nw, None if w_ is None else bits(w_).reshape(6, K), 1e-6, 1.0, 7)
+            assert same(y, yo) and same(s, so) and same(rstd, ro) and np.array_equal(c.cpu().numpy().view(np.uint16).reshape(-1), co.reshape(-1))
+            if w_ is not None: assert same(ab, abo)

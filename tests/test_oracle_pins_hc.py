@@ -96,3 +96,41 @@ def test_qk_nr_float64():
     ref[:, nrot // 2:nrot] = n64[:, :nrot // 2] * np.sin(th) + n64[:, nrot // 2:nrot] * np.cos(th)
     assert np.abs(got - ref).max() <= (1e-5 + 2.0 ** -22 * (pos0 + rows)) * np.abs(ref).max()
     assert np.array_equal(got[:, nrot:], oracle.pf_rms_mul(np.ascontiguousarray(x[:, :D]), w, 1e-6, D)[0][:, nrot:] * 0 + got[:, nrot:])
+
+
+def test_actq_family_against_float64():
+    """the activation quantiser against a float64 model of qat's fq_act(rotate(x, 128)): the scale within bf16 rounding of
+    amax clip / qmax, every dequantised value within half a step plus bf16 rounding of the rotated value, the packed codes
+    consistent with the dequantised values; block_entry's rstd and gate projections against float64"""
+    g = np.random.default_rng(12); M, K = 9, 896 + 128
+    H = np.array([[1.0]])
+    for _ in range(7): H = np.block([[H, H], [H, -H]])
+
+    def check(src64, y, s, codes, qmax=7):
+        u = (src64.reshape(M, -1, 128) @ H) * 0.08837890625
+        s64 = np.abs(u).max((1, 2)) / qmax
+        assert np.abs(s / s64 - 1).max() < 2.0 ** -7
+        yf = bf(y).float().numpy().astype(np.float64)
+        assert (np.abs(yf.reshape(u.shape) - u) <= (0.5 + 2.0 ** -6 * qmax) * s[:, None, None] + 2.0 ** -7 * np.abs(u)).all()
+        q = ((codes[:, :, None] >> (4 * np.arange(4))) & 15).reshape(M, -1).astype(np.int32); q = np.where(q > 7, q - 16, q)
+        assert np.abs(q).max() <= qmax + 1 and np.abs(q * s[:, None] - yf).max() <= 2.0 ** -7 * qmax * s.max()
+
+    x = torch.from_numpy(acts(g, (M, K), 2.0))
+    y, s, codes = oracle.actq_fwd(x.numpy(), 1.0, 7)
+    check(x.bfloat16().double().numpy(), y, s, codes)
+    y2, s2, codes2 = oracle.actq_fwd(bits(x.bfloat16()), 1.0, 7)
+    assert np.array_equal(y, y2) and np.array_equal(codes, codes2)                       # fp32 input is rounded to bf16 first
+    gu = torch.from_numpy(acts(g, (M, 2 * K), 2.0)).bfloat16()
+    y, s, codes = oracle.silu_mul_actq_fwd(bits(gu), K, 1.0, 7)
+    act = (torch.nn.functional.silu(gu[:, :K].double()).bfloat16().double() * gu[:, K:].double()).bfloat16().double().numpy()
+    check(act, y, s, codes)
+    assert np.array_equal(oracle.actq_fwd(oracle.silu_mul_bf16(bits(gu), K).reshape(M, K), 1.0, 7)[0], y)   # fused == unfused
+    nw = (g.random(K) + 0.5).astype(np.float32); wab = torch.from_numpy(acts(g, (4, K), 0.05)).bfloat16()
+    y, s, codes, ab, rstd = oracle.block_entry_fwd(x.numpy(), nw, bits(wab), 1e-6, 1.0, 7)
+    x64 = x.double().numpy(); r64 = 1 / np.sqrt((x64 ** 2).mean(-1) + 1e-6)
+    assert np.abs(rstd / r64 - 1).max() < 3e-7
+    h64 = x64 * r64[:, None] * nw
+    check(torch.from_numpy(h64).bfloat16().double().numpy(), y, s, codes)
+    ab64 = torch.from_numpy(h64).bfloat16().double().numpy() @ wab.double().numpy().T
+    assert np.abs(bf(ab).float().numpy() - ab64).max() <= 2.0 ** -7 * np.abs(ab64).max() + 1e-6
+    assert np.array_equal(oracle.rmsnorm_f32(x.numpy(), nw, 1e-6), (x.numpy() * rstd[:, None]) * nw)        # the two norms agree
