@@ -25,7 +25,7 @@ def bits(a):
     if torch.is_tensor(a):
         a = a.detach().cpu()
         a = a.view(torch.int16).numpy() if a.dtype == torch.bfloat16 else a.numpy()
-    return np.ascontiguousarray(a).view({2: np.uint16, 4: np.uint32}[a.dtype.itemsize]).reshape(-1)
+    return np.ascontiguousarray(a).view({1: np.uint8, 2: np.uint16, 4: np.uint32}[a.dtype.itemsize]).reshape(-1)
 
 
 def same(a, b): return np.array_equal(bits(a), bits(b))
