@@ -219,6 +219,41 @@ def single_op_lines(torch, dev, peak):
     toks = torch.randint(0, vocab, (n,), device=dev, dtype=torch.int32, generator=g)
     xo = [torch.empty(n, N, device=dev) for _ in range(2)]
     line('q4k_get_rows_16384x2048', n * (4 + 1152 + 8192), timed(lambda i: O.emb(W.view(-1), 1152, vocab, toks, xo[i], n, N), rot=2), n, 'rows_per_s')
+    del W, toks, xo
+    # ---- the later rows of the path (hyper-connection glue, MMQ layout, Q8_0 KV form, the training line's quantiser) ----
+    import ctypes
+    from caminus_b200.prefill import glue as PG
+    from caminus_b200.train import actq as A
+    rnd = lambda *s_, scale=1.0: torch.randn(*s_, device=dev, generator=g) * scale
+    gl = PG.Glue(dev); D = gl.D; T, HC = 8192, 4; R = T * HC
+    x = rnd(R, D, scale=3.0); w = 0.5 + torch.rand(HC, D, device=dev, generator=g); y = torch.empty_like(x); ybf = torch.empty(R, D, dtype=torch.bfloat16, device=dev)
+    scl = torch.empty(R, device=dev)
+    line('pf_rms_mul_R32768_K2560_bf16_scale', R * D * (4 + 2) + R * 4, timed(lambda i: gl.rms_mul(x, w, None, R, 1e-6, ybf=ybf, scale=scl)), R, 'rows_per_s')
+    line('pf_rms_mul_R32768_K2560_f32', R * D * 8, timed(lambda i: gl.rms_mul(x, w, y, R, 1e-6)), R, 'rows_per_s')
+    b = rnd(T, D); inj = rnd(T, HC, scale=3.0)
+    line('pf_hc_post_rms_T8192_HC4_bf16_scale', R * D * (8 + 2) + T * D * 4, timed(lambda i: gl.hc_post_rms(b, inj, x, w, T, HC, 1e-6, xnbf=ybf, scale=scl)), T, 'tokens_per_s')
+    gate = rnd(R, D); outm = torch.empty(T, D, device=dev)
+    line('pf_hc_mean_T8192_HC4', R * D * 8 + T * D * 4, timed(lambda i: gl.hc_mean(x, gate, outm, T, HC, scale=scl, w=w)), T, 'tokens_per_s')
+    del x, y, ybf, gate, outm, b
+    rows, K = 8192, 25600
+    gh = (rnd(rows, K, scale=1.5)).half(); uh = (rnd(rows, K, scale=1.5)).half(); ym = torch.empty(K // 128, rows, 144, dtype=torch.uint8, device=dev)
+    line('swiglu_mmq_q8_1_f16_T8192_K25600_D4', rows * K * 4 + rows * K // 128 * 144, timed(lambda i: gguf.quantize_mmq_q8_1(gh, 'D4', u=uh, y=ym)), rows, 'tokens_per_s')
+    del gh, uh, ym
+    T, nh, nkv = 4096, 32, 4; M = nkv * 128; ldq = nh * 128 + 2 * M; rowb = 2 * (M // 32) * 34
+    Q8 = q3m_ops.Ops(dev, q8=True)
+    qkv = [rnd(T * ldq, scale=3.0) for _ in range(2)]; q16 = torch.empty(T, nh, 128, dtype=torch.float16, device=dev)
+    cache = torch.zeros(T * rowb, dtype=torch.uint8, device=dev); err = torch.zeros(1, dtype=torch.int32, device=dev)
+    line('qk_rope_q8_f32_T4096', T * (ldq * 4 + nh * 256 + rowb), timed(lambda i: Q8.qk_rope(qkv[i], ldq, nh, nkv, par, 0, q16, cache, T, err=err), rot=2), T, 'tokens_per_s')
+    F16 = q3m_ops.Ops(dev); c16 = torch.zeros(T * 2 * M, dtype=torch.float16, device=dev)
+    line('qk_rope_f32_cache_T4096', T * (ldq * 4 + nh * 256 + 2 * M * 2), timed(lambda i: F16.qk_rope(qkv[i], ldq, nh, nkv, par, 0, q16, c16, T), rot=2), T, 'tokens_per_s')
+    del qkv, cache, c16
+    Mr, Kq = 32768, 1024
+    xa = rnd(Mr, Kq, scale=2.0).bfloat16()
+    line('actq_codes_bf16_M32768_K1024', Mr * Kq * (2 + 2 + 0.5) + Mr * 4, timed(lambda i: A.actq_codes(xa, 4, 1.0)), Mr, 'rows_per_s')
+    gu = rnd(8192, 2 * 4096, scale=2.0).bfloat16()
+    line('silu_mul_actq_M8192_F4096', 8192 * 4096 * (4 + 2 + 0.5) + 8192 * 4, timed(lambda i: A.silu_mul_actq(gu, 4, 1.0)), 8192, 'rows_per_s')
+    xe = rnd(Mr, 896, scale=2.0); nwe = 0.5 + torch.rand(896, device=dev, generator=g); wab = rnd(8, 896, scale=0.05).bfloat16()
+    line('block_entry_M32768_d896_nab8', Mr * 896 * (4 + 2 + 0.5) + Mr * (8 + 16), timed(lambda i: A.block_entry(xe, nwe, wab, 1e-6, 4, 1.0)), Mr, 'rows_per_s')
     return out
 
 
