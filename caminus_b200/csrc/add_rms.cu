@@ -216,6 +216,64 @@ __global__ void __launch_bounds__(256) add_rms_f32_row_kernel(float * __restrict
         }
 }
 
+// ---- the hyper-connection line's row norms on the warp-per-row mapping (pf_rms_mul, pf_hc_post_rms; K = 128 CH) -----------------
+// The same reference-order reduction as above. POST: the row is res[t, h], first updated in place to fma(b[t], p, res) with
+// p = 2 sigmoid(inj[t, h] rs). Outputs optional: y fp32, ybf bf16 (round to nearest even, no NaN case: prefill_glue.hip's to_bf16), scl.
+CAM_DEV uint32_t bf16x2_rne(float a, float b) {
+    const uint32_t ua = __float_as_uint(a), ub = __float_as_uint(b);
+    return ((ua + 0x7FFFu + ((ua >> 16) & 1u)) >> 16) | ((ub + 0x7FFFu + ((ub >> 16) & 1u)) & 0xffff0000u);
+}
+template <int CH, bool POST>
+__global__ void __launch_bounds__(RMS_WARPS * 32) rms_rows_vec_kernel(float * x, const float * __restrict__ w, float * y, uint16_t * __restrict__ ybf,
+                                                                      float * __restrict__ scl, int R, int wr, float eps, const float * __restrict__ b,
+                                                                      const float * __restrict__ inj, int HC, float rs) {
+    constexpr int K = 128 * CH;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int t = blockIdx.x * RMS_WARPS + warp; t < R; t += gridDim.x * RMS_WARPS) {
+        float * xr = x + (size_t)t * K + 4 * lane;
+        float4 xv[CH];
+#pragma unroll
+        for (int m = 0; m < CH; m++) xv[m] = *reinterpret_cast<const float4 *>(xr + 128 * m);
+        if (POST) {
+            const float * br = b + (size_t)(t / HC) * K + 4 * lane;
+            const float p = fmul(fdiv(1.0f, fadd(1.0f, cam_expf(-fmul(__ldg(inj + t), rs)))), 2.0f);
+#pragma unroll
+            for (int m = 0; m < CH; m++) {
+                const float4 bv = __ldg(reinterpret_cast<const float4 *>(br + 128 * m));
+                xv[m] = make_float4(ffma(bv.x, p, xv[m].x), ffma(bv.y, p, xv[m].y), ffma(bv.z, p, xv[m].z), ffma(bv.w, p, xv[m].w));
+                *reinterpret_cast<float4 *>(xr + 128 * m) = xv[m];
+            }
+        }
+        float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int m = 0; m < CH; m++) {
+            const int q = 4 * (m & 1);
+            a[q + 0] = ffma(xv[m].x, xv[m].x, a[q + 0]); a[q + 1] = ffma(xv[m].y, xv[m].y, a[q + 1]);
+            a[q + 2] = ffma(xv[m].z, xv[m].z, a[q + 2]); a[q + 3] = ffma(xv[m].w, xv[m].w, a[q + 3]);
+        }
+        const float tot = ref_total_f32(a, lane);
+        const float scale = cam_rsqrt(fadd(fdiv(tot, (float)K), eps));
+        if (scl && lane == 0) scl[t] = scale;
+        const float * wv = w + (size_t)(POST ? t % HC : t % wr) * K + 4 * lane;
+#pragma unroll
+        for (int m = 0; m < CH; m++) {
+            const float4 ww = __ldg(reinterpret_cast<const float4 *>(wv + 128 * m));
+            const float4 v = make_float4(fmul(fmul(xv[m].x, scale), ww.x), fmul(fmul(xv[m].y, scale), ww.y), fmul(fmul(xv[m].z, scale), ww.z),
+                                         fmul(fmul(xv[m].w, scale), ww.w));
+            if (y) *reinterpret_cast<float4 *>(y + (size_t)t * K + 4 * lane + 128 * m) = v;
+            if (ybf) st64_stream(ybf + (size_t)t * K + 4 * lane + 128 * m, make_uint2(bf16x2_rne(v.x, v.y), bf16x2_rne(v.z, v.w)));
+        }
+    }
+}
+
+template <int CH, bool POST>
+int launch_rows_vec(float * x, const float * w, float * y, uint16_t * ybf, float * scl, int R, int wr, float eps, const float * b, const float * inj,
+                    int HC, float rs, cudaStream_t stream) {
+    const int grid = cam_resident_grid(rms_rows_vec_kernel<CH, POST>, RMS_WARPS * 32, 0, ((long)R + RMS_WARPS - 1) / RMS_WARPS);
+    rms_rows_vec_kernel<CH, POST><<<grid, RMS_WARPS * 32, 0, stream>>>(x, w, y, ybf, scl, R, wr, eps, b, inj, HC, rs);
+    return (int)cudaGetLastError();
+}
+
 // ---- fp16 rows, staged through shared memory with cp.async ------------------------------------------------------------------
 // Each warp keeps STAGES rows (x and d, 2 N bytes each) in flight in its own slice of shared memory; a lane copies exactly
 // the 16-byte chunks it will read back, so waiting on its own copy groups is the only synchronisation. The row is read
@@ -533,4 +591,19 @@ extern "C" int cam_rms_norm_f16_static(int n, void * x, const void * d, const fl
     r = launch_f16<1>((uint16_t *)x, (const uint16_t *)d, nullptr, 0.0f, nullptr, ss, nullptr, N, N, n, (cudaStream_t)stream);
     if (r != CAM_OK) return r;
     return launch_f16<2>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, nullptr, ss, N, N, n, (cudaStream_t)stream);
+}
+
+// The vector path of pf_rms_mul / pf_hc_post_rms (csrc/hc_glue.cu): K in {2048, 2560, 5120}, 16-byte aligned buffers, enough rows to
+// fill the device. Returns CAM_ERR_SHAPE when it does not apply (the caller then uses its block-per-row kernel).
+int cam_rms_rows_vec(float * x, const float * w, float * y, void * ybf, float * scl, int R, int wr, float eps, int K, const float * b,
+                     const float * inj, int HC, float rs, void * stream) {
+    if (R < 2 * cam_sm_count() || !cam_aligned16(x) || !cam_aligned16(w) || (y && !cam_aligned16(y)) || (ybf && (reinterpret_cast<uintptr_t>(ybf) & 7u)) ||
+        (b && !cam_aligned16(b))) return CAM_ERR_SHAPE;
+    uint16_t * yb = (uint16_t *)ybf; cudaStream_t st = (cudaStream_t)stream;
+    switch (K) {
+        case 2048: return b ? launch_rows_vec<16, true>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st) : launch_rows_vec<16, false>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st);
+        case 2560: return b ? launch_rows_vec<20, true>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st) : launch_rows_vec<20, false>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st);
+        case 5120: return b ? launch_rows_vec<40, true>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st) : launch_rows_vec<40, false>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st);
+        default: return CAM_ERR_SHAPE;
+    }
 }

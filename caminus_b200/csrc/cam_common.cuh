@@ -117,3 +117,7 @@ static inline int cam_resident_grid(K kernel, int threads, size_t smem, long wan
     const long cap = (long)cam_sm_count() * per_sm;
     return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
 }
+
+// csrc/add_rms.cu: the warp-per-row path of the hyper-connection norms (CAM_ERR_SHAPE: does not apply to this call)
+int cam_rms_rows_vec(float * x, const float * w, float * y, void * ybf, float * scl, int R, int wr, float eps, int K, const float * b,
+                     const float * inj, int HC, float rs, void * stream);

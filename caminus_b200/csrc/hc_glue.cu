@@ -108,6 +108,42 @@ __global__ void __launch_bounds__(256) hc_mean_kernel(const float * __restrict__
     }
 }
 
+// the two stream kernels, four consecutive elements per thread (D a multiple of 4, 16-byte aligned buffers)
+__global__ void __launch_bounds__(256) hc_post_vec_kernel(const float * __restrict__ b, const float * __restrict__ inj, float * res, int T, int HC, int D, float rs) {
+    const int D4 = D >> 2; const long n = (long)T * D4;
+    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {
+        const int tt = (int)(i / D4), i4 = (int)(i - (long)tt * D4);
+        const float4 bv = __ldg(reinterpret_cast<const float4 *>(b) + i);
+        for (int h = 0; h < HC; h++) {
+            const float ph = fmul(cam_sigmoid(fmul(__ldg(inj + tt * HC + h), rs)), 2.0f);
+            float4 * o = reinterpret_cast<float4 *>(res + (size_t)(tt * HC + h) * D) + i4;
+            const float4 r = *o;
+            *o = make_float4(ffma(bv.x, ph, r.x), ffma(bv.y, ph, r.y), ffma(bv.z, ph, r.z), ffma(bv.w, ph, r.w));
+        }
+    }
+}
+__global__ void __launch_bounds__(256) hc_mean_vec_kernel(const float * __restrict__ x, const float * __restrict__ scl, const float * __restrict__ w,
+                                                          const float * __restrict__ g, float * __restrict__ out, int T, int HC, int D, float rs) {
+    const int D4 = D >> 2; const long n = (long)T * D4;
+    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {
+        const int tt = (int)(i / D4), i4 = (int)(i - (long)tt * D4);
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int h = 0; h < HC; h++) {
+            const size_t o = (size_t)(tt * HC + h) * D4 + i4;
+            float4 xv = __ldg(reinterpret_cast<const float4 *>(x) + o);
+            const float4 gv = __ldg(reinterpret_cast<const float4 *>(g) + o);
+            if (scl) {
+                const float sc = __ldg(scl + tt * HC + h);
+                const float4 wv = __ldg(reinterpret_cast<const float4 *>(w) + (size_t)h * D4 + i4);
+                xv = make_float4(fmul(fmul(xv.x, sc), wv.x), fmul(fmul(xv.y, sc), wv.y), fmul(fmul(xv.z, sc), wv.z), fmul(fmul(xv.w, sc), wv.w));
+            }
+            sum = make_float4(ffma(xv.x, cam_sigmoid(gv.x), sum.x), ffma(xv.y, cam_sigmoid(gv.y), sum.y), ffma(xv.z, cam_sigmoid(gv.z), sum.z),
+                              ffma(xv.w, cam_sigmoid(gv.w), sum.w));
+        }
+        __stcs(reinterpret_cast<float4 *>(out) + i, make_float4(fmul(rs, sum.x), fmul(rs, sum.y), fmul(rs, sum.z), fmul(rs, sum.w)));
+    }
+}
+
 // elementwise ops selected at compile time
 enum { EW_ADD_SUM, EW_SWIGLU, EW_RESIDUAL3, EW_CAST_BF16 };
 template <int OP>
@@ -212,6 +248,10 @@ int grid_for(long n) {
 extern "C" int pf_rms_mul(const float * x, const float * w, float * y, void * ybf, float * scl, int R, int wr, float eps, int K, void * stream) {
     if (R < 0 || wr < 1 || K < 1 || K > 256 * ROW_MAX_NI || !x || !w) return CAM_ERR_ARG;
     if (R == 0) return CAM_OK;
+    {   // in place (y == x) is safe on the vector path too: a lane reads all of its row's values before it stores any
+        const int r = cam_rms_rows_vec(const_cast<float *>(x), w, y, ybf, scl, R, wr, eps, K, nullptr, nullptr, 1, 0.0f, stream);
+        if (r != CAM_ERR_SHAPE) return r;
+    }
     rms_rows_kernel<0><<<R < cam_sm_count() * 8 ? R : cam_sm_count() * 8, 256, 0, CAM_STREAM>>>(x, w, y, (uint16_t *)ybf, scl, R, wr, eps, K, nullptr, nullptr, 1, 0.0f);
     return (int)cudaGetLastError();
 }
@@ -222,6 +262,10 @@ extern "C" int pf_hc_post_rms(const float * b, const float * inj, float * res, c
     const long R = (long)T * HC;
     if (R == 0) return CAM_OK;
     if (R > 0x7fffffffL) return CAM_ERR_SHAPE;
+    {
+        const int r = cam_rms_rows_vec(res, w, xn, xnbf, scl, (int)R, 1, eps, N, b, inj, HC, rs, stream);
+        if (r != CAM_ERR_SHAPE) return r;
+    }
     const int grid = (int)(R < (long)cam_sm_count() * 8 ? R : (long)cam_sm_count() * 8);
     rms_rows_kernel<1><<<grid, 256, 0, CAM_STREAM>>>(res, w, xn, (uint16_t *)xnbf, scl, (int)R, 1, eps, N, b, inj, HC, rs);
     return (int)cudaGetLastError();
@@ -230,13 +274,16 @@ extern "C" int pf_hc_post_rms(const float * b, const float * inj, float * res, c
 extern "C" int pf_hc_post(const float * b, const float * inj, float * res, int T, int HC, int D, float rs, void * stream) {
     if (T < 0 || HC < 1 || D < 1 || !b || !inj || !res) return CAM_ERR_ARG;
     if (T == 0) return CAM_OK;
-    hc_post_kernel<<<grid_for((long)T * D), 256, 0, CAM_STREAM>>>(b, inj, res, T, HC, D, rs);
+    if (!(D & 3) && cam_aligned16(b) && cam_aligned16(res)) hc_post_vec_kernel<<<grid_for((long)T * D / 4), 256, 0, CAM_STREAM>>>(b, inj, res, T, HC, D, rs);
+    else hc_post_kernel<<<grid_for((long)T * D), 256, 0, CAM_STREAM>>>(b, inj, res, T, HC, D, rs);
     return (int)cudaGetLastError();
 }
 extern "C" int pf_hc_mean(const float * x, const float * scl, const float * w, const float * g, float * out, int T, int HC, int D, float rs, void * stream) {
     if (T < 0 || HC < 1 || D < 1 || !x || !g || !out || (scl && !w)) return CAM_ERR_ARG;
     if (T == 0) return CAM_OK;
-    hc_mean_kernel<<<grid_for((long)T * D), 256, 0, CAM_STREAM>>>(x, scl, w, g, out, T, HC, D, rs);
+    if (!(D & 3) && cam_aligned16(x) && cam_aligned16(g) && cam_aligned16(out) && (!w || cam_aligned16(w)))
+        hc_mean_vec_kernel<<<grid_for((long)T * D / 4), 256, 0, CAM_STREAM>>>(x, scl, w, g, out, T, HC, D, rs);
+    else hc_mean_kernel<<<grid_for((long)T * D), 256, 0, CAM_STREAM>>>(x, scl, w, g, out, T, HC, D, rs);
     return (int)cudaGetLastError();
 }
 extern "C" int pf_add_sum(const float * a, const float * b, float * y, long n, void * stream) {
