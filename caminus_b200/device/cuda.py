@@ -22,7 +22,7 @@ LOADED = []    # module names this process asked for, in order (the reference's 
 
 # kernel -> (C entry, how many leading counts come from the launch grid)
 _Q3M = {'q3p_emb': ('q3p_emb', 1), 'q3p_add_rms16': ('q3p_add_rms16', 1), 'q3p_swiglu': ('q3p_swiglu', 0),
-        'q3p_qk_rope': ('q3p_qk_rope', 1)}
+        'q3p_qk_rope': ('q3p_qk_rope', 1), 'q3p_router': ('q3p_router', 1), 'q3p_topk': ('q3p_topk', 1), 'q3p_group': ('q3p_group', 0)}
 def _glue(K):
     """the hyper-connection glue object of row width K (the reference bakes K into the code object: GLUE_NI x 256)"""
     return {'pf_rms_mul': ('pf_rms_mul', 0, (K,)), 'pf_hc_post_rms': ('pf_hc_post_rms', 0, (K,)), 'pf_hc_post': ('pf_hc_post', 0),

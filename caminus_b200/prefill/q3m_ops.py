@@ -16,6 +16,14 @@ YARN_MODULE = {False: 'q3m_prefill_yarn', True: 'q3m_prefill_kvq8_yarn'}
 YARN_PAR = 2 * 128 + 2 + k3.YARN_TABLE_FLOATS      # q_norm | k_norm | theta_scale, eps | freq [64] | mscale
 
 
+MM_M = 64                    # pairs per grouped work item
+
+
+def items_bound(npairs, n_exp):
+    """the most work items q3p_group can write for npairs pairs over n_exp experts"""
+    return -(-npairs // MM_M) + n_exp
+
+
 class _On:
     """`with _On(dev):` makes dev the current device for a launch; free when it already is (the common case)"""
     __slots__ = ('dev', 'ctx')
@@ -51,6 +59,18 @@ class Ops:
         with _On(self.dev):
             self.mod.q3p_add_rms16((n,), (256,), x, NULL if d is None else d, NULL if w is None else w, I(S), nw, F(eps),
                                    NULL if h is None else h, h16, I(N))
+
+    def router(self, h, Wr, E, K, logits, n):
+        if K % 128: raise ValueError(f'q3m router: K {K} (a multiple of 128)')
+        with _On(self.dev): self.mod.q3p_router((n,), (256,), h, Wr, I(E), I(K), logits)
+
+    def topk(self, logits, E, k, floor_, ids, wts, err, n):
+        if E > 128 or k > 32: raise ValueError(f'q3m topk: E {E} (<= 128), k {k} (<= 32)')
+        with _On(self.dev): self.mod.q3p_topk((n,), (32,), logits, I(E), I(k), F(floor_), ids, wts, err)
+
+    def group(self, ids, npairs, k, E, xs, yd, items, nitems, err):
+        if E > 1024: raise ValueError(f'q3m group: E {E} (<= 1024)')
+        with _On(self.dev): self.mod.q3p_group((1,), (1024,), ids, I(npairs), I(k), I(E), xs, yd, items, nitems, err)
 
     def swiglu(self, g, u, y16, n):
         with _On(self.dev):

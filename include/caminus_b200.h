@@ -125,6 +125,16 @@ int q3p_qk_rope_q8_yarn(int n, const float * qkv, int ldq, int nh, int nkv, cons
 int cam_qk_rope_f16(int n, const void * q, const void * k, int nh, int nkv, const float * par, int pos0, void * qo, void * ko,
                     int yarn, void * stream);
 
+/* ---- the router glue of the Qwen3-MoE prefill: kernels/q3m_prefill.hip:417-513; wrappers python/caminus/prefill/q3m_ops.py:94-104 ----
+ * q3p_router: logits [n][E] = h [n][K] . Wr [E][K] in fp32 (n = grid.x; K a multiple of 128).
+ * q3p_topk: per token softmax over E <= 128 logits, the k <= 32 most probable (ties: lower index first), ids int32 [n][k], wts =
+ *   p / max(sum of the k, floor_); err |= 1 for a logit that is not finite (n = grid.x).
+ * q3p_group: the n * k (token, slot) pairs grouped by expert: xs[i] = token, yd[i] = pair, work items { int e, off, cnt, pad } of at
+ *   most 64 pairs, their count in *nitems; an id outside [0, E) sets err |= 2 and counts as expert 0. */
+int q3p_router(int n, const float * h, const float * Wr, int E, int K, float * logits, void * stream);
+int q3p_topk(int n, const float * logits, int E, int k, float floor_, int * ids, float * wts, int * err, void * stream);
+int q3p_group(const int * ids, int npairs, int k, int E, int * xs, int * yd, void * items, int * nitems, int * err, void * stream);
+
 /* ---- Q8_1 in the MMQ layout (block_q8_1_mmq, kernels/ggml_mmq/mmq.cuh:63-82): blocks [Kpad / 128][rows] of 144 bytes = 16 bytes of
  * per-32 scales + 128 int8; d_inv = 127 / amax, q = roundf(x * d_inv), d = 1 / d_inv. layout 0 = D4 (four fp32 d), 1 = DS4 (four
  * (fp16 d, fp16 sum)). x rows of stride ld, kvalid values each (a multiple of 4), zero-padded to Kpad (a multiple of 128). An

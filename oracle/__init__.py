@@ -412,3 +412,16 @@ def block_entry_fwd(x, nw, wab, eps, clip, qmax):
     ab = np.empty((M, nab), np.uint16); rstd = np.empty(M, np.float32)
     lib().orc_block_entry_fwd(_p(x), _p(nw), _p(wab), I(nab), F(eps), _p(y), _p(s), _p(codes), _p(ab), _p(rstd), I(M), I(d), F(clip), I(qmax))
     return y, s, codes, ab, rstd
+
+
+def router(h, Wr):
+    h = _f32(h); Wr = _f32(Wr); n, K = h.shape; E = Wr.shape[0]; out = np.empty((n, E), np.float32)
+    lib().orc_router(_p(h), _p(Wr), I(E), I(K), _p(out), I(n))
+    return out
+
+
+def topk(logits, k, floor_):
+    lg = _f32(logits); n, E = lg.shape
+    ids = np.empty((n, k), np.int32); wts = np.empty((n, k), np.float32); err = np.zeros(1, np.int32)
+    lib().orc_topk(_p(lg), I(E), I(k), F(floor_), _p(ids), _p(wts), _p(err), I(n))
+    return ids, wts, int(err[0])

@@ -761,3 +761,47 @@ void orc_block_entry_fwd(const float * x, const float * nw, const uint16_t * wab
         }
     }
 }
+
+/* ==== the router glue of the Qwen3-MoE prefill (kernels/q3m_prefill.hip:417-513) ===================================================== */
+/* q3p_router: logits[t][e] = h[t] . Wr[e]: lane l sums float4 dots at k0 = 4 l + 128 i (i ascending), then the wave butterfly. The
+ * reference leaves the contraction of its dot to the compiler; here a dot is w0 x0, then three fma, added to the lane's sum. */
+void orc_router(const float * h, const float * Wr, int E, int K, float * logits, int n) {
+    for (int t = 0; t < n; t++) for (int e = 0; e < E; e++) {
+        const float * x = h + (size_t)t * K, * wr = Wr + (size_t)e * K; float v[32];
+        for (int l = 0; l < 32; l++) {
+            float acc = 0.0f;
+            for (int k0 = 4 * l; k0 < K; k0 += 128) {
+                float d = wr[k0] * x[k0]; d = fmaf(wr[k0 + 1], x[k0 + 1], d); d = fmaf(wr[k0 + 2], x[k0 + 2], d); d = fmaf(wr[k0 + 3], x[k0 + 3], d);
+                acc = acc + d;
+            }
+            v[l] = acc;
+        }
+        logits[(size_t)t * E + e] = wave_sum(v);
+    }
+}
+/* q3p_topk: softmax over E <= 128 logits (lane owns logits lane + 32 j: max, exp(v - m), the lane's sum over j then the butterfly,
+ * p = v (1 / sum)), rank = #{p_j > p_i, or p_j == p_i and j < i}, the k lowest ranks in rank order, weights p / max(sum of the k in
+ * slot order, floor); err |= 1 for a logit that is not finite */
+void orc_topk(const float * logits, int E, int k, float floor_, int32_t * ids, float * wts, int32_t * err, int n) {
+    for (int t = 0; t < n; t++) {
+        const float * lg = logits + (size_t)t * E; float v[128], lane_sum[32]; float m = -INFINITY;
+        for (int e = 0; e < E; e++) { if (!isfinite(lg[e])) *err |= 1; m = fmaxf(m, lg[e]); }
+        for (int l = 0; l < 32; l++) {
+            float s = 0.0f;
+            for (int j = 0; j < 4; j++) { const int e = l + 32 * j; if (e < E) { v[e] = orc_expf(lg[e] - m); s += v[e]; } }
+            lane_sum[l] = s;
+        }
+        const float inv = 1.0f / wave_sum(lane_sum);
+        for (int e = 0; e < E; e++) v[e] = v[e] * inv;
+        int sel[64];
+        for (int i = 0; i < E; i++) {
+            int rk = 0;
+            for (int j = 0; j < E; j++) rk += (v[j] > v[i]) || (v[j] == v[i] && j < i);
+            if (rk < k) sel[rk] = i;
+        }
+        float ws = 0.0f;
+        for (int j = 0; j < k; j++) ws = ws + v[sel[j]];
+        ws = fmaxf(ws, floor_);
+        for (int j = 0; j < k; j++) { ids[(size_t)t * k + j] = sel[j]; wts[(size_t)t * k + j] = v[sel[j]] / ws; }
+    }
+}

@@ -174,3 +174,35 @@ def test_actq_family(M, K):
             yo, so, co, abo, ro = oracle.block_entry_fwd(x, nw, None if w_ is None else bits(w_).reshape(6, K), 1e-6, 1.0, 7)
             assert same(y, yo) and same(s, so) and same(rstd, ro) and np.array_equal(c.cpu().numpy().view(np.uint16).reshape(-1), co.reshape(-1))
             if w_ is not None: assert same(ab, abo)
+
+
+def test_router_topk_group():
+    """the router glue: logits, ids and weights are the oracle's bytes; the grouping puts every pair once under its expert
+    (tests/prefill/test_q3m_ops.py:118-129, 165-182)"""
+    from caminus_b200.prefill import q3m_ops
+    O = q3m_ops.Ops(DEV); g = np.random.default_rng(21); n, D, E, k = 150, 2048, 128, 8
+    hh = g.standard_normal((n, D)).astype(np.float32); Wr = (g.standard_normal((E, D)) * 0.05).astype(np.float32)
+    lg = torch.zeros(n, E, device=DEV)
+    O.router(cu(hh), cu(Wr), E, D, lg, n)
+    lo = oracle.router(hh, Wr)
+    assert same(lg, lo)
+    lo[3, 7] = lo[3, 9] = lo[3].max() + 1.0
+    ids = torch.zeros(n * k, dtype=torch.int32, device=DEV); wts = torch.zeros(n * k, device=DEV); err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    O.topk(cu(lo), E, k, 6.103515625e-5, ids, wts, err, n)
+    io, wo, eo = oracle.topk(lo, k, 6.103515625e-5)
+    assert int(err.item()) == 0 == eo and np.array_equal(ids.cpu().numpy().reshape(n, k), io) and same(wts, wo)
+    lo[5, 2] = np.nan; err.zero_()
+    O.topk(cu(lo), E, k, 6.103515625e-5, ids, wts, err, n)
+    assert int(err.item()) & 1
+    use = g.choice(E, 12, replace=False)
+    ids_np = np.stack([g.choice(use, k, replace=False) for _ in range(n)]).astype(np.int32)
+    bound = q3m_ops.items_bound(n * k, E)
+    xs, yd = (torch.zeros(n * k, dtype=torch.int32, device=DEV) for _ in range(2))
+    items = torch.zeros(bound, 4, dtype=torch.int32, device=DEV); nitems = torch.zeros(1, dtype=torch.int32, device=DEV); err.zero_()
+    O.group(cu(ids_np.reshape(-1)), n * k, k, E, xs, yd, items, nitems, err)
+    it = items[:int(nitems.item())].cpu().numpy(); cnt = np.bincount(ids_np.reshape(-1), minlength=E); ydn = yd.cpu().numpy()
+    assert int(err.item()) == 0 and int(nitems.item()) == sum(-(-c // 64) for c in cnt) and sorted(ydn.tolist()) == list(range(n * k))
+    assert all(ids_np.reshape(-1)[ydn[i0:i0 + c]].tolist() == [e] * c for e, i0, c, _ in it) and np.array_equal(xs.cpu().numpy(), ydn // k)
+    bad = ids_np.reshape(-1).copy(); bad[10] = E + 5; err.zero_()
+    O.group(cu(bad), n * k, k, E, xs, yd, items, nitems, err)
+    assert int(err.item()) & 2

@@ -134,3 +134,23 @@ def test_actq_family_against_float64():
     ab64 = torch.from_numpy(h64).bfloat16().double().numpy() @ wab.double().numpy().T
     assert np.abs(bf(ab).float().numpy() - ab64).max() <= 2.0 ** -7 * np.abs(ab64).max() + 1e-6
     assert np.array_equal(oracle.rmsnorm_f32(x.numpy(), nw, 1e-6), (x.numpy() * rstd[:, None]) * nw)        # the two norms agree
+
+
+def test_router_glue_as_the_reference_tests_it():
+    """tests/prefill/test_q3m_ops.py:165-182: logits vs float64 < 1e-5; ids = the ranking of the float32 softmax (a forced tie: the
+    lower index first), weights within 1e-6; a NaN logit sets the flag"""
+    g = np.random.default_rng(17); n, D, E = 37, 2048, 128
+    hh = g.standard_normal((n, D)).astype(np.float32); Wr = (g.standard_normal((E, D)) * 0.05).astype(np.float32)
+    lg = oracle.router(hh, Wr)
+    ref = hh.astype(np.float64) @ Wr.astype(np.float64).T
+    assert np.abs(lg - ref).max() / np.sqrt((ref ** 2).mean()) < 1e-5
+    lg[3, 7] = lg[3, 9] = lg[3].max() + 1.0
+    ids, wts, err = oracle.topk(lg, 8, 6.103515625e-5)
+    p32 = np.exp(lg - lg.max(-1, keepdims=True)); p32 = p32 / p32.sum(-1, keepdims=True)
+    rid = np.stack([sorted(range(E), key=lambda e: (-p32[t, e], e))[:8] for t in range(n)])
+    rw = np.take_along_axis(p32, rid, 1); rw = rw / rw.sum(-1, keepdims=True)
+    assert err == 0 and ids[3, 0] == 7 and ids[3, 1] == 9
+    near = np.abs(np.diff(np.sort(p32, -1)[:, ::-1][:, :9], axis=-1)).min(-1) < 1e-6 * p32.max(-1)     # rows where two of the top 9 nearly tie
+    assert np.array_equal(ids[~near], rid[~near]) and np.abs(wts - rw)[~near].max() < 1e-6
+    lg[5, 2] = np.nan
+    assert oracle.topk(lg, 8, 6.103515625e-5)[2] & 1
