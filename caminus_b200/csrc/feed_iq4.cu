@@ -1,0 +1,70 @@
+// The IQ4 row gathers of the prefill's host feed (the reference's embd_rows_iq4xs and ple_rows_iq4nl, kernels/prefill_feed.hip:24-54;
+// siblings of the Q4_K embedding gather): bitwise the host decoders (python/caminus/own_dequant.py iq4_xs; gguf-py).
+// y = (d * (ls - 32)) * kvalue (IQ4_XS) / d * kvalue (IQ4_NL): lone products, rounded one by one. The 16 kvalues are ggml's IQ4_NL
+// codebook, part of the format's definition. An index outside its table is clamped before the read and reported in *err.
+// Mapping: a thread per four consecutive outputs (one 16-byte store); their nibbles are four consecutive bytes of the block.
+#include "cam_common.cuh"
+
+namespace {
+
+__constant__ float kIQ4NL[16] = {-127.f, -104.f, -83.f, -65.f, -49.f, -35.f, -22.f, -10.f, 1.f, 13.f, 25.f, 38.f, 53.f, 69.f, 89.f, 113.f};
+
+CAM_DEV float f16_at(const uint8_t * p) { return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8)))); }
+
+__global__ void __launch_bounds__(256) embd_rows_iq4xs_kernel(const uint8_t * __restrict__ table, const int * __restrict__ tok, int nvocab, int n, int nblk,
+                                                              float * __restrict__ out, int * err) {
+    const int D4 = nblk * 64; const long total = (long)n * D4;
+    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long)gridDim.x * 256) {
+        const int p = (int)(i / D4), k = (int)(i - (long)p * D4) * 4, bl = k >> 8, w = k & 255, ib = w >> 5, j = w & 31;
+        int t = __ldg(tok + p);
+        if (t < 0 || t >= nvocab) { atomicOr(err, 2); t = t < 0 ? 0 : nvocab - 1; }
+        const uint8_t * b = table + (size_t)t * (size_t)(nblk * 136) + (size_t)bl * 136;
+        const int sh = b[2] | (b[3] << 8), sl = b[4 + (ib >> 1)];
+        const int ls = ((sl >> ((ib & 1) * 4)) & 15) | (((sh >> (2 * ib)) & 3) << 4);
+        const float dl = fmul(f16_at(b), (float)(ls - 32));
+        const uint8_t * qp = b + 8 + 16 * ib + (j & 15);
+        const int hi = j < 16 ? 0 : 4;
+        float4 y;
+        y.x = fmul(dl, kIQ4NL[(qp[0] >> hi) & 15]); y.y = fmul(dl, kIQ4NL[(qp[1] >> hi) & 15]);
+        y.z = fmul(dl, kIQ4NL[(qp[2] >> hi) & 15]); y.w = fmul(dl, kIQ4NL[(qp[3] >> hi) & 15]);
+        __stcs(reinterpret_cast<float4 *>(out) + i, y);
+    }
+}
+
+__global__ void __launch_bounds__(256) ple_rows_iq4nl_kernel(const uint8_t * __restrict__ raw, const int * __restrict__ inv, int nuniq, int nrows, int bpr,
+                                                             float * __restrict__ out, int * err) {
+    const int hd4 = bpr * 8; const long total = (long)nrows * hd4;
+    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long)gridDim.x * 256) {
+        const int r = (int)(i / hd4), k = (int)(i - (long)r * hd4) * 4, b = k >> 5, j = k & 31;
+        int u = __ldg(inv + r);
+        if (u < 0 || u >= nuniq) { atomicOr(err, 1); u = u < 0 ? 0 : nuniq - 1; }
+        const uint8_t * blk = raw + (size_t)u * (size_t)(bpr * 18) + (size_t)b * 18;
+        const float d = f16_at(blk);
+        const uint8_t * qp = blk + 2 + (j & 15);
+        const int hi = j < 16 ? 0 : 4;
+        float4 y;
+        y.x = fmul(d, kIQ4NL[(qp[0] >> hi) & 15]); y.y = fmul(d, kIQ4NL[(qp[1] >> hi) & 15]);
+        y.z = fmul(d, kIQ4NL[(qp[2] >> hi) & 15]); y.w = fmul(d, kIQ4NL[(qp[3] >> hi) & 15]);
+        __stcs(reinterpret_cast<float4 *>(out) + i, y);
+    }
+}
+
+}   // namespace
+
+// embd_rows_iq4xs / ple_rows_iq4nl: kernels/prefill_feed.hip:40-41, 24-25 (one thread per output float there)
+extern "C" int embd_rows_iq4xs(const void * table, const int * tok, int nvocab, int n, int nblk, float * out, int * err, void * stream) {
+    if (n < 0 || nvocab < 1 || nblk < 1 || !table || !tok || !out || !err) return CAM_ERR_ARG;
+    if (!cam_aligned16(out)) return CAM_ERR_ALIGN;
+    if (n == 0) return CAM_OK;
+    const long want = ((long)n * nblk * 64 + 255) / 256;
+    embd_rows_iq4xs_kernel<<<cam_resident_grid(embd_rows_iq4xs_kernel, 256, 0, want), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)table, tok, nvocab, n, nblk, out, err);
+    return (int)cudaGetLastError();
+}
+extern "C" int ple_rows_iq4nl(const void * raw, const int * inv, int nuniq, int nrows, int bpr, float * out, int * err, void * stream) {
+    if (nrows < 0 || nuniq < 1 || bpr < 1 || !raw || !inv || !out || !err) return CAM_ERR_ARG;
+    if (!cam_aligned16(out)) return CAM_ERR_ALIGN;
+    if (nrows == 0) return CAM_OK;
+    const long want = ((long)nrows * bpr * 8 + 255) / 256;
+    ple_rows_iq4nl_kernel<<<cam_resident_grid(ple_rows_iq4nl_kernel, 256, 0, want), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)raw, inv, nuniq, nrows, bpr, out, err);
+    return (int)cudaGetLastError();
+}

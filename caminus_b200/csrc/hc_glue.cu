@@ -42,7 +42,8 @@ CAM_DEV float block_total(float ss, float * part) {
 template <int MODE>
 __global__ void __launch_bounds__(256) rms_rows_kernel(const float * x, const float * __restrict__ w, float * y,
                                                        uint16_t * __restrict__ ybf, float * __restrict__ scl, int R, int wr, float eps, int K,
-                                                       const float * __restrict__ b, const float * __restrict__ inj, int HC, float rs) {
+                                                       const float * __restrict__ b, const float * __restrict__ inj, int HC, float rs,
+                                                       uint8_t * __restrict__ yq) {
     __shared__ float part[8];
     const int tid = threadIdx.x;
     for (int t = blockIdx.x; t < R; t += gridDim.x) {
@@ -75,6 +76,16 @@ __global__ void __launch_bounds__(256) rms_rows_kernel(const float * x, const fl
                 const float v = fmul(fmul(xv[j], scale), __ldg(wv + tid + 256 * j));
                 if (y) y[(size_t)t * K + tid + 256 * j] = v;
                 if (ybf) ybf[(size_t)t * K + tid + 256 * j] = bf16_rne(v);
+                if (yq) {      // the Q8_1 copy (q8_emit: the warp's 32 consecutive values are one block; K a multiple of 32 keeps a warp whole)
+                    float amax = fabsf(v), sum = v;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) { amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, o)); sum = fadd(sum, __shfl_xor_sync(CAM_FULL, sum, o)); }
+                    const float d = fdiv(amax, 127.0f);
+                    const float qv = fdiv(v, d);
+                    uint8_t * blk = yq + ((size_t)t * K + tid + 256 * j) / 32 * 36;
+                    blk[4 + (tid & 31)] = (uint8_t)((amax != 0.0f && fabsf(qv) < 127.5f) ? __float2int_rn(roundf(qv)) : 0);
+                    if ((tid & 31) == 0) *reinterpret_cast<uint32_t *>(blk) = f2_to_h2(d, sum);
+                }
             }
         __syncthreads();      // part[] is reused by the next row
     }
@@ -252,7 +263,17 @@ extern "C" int pf_rms_mul(const float * x, const float * w, float * y, void * yb
         const int r = cam_rms_rows_vec(const_cast<float *>(x), w, y, ybf, scl, R, wr, eps, K, nullptr, nullptr, 1, 0.0f, stream);
         if (r != CAM_ERR_SHAPE) return r;
     }
-    rms_rows_kernel<0><<<R < cam_sm_count() * 8 ? R : cam_sm_count() * 8, 256, 0, CAM_STREAM>>>(x, w, y, (uint16_t *)ybf, scl, R, wr, eps, K, nullptr, nullptr, 1, 0.0f);
+    rms_rows_kernel<0><<<R < cam_sm_count() * 8 ? R : cam_sm_count() * 8, 256, 0, CAM_STREAM>>>(x, w, y, (uint16_t *)ybf, scl, R, wr, eps, K, nullptr, nullptr, 1, 0.0f, nullptr);
+    return (int)cudaGetLastError();
+}
+// cam_rms_mul_q8_1: pf_rms_mul's norm with the Q8_1 copy of the normed rows the decode op emits for the quantised matvec that follows
+// (op_rms_mul with Seg.asum: q8_emit_n, kernels/k3_gguf_ops.h:178-196, 1253): yq = R * K / 32 blocks of 36 bytes, the bytes
+// gg_quantize_q8_1 gives for y (quantize_q8_1_lane: lane butterfly sums); y fp32 optional. K a multiple of 32.
+extern "C" int cam_rms_mul_q8_1(const float * x, const float * w, float * y, void * yq, int R, int wr, float eps, int K, void * stream) {
+    if (R < 0 || wr < 1 || K < 32 || (K & 31) || K > 256 * ROW_MAX_NI || !x || !w || !yq) return CAM_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(yq) & 3u) return CAM_ERR_ALIGN;
+    if (R == 0) return CAM_OK;
+    rms_rows_kernel<0><<<R < cam_sm_count() * 8 ? R : cam_sm_count() * 8, 256, 0, CAM_STREAM>>>(x, w, y, nullptr, nullptr, R, wr, eps, K, nullptr, nullptr, 1, 0.0f, (uint8_t *)yq);
     return (int)cudaGetLastError();
 }
 // pf_hc_post_rms: kernels/prefill_glue.hip:130-131; wrapper python/caminus/prefill/glue.py:155-164. N = the row length (as K above).
@@ -267,7 +288,7 @@ extern "C" int pf_hc_post_rms(const float * b, const float * inj, float * res, c
         if (r != CAM_ERR_SHAPE) return r;
     }
     const int grid = (int)(R < (long)cam_sm_count() * 8 ? R : (long)cam_sm_count() * 8);
-    rms_rows_kernel<1><<<grid, 256, 0, CAM_STREAM>>>(res, w, xn, (uint16_t *)xnbf, scl, (int)R, 1, eps, N, b, inj, HC, rs);
+    rms_rows_kernel<1><<<grid, 256, 0, CAM_STREAM>>>(res, w, xn, (uint16_t *)xnbf, scl, (int)R, 1, eps, N, b, inj, HC, rs, nullptr);
     return (int)cudaGetLastError();
 }
 // pf_hc_post / pf_hc_mean / pf_add_sum: kernels/prefill_glue.hip:175-176, 194-195, 417
@@ -332,7 +353,7 @@ extern "C" int embedding_f32(int T, const int * tok, const float * emb, float * 
 extern "C" int rmsnorm_f32(int rows, const float * x, const float * w, float * out, int D, float eps, void * stream) {
     if (rows < 0 || D < 1 || D > 256 * ROW_MAX_NI || !x || !w || !out) return CAM_ERR_ARG;
     if (rows == 0) return CAM_OK;
-    rms_rows_kernel<2><<<rows < cam_sm_count() * 8 ? rows : cam_sm_count() * 8, 256, 0, CAM_STREAM>>>(x, w, out, nullptr, nullptr, rows, 1, eps, D, nullptr, nullptr, 1, 0.0f);
+    rms_rows_kernel<2><<<rows < cam_sm_count() * 8 ? rows : cam_sm_count() * 8, 256, 0, CAM_STREAM>>>(x, w, out, nullptr, nullptr, rows, 1, eps, D, nullptr, nullptr, 1, 0.0f, nullptr);
     return (int)cudaGetLastError();
 }
 extern "C" int silu_mul_bf16(const void * gu, void * act, int H, long n, void * stream) {

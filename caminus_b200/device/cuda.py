@@ -36,6 +36,7 @@ MODULES = {
     'core': {'embedding_f32': ('embedding_f32', 1), 'rmsnorm_f32': ('rmsnorm_f32', 1), 'silu_mul_bf16': ('silu_mul_bf16', 0),
              'residual3': ('residual3', 0), 'cast_bf16': ('cast_bf16', 0)},
     'fuse': {'residual_slices_fwd': ('residual_slices_fwd', 0)},
+    'prefill_feed': {'embd_rows_iq4xs': ('embd_rows_iq4xs', 0), 'ple_rows_iq4nl': ('ple_rows_iq4nl', 0)},
     'actq': {k: (k, 1) for k in ('actq_fwd_bf16', 'actq_fwd_f32', 'actq_fwd_codes_bf16', 'actq_fwd_codes_f32', 'silu_mul_actq_fwd', 'block_entry_fwd')},
     'q3m_prefill': _Q3M,
     'q3m_prefill_yarn': dict(_Q3M, q3p_qk_rope=('q3p_qk_rope_yarn', 1)),

@@ -43,10 +43,13 @@ SIGNATURES = {
     'actq_fwd_codes_f32': [I, P, P, P, P, I, F, I, P],
     'silu_mul_actq_fwd': [I, P, I, I, P, P, P, F, I, P],
     'block_entry_fwd': [I, P, P, P, I, F, P, P, P, P, P, I, F, I, P],
+    'embd_rows_iq4xs': [P, P, I, I, I, P, P, P],
+    'ple_rows_iq4nl': [P, P, I, I, I, P, P, P],
     'q3p_router': [I, P, P, I, I, P, P],
     'q3p_topk': [I, P, I, I, F, P, P, P, P],
     'q3p_group': [P, I, I, I, P, P, P, P, P, P],
     'pf_rms_mul': [P, P, P, P, P, I, I, F, I, P],
+    'cam_rms_mul_q8_1': [P, P, P, P, I, I, F, I, P],
     'pf_hc_post_rms': [P, P, P, P, P, P, P, I, I, F, F, I, P],
     'pf_hc_post': [P, P, P, I, I, I, F, P],
     'pf_hc_mean': [P, P, P, P, P, I, I, I, F, P],

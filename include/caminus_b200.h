@@ -125,6 +125,13 @@ int q3p_qk_rope_q8_yarn(int n, const float * qkv, int ldq, int nh, int nkv, cons
 int cam_qk_rope_f16(int n, const void * q, const void * k, int nh, int nkv, const float * par, int pos0, void * qo, void * ko,
                     int yarn, void * stream);
 
+/* ---- the IQ4 row gathers of the host feed: kernels/prefill_feed.hip:24-54 (module prefill_feed). out fp32, bitwise the host decoders.
+ * embd_rows_iq4xs: out [n][nblk * 256] = rows tok[p] of an IQ4_XS table (nblk * 136 bytes per row); a token outside [0, nvocab) is
+ *   clamped and sets err |= 2. ple_rows_iq4nl: out [nrows][bpr * 32] = rows inv[r] of an IQ4_NL table (bpr * 18 bytes per row); an
+ *   index outside [0, nuniq) is clamped and sets err |= 1. ---- */
+int embd_rows_iq4xs(const void * table, const int * tok, int nvocab, int n, int nblk, float * out, int * err, void * stream);
+int ple_rows_iq4nl(const void * raw, const int * inv, int nuniq, int nrows, int bpr, float * out, int * err, void * stream);
+
 /* ---- the router glue of the Qwen3-MoE prefill: kernels/q3m_prefill.hip:417-513; wrappers python/caminus/prefill/q3m_ops.py:94-104 ----
  * q3p_router: logits [n][E] = h [n][K] . Wr [E][K] in fp32 (n = grid.x; K a multiple of 128).
  * q3p_topk: per token softmax over E <= 128 logits, the k <= 32 most probable (ties: lower index first), ids int32 [n][k], wts =
@@ -153,6 +160,9 @@ int cam_swiglu_mmq_q8_1_f16(const void * g, const void * u, void * y, int kvalid
 /* y[r] = (x[r] * rsqrt(mean(x[r]^2) + eps)) * w[r % wr]; outputs optional: y fp32 (may be x), ybf its bf16 copy (round to
  * nearest even), scl [R] the row scale. Replaces pf_rms_mul, kernels/prefill_glue.hip:94-95 (= op_rms_mul, k3_gguf_ops.h:1230-1268). */
 int pf_rms_mul(const float * x, const float * w, float * y, void * ybf, float * scl, int R, int wr, float eps, int K, void * stream);
+/* pf_rms_mul's norm that also emits the Q8_1 copy of the normed rows (36-byte blocks, the bytes gg_quantize_q8_1 gives for y) for the
+ * quantised matvec that follows: the decode op's op_rms_mul with its q8_emit_n, kernels/k3_gguf_ops.h:178-196, 1253. y optional. */
+int cam_rms_mul_q8_1(const float * x, const float * w, float * y, void * yq, int R, int wr, float eps, int K, void * stream);
 /* res[t, h] = b[t] * 2 sigmoid(inj[t, h] * rs) + res[t, h] in place, then that row's norm with w[h]: xn fp32, xnbf bf16, scl,
  * each optional. Replaces pf_hc_post_rms, kernels/prefill_glue.hip:130-131. */
 int pf_hc_post_rms(const float * b, const float * inj, float * res, const float * w, float * xn, void * xnbf, float * scl, int T, int HC,

@@ -425,3 +425,15 @@ def topk(logits, k, floor_):
     ids = np.empty((n, k), np.int32); wts = np.empty((n, k), np.float32); err = np.zeros(1, np.int32)
     lib().orc_topk(_p(lg), I(E), I(k), F(floor_), _p(ids), _p(wts), _p(err), I(n))
     return ids, wts, int(err[0])
+
+
+def embd_rows_iq4xs(table, tok, nvocab, nblk):
+    table = _c(table, np.uint8).reshape(-1); tok = _c(tok, np.int32); out = np.empty((tok.size, nblk * 256), np.float32); err = np.zeros(1, np.int32)
+    lib().orc_embd_rows_iq4xs(_p(table), _p(tok), I(nvocab), I(tok.size), I(nblk), _p(out), _p(err))
+    return out, int(err[0])
+
+
+def ple_rows_iq4nl(raw, inv, nuniq, bpr):
+    raw = _c(raw, np.uint8).reshape(-1); inv = _c(inv, np.int32); out = np.empty((inv.size, bpr * 32), np.float32); err = np.zeros(1, np.int32)
+    lib().orc_ple_rows_iq4nl(_p(raw), _p(inv), I(nuniq), I(inv.size), I(bpr), _p(out), _p(err))
+    return out, int(err[0])

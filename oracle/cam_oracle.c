@@ -805,3 +805,35 @@ void orc_topk(const float * logits, int E, int k, float floor_, int32_t * ids, f
         for (int j = 0; j < k; j++) { ids[(size_t)t * k + j] = sel[j]; wts[(size_t)t * k + j] = v[sel[j]] / ws; }
     }
 }
+
+/* ==== the IQ4 row gathers of the host feed (kernels/prefill_feed.hip:24-54; host decoders python/caminus/own_dequant.py iq4_xs) ====
+ * The 16 values of a 4-bit index are ggml's IQ4_NL codebook (part of the format's definition). IQ4_NL block: f16 d, 16 bytes of
+ * nibbles (low nibble = value j, high = value j + 16), y = d * kvalue. IQ4_XS block (136 bytes, 256 values): f16 d, u16 scales_h,
+ * u8 scales_l[4], qs[128]; sub-block ib's scale ls = (scales_l[ib / 2] >> 4 (ib & 1)) & 15 | ((scales_h >> 2 ib) & 3) << 4,
+ * y = (d * (ls - 32)) * kvalue. An index outside its table is clamped and reported in err (bit 0 / bit 1). */
+static const float kIQ4NL[16] = {-127.f, -104.f, -83.f, -65.f, -49.f, -35.f, -22.f, -10.f, 1.f, 13.f, 25.f, 38.f, 53.f, 69.f, 89.f, 113.f};
+void orc_ple_rows_iq4nl(const uint8_t * raw, const int32_t * inv, int nuniq, int nrows, int bpr, float * out, int32_t * err) {
+    const int hd = bpr * 32;
+    for (long i = 0; i < (long)nrows * hd; i++) {
+        const int r = (int)(i / hd), k = (int)(i % hd), b = k >> 5, j = k & 31;
+        int u = inv[r];
+        if (u < 0 || u >= nuniq) { *err |= 1; u = u < 0 ? 0 : nuniq - 1; }
+        const uint8_t * blk = raw + (size_t)u * (size_t)(bpr * 18) + (size_t)b * 18;
+        const uint8_t q = blk[2 + (j & 15)];
+        out[i] = h2f((uint16_t)(blk[0] | (blk[1] << 8))) * kIQ4NL[j < 16 ? (q & 15) : (q >> 4)];
+    }
+}
+void orc_embd_rows_iq4xs(const uint8_t * table, const int32_t * tok, int nvocab, int n, int nblk, float * out, int32_t * err) {
+    const int D = nblk * 256;
+    for (long i = 0; i < (long)n * D; i++) {
+        const int p = (int)(i / D), k = (int)(i % D), bl = k >> 8, w = k & 255, ib = w >> 5, j = w & 31;
+        int t = tok[p];
+        if (t < 0 || t >= nvocab) { *err |= 2; t = t < 0 ? 0 : nvocab - 1; }
+        const uint8_t * b = table + (size_t)t * (size_t)(nblk * 136) + (size_t)bl * 136;
+        const int sh = b[2] | (b[3] << 8), sl = b[4 + (ib >> 1)];
+        const int ls = ((sl >> ((ib & 1) * 4)) & 15) | (((sh >> (2 * ib)) & 3) << 4);
+        const float dl = h2f((uint16_t)(b[0] | (b[1] << 8))) * (float)(ls - 32);
+        const uint8_t q = b[8 + 16 * ib + (j & 15)];
+        out[i] = dl * kIQ4NL[j < 16 ? (q & 15) : (q >> 4)];
+    }
+}

@@ -148,7 +148,21 @@ def make_q8_kv():
     np.savez_compressed(os.path.join(OUT, 'q8_kv.npz'), K=K, V=V, H=H, raw=raw)
 
 
+def make_iq4():
+    """IQ4_XS and IQ4_NL rows: own_dequant's decoders (bitwise gguf-py upstream, tests/io/test_own_dequant.py), small finite scales"""
+    g = np.random.default_rng(20261110); vocab, nblk = 23, 2
+    T = g.integers(0, 256, (vocab, nblk, 136), dtype=np.uint8)
+    T[:, :, 0:2] = (g.standard_normal((vocab, nblk, 1)) * 1e-2).astype(np.float16).view(np.uint8).reshape(vocab, nblk, 2)
+    xs = np.stack([own_dequant.iq4_xs(T[t].reshape(-1)) for t in range(vocab)]).astype(np.float32)
+    assert np.array_equal(xs.view(np.uint32), np.stack([gq.dequantize(T[t].reshape(1, -1), QT.IQ4_XS).reshape(-1) for t in range(vocab)]).astype(np.float32).view(np.uint32))
+    nuniq, bpr = 11, 5
+    R = g.integers(0, 256, (nuniq, bpr, 18), dtype=np.uint8)
+    R[:, :, 0:2] = (g.standard_normal((nuniq, bpr, 1)) * 1e-2).astype(np.float16).view(np.uint8).reshape(nuniq, bpr, 2)
+    nl = np.stack([gq.dequantize(R[u].reshape(1, -1), QT.IQ4_NL).reshape(-1) for u in range(nuniq)]).astype(np.float32)
+    np.savez_compressed(os.path.join(OUT, 'iq4_rows.npz'), T=T, xs=xs, R=R, nl=nl)
+
+
 if __name__ == '__main__':
-    make_q4k(); make_q8(); make_swiglu(); make_rms(); make_rope(); make_q8_kv()
+    make_iq4(); make_q4k(); make_q8(); make_swiglu(); make_rms(); make_rope(); make_q8_kv()
     for f in sorted(os.listdir(OUT)):
         if f.endswith('.npz'): print(f, os.path.getsize(os.path.join(OUT, f)), 'bytes')

@@ -206,3 +206,29 @@ def test_router_topk_group():
     bad = ids_np.reshape(-1).copy(); bad[10] = E + 5; err.zero_()
     O.group(cu(bad), n * k, k, E, xs, yd, items, nitems, err)
     assert int(err.item()) & 2
+
+
+def test_iq4_row_gathers(golden):
+    f = golden('iq4_rows'); T, R = f['T'], f['R']; vocab, nblk = T.shape[:2]; nuniq, bpr = R.shape[:2]
+    m = hip.Module('prefill_feed'); g = np.random.default_rng(1)
+    tok = np.concatenate([[0, 22, 99, -1], g.integers(0, vocab, 300)]).astype(np.int32)
+    out = torch.zeros(len(tok), nblk * 256, device=DEV); err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    m.embd_rows_iq4xs((1,), (256,), cu(T.reshape(-1)), cu(tok), I(vocab), I(len(tok)), I(nblk), out, err)
+    oo, eo = oracle.embd_rows_iq4xs(T, tok, vocab, nblk)
+    assert same(out, oo) and int(err.item()) == eo == 2 and same(out, f['xs'][np.clip(tok, 0, vocab - 1)])
+    inv = np.concatenate([[3, 11, -2], g.integers(0, nuniq, 200)]).astype(np.int32)
+    out = torch.zeros(len(inv), bpr * 32, device=DEV); err.zero_()
+    m.ple_rows_iq4nl((1,), (256,), cu(R.reshape(-1)), cu(inv), I(nuniq), I(len(inv)), I(bpr), out, err)
+    oo, eo = oracle.ple_rows_iq4nl(R, inv, nuniq, bpr)
+    assert same(out, oo) and int(err.item()) == eo == 1 and same(out, f['nl'][np.clip(inv, 0, nuniq - 1)])
+
+
+@pytest.mark.parametrize('R,K,wr', [(5, 2560, 1), (300, 2048, 4), (7, 320, 1)])
+def test_rms_mul_q8_1_copy(R, K, wr):
+    """the norm that also emits the Q8_1 copy: the bytes of the plain quantiser run on the normed rows (fused == unfused)"""
+    from caminus_b200 import lib
+    g = np.random.default_rng(R + K); x = acts(g, (R, K), 3.0); w = (g.random((wr, K)) + 0.5).astype(np.float32)
+    y = torch.zeros(R, K, device=DEV); yq = torch.zeros(R * K // 32 * 36, dtype=torch.uint8, device=DEV)
+    lib.check(lib.load().cam_rms_mul_q8_1(cu(x).data_ptr(), cu(w).data_ptr(), y.data_ptr(), yq.data_ptr(), R, wr, 1e-6, K, torch.cuda.current_stream().cuda_stream))
+    yo, _, _ = oracle.pf_rms_mul(x, w, 1e-6, K)
+    assert same(y, yo) and same(yq, oracle.q8_1(yo.reshape(-1), sum_order=0))

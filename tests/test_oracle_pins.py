@@ -173,3 +173,14 @@ def test_q8_kv_rows_bitwise(golden):
     bad = qkv.copy(); bad[1, nh * 128 + 3] = np.inf
     _, _, err = oracle.qk_rope_q8(bad, ldq, nh, nkv, par, pos0, np.zeros((pos0 + n) * 2 * (M // 32) * 34, np.uint8), n)
     assert err == 2                                                    # a refused block sets the prefill's error word
+
+
+def test_iq4_rows_bitwise(golden):
+    """IQ4_XS / IQ4_NL row gathers: the reference's host decoders (own_dequant.iq4_xs, gguf-py), bit for bit; clamped ids reported"""
+    f = golden('iq4_rows'); T, R = f['T'], f['R']; vocab, nblk = T.shape[:2]; nuniq, bpr = R.shape[:2]
+    tok = np.array([0, 22, 5, 99, -1, 7], np.int32)
+    out, err = oracle.embd_rows_iq4xs(T, tok, vocab, nblk)
+    assert err == 2 and np.array_equal(out.view(np.uint32), f['xs'][np.clip(tok, 0, vocab - 1)].view(np.uint32))
+    inv = np.array([3, 0, 10, 11, -2, 4], np.int32)
+    out, err = oracle.ple_rows_iq4nl(R, inv, nuniq, bpr)
+    assert err == 1 and np.array_equal(out.view(np.uint32), f['nl'][np.clip(inv, 0, nuniq - 1)].view(np.uint32))
