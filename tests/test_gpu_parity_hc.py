@@ -229,6 +229,7 @@ def test_rms_mul_q8_1_copy(R, K, wr):
     from caminus_b200 import lib
     g = np.random.default_rng(R + K); x = acts(g, (R, K), 3.0); w = (g.random((wr, K)) + 0.5).astype(np.float32)
     y = torch.zeros(R, K, device=DEV); yq = torch.zeros(R * K // 32 * 36, dtype=torch.uint8, device=DEV)
-    lib.check(lib.load().cam_rms_mul_q8_1(cu(x).data_ptr(), cu(w).data_ptr(), y.data_ptr(), yq.data_ptr(), R, wr, 1e-6, K, torch.cuda.current_stream().cuda_stream))
+    xd, wd = cu(x), cu(w)      # (kept alive until the launch has run)
+    lib.check(lib.load().cam_rms_mul_q8_1(xd.data_ptr(), wd.data_ptr(), y.data_ptr(), yq.data_ptr(), R, wr, 1e-6, K, torch.cuda.current_stream().cuda_stream))
     yo, _, _ = oracle.pf_rms_mul(x, w, 1e-6, K)
     assert same(y, yo) and same(yq, oracle.q8_1(yo.reshape(-1), sum_order=0))
