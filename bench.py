@@ -145,7 +145,7 @@ def run_reference(args, rank):
         'gpu_launches': 0}), flush=True)
 
 
-def single_op_lines(torch, dev, peak):
+def single_op_lines(torch, dev, peak, only=()):
     """device-resident GB/s of the single-op configs 1-4 (median of 20 event-timed launches; buffers rotated where a
     config's data would fit in L2)"""
     from caminus_b200 import glue, synth
@@ -157,15 +157,17 @@ def single_op_lines(torch, dev, peak):
     def timed(fn, reps=9, rot=1, inner=10):
         """per-launch seconds: `inner` launches back to back between two events (the queue never runs dry, as inside a model's
         layer loop), median and minimum over `reps` such batches"""
-        for i in range(3): fn(i % rot)
-        torch.cuda.synchronize(dev)
-        ts = []
-        for r in range(reps):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            for i in range(inner): fn((r * inner + i) % rot)
-            b.record(); b.synchronize(); ts.append(a.elapsed_time(b) * 1e-3 / inner)
-        return float(np.median(ts)), float(np.min(ts))
+        def run():
+            for i in range(3): fn(i % rot)
+            torch.cuda.synchronize(dev)
+            ts = []
+            for r in range(reps):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for i in range(inner): fn((r * inner + i) % rot)
+                b.record(); b.synchronize(); ts.append(a.elapsed_time(b) * 1e-3 / inner)
+            return float(np.median(ts)), float(np.min(ts))
+        return run              # (run by line() if the op is selected)
 
     def graphed(fn, launches=200):
         """per-launch seconds of `launches` launches captured in one CUDA graph (no host launch cost between them)"""
@@ -184,7 +186,8 @@ def single_op_lines(torch, dev, peak):
             return f'{type(e).__name__}: {e}'[:160]
 
     def line(name, nbytes, sec, units, unit):
-        med, mn = sec
+        if only and not any(o in name for o in only): return
+        med, mn = sec()
         out[name] = {'bytes': nbytes, 'us_median': med * 1e6, 'us_min': mn * 1e6, 'gbs': nbytes / med / 1e9, 'frac_of_peak': nbytes / med / 1e9 / peak,
                      'frac_of_8tbs': nbytes / med / 8e12, unit: units / med}
 
@@ -196,7 +199,7 @@ def single_op_lines(torch, dev, peak):
         nw = 1 + 0.05 * torch.randn(2048, device=dev, generator=g); h = torch.empty(T, 2048, device=dev); h16 = torch.empty(T, 2048, dtype=torch.float16, device=dev)
         sec = timed(lambda i: O.add_rms16(xs[i], nw, 1e-6, h16, T, 2048, d=d, S=1, h=h), rot=rot, inner=100 if T == 1 else 10)
         line(f'add_rms16_f32_h2048_T{T}', T * (4 * 8192 + 4096) + 8192, sec, T, 'tokens_per_s')
-        if T == 1:
+        if T == 1 and f'add_rms16_f32_h2048_T{T}' in out:
             gs = graphed(lambda i: O.add_rms16(xs[i % rot], nw, 1e-6, h16, T, 2048, d=d, S=1, h=h))
             out[f'add_rms16_f32_h2048_T{T}']['us_in_cuda_graph'] = gs * 1e6 if isinstance(gs, float) else gs
         del xs, d, h, h16
@@ -254,6 +257,37 @@ def single_op_lines(torch, dev, peak):
     line('silu_mul_actq_M8192_F4096', 8192 * 4096 * (4 + 2 + 0.5) + 8192 * 4, timed(lambda i: A.silu_mul_actq(gu, 4, 1.0)), 8192, 'rows_per_s')
     xe = rnd(Mr, 896, scale=2.0); nwe = 0.5 + torch.rand(896, device=dev, generator=g); wab = rnd(8, 896, scale=0.05).bfloat16()
     line('block_entry_M32768_d896_nab8', Mr * 896 * (4 + 2 + 0.5) + Mr * (8 + 16), timed(lambda i: A.block_entry(xe, nwe, wab, 1e-6, 4, 1.0)), Mr, 'rows_per_s')
+    # ---- router glue (Qwen3-30B-A3B shapes: hidden 2048, 128 experts, top 8), IQ4 row gathers, the norm with a Q8_1 copy ----
+    n, E, K, k = 8192, 128, 2048, 8
+    hh = rnd(n, K); Wr = rnd(E, K, scale=0.05); lg = torch.empty(n, E, device=dev)
+    line('q3p_router_T8192_E128_K2048', n * K * 4 + E * K * 4 + n * E * 4, timed(lambda i: O.router(hh, Wr, E, K, lg, n)), n, 'tokens_per_s')
+    if 'q3p_router_T8192_E128_K2048' in out: out['q3p_router_T8192_E128_K2048']['gflops'] = 2.0 * n * E * K / out['q3p_router_T8192_E128_K2048']['us_median'] / 1e3
+    ids = torch.zeros(n * k, dtype=torch.int32, device=dev); wts = torch.zeros(n * k, device=dev); er = torch.zeros(1, dtype=torch.int32, device=dev)
+    line('q3p_topk_T8192_E128_k8', n * E * 4 + n * k * 8, timed(lambda i: O.topk(lg, E, k, 6.103515625e-5, ids, wts, er, n)), n, 'tokens_per_s')
+    xs_, yd_ = (torch.zeros(n * k, dtype=torch.int32, device=dev) for _ in range(2))
+    items = torch.zeros(q3m_ops.items_bound(n * k, E), 4, dtype=torch.int32, device=dev); nit = torch.zeros(1, dtype=torch.int32, device=dev)
+    line('q3p_group_65536_pairs_E128', n * k * 12, timed(lambda i: O.group(ids, n * k, k, E, xs_, yd_, items, nit, er)), n, 'tokens_per_s')
+    del hh, Wr, lg
+    from caminus_b200.device import cuda as CU
+    feed = CU.Module('prefill_feed'); I = ctypes.c_int
+    vocab, nblk, nt = 151936, 8, 16384
+    tab = torch.randint(0, 256, (vocab, nblk, 136), device=dev, dtype=torch.uint8, generator=g)
+    tab[:, :, 0:2] = (torch.randn(vocab, nblk, 1, device=dev, generator=g) * 1e-3).abs().half().view(torch.uint8).view(vocab, nblk, 2)
+    tk = torch.randint(0, vocab, (nt,), device=dev, dtype=torch.int32, generator=g); xo = [torch.empty(nt, nblk * 256, device=dev) for _ in range(2)]
+    line('embd_rows_iq4xs_16384x2048', nt * (4 + nblk * 136 + nblk * 1024), timed(lambda i: feed.embd_rows_iq4xs((1,), (256,), tab.view(-1), tk, I(vocab), I(nt), I(nblk), xo[i], er), rot=2), nt, 'rows_per_s')
+    bpr = 64; raw = torch.randint(0, 256, (vocab, bpr, 18), device=dev, dtype=torch.uint8, generator=g)
+    raw[:, :, 0:2] = (torch.randn(vocab, bpr, 1, device=dev, generator=g) * 1e-3).abs().half().view(torch.uint8).view(vocab, bpr, 2)
+    line('ple_rows_iq4nl_16384x2048', nt * (4 + bpr * 18 + bpr * 128), timed(lambda i: feed.ple_rows_iq4nl((1,), (256,), raw.view(-1), tk, I(vocab), I(nt), I(bpr), xo[i], er), rot=2), nt, 'rows_per_s')
+    del tab, raw, xo
+    from caminus_b200 import lib as LB
+    Rq, Kq8 = 32768, 2560
+    xq = rnd(Rq, Kq8, scale=3.0); wq8 = 0.5 + torch.rand(1, Kq8, device=dev, generator=g); yq8 = torch.empty(Rq, Kq8, device=dev)
+    q8o = torch.empty(Rq * Kq8 // 32 * 36, dtype=torch.uint8, device=dev); Lc = LB.load(); cs = torch.cuda.current_stream(dev).cuda_stream
+    line('rms_mul_q8_1_R32768_K2560', Rq * Kq8 * 8 + Rq * Kq8 // 32 * 36,
+         timed(lambda i: LB.check(Lc.cam_rms_mul_q8_1(xq.data_ptr(), wq8.data_ptr(), yq8.data_ptr(), q8o.data_ptr(), Rq, 1, 1e-6, Kq8, cs), 'cam_rms_mul_q8_1')), Rq, 'rows_per_s')
+    del xq, yq8, q8o
+    xm = rnd(8192, 5120, scale=2.0); ym2 = torch.empty(5120 // 128, 8192, 144, dtype=torch.uint8, device=dev)
+    line('quantize_mmq_q8_1_f32_8192x5120_D4', 8192 * 5120 * 4 + 8192 * 40 * 144, timed(lambda i: gguf.quantize_mmq_q8_1(xm, 'D4', y=ym2)), 8192, 'rows_per_s')
     return out
 
 
@@ -263,6 +297,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--rows', type=int, default=T_PER_GPU, help='token rows per GPU (the configured workload is 65536)')
     ap.add_argument('--ops', action='store_true', help='also time the single-op configs 1-4 on rank 0')
+    ap.add_argument('--only', default='', help='with --ops: comma-separated substrings of the op names to time (default: all)')
     ap.add_argument('--cpu-sample', type=int, default=512)
     ap.add_argument('--skip-e2e', action='store_true', help='leave out the host-buffer leg (profiling runs)')
     ap.add_argument('--skip-cpu', action='store_true', help='leave out the CPU baseline leg (profiling runs)')
@@ -392,7 +427,7 @@ def main():
             'cpu_baseline': cpu,
             'tp_rmsnorm': tp,
         }
-        if args.ops: line['ops'] = single_op_lines(torch, dev, peak)
+        if args.ops: line['ops'] = single_op_lines(torch, dev, peak, tuple(o for o in args.only.split(',') if o))
         print(json.dumps(line), flush=True)
     if world > 1: torch.distributed.destroy_process_group()
 

@@ -29,12 +29,11 @@ CAM_DEV void fwht128(float (&v)[4], int lane) {
     a = v[0]; b = v[2]; v[0] = fadd(a, b); v[2] = fsub(a, b);
     a = v[1]; b = v[3]; v[1] = fadd(a, b); v[3] = fsub(a, b);
 #pragma unroll
-    for (int m = 1; m < 32; m <<= 1)
+    for (int m = 1; m < 32; m <<= 1) {
+        const float sg = (lane & m) ? -1.0f : 1.0f;      // the upper lane of a pair holds partner - own: fma(own, -1, partner), one rounding
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const float p = __shfl_xor_sync(CAM_FULL, v[e], m);
-            v[e] = (lane & m) ? fsub(p, v[e]) : fadd(v[e], p);
-        }
+        for (int e = 0; e < 4; e++) v[e] = ffma(v[e], sg, __shfl_xor_sync(CAM_FULL, v[e], m));
+    }
 }
 CAM_DEV float wave_max(float v) {
 #pragma unroll

@@ -223,10 +223,15 @@ CAM_DEV uint32_t bf16x2_rne(float a, float b) {
     const uint32_t ua = __float_as_uint(a), ub = __float_as_uint(b);
     return ((ua + 0x7FFFu + ((ua >> 16) & 1u)) >> 16) | ((ub + 0x7FFFu + ((ub >> 16) & 1u)) & 0xffff0000u);
 }
-template <int CH, bool POST>
+// Q8: also the Q8_1 copy of the normed row (yq: 36-byte blocks, the bytes of gg_quantize_q8_1 on y). 8 adjacent lanes hold a block
+// of 32. The block sum follows the quantiser's 32-lane butterfly (partners 16, 8, 4 are lanes l ^ 4, 2, 1 here, partners 2, 1
+// are inside the lane). The codes roundf(v / d) come from v * rcp(d) where that provably rounds the same way: the product is
+// within 1.8e-7 |t| of the IEEE quotient; if t (1 - 4.8e-7) and t (1 + 4.8e-7) round to one integer, no rounding boundary lies
+// between them and that integer is the quotient's. A lane where they differ (or with a zero, tiny or non-finite block) divides.
+template <int CH, bool POST, bool Q8>
 __global__ void __launch_bounds__(RMS_WARPS * 32) rms_rows_vec_kernel(float * x, const float * __restrict__ w, float * y, uint16_t * __restrict__ ybf,
                                                                       float * __restrict__ scl, int R, int wr, float eps, const float * __restrict__ b,
-                                                                      const float * __restrict__ inj, int HC, float rs) {
+                                                                      const float * __restrict__ inj, int HC, float rs, uint8_t * __restrict__ yq) {
     constexpr int K = 128 * CH;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int t = blockIdx.x * RMS_WARPS + warp; t < R; t += gridDim.x * RMS_WARPS) {
@@ -262,15 +267,50 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) rms_rows_vec_kernel(float * x,
                                          fmul(fmul(xv[m].w, scale), ww.w));
             if (y) *reinterpret_cast<float4 *>(y + (size_t)t * K + 4 * lane + 128 * m) = v;
             if (ybf) st64_stream(ybf + (size_t)t * K + 4 * lane + 128 * m, make_uint2(bf16x2_rne(v.x, v.y), bf16x2_rne(v.z, v.w)));
+            if (Q8) {
+                float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+                float s0 = v.x, s1 = v.y, s2 = v.z, s3 = v.w;
+#pragma unroll
+                for (int o = 4; o > 0; o >>= 1) {
+                    amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, o));
+                    s0 = fadd(s0, __shfl_xor_sync(CAM_FULL, s0, o)); s1 = fadd(s1, __shfl_xor_sync(CAM_FULL, s1, o));
+                    s2 = fadd(s2, __shfl_xor_sync(CAM_FULL, s2, o)); s3 = fadd(s3, __shfl_xor_sync(CAM_FULL, s3, o));
+                }
+                const float sum = fadd(fadd(s0, s2), fadd(s1, s3));
+                const float d = fdiv(amax, 127.0f);
+                const float inv = rcp_approx(d);
+                const float inv_hi = fmul(inv, 0x1.000008p+0f), inv_lo = fmul(inv, 0x1.fffff0p-1f);
+                const float vv[4] = {v.x, v.y, v.z, v.w};
+                uint32_t c[4], differ = 0;
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    c[e] = __float_as_uint(ffma(vv[e], inv_hi, 12582912.0f));
+                    differ |= c[e] ^ __float_as_uint(ffma(vv[e], inv_lo, 12582912.0f));
+                }
+                uint32_t word = __byte_perm(__byte_perm(c[0], c[1], 0x0040), __byte_perm(c[2], c[3], 0x0040), 0x5410);
+                const float mag = fadd(fadd(fabsf(v.x), fabsf(v.y)), fadd(fabsf(v.z), fabsf(v.w)));
+                if (differ != 0 || !(d >= 1.0e-30f) || !(mag < 3.0e38f)) {      // the exact statements for this lane's four values
+                    word = 0;
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float qv = fdiv(vv[e], d);
+                        const int q = (amax != 0.0f && fabsf(qv) < 127.5f) ? __float2int_rn(roundf(qv)) : 0;
+                        word |= (uint32_t)(q & 0xff) << (8 * e);
+                    }
+                }
+                uint32_t * blk = reinterpret_cast<uint32_t *>(yq + ((size_t)t * (K / 32) + 4 * m + (lane >> 3)) * 36);
+                __stcs(blk + 1 + (lane & 7), word);
+                if ((lane & 7) == 0) __stcs(blk, f2_to_h2(d, sum));
+            }
         }
     }
 }
 
-template <int CH, bool POST>
+template <int CH, bool POST, bool Q8 = false>
 int launch_rows_vec(float * x, const float * w, float * y, uint16_t * ybf, float * scl, int R, int wr, float eps, const float * b, const float * inj,
-                    int HC, float rs, cudaStream_t stream) {
-    const int grid = cam_resident_grid(rms_rows_vec_kernel<CH, POST>, RMS_WARPS * 32, 0, ((long)R + RMS_WARPS - 1) / RMS_WARPS);
-    rms_rows_vec_kernel<CH, POST><<<grid, RMS_WARPS * 32, 0, stream>>>(x, w, y, ybf, scl, R, wr, eps, b, inj, HC, rs);
+                    int HC, float rs, cudaStream_t stream, uint8_t * yq = nullptr) {
+    const int grid = cam_resident_grid(rms_rows_vec_kernel<CH, POST, Q8>, RMS_WARPS * 32, 0, ((long)R + RMS_WARPS - 1) / RMS_WARPS);
+    rms_rows_vec_kernel<CH, POST, Q8><<<grid, RMS_WARPS * 32, 0, stream>>>(x, w, y, ybf, scl, R, wr, eps, b, inj, HC, rs, yq);
     return (int)cudaGetLastError();
 }
 
@@ -596,10 +636,19 @@ extern "C" int cam_rms_norm_f16_static(int n, void * x, const void * d, const fl
 // The vector path of pf_rms_mul / pf_hc_post_rms (csrc/hc_glue.cu): K in {2048, 2560, 5120}, 16-byte aligned buffers, enough rows to
 // fill the device. Returns CAM_ERR_SHAPE when it does not apply (the caller then uses its block-per-row kernel).
 int cam_rms_rows_vec(float * x, const float * w, float * y, void * ybf, float * scl, int R, int wr, float eps, int K, const float * b,
-                     const float * inj, int HC, float rs, void * stream) {
+                     const float * inj, int HC, float rs, void * stream, void * yq) {
     if (R < 2 * cam_sm_count() || !cam_aligned16(x) || !cam_aligned16(w) || (y && !cam_aligned16(y)) || (ybf && (reinterpret_cast<uintptr_t>(ybf) & 7u)) ||
         (b && !cam_aligned16(b))) return CAM_ERR_SHAPE;
     uint16_t * yb = (uint16_t *)ybf; cudaStream_t st = (cudaStream_t)stream;
+    if (yq) {       // pf_rms_mul's norm with the Q8_1 copy
+        if (b || ybf || scl) return CAM_ERR_SHAPE;
+        switch (K) {
+            case 2048: return launch_rows_vec<16, false, true>(x, w, y, nullptr, nullptr, R, wr, eps, nullptr, nullptr, 1, 0.0f, st, (uint8_t *)yq);
+            case 2560: return launch_rows_vec<20, false, true>(x, w, y, nullptr, nullptr, R, wr, eps, nullptr, nullptr, 1, 0.0f, st, (uint8_t *)yq);
+            case 5120: return launch_rows_vec<40, false, true>(x, w, y, nullptr, nullptr, R, wr, eps, nullptr, nullptr, 1, 0.0f, st, (uint8_t *)yq);
+            default: return CAM_ERR_SHAPE;
+        }
+    }
     switch (K) {
         case 2048: return b ? launch_rows_vec<16, true>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st) : launch_rows_vec<16, false>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st);
         case 2560: return b ? launch_rows_vec<20, true>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st) : launch_rows_vec<20, false>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st);

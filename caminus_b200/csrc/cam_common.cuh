@@ -93,6 +93,30 @@ CAM_DEV void st64(void * p, uint2 v) { *reinterpret_cast<uint2 *>(p) = v; }
 CAM_DEV void st128_stream(void * p, uint4 v) { __stcs(reinterpret_cast<uint4 *>(p), v); }           // written once, not re-read here
 CAM_DEV void st64_stream(void * p, uint2 v) { __stcs(reinterpret_cast<uint2 *>(p), v); }
 
+// ---- 8 consecutive values of a row as fp32 (fp32 or fp16 storage), and one value -----------------------------------------
+template <typename T> struct Load8;
+template <> struct Load8<float> {
+    static CAM_DEV void get(const float * p, float (&f)[8]) {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(p)), b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+    static CAM_DEV float one(const float * p) { return __ldg(p); }
+};
+template <> struct Load8<uint16_t> {
+    static CAM_DEV void get(const uint16_t * p, float (&f)[8]) {
+        const uint4 v = ldg128(p);
+        const float2 a = h2_to_f2(v.x), b = h2_to_f2(v.y), c = h2_to_f2(v.z), e = h2_to_f2(v.w);
+        f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = e.x; f[7] = e.y;
+    }
+    static CAM_DEV float one(const uint16_t * p) { return __half2float(__ushort_as_half(__ldg(p))); }
+};
+
+// ---- the special-function unit's approximations, used only where a kernel proves the stored bytes do not depend on them ---
+// (.ftz: a denormal exponent argument counts as 0 and a denormal 2^a as 0; both are below 1e-38 beside the 1 they are added to)
+CAM_DEV float ex2_approx(float a) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
+CAM_DEV float rcp_approx(float a) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
+
+
 // ---- cp.async (16 bytes per thread, L2 only) with commit / wait groups --------------------------------------------------------
 CAM_DEV void cp_async16(void * smem, const void * gmem) {
     const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -120,4 +144,4 @@ static inline int cam_resident_grid(K kernel, int threads, size_t smem, long wan
 
 // csrc/add_rms.cu: the warp-per-row path of the hyper-connection norms (CAM_ERR_SHAPE: does not apply to this call)
 int cam_rms_rows_vec(float * x, const float * w, float * y, void * ybf, float * scl, int R, int wr, float eps, int K, const float * b,
-                     const float * inj, int HC, float rs, void * stream);
+                     const float * inj, int HC, float rs, void * stream, void * yq = nullptr);

@@ -2,7 +2,11 @@
 // siblings of the Q4_K embedding gather): bitwise the host decoders (python/caminus/own_dequant.py iq4_xs; gguf-py).
 // y = (d * (ls - 32)) * kvalue (IQ4_XS) / d * kvalue (IQ4_NL): lone products, rounded one by one. The 16 kvalues are ggml's IQ4_NL
 // codebook, part of the format's definition. An index outside its table is clamped before the read and reported in *err.
-// Mapping: a thread per four consecutive outputs (one 16-byte store); their nibbles are four consecutive bytes of the block.
+// Mapping: a block per row, looping over rows; a thread takes four consecutive bytes of a 32-value sub-block (one 32-bit load) and
+// writes the eight outputs they hold: values j .. j + 3 from the low nibbles, 16 + j .. 16 + j + 3 from the high ones (two 16-byte
+// stores). The codebook sits in shared memory (16 words in 16 banks: any mix of indices is served in one pass; from constant
+// memory, lanes with different indices are served one after another). Tables that are not 8-byte (IQ4_XS) / 2-byte (IQ4_NL)
+// aligned take the byte-wise kernels.
 #include "cam_common.cuh"
 
 namespace {
@@ -11,7 +15,7 @@ __constant__ float kIQ4NL[16] = {-127.f, -104.f, -83.f, -65.f, -49.f, -35.f, -22
 
 CAM_DEV float f16_at(const uint8_t * p) { return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8)))); }
 
-__global__ void __launch_bounds__(256) embd_rows_iq4xs_kernel(const uint8_t * __restrict__ table, const int * __restrict__ tok, int nvocab, int n, int nblk,
+__global__ void __launch_bounds__(256) embd_rows_iq4xs_bytes_kernel(const uint8_t * __restrict__ table, const int * __restrict__ tok, int nvocab, int n, int nblk,
                                                               float * __restrict__ out, int * err) {
     const int D4 = nblk * 64; const long total = (long)n * D4;
     for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long)gridDim.x * 256) {
@@ -31,7 +35,7 @@ __global__ void __launch_bounds__(256) embd_rows_iq4xs_kernel(const uint8_t * __
     }
 }
 
-__global__ void __launch_bounds__(256) ple_rows_iq4nl_kernel(const uint8_t * __restrict__ raw, const int * __restrict__ inv, int nuniq, int nrows, int bpr,
+__global__ void __launch_bounds__(256) ple_rows_iq4nl_bytes_kernel(const uint8_t * __restrict__ raw, const int * __restrict__ inv, int nuniq, int nrows, int bpr,
                                                              float * __restrict__ out, int * err) {
     const int hd4 = bpr * 8; const long total = (long)nrows * hd4;
     for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long)gridDim.x * 256) {
@@ -49,6 +53,57 @@ __global__ void __launch_bounds__(256) ple_rows_iq4nl_kernel(const uint8_t * __r
     }
 }
 
+CAM_DEV void iq4_store8(float * o, const float * kv, uint32_t w, float dl) {
+    float4 lo, hi;
+    lo.x = fmul(dl, kv[w & 15]); lo.y = fmul(dl, kv[(w >> 8) & 15]); lo.z = fmul(dl, kv[(w >> 16) & 15]); lo.w = fmul(dl, kv[(w >> 24) & 15]);
+    hi.x = fmul(dl, kv[(w >> 4) & 15]); hi.y = fmul(dl, kv[(w >> 12) & 15]); hi.z = fmul(dl, kv[(w >> 20) & 15]); hi.w = fmul(dl, kv[w >> 28]);
+    __stcs(reinterpret_cast<float4 *>(o), lo);
+    __stcs(reinterpret_cast<float4 *>(o + 16), hi);
+}
+
+__global__ void __launch_bounds__(256) embd_rows_iq4xs_kernel(const uint8_t * __restrict__ table, const int * __restrict__ tok, int nvocab, int n, int nblk,
+                                                              float * __restrict__ out, int * err) {
+    __shared__ float kv[16];
+    if (threadIdx.x < 16) kv[threadIdx.x] = kIQ4NL[threadIdx.x];
+    __syncthreads();
+    const int units = nblk * 32;
+    for (int p = blockIdx.x; p < n; p += gridDim.x) {
+        int t = __ldg(tok + p);
+        if (t < 0 || t >= nvocab) { if (threadIdx.x == 0) atomicOr(err, 2); t = t < 0 ? 0 : nvocab - 1; }
+        const uint8_t * row = table + (size_t)t * (size_t)(nblk * 136);
+        float * orow = out + (size_t)p * (size_t)(nblk * 256);
+        for (int q = threadIdx.x; q < units; q += 256) {
+            const int bl = q >> 5, ib = (q >> 2) & 7, jq = q & 3;
+            const uint8_t * b = row + (size_t)bl * 136;
+            const uint2 hd = __ldg(reinterpret_cast<const uint2 *>(b));                         // d | scales_h | scales_l[4]
+            const int sh = hd.x >> 16, sl = (hd.y >> (8 * (ib >> 1))) & 0xff;
+            const int ls = ((sl >> ((ib & 1) * 4)) & 15) | (((sh >> (2 * ib)) & 3) << 4);
+            const float dl = fmul(__half2float(__ushort_as_half((unsigned short)(hd.x & 0xffffu))), (float)(ls - 32));
+            iq4_store8(orow + bl * 256 + ib * 32 + 4 * jq, kv, __ldg(reinterpret_cast<const uint32_t *>(b + 8 + 16 * ib + 4 * jq)), dl);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) ple_rows_iq4nl_kernel(const uint8_t * __restrict__ raw, const int * __restrict__ inv, int nuniq, int nrows, int bpr,
+                                                             float * __restrict__ out, int * err) {
+    __shared__ float kv[16];
+    if (threadIdx.x < 16) kv[threadIdx.x] = kIQ4NL[threadIdx.x];
+    __syncthreads();
+    const int units = bpr * 4;
+    for (int r = blockIdx.x; r < nrows; r += gridDim.x) {
+        int u = __ldg(inv + r);
+        if (u < 0 || u >= nuniq) { if (threadIdx.x == 0) atomicOr(err, 1); u = u < 0 ? 0 : nuniq - 1; }
+        const uint8_t * row = raw + (size_t)u * (size_t)(bpr * 18);
+        float * orow = out + (size_t)r * (size_t)(bpr * 32);
+        for (int q = threadIdx.x; q < units; q += 256) {
+            const int b = q >> 2, jq = q & 3;
+            const uint16_t * blk = reinterpret_cast<const uint16_t *>(row + (size_t)b * 18);    // d, then 16 bytes of nibbles
+            const uint32_t w = (uint32_t)__ldg(blk + 1 + 2 * jq) | ((uint32_t)__ldg(blk + 2 + 2 * jq) << 16);
+            iq4_store8(orow + b * 32 + 4 * jq, kv, w, __half2float(__ushort_as_half(__ldg(blk))));
+        }
+    }
+}
+
 }   // namespace
 
 // embd_rows_iq4xs / ple_rows_iq4nl: kernels/prefill_feed.hip:40-41, 24-25 (one thread per output float there)
@@ -57,7 +112,9 @@ extern "C" int embd_rows_iq4xs(const void * table, const int * tok, int nvocab, 
     if (!cam_aligned16(out)) return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
     const long want = ((long)n * nblk * 64 + 255) / 256;
-    embd_rows_iq4xs_kernel<<<cam_resident_grid(embd_rows_iq4xs_kernel, 256, 0, want), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)table, tok, nvocab, n, nblk, out, err);
+    if (reinterpret_cast<uintptr_t>(table) & 7u)
+        embd_rows_iq4xs_bytes_kernel<<<cam_resident_grid(embd_rows_iq4xs_bytes_kernel, 256, 0, want), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)table, tok, nvocab, n, nblk, out, err);
+    else embd_rows_iq4xs_kernel<<<cam_resident_grid(embd_rows_iq4xs_kernel, 256, 0, n), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)table, tok, nvocab, n, nblk, out, err);
     return (int)cudaGetLastError();
 }
 extern "C" int ple_rows_iq4nl(const void * raw, const int * inv, int nuniq, int nrows, int bpr, float * out, int * err, void * stream) {
@@ -65,6 +122,8 @@ extern "C" int ple_rows_iq4nl(const void * raw, const int * inv, int nuniq, int 
     if (!cam_aligned16(out)) return CAM_ERR_ALIGN;
     if (nrows == 0) return CAM_OK;
     const long want = ((long)nrows * bpr * 8 + 255) / 256;
-    ple_rows_iq4nl_kernel<<<cam_resident_grid(ple_rows_iq4nl_kernel, 256, 0, want), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)raw, inv, nuniq, nrows, bpr, out, err);
+    if (reinterpret_cast<uintptr_t>(raw) & 1u)
+        ple_rows_iq4nl_bytes_kernel<<<cam_resident_grid(ple_rows_iq4nl_bytes_kernel, 256, 0, want), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)raw, inv, nuniq, nrows, bpr, out, err);
+    else ple_rows_iq4nl_kernel<<<cam_resident_grid(ple_rows_iq4nl_kernel, 256, 0, nrows), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)raw, inv, nuniq, nrows, bpr, out, err);
     return (int)cudaGetLastError();
 }

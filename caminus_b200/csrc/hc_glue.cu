@@ -273,6 +273,10 @@ extern "C" int cam_rms_mul_q8_1(const float * x, const float * w, float * y, voi
     if (R < 0 || wr < 1 || K < 32 || (K & 31) || K > 256 * ROW_MAX_NI || !x || !w || !yq) return CAM_ERR_ARG;
     if (reinterpret_cast<uintptr_t>(yq) & 3u) return CAM_ERR_ALIGN;
     if (R == 0) return CAM_OK;
+    {
+        const int r = cam_rms_rows_vec(const_cast<float *>(x), w, y, nullptr, nullptr, R, wr, eps, K, nullptr, nullptr, 1, 0.0f, stream, yq);
+        if (r != CAM_ERR_SHAPE) return r;
+    }
     rms_rows_kernel<0><<<R < cam_sm_count() * 8 ? R : cam_sm_count() * 8, 256, 0, CAM_STREAM>>>(x, w, y, nullptr, nullptr, R, wr, eps, K, nullptr, nullptr, 1, 0.0f, (uint8_t *)yq);
     return (int)cudaGetLastError();
 }

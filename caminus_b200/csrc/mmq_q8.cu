@@ -65,6 +65,179 @@ __global__ void __launch_bounds__(256) mmq_q8_1_kernel(const void * __restrict__
     }
 }
 
+// ---- SwiGLU into D4 blocks at memory speed: a fast pass with proof margins, exact recomputation where a margin is not met ---
+//
+// The scale of this layout is a full fp32 number, d = 1.0f / (127.0f / amax), so it needs the exact statements' amax bit for bit.
+// The fast pass evaluates h^ = g * rcp(1 + ex2(-g log2 e)) * u on the special-function unit; with h the exact statements' value
+// of an element, |h^ - h| <= EPS |h|, EPS = 1.35e-6, whenever g >= -8 and g is not so small that g / (1 + e) is denormal
+// (the derivation is in the header of swiglu_q8_fast_kernel, csrc/swiglu_q8.cu). From that, per group of 32 values:
+//   amax:  the element with the largest exact |h| is among those with |h^| >= amax^ (1 - 3e-6) (amax^ = max |h^|). Where
+//          exactly one element of the group passes that threshold, it IS the exact argmax, and the exact statements are
+//          evaluated for that one element only: amax, d_inv = 127 / amax and d = 1 / d_inv are then the exact statements' bits.
+//   codes: t^ = h^ d_inv is within 1.41e-6 |t| of the exact fp32 product t = h d_inv. If t^ (1 - 1.7e-6) and t^ (1 + 1.7e-6) round
+//          to the same integer, no rounding boundary and no tie lies in the interval that holds t, and that integer is roundf(t).
+// A group where this fails (two candidates, an interval that holds a boundary, some g < -8, a NaN or infinity, amax^ outside
+// [1e-30, 3e38)) is recomputed by the whole warp with the exact statements, one lane per value. Every stored byte is
+// therefore the exact statements' byte.
+//
+// Mapping: a lane holds 8 consecutive values (one 16-byte load of fp16 gate and up), 4 lanes a group of 32, a half-warp a
+// block of 128; a warp takes two K-blocks of four consecutive rows (4 "chunks" of 256 values). The four candidates of a
+// lane quad (one per chunk) are moved one to each of its lanes, so that the exact evaluation and the two IEEE divisions run
+// once per four chunks; that lane also stores the group's scale.
+CAM_DEV float max_nan(float a, float b) { float r; asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
+// bits |= bit where |h| >= thr (a compare and a predicated OR)
+CAM_DEV void or_if_ge(uint32_t & bits, float h, float thr, uint32_t bit) {
+    asm("{\n .reg .pred p;\n setp.ge.f32 p, %1, %2;\n @p or.b32 %0, %0, %3;\n}" : "+r"(bits) : "f"(fabsf(h)), "f"(thr), "r"(bit));
+}
+
+// 8 consecutive values as they were loaded: widened on use, so that the next task's loads can fly during this task's arithmetic
+template <typename T> struct Raw8;
+template <> struct Raw8<uint16_t> {
+    uint4 v;
+    CAM_DEV void load(const uint16_t * p) { v = ldg128(p); }
+    CAM_DEV void fill(float x) { const uint32_t w = f2_to_h2(x, x); v = make_uint4(w, w, w, w); }
+    CAM_DEV void get(float (&f)[8]) const {
+        const float2 a = h2_to_f2(v.x), b = h2_to_f2(v.y), c = h2_to_f2(v.z), e = h2_to_f2(v.w);
+        f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = e.x; f[7] = e.y;
+    }
+    CAM_DEV float pick(int i) const {
+        const uint32_t w = i < 4 ? (i < 2 ? v.x : v.y) : (i < 6 ? v.z : v.w);
+        return __half2float(__ushort_as_half((uint16_t)((i & 1) ? w >> 16 : w)));
+    }
+};
+template <> struct Raw8<float> {
+    float4 a, b;
+    CAM_DEV void load(const float * p) { a = __ldg(reinterpret_cast<const float4 *>(p)); b = __ldg(reinterpret_cast<const float4 *>(p) + 1); }
+    CAM_DEV void fill(float x) { a = make_float4(x, x, x, x); b = a; }
+    CAM_DEV void get(float (&f)[8]) const { f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w; }
+    CAM_DEV float pick(int i) const {
+        const float4 h = i < 4 ? a : b;
+        return (i & 2) ? ((i & 1) ? h.w : h.z) : ((i & 1) ? h.y : h.x);
+    }
+};
+
+// a warp's task: K-blocks 2 kp, 2 kp + 1 (one per half-warp) of rows r0 .. r0 + 3
+struct MmqTask {
+    int r0, kb, k;
+    bool kon, kin;
+    CAM_DEV MmqTask(long task, int nrq, int lane, int nkb, int kvalid) {
+        const int kp = (int)(task / nrq);
+        r0 = (int)(task - (long)kp * nrq) * 4;
+        kb = kp * 2 + (lane >> 4); k = kb * 128 + (lane & 15) * 8;
+        kon = kb < nkb; kin = kon && k < kvalid;
+    }
+};
+
+template <typename T>
+CAM_DEV void mmq_fetch(const T * __restrict__ g, const T * __restrict__ u, const MmqTask & t, long ld, int rows, Raw8<T> (&rg)[4], Raw8<T> (&ru)[4]) {
+    const T * gp = g + (size_t)t.r0 * ld + t.k, * up = u + (size_t)t.r0 * ld + t.k;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        if (t.kin && t.r0 + c < rows) { rg[c].load(gp + c * ld); ru[c].load(up + c * ld); }
+        else { rg[c].fill(1.0f); ru[c].fill(0.0f); }                  // h = 0 on both passes
+    }
+}
+
+// PF: the next task's values are loaded before this task's arithmetic (fp16: 32 more registers)
+template <typename T, bool PF>
+__global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y,
+                                                                 int kvalid, int nkb, long ld, int rows) {
+    const int lane = threadIdx.x & 31, qb = lane & 28, qi = lane & 3;
+    const int nrq = (rows + 3) >> 2;
+    const long total = (long)((nkb + 1) >> 1) * nrq, stride = (long)gridDim.x * 8;
+    long task = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (task >= total) return;
+    Raw8<T> rg[4], ru[4], ng[4], nu[4];
+    if (PF) mmq_fetch(g, u, MmqTask(task, nrq, lane, nkb, kvalid), ld, rows, rg, ru);
+    for (; task < total; task += stride) {
+        const MmqTask t(task, nrq, lane, nkb, kvalid);
+        if (!PF) mmq_fetch(g, u, t, ld, rows, rg, ru);
+        else if (task + stride < total) mmq_fetch(g, u, MmqTask(task + stride, nrq, lane, nkb, kvalid), ld, rows, ng, nu);
+        float h[4][8], eg = 1.0f, eu = 0.0f;
+        uint32_t bad = 0;                                             // bit c: chunk c of this lane fails a margin
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            float gv[8], uv[8];
+            rg[c].get(gv); ru[c].get(uv);
+            float amax = 0.0f, gmin = gv[0], gsm = fabsf(gv[0]);
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const float ex = ex2_approx(fmul(gv[e], -0x1.715476p+0f));
+                h[c][e] = fmul(fmul(gv[e], rcp_approx(fadd(1.0f, ex))), uv[e]);
+                amax = max_nan(amax, fabsf(h[c][e]));
+                gmin = fminf(gmin, gv[e]);
+                if (sizeof(T) == 4) gsm = fminf(gsm, fabsf(gv[e]));
+            }
+            amax = max_nan(amax, __shfl_xor_sync(CAM_FULL, amax, 1));
+            amax = max_nan(amax, __shfl_xor_sync(CAM_FULL, amax, 2));
+            const float thr = fmul(amax, 0.999997f);
+            uint32_t bits = 0;
+#pragma unroll
+            for (int e = 0; e < 8; e++) or_if_ge(bits, h[c][e], thr, 1u << e);
+            const uint32_t ball = (__ballot_sync(CAM_FULL, bits != 0) >> qb) & 0xfu;
+            if ((bits & (bits - 1)) != 0 || (ball & (ball - 1)) != 0 || ball == 0 || !(gmin >= -8.0f) || !(amax >= 1.0e-30f && amax < 3.0e38f) ||
+                (sizeof(T) == 4 && !(gsm >= 3.0e-38f))) bad |= 1u << c;
+            const int idx = (__ffs(bits) - 1) & 7, src = qb + ((__ffs(ball) - 1) & 3);
+            const float tg = __shfl_sync(CAM_FULL, rg[c].pick(idx), src), tu = __shfl_sync(CAM_FULL, ru[c].pick(idx), src);
+            if (qi == c) { eg = tg; eu = tu; }
+        }
+        // the exact statements for the quad's four candidates, one per lane
+        const float am = fabsf(fmul(cam_silu(eg), eu));
+        const float d_inv = fdiv(127.0f, am), d = fdiv(1.0f, d_inv);
+        uint8_t * const yb = y + ((size_t)t.kb * rows + t.r0) * 144;           // row r0's block of this half-warp's K-block
+        uint32_t redo = 0;                                            // bit 4 j + c: group j of chunk c is recomputed
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const float di = __shfl_sync(CAM_FULL, d_inv, qb + c);
+            const float inv_hi = fmul(di, 0x1.00001cp+0f), inv_lo = fmul(di, 0x1.ffffc8p-1f);      // 1 +- 1.67e-6
+            uint32_t v[8], differ = 0;
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                v[e] = __float_as_uint(ffma(h[c][e], inv_hi, 12582912.0f));
+                differ |= v[e] ^ __float_as_uint(ffma(h[c][e], inv_lo, 12582912.0f));
+            }
+            const bool on = t.kon && t.r0 + c < rows;
+            const uint32_t mask = __ballot_sync(CAM_FULL, (differ != 0 || ((bad >> c) & 1u)) && on);
+            const uint32_t quad = (mask | (mask >> 1) | (mask >> 2) | (mask >> 3)) & 0x11111111u;
+            redo |= quad << c;
+            if (on && !((quad >> qb) & 1u)) {
+                const uint32_t w0 = __byte_perm(__byte_perm(v[0], v[1], 0x0040), __byte_perm(v[2], v[3], 0x0040), 0x5410);
+                const uint32_t w1 = __byte_perm(__byte_perm(v[4], v[5], 0x0040), __byte_perm(v[6], v[7], 0x0040), 0x5410);
+                st64_stream(yb + c * 144 + 16 + (lane & 15) * 8, make_uint2(w0, w1));
+            }
+        }
+        // the scale of chunk qi, group lane / 4 (this lane evaluated it)
+        if (t.kon && t.r0 + qi < rows && !((redo >> (qb + qi)) & 1u)) reinterpret_cast<float *>(yb + qi * 144)[(lane >> 2) & 3] = d;
+        // exact recomputation of the flagged groups: the whole warp, one lane per value (uniform: redo is the same in every lane)
+        for (uint32_t m = redo; m; m &= m - 1) {
+            const int bit = __ffs(m) - 1, j = bit >> 2, c = bit & 3;     // group j of the warp's 8: K-block j / 4, group j % 4
+            const int kbj = (t.kb - (lane >> 4)) + (j >> 2), kj = kbj * 128 + (j & 3) * 32 + lane;
+            float x = 0.0f;
+            if (kj < kvalid) {
+                const size_t at = (size_t)(t.r0 + c) * ld + kj;
+                x = fmul(cam_silu(Load8<T>::one(g + at)), Load8<T>::one(u + at));
+            }
+            float a = fabsf(x);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(CAM_FULL, a, o));
+            uint8_t * blk = y + ((size_t)kbj * rows + t.r0 + c) * 144;
+            float de = 0.0f;
+            int code = 0;
+            if (a != 0.0f) {
+                const float di = fdiv(127.0f, a), tq = fmul(x, di);
+                code = fabsf(tq) < 127.5f ? __float2int_rn(roundf(tq)) : 0;
+                de = fdiv(1.0f, di);
+            }
+            blk[16 + (j & 3) * 32 + lane] = (uint8_t)code;
+            if (lane == 0) reinterpret_cast<float *>(blk)[j & 3] = de;
+        }
+        if (PF) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) { rg[c] = ng[c]; ru[c] = nu[c]; }
+        }
+    }
+}
+
 template <int MODE>
 int launch_mmq(const void * x, const void * u, void * y, int kvalid, int Kpad, long ld, int rows, int layout, cudaStream_t stream) {
     if (rows < 0 || Kpad < 128 || (Kpad & 127) || kvalid < 0 || kvalid > Kpad || (kvalid & 3) || ld < kvalid || (ld & 3) || !x || !y ||
@@ -72,6 +245,14 @@ int launch_mmq(const void * x, const void * u, void * y, int kvalid, int Kpad, l
     const int elt = MODE == 2 ? 8 : 16;
     if ((reinterpret_cast<uintptr_t>(x) & (elt - 1)) || (u && (reinterpret_cast<uintptr_t>(u) & (elt - 1))) || !cam_aligned16(y)) return CAM_ERR_ALIGN;
     if (rows == 0) return CAM_OK;
+    if (MODE != 0 && layout == 0 && !(kvalid & 7) && !(ld & 7) && cam_aligned16(x) && cam_aligned16(u)) {
+        const long want = (long)((Kpad / 128 + 1) / 2) * ((rows + 3) / 4);
+        if (MODE == 2) mmq_swiglu_fast_kernel<uint16_t, true><<<cam_resident_grid(mmq_swiglu_fast_kernel<uint16_t, true>, 256, 0, (want + 7) / 8), 256, 0, stream>>>(
+                (const uint16_t *)x, (const uint16_t *)u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
+        else mmq_swiglu_fast_kernel<float, false><<<cam_resident_grid(mmq_swiglu_fast_kernel<float, false>, 256, 0, (want + 7) / 8), 256, 0, stream>>>(
+                (const float *)x, (const float *)u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
+        return (int)cudaGetLastError();
+    }
     const long total = (long)(Kpad / 128) * rows, want = (total + 7) / 8;
     if (layout == 0) mmq_q8_1_kernel<MODE, 0><<<cam_resident_grid(mmq_q8_1_kernel<MODE, 0>, 256, 0, want), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
     else mmq_q8_1_kernel<MODE, 1><<<cam_resident_grid(mmq_q8_1_kernel<MODE, 1>, 256, 0, want), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);

@@ -17,6 +17,7 @@
 // on a kernel that is instruction-bound; the sum is one input of a tolerance-gated fp16 result.) Every other statement is
 // the reference's.
 #include "cam_common.cuh"
+#include "kv_q8.cuh"
 
 #include <cstdio>
 #include <cstdlib>
@@ -30,6 +31,7 @@ struct RopeArgs {
     uint16_t * out0;       // q16 [n][nh][128]
     uint16_t * out1;       // CACHE: the KV cache (rows of 2 nkv 128 halves). Otherwise k out [n][nkv][128]
     int ldq, nh, nkv, pos0, n, yarn;
+    int * err;             // Q8: the word a refused Q8_0 block ORs 2 into
 };
 
 template <typename T> struct In;
@@ -50,12 +52,14 @@ template <> struct In<uint16_t> {
 // T: the input type. CACHE: the reference's signature (fp32 qkv rows in, q16 and the cache row's K | V halves out).
 // P: heads per half-warp and round: a warp takes 2 P heads of a token at a time, reduces them all, then ONE pass of the
 // scale's square root and divisions serves all of them (lane j computes head j's), instead of one per head.
+// Q8 (with CACHE): the Q8_0 KV cache form (q3p_qk_rope_q8, kernels/q3m_prefill.hip:526-535, 572-583; csrc/kv_q8.cuh): out1 is the
+// byte cache, q16 and K are Hadamard-transformed, K and V are stored as Q8_0 blocks.
 // ONE: the block's warps cover the token's heads in exactly one round (H = 2 P warps): no head loop and no bounds tests, and
 // everything that depends only on the head (offsets in the stage and in the output, the weight row) is computed before
 // the token loop.
 constexpr int ROPE_STAGES = 3;        // tokens in flight per block: two copies fly while one token is computed
 
-template <typename T, bool CACHE, int P, bool ONE>
+template <typename T, bool CACHE, int P, bool ONE, bool Q8 = false>
 __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -127,6 +131,7 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
         const int pos = A.pos0 + t;
         uint16_t * const qbase = A.out0 + (size_t)t * nh * 128;
         uint16_t * const kbase = CACHE ? A.out1 + (size_t)pos * 2 * nkv * 128 : A.out1 + (size_t)t * nkv * 128;
+        uint8_t * const cw = reinterpret_cast<uint8_t *>(A.out1) + (size_t)pos * (2 * nkv * 4 * 34);       // Q8: the row's K blocks | V blocks
         for (int h0 = 2 * warp * P; h0 < H; h0 += 2 * nwarps * P) {        // this warp's heads h0 .. h0 + 2 P - 1 (ONE: a single round)
             float x[P][8], tot[P];
 #pragma unroll
@@ -164,7 +169,8 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
             for (int p = 0; p < P; p++) {
                 const float scale = __shfl_sync(CAM_FULL, scale_mine, 2 * p + hw);
                 const int hy = h0 + 2 * p + hw;
-                if (ONE || hy < H) {
+                const bool on = ONE || hy < H;
+                if (Q8 || on) {                 // (Q8: every lane takes part in the exchanges below; an idle half-warp holds zeros)
                     const bool isq = ONE ? isq_[p] : hy < nh;
                     const float * wn = ONE ? wrow[p] : (isq ? wq : wk) + 4 * l16;
                     const float4 wlo = *reinterpret_cast<const float4 *>(wn), whi = *reinterpret_cast<const float4 *>(wn + 64);
@@ -176,13 +182,41 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
                         ylo[c] = ffma(x0, cc[c], -fmul(x1, sn[c]));
                         yhi[c] = ffma(x1, cc[c], fmul(x0, sn[c]));
                     }
-                    uint16_t * o = (isq ? qbase : kbase) + (ONE ? ooff[p] : (isq ? hy : hy - nh) * 128 + 4 * l16);
-                    st64_stream(o, make_uint2(f2_to_h2(ylo[0], ylo[1]), f2_to_h2(ylo[2], ylo[3])));
-                    st64_stream(o + 64, make_uint2(f2_to_h2(yhi[0], yhi[1]), f2_to_h2(yhi[2], yhi[3])));
+                    if (!Q8) {
+                        uint16_t * o = (isq ? qbase : kbase) + (ONE ? ooff[p] : (isq ? hy : hy - nh) * 128 + 4 * l16);
+                        st64_stream(o, make_uint2(f2_to_h2(ylo[0], ylo[1]), f2_to_h2(ylo[2], ylo[3])));
+                        st64_stream(o + 64, make_uint2(f2_to_h2(yhi[0], yhi[1]), f2_to_h2(yhi[2], yhi[3])));
+                    } else {
+                        float y[8];
+#pragma unroll
+                        for (int c = 0; c < 4; c++) { y[c] = f16r(ylo[c]); y[4 + c] = f16r(yhi[c]); }
+                        hadamard128(y, l16);
+                        if (on && isq) {
+                            uint16_t * o = qbase + (ONE ? ooff[p] : hy * 128 + 4 * l16);
+                            st64_stream(o, make_uint2(f2_to_h2(y[0], y[1]), f2_to_h2(y[2], y[3])));
+                            st64_stream(o + 64, make_uint2(f2_to_h2(y[4], y[5]), f2_to_h2(y[6], y[7])));
+                        }
+                        // a warp's second head is the later one: it is a k head whenever either is (warp-uniform test)
+                        if (ONE ? 2 * (warp * P + p) + 1 >= nh : __any_sync(CAM_FULL, on && !isq)) {
+                            const bool kv = on && !isq;
+                            uint8_t * kb = cw + (size_t)(kv ? hy - nh : 0) * 4 * 34 + (size_t)(l16 >> 3) * 34;
+                            const float klo[4] = {y[0], y[1], y[2], y[3]}, khi[4] = {y[4], y[5], y[6], y[7]};
+                            q8_0_store(klo, kb, l16 & 7, A.err, kv);
+                            q8_0_store(khi, kb + 2 * 34, l16 & 7, A.err, kv);
+                        }
+                    }
                 }
             }
         }
-        if (CACHE) {      // v: copied as fp16 into the row's V half
+        if (CACHE && Q8) {      // v: rounded to fp16, then Q8_0 blocks of 32: 8 lanes a block (whole warps: nkv 32 is a multiple of 32)
+            const float * vs = reinterpret_cast<const float *>(s) + (size_t)H * 128;
+            uint8_t * vb = cw + (size_t)nkv * 4 * 34;
+            for (int c = tid; c < nkv * 32; c += blockDim.x) {
+                const float4 v = *reinterpret_cast<const float4 *>(vs + 4 * c);
+                const float vv[4] = {f16r(v.x), f16r(v.y), f16r(v.z), f16r(v.w)};
+                q8_0_store(vv, vb + (size_t)(c >> 3) * 34, c & 7, A.err, true);
+            }
+        } else if (CACHE) {      // v: copied as fp16 into the row's V half
             const float * vs = reinterpret_cast<const float *>(s) + (size_t)H * 128;
             uint16_t * vo = kbase + (size_t)nkv * 128;
             for (int c = tid; c < nkv * 32; c += blockDim.x) {
@@ -212,16 +246,16 @@ void pick_shape(int H, int & warps, int & P) {
         }
 }
 
-template <typename T, bool CACHE, int P, bool ONE>
+template <typename T, bool CACHE, int P, bool ONE, bool Q8>
 int launch_rope_p(const RopeArgs & A, int warps, size_t smem, cudaStream_t stream) {
-    const cudaError_t e = cudaFuncSetAttribute(qk_rope_kernel<T, CACHE, P, ONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    const cudaError_t e = cudaFuncSetAttribute(qk_rope_kernel<T, CACHE, P, ONE, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
-    const int grid = cam_resident_grid(qk_rope_kernel<T, CACHE, P, ONE>, warps * 32, smem, A.n);
-    qk_rope_kernel<T, CACHE, P, ONE><<<grid, warps * 32, smem, stream>>>(A);
+    const int grid = cam_resident_grid(qk_rope_kernel<T, CACHE, P, ONE, Q8>, warps * 32, smem, A.n);
+    qk_rope_kernel<T, CACHE, P, ONE, Q8><<<grid, warps * 32, smem, stream>>>(A);
     return (int)cudaGetLastError();
 }
 
-template <typename T, bool CACHE>
+template <typename T, bool CACHE, bool Q8 = false>
 int launch_rope(const RopeArgs & A, cudaStream_t stream) {
     const int H = A.nh + A.nkv;
     const int in_heads = CACHE ? A.nh + 2 * A.nkv : H;
@@ -231,10 +265,10 @@ int launch_rope(const RopeArgs & A, cudaStream_t stream) {
     pick_shape(H, warps, P);
     const bool one = H == 2 * warps * P;
 #define CAM_ROPE_CASE(PV) \
-    case PV: return one ? launch_rope_p<T, CACHE, PV, true>(A, warps, smem, stream) : launch_rope_p<T, CACHE, PV, false>(A, warps, smem, stream);
+    case PV: return one ? launch_rope_p<T, CACHE, PV, true, Q8>(A, warps, smem, stream) : launch_rope_p<T, CACHE, PV, false, Q8>(A, warps, smem, stream);
     switch (P) {
         CAM_ROPE_CASE(1) CAM_ROPE_CASE(2) CAM_ROPE_CASE(3)
-        default: return one ? launch_rope_p<T, CACHE, 4, true>(A, warps, smem, stream) : launch_rope_p<T, CACHE, 4, false>(A, warps, smem, stream);
+        default: return one ? launch_rope_p<T, CACHE, 4, true, Q8>(A, warps, smem, stream) : launch_rope_p<T, CACHE, 4, false, Q8>(A, warps, smem, stream);
     }
 #undef CAM_ROPE_CASE
 }
@@ -260,7 +294,7 @@ static int qk_rope_entry(int n, const float * qkv, int ldq, int nh, int nkv, con
     if (!cam_aligned16(qkv) || (ldq & 3) || (reinterpret_cast<uintptr_t>(q16) & 7u) || (reinterpret_cast<uintptr_t>(cache) & 7u))
         return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
-    const RopeArgs A = {qkv, nullptr, par, (uint16_t *)q16, (uint16_t *)cache, ldq, nh, nkv, pos0, n, yarn};
+    const RopeArgs A = {qkv, nullptr, par, (uint16_t *)q16, (uint16_t *)cache, ldq, nh, nkv, pos0, n, yarn, nullptr};
     return launch_rope<float, true>(A, (cudaStream_t)stream);
 }
 extern "C" int q3p_qk_rope(int n, const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, void * q16, void * cache,
@@ -270,6 +304,28 @@ extern "C" int q3p_qk_rope(int n, const float * qkv, int ldq, int nh, int nkv, c
 extern "C" int q3p_qk_rope_yarn(int n, const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, void * q16,
                                 void * cache, void * stream) {
     return qk_rope_entry(n, qkv, ldq, nh, nkv, par, pos0, q16, cache, 1, stream);
+}
+
+// q3p_qk_rope_q8 / its YaRN object: as q3p_qk_rope with the cache a uint8 buffer of Q8_0 rows (2 * (nkv * 128 / 32) * 34 bytes per
+// position) and err an int32 word a refused block ORs 2 into. Replaces q3p_qk_rope_q8, kernels/q3m_prefill.hip:534-535 (objects
+// q3m_prefill_kvq8 and q3m_prefill_kvq8_yarn); wrapper python/caminus/prefill/q3m_ops.py:122-137.
+static int rope_q8_entry(int n, const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, void * q16, void * cache, int * err,
+                         int yarn, void * stream) {
+    if (n < 0 || nh < 1 || nkv < 1 || !qkv || !par || !q16 || !cache || !err || pos0 < 0 || ldq < (nh + 2 * nkv) * 128) return CAM_ERR_ARG;
+    if ((long)pos0 + n > (1L << 22)) return CAM_ERR_SHAPE;
+    if (!cam_aligned16(qkv) || (ldq & 3) || (reinterpret_cast<uintptr_t>(q16) & 7u) || (reinterpret_cast<uintptr_t>(cache) & 3u) ||
+        (reinterpret_cast<uintptr_t>(err) & 3u)) return CAM_ERR_ALIGN;
+    if (n == 0) return CAM_OK;
+    const RopeArgs A = {qkv, nullptr, par, (uint16_t *)q16, (uint16_t *)cache, ldq, nh, nkv, pos0, n, yarn, err};
+    return launch_rope<float, true, true>(A, (cudaStream_t)stream);
+}
+extern "C" int q3p_qk_rope_q8(int n, const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, void * q16, void * cache, int * err,
+                              void * stream) {
+    return rope_q8_entry(n, qkv, ldq, nh, nkv, par, pos0, q16, cache, err, 0, stream);
+}
+extern "C" int q3p_qk_rope_q8_yarn(int n, const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, void * q16, void * cache,
+                                   int * err, void * stream) {
+    return rope_q8_entry(n, qkv, ldq, nh, nkv, par, pos0, q16, cache, err, 1, stream);
 }
 
 // cam_qk_rope_f16: the same statements on fp16 q [n][nh][128] and k [n][nkv][128] (widened exactly), fp16 out (qo / ko may be
@@ -282,6 +338,6 @@ extern "C" int cam_qk_rope_f16(int n, const void * q, const void * k, int nh, in
     if (!q || !qo || (nkv > 0 && (!k || !ko))) return CAM_ERR_ARG;
     if (!cam_aligned16(q) || !cam_aligned16(qo) || (nkv > 0 && (!cam_aligned16(k) || !cam_aligned16(ko)))) return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
-    const RopeArgs A = {q, k, par, (uint16_t *)qo, (uint16_t *)ko, 0, nh, nkv, pos0, n, yarn};
+    const RopeArgs A = {q, k, par, (uint16_t *)qo, (uint16_t *)ko, 0, nh, nkv, pos0, n, yarn, nullptr};
     return launch_rope<uint16_t, false>(A, (cudaStream_t)stream);
 }

@@ -37,10 +37,56 @@ __global__ void __launch_bounds__(256) router_kernel(const float * __restrict__ 
     }
 }
 
-__global__ void __launch_bounds__(32) topk_kernel(const float * __restrict__ logits, int E, int k, float floor_, int * __restrict__ ids,
-                                                  float * __restrict__ wts, int * __restrict__ err) {
-    __shared__ int sel[64];
-    const int lane = threadIdx.x, t = blockIdx.x;
+// The same sums for many tokens: a warp holds TT tokens x EE experts (one accumulator per pair in every lane, the lanes
+// splitting K as above), so a step over 128 values of K costs TT + EE 16-byte loads for TT EE pairs instead of two per pair; the
+// 16 warps of a block take 16 EE experts of the same TT tokens, whose rows they share through L1. Per pair the statements and
+// their order are router_kernel's.
+template <int TT, int EE>
+__global__ void __launch_bounds__(512) router_tile_kernel(const float * __restrict__ h, const float * __restrict__ Wr, int E, int K,
+                                                          float * __restrict__ logits, int n) {
+    const int lane = threadIdx.x & 31, wave = threadIdx.x >> 5;
+    const int t0 = blockIdx.x * TT, e0 = (blockIdx.y * 16 + wave) * EE;
+    if (e0 >= E) return;
+    const float * xp[TT], * wp[EE];
+#pragma unroll
+    for (int i = 0; i < TT; i++) xp[i] = h + (size_t)min(t0 + i, n - 1) * K + lane * 4;       // (a tile's overhang recomputes the last row / expert)
+#pragma unroll
+    for (int j = 0; j < EE; j++) wp[j] = Wr + (size_t)min(e0 + j, E - 1) * K + lane * 4;
+    float acc[TT][EE];
+#pragma unroll
+    for (int i = 0; i < TT; i++)
+#pragma unroll
+        for (int j = 0; j < EE; j++) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += 128) {
+        float4 xv[TT], wv[EE];
+#pragma unroll
+        for (int i = 0; i < TT; i++) xv[i] = __ldg(reinterpret_cast<const float4 *>(xp[i] + k0));
+#pragma unroll
+        for (int j = 0; j < EE; j++) wv[j] = __ldg(reinterpret_cast<const float4 *>(wp[j] + k0));
+#pragma unroll
+        for (int i = 0; i < TT; i++)
+#pragma unroll
+            for (int j = 0; j < EE; j++) {
+                float d = fmul(wv[j].x, xv[i].x); d = ffma(wv[j].y, xv[i].y, d); d = ffma(wv[j].z, xv[i].z, d); d = ffma(wv[j].w, xv[i].w, d);
+                acc[i][j] = fadd(acc[i][j], d);
+            }
+    }
+    float mine = 0.0f;
+#pragma unroll
+    for (int i = 0; i < TT; i++)
+#pragma unroll
+        for (int j = 0; j < EE; j++) { const float v = wsum(acc[i][j]); if (lane == i * EE + j) mine = v; }      // (every lane holds the same total)
+    const int ti = t0 + lane / EE, ej = e0 + lane % EE;
+    if (lane < TT * EE && ti < n && ej < E) logits[(size_t)ti * E + ej] = mine;
+}
+
+// (a warp per token as in the reference, eight tokens to a block)
+__global__ void __launch_bounds__(256) topk_kernel(const float * __restrict__ logits, int E, int k, float floor_, int * __restrict__ ids,
+                                                   float * __restrict__ wts, int * __restrict__ err, int n) {
+    __shared__ int sel_[8][64];
+    const int lane = threadIdx.x & 31, t = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (t >= n) return;                                  // (whole warps; no block-wide barrier below)
+    int * sel = sel_[threadIdx.x >> 5];
     const float * lg = logits + (size_t)t * E;
     float v[4]; bool bad = false;
 #pragma unroll
@@ -115,14 +161,15 @@ extern "C" int q3p_router(int n, const float * h, const float * Wr, int E, int K
     if (n < 0 || E < 1 || K < 128 || (K & 127) || !h || !Wr || !logits) return CAM_ERR_ARG;
     if (!cam_aligned16(h) || !cam_aligned16(Wr)) return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
-    router_kernel<<<n, 256, 0, (cudaStream_t)stream>>>(h, Wr, E, K, logits);
+    if (n >= 64) router_tile_kernel<8, 4><<<dim3((n + 7) / 8, (E + 63) / 64), 512, 0, (cudaStream_t)stream>>>(h, Wr, E, K, logits, n);
+    else router_kernel<<<n, 256, 0, (cudaStream_t)stream>>>(h, Wr, E, K, logits);
     return (int)cudaGetLastError();
 }
 // q3p_topk: kernels/q3m_prefill.hip:440-441 (n = grid.x); E <= 128, k <= 32
 extern "C" int q3p_topk(int n, const float * logits, int E, int k, float floor_, int * ids, float * wts, int * err, void * stream) {
     if (n < 0 || E < 1 || E > 128 || k < 1 || k > 32 || k > E || !logits || !ids || !wts || !err) return CAM_ERR_ARG;
     if (n == 0) return CAM_OK;
-    topk_kernel<<<n, 32, 0, (cudaStream_t)stream>>>(logits, E, k, floor_, ids, wts, err);
+    topk_kernel<<<(n + 7) / 8, 256, 0, (cudaStream_t)stream>>>(logits, E, k, floor_, ids, wts, err, n);
     return (int)cudaGetLastError();
 }
 // q3p_group: kernels/q3m_prefill.hip:490-492; items are { int e, off, cnt, pad }; E <= 1024

@@ -18,23 +18,6 @@ namespace {
 
 constexpr int Q8_THREADS = 256;
 
-template <typename T> struct Load8;
-template <> struct Load8<float> {
-    static CAM_DEV void get(const float * p, float (&f)[8]) {
-        const float4 a = __ldg(reinterpret_cast<const float4 *>(p)), b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
-        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-    }
-    static CAM_DEV float one(const float * p) { return __ldg(p); }
-};
-template <> struct Load8<uint16_t> {
-    static CAM_DEV void get(const uint16_t * p, float (&f)[8]) {
-        const uint4 v = ldg128(p);
-        const float2 a = h2_to_f2(v.x), b = h2_to_f2(v.y), c = h2_to_f2(v.z), e = h2_to_f2(v.w);
-        f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = e.x; f[7] = e.y;
-    }
-    static CAM_DEV float one(const uint16_t * p) { return __half2float(__ushort_as_half(__ldg(p))); }
-};
-
 CAM_DEV int q8_code(float x, float d, float amax) {
     const float v = fdiv(x, d);
     return (amax != 0.0f && fabsf(v) < 127.5f) ? __float2int_rn(roundf(v)) : 0;   // (false for a NaN: code 0)
@@ -108,10 +91,6 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_1_kernel(const T * __restrict__
 // fast pass is the fp16 rounding of the same-order sum of the h^: it can differ from the exact statements' sum by one fp16
 // ulp (or by 1.6e-6 sum |h| when the values cancel). The reference reports that field and does not gate it
 // (tests/engine/golden_util.py:145-146); the strict kernel above gives its exact bytes too.
-// (.ftz: a denormal exponent argument counts as 0 and a denormal 2^a as 0; both are below 1e-38 beside the 1 they are added to)
-CAM_DEV float ex2_approx(float a) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
-CAM_DEV float rcp_approx(float a) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
-
 // one warp-wide step over 8 blocks (256 values) starting at group `base` (a multiple of 32). FULL: all 32 lanes have a group.
 template <typename T, bool FULL>
 CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y, int base, int ngroups, int lane) {

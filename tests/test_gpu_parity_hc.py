@@ -148,6 +148,44 @@ def test_mmq_q8_1(layout, rows, K):
     assert same(fused, gguf.quantize_mmq_q8_1(cu(h), layout))
 
 
+@pytest.mark.parametrize('dt', [np.float16, np.float32])
+@pytest.mark.parametrize('rows,K,kvalid', [(1, 128, 128), (3, 384, 384), (6, 640, 600), (13, 1024, 1024), (64, 2560, 2560)])
+def test_swiglu_mmq_hard_inputs(dt, rows, K, kvalid):
+    """the D4 fast pass: every byte is the exact statements' byte on inputs built to sit on its margins: duplicated and nearly
+    equal maxima, products on rounding boundaries, gates below -8, zero groups, tiny and huge values, NaN and infinities; odd
+    K-block counts, row counts that do not fill a warp's four rows, kvalid below K"""
+    from caminus_b200.engine import gguf
+    rng = np.random.default_rng(rows * 7 + K)
+    g = acts(rng, (rows, K), 1.5).astype(dt); u = acts(rng, (rows, K)).astype(dt)
+    r = np.arange(rows)
+    g[r, (r * 37) % K] = -9.5; g[r, (r * 11 + 5) % K] = 30.0
+    g[:, 32:40] = g[:, 40:48]; u[:, 32:40] = u[:, 40:48]                        # every value of these lanes twice: duplicated maxima
+    if K >= 384: g[:, 256:288] = 0; u[:, 300:310] = 0                          # a zero group
+    if K >= 640:
+        g[:, 512:544] = (g[:, 512:544].astype(np.float32) * 1e-3).astype(dt); u[:, 512:544] = (u[:, 512:544].astype(np.float32) * 1e-3).astype(dt)
+        u[:, 544:576] = 60000.0 if dt == np.float16 else 1e30
+    if rows > 2: g[2, 70] = np.nan; u[2, 100] = np.inf; g[1, 3] = np.inf
+    if dt == np.float32 and rows > 4: g[4, 200 % K] = 1e-40; u[4, 200 % K] = 3e38; g[3, :64] *= 1e-20
+    # halves of the maximum: codes on the .5 boundaries
+    h = oracle.swiglu_f32_from_f16(g.reshape(-1), u.reshape(-1)).reshape(rows, K) if dt == np.float16 else None
+    Kp = (K + 127) // 128 * 128
+    got = gguf.quantize_mmq_q8_1(cu(g), 'D4', u=cu(u), kvalid=kvalid)
+    assert same(got, oracle.mmq_q8_1(g, kvalid, Kp, 0, u=u))
+    if h is not None and kvalid == K: assert same(got, gguf.quantize_mmq_q8_1(cu(h), 'D4'))
+
+
+def test_swiglu_mmq_fast_equals_unfused_large():
+    """2048 x 25600 fp16 values: the fused D4 blocks equal the plain quantiser's over gg_silu_mul's fp32 products (both the exact
+    statements for every value), byte for byte"""
+    from caminus_b200.engine import gguf
+    gen = torch.Generator(device=DEV); gen.manual_seed(5)
+    T, K = 2048, 25600
+    g = (torch.randn(T, K, device=DEV, generator=gen) * 1.5).half(); u = torch.randn(T, K, device=DEV, generator=gen).half()
+    fused = gguf.quantize_mmq_q8_1(g, 'D4', u=u)
+    h = gguf.silu_mul(g.float().reshape(-1), u.float().reshape(-1)).reshape(T, K)
+    assert torch.equal(fused, gguf.quantize_mmq_q8_1(h, 'D4'))
+
+
 @pytest.mark.parametrize('M,K', [(1, 128), (37, 896), (300, 1024), (5, 8192)])
 def test_actq_family(M, K):
     """actq_fwd_*, silu_mul_actq_fwd, block_entry_fwd: values, scales and packed codes are the oracle's bytes; silu extremes and a
@@ -186,6 +224,11 @@ def test_router_topk_group():
     O.router(cu(hh), cu(Wr), E, D, lg, n)
     lo = oracle.router(hh, Wr)
     assert same(lg, lo)
+    for n2, E2, D2 in ((5, 128, 2048), (70, 61, 256), (64, 4, 128)):          # few tokens (a block per token); tiles that overhang n and E
+        h2 = g.standard_normal((n2, D2)).astype(np.float32); W2 = g.standard_normal((E2, D2)).astype(np.float32)
+        l2 = torch.zeros(n2, E2, device=DEV); hd, wd = cu(h2), cu(W2)
+        O.router(hd, wd, E2, D2, l2, n2)
+        assert same(l2, oracle.router(h2, W2))
     lo[3, 7] = lo[3, 9] = lo[3].max() + 1.0
     ids = torch.zeros(n * k, dtype=torch.int32, device=DEV); wts = torch.zeros(n * k, device=DEV); err = torch.zeros(1, dtype=torch.int32, device=DEV)
     O.topk(cu(lo), E, k, 6.103515625e-5, ids, wts, err, n)
@@ -221,13 +264,23 @@ def test_iq4_row_gathers(golden):
     m.ple_rows_iq4nl((1,), (256,), cu(R.reshape(-1)), cu(inv), I(nuniq), I(len(inv)), I(bpr), out, err)
     oo, eo = oracle.ple_rows_iq4nl(R, inv, nuniq, bpr)
     assert same(out, oo) and int(err.item()) == eo == 1 and same(out, f['nl'][np.clip(inv, 0, nuniq - 1)])
+    # tables at odd addresses take the byte-wise kernels: the same floats
+    Tb = torch.zeros(T.size + 16, dtype=torch.uint8, device=DEV); Tb[4:4 + T.size] = cu(T.reshape(-1))
+    o2 = torch.zeros(len(tok), nblk * 256, device=DEV)
+    m.embd_rows_iq4xs((1,), (256,), Tb[4:], cu(tok), I(vocab), I(len(tok)), I(nblk), o2, err)
+    assert same(o2, f['xs'][np.clip(tok, 0, vocab - 1)])
+    Rb = torch.zeros(R.size + 16, dtype=torch.uint8, device=DEV); Rb[1:1 + R.size] = cu(R.reshape(-1))
+    o3 = torch.zeros(len(inv), bpr * 32, device=DEV)
+    m.ple_rows_iq4nl((1,), (256,), Rb[1:], cu(inv), I(nuniq), I(len(inv)), I(bpr), o3, err)
+    assert same(o3, f['nl'][np.clip(inv, 0, nuniq - 1)])
 
 
-@pytest.mark.parametrize('R,K,wr', [(5, 2560, 1), (300, 2048, 4), (7, 320, 1)])
+@pytest.mark.parametrize('R,K,wr', [(5, 2560, 1), (300, 2048, 4), (7, 320, 1), (1000, 2560, 1), (601, 5120, 2)])
 def test_rms_mul_q8_1_copy(R, K, wr):
     """the norm that also emits the Q8_1 copy: the bytes of the plain quantiser run on the normed rows (fused == unfused)"""
     from caminus_b200 import lib
     g = np.random.default_rng(R + K); x = acts(g, (R, K), 3.0); w = (g.random((wr, K)) + 0.5).astype(np.float32)
+    x[R // 2] = 0; x[R // 3, 64:96] = 0; x[R // 4, 5] = 1e15; x[R - 1, :32] *= 1e-30       # a zero row, a zero block, a dominated row, a tiny block
     y = torch.zeros(R, K, device=DEV); yq = torch.zeros(R * K // 32 * 36, dtype=torch.uint8, device=DEV)
     xd, wd = cu(x), cu(w)      # (kept alive until the launch has run)
     lib.check(lib.load().cam_rms_mul_q8_1(xd.data_ptr(), wd.data_ptr(), y.data_ptr(), yq.data_ptr(), R, wr, 1e-6, K, torch.cuda.current_stream().cuda_stream))
