@@ -7,7 +7,10 @@
 // clamp(rint(u / s), -qmax - 1, qmax); outputs: the dequantised bf16 values (optional), the row scale, the int4 codes packed four
 // to 16 bits (optional). Sources: a bf16 or fp32 tensor; the MLP activation bf16(bf16(silu(g)) u) computed from [g | u] rows; the
 // RMSNorm (x rstd) w never materialised (block entry), which also emits up to 16 thin bf16 gate projections.
-// The mapping is the reference's (one block of 8 warps per row, warp w takes chunks w, w + 8, ..), so every reduction has its order.
+// Rows of up to 2048 values: a warp per row (the row's chunks in the warp's registers between the amax and the codes; no barrier):
+// the butterflies of a chunk are the reference's lane for lane, the row's amax is order-free, and the block entry's two ordered sums
+// (sum of squares, thin projections: thread tid owns tid + 256 j, wave butterflies, 8 wave sums in order) are reproduced on the warp
+// by ref_total_f32. Longer rows: the reference's mapping (one block of 8 warps per row, warp w takes chunks w, w + 8, ..).
 #include "cam_common.cuh"
 
 namespace {
@@ -22,6 +25,12 @@ CAM_DEV uint16_t f2bf(float f) {
     return (uint16_t)(u >> 16);
 }
 CAM_DEV float rbf(float f) { return bf2f(f2bf(f)); }
+// four values rounded to bf16 (the conversion instruction, two values at a time), and packed bf16 pairs widened again
+CAM_DEV uint2 pack4(const float (&v)[4]) { return make_uint2(bf16x2<true>(v[0], v[1]), bf16x2<true>(v[2], v[3])); }
+CAM_DEV void unpack4(uint2 p, float (&v)[4]) {
+    v[0] = __uint_as_float(p.x << 16); v[1] = __uint_as_float(p.x & 0xffff0000u); v[2] = __uint_as_float(p.y << 16); v[3] = __uint_as_float(p.y & 0xffff0000u);
+}
+CAM_DEV void rbf4(float (&v)[4]) { unpack4(pack4(v), v); }
 
 CAM_DEV void fwht128(float (&v)[4], int lane) {
     float a = v[0], b = v[1]; v[0] = fadd(a, b); v[1] = fsub(a, b);
@@ -54,14 +63,40 @@ CAM_DEV float block_reduce(float v, float * lds, int wave, int lane, bool is_max
     return r;
 }
 
-struct PlainBf16 { const uint16_t * x; int K; CAM_DEV float operator()(int row, int k) const { return bf2f(__ldg(x + (size_t)row * K + k)); } };
-struct PlainF32 { const float * x; int K; CAM_DEV float operator()(int row, int k) const { return __ldg(x + (size_t)row * K + k); } };
+CAM_DEV void bf4(uint2 w, float (&v)[4]) { v[0] = __uint_as_float(w.x << 16); v[1] = __uint_as_float(w.x & 0xffff0000u); v[2] = __uint_as_float(w.y << 16); v[3] = __uint_as_float(w.y & 0xffff0000u); }
+// get4: four consecutive values at k (a multiple of 4; rows 8-byte / 16-byte aligned: checked by the launcher)
+struct PlainBf16 {
+    const uint16_t * x; int K;
+    CAM_DEV float operator()(int row, int k) const { return bf2f(__ldg(x + (size_t)row * K + k)); }
+    CAM_DEV void get4(int row, int k, float (&v)[4]) const { bf4(__ldg(reinterpret_cast<const uint2 *>(x + (size_t)row * K + k)), v); }
+    static constexpr bool kBf16 = true;            // get4's values are bf16 numbers already
+};
+struct PlainF32 {
+    const float * x; int K;
+    CAM_DEV float operator()(int row, int k) const { return __ldg(x + (size_t)row * K + k); }
+    CAM_DEV void get4(int row, int k, float (&v)[4]) const {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(x + (size_t)row * K + k)); v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    }
+    static constexpr bool kBf16 = false;
+};
 struct SiluMulSrc {
     const uint16_t * gu; int ld, F;
     CAM_DEV float operator()(int row, int k) const {
         const uint16_t * r = gu + (size_t)row * ld;
         return rbf(fmul(rbf(cam_silu(bf2f(__ldg(r + k)))), bf2f(__ldg(r + F + k))));
     }
+    CAM_DEV void get4(int row, int k, float (&v)[4]) const {
+        const uint16_t * r = gu + (size_t)row * ld;
+        float g[4], u[4];
+        bf4(__ldg(reinterpret_cast<const uint2 *>(r + k)), g); bf4(__ldg(reinterpret_cast<const uint2 *>(r + F + k)), u);
+#pragma unroll
+        for (int e = 0; e < 4; e++) v[e] = cam_silu(g[e]);
+        rbf4(v);
+#pragma unroll
+        for (int e = 0; e < 4; e++) v[e] = fmul(v[e], u[e]);
+        rbf4(v);
+    }
+    static constexpr bool kBf16 = true;
 };
 struct RmsSrc {
     const float * x; const float * w; float rstd; int d;
@@ -79,29 +114,37 @@ CAM_DEV void actq_fwd_src(Src src, uint16_t * __restrict__ y, float * __restrict
         const int ch = wave + c * AQ_WAVES;
         if (ch < nch) {                                            // (uniform per warp)
 #pragma unroll
-            for (int e = 0; e < 4; e++) u[c][e] = rbf(src(row, ch * 128 + lane * 4 + e));
+            for (int e = 0; e < 4; e++) u[c][e] = src(row, ch * 128 + lane * 4 + e);
+            rbf4(u[c]);
             fwht128(u[c], lane);
 #pragma unroll
-            for (int e = 0; e < 4; e++) { u[c][e] = rbf(fmul(u[c][e], 0.08837890625f)); amax = fmaxf(amax, fabsf(u[c][e])); }
+            for (int e = 0; e < 4; e++) u[c][e] = fmul(u[c][e], 0.08837890625f);
+            rbf4(u[c]);
+#pragma unroll
+            for (int e = 0; e < 4; e++) amax = fmaxf(amax, fabsf(u[c][e]));
         }
     }
     amax = block_reduce(wave_max(amax), lds, wave, lane, true);
     const float s = fmaxf(fdiv(fmul(amax, clip), (float)qmax), 1e-8f);
     if (threadIdx.x == 0 && s_out) s_out[row] = s;
+    const float inv = rcp_approx(s);
+    const float inv_hi = fmul(inv, 0x1.000008p+0f), inv_lo = fmul(inv, 0x1.fffff0p-1f);
+    const bool fast = s < 3.0e38f && fmul(amax, inv) < 4.0e6f;
     uint16_t * yr = y ? y + (size_t)row * K : nullptr;
 #pragma unroll
     for (int c = 0; c < AQ_MAXC; c++) {
         const int ch = wave + c * AQ_WAVES;
         if (ch < nch) {
-            uint32_t pk = 0;
-            uint16_t o[4];
+            float q[4];
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float q = fminf(fmaxf(rintf(fdiv(u[c][e], s)), (float)(-qmax - 1)), (float)qmax);
-                o[e] = f2bf(fmul(q, s));
-                pk |= ((uint32_t)(int)q & 0xFu) << (4 * e);
+            for (int e = 0; e < 4; e++) {       // (the division-free rint of actq_emit below)
+                const float vh = ffma(u[c][e], inv_hi, 12582912.0f), vl = ffma(u[c][e], inv_lo, 12582912.0f);
+                q[e] = __uint_as_float(__float_as_uint(fsub(vh, 12582912.0f)) | (__float_as_uint(u[c][e]) & 0x80000000u));
+                if (!fast || vh != vl) q[e] = rintf(fdiv(u[c][e], s));
+                q[e] = fminf(fmaxf(q[e], (float)(-qmax - 1)), (float)qmax);
             }
-            if (y) st64(yr + ch * 128 + lane * 4, make_uint2(o[0] | ((uint32_t)o[1] << 16), o[2] | ((uint32_t)o[3] << 16)));
+            const uint32_t pk = ((uint32_t)(int)q[0] & 0xFu) | (((uint32_t)(int)q[1] & 0xFu) << 4) | (((uint32_t)(int)q[2] & 0xFu) << 8) | (((uint32_t)(int)q[3] & 0xFu) << 12);
+            if (y) st64(yr + ch * 128 + lane * 4, make_uint2(bf16x2<true>(fmul(q[0], s), fmul(q[1], s)), bf16x2<true>(fmul(q[2], s), fmul(q[3], s))));
             if (codes) codes[(size_t)row * (K / 4) + ch * 32 + lane] = (uint16_t)pk;
         }
     }
@@ -148,6 +191,140 @@ __global__ void __launch_bounds__(256) block_entry_kernel(const float * __restri
     }
 }
 
+// ---- a warp per row (K <= 128 MAXC) ---------------------------------------------------------------------------------------------
+// the codes, values and scale of a row whose transformed chunks u[c] (c < nch) are in the warp's registers
+template <int MAXC>
+CAM_DEV void actq_emit(const uint2 (&up)[MAXC], float amax, int nch, int row, int lane, uint16_t * __restrict__ y, float * __restrict__ s_out, int K,
+                       float clip, int qmax, uint16_t * __restrict__ codes) {
+    amax = wave_max(amax);
+    const float s = fmaxf(fdiv(fmul(amax, clip), (float)qmax), 1e-8f);
+    if (lane == 0 && s_out) s_out[row] = s;
+    const float lo = (float)(-qmax - 1), hi = (float)qmax;
+    // rint(u / s) without the division where that is provably the same integer: u * rcp(s) is within 1.8e-7 |t| of the IEEE quotient
+    // t; if u * rcp(s) (1 - 4.8e-7) and u * rcp(s) (1 + 4.8e-7) round to one integer, no rounding boundary and no tie lies between
+    // them, and that integer is rint(t). Otherwise (and for a row whose scale is not an ordinary number) the value is divided.
+    const float inv = rcp_approx(s);
+    const float inv_hi = fmul(inv, 0x1.000008p+0f), inv_lo = fmul(inv, 0x1.fffff0p-1f);
+    const bool fast = s < 3.0e38f && fmul(amax, inv) < 4.0e6f;                 // (s >= 1e-8; false for a NaN)
+#pragma unroll
+    for (int c = 0; c < MAXC; c++)
+        if (c < nch) {
+            float q[4], u[4];
+            unpack4(up[c], u);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float vh = ffma(u[e], inv_hi, 12582912.0f), vl = ffma(u[e], inv_lo, 12582912.0f);
+                q[e] = __uint_as_float(__float_as_uint(fsub(vh, 12582912.0f)) | (__float_as_uint(u[e]) & 0x80000000u));     // (rint keeps the sign of a zero)
+                if (!fast || vh != vl) q[e] = rintf(fdiv(u[e], s));
+                q[e] = fminf(fmaxf(q[e], lo), hi);
+            }
+            const uint32_t pk = ((uint32_t)(int)q[0] & 0xFu) | (((uint32_t)(int)q[1] & 0xFu) << 4) | (((uint32_t)(int)q[2] & 0xFu) << 8) | (((uint32_t)(int)q[3] & 0xFu) << 12);
+            if (y) st64_stream(y + (size_t)row * K + c * 128 + lane * 4, make_uint2(bf16x2<true>(fmul(q[0], s), fmul(q[1], s)), bf16x2<true>(fmul(q[2], s), fmul(q[3], s))));
+            if (codes) codes[(size_t)row * (K / 4) + c * 32 + lane] = (uint16_t)pk;
+        }
+}
+
+template <typename Src, int MAXC>
+__global__ void __launch_bounds__(256) actq_rows_kernel(Src src, uint16_t * __restrict__ y, float * __restrict__ s_out, int K, float clip, int qmax,
+                                                        uint16_t * __restrict__ codes, int M) {
+    const int lane = threadIdx.x & 31, nch = K >> 7;
+    for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < M; row += gridDim.x * 8) {
+        uint2 up[MAXC];                                                   // the row's transformed values, bf16 pairs
+        float amax = 0.f;
+#pragma unroll
+        for (int c0 = 0; c0 < MAXC; c0 += 8) {                           // eight chunks' loads in flight at a time
+            float u[8][4];
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                if (c0 + c < nch) src.get4(row, (c0 + c) * 128 + lane * 4, u[c]);
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                if (c0 + c < nch) {
+                    if (!Src::kBf16) rbf4(u[c]);
+                    fwht128(u[c], lane);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) u[c][e] = fmul(u[c][e], 0.08837890625f);
+                    up[c0 + c] = pack4(u[c]);
+                    unpack4(up[c0 + c], u[c]);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) amax = fmaxf(amax, fabsf(u[c][e]));
+                }
+        }
+        actq_emit<MAXC>(up, amax, nch, row, lane, y, s_out, K, clip, qmax, codes);
+    }
+}
+
+template <int MAXC>
+__global__ void __launch_bounds__(256) block_entry_rows_kernel(const float * __restrict__ x, const float * __restrict__ nw, const uint16_t * __restrict__ wab,
+                                                               int nab, float eps, uint16_t * __restrict__ y, float * __restrict__ s_out,
+                                                               uint16_t * __restrict__ codes, uint16_t * __restrict__ ab, float * __restrict__ rstd_out,
+                                                               int d, float clip, int qmax, int M) {
+    const int lane = threadIdx.x & 31, nch = d >> 7;
+    for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < M; row += gridDim.x * 8) {
+        float u[MAXC][4];
+        const float * xr = x + (size_t)row * d + lane * 4;
+#pragma unroll
+        for (int c = 0; c < MAXC; c++)
+            if (c < nch) { const float4 a = __ldg(reinterpret_cast<const float4 *>(xr + c * 128)); u[c][0] = a.x; u[c][1] = a.y; u[c][2] = a.z; u[c][3] = a.w; }
+        float a8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < MAXC; c++)
+            if (c < nch) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) a8[4 * (c & 1) + e] = ffma(u[c][e], u[c][e], a8[4 * (c & 1) + e]);
+            }
+        const float rstd = cam_rsqrt(fadd(fdiv(ref_total_f32(a8, lane), (float)d), eps));
+        if (lane == 0) rstd_out[row] = rstd;
+        // hb = bf16((x rstd) w): the quantiser's source and the projections' operand
+#pragma unroll
+        for (int c = 0; c < MAXC; c++)
+            if (c < nch) {
+                const float4 w4 = __ldg(reinterpret_cast<const float4 *>(nw + c * 128 + lane * 4));
+                u[c][0] = fmul(fmul(u[c][0], rstd), w4.x); u[c][1] = fmul(fmul(u[c][1], rstd), w4.y);
+                u[c][2] = fmul(fmul(u[c][2], rstd), w4.z); u[c][3] = fmul(fmul(u[c][3], rstd), w4.w);
+                rbf4(u[c]);
+            }
+        for (int j = 0; j < nab; j++) {
+            const uint16_t * wr = wab + (size_t)j * d + lane * 4;
+            float p8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < MAXC; c++)
+                if (c < nch) {
+                    float wv[4];
+                    bf4(__ldg(reinterpret_cast<const uint2 *>(wr + c * 128)), wv);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) p8[4 * (c & 1) + e] = ffma(u[c][e], wv[e], p8[4 * (c & 1) + e]);
+                }
+            const float tot = ref_total_f32(p8, lane);
+            if (lane == 0) ab[(size_t)row * nab + j] = f2bf(tot);
+        }
+        float amax = 0.f;
+        uint2 up[MAXC];
+#pragma unroll
+        for (int c = 0; c < MAXC; c++)
+            if (c < nch) {
+                fwht128(u[c], lane);
+#pragma unroll
+                for (int e = 0; e < 4; e++) u[c][e] = fmul(u[c][e], 0.08837890625f);
+                up[c] = pack4(u[c]);
+                unpack4(up[c], u[c]);
+#pragma unroll
+                for (int e = 0; e < 4; e++) amax = fmaxf(amax, fabsf(u[c][e]));
+            }
+        actq_emit<MAXC>(up, amax, nch, row, lane, y, s_out, d, clip, qmax, codes);
+    }
+}
+
+// the warp-per-row launch when the row fits (K <= 2048) and its loads are aligned; false: the caller uses the block-per-row kernel
+template <typename Src>
+bool launch_actq_rows(Src src, bool aligned, int M, uint16_t * y, float * s, int K, float clip, int qmax, uint16_t * codes, cudaStream_t stream) {
+    if (!aligned || K > 2048) return false;
+    const long want = ((long)M + 7) / 8;
+    if (K <= 1024) actq_rows_kernel<Src, 8><<<cam_resident_grid(actq_rows_kernel<Src, 8>, 256, 0, want), 256, 0, stream>>>(src, y, s, K, clip, qmax, codes, M);
+    else actq_rows_kernel<Src, 16><<<cam_resident_grid(actq_rows_kernel<Src, 16>, 256, 0, want), 256, 0, stream>>>(src, y, s, K, clip, qmax, codes, M);
+    return true;
+}
+
 int check_actq(int M, int K, int qmax, const void * x, const void * s) {
     if (M < 0 || K < 128 || (K & 127) || K > AQ_WAVES * AQ_MAXC * 128 || qmax < 1 || qmax > 7 || !x || !s) return CAM_ERR_ARG;
     return CAM_OK;
@@ -163,13 +340,15 @@ bool misaligned8(const void * p) { return p && (reinterpret_cast<uintptr_t>(p) &
 extern "C" int actq_fwd_codes_bf16(int M, const void * x, void * y, float * s, void * codes, int K, float clip, int qmax, void * stream) {
     const int r = check_actq(M, K, qmax, x, s); if (r || M == 0) return r;
     if (misaligned8(y)) return CAM_ERR_ALIGN;
-    actq_kernel<<<M, 256, 0, CAM_ST>>>(PlainBf16{(const uint16_t *)x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
+    if (!launch_actq_rows(PlainBf16{(const uint16_t *)x, K}, !misaligned8(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST))
+        actq_kernel<<<M, 256, 0, CAM_ST>>>(PlainBf16{(const uint16_t *)x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
     return (int)cudaGetLastError();
 }
 extern "C" int actq_fwd_codes_f32(int M, const float * x, void * y, float * s, void * codes, int K, float clip, int qmax, void * stream) {
     const int r = check_actq(M, K, qmax, x, s); if (r || M == 0) return r;
     if (misaligned8(y)) return CAM_ERR_ALIGN;
-    actq_kernel<<<M, 256, 0, CAM_ST>>>(PlainF32{x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
+    if (!launch_actq_rows(PlainF32{x, K}, cam_aligned16(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST))
+        actq_kernel<<<M, 256, 0, CAM_ST>>>(PlainF32{x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
     return (int)cudaGetLastError();
 }
 extern "C" int actq_fwd_bf16(int M, const void * x, void * y, float * s, int K, float clip, int qmax, void * stream) {
@@ -184,7 +363,8 @@ extern "C" int silu_mul_actq_fwd(int M, const void * gu, int ld, int F, void * y
     if (ld < 2 * F) return CAM_ERR_ARG;
     if (misaligned8(y)) return CAM_ERR_ALIGN;
     if (M == 0) return CAM_OK;
-    actq_kernel<<<M, 256, 0, CAM_ST>>>(SiluMulSrc{(const uint16_t *)gu, ld, F}, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes);
+    if (!launch_actq_rows(SiluMulSrc{(const uint16_t *)gu, ld, F}, !misaligned8(gu) && !(ld & 3), M, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes, CAM_ST))
+        actq_kernel<<<M, 256, 0, CAM_ST>>>(SiluMulSrc{(const uint16_t *)gu, ld, F}, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes);
     return (int)cudaGetLastError();
 }
 // block_entry_fwd: kernels/actq.hip:247-249 (M = grid.x); wrapper python/caminus/train/actq.py:131-151. d <= 1024 in the reference's
@@ -195,6 +375,11 @@ extern "C" int block_entry_fwd(int M, const float * x, const float * nw, const v
     if (!nw || !rstd_out || nab < 0 || nab > AQ_NAB || (nab && (!wab || !ab))) return CAM_ERR_ARG;
     if (misaligned8(y)) return CAM_ERR_ALIGN;
     if (M == 0) return CAM_OK;
-    block_entry_kernel<<<M, 256, 0, CAM_ST>>>(x, nw, (const uint16_t *)wab, nab, eps, (uint16_t *)y, s, (uint16_t *)codes, (uint16_t *)ab, rstd_out, d, clip, qmax);
+    if (d <= 1024 && cam_aligned16(x) && cam_aligned16(nw) && !misaligned8(wab)) {
+        const long want = ((long)M + 7) / 8;
+        block_entry_rows_kernel<8><<<cam_resident_grid(block_entry_rows_kernel<8>, 256, 0, want), 256, 0, CAM_ST>>>(
+            x, nw, (const uint16_t *)wab, nab, eps, (uint16_t *)y, s, (uint16_t *)codes, (uint16_t *)ab, rstd_out, d, clip, qmax, M);
+    } else
+        block_entry_kernel<<<M, 256, 0, CAM_ST>>>(x, nw, (const uint16_t *)wab, nab, eps, (uint16_t *)y, s, (uint16_t *)codes, (uint16_t *)ab, rstd_out, d, clip, qmax);
     return (int)cudaGetLastError();
 }

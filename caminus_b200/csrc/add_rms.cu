@@ -19,23 +19,7 @@
 namespace {
 
 // ---- the reference's reduction on this file's two layouts ------------------------------------------------------------------
-// fp32 layout: a[c + 4 b] (c < 4, b < 2). Returns the workgroup total (every lane).
-CAM_DEV float ref_total_f32(float (&a)[8], int lane) {
-#pragma unroll
-    for (int o = 4; o > 0; o >>= 1)
-#pragma unroll
-        for (int k = 0; k < 8; k++) a[k] = fadd(a[k], __shfl_xor_sync(CAM_FULL, a[k], o));
-    float P[2];
-#pragma unroll
-    for (int b = 0; b < 2; b++) {
-        const float t0 = fadd(a[4 * b + 0], a[4 * b + 2]), t1 = fadd(a[4 * b + 1], a[4 * b + 3]);   // partner 2
-        P[b] = fadd(t0, t1);                                                                        // partner 1
-    }
-    float tot = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 8; w++) tot = fadd(tot, __shfl_sync(CAM_FULL, P[w >> 2], 8 * (w & 3)));    // wave w: lanes 8 (w & 3) .., b = w >> 2
-    return tot;
-}
+// (ref_total_f32, the fp32 layout's reduction, is in cam_common.cuh: the training line's block entry uses it too)
 // fp16 layout: a[c] (c < 8)
 CAM_DEV float ref_total_f16(float (&a)[8], int lane) {
 #pragma unroll

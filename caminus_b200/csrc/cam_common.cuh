@@ -85,6 +85,22 @@ CAM_DEV uint32_t f2_to_h2(float a, float b) {
 }
 CAM_DEV uint16_t f_to_h(float a) { return __half_as_ushort(__float2half_rn(a)); }
 
+// ---- fp32 -> bf16, round to nearest even, two at a time (lo in the low half) ---------------------------------------------------
+// The reference's integer statements, u + 0x7fff + ((u >> 16) & 1), are IEEE round-to-nearest-even for every number, which is what
+// the conversion instruction does. For a NaN operand the integer statements decide the bits: NANQ true: 0x7fc0 (the training
+// line's f2bf, kernels/actq.hip:23-28, kernels/core.hip); false: the carry may turn a NaN into an infinity (prefill_glue's to_bf16).
+template <bool NANQ> CAM_DEV uint32_t bf16_soft(float f) {
+    uint32_t u = __float_as_uint(f);
+    if (NANQ && (u & 0x7fffffffu) > 0x7f800000u) return 0x7fc0u;
+    return (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+}
+template <bool NANQ> CAM_DEV uint32_t bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    if (lo != lo || hi != hi) r = bf16_soft<NANQ>(lo) | (bf16_soft<NANQ>(hi) << 16);
+    return r;
+}
+
 // ---- 128-bit global accesses ------------------------------------------------------------------------------------------
 CAM_DEV uint4 ldg128(const void * p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }          // read-only data
 CAM_DEV uint4 ld128(const void * p) { return *reinterpret_cast<const uint4 *>(p); }                 // data this kernel also writes
@@ -116,6 +132,28 @@ template <> struct Load8<uint16_t> {
 CAM_DEV float ex2_approx(float a) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
 CAM_DEV float rcp_approx(float a) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
 
+
+// ---- the reference's 256-thread sum on a warp: thread tid owns elements tid + 256 j (an fma chain over j), the 32 lanes of a wave
+// add by the xor butterfly 16, 8, 4, 2, 1, the 8 wave sums are added in order. Here lane l holds elements 128 m + 4 l + c, i.e.
+// thread 128 (m & 1) + 4 l + c with j = m >> 1: accumulator a[c + 4 (m & 1)]; partners 16, 8, 4 are lanes l ^ 4, 2, 1, partners 2, 1
+// are inside the lane; wave w is lanes 8 (w & 3) .. with b = w >> 2.
+// a[c + 4 b] (c < 4, b < 2). Returns the workgroup total (every lane).
+CAM_DEV float ref_total_f32(float (&a)[8], int lane) {
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1)
+#pragma unroll
+        for (int k = 0; k < 8; k++) a[k] = fadd(a[k], __shfl_xor_sync(CAM_FULL, a[k], o));
+    float P[2];
+#pragma unroll
+    for (int b = 0; b < 2; b++) {
+        const float t0 = fadd(a[4 * b + 0], a[4 * b + 2]), t1 = fadd(a[4 * b + 1], a[4 * b + 3]);   // partner 2
+        P[b] = fadd(t0, t1);                                                                        // partner 1
+    }
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) tot = fadd(tot, __shfl_sync(CAM_FULL, P[w >> 2], 8 * (w & 3)));    // wave w: lanes 8 (w & 3) .., b = w >> 2
+    return tot;
+}
 
 // ---- cp.async (16 bytes per thread, L2 only) with commit / wait groups --------------------------------------------------------
 CAM_DEV void cp_async16(void * smem, const void * gmem) {

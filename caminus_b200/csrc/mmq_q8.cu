@@ -14,55 +14,134 @@
 namespace {
 
 // MODE 0: values = x (fp32). MODE 1: silu(x) * u (fp32). MODE 2: silu(g) * u (fp16 in).
+// what a lane loads for its four values of one task (held raw so that two tasks' loads fly together)
+template <int MODE> struct MmqRaw { float4 a, b; };
+template <> struct MmqRaw<2> { uint2 a, b; };
+
+// a lane's four values of K-block kb of row r
+template <int MODE>
+CAM_DEV MmqRaw<MODE> mmq_load(const void * __restrict__ xv, const void * __restrict__ uv, int kb, int r, int kvalid, long ld, int lane, bool & in) {
+    const int k = kb * 128 + 4 * lane;
+    MmqRaw<MODE> raw;
+    in = k < kvalid;            // (kvalid and ld are multiples of 4: a lane's four values are all inside or all outside)
+    if (in) {
+        if constexpr (MODE == 2) {
+            raw.a = __ldg(reinterpret_cast<const uint2 *>((const uint16_t *)xv + (size_t)r * ld + k));
+            raw.b = __ldg(reinterpret_cast<const uint2 *>((const uint16_t *)uv + (size_t)r * ld + k));
+        } else {
+            raw.a = __ldg(reinterpret_cast<const float4 *>((const float *)xv + (size_t)r * ld + k));
+            if constexpr (MODE == 1) raw.b = __ldg(reinterpret_cast<const float4 *>((const float *)uv + (size_t)r * ld + k));
+        }
+    }
+    return raw;
+}
+CAM_DEV void mmq_values(const MmqRaw<0> & raw, float (&v)[4]) { v[0] = raw.a.x; v[1] = raw.a.y; v[2] = raw.a.z; v[3] = raw.a.w; }
+CAM_DEV void mmq_values(const MmqRaw<1> & raw, float (&v)[4]) {
+    v[0] = fmul(cam_silu(raw.a.x), raw.b.x); v[1] = fmul(cam_silu(raw.a.y), raw.b.y);
+    v[2] = fmul(cam_silu(raw.a.z), raw.b.z); v[3] = fmul(cam_silu(raw.a.w), raw.b.w);
+}
+CAM_DEV void mmq_values(const MmqRaw<2> & raw, float (&v)[4]) {
+    const float2 g0 = h2_to_f2(raw.a.x), g1 = h2_to_f2(raw.a.y), u0 = h2_to_f2(raw.b.x), u1 = h2_to_f2(raw.b.y);
+    v[0] = fmul(cam_silu(g0.x), u0.x); v[1] = fmul(cam_silu(g0.y), u0.y);
+    v[2] = fmul(cam_silu(g1.x), u1.x); v[3] = fmul(cam_silu(g1.y), u1.y);
+}
+
+// the lane's code word and (in lanes 0, 8, 16, 24) the group's scale word
+template <int LAYOUT>
+CAM_DEV void mmq_quant(const float (&v)[4], uint32_t & w, uint32_t & hdr) {
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    float sum = fadd(fadd(fadd(v[0], v[1]), v[2]), v[3]);
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, o));
+        if (LAYOUT == 1) sum = fadd(sum, __shfl_xor_sync(CAM_FULL, sum, o));
+    }
+    float d = 0.0f;
+    w = 0;
+    if (amax != 0.0f) {
+        const float d_inv = fdiv(127.0f, amax);
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const float t = fmul(v[c], d_inv);
+            const int q = fabsf(t) < 127.5f ? __float2int_rn(roundf(t)) : 0;
+            w |= (uint32_t)(q & 0xff) << (8 * c);
+        }
+        d = fdiv(1.0f, d_inv);
+    }
+    hdr = LAYOUT == 0 ? __float_as_uint(d) : f2_to_h2(d, sum);
+}
+CAM_DEV void mmq_write(uint8_t * __restrict__ blk, int lane, uint32_t w, uint32_t hdr) {
+    __stcs(reinterpret_cast<uint32_t *>(blk + 16) + lane, w);
+    if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = hdr;
+}
+template <int LAYOUT>
+CAM_DEV void mmq_block(const float (&v)[4], uint8_t * __restrict__ blk, int lane) {
+    uint32_t w, hdr;
+    mmq_quant<LAYOUT>(v, w, hdr);
+    mmq_write(blk, lane, w, hdr);
+}
+
+// The indexed forms of the reference's quantiser (kernels/ggml_mmq/quantize_mmq.cuh:41-140; wrappers
+// python/caminus/prefill/mmq.py:245-281). Gather (SCATTER false): column c of y = row ids[c] of x (ids null: row c).
+// Scatter: row t of x is quantised once and written to the k columns ids[t k + slot] of y (ncols columns in all).
+// An index outside its range is clamped (the reference's host code builds them in range).
+template <int LAYOUT, bool SCATTER>
+__global__ void __launch_bounds__(256) mmq_q8_1_rows_kernel(const float * __restrict__ x, const int * __restrict__ ids, uint8_t * __restrict__ y,
+                                                            int kvalid, int nkb, long ld, int nrows, int k, int ncols) {
+    const int lane = threadIdx.x & 31;
+    for (int kb = blockIdx.y * 8 + (threadIdx.x >> 5); kb < nkb; kb += gridDim.y * 8)
+    for (int r = blockIdx.x; r < nrows; r += gridDim.x) {
+        const int kk = kb * 128 + 4 * lane;
+        int src = r;
+        if (!SCATTER && ids) src = min(max(__ldg(ids + r), 0), nrows - 1);
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (kk < kvalid) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(x + (size_t)src * ld + kk));
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        }
+        uint32_t w, hdr;
+        mmq_quant<LAYOUT>(v, w, hdr);
+        if (!SCATTER) mmq_write(y + ((size_t)kb * nrows + r) * 144, lane, w, hdr);
+        else
+            for (int slot = 0; slot < k; slot++) {
+                const int c = min(max(__ldg(ids + (size_t)r * k + slot), 0), ncols - 1);
+                mmq_write(y + ((size_t)kb * ncols + c) * 144, lane, w, hdr);
+            }
+    }
+}
+
+// grid.x walks the rows, grid.y groups of 8 K-blocks (one per warp): a block reads 4 KB of a row; two rows per pass, both rows'
+// loads issued before either is used. (No index is divided: a 64-bit division per task costs more than the task's arithmetic.)
 template <int MODE, int LAYOUT>
 __global__ void __launch_bounds__(256) mmq_q8_1_kernel(const void * __restrict__ xv, const void * __restrict__ uv, uint8_t * __restrict__ y,
                                                        int kvalid, int nkb, long ld, int rows) {
     const int lane = threadIdx.x & 31;
-    const long total = (long)nkb * rows;
-    for (long task = (long)blockIdx.x * 8 + (threadIdx.x >> 5); task < total; task += (long)gridDim.x * 8) {
-        const int kb = (int)(task / rows), r = (int)(task - (long)kb * rows);
-        const int k = kb * 128 + 4 * lane;
-        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (k < kvalid) {       // (kvalid and ld are multiples of 4: a lane's four values are all inside or all outside)
-            if (MODE == 2) {
-                const uint2 g = __ldg(reinterpret_cast<const uint2 *>((const uint16_t *)xv + (size_t)r * ld + k));
-                const uint2 u = __ldg(reinterpret_cast<const uint2 *>((const uint16_t *)uv + (size_t)r * ld + k));
-                const float2 g0 = h2_to_f2(g.x), g1 = h2_to_f2(g.y), u0 = h2_to_f2(u.x), u1 = h2_to_f2(u.y);
-                v[0] = fmul(cam_silu(g0.x), u0.x); v[1] = fmul(cam_silu(g0.y), u0.y);
-                v[2] = fmul(cam_silu(g1.x), u1.x); v[3] = fmul(cam_silu(g1.y), u1.y);
-            } else {
-                const float4 a = __ldg(reinterpret_cast<const float4 *>((const float *)xv + (size_t)r * ld + k));
-                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-                if (MODE == 1) {
-                    const float4 b = __ldg(reinterpret_cast<const float4 *>((const float *)uv + (size_t)r * ld + k));
-                    v[0] = fmul(cam_silu(v[0]), b.x); v[1] = fmul(cam_silu(v[1]), b.y);
-                    v[2] = fmul(cam_silu(v[2]), b.z); v[3] = fmul(cam_silu(v[3]), b.w);
-                }
+    for (int kb = blockIdx.y * 8 + (threadIdx.x >> 5); kb < nkb; kb += gridDim.y * 8) {
+        for (int r = blockIdx.x; r < rows; r += 2 * gridDim.x) {
+            const int r2 = r + gridDim.x;
+            bool in0, in1 = false;
+            const MmqRaw<MODE> a0 = mmq_load<MODE>(xv, uv, kb, r, kvalid, ld, lane, in0);
+            MmqRaw<MODE> a1;
+            if (r2 < rows) a1 = mmq_load<MODE>(xv, uv, kb, r2, kvalid, ld, lane, in1);
+            float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (in0) mmq_values(a0, v);
+            mmq_block<LAYOUT>(v, y + ((size_t)kb * rows + r) * 144, lane);
+            if (r2 < rows) {
+                float v1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (in1) mmq_values(a1, v1);
+                mmq_block<LAYOUT>(v1, y + ((size_t)kb * rows + r2) * 144, lane);
             }
         }
-        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-        float sum = fadd(fadd(fadd(v[0], v[1]), v[2]), v[3]);
-#pragma unroll
-        for (int o = 4; o > 0; o >>= 1) {
-            amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, o));
-            sum = fadd(sum, __shfl_xor_sync(CAM_FULL, sum, o));
-        }
-        float d = 0.0f;
-        uint32_t w = 0;
-        if (amax != 0.0f) {
-            const float d_inv = fdiv(127.0f, amax);
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                const float t = fmul(v[c], d_inv);
-                const int q = fabsf(t) < 127.5f ? __float2int_rn(roundf(t)) : 0;
-                w |= (uint32_t)(q & 0xff) << (8 * c);
-            }
-            d = fdiv(1.0f, d_inv);
-        }
-        uint8_t * blk = y + (size_t)task * 144;
-        reinterpret_cast<uint32_t *>(blk + 16)[lane] = w;
-        if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = LAYOUT == 0 ? __float_as_uint(d) : f2_to_h2(d, sum);
     }
+}
+
+// the 2-D persistent grid of the kernels here: x over `nx` units, y over `ny`, together at most the resident blocks
+template <typename K>
+static dim3 mmq_grid(K kernel, long nx, long ny) {
+    const long cap = cam_resident_grid(kernel, 256, 0, 1L << 40);
+    const long gx = nx < cap ? (nx < 1 ? 1 : nx) : cap;
+    long gy = cap / gx; if (gy < 1) gy = 1; if (gy > ny) gy = ny;
+    return dim3((unsigned)gx, (unsigned)gy);
 }
 
 // ---- SwiGLU into D4 blocks at memory speed: a fast pass with proof margins, exact recomputation where a margin is not met ---
@@ -120,9 +199,8 @@ template <> struct Raw8<float> {
 struct MmqTask {
     int r0, kb, k;
     bool kon, kin;
-    CAM_DEV MmqTask(long task, int nrq, int lane, int nkb, int kvalid) {
-        const int kp = (int)(task / nrq);
-        r0 = (int)(task - (long)kp * nrq) * 4;
+    CAM_DEV MmqTask(int kp, int rq, int lane, int nkb, int kvalid) {
+        r0 = rq * 4;
         kb = kp * 2 + (lane >> 4); k = kb * 128 + (lane & 15) * 8;
         kon = kb < nkb; kin = kon && k < kvalid;
     }
@@ -143,16 +221,20 @@ template <typename T, bool PF>
 __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y,
                                                                  int kvalid, int nkb, long ld, int rows) {
     const int lane = threadIdx.x & 31, qb = lane & 28, qi = lane & 3;
-    const int nrq = (rows + 3) >> 2;
-    const long total = (long)((nkb + 1) >> 1) * nrq, stride = (long)gridDim.x * 8;
-    long task = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (task >= total) return;
+    // grid.x walks groups of four rows (8 per block, one per warp), grid.y the pairs of K-blocks; no index is divided
+    const int nrq = (rows + 3) >> 2, nkp = (nkb + 1) >> 1;
+    const int rq0 = blockIdx.x * 8 + (threadIdx.x >> 5), rstride = gridDim.x * 8;
+    if (rq0 >= nrq) return;
+    int kp = blockIdx.y, rq = rq0;
     Raw8<T> rg[4], ru[4], ng[4], nu[4];
-    if (PF) mmq_fetch(g, u, MmqTask(task, nrq, lane, nkb, kvalid), ld, rows, rg, ru);
-    for (; task < total; task += stride) {
-        const MmqTask t(task, nrq, lane, nkb, kvalid);
+    if (PF && kp < nkp) mmq_fetch(g, u, MmqTask(kp, rq, lane, nkb, kvalid), ld, rows, rg, ru);
+    while (kp < nkp) {
+        const MmqTask t(kp, rq, lane, nkb, kvalid);
+        const int kp_now = kp;
+        rq += rstride;                                                // the next task
+        if (rq >= nrq) { rq = rq0; kp += gridDim.y; }
         if (!PF) mmq_fetch(g, u, t, ld, rows, rg, ru);
-        else if (task + stride < total) mmq_fetch(g, u, MmqTask(task + stride, nrq, lane, nkb, kvalid), ld, rows, ng, nu);
+        else if (kp < nkp) mmq_fetch(g, u, MmqTask(kp, rq, lane, nkb, kvalid), ld, rows, ng, nu);
         float h[4][8], eg = 1.0f, eu = 0.0f;
         uint32_t bad = 0;                                             // bit c: chunk c of this lane fails a margin
 #pragma unroll
@@ -211,7 +293,7 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
         // exact recomputation of the flagged groups: the whole warp, one lane per value (uniform: redo is the same in every lane)
         for (uint32_t m = redo; m; m &= m - 1) {
             const int bit = __ffs(m) - 1, j = bit >> 2, c = bit & 3;     // group j of the warp's 8: K-block j / 4, group j % 4
-            const int kbj = (t.kb - (lane >> 4)) + (j >> 2), kj = kbj * 128 + (j & 3) * 32 + lane;
+            const int kbj = kp_now * 2 + (j >> 2), kj = kbj * 128 + (j & 3) * 32 + lane;
             float x = 0.0f;
             if (kj < kvalid) {
                 const size_t at = (size_t)(t.r0 + c) * ld + kj;
@@ -246,16 +328,16 @@ int launch_mmq(const void * x, const void * u, void * y, int kvalid, int Kpad, l
     if ((reinterpret_cast<uintptr_t>(x) & (elt - 1)) || (u && (reinterpret_cast<uintptr_t>(u) & (elt - 1))) || !cam_aligned16(y)) return CAM_ERR_ALIGN;
     if (rows == 0) return CAM_OK;
     if (MODE != 0 && layout == 0 && !(kvalid & 7) && !(ld & 7) && cam_aligned16(x) && cam_aligned16(u)) {
-        const long want = (long)((Kpad / 128 + 1) / 2) * ((rows + 3) / 4);
-        if (MODE == 2) mmq_swiglu_fast_kernel<uint16_t, true><<<cam_resident_grid(mmq_swiglu_fast_kernel<uint16_t, true>, 256, 0, (want + 7) / 8), 256, 0, stream>>>(
+        const long nx = ((rows + 3) / 4 + 7) / 8, ny = (Kpad / 128 + 1) / 2;
+        if (MODE == 2) mmq_swiglu_fast_kernel<uint16_t, true><<<mmq_grid(mmq_swiglu_fast_kernel<uint16_t, true>, nx, ny), 256, 0, stream>>>(
                 (const uint16_t *)x, (const uint16_t *)u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
-        else mmq_swiglu_fast_kernel<float, false><<<cam_resident_grid(mmq_swiglu_fast_kernel<float, false>, 256, 0, (want + 7) / 8), 256, 0, stream>>>(
+        else mmq_swiglu_fast_kernel<float, false><<<mmq_grid(mmq_swiglu_fast_kernel<float, false>, nx, ny), 256, 0, stream>>>(
                 (const float *)x, (const float *)u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
         return (int)cudaGetLastError();
     }
-    const long total = (long)(Kpad / 128) * rows, want = (total + 7) / 8;
-    if (layout == 0) mmq_q8_1_kernel<MODE, 0><<<cam_resident_grid(mmq_q8_1_kernel<MODE, 0>, 256, 0, want), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
-    else mmq_q8_1_kernel<MODE, 1><<<cam_resident_grid(mmq_q8_1_kernel<MODE, 1>, 256, 0, want), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
+    const long ny = (Kpad / 128 + 7) / 8;
+    if (layout == 0) mmq_q8_1_kernel<MODE, 0><<<mmq_grid(mmq_q8_1_kernel<MODE, 0>, rows, ny), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
+    else mmq_q8_1_kernel<MODE, 1><<<mmq_grid(mmq_q8_1_kernel<MODE, 1>, rows, ny), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
     return (int)cudaGetLastError();
 }
 
@@ -274,4 +356,32 @@ extern "C" int cam_swiglu_mmq_q8_1(const float * g, const float * u, void * y, i
 }
 extern "C" int cam_swiglu_mmq_q8_1_f16(const void * g, const void * u, void * y, int kvalid, int Kpad, long ld, int rows, int layout, void * stream) {
     return launch_mmq<2>(g, u, y, kvalid, Kpad, ld, rows, layout, (cudaStream_t)stream);
+}
+
+// cam_quantize_mmq_q8_1_ids: column c of y (ncols columns) = row ids[c] of x (ids null: row c); x fp32 with row stride s01 floats,
+// K values per row (a multiple of 4), zero-padded to Kpad. The reference's quantize_mmq_q8_1<layout, false>,
+// kernels/ggml_mmq/quantize_mmq.cuh:41-45 (instances kernels/prefill_mmq.hip:101-107); wrapper Mmq.quantize,
+// python/caminus/prefill/mmq.py:245-262.
+extern "C" int cam_quantize_mmq_q8_1_ids(const float * x, const int * ids, void * y, int K, int Kpad, long s01, int ncols, int layout, void * stream) {
+    if (ncols < 0 || Kpad < 128 || (Kpad & 127) || K < 0 || K > Kpad || (K & 3) || s01 < K || (s01 & 3) || !x || !y || (layout != 0 && layout != 1)) return CAM_ERR_ARG;
+    if (!cam_aligned16(x) || !cam_aligned16(y) || (ids && (reinterpret_cast<uintptr_t>(ids) & 3u))) return CAM_ERR_ALIGN;
+    if (ncols == 0) return CAM_OK;
+    const long ny = (Kpad / 128 + 7) / 8;
+    if (layout == 0) mmq_q8_1_rows_kernel<0, false><<<mmq_grid(mmq_q8_1_rows_kernel<0, false>, ncols, ny), 256, 0, (cudaStream_t)stream>>>(x, ids, (uint8_t *)y, K, Kpad / 128, s01, ncols, 1, ncols);
+    else mmq_q8_1_rows_kernel<1, false><<<mmq_grid(mmq_q8_1_rows_kernel<1, false>, ncols, ny), 256, 0, (cudaStream_t)stream>>>(x, ids, (uint8_t *)y, K, Kpad / 128, s01, ncols, 1, ncols);
+    return (int)cudaGetLastError();
+}
+// cam_quantize_mmq_q8_1_scatter: row t of x (ntok rows, stride s_tok floats) quantised once and written to the k columns
+// ids_inv[t k + slot] of y (ntok k columns). The reference's quantize_mmq_q8_1<layout, true>; wrapper Mmq.quantize_scatter,
+// python/caminus/prefill/mmq.py:264-281.
+extern "C" int cam_quantize_mmq_q8_1_scatter(const float * x, const int * ids_inv, void * y, int K, int Kpad, long s_tok, int ntok, int k, int layout,
+                                             void * stream) {
+    if (ntok < 0 || k < 1 || Kpad < 128 || (Kpad & 127) || K < 0 || K > Kpad || (K & 3) || s_tok < K || (s_tok & 3) || !x || !y || !ids_inv ||
+        (layout != 0 && layout != 1) || (long)ntok * k > 0x7fffffffL) return CAM_ERR_ARG;
+    if (!cam_aligned16(x) || !cam_aligned16(y) || (reinterpret_cast<uintptr_t>(ids_inv) & 3u)) return CAM_ERR_ALIGN;
+    if (ntok == 0) return CAM_OK;
+    const long ny = (Kpad / 128 + 7) / 8;
+    if (layout == 0) mmq_q8_1_rows_kernel<0, true><<<mmq_grid(mmq_q8_1_rows_kernel<0, true>, ntok, ny), 256, 0, (cudaStream_t)stream>>>(x, ids_inv, (uint8_t *)y, K, Kpad / 128, s_tok, ntok, k, ntok * k);
+    else mmq_q8_1_rows_kernel<1, true><<<mmq_grid(mmq_q8_1_rows_kernel<1, true>, ntok, ny), 256, 0, (cudaStream_t)stream>>>(x, ids_inv, (uint8_t *)y, K, Kpad / 128, s_tok, ntok, k, ntok * k);
+    return (int)cudaGetLastError();
 }

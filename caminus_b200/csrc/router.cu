@@ -37,56 +37,77 @@ __global__ void __launch_bounds__(256) router_kernel(const float * __restrict__ 
     }
 }
 
-// The same sums for many tokens: a warp holds TT tokens x EE experts (one accumulator per pair in every lane, the lanes
-// splitting K as above), so a step over 128 values of K costs TT + EE 16-byte loads for TT EE pairs instead of two per pair; the
-// 16 warps of a block take 16 EE experts of the same TT tokens, whose rows they share through L1. Per pair the statements and
-// their order are router_kernel's.
-template <int TT, int EE>
-__global__ void __launch_bounds__(512) router_tile_kernel(const float * __restrict__ h, const float * __restrict__ Wr, int E, int K,
+// The same sums for many tokens: a block takes a tile of 32 tokens x 16 experts, a warp 8 tokens x 8 experts of it (one
+// accumulator per pair in every lane, the lanes splitting K as above). Steps of 128 values of K are brought into shared memory
+// with cp.async, three stages deep (32 rows of h and 16 of Wr, 512 bytes each), so a step costs a warp 16 16-byte shared-memory
+// loads for 64 pairs instead of two global loads per pair, and no load waits on DRAM. Per pair the statements and their order
+// are router_kernel's.
+constexpr int RT_TOK = 32, RT_EXP = 16, RT_STAGES = 3, RT_STAGE_FLOATS = (RT_TOK + RT_EXP) * 128;
+
+__global__ void __launch_bounds__(256) router_tile_kernel(const float * __restrict__ h, const float * __restrict__ Wr, int E, int K,
                                                           float * __restrict__ logits, int n) {
-    const int lane = threadIdx.x & 31, wave = threadIdx.x >> 5;
-    const int t0 = blockIdx.x * TT, e0 = (blockIdx.y * 16 + wave) * EE;
-    if (e0 >= E) return;
-    const float * xp[TT], * wp[EE];
+    extern __shared__ __align__(16) float rt_smem[];
+    const int tid = threadIdx.x, lane = tid & 31, wave = tid >> 5;
+    const int t0 = blockIdx.x * RT_TOK, e0 = blockIdx.y * RT_EXP;
+    const int wt = (wave >> 1) * 8, we = (wave & 1) * 8;                   // this warp's tokens wt .. wt + 7, experts we .. we + 7 of the tile
+    // a thread copies chunks tid, tid + 256, .. of a stage's 1536 (row = chunk / 32: 32 token rows, then 16 expert rows)
+    const float * src[6];
 #pragma unroll
-    for (int i = 0; i < TT; i++) xp[i] = h + (size_t)min(t0 + i, n - 1) * K + lane * 4;       // (a tile's overhang recomputes the last row / expert)
+    for (int c = 0; c < 6; c++) {
+        const int row = (tid + 256 * c) >> 5;
+        src[c] = (row < RT_TOK ? h + (size_t)min(t0 + row, n - 1) * K : Wr + (size_t)min(e0 + row - RT_TOK, E - 1) * K) + 4 * lane;
+    }                                                                      // (a tile's overhang recomputes the last row / expert)
+    const int nks = K >> 7;
+    auto issue = [&](int ks) {
+        if (ks < nks) {
+            float * st = rt_smem + (ks % RT_STAGES) * RT_STAGE_FLOATS;
 #pragma unroll
-    for (int j = 0; j < EE; j++) wp[j] = Wr + (size_t)min(e0 + j, E - 1) * K + lane * 4;
-    float acc[TT][EE];
+            for (int c = 0; c < 6; c++) cp_async16(st + (tid + 256 * c) * 4, src[c] + ks * 128);
+        }
+        cp_async_commit();
+    };
+    float acc[8][8];
 #pragma unroll
-    for (int i = 0; i < TT; i++)
+    for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < EE; j++) acc[i][j] = 0.0f;
-    for (int k0 = 0; k0 < K; k0 += 128) {
-        float4 xv[TT], wv[EE];
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+    issue(0); issue(1);
+    for (int ks = 0; ks < nks; ks++) {
+        cp_async_wait<1>();
+        __syncthreads();                                                   // stage ks has landed for everyone; everyone is done with stage ks - 1
+        issue(ks + 2);
+        const float * st = rt_smem + (ks % RT_STAGES) * RT_STAGE_FLOATS + 4 * lane;
+        float4 xv[8], wv[8];
 #pragma unroll
-        for (int i = 0; i < TT; i++) xv[i] = __ldg(reinterpret_cast<const float4 *>(xp[i] + k0));
+        for (int i = 0; i < 8; i++) xv[i] = *reinterpret_cast<const float4 *>(st + (wt + i) * 128);
 #pragma unroll
-        for (int j = 0; j < EE; j++) wv[j] = __ldg(reinterpret_cast<const float4 *>(wp[j] + k0));
+        for (int j = 0; j < 8; j++) wv[j] = *reinterpret_cast<const float4 *>(st + (RT_TOK + we + j) * 128);
 #pragma unroll
-        for (int i = 0; i < TT; i++)
+        for (int i = 0; i < 8; i++)
 #pragma unroll
-            for (int j = 0; j < EE; j++) {
+            for (int j = 0; j < 8; j++) {
                 float d = fmul(wv[j].x, xv[i].x); d = ffma(wv[j].y, xv[i].y, d); d = ffma(wv[j].z, xv[i].z, d); d = ffma(wv[j].w, xv[i].w, d);
                 acc[i][j] = fadd(acc[i][j], d);
             }
     }
-    float mine = 0.0f;
+    cp_async_wait<0>();
+    float mine[2] = {0.0f, 0.0f};                                          // lane l stores pairs (token l / 8 and 4 + l / 8, expert l % 8)
 #pragma unroll
-    for (int i = 0; i < TT; i++)
+    for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < EE; j++) { const float v = wsum(acc[i][j]); if (lane == i * EE + j) mine = v; }      // (every lane holds the same total)
-    const int ti = t0 + lane / EE, ej = e0 + lane % EE;
-    if (lane < TT * EE && ti < n && ej < E) logits[(size_t)ti * E + ej] = mine;
+        for (int j = 0; j < 8; j++) { const float v = wsum(acc[i][j]); if (lane == (i & 3) * 8 + j) mine[i >> 2] = v; }      // (every lane holds the same total)
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) {
+        const int ti = t0 + wt + 4 * hh + (lane >> 3), ej = e0 + we + (lane & 7);
+        if (ti < n && ej < E) logits[(size_t)ti * E + ej] = mine[hh];
+    }
 }
 
 // (a warp per token as in the reference, eight tokens to a block)
 __global__ void __launch_bounds__(256) topk_kernel(const float * __restrict__ logits, int E, int k, float floor_, int * __restrict__ ids,
                                                    float * __restrict__ wts, int * __restrict__ err, int n) {
-    __shared__ int sel_[8][64];
     const int lane = threadIdx.x & 31, t = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (t >= n) return;                                  // (whole warps; no block-wide barrier below)
-    int * sel = sel_[threadIdx.x >> 5];
     const float * lg = logits + (size_t)t * E;
     float v[4]; bool bad = false;
 #pragma unroll
@@ -101,19 +122,29 @@ __global__ void __launch_bounds__(256) topk_kernel(const float * __restrict__ lo
     const float inv = fdiv(1.0f, sum);
 #pragma unroll
     for (int j = 0; j < 4; j++) v[j] = fmul(v[j], inv);
-    int rk[4] = {0, 0, 0, 0};
-    for (int src = 0; src < 32; src++) {
+    // rank-based top-k (rank = how many probabilities are larger, or equal with a lower index): the element of rank r is the r-th
+    // maximum under that order, so k rounds of a warp-wide argmax over the key (probability bits, then lower index first) give
+    // sel[0 .. k - 1]. Probabilities are >= 0, so their bit patterns order like the numbers.
+    long long key[4];
 #pragma unroll
-        for (int jj = 0; jj < 4; jj++) {
-            const float pj = __shfl_sync(CAM_FULL, v[jj], src); const int ej = src + 32 * jj;
+    for (int j = 0; j < 4; j++) {
+        const int e = lane + 32 * j;
+        key[j] = e < E ? (long long)(((unsigned long long)__float_as_uint(v[j]) << 32) | (unsigned)(0x7fffffff - e)) : -1;
+    }
+    int i = 0;
+    for (int r = 0; r < k; r++) {
+        long long best = key[0] > key[1] ? key[0] : key[1];
+        const long long b2 = key[2] > key[3] ? key[2] : key[3];
+        best = best > b2 ? best : b2;
 #pragma unroll
-            for (int j = 0; j < 4; j++) { const int ei = lane + 32 * j; if (ej < E && ei < E) rk[j] += (pj > v[j]) || (pj == v[j] && ej < ei); }
+        for (int o = 16; o > 0; o >>= 1) { const long long q = __shfl_xor_sync(CAM_FULL, best, o); best = q > best ? q : best; }
+        const int e = 0x7fffffff - (int)(unsigned)(best & 0xffffffffll);
+        if (lane == r) i = e;
+        if (lane == (e & 31)) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) if ((e >> 5) == j) key[j] = -1;
         }
     }
-#pragma unroll
-    for (int j = 0; j < 4; j++) if (lane + 32 * j < E && rk[j] < k) sel[rk[j]] = lane + 32 * j;
-    __syncwarp();
-    const int i = lane < k ? sel[lane] : 0;
     float pv[4];
 #pragma unroll
     for (int j = 0; j < 4; j++) pv[j] = __shfl_sync(CAM_FULL, v[j], i & 31);
@@ -161,8 +192,12 @@ extern "C" int q3p_router(int n, const float * h, const float * Wr, int E, int K
     if (n < 0 || E < 1 || K < 128 || (K & 127) || !h || !Wr || !logits) return CAM_ERR_ARG;
     if (!cam_aligned16(h) || !cam_aligned16(Wr)) return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
-    if (n >= 64) router_tile_kernel<8, 4><<<dim3((n + 7) / 8, (E + 63) / 64), 512, 0, (cudaStream_t)stream>>>(h, Wr, E, K, logits, n);
-    else router_kernel<<<n, 256, 0, (cudaStream_t)stream>>>(h, Wr, E, K, logits);
+    if (n >= 64) {
+        const size_t smem = (size_t)RT_STAGES * RT_STAGE_FLOATS * 4;
+        const cudaError_t e = cudaFuncSetAttribute(router_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     // (72 KB: above the default limit)
+        if (e != cudaSuccess) return (int)e;
+        router_tile_kernel<<<dim3((n + RT_TOK - 1) / RT_TOK, (E + RT_EXP - 1) / RT_EXP), 256, smem, (cudaStream_t)stream>>>(h, Wr, E, K, logits, n);
+    } else router_kernel<<<n, 256, 0, (cudaStream_t)stream>>>(h, Wr, E, K, logits);
     return (int)cudaGetLastError();
 }
 // q3p_topk: kernels/q3m_prefill.hip:440-441 (n = grid.x); E <= 128, k <= 32

@@ -37,6 +37,8 @@ SIGNATURES = {
     'cam_quantize_mmq_q8_1': [P, P, I, I, L, I, I, P],
     'cam_swiglu_mmq_q8_1': [P, P, P, I, I, L, I, I, P],
     'cam_swiglu_mmq_q8_1_f16': [P, P, P, I, I, L, I, I, P],
+    'cam_quantize_mmq_q8_1_ids': [P, P, P, I, I, L, I, I, P],
+    'cam_quantize_mmq_q8_1_scatter': [P, P, P, I, I, L, I, I, I, P],
     'actq_fwd_bf16': [I, P, P, P, I, F, I, P],
     'actq_fwd_f32': [I, P, P, P, I, F, I, P],
     'actq_fwd_codes_bf16': [I, P, P, P, P, I, F, I, P],

@@ -152,6 +152,13 @@ int q3p_group(const int * ids, int npairs, int k, int E, int * xs, int * yd, voi
 int cam_quantize_mmq_q8_1(const float * x, void * y, int kvalid, int Kpad, long ld, int rows, int layout, void * stream);
 int cam_swiglu_mmq_q8_1(const float * g, const float * u, void * y, int kvalid, int Kpad, long ld, int rows, int layout, void * stream);
 int cam_swiglu_mmq_q8_1_f16(const void * g, const void * u, void * y, int kvalid, int Kpad, long ld, int rows, int layout, void * stream);
+/* The indexed forms of quantize_mmq_q8_1 (kernels/ggml_mmq/quantize_mmq.cuh:41-140; instances kernels/prefill_mmq.hip:101-107; wrappers
+ * Mmq.quantize / Mmq.quantize_scatter, python/caminus/prefill/mmq.py:245-281). _ids: column c of y (ncols columns) = row ids[c] of x
+ * (ids null: row c; x holds ncols rows of stride s01). _scatter: row t of x (ntok rows of stride s_tok) is quantised once and written
+ * to the k columns ids_inv[t k + slot] of y (ntok k columns). An index outside its range is clamped. */
+int cam_quantize_mmq_q8_1_ids(const float * x, const int * ids, void * y, int K, int Kpad, long s01, int ncols, int layout, void * stream);
+int cam_quantize_mmq_q8_1_scatter(const float * x, const int * ids_inv, void * y, int K, int Kpad, long s_tok, int ntok, int k, int layout,
+                                  void * stream);
 
 /* ---- the hyper-connection ("Coder") line's glue: kernels/prefill_glue.hip; wrappers python/caminus/prefill/glue.py:143-313 ----
  * The reference bakes the row width (GLUE_NI x 256 = 2560 / 2048 / 5120) into three code objects; here it is the last argument

@@ -186,16 +186,44 @@ def test_swiglu_mmq_fast_equals_unfused_large():
     assert torch.equal(fused, gguf.quantize_mmq_q8_1(h, 'D4'))
 
 
-@pytest.mark.parametrize('M,K', [(1, 128), (37, 896), (300, 1024), (5, 8192)])
+@pytest.mark.parametrize('layout', [0, 1])
+def test_mmq_quantize_ids_and_scatter(layout):
+    """Mmq.quantize with a row index and Mmq.quantize_scatter: every column holds the oracle's block of the row it names
+    (the reference runs both forms through its MMQ and compares the products, tests/prefill/test_prefill_mmq.py:226-233)"""
+    from caminus_b200.prefill import mmq
+    g = np.random.default_rng(31 + layout); ntok, k, K, s01 = 37, 4, 600, 640
+    M = mmq.Mmq(DEV); Kp = mmq.k_pad(K)
+    x = acts(g, (ntok * k, s01), 2.0); x[3, :40] = 0
+    plain = oracle.mmq_q8_1(x, K, Kp, layout)                                   # [Kp / 128, rows, 144] of the rows in order
+    xd = cu(x.reshape(-1))
+    def run(fn, ncols):
+        y = torch.zeros(mmq.y_bytes(K, ncols), dtype=torch.uint8, device=DEV); fn(y)
+        return y[:Kp // 128 * ncols * 144].cpu().numpy().reshape(Kp // 128, ncols, 144)
+    ncols = ntok * k
+    assert np.array_equal(run(lambda y: M.quantize(xd, K, ncols, y, layout, s01=s01), ncols), plain)
+    ids = g.permutation(ncols).astype(np.int32); idd = cu(ids)
+    assert np.array_equal(run(lambda y: M.quantize(xd, K, ncols, y, layout, s01=s01, ids=idd), ncols), plain[:, ids])
+    inv = g.permutation(ncols).astype(np.int32); invd = cu(inv)                # token t's k columns
+    got = run(lambda y: M.quantize_scatter(xd, K, ntok, invd, k, y, layout, s_tok=s01), ncols)
+    want = np.zeros_like(got)
+    for t in range(ntok): want[:, inv[t * k:(t + 1) * k]] = plain[:, t:t + 1]
+    assert np.array_equal(got, want)
+    with pytest.raises(ValueError): M.quantize(xd, K + 2, ncols, torch.zeros(mmq.y_bytes(K, ncols), dtype=torch.uint8, device=DEV), layout)
+    with pytest.raises(ValueError): M.quantize(xd, K, ncols, torch.zeros(100, dtype=torch.uint8, device=DEV), layout)
+
+
+@pytest.mark.parametrize('M,K', [(1, 128), (37, 896), (300, 1024), (5, 8192), (20, 2048), (9, 4096), (3, 384)])
 def test_actq_family(M, K):
     """actq_fwd_*, silu_mul_actq_fwd, block_entry_fwd: values, scales and packed codes are the oracle's bytes; silu extremes and a
     row-strided view as tests/train/test_silu_mul_actq.py:21-47"""
     from caminus_b200.train import actq as A
     g = np.random.default_rng(M + K)
     x = acts(g, (M, K), 2.0)
-    for xin in (cu(x), cu(x).bfloat16()):
+    xs = x.copy()
+    if M >= 5: xs[1] = 0; xs[2, 3] = np.inf; xs[3, 5] = np.nan; xs[4] *= 1e-20      # a zero row, rows with an infinity / a NaN, a tiny row
+    for xin in (cu(xs), cu(xs).bfloat16()):
         y, c, s = A.actq_codes(xin, 4, 1.0)
-        ref = x if xin.dtype == torch.float32 else bits(xin).reshape(M, K)
+        ref = xs if xin.dtype == torch.float32 else bits(xin).reshape(M, K)
         yo, so, co = oracle.actq_fwd(ref, 1.0, 7)
         assert same(y, yo) and same(s, so) and np.array_equal(c.cpu().numpy().view(np.uint16).reshape(-1), co.reshape(-1))
         assert same(A.actq(xin, 4, 1.0), yo)
