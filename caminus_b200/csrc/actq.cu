@@ -137,12 +137,19 @@ CAM_DEV void actq_fwd_src(Src src, uint16_t * __restrict__ y, float * __restrict
         if (ch < nch) {
             float q[4];
 #pragma unroll
+            bool slow = !fast;
+#pragma unroll
             for (int e = 0; e < 4; e++) {       // (the division-free rint of actq_emit below)
                 const float vh = ffma(u[c][e], inv_hi, 12582912.0f), vl = ffma(u[c][e], inv_lo, 12582912.0f);
                 q[e] = __uint_as_float(__float_as_uint(fsub(vh, 12582912.0f)) | (__float_as_uint(u[c][e]) & 0x80000000u));
-                if (!fast || vh != vl) q[e] = rintf(fdiv(u[c][e], s));
-                q[e] = fminf(fmaxf(q[e], (float)(-qmax - 1)), (float)qmax);
+                slow |= vh != vl;
             }
+            if (slow) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) q[e] = rintf(fdiv(u[c][e], s));
+            }
+#pragma unroll
+            for (int e = 0; e < 4; e++) q[e] = fminf(fmaxf(q[e], (float)(-qmax - 1)), (float)qmax);
             const uint32_t pk = ((uint32_t)(int)q[0] & 0xFu) | (((uint32_t)(int)q[1] & 0xFu) << 4) | (((uint32_t)(int)q[2] & 0xFu) << 8) | (((uint32_t)(int)q[3] & 0xFu) << 12);
             if (y) st64(yr + ch * 128 + lane * 4, make_uint2(bf16x2<true>(fmul(q[0], s), fmul(q[1], s)), bf16x2<true>(fmul(q[2], s), fmul(q[3], s))));
             if (codes) codes[(size_t)row * (K / 4) + ch * 32 + lane] = (uint16_t)pk;
@@ -212,12 +219,19 @@ CAM_DEV void actq_emit(const uint2 (&up)[MAXC], float amax, int nch, int row, in
             float q[4], u[4];
             unpack4(up[c], u);
 #pragma unroll
+            bool slow = !fast;
+#pragma unroll
             for (int e = 0; e < 4; e++) {
                 const float vh = ffma(u[e], inv_hi, 12582912.0f), vl = ffma(u[e], inv_lo, 12582912.0f);
                 q[e] = __uint_as_float(__float_as_uint(fsub(vh, 12582912.0f)) | (__float_as_uint(u[e]) & 0x80000000u));     // (rint keeps the sign of a zero)
-                if (!fast || vh != vl) q[e] = rintf(fdiv(u[e], s));
-                q[e] = fminf(fmaxf(q[e], lo), hi);
+                slow |= vh != vl;
             }
+            if (slow) {                              // (one branch for the lane's four values)
+#pragma unroll
+                for (int e = 0; e < 4; e++) q[e] = rintf(fdiv(u[e], s));
+            }
+#pragma unroll
+            for (int e = 0; e < 4; e++) q[e] = fminf(fmaxf(q[e], lo), hi);
             const uint32_t pk = ((uint32_t)(int)q[0] & 0xFu) | (((uint32_t)(int)q[1] & 0xFu) << 4) | (((uint32_t)(int)q[2] & 0xFu) << 8) | (((uint32_t)(int)q[3] & 0xFu) << 12);
             if (y) st64_stream(y + (size_t)row * K + c * 128 + lane * 4, make_uint2(bf16x2<true>(fmul(q[0], s), fmul(q[1], s)), bf16x2<true>(fmul(q[2], s), fmul(q[3], s))));
             if (codes) codes[(size_t)row * (K / 4) + c * 32 + lane] = (uint16_t)pk;
