@@ -296,6 +296,7 @@ def main():
     ap.add_argument('--gpus', type=int, default=1); ap.add_argument('--steps', type=int, default=20); ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--rows', type=int, default=T_PER_GPU, help='token rows per GPU (the configured workload is 65536)')
+    ap.add_argument('--e2e-chunk', type=int, default=1024, help='rows per chunk of the host-buffer pass (two chunks in flight)')
     ap.add_argument('--ops', action='store_true', help='also time the single-op configs 1-4 on rank 0')
     ap.add_argument('--only', default='', help='with --ops: comma-separated substrings of the op names to time (default: all)')
     ap.add_argument('--cpu-sample', type=int, default=512)
@@ -377,11 +378,11 @@ def main():
     Te = min(T, args.e2e_rows)
     e2e = None
     if not args.skip_e2e:
-        Hrun = host.HostLayerGlue(Te, HIDDEN, NH, NKV, INTER, nw, par, dev)
+        Hrun = host.HostLayerGlue(Te, HIDDEN, NH, NKV, INTER, nw, par, dev, chunk=args.e2e_chunk)
         Hrun.fill_from(x, resid, q, k, gate, up)
         del gate, up, yq, h16, x, q, k, resid
         torch.cuda.empty_cache()
-        for _ in range(2): Hrun.run()
+        for _ in range(3): Hrun.run()
         barrier()
         e2e_steps = max(2, min(args.steps, 5))
         t0 = time.perf_counter()

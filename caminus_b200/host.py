@@ -10,7 +10,7 @@ from . import glue
 
 
 class HostLayerGlue:
-    def __init__(self, T, hidden, nh, nkv, inter, nw, par, dev, chunk=4096, eps=1e-6, yarn=False):
+    def __init__(self, T, hidden, nh, nkv, inter, nw, par, dev, chunk=1024, eps=1e-6, yarn=False):
         self.T, self.dev, self.chunk = int(T), torch.device(dev), int(min(chunk, T))
         self.layer = glue.LayerGlue(nw, par, eps, yarn)
         pin = lambda *s, dt=torch.float16: torch.empty(*s, dtype=dt, pin_memory=True)
