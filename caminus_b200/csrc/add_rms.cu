@@ -20,19 +20,7 @@ namespace {
 
 // ---- the reference's reduction on this file's two layouts ------------------------------------------------------------------
 // (ref_total_f32, the fp32 layout's reduction, is in cam_common.cuh: the training line's block entry uses it too)
-// fp16 layout: a[c] (c < 8)
-CAM_DEV float ref_total_f16(float (&a)[8], int lane) {
-#pragma unroll
-    for (int o = 2; o > 0; o >>= 1)
-#pragma unroll
-        for (int k = 0; k < 8; k++) a[k] = fadd(a[k], __shfl_xor_sync(CAM_FULL, a[k], o));
-    const float u0 = fadd(a[0], a[4]), u1 = fadd(a[1], a[5]), u2 = fadd(a[2], a[6]), u3 = fadd(a[3], a[7]);   // partner 4
-    const float P = fadd(fadd(u0, u2), fadd(u1, u3));                                                           // partners 2, 1
-    float tot = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 8; w++) tot = fadd(tot, __shfl_sync(CAM_FULL, P, 4 * w));
-    return tot;
-}
+// (ref_total_f16, the fp16 layout's reduction, is in cam_common.cuh as well: the one-kernel tensor-parallel norm uses it)
 
 // ---- fp32 rows ----------------------------------------------------------------------------------------------------------
 // CH > 0: N = 128 CH, the row stays in registers. CH = 0: any N (a multiple of 256), the row is read again from memory.

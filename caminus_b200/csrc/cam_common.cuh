@@ -155,6 +155,21 @@ CAM_DEV float ref_total_f32(float (&a)[8], int lane) {
     return tot;
 }
 
+// the same sum for fp16 rows, where lane l holds the 8 halves at 8 l + 256 m: accumulator c is thread 8 l + c with j = m; wave l >> 2,
+// wave lane 8 (l & 3) + c: partners 16, 8 are lanes l ^ 2, l ^ 1; partners 4, 2, 1 are inside the lane
+CAM_DEV float ref_total_f16(float (&a)[8], int lane) {
+#pragma unroll
+    for (int o = 2; o > 0; o >>= 1)
+#pragma unroll
+        for (int k = 0; k < 8; k++) a[k] = fadd(a[k], __shfl_xor_sync(CAM_FULL, a[k], o));
+    const float u0 = fadd(a[0], a[4]), u1 = fadd(a[1], a[5]), u2 = fadd(a[2], a[6]), u3 = fadd(a[3], a[7]);   // partner 4
+    const float P = fadd(fadd(u0, u2), fadd(u1, u3));                                                           // partners 2, 1
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) tot = fadd(tot, __shfl_sync(CAM_FULL, P, 4 * w));
+    return tot;
+}
+
 // ---- cp.async (16 bytes per thread, L2 only) with commit / wait groups --------------------------------------------------------
 CAM_DEV void cp_async16(void * smem, const void * gmem) {
     const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);

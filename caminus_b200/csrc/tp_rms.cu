@@ -1,0 +1,316 @@
+// Tensor-parallel RMSNorm as ONE kernel: the hidden dimension is sharded over the ranks (one GPU each); a rank reduces its
+// columns of a row to one fp32 sum of squares, writes it straight into every rank's exchange buffer over NVLink (plain peer
+// stores), and normalises its columns once all ranks' partials of that row have arrived in its own buffer. The two-kernel form
+// (cam_rms_partial_f16 -> all-reduce of [T] floats -> cam_rms_apply_f16, csrc/add_rms.cu) reads every row twice from HBM and pays a
+// collective's launch between the kernels; here a warp keeps its rows in shared memory from the sum of squares to the
+// normalisation (rows too long for that are read a second time, a few rows later), and the exchange overlaps the arithmetic row
+// by row. The reference has no counterpart (it replicates its norms,
+// python/caminus/engine/q3moe_tp.py:18-20).
+//
+// Exchange buffer of a rank (the caller allocates it and maps every rank's into every process): 64-bit words
+// [2 parities][world sources][cap rows], word = (tag << 32) | bits of the fp32 partial. The tag is the call's sequence number
+// (never 0; the buffer starts zeroed), the same on every rank, so a word is valid exactly when its tag matches: no flags to
+// reset, no fence between value and flag (one 8-byte store), and a call cannot mistake the previous call's words (parity = tag & 1
+// alternates; a rank can be at most one call ahead of another, because it needs the other's partials of this call to finish).
+// Row total = the partials added in rank order from 0.0f: the same bits on every rank.
+//
+// Every wait is bounded: a lane polls its source's word for at most CAM_TP_WAIT_NS of the global timer; on expiry the warp ORs 1
+// into *status and stops taking rows (its peers' waits for this rank's later rows expire the same way). Nothing is left in flight:
+// the kernel uses plain loads and stores only. Ranks run on different GPUs; this kernel must never be launched for two ranks on
+// one GPU (the second would wait for a kernel that cannot start).
+#include "cam_common.cuh"
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+namespace {
+
+constexpr unsigned long long CAM_TP_WAIT_NS = 2000000000ull;      // 2 s
+
+CAM_DEV void st_sys_u64(unsigned long long * p, unsigned long long v) { asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory"); }
+CAM_DEV unsigned long long ld_sys_u64(const unsigned long long * p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+CAM_DEV unsigned long long global_ns() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+
+CAM_DEV void widen8(const uint4 v, float (&f)[8]) {
+    const float2 a = h2_to_f2(v.x), b = h2_to_f2(v.y), c = h2_to_f2(v.z), e = h2_to_f2(v.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = e.x; f[7] = e.y;
+}
+// DEPTH: rows between a warp's partial of a row and its normalisation of that row (the exchange's round trip hides behind them)
+template <int DEPTH>
+__global__ void __launch_bounds__(128) tp_rms_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d, const float * __restrict__ nw, float eps,
+                                                     uint16_t * __restrict__ h16, int Ns, int Nfull, int n, unsigned long long * const * __restrict__ peers,
+                                                     int rank, int world, int cap, unsigned tag, int * status) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nch = (Ns + 255) >> 8;                                     // 16-byte chunks per lane and row (the last may be short)
+    const int t0 = blockIdx.x * 4 + warp, stride = gridDim.x * 4;
+    const size_t slot0 = (size_t)(tag & 1u) * world * cap;               // this call's half of every buffer
+    unsigned long long * const mine = lane < world ? peers[lane] + slot0 + (size_t)rank * cap : nullptr;   // where lane r writes: rank r's buffer, source = this rank
+    const unsigned long long * const from = lane < world ? peers[rank] + slot0 + (size_t)lane * cap : nullptr;   // where lane r polls: own buffer, source r
+    const int rows = t0 < n ? (n - t0 + stride - 1) / stride : 0;       // this warp's rows t0, t0 + stride, ..
+    bool dead = false;
+    for (int k = 0; k < rows + DEPTH; k++) {
+        if (k < rows && !dead) {                                         // ---- this shard's sum of squares of row t, sent to every rank
+            const int t = t0 + k * stride;
+            const uint16_t * xr = x + (size_t)t * Ns, * dr = d ? d + (size_t)t * Ns : nullptr;
+            float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+            for (int m = 0; m < nch; m++) {
+                const int i = 8 * lane + 256 * m;
+                if (i >= Ns) break;
+                float xs[8];
+                widen8(ld128(xr + i), xs);
+                if (dr) {
+                    float dv[8];
+                    widen8(ldg128(dr + i), dv);
+#pragma unroll
+                    for (int c = 0; c < 8; c++) xs[c] = fadd(xs[c], dv[c]);
+                }
+#pragma unroll
+                for (int c = 0; c < 8; c++) a[c] = ffma(xs[c], xs[c], a[c]);
+            }
+            const float part = ref_total_f16(a, lane);      // (the bits of cam_rms_partial_f16)
+            if (mine) st_sys_u64(mine + t, ((unsigned long long)tag << 32) | __float_as_uint(part));
+        }
+        const int kd = k - DEPTH;
+        if (kd >= 0 && kd < rows && !dead) {                             // ---- row t of DEPTH rows ago: gather the partials, normalise
+            const int t = t0 + kd * stride;
+            float part = 0.0f;
+            bool late = false;
+            if (from) {
+                unsigned long long w = ld_sys_u64(from + t);
+                if ((unsigned)(w >> 32) != tag) {
+                    const unsigned long long start = global_ns();
+                    do {
+                        __nanosleep(64);
+                        w = ld_sys_u64(from + t);
+                        late = (unsigned)(w >> 32) != tag;
+                    } while (late && global_ns() - start < CAM_TP_WAIT_NS);
+                }
+                part = __uint_as_float((unsigned)w);
+            }
+            if (__any_sync(CAM_FULL, late)) {                            // a source never arrived: report, take no more rows
+                if (lane == 0) atomicOr(status, 1);
+                dead = true;
+                continue;
+            }
+            float tot = 0.0f;
+            for (int r = 0; r < world; r++) tot = fadd(tot, __shfl_sync(CAM_FULL, part, r));
+            const float scale = cam_rsqrt(fadd(fdiv(tot, (float)Nfull), eps));
+            uint16_t * xr = x + (size_t)t * Ns, * hr = h16 + (size_t)t * Ns;
+            const uint16_t * dr = d ? d + (size_t)t * Ns : nullptr;
+#pragma unroll 2
+            for (int m = 0; m < nch; m++) {
+                const int i = 8 * lane + 256 * m;
+                if (i >= Ns) break;
+                float xs[8];
+                widen8(ld128(xr + i), xs);
+                if (dr) {
+                    float dv[8];
+                    widen8(ldg128(dr + i), dv);
+#pragma unroll
+                    for (int c = 0; c < 8; c++) xs[c] = fadd(xs[c], dv[c]);
+                    st128(xr + i, make_uint4(f2_to_h2(xs[0], xs[1]), f2_to_h2(xs[2], xs[3]), f2_to_h2(xs[4], xs[5]), f2_to_h2(xs[6], xs[7])));
+                }
+                const float4 w0 = __ldg(reinterpret_cast<const float4 *>(nw + i)), w1 = __ldg(reinterpret_cast<const float4 *>(nw + i + 4));
+                float v[8];
+                v[0] = fmul(fmul(xs[0], scale), w0.x); v[1] = fmul(fmul(xs[1], scale), w0.y);
+                v[2] = fmul(fmul(xs[2], scale), w0.z); v[3] = fmul(fmul(xs[3], scale), w0.w);
+                v[4] = fmul(fmul(xs[4], scale), w1.x); v[5] = fmul(fmul(xs[5], scale), w1.y);
+                v[6] = fmul(fmul(xs[6], scale), w1.z); v[7] = fmul(fmul(xs[7], scale), w1.w);
+                st128_stream(hr + i, make_uint4(f2_to_h2(v[0], v[1]), f2_to_h2(v[2], v[3]), f2_to_h2(v[4], v[5]), f2_to_h2(v[6], v[7])));
+            }
+        }
+    }
+}
+
+// The staged form: a warp keeps LA + DEPTH + 1 rows of its shard (x and d as stored) in its own slice of shared memory, brought in with
+// cp.async (a lane copies exactly the 16-byte chunks it reads back, so its own copy groups are the only synchronisation). Per step
+// k of a warp: row k + LA is requested; row k has landed: its sum of squares is formed and sent to every rank; row k - DEPTH, whose
+// partials have had DEPTH rows of time to cross NVLink, is gathered, normalised from shared memory and stored. No row is read from
+// HBM twice. A warp's wait (for its row, for the partials) is covered by the other warps of the multiprocessor: the launcher
+// trades slots per warp for resident warps.
+template <int LA, int DEPTH>
+__global__ void __launch_bounds__(256) tp_rms_staged_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d, const float * __restrict__ nw, float eps,
+                                                            uint16_t * __restrict__ h16, int Ns, int Nfull, int n, unsigned long long * const * __restrict__ peers,
+                                                            int rank, int world, int cap, unsigned tag, int * status, int warps) {
+    constexpr int S = LA + DEPTH + 1;
+    extern __shared__ __align__(16) unsigned char tp_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nch = (Ns + 255) >> 8;
+    const size_t half_bytes = (size_t)nch * 512, row_bytes = (d ? 2 : 1) * half_bytes;
+    unsigned char * const slots = tp_smem + (size_t)warp * S * row_bytes;
+    const int t0 = blockIdx.x * warps + warp, stride = gridDim.x * warps;
+    const size_t slot0 = (size_t)(tag & 1u) * world * cap;
+    unsigned long long * const mine = lane < world ? peers[lane] + slot0 + (size_t)rank * cap : nullptr;
+    const unsigned long long * const from = lane < world ? peers[rank] + slot0 + (size_t)lane * cap : nullptr;
+    const int rows = t0 < n ? (n - t0 + stride - 1) / stride : 0;
+
+    auto request = [&](int k) {                                          // row k of this warp into slot k % S (one copy group per call)
+        if (k < rows) {
+            unsigned char * sx = slots + (size_t)(k % S) * row_bytes;
+            const size_t at = (size_t)(t0 + k * stride) * Ns + 8 * lane;
+            for (int m = 0; m < nch; m++)
+                if (8 * lane + 256 * m < Ns) {
+                    cp_async16(sx + (size_t)(m * 32 + lane) * 16, x + at + 256 * m);
+                    if (d) cp_async16(sx + half_bytes + (size_t)(m * 32 + lane) * 16, d + at + 256 * m);
+                }
+        }
+        cp_async_commit();
+    };
+    auto row_values = [&](const unsigned char * sx, int m, float (&xs)[8]) {   // xs = x + d of this lane's chunk m
+        widen8(*reinterpret_cast<const uint4 *>(sx + (size_t)(m * 32 + lane) * 16), xs);
+        if (d) {
+            float dv[8];
+            widen8(*reinterpret_cast<const uint4 *>(sx + half_bytes + (size_t)(m * 32 + lane) * 16), dv);
+#pragma unroll
+            for (int c = 0; c < 8; c++) xs[c] = fadd(xs[c], dv[c]);
+        }
+    };
+
+#pragma unroll
+    for (int k = 0; k < LA; k++) request(k);
+    bool dead = false;
+    for (int k = 0; k < rows + DEPTH; k++) {
+        request(k + LA);                                                 // (its slot held row k - DEPTH - 1, stored a step ago)
+        cp_async_wait<LA>();                                             // row k has landed (later rows may still fly)
+        if (k < rows && !dead) {                                         // ---- row k: this shard's sum of squares, sent to every rank
+            const unsigned char * sx = slots + (size_t)(k % S) * row_bytes;
+            float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+            for (int m = 0; m < nch; m++) {
+                if (8 * lane + 256 * m >= Ns) break;
+                float xs[8];
+                row_values(sx, m, xs);
+#pragma unroll
+                for (int c = 0; c < 8; c++) a[c] = ffma(xs[c], xs[c], a[c]);
+            }
+            const float part = ref_total_f16(a, lane);                   // (the bits of cam_rms_partial_f16)
+            if (mine) st_sys_u64(mine + (t0 + k * stride), ((unsigned long long)tag << 32) | __float_as_uint(part));
+        }
+        const int kd = k - DEPTH;
+        if (kd >= 0 && kd < rows && !dead) {                             // ---- row kd: gather the partials, normalise, store
+            const int t = t0 + kd * stride;
+            float part = 0.0f;
+            bool late = false;
+            if (from) {
+                unsigned long long w = ld_sys_u64(from + t);
+                if ((unsigned)(w >> 32) != tag) {
+                    const unsigned long long start = global_ns();
+                    do {
+                        __nanosleep(64);
+                        w = ld_sys_u64(from + t);
+                        late = (unsigned)(w >> 32) != tag;
+                    } while (late && global_ns() - start < CAM_TP_WAIT_NS);
+                }
+                part = __uint_as_float((unsigned)w);
+            }
+            if (__any_sync(CAM_FULL, late)) {                            // a source never arrived: report, take no more rows
+                if (lane == 0) atomicOr(status, 1);
+                dead = true;
+                continue;
+            }
+            float tot = 0.0f;
+            for (int r = 0; r < world; r++) tot = fadd(tot, __shfl_sync(CAM_FULL, part, r));
+            const float scale = cam_rsqrt(fadd(fdiv(tot, (float)Nfull), eps));
+            const unsigned char * sx = slots + (size_t)(kd % S) * row_bytes;
+            const size_t at = (size_t)t * Ns + 8 * lane;
+#pragma unroll 2
+            for (int m = 0; m < nch; m++) {
+                const int i = 8 * lane + 256 * m;
+                if (i >= Ns) break;
+                float xs[8];
+                row_values(sx, m, xs);
+                if (d) st128(x + at + 256 * m, make_uint4(f2_to_h2(xs[0], xs[1]), f2_to_h2(xs[2], xs[3]), f2_to_h2(xs[4], xs[5]), f2_to_h2(xs[6], xs[7])));
+                const float4 w0 = __ldg(reinterpret_cast<const float4 *>(nw + i)), w1 = __ldg(reinterpret_cast<const float4 *>(nw + i + 4));
+                float v[8];
+                v[0] = fmul(fmul(xs[0], scale), w0.x); v[1] = fmul(fmul(xs[1], scale), w0.y);
+                v[2] = fmul(fmul(xs[2], scale), w0.z); v[3] = fmul(fmul(xs[3], scale), w0.w);
+                v[4] = fmul(fmul(xs[4], scale), w1.x); v[5] = fmul(fmul(xs[5], scale), w1.y);
+                v[6] = fmul(fmul(xs[6], scale), w1.z); v[7] = fmul(fmul(xs[7], scale), w1.w);
+                st128_stream(h16 + at + 256 * m, make_uint4(f2_to_h2(v[0], v[1]), f2_to_h2(v[2], v[3]), f2_to_h2(v[4], v[5]), f2_to_h2(v[6], v[7])));
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
+template <int LA, int DEPTH>
+int launch_tp_staged(int warps, size_t smem, int n, void * x, const void * d, const float * nw, float eps, void * h16, int Ns, int Nfull, const void * peers,
+                     int rank, int world, int cap, unsigned tag, int * status, cudaStream_t stream) {
+    const cudaError_t e = cudaFuncSetAttribute(tp_rms_staged_kernel<LA, DEPTH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    const int grid = cam_resident_grid(tp_rms_staged_kernel<LA, DEPTH>, warps * 32, smem, ((long)n + warps - 1) / warps);
+    tp_rms_staged_kernel<LA, DEPTH><<<grid, warps * 32, smem, stream>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Ns, Nfull, n,
+                                                                        (unsigned long long * const *)peers, rank, world, cap, tag, status, warps);
+    return (int)cudaGetLastError();
+}
+
+}   // namespace
+
+// cam_tp_rms_words: 64-bit words of one rank's exchange buffer for up to cap rows per call (the caller allocates them zeroed)
+extern "C" int cam_tp_rms_words(int cap, int world) {
+    const long w = 2L * world * cap;
+    return cap < 1 || world < 1 || world > 32 || w > 0x7fffffffL ? CAM_ERR_ARG : (int)w;
+}
+
+// cam_tp_rms_norm_f16: x [n][Ns] fp16 = this rank's columns (updated in place to fp16(x + d) when d is given), d fp16 (nullable),
+// nw fp32 [Ns] = this rank's weights, h16 fp16 [n][Ns] out; Nfull = the row length over all ranks. peers: device array of `world`
+// pointers, entry r = rank r's exchange buffer as mapped in this process (entry `rank` = this rank's own), each
+// cam_tp_rms_words(cap, world) words; n <= cap (CAM_ERR_CAPACITY beyond). tag: the call's sequence number, not 0, the same on
+// every rank, consecutive calls differing in parity (1, 2, 3, ..). status: an int32 word in this rank's memory; bit 0 is set when
+// a wait ran out (some rank did not take part, or not with the same n and tag), in which case rows are left unnormalised.
+// Every rank must make the matching call; no rank's call may share a GPU with another's. Ns a multiple of 8, world <= 32.
+extern "C" int cam_tp_rms_norm_f16(int n, void * x, const void * d, const float * nw, float eps, void * h16, int Ns, int Nfull,
+                                   const void * peers, int rank, int world, int cap, unsigned tag, int * status, void * stream) {
+    if (n < 0 || Ns < 8 || (Ns & 7) || Nfull < Ns || world < 1 || world > 32 || rank < 0 || rank >= world || cap < 1 || tag == 0 || !x || !nw || !h16 ||
+        !peers || !status) return CAM_ERR_ARG;
+    if (n > cap) return CAM_ERR_CAPACITY;
+    if (!cam_aligned16(x) || (d && !cam_aligned16(d)) || !cam_aligned16(nw) || !cam_aligned16(h16) || (reinterpret_cast<uintptr_t>(peers) & 7u) ||
+        (reinterpret_cast<uintptr_t>(status) & 3u)) return CAM_ERR_ALIGN;
+    if (n == 0) return CAM_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    // Rows staged in shared memory. Measured on B200 (T = 65536, shards of 640 / 1280 / 2560 columns): resident warps matter more than
+    // rows in flight per warp: two slots per warp (one row waiting for its partials while the next is loaded and reduced) where
+    // that still leaves 20 warps per multiprocessor, else one slot. CAMINUS_B200_TP_CFG="slots,warps" overrides (tuning).
+    {
+        const size_t row_bytes = (size_t)(d ? 2 : 1) * ((Ns + 255) >> 8) * 512, budget = 224 * 1024;
+        int slots = 2 * 20 * row_bytes <= budget ? 2 : 1, warps = 8;
+        if (const char * e = getenv("CAMINUS_B200_TP_CFG")) {
+            int sl = 0, wp = 0;
+            if (sscanf(e, "%d,%d", &sl, &wp) == 2 && sl >= 1 && sl <= 4 && wp >= 1 && wp <= 8) { slots = sl; warps = wp; }
+        }
+        while (warps > 1 && (size_t)slots * warps * row_bytes > budget) warps--;
+        const size_t smem = (size_t)slots * warps * row_bytes;
+        if (smem <= budget) {
+#define CAM_TP_STAGED(LAV, DV) return launch_tp_staged<LAV, DV>(warps, smem, n, x, d, nw, eps, h16, Ns, Nfull, peers, rank, world, cap, tag, status, st);
+            switch (slots) {
+                case 1: CAM_TP_STAGED(0, 0)
+                case 2: CAM_TP_STAGED(0, 1)
+                case 3: CAM_TP_STAGED(1, 1)
+                default: CAM_TP_STAGED(1, 2)
+            }
+#undef CAM_TP_STAGED
+        }
+    }
+    // longer rows: two passes over the row, four rows apart
+    const int grid = cam_resident_grid(tp_rms_kernel<4>, 128, 0, ((long)n + 3) / 4);
+    tp_rms_kernel<4><<<grid, 128, 0, st>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Ns, Nfull, n,
+                                           (unsigned long long * const *)peers, rank, world, cap, tag, status);
+    return (int)cudaGetLastError();
+}
+
+// cam_ipc_open: maps an allocation another process exported (the 64 bytes of its cudaIpcMemHandle_t) into the current device's
+// address space, enabling peer access to the exporting device when it is another one (kernels of the current device can then
+// load and store there over NVLink). *base = the start of that allocation. cam_ipc_close unmaps it. Nothing is allocated.
+extern "C" int cam_ipc_open(const void * handle64, void ** base) {
+    if (!handle64 || !base) return CAM_ERR_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    return (int)cudaIpcOpenMemHandle(base, h, cudaIpcMemLazyEnablePeerAccess);
+}
+extern "C" int cam_ipc_close(void * base) { return base ? (int)cudaIpcCloseMemHandle(base) : CAM_ERR_ARG; }

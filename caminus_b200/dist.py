@@ -5,7 +5,8 @@ independent rows, so rank r of G takes rows [r T / G, (r + 1) T / G) and the nor
 are replicated. The tensor-parallel RMSNorm shards the hidden dimension instead: each rank reduces its columns to one fp32
 sum of squares per row, the [T] partials are all-reduced (the only bytes that cross NVLink), and each rank normalises its
 own columns. The reference has no counterpart: it replicates norms and the residual on both of its cards
-(python/caminus/engine/q3moe_tp.py:18-20).
+(python/caminus/engine/q3moe_tp.py:18-20). TPRmsNormFused is the same norm as one kernel per rank: the partials go straight into
+every rank's exchange buffer by peer stores over NVLink and a row is normalised as soon as its partials have arrived.
 """
 import torch
 import torch.distributed as dist
@@ -66,3 +67,82 @@ class TPRmsNorm:
         ss = self.partial(x, d)
         self._all_reduce(ss)
         return self.apply(x, ss, h16, d)
+
+
+class TPRmsNormFused:
+    """The tensor-parallel RMSNorm as ONE launch per rank (cam_tp_rms_norm_f16): no collective call, no second pass over HBM.
+
+    Every rank of `group` constructs it with the same `cap` (rows per call at most) and then makes the same sequence of calls.
+    Construction allocates this rank's exchange buffer (2 * world * cap 64-bit words, zeroed), shares it with the other ranks'
+    processes through CUDA IPC (torch's tensor sharing; the handles travel by all_gather_object) and keeps the peers' mappings.
+    __call__(x, d) as TPRmsNorm.__call__. check() synchronises and raises if a wait ran out (a rank that did not take part).
+    One rank per GPU: two ranks' kernels on one GPU would wait for each other."""
+
+    def __init__(self, nw_shard, Nfull, cap, eps=1e-6, group=None, device=None):
+        self.nw, self.Nfull, self.eps, self.cap, self.group = nw_shard, int(Nfull), float(eps), int(cap), group
+        self.dev = torch.device(device) if device is not None else nw_shard.device
+        one = group is None and not dist.is_initialized()
+        self.world = 1 if one else dist.get_world_size(group)
+        self.rank = 0 if one else dist.get_rank(group)
+        L = _lib.load()
+        words = L.cam_tp_rms_words(self.cap, self.world)
+        if words < 0: raise ValueError(f'TPRmsNormFused: cap {cap}, world {self.world}')
+        self.buf = torch.zeros(words, dtype=torch.int64, device=self.dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.tag = 0
+        self._mapped = []                                        # bases of the peers' allocations mapped into this process
+        ptrs = [0] * self.world
+        if self.world > 1:
+            import ctypes
+            torch.cuda.synchronize(self.dev)                     # the zeros are in place before any peer can write
+            # CUDA IPC: the handle of the allocation that holds buf and buf's offset in it (torch's own export call, which also
+            # keeps the allocation from being reused while it is shared)
+            shared = self.buf.untyped_storage()._share_cuda_()
+            raw = bytes(shared[1])
+            # (torch wraps the 64-byte cudaIpcMemHandle_t: a version byte and a kind byte, 'c' = a cudaMalloc block, in front)
+            if len(raw) < 64 or (len(raw) > 64 and raw[-65:-64] != b'c'):
+                raise RuntimeError(f'TPRmsNormFused: the allocator exported a handle this code does not map ({len(raw)} bytes, kind {raw[-65:-64]!r}): '
+                                   'expandable segments are not supported')
+            mine = (raw[-64:], int(shared[3]))
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, mine, group=group)
+            with torch.cuda.device(self.dev):
+                for r, (handle, offset) in enumerate(everyone):
+                    if r == self.rank: continue
+                    base = ctypes.c_void_p()
+                    _lib.check(L.cam_ipc_open(handle, ctypes.byref(base)), f'cam_ipc_open (rank {r})')
+                    self._mapped.append(base)
+                    ptrs[r] = base.value + offset
+            dist.barrier(group=group)                            # every rank has mapped every buffer before the first launch
+        ptrs[self.rank] = self.buf.data_ptr()
+        self.peers = torch.tensor(ptrs, dtype=torch.int64, device=self.dev)
+
+    def __call__(self, x, d=None, h16=None):
+        if x.dtype != torch.float16 or not x.is_contiguous() or x.dim() != 2 or x.shape[1] % 8 or x.device != self.dev:
+            raise ValueError(f'TPRmsNormFused: x must be contiguous fp16 [T, Ns] on {self.dev} with Ns a multiple of 8, not {tuple(x.shape)} {x.dtype}')
+        if d is not None and (d.shape != x.shape or d.dtype != x.dtype or not d.is_contiguous()):
+            raise ValueError('TPRmsNormFused: d must match x')
+        if self.nw.numel() != x.shape[1]: raise ValueError(f'TPRmsNormFused: {self.nw.numel()} weights for {x.shape[1]} columns')
+        T, Ns = x.shape
+        if T > self.cap: raise ValueError(f'TPRmsNormFused: {T} rows, built for {self.cap}')
+        if h16 is None: h16 = torch.empty_like(x)
+        self.tag = self.tag % 0xfffffffe + 1                     # 1, 2, .. (never 0; consecutive calls alternate parity)
+        with torch.cuda.device(self.dev):
+            s = torch.cuda.current_stream().cuda_stream
+            _lib.check(_lib.load().cam_tp_rms_norm_f16(T, x.data_ptr(), 0 if d is None else d.data_ptr(), self.nw.data_ptr(), self.eps, h16.data_ptr(),
+                                                       Ns, self.Nfull, self.peers.data_ptr(), self.rank, self.world, self.cap, self.tag,
+                                                       self.status.data_ptr(), s), 'cam_tp_rms_norm_f16')
+        return h16
+
+    def close(self):
+        """unmap the peers' buffers (after the last call has finished on every rank)"""
+        torch.cuda.synchronize(self.dev)
+        with torch.cuda.device(self.dev):
+            for base in self._mapped: _lib.load().cam_ipc_close(base)
+        self._mapped = []
+
+    def check(self):
+        torch.cuda.synchronize(self.dev)
+        if int(self.status.item()) != 0:
+            self.status.zero_()
+            raise RuntimeError('TPRmsNormFused: a wait for another rank ran out (a rank did not make the matching call)')

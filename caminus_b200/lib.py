@@ -11,7 +11,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 DEFAULT_PATH = os.path.join(_HERE, 'lib', 'libcaminus_b200.so')
 ABI_VERSION = 1
 
-P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
+P, I, L, F, U = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float, ctypes.c_uint
 
 # entry -> argument types, in the order of include/caminus_b200.h (every entry returns int)
 SIGNATURES = {
@@ -19,6 +19,10 @@ SIGNATURES = {
     'q3p_add_rms16': [I, P, P, P, I, P, F, P, P, I, P],
     'q35p_add_rms16': [I, P, P, P, F, P, P, I, P],
     'cam_add_rms_f16': [I, P, P, P, F, P, I, P],
+    'cam_ipc_open': [P, P],
+    'cam_ipc_close': [P],
+    'cam_tp_rms_words': [I, I],
+    'cam_tp_rms_norm_f16': [I, P, P, P, F, P, I, I, P, I, I, I, U, P, P],
     'cam_rms_partial_f16': [I, P, P, P, I, P],
     'cam_rms_apply_f16': [I, P, P, P, P, F, P, I, I, P],
     'cam_rms_norm_f16_static': [I, P, P, P, F, P, I, P],

@@ -64,6 +64,17 @@ int cam_rms_partial_f16(int n, const void * x, const void * d, float * ss, int N
 int cam_rms_apply_f16(int n, void * x, const void * d, const float * tot, const float * nw, float eps, void * h16, int Ns,
                       int Nfull, void * stream);
 
+/* The tensor-parallel RMSNorm as one kernel per rank (no reference counterpart; one rank per GPU). Each rank's exchange buffer holds
+ * cam_tp_rms_words(cap, world) 64-bit words, zeroed once, and is mapped into every rank's process; peers is a device array of `world`
+ * pointers to them (entry `rank` = the caller's own). A rank writes its per-row partial sums into every buffer by peer stores and
+ * normalises a row when all ranks' partials have arrived; tag = the call's sequence number (1, 2, 3, ..: never 0, the same on every
+ * rank). Waits are bounded (2 s): on expiry bit 0 of *status is set and rows are left unnormalised. n <= cap. */
+int cam_ipc_open(const void * handle64, void ** base);      /* map another process's exported allocation (its 64-byte cudaIpcMemHandle_t) for the current device, peer access included */
+int cam_ipc_close(void * base);
+int cam_tp_rms_words(int cap, int world);
+int cam_tp_rms_norm_f16(int n, void * x, const void * d, const float * nw, float eps, void * h16, int Ns, int Nfull, const void * peers, int rank,
+                        int world, int cap, unsigned tag, int * status, void * stream);
+
 /* The partial / apply pair above as ONE call that allocates nothing: the per-row sums of squares that pass from the first
  * kernel to the second live in a static device array inside the library (65536 floats, 256 KB per device that loads it)
  * instead of a caller's buffer. For callers that must not allocate device memory: a plugin working in buffers its engine

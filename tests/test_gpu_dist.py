@@ -1,5 +1,5 @@
-"""Multi-GPU checks (skipped with fewer than two GPUs): the hidden-sharded RMSNorm over NCCL against the unsharded kernel,
-and row sharding (no collective). One process per GPU, NVLS off (a test must leave the other ranks' GPUs sound whatever
+"""Multi-GPU checks (skipped with fewer than two GPUs): the hidden-sharded RMSNorm over NCCL against the unsharded kernel, its
+one-kernel form (partials by peer stores) against the two-kernel form bit for bit, and row sharding (no collective). One process per GPU, NVLS off (a test must leave the other ranks' GPUs sound whatever
 happens to one rank)."""
 import os
 import socket
@@ -28,22 +28,39 @@ def _rank(rank, world, port, T, N, out):
         a, b = D.col_shard(N, rank, world)
         xs = torch.from_numpy(np.ascontiguousarray(x0[:, a:b])).to(dev); rs = torch.from_numpy(np.ascontiguousarray(r0[:, a:b])).to(dev)
         norm = D.TPRmsNorm(torch.from_numpy(w[a:b].copy()).to(dev), N, 1e-6)
+        x_in = xs.clone()
         h = norm(xs, rs)
+        # the one-kernel form: partials exchanged by peer stores. Reference: this rank's apply kernel on the partials of all ranks
+        # added in rank order (the fused kernel's order), so the comparison is bit for bit; two calls (the tag's parity alternates)
+        fused = D.TPRmsNormFused(norm.nw, N, T, 1e-6)
+        fused_ok = True
+        for rep in range(2):
+            xa = x_in.clone() if rep == 0 else (x_in * 0.5).clone()
+            xb = xa.clone()
+            parts = [torch.empty(T, device=dev) for _ in range(world)]
+            dist.all_gather(parts, norm.partial(xa, rs).clone())
+            tot = torch.zeros(T, device=dev)
+            for p_ in parts: tot = tot + p_
+            h_ref = norm.apply(xa, tot, d=rs)
+            h_f = fused(xb, rs); fused.check()
+            fused_ok = fused_ok and torch.equal(h_f, h_ref) and torch.equal(xa, xb)
+        dist.barrier()
+        fused.close()
         # the unsharded kernel on this rank's rows of the full-width batch (row sharding: no collective)
         ra, rb = D.row_shard(T, rank, world)
         xr = torch.from_numpy(x0[ra:rb].copy()).to(dev)
         hr = glue.add_rms_f16(xr, torch.from_numpy(w).to(dev), 1e-6, d=torch.from_numpy(r0[ra:rb].copy()).to(dev))
         torch.cuda.synchronize()
         gath = [None] * world
-        dist.all_gather_object(gath, (a, b, xs.cpu().numpy(), h.cpu().numpy(), ra, rb, xr.cpu().numpy(), hr.cpu().numpy()))
+        dist.all_gather_object(gath, (a, b, xs.cpu().numpy(), h.cpu().numpy(), ra, rb, xr.cpu().numpy(), hr.cpu().numpy(), fused_ok))
         if rank == 0:
             X = np.zeros((T, N), np.float16); H = np.zeros((T, N), np.float16); XR = np.zeros((T, N), np.float16); HR = np.zeros((T, N), np.float16)
-            for a_, b_, xs_, h_, ra_, rb_, xr_, hr_ in gath:
+            for a_, b_, xs_, h_, ra_, rb_, xr_, hr_, _ in gath:
                 X[:, a_:b_] = xs_; H[:, a_:b_] = h_; XR[ra_:rb_] = xr_; HR[ra_:rb_] = hr_
             ref = HR.astype(np.float64); ulp = np.abs(np.spacing(np.abs(HR))).astype(np.float64)
             ok = np.array_equal(X.view(np.uint16), XR.view(np.uint16)) and \
                 bool((np.abs(H.astype(np.float64) - ref) <= ulp + 1e-5 * np.abs(ref).max()).all())
-            out.put(ok)
+            out.put(ok and all(g_[-1] for g_ in gath))
     finally:
         dist.destroy_process_group()
 

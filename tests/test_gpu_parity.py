@@ -403,3 +403,71 @@ def test_qk_rope_q8(n, nh, nkv, pos0, yarn):
     assert int(err.item()) == 2 == eo and np.array_equal(cache.cpu().numpy(), co)
     with pytest.raises(ValueError): R.qk_rope(cu(qkv.reshape(-1)), ldq, nh, nkv, cu(par), pos0, q16, cache, n)          # err is required
     with pytest.raises(k3.ContextBoundsError): R.qk_rope(cu(qkv.reshape(-1)), ldq, nh, nkv, cu(par), pos0 + 3, q16, cache, n, err=err)
+
+
+# ---- the one-kernel tensor-parallel RMSNorm on ONE GPU: a single rank; two ranks with the other rank's words written beforehand
+# (no kernel waits for another kernel); a wait that nothing answers (bounded: the status word reports it)
+def _tp_words(part, tag):
+    return (np.uint64(tag) << np.uint64(32)) | part.view(np.uint32).astype(np.uint64)
+
+
+def test_tp_rms_fused_single_rank_is_the_unsharded_norm():
+    from caminus_b200 import dist as D
+    T, N = 700, 5120
+    x0, r0, w = synth.add_rms_inputs(T, N, seed=11, dtype=np.float16)
+    F_ = D.TPRmsNormFused(cu(w), N, T, 1e-6, device=DEV)
+    for rep in range(3):                                            # (tags 1, 2, 3: both halves of the buffer)
+        x = cu(x0); h = F_(x, cu(r0)); F_.check()
+        xo, ho = oracle.add_rms_f16(x0, w, 1e-6, r0)
+        assert same(x, xo) and same(h, ho)
+    with pytest.raises(ValueError): F_(cu(np.zeros((T + 1, N), np.float16)))
+    for N2 in (2048, 640, 1288):                                       # rows held in registers (one row / two rows deep), a short last chunk
+        x0, r0, w = synth.add_rms_inputs(T, N2, seed=N2, dtype=np.float16)
+        F2 = D.TPRmsNormFused(cu(w), N2, T, 1e-6, device=DEV)
+        for dd in (r0, None):
+            x = cu(x0); h = F2(x, None if dd is None else cu(dd)); F2.check()
+            tot = np.float32(0) + oracle.rms_partial_f16(x0, dd)
+            xo, ho = oracle.rms_apply_f16(x0, tot, w, 1e-6, N2, dd)
+            assert same(x, xo) and same(h, ho)
+
+
+def test_tp_rms_fused_two_ranks_with_the_peer_words_in_place():
+    from caminus_b200 import lib
+    T, N, world, tag = 300, 2560, 2, 5
+    x0, r0, w = synth.add_rms_inputs(T, N, seed=12, dtype=np.float16)
+    Ns = N // world; L = lib.load(); words = L.cam_tp_rms_words(T, world)
+    parts = [oracle.rms_partial_f16(x0[:, r * Ns:(r + 1) * Ns], r0[:, r * Ns:(r + 1) * Ns]) for r in range(world)]
+    tot = (np.float32(0) + parts[0]) + parts[1]
+    for rank in range(world):
+        other = 1 - rank
+        own = np.zeros(words, np.uint64); half = (tag & 1) * world * T
+        own[half + other * T: half + other * T + T] = _tp_words(parts[other], tag)      # the other rank's partials, as its kernel would have stored them
+        own_d = torch.from_numpy(own.view(np.int64)).to(DEV); peer_d = torch.zeros(words, dtype=torch.int64, device=DEV)
+        ptrs = [0, 0]; ptrs[rank] = own_d.data_ptr(); ptrs[other] = peer_d.data_ptr()
+        peers = torch.tensor(ptrs, dtype=torch.int64, device=DEV); status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        xs = cu(np.ascontiguousarray(x0[:, rank * Ns:(rank + 1) * Ns])); ds = cu(np.ascontiguousarray(r0[:, rank * Ns:(rank + 1) * Ns]))
+        nw = cu(w[rank * Ns:(rank + 1) * Ns].copy()); h = torch.zeros_like(xs)
+        lib.check(L.cam_tp_rms_norm_f16(T, xs.data_ptr(), ds.data_ptr(), nw.data_ptr(), 1e-6, h.data_ptr(), Ns, N, peers.data_ptr(), rank, world, T, tag,
+                                        status.data_ptr(), torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        xo, ho = oracle.rms_apply_f16(x0[:, rank * Ns:(rank + 1) * Ns], tot, w[rank * Ns:(rank + 1) * Ns], 1e-6, N, r0[:, rank * Ns:(rank + 1) * Ns])
+        assert int(status.item()) == 0 and same(xs, xo) and same(h, ho)
+        sent = peer_d.cpu().numpy().view(np.uint64)[half + rank * T: half + rank * T + T]   # what this rank stored into the peer's buffer
+        assert np.array_equal(sent, _tp_words(parts[rank], tag))
+        assert np.array_equal(own_d.cpu().numpy().view(np.uint64)[half + rank * T: half + rank * T + T], _tp_words(parts[rank], tag))
+
+
+def test_tp_rms_fused_wait_runs_out_and_reports():
+    """a peer that never writes: every wait ends at its limit, the status word says so, the rows are left alone, the context lives on"""
+    from caminus_b200 import lib
+    T, Ns, world = 16, 256, 2
+    L = lib.load(); words = L.cam_tp_rms_words(T, world)
+    own = torch.zeros(words, dtype=torch.int64, device=DEV); peer = torch.zeros(words, dtype=torch.int64, device=DEV)
+    peers = torch.tensor([own.data_ptr(), peer.data_ptr()], dtype=torch.int64, device=DEV); status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    x = torch.ones(T, Ns, dtype=torch.float16, device=DEV); nw = torch.ones(Ns, device=DEV); h = torch.zeros_like(x)
+    lib.check(L.cam_tp_rms_norm_f16(T, x.data_ptr(), 0, nw.data_ptr(), 1e-6, h.data_ptr(), Ns, 2 * Ns, peers.data_ptr(), 0, world, T, 1, status.data_ptr(),
+                                    torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1 and not h.any().item()
+    assert float((x + 1).sum().item()) == 2.0 * T * Ns                 # (the context still runs kernels)
+    assert L.cam_tp_rms_norm_f16(T + 1, x.data_ptr(), 0, nw.data_ptr(), 1e-6, h.data_ptr(), Ns, 2 * Ns, peers.data_ptr(), 0, world, T, 1, status.data_ptr(), 0) == -4
