@@ -106,14 +106,23 @@ class TPRmsNormFused:
             mine = (raw[-64:], int(shared[3]))
             everyone = [None] * self.world
             dist.all_gather_object(everyone, mine, group=group)
-            with torch.cuda.device(self.dev):
-                for r, (handle, offset) in enumerate(everyone):
-                    if r == self.rank: continue
-                    base = ctypes.c_void_p()
-                    _lib.check(L.cam_ipc_open(handle, ctypes.byref(base)), f'cam_ipc_open (rank {r})')
-                    self._mapped.append(base)
-                    ptrs[r] = base.value + offset
-            dist.barrier(group=group)                            # every rank has mapped every buffer before the first launch
+            failed = None
+            try:
+                with torch.cuda.device(self.dev):
+                    for r, (handle, offset) in enumerate(everyone):
+                        if r == self.rank: continue
+                        base = ctypes.c_void_p()
+                        _lib.check(L.cam_ipc_open(handle, ctypes.byref(base)), f'cam_ipc_open (rank {r})')
+                        self._mapped.append(base)
+                        ptrs[r] = base.value + offset
+            except Exception as e:                               # (reported below on every rank: no rank is left waiting for this one)
+                failed = e
+            # every rank has mapped every buffer before the first launch, or every rank learns that one could not
+            flag = torch.tensor([0 if failed is None else 1], dtype=torch.int32, device=self.dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+            if int(flag.item()):
+                self.close()
+                raise RuntimeError('TPRmsNormFused: a rank could not map a peer\'s exchange buffer' + (f': {failed}' if failed else '')) from failed
         ptrs[self.rank] = self.buf.data_ptr()
         self.peers = torch.tensor(ptrs, dtype=torch.int64, device=self.dev)
 
