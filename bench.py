@@ -286,6 +286,13 @@ def single_op_lines(torch, dev, peak, only=()):
     line('rms_mul_q8_1_R32768_K2560', Rq * Kq8 * 8 + Rq * Kq8 // 32 * 36,
          timed(lambda i: LB.check(Lc.cam_rms_mul_q8_1(xq.data_ptr(), wq8.data_ptr(), yq8.data_ptr(), q8o.data_ptr(), Rq, 1, 1e-6, Kq8, cs), 'cam_rms_mul_q8_1')), Rq, 'rows_per_s')
     del xq, yq8, q8o
+    # the one-kernel tensor-parallel norm run by a single rank (its own partial is the only word it waits for): the kernel's HBM side
+    from caminus_b200 import dist as DD
+    for Ns_ in (640, 2560):
+        xt = rnd(65536, Ns_).half(); dt_ = rnd(65536, Ns_).half(); ht = torch.empty_like(xt)
+        ft = DD.TPRmsNormFused(torch.ones(Ns_, device=dev), Ns_, 65536, 1e-6, device=dev)
+        line(f'tp_rms_fused_one_rank_T65536_Ns{Ns_}', 65536 * Ns_ * 8, timed(lambda i: ft(xt, dt_, ht)), 65536, 'rows_per_s')
+        ft.check(); del xt, dt_, ht
     xm = rnd(8192, 5120, scale=2.0); ym2 = torch.empty(5120 // 128, 8192, 144, dtype=torch.uint8, device=dev)
     line('quantize_mmq_q8_1_f32_8192x5120_D4', 8192 * 5120 * 4 + 8192 * 40 * 144, timed(lambda i: gguf.quantize_mmq_q8_1(xm, 'D4', y=ym2)), 8192, 'rows_per_s')
     return out

@@ -72,6 +72,22 @@ class Ops:
         if E > 1024: raise ValueError(f'q3m group: E {E} (<= 1024)')
         with _On(self.dev): self.mod.q3p_group((1,), (1024,), ids, I(npairs), I(k), I(E), xs, yd, items, nitems, err)
 
+    def check_flags(self, err, what='prefill'):
+        """after the stream has drained: raise if a launch set the routing flag word (1: a router logit not finite; 2: an expert
+        id out of range), and clear it (python/caminus/prefill/q3m.py:167-173)"""
+        e = int(err.item())
+        if e:
+            err.zero_()
+            raise k3.ContextBoundsError(f'{what}: the routing flag word is {e:#x} (1: a router logit not finite, 2: an id out of range)')
+
+    def check_kv_code(self, err):
+        """after the stream has drained: a Q8_0 KV encoder's error word (q3p_qk_rope_q8 ORs 2 into it for a refused block) raises
+        InvalidKVEncoding; the word stays set (python/caminus/engine/k3.py:1653-1659)"""
+        code = int(err.item())
+        if code:
+            from ..errors import InvalidKVEncoding
+            raise InvalidKVEncoding(f'q3m_prefill: invalid KV encoding (error {code:#x}); cache result is unusable')
+
     def swiglu(self, g, u, y16, n):
         with _On(self.dev):
             self.mod.q3p_swiglu((min(-(-n // 256), 4096),), (256,), g, u, y16, I(n))

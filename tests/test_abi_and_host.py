@@ -87,3 +87,19 @@ def test_synth_is_seeded():
     assert W.shape == (5, 2, 144) and (W[:, :, 0:4].copy().view(np.float16) >= 0).all()
     par = synth.rope_par(yarn_table=synth.yarn_table())
     assert par.size == 258 + 65 and par[256] == np.float32(np.float32(1e6) ** np.float32(-2.0 / 128))
+
+
+def test_flag_word_checks_raise_the_reference_errors():
+    """the third error tier: sticky device flag words read on the host (no GPU needed: the words are plain tensors here)"""
+    import torch
+    from caminus_b200.engine import k3
+    from caminus_b200.errors import InvalidKVEncoding, NumericalFailure
+    from caminus_b200.prefill.q3m_ops import Ops
+    O = Ops.__new__(Ops)                                       # (the checks use no device state)
+    err = torch.tensor([3], dtype=torch.int32)
+    with pytest.raises(k3.ContextBoundsError, match='0x3'): O.check_flags(err, 'chunk')
+    assert int(err.item()) == 0
+    O.check_flags(err); O.check_kv_code(err)
+    err[0] = 2
+    with pytest.raises(InvalidKVEncoding): O.check_kv_code(err)
+    assert int(err.item()) == 2 and issubclass(InvalidKVEncoding, NumericalFailure) and issubclass(NumericalFailure, RuntimeError)

@@ -401,6 +401,9 @@ def test_qk_rope_q8(n, nh, nkv, pos0, yarn):
     R.qk_rope(cu(bad.reshape(-1)), ldq, nh, nkv, cu(par), pos0, q16, cache, n, err=err)
     _, co, eo = oracle.qk_rope_q8(bad, ldq, nh, nkv, par, pos0, cache0, n, yarn=yarn, sum_order=1)
     assert int(err.item()) == 2 == eo and np.array_equal(cache.cpu().numpy(), co)
+    from caminus_b200.errors import InvalidKVEncoding, NumericalFailure
+    with pytest.raises(InvalidKVEncoding): R.check_kv_code(err)                     # the host's reading of the word: terminal, and sticky
+    assert int(err.item()) == 2 and issubclass(InvalidKVEncoding, NumericalFailure)
     with pytest.raises(ValueError): R.qk_rope(cu(qkv.reshape(-1)), ldq, nh, nkv, cu(par), pos0, q16, cache, n)          # err is required
     with pytest.raises(k3.ContextBoundsError): R.qk_rope(cu(qkv.reshape(-1)), ldq, nh, nkv, cu(par), pos0 + 3, q16, cache, n, err=err)
 

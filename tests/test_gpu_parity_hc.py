@@ -265,6 +265,10 @@ def test_router_topk_group():
     lo[5, 2] = np.nan; err.zero_()
     O.topk(cu(lo), E, k, 6.103515625e-5, ids, wts, err, n)
     assert int(err.item()) & 1
+    from caminus_b200.engine import k3
+    with pytest.raises(k3.ContextBoundsError): O.check_flags(err)                   # the host's reading of the flag word: raises and clears
+    assert int(err.item()) == 0
+    O.check_flags(err)
     use = g.choice(E, 12, replace=False)
     ids_np = np.stack([g.choice(use, k, replace=False) for _ in range(n)]).astype(np.int32)
     bound = q3m_ops.items_bound(n * k, E)
