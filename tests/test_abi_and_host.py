@@ -103,3 +103,12 @@ def test_flag_word_checks_raise_the_reference_errors():
     err[0] = 2
     with pytest.raises(InvalidKVEncoding): O.check_kv_code(err)
     assert int(err.item()) == 2 and issubclass(InvalidKVEncoding, NumericalFailure) and issubclass(NumericalFailure, RuntimeError)
+
+
+def test_mmq_buffer_arithmetic_matches_the_reference():
+    """k_pad / y_bytes size the quantised activation buffer as python/caminus/prefill/mmq.py:102-108 does (K padded to 512, 144-byte
+    blocks of 128 values, an 18432-byte tail)"""
+    from caminus_b200.prefill import mmq
+    assert [mmq.k_pad(k) for k in (1, 512, 513, 2048, 2560, 25600)] == [512, 512, 1024, 2048, 2560, 25600]
+    assert mmq.y_bytes(2048, 10) == 2048 // 128 * 10 * 144 + 18432 and mmq.y_bytes(600, 3) == 1024 // 128 * 3 * 144 + 18432
+    assert (mmq.D4, mmq.DS4) == (0, 1)
