@@ -6,8 +6,8 @@
 // roundf(xi / d) with a true division, block = { half d, half sum, int8 qs[32] } = 36 bytes. Unfused forms: q3p_swiglu
 // (kernels/q3m_prefill.hip:515-518), gg_silu_mul (kernels/k3_gguf.hip:74-77), gg_quantize_q8_1 (kernels/k3_gguf.hip:29-36).
 //
-// Mapping: a thread owns 8 consecutive values (one 16-byte load of fp16 gate and up, or two of fp32), 4 adjacent lanes own a
-// block. amax is order-free; the block sum follows the order of the reference's 8-lane quantiser aq_fill
+// Mapping of the exact kernel: a thread owns 8 consecutive values (one 16-byte load of fp16 gate and up, or two of fp32), 4 adjacent
+// lanes own a block (the fused fast pass further down takes 16 values per thread, 2 lanes per block). amax is order-free; the block sum follows the order of the reference's 8-lane quantiser aq_fill
 // (kernels/k3_gguf_ops.h:83-120): (e0 + e1) + (e2 + e3) per group of four, then partners 4, 2, 1 over the 8 groups. A lane
 // holds groups 2q and 2q + 1 (q its place in the quad): partner 4 is lane q ^ 2, partner 2 is lane q ^ 1, partner 1 is the
 // lane's other group. d and the codes are quantize_q8_1_lane's bits whatever the order.
@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_1_kernel(const T * __restrict__
 // memory system leaves time for. The fast pass therefore evaluates h^ = g * rcp(1 + ex2(-g log2 e)) * u on the
 // special-function unit and quantises with a reciprocal, which is NOT bit-reproducible by itself. It is used only where it
 // provably gives the exact statements' bytes. With h the exact value of an element, |h^ - h| <= EPS |h|, EPS = 1.35e-6,
-// whenever g >= -8: against the true value the fast pass is within 1.02e-6 (the rounding of ex2's argument, 6e-8 |g|, and
+// whenever g >= -8 (and |g| >= 3e-38, which only an fp32 gate can miss): against the true value the fast pass is within 1.02e-6 (the rounding of ex2's argument, 6e-8 |g|, and
 // ex2.approx's 2^-22, both scaled by e / (1 + e) <= 1; the rounding of 1 + e; rcp.approx's 2^-23; two products) and the exact
 // sequence within 3.2e-7 (2.2 ulp measured over the whole range, and its product). From that:
 //   d:     d^ = amax^ / 127 is within 1.53e-6 (< 26 fp32 ulps) of the exact fp32 d. If d^'s low 13 bits are more than 40 away
@@ -91,58 +91,76 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_1_kernel(const T * __restrict__
 // fast pass is the fp16 rounding of the same-order sum of the h^: it can differ from the exact statements' sum by one fp16
 // ulp (or by 1.6e-6 sum |h| when the values cancel). The reference reports that field and does not gate it
 // (tests/engine/golden_util.py:145-146); the strict kernel above gives its exact bytes too.
-// one warp-wide step over 8 blocks (256 values) starting at group `base` (a multiple of 32). FULL: all 32 lanes have a group.
+// One warp-wide step over 16 blocks (512 values) starting at pair `base` (a multiple of 32): 16 values per lane, two lanes per block.
+// (With 8 values per lane and four lanes per block the same pass ran at 88 % of the copy bandwidth: the work that does not depend on
+// the number of values (loop, indices, margins, ballots, store addresses) was a third of its instructions; spent once per 16 values
+// the kernel is memory-bound.) FULL: all 32 lanes have a pair.
+// Block sum in aq_fill's order: a lane holds groups 4 q .. 4 q + 3 (q its place in the pair): partner 4 is the other lane, partners 2
+// and 1 are the lane's own groups.
 template <typename T, bool FULL>
-CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y, int base, int ngroups, int lane) {
-    const int gi = base + lane, q = lane & 3;
-    const bool on = FULL || gi < ngroups;
-    float gv[8], uv[8], h[8];
-    if (on) { Load8<T>::get(g + (size_t)gi * 8, gv); Load8<T>::get(u + (size_t)gi * 8, uv); }
-    else {
+CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y, int base, int npairs, int lane) {
+    const int pi = base + lane, q = lane & 1;
+    const bool on = FULL || pi < npairs;
+    float gv[16], uv[16], h[16];
+    if (on) {
+        float t[8];
+        Load8<T>::get(g + (size_t)pi * 16, t);
 #pragma unroll
-        for (int k = 0; k < 8; k++) { gv[k] = 0.0f; uv[k] = 0.0f; }
+        for (int k = 0; k < 8; k++) gv[k] = t[k];
+        Load8<T>::get(g + (size_t)pi * 16 + 8, t);
+#pragma unroll
+        for (int k = 0; k < 8; k++) gv[8 + k] = t[k];
+        Load8<T>::get(u + (size_t)pi * 16, t);
+#pragma unroll
+        for (int k = 0; k < 8; k++) uv[k] = t[k];
+        Load8<T>::get(u + (size_t)pi * 16 + 8, t);
+#pragma unroll
+        for (int k = 0; k < 8; k++) uv[8 + k] = t[k];
+    } else {
+#pragma unroll
+        for (int k = 0; k < 16; k++) { gv[k] = 0.0f; uv[k] = 0.0f; }
     }
-    float gmin = gv[0], amax = 0.0f;
+    float gmin = gv[0], amax = 0.0f, gsm = fabsf(gv[0]);
 #pragma unroll
-    for (int k = 1; k < 8; k++) gmin = fminf(gmin, gv[k]);
+    for (int k = 1; k < 16; k++) { gmin = fminf(gmin, gv[k]); if (sizeof(T) == 4) gsm = fminf(gsm, fabsf(gv[k])); }
 #pragma unroll
-    for (int k = 0; k < 8; k++) {
+    for (int k = 0; k < 16; k++) {
         const float e = ex2_approx(fmul(gv[k], -0x1.715476p+0f));
         h[k] = fmul(fmul(gv[k], rcp_approx(fadd(1.0f, e))), uv[k]);
         amax = fmaxf(amax, fabsf(h[k]));
     }
     amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 2));
-    float sa = fadd(fadd(h[0], h[1]), fadd(h[2], h[3])), sb = fadd(fadd(h[4], h[5]), fadd(h[6], h[7]));
-    sa = fadd(sa, __shfl_xor_sync(CAM_FULL, sa, 2)); sb = fadd(sb, __shfl_xor_sync(CAM_FULL, sb, 2));
-    sa = fadd(sa, __shfl_xor_sync(CAM_FULL, sa, 1)); sb = fadd(sb, __shfl_xor_sync(CAM_FULL, sb, 1));
-    const float sum = fadd(sa, sb);
-    const float d = fmul(amax, 0x1.020408p-7f);                             // amax / 127 within 1.2e-7
-    const float inv = rcp_approx(d);
-    // the quotient's two ends, t (1 +- 3.2e-6), each rounded to an integer (ties to even) in the low mantissa bits of
-    // t + 1.5 * 2^23: equal integers mean no rounding boundary (and no tie) lies within the error interval of the quotient
-    const float inv_hi = fmul(inv, 0x1.000036p+0f), inv_lo = fmul(inv, 0x1.ffff94p-1f);
-    uint32_t v[8], differ = 0;
+    float sg[4];
 #pragma unroll
-    for (int k = 0; k < 8; k++) {
+    for (int j = 0; j < 4; j++) {
+        sg[j] = fadd(fadd(h[4 * j], h[4 * j + 1]), fadd(h[4 * j + 2], h[4 * j + 3]));
+        sg[j] = fadd(sg[j], __shfl_xor_sync(CAM_FULL, sg[j], 1));                                         // partner 4
+    }
+    const float sum = fadd(fadd(sg[0], sg[2]), fadd(sg[1], sg[3]));                                        // partners 2, 1
+    const float d = fmul(amax, 0x1.020408p-7f);
+    const float inv = rcp_approx(d);
+    const float inv_hi = fmul(inv, 0x1.000036p+0f), inv_lo = fmul(inv, 0x1.ffff94p-1f);
+    uint32_t v[16], differ = 0;
+#pragma unroll
+    for (int k = 0; k < 16; k++) {
         v[k] = __float_as_uint(ffma(h[k], inv_hi, 12582912.0f));
         differ |= v[k] ^ __float_as_uint(ffma(h[k], inv_lo, 12582912.0f));
     }
     const int low = (int)(__float_as_uint(d) & 0x1fffu) - 0x1000;
-    const bool redo = differ != 0 || !(gmin >= -8.0f) || !(d >= 6.2e-5f && d < 6.0e4f) || (low >= -40 && low <= 40) || !(fabsf(sum) < 3.0e38f);
+    const bool redo = differ != 0 || !(gmin >= -8.0f) || !(d >= 6.2e-5f && d < 6.0e4f) || (low >= -40 && low <= 40) || !(fabsf(sum) < 3.0e38f) ||
+                      (sizeof(T) == 4 && on && !(gsm >= 3.0e-38f));
     const uint32_t mask = __ballot_sync(CAM_FULL, redo && on);
-    const uint32_t quad = (mask | (mask >> 1) | (mask >> 2) | (mask >> 3)) & 0x11111111u;   // bit 4 j: block j of this warp
-    if (on && !((quad >> (lane & ~3)) & 1u)) {
-        const uint32_t w0 = __byte_perm(__byte_perm(v[0], v[1], 0x0040), __byte_perm(v[2], v[3], 0x0040), 0x5410);
-        const uint32_t w1 = __byte_perm(__byte_perm(v[4], v[5], 0x0040), __byte_perm(v[6], v[7], 0x0040), 0x5410);
-        uint32_t * o = reinterpret_cast<uint32_t *>(y + (size_t)(gi >> 2) * 36);
+    const uint32_t pairs = (mask | (mask >> 1)) & 0x55555555u;              // bit 2 j: block j of this warp
+    if (on && !((pairs >> (lane & ~1)) & 1u)) {
+        uint32_t * o = reinterpret_cast<uint32_t *>(y + (size_t)(pi >> 1) * 36);
         if (q == 0) __stcs(o, f2_to_h2(d, sum));
-        __stcs(o + 1 + 2 * q, w0);
-        __stcs(o + 2 + 2 * q, w1);
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            __stcs(o + 1 + 4 * q + j, __byte_perm(__byte_perm(v[4 * j], v[4 * j + 1], 0x0040), __byte_perm(v[4 * j + 2], v[4 * j + 3], 0x0040), 0x5410));
     }
-    // exact recomputation of the flagged blocks: the whole warp, one lane per value (uniform: quad is the same in every lane)
-    for (uint32_t m = quad; m; m &= m - 1) {
-        const size_t blk = (size_t)(base >> 2) + ((__ffs(m) - 1) >> 2);
+    // exact recomputation of the flagged blocks: the whole warp, one lane per value (uniform: pairs is the same in every lane)
+    for (uint32_t m = pairs; m; m &= m - 1) {
+        const size_t blk = (size_t)(base >> 1) + ((__ffs(m) - 1) >> 1);
         const float x = fmul(cam_silu(Load8<T>::one(g + blk * 32 + lane)), Load8<T>::one(u + blk * 32 + lane));
         float am = fabsf(x);
 #pragma unroll
@@ -159,16 +177,15 @@ CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, 
     }
 }
 
-// nb < 2^29 blocks per launch (32-bit group indices); the host splits longer inputs
 template <typename T>
 __global__ void __launch_bounds__(Q8_THREADS) swiglu_q8_fast_kernel(const T * __restrict__ g, const T * __restrict__ u,
-                                                                    uint8_t * __restrict__ y, int nb) {
+                                                                      uint8_t * __restrict__ y, int nb) {
     const int lane = threadIdx.x & 31;
-    const int ngroups = nb * 4;
+    const int npairs = nb * 2;
     const int stride = gridDim.x * Q8_THREADS;
     int base = blockIdx.x * Q8_THREADS + (threadIdx.x & ~31);
-    for (; base + 32 <= ngroups; base += stride) swiglu_q8_step<T, true>(g, u, y, base, ngroups, lane);
-    if (base < ngroups) swiglu_q8_step<T, false>(g, u, y, base, ngroups, lane);
+    for (; base + 32 <= npairs; base += stride) swiglu_q8_step<T, true>(g, u, y, base, npairs, lane);
+    if (base < npairs) swiglu_q8_step<T, false>(g, u, y, base, npairs, lane);
 }
 
 // the last, partial block (n % 32 values, the rest 0): one warp, one lane per value
@@ -208,7 +225,7 @@ int launch_q8(const T * g, const T * u, void * y, long n, cudaStream_t stream) {
             const long piece = 1L << 28;                                   // blocks per launch
             for (long b0 = 0; b0 < nb; b0 += piece) {
                 const long m = nb - b0 < piece ? nb - b0 : piece;
-                const long w = (m * 4 + Q8_THREADS - 1) / Q8_THREADS;
+                const long w = (m * 2 + Q8_THREADS - 1) / Q8_THREADS;
                 swiglu_q8_fast_kernel<T><<<cam_resident_grid(swiglu_q8_fast_kernel<T>, Q8_THREADS, 0, w), Q8_THREADS, 0, stream>>>(
                     g + b0 * 32, u + b0 * 32, (uint8_t *)y + b0 * 36, (int)m);
             }

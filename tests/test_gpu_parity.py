@@ -181,6 +181,23 @@ def test_swiglu_q8_1_hard_inputs(kind):
     if kind != 'nonfinite': assert sums_close(y, want, oracle.swiglu_f32_from_f16(gate, up))
 
 
+def test_swiglu_q8_1_f32_denormal_gates():
+    """fp32 gates so small that the exact statements' g / (1 + e) is a denormal (its rounding is not the fast product's), next to
+    huge ups that bring the product back to the block's scale; zero gates; the fused entries still give the exact statements' bytes"""
+    g_ = np.random.default_rng(77); n = 1 << 16
+    gate = (g_.standard_normal(n) * 1.5).astype(np.float32); up = (g_.standard_normal(n) * 1.5).astype(np.float32)
+    idx = np.arange(0, n, 37)
+    gate[idx] = (g_.integers(1, 1 << 20, idx.size) * np.float64(1.4e-45)).astype(np.float32) * np.where(g_.random(idx.size) < 0.5, -1, 1).astype(np.float32)
+    up[idx] = (g_.random(idx.size).astype(np.float32) + 0.5) * np.float32(2e38)
+    gate[5::101] = 0.0
+    want = oracle.swiglu_q8_1(gate, up, sum_order=1)
+    for strict in (False, True):
+        y = gguf.swiglu_q8_1(cu(gate), cu(up), strict=strict).cpu().numpy()
+        d, s_, q = oracle.q8_split(y); d1, s1, q1 = oracle.q8_split(want)
+        assert np.array_equal(q, q1) and np.array_equal(d.view(np.uint16), d1.view(np.uint16))
+        if strict: assert np.array_equal(y, want)
+
+
 def test_swiglu_golden_reference_host_path(golden):
     """against the reference's host path (numpy float32 silu, q8_host): the flip rule of tests/engine/golden_util.py:132-173"""
     f = golden('swiglu')
