@@ -5,80 +5,92 @@
 // q = roundf(x * d_inv), d = 1.0f / d_inv; D4 stores four fp32 d, DS4 four (fp16 d, fp16 sum) with sum = ((x0 + x1) + x2) + x3
 // per four values then partners 4, 2, 1. An all-zero group stores d = 0 and codes 0 explicitly.
 //
-// Mapping: a warp per block of 128 values: a lane holds 4 consecutive values (one 16-byte load of fp32, 8-byte of fp16), the 8
-// lanes of a group reduce by shuffles, the warp writes the block's 128 codes as one 4-byte word per lane and the four scales
-// from lanes 0, 8, 16, 24: 144 contiguous bytes. Consecutive warps take consecutive rows of the same K-block, so their blocks
-// are adjacent in memory.
+// Mapping: a lane holds 16 consecutive values (four 16-byte loads of fp32, 8-byte of fp16), two lanes a group of 32, eight lanes a
+// block of 128, a warp four consecutive K-blocks of a row; a lane writes its 16 codes as one 16-byte store, the even lanes the
+// groups' scales. Consecutive blocks of the grid take consecutive rows, so their 144-byte blocks are adjacent in memory.
 #include "cam_common.cuh"
 
 namespace {
 
 // MODE 0: values = x (fp32). MODE 1: silu(x) * u (fp32). MODE 2: silu(g) * u (fp16 in).
-// what a lane loads for its four values of one task (held raw so that two tasks' loads fly together)
-template <int MODE> struct MmqRaw { float4 a, b; };
-template <> struct MmqRaw<2> { uint2 a, b; };
+// A lane takes 16 consecutive values (two lanes a group of 32, eight lanes a block of 128, a warp four K-blocks), so the group's
+// two IEEE divisions and its reductions are spent once per 16 values of a lane. What a lane loads is held raw, so that two rows'
+// loads fly together. kvalid and ld are multiples of 4: each of the lane's four quads is all inside the row or all outside.
+template <int MODE> struct MmqRaw { float4 a[4], b[4]; };
+template <> struct MmqRaw<0> { float4 a[4]; };
+template <> struct MmqRaw<2> { uint2 a[4], b[4]; };
 
-// a lane's four values of K-block kb of row r
 template <int MODE>
-CAM_DEV MmqRaw<MODE> mmq_load(const void * __restrict__ xv, const void * __restrict__ uv, int kb, int r, int kvalid, long ld, int lane, bool & in) {
-    const int k = kb * 128 + 4 * lane;
-    MmqRaw<MODE> raw;
-    in = k < kvalid;            // (kvalid and ld are multiples of 4: a lane's four values are all inside or all outside)
-    if (in) {
+CAM_DEV void mmq_load(MmqRaw<MODE> & raw, const void * __restrict__ xv, const void * __restrict__ uv, int k, size_t row_at, int kvalid) {
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+        const bool in = k + 4 * s < kvalid;
         if constexpr (MODE == 2) {
-            raw.a = __ldg(reinterpret_cast<const uint2 *>((const uint16_t *)xv + (size_t)r * ld + k));
-            raw.b = __ldg(reinterpret_cast<const uint2 *>((const uint16_t *)uv + (size_t)r * ld + k));
+            raw.a[s] = in ? __ldg(reinterpret_cast<const uint2 *>((const uint16_t *)xv + row_at + k + 4 * s)) : make_uint2(0u, 0u);
+            raw.b[s] = in ? __ldg(reinterpret_cast<const uint2 *>((const uint16_t *)uv + row_at + k + 4 * s)) : make_uint2(0u, 0u);
         } else {
-            raw.a = __ldg(reinterpret_cast<const float4 *>((const float *)xv + (size_t)r * ld + k));
-            if constexpr (MODE == 1) raw.b = __ldg(reinterpret_cast<const float4 *>((const float *)uv + (size_t)r * ld + k));
+            raw.a[s] = in ? __ldg(reinterpret_cast<const float4 *>((const float *)xv + row_at + k + 4 * s)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if constexpr (MODE == 1) raw.b[s] = in ? __ldg(reinterpret_cast<const float4 *>((const float *)uv + row_at + k + 4 * s)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
     }
-    return raw;
 }
-CAM_DEV void mmq_values(const MmqRaw<0> & raw, float (&v)[4]) { v[0] = raw.a.x; v[1] = raw.a.y; v[2] = raw.a.z; v[3] = raw.a.w; }
-CAM_DEV void mmq_values(const MmqRaw<1> & raw, float (&v)[4]) {
-    v[0] = fmul(cam_silu(raw.a.x), raw.b.x); v[1] = fmul(cam_silu(raw.a.y), raw.b.y);
-    v[2] = fmul(cam_silu(raw.a.z), raw.b.z); v[3] = fmul(cam_silu(raw.a.w), raw.b.w);
+// (a quad outside the row loads zeros: silu(0) * 0 = 0 exactly)
+CAM_DEV void mmq_values(const MmqRaw<0> & raw, float (&v)[16]) {
+#pragma unroll
+    for (int s = 0; s < 4; s++) { v[4 * s] = raw.a[s].x; v[4 * s + 1] = raw.a[s].y; v[4 * s + 2] = raw.a[s].z; v[4 * s + 3] = raw.a[s].w; }
 }
-CAM_DEV void mmq_values(const MmqRaw<2> & raw, float (&v)[4]) {
-    const float2 g0 = h2_to_f2(raw.a.x), g1 = h2_to_f2(raw.a.y), u0 = h2_to_f2(raw.b.x), u1 = h2_to_f2(raw.b.y);
-    v[0] = fmul(cam_silu(g0.x), u0.x); v[1] = fmul(cam_silu(g0.y), u0.y);
-    v[2] = fmul(cam_silu(g1.x), u1.x); v[3] = fmul(cam_silu(g1.y), u1.y);
+CAM_DEV void mmq_values(const MmqRaw<1> & raw, float (&v)[16]) {
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+        v[4 * s] = fmul(cam_silu(raw.a[s].x), raw.b[s].x); v[4 * s + 1] = fmul(cam_silu(raw.a[s].y), raw.b[s].y);
+        v[4 * s + 2] = fmul(cam_silu(raw.a[s].z), raw.b[s].z); v[4 * s + 3] = fmul(cam_silu(raw.a[s].w), raw.b[s].w);
+    }
+}
+CAM_DEV void mmq_values(const MmqRaw<2> & raw, float (&v)[16]) {
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+        const float2 g0 = h2_to_f2(raw.a[s].x), g1 = h2_to_f2(raw.a[s].y), u0 = h2_to_f2(raw.b[s].x), u1 = h2_to_f2(raw.b[s].y);
+        v[4 * s] = fmul(cam_silu(g0.x), u0.x); v[4 * s + 1] = fmul(cam_silu(g0.y), u0.y);
+        v[4 * s + 2] = fmul(cam_silu(g1.x), u1.x); v[4 * s + 3] = fmul(cam_silu(g1.y), u1.y);
+    }
 }
 
-// the lane's code word and (in lanes 0, 8, 16, 24) the group's scale word
+// the lane's 16 codes and the group's scale word. The DS4 sum in the reference's order: ((x0 + x1) + x2) + x3 per quad (its
+// thread), then the quads' partners 4 (the other lane), 2 and 1 (inside the lane).
 template <int LAYOUT>
-CAM_DEV void mmq_quant(const float (&v)[4], uint32_t & w, uint32_t & hdr) {
-    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-    float sum = fadd(fadd(fadd(v[0], v[1]), v[2]), v[3]);
+CAM_DEV void mmq_quant(const float (&v)[16], uint4 & w, uint32_t & hdr) {
+    float amax = 0.0f, ts[4];
 #pragma unroll
-    for (int o = 4; o > 0; o >>= 1) {
-        amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, o));
-        if (LAYOUT == 1) sum = fadd(sum, __shfl_xor_sync(CAM_FULL, sum, o));
+    for (int s = 0; s < 4; s++) {
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[4 * s]), fabsf(v[4 * s + 1])), fmaxf(fabsf(v[4 * s + 2]), fabsf(v[4 * s + 3]))));
+        ts[s] = fadd(fadd(fadd(v[4 * s], v[4 * s + 1]), v[4 * s + 2]), v[4 * s + 3]);
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 1));
+    float sum = 0.0f;
+    if (LAYOUT == 1) {
+#pragma unroll
+        for (int s = 0; s < 4; s++) ts[s] = fadd(ts[s], __shfl_xor_sync(CAM_FULL, ts[s], 1));
+        sum = fadd(fadd(ts[0], ts[2]), fadd(ts[1], ts[3]));
     }
     float d = 0.0f;
-    w = 0;
+    uint32_t ww[4] = {0u, 0u, 0u, 0u};
     if (amax != 0.0f) {
         const float d_inv = fdiv(127.0f, amax);
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
+        for (int c = 0; c < 16; c++) {
             const float t = fmul(v[c], d_inv);
             const int q = fabsf(t) < 127.5f ? __float2int_rn(roundf(t)) : 0;
-            w |= (uint32_t)(q & 0xff) << (8 * c);
+            ww[c >> 2] |= (uint32_t)(q & 0xff) << (8 * (c & 3));
         }
         d = fdiv(1.0f, d_inv);
     }
+    w = make_uint4(ww[0], ww[1], ww[2], ww[3]);
     hdr = LAYOUT == 0 ? __float_as_uint(d) : f2_to_h2(d, sum);
 }
-CAM_DEV void mmq_write(uint8_t * __restrict__ blk, int lane, uint32_t w, uint32_t hdr) {
-    __stcs(reinterpret_cast<uint32_t *>(blk + 16) + lane, w);
-    if ((lane & 7) == 0) reinterpret_cast<uint32_t *>(blk)[lane >> 3] = hdr;
-}
-template <int LAYOUT>
-CAM_DEV void mmq_block(const float (&v)[4], uint8_t * __restrict__ blk, int lane) {
-    uint32_t w, hdr;
-    mmq_quant<LAYOUT>(v, w, hdr);
-    mmq_write(blk, lane, w, hdr);
+// blk: the lane's K-block (lanes 8 b .. 8 b + 7 of the warp hold K-block b of the warp's four)
+CAM_DEV void mmq_write(uint8_t * __restrict__ blk, int lane, uint4 w, uint32_t hdr) {
+    st128_stream(blk + 16 + (lane & 7) * 16, w);
+    if ((lane & 1) == 0) reinterpret_cast<uint32_t *>(blk)[(lane >> 1) & 3] = hdr;
 }
 
 // The indexed forms of the reference's quantiser (kernels/ggml_mmq/quantize_mmq.cuh:41-140; wrappers
@@ -89,47 +101,53 @@ template <int LAYOUT, bool SCATTER>
 __global__ void __launch_bounds__(256) mmq_q8_1_rows_kernel(const float * __restrict__ x, const int * __restrict__ ids, uint8_t * __restrict__ y,
                                                             int kvalid, int nkb, long ld, int nrows, int k, int ncols) {
     const int lane = threadIdx.x & 31;
-    for (int kb = blockIdx.y * 8 + (threadIdx.x >> 5); kb < nkb; kb += gridDim.y * 8)
-    for (int r = blockIdx.x; r < nrows; r += gridDim.x) {
-        const int kk = kb * 128 + 4 * lane;
-        int src = r;
-        if (!SCATTER && ids) src = min(max(__ldg(ids + r), 0), nrows - 1);
-        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (kk < kvalid) {
-            const float4 a = __ldg(reinterpret_cast<const float4 *>(x + (size_t)src * ld + kk));
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    for (int kb0 = (blockIdx.y * 8 + (threadIdx.x >> 5)) * 4; kb0 < nkb; kb0 += gridDim.y * 32) {
+        const int kb = kb0 + (lane >> 3), kk = kb * 128 + (lane & 7) * 16;
+        const bool kon = kb < nkb;
+        for (int r = blockIdx.x; r < nrows; r += gridDim.x) {
+            int src = r;
+            if (!SCATTER && ids) src = min(max(__ldg(ids + r), 0), nrows - 1);
+            MmqRaw<0> raw;
+            mmq_load<0>(raw, x, nullptr, kk, (size_t)src * ld, kon ? kvalid : 0);
+            float v[16];
+            mmq_values(raw, v);
+            uint4 w; uint32_t hdr;
+            mmq_quant<LAYOUT>(v, w, hdr);
+            if (!kon) continue;                                   // (after the exchanges: every lane takes part in them)
+            if (!SCATTER) mmq_write(y + ((size_t)kb * nrows + r) * 144, lane, w, hdr);
+            else
+                for (int slot = 0; slot < k; slot++) {
+                    const int c = min(max(__ldg(ids + (size_t)r * k + slot), 0), ncols - 1);
+                    mmq_write(y + ((size_t)kb * ncols + c) * 144, lane, w, hdr);
+                }
         }
-        uint32_t w, hdr;
-        mmq_quant<LAYOUT>(v, w, hdr);
-        if (!SCATTER) mmq_write(y + ((size_t)kb * nrows + r) * 144, lane, w, hdr);
-        else
-            for (int slot = 0; slot < k; slot++) {
-                const int c = min(max(__ldg(ids + (size_t)r * k + slot), 0), ncols - 1);
-                mmq_write(y + ((size_t)kb * ncols + c) * 144, lane, w, hdr);
-            }
     }
 }
 
-// grid.x walks the rows, grid.y groups of 8 K-blocks (one per warp): a block reads 4 KB of a row; two rows per pass, both rows'
+// grid.x walks the rows, grid.y groups of 32 K-blocks (four per warp): a block reads 16 KB of a row; two rows per pass, both rows'
 // loads issued before either is used. (No index is divided: a 64-bit division per task costs more than the task's arithmetic.)
 template <int MODE, int LAYOUT>
 __global__ void __launch_bounds__(256) mmq_q8_1_kernel(const void * __restrict__ xv, const void * __restrict__ uv, uint8_t * __restrict__ y,
                                                        int kvalid, int nkb, long ld, int rows) {
     const int lane = threadIdx.x & 31;
-    for (int kb = blockIdx.y * 8 + (threadIdx.x >> 5); kb < nkb; kb += gridDim.y * 8) {
+    for (int kb0 = (blockIdx.y * 8 + (threadIdx.x >> 5)) * 4; kb0 < nkb; kb0 += gridDim.y * 32) {
+        const int kb = kb0 + (lane >> 3), k = kb * 128 + (lane & 7) * 16;
+        const bool kon = kb < nkb;
+        const int kv = kon ? kvalid : 0;
         for (int r = blockIdx.x; r < rows; r += 2 * gridDim.x) {
             const int r2 = r + gridDim.x;
-            bool in0, in1 = false;
-            const MmqRaw<MODE> a0 = mmq_load<MODE>(xv, uv, kb, r, kvalid, ld, lane, in0);
-            MmqRaw<MODE> a1;
-            if (r2 < rows) a1 = mmq_load<MODE>(xv, uv, kb, r2, kvalid, ld, lane, in1);
-            float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            if (in0) mmq_values(a0, v);
-            mmq_block<LAYOUT>(v, y + ((size_t)kb * rows + r) * 144, lane);
+            MmqRaw<MODE> a0, a1;
+            mmq_load<MODE>(a0, xv, uv, k, (size_t)r * ld, kv);
+            if (r2 < rows) mmq_load<MODE>(a1, xv, uv, k, (size_t)r2 * ld, kv);
+            float v[16];
+            uint4 w; uint32_t hdr;
+            mmq_values(a0, v);
+            mmq_quant<LAYOUT>(v, w, hdr);
+            if (kon) mmq_write(y + ((size_t)kb * rows + r) * 144, lane, w, hdr);
             if (r2 < rows) {
-                float v1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                if (in1) mmq_values(a1, v1);
-                mmq_block<LAYOUT>(v1, y + ((size_t)kb * rows + r2) * 144, lane);
+                mmq_values(a1, v);
+                mmq_quant<LAYOUT>(v, w, hdr);
+                if (kon) mmq_write(y + ((size_t)kb * rows + r2) * 144, lane, w, hdr);
             }
         }
     }
@@ -159,10 +177,11 @@ static dim3 mmq_grid(K kernel, long nx, long ny) {
 // [1e-30, 3e38)) is recomputed by the whole warp with the exact statements, one lane per value. Every stored byte is
 // therefore the exact statements' byte.
 //
-// Mapping: a lane holds 8 consecutive values (one 16-byte load of fp16 gate and up), 4 lanes a group of 32, a half-warp a
-// block of 128; a warp takes two K-blocks of four consecutive rows (4 "chunks" of 256 values). The four candidates of a
-// lane quad (one per chunk) are moved one to each of its lanes, so that the exact evaluation and the two IEEE divisions run
-// once per four chunks; that lane also stores the group's scale.
+// Mapping: a lane holds 16 consecutive values (two 16-byte loads of fp16 gate and up), 2 lanes a group of 32, 8 lanes a block
+// of 128; a warp takes four K-blocks of two consecutive rows (2 "chunks" of 512 values). The two candidates of a lane pair
+// (one per chunk) are moved one to each of its lanes, so that the exact evaluation and the two IEEE divisions run once per
+// two chunks; that lane also stores the group's scale. (16 values per lane: the per-step work that does not depend on the
+// number of values is spent half as often as with 8.)
 CAM_DEV float max_nan(float a, float b) { float r; asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
 // bits |= bit where |h| >= thr (a compare and a predicated OR)
 CAM_DEV void or_if_ge(uint32_t & bits, float h, float thr, uint32_t bit) {
@@ -195,55 +214,72 @@ template <> struct Raw8<float> {
     }
 };
 
-// a warp's task: K-blocks 2 kp, 2 kp + 1 (one per half-warp) of rows r0 .. r0 + 3
+// a warp's task: K-blocks 4 kq .. 4 kq + 3 (8 lanes each, 16 values per lane) of rows r0, r0 + 1
 struct MmqTask {
     int r0, kb, k;
     bool kon, kin;
-    CAM_DEV MmqTask(int kp, int rq, int lane, int nkb, int kvalid) {
-        r0 = rq * 4;
-        kb = kp * 2 + (lane >> 4); k = kb * 128 + (lane & 15) * 8;
+    CAM_DEV MmqTask(int kq, int rp, int lane, int nkb, int kvalid) {
+        r0 = rp * 2;
+        kb = kq * 4 + (lane >> 3); k = kb * 128 + (lane & 7) * 16;
         kon = kb < nkb; kin = kon && k < kvalid;
     }
 };
 
+// chunk c (row r0 + c) of a task: a lane's 16 values as two loads of 8
 template <typename T>
-CAM_DEV void mmq_fetch(const T * __restrict__ g, const T * __restrict__ u, const MmqTask & t, long ld, int rows, Raw8<T> (&rg)[4], Raw8<T> (&ru)[4]) {
+CAM_DEV void mmq_fetch(const T * __restrict__ g, const T * __restrict__ u, const MmqTask & t, long ld, int rows, Raw8<T> (&rg)[2][2], Raw8<T> (&ru)[2][2]) {
     const T * gp = g + (size_t)t.r0 * ld + t.k, * up = u + (size_t)t.r0 * ld + t.k;
 #pragma unroll
-    for (int c = 0; c < 4; c++) {
-        if (t.kin && t.r0 + c < rows) { rg[c].load(gp + c * ld); ru[c].load(up + c * ld); }
-        else { rg[c].fill(1.0f); ru[c].fill(0.0f); }                  // h = 0 on both passes
-    }
+    for (int c = 0; c < 2; c++)
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+            if (t.kin && t.r0 + c < rows) { rg[c][hf].load(gp + c * ld + 8 * hf); ru[c][hf].load(up + c * ld + 8 * hf); }
+            else { rg[c][hf].fill(1.0f); ru[c][hf].fill(0.0f); }      // h = 0 on both passes
+        }
 }
 
 // PF: the next task's values are loaded before this task's arithmetic (fp16: 32 more registers)
 template <typename T, bool PF>
 __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y,
                                                                  int kvalid, int nkb, long ld, int rows) {
-    const int lane = threadIdx.x & 31, qb = lane & 28, qi = lane & 3;
-    // grid.x walks groups of four rows (8 per block, one per warp), grid.y the pairs of K-blocks; no index is divided
-    const int nrq = (rows + 3) >> 2, nkp = (nkb + 1) >> 1;
-    const int rq0 = blockIdx.x * 8 + (threadIdx.x >> 5), rstride = gridDim.x * 8;
-    if (rq0 >= nrq) return;
-    int kp = blockIdx.y, rq = rq0;
-    Raw8<T> rg[4], ru[4], ng[4], nu[4];
-    if (PF && kp < nkp) mmq_fetch(g, u, MmqTask(kp, rq, lane, nkb, kvalid), ld, rows, rg, ru);
-    while (kp < nkp) {
-        const MmqTask t(kp, rq, lane, nkb, kvalid);
-        const int kp_now = kp;
-        rq += rstride;                                                // the next task
-        if (rq >= nrq) { rq = rq0; kp += gridDim.y; }
+    const int lane = threadIdx.x & 31, pb = lane & 30, pi = lane & 1;      // a group of 32 values = the lane pair pb, pb + 1
+    // grid.x walks pairs of rows (8 per block, one per warp), grid.y the quads of K-blocks; no index is divided
+    const int nrp = (rows + 1) >> 1, nkq = (nkb + 3) >> 2;
+    const int rp0 = blockIdx.x * 8 + (threadIdx.x >> 5), rstride = gridDim.x * 8;
+    if (rp0 >= nrp) return;
+    int kq = blockIdx.y, rp = rp0;
+    Raw8<T> rg[2][2], ru[2][2], ng[2][2], nu[2][2];
+    if (PF && kq < nkq) mmq_fetch(g, u, MmqTask(kq, rp, lane, nkb, kvalid), ld, rows, rg, ru);
+    while (kq < nkq) {
+        const MmqTask t(kq, rp, lane, nkb, kvalid);
+        const int kq_now = kq;
+        rp += rstride;                                                // the next task
+        if (rp >= nrp) { rp = rp0; kq += gridDim.y; }
         if (!PF) mmq_fetch(g, u, t, ld, rows, rg, ru);
-        else if (kp < nkp) mmq_fetch(g, u, MmqTask(kp, rq, lane, nkb, kvalid), ld, rows, ng, nu);
-        float h[4][8], eg = 1.0f, eu = 0.0f;
+        else if (kq < nkq) mmq_fetch(g, u, MmqTask(kq, rp, lane, nkb, kvalid), ld, rows, ng, nu);
+        float h[2][16], eg = 1.0f, eu = 0.0f;
         uint32_t bad = 0;                                             // bit c: chunk c of this lane fails a margin
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-            float gv[8], uv[8];
-            rg[c].get(gv); ru[c].get(uv);
+        for (int c = 0; c < 2; c++) {
+            float gv[16], uv[16];
+            {
+                float t8[8];
+                rg[c][0].get(t8);
+#pragma unroll
+                for (int e = 0; e < 8; e++) gv[e] = t8[e];
+                rg[c][1].get(t8);
+#pragma unroll
+                for (int e = 0; e < 8; e++) gv[8 + e] = t8[e];
+                ru[c][0].get(t8);
+#pragma unroll
+                for (int e = 0; e < 8; e++) uv[e] = t8[e];
+                ru[c][1].get(t8);
+#pragma unroll
+                for (int e = 0; e < 8; e++) uv[8 + e] = t8[e];
+            }
             float amax = 0.0f, gmin = gv[0], gsm = fabsf(gv[0]);
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
+            for (int e = 0; e < 16; e++) {
                 const float ex = ex2_approx(fmul(gv[e], -0x1.715476p+0f));
                 h[c][e] = fmul(fmul(gv[e], rcp_approx(fadd(1.0f, ex))), uv[e]);
                 amax = max_nan(amax, fabsf(h[c][e]));
@@ -251,49 +287,52 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
                 if (sizeof(T) == 4) gsm = fminf(gsm, fabsf(gv[e]));
             }
             amax = max_nan(amax, __shfl_xor_sync(CAM_FULL, amax, 1));
-            amax = max_nan(amax, __shfl_xor_sync(CAM_FULL, amax, 2));
             const float thr = fmul(amax, 0.999997f);
             uint32_t bits = 0;
 #pragma unroll
-            for (int e = 0; e < 8; e++) or_if_ge(bits, h[c][e], thr, 1u << e);
-            const uint32_t ball = (__ballot_sync(CAM_FULL, bits != 0) >> qb) & 0xfu;
-            if ((bits & (bits - 1)) != 0 || (ball & (ball - 1)) != 0 || ball == 0 || !(gmin >= -8.0f) || !(amax >= 1.0e-30f && amax < 3.0e38f) ||
+            for (int e = 0; e < 16; e++) or_if_ge(bits, h[c][e], thr, 1u << e);
+            const uint32_t ball = (__ballot_sync(CAM_FULL, bits != 0) >> pb) & 0x3u;
+            if ((bits & (bits - 1)) != 0 || ball == 3u || ball == 0 || !(gmin >= -8.0f) || !(amax >= 1.0e-30f && amax < 3.0e38f) ||
                 (sizeof(T) == 4 && !(gsm >= 3.0e-38f))) bad |= 1u << c;
-            const int idx = (__ffs(bits) - 1) & 7, src = qb + ((__ffs(ball) - 1) & 3);
-            const float tg = __shfl_sync(CAM_FULL, rg[c].pick(idx), src), tu = __shfl_sync(CAM_FULL, ru[c].pick(idx), src);
-            if (qi == c) { eg = tg; eu = tu; }
+            const int idx = (__ffs(bits) - 1) & 15, src = pb + ((ball >> 1) & 1u);
+            const float cg = idx < 8 ? rg[c][0].pick(idx) : rg[c][1].pick(idx - 8), cu = idx < 8 ? ru[c][0].pick(idx) : ru[c][1].pick(idx - 8);
+            const float tg = __shfl_sync(CAM_FULL, cg, src), tu = __shfl_sync(CAM_FULL, cu, src);
+            if (pi == c) { eg = tg; eu = tu; }
         }
-        // the exact statements for the quad's four candidates, one per lane
+        // the exact statements for the pair's two candidates, one per lane
         const float am = fabsf(fmul(cam_silu(eg), eu));
         const float d_inv = fdiv(127.0f, am), d = fdiv(1.0f, d_inv);
-        uint8_t * const yb = y + ((size_t)t.kb * rows + t.r0) * 144;           // row r0's block of this half-warp's K-block
-        uint32_t redo = 0;                                            // bit 4 j + c: group j of chunk c is recomputed
+        uint8_t * const yb = y + ((size_t)t.kb * rows + t.r0) * 144;           // row r0's block of this lane's K-block
+        uint32_t redo = 0;                                            // bit 2 j + c: group j (of the warp's 16) of chunk c is recomputed
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-            const float di = __shfl_sync(CAM_FULL, d_inv, qb + c);
+        for (int c = 0; c < 2; c++) {
+            const float di = __shfl_sync(CAM_FULL, d_inv, pb + c);
             const float inv_hi = fmul(di, 0x1.00001cp+0f), inv_lo = fmul(di, 0x1.ffffc8p-1f);      // 1 +- 1.67e-6
-            uint32_t v[8], differ = 0;
+            uint32_t v[16], differ = 0;
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
+            for (int e = 0; e < 16; e++) {
                 v[e] = __float_as_uint(ffma(h[c][e], inv_hi, 12582912.0f));
                 differ |= v[e] ^ __float_as_uint(ffma(h[c][e], inv_lo, 12582912.0f));
             }
             const bool on = t.kon && t.r0 + c < rows;
             const uint32_t mask = __ballot_sync(CAM_FULL, (differ != 0 || ((bad >> c) & 1u)) && on);
-            const uint32_t quad = (mask | (mask >> 1) | (mask >> 2) | (mask >> 3)) & 0x11111111u;
-            redo |= quad << c;
-            if (on && !((quad >> qb) & 1u)) {
-                const uint32_t w0 = __byte_perm(__byte_perm(v[0], v[1], 0x0040), __byte_perm(v[2], v[3], 0x0040), 0x5410);
-                const uint32_t w1 = __byte_perm(__byte_perm(v[4], v[5], 0x0040), __byte_perm(v[6], v[7], 0x0040), 0x5410);
-                st64_stream(yb + c * 144 + 16 + (lane & 15) * 8, make_uint2(w0, w1));
+            const uint32_t pair = (mask | (mask >> 1)) & 0x55555555u;
+            redo |= pair << c;
+            if (on && !((pair >> pb) & 1u)) {
+                uint4 w;
+                w.x = __byte_perm(__byte_perm(v[0], v[1], 0x0040), __byte_perm(v[2], v[3], 0x0040), 0x5410);
+                w.y = __byte_perm(__byte_perm(v[4], v[5], 0x0040), __byte_perm(v[6], v[7], 0x0040), 0x5410);
+                w.z = __byte_perm(__byte_perm(v[8], v[9], 0x0040), __byte_perm(v[10], v[11], 0x0040), 0x5410);
+                w.w = __byte_perm(__byte_perm(v[12], v[13], 0x0040), __byte_perm(v[14], v[15], 0x0040), 0x5410);
+                st128_stream(yb + c * 144 + 16 + (lane & 7) * 16, w);
             }
         }
-        // the scale of chunk qi, group lane / 4 (this lane evaluated it)
-        if (t.kon && t.r0 + qi < rows && !((redo >> (qb + qi)) & 1u)) reinterpret_cast<float *>(yb + qi * 144)[(lane >> 2) & 3] = d;
+        // the scale of chunk pi, group (lane / 2) % 4 of this lane's K-block (this lane evaluated it)
+        if (t.kon && t.r0 + pi < rows && !((redo >> (pb + pi)) & 1u)) reinterpret_cast<float *>(yb + pi * 144)[(lane >> 1) & 3] = d;
         // exact recomputation of the flagged groups: the whole warp, one lane per value (uniform: redo is the same in every lane)
         for (uint32_t m = redo; m; m &= m - 1) {
-            const int bit = __ffs(m) - 1, j = bit >> 2, c = bit & 3;     // group j of the warp's 8: K-block j / 4, group j % 4
-            const int kbj = kp_now * 2 + (j >> 2), kj = kbj * 128 + (j & 3) * 32 + lane;
+            const int bit = __ffs(m) - 1, j = bit >> 1, c = bit & 1;     // group j of the warp's 16: K-block j / 4, group j % 4
+            const int kbj = kq_now * 4 + (j >> 2), kj = kbj * 128 + (j & 3) * 32 + lane;
             float x = 0.0f;
             if (kj < kvalid) {
                 const size_t at = (size_t)(t.r0 + c) * ld + kj;
@@ -315,7 +354,9 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
         }
         if (PF) {
 #pragma unroll
-            for (int c = 0; c < 4; c++) { rg[c] = ng[c]; ru[c] = nu[c]; }
+            for (int c = 0; c < 2; c++)
+#pragma unroll
+                for (int hf = 0; hf < 2; hf++) { rg[c][hf] = ng[c][hf]; ru[c][hf] = nu[c][hf]; }
         }
     }
 }
@@ -327,15 +368,15 @@ int launch_mmq(const void * x, const void * u, void * y, int kvalid, int Kpad, l
     const int elt = MODE == 2 ? 8 : 16;
     if ((reinterpret_cast<uintptr_t>(x) & (elt - 1)) || (u && (reinterpret_cast<uintptr_t>(u) & (elt - 1))) || !cam_aligned16(y)) return CAM_ERR_ALIGN;
     if (rows == 0) return CAM_OK;
-    if (MODE != 0 && layout == 0 && !(kvalid & 7) && !(ld & 7) && cam_aligned16(x) && cam_aligned16(u)) {
-        const long nx = ((rows + 3) / 4 + 7) / 8, ny = (Kpad / 128 + 1) / 2;
+    if (MODE != 0 && layout == 0 && !(kvalid & 15) && !(ld & 7) && cam_aligned16(x) && cam_aligned16(u)) {
+        const long nx = ((rows + 1) / 2 + 7) / 8, ny = (Kpad / 128 + 3) / 4;
         if (MODE == 2) mmq_swiglu_fast_kernel<uint16_t, true><<<mmq_grid(mmq_swiglu_fast_kernel<uint16_t, true>, nx, ny), 256, 0, stream>>>(
                 (const uint16_t *)x, (const uint16_t *)u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
         else mmq_swiglu_fast_kernel<float, false><<<mmq_grid(mmq_swiglu_fast_kernel<float, false>, nx, ny), 256, 0, stream>>>(
                 (const float *)x, (const float *)u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
         return (int)cudaGetLastError();
     }
-    const long ny = (Kpad / 128 + 7) / 8;
+    const long ny = (Kpad / 128 + 31) / 32;
     if (layout == 0) mmq_q8_1_kernel<MODE, 0><<<mmq_grid(mmq_q8_1_kernel<MODE, 0>, rows, ny), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
     else mmq_q8_1_kernel<MODE, 1><<<mmq_grid(mmq_q8_1_kernel<MODE, 1>, rows, ny), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
     return (int)cudaGetLastError();
@@ -366,7 +407,7 @@ extern "C" int cam_quantize_mmq_q8_1_ids(const float * x, const int * ids, void 
     if (ncols < 0 || Kpad < 128 || (Kpad & 127) || K < 0 || K > Kpad || (K & 3) || s01 < K || (s01 & 3) || !x || !y || (layout != 0 && layout != 1)) return CAM_ERR_ARG;
     if (!cam_aligned16(x) || !cam_aligned16(y) || (ids && (reinterpret_cast<uintptr_t>(ids) & 3u))) return CAM_ERR_ALIGN;
     if (ncols == 0) return CAM_OK;
-    const long ny = (Kpad / 128 + 7) / 8;
+    const long ny = (Kpad / 128 + 31) / 32;
     if (layout == 0) mmq_q8_1_rows_kernel<0, false><<<mmq_grid(mmq_q8_1_rows_kernel<0, false>, ncols, ny), 256, 0, (cudaStream_t)stream>>>(x, ids, (uint8_t *)y, K, Kpad / 128, s01, ncols, 1, ncols);
     else mmq_q8_1_rows_kernel<1, false><<<mmq_grid(mmq_q8_1_rows_kernel<1, false>, ncols, ny), 256, 0, (cudaStream_t)stream>>>(x, ids, (uint8_t *)y, K, Kpad / 128, s01, ncols, 1, ncols);
     return (int)cudaGetLastError();
@@ -380,7 +421,7 @@ extern "C" int cam_quantize_mmq_q8_1_scatter(const float * x, const int * ids_in
         (layout != 0 && layout != 1) || (long)ntok * k > 0x7fffffffL) return CAM_ERR_ARG;
     if (!cam_aligned16(x) || !cam_aligned16(y) || (reinterpret_cast<uintptr_t>(ids_inv) & 3u)) return CAM_ERR_ALIGN;
     if (ntok == 0) return CAM_OK;
-    const long ny = (Kpad / 128 + 7) / 8;
+    const long ny = (Kpad / 128 + 31) / 32;
     if (layout == 0) mmq_q8_1_rows_kernel<0, true><<<mmq_grid(mmq_q8_1_rows_kernel<0, true>, ntok, ny), 256, 0, (cudaStream_t)stream>>>(x, ids_inv, (uint8_t *)y, K, Kpad / 128, s_tok, ntok, k, ntok * k);
     else mmq_q8_1_rows_kernel<1, true><<<mmq_grid(mmq_q8_1_rows_kernel<1, true>, ntok, ny), 256, 0, (cudaStream_t)stream>>>(x, ids_inv, (uint8_t *)y, K, Kpad / 128, s_tok, ntok, k, ntok * k);
     return (int)cudaGetLastError();

@@ -149,7 +149,7 @@ def test_mmq_q8_1(layout, rows, K):
 
 
 @pytest.mark.parametrize('dt', [np.float16, np.float32])
-@pytest.mark.parametrize('rows,K,kvalid', [(1, 128, 128), (3, 384, 384), (6, 640, 600), (13, 1024, 1024), (64, 2560, 2560)])
+@pytest.mark.parametrize('rows,K,kvalid', [(1, 128, 128), (3, 384, 384), (6, 640, 592), (13, 1024, 1024), (5, 896, 888), (64, 2560, 2560)])
 def test_swiglu_mmq_hard_inputs(dt, rows, K, kvalid):
     """the D4 fast pass: every byte is the exact statements' byte on inputs built to sit on its margins: duplicated and nearly
     equal maxima, products on rounding boundaries, gates below -8, zero groups, tiny and huge values, NaN and infinities; odd
