@@ -30,7 +30,7 @@ BYTES_PER_TOKEN = {'add_rms_f16': 4 * HIDDEN * 2, 'qk_rope_f16': (NH + NKV) * 12
 # DRAM bytes per token row of the dominant kernel, from one ncu capture at T = 8192 (profiles/swiglu_q8_fast_kernel_T8192_I25600.md:
 # dram__bytes_read.sum + dram__bytes_write.sum = 838.95 + 217.91 MB); the traffic grows in proportion to the rows, so a launch
 # of T rows is scaled from it
-SWIGLU_DRAM_BYTES_PER_TOKEN = (838_954_496 + 217_908_736) / 8192
+SWIGLU_DRAM_BYTES_PER_TOKEN = (838_906_880 + 216_342_016) / 8192
 METRIC = 'per-layer glue throughput (residual add + RMSNorm -> q/k norm + RoPE -> SwiGLU + Q8_1), tokens/s'
 
 
