@@ -286,6 +286,11 @@ def single_op_lines(torch, dev, peak, only=()):
     line('rms_mul_q8_1_R32768_K2560', Rq * Kq8 * 8 + Rq * Kq8 // 32 * 36,
          timed(lambda i: LB.check(Lc.cam_rms_mul_q8_1(xq.data_ptr(), wq8.data_ptr(), yq8.data_ptr(), q8o.data_ptr(), Rq, 1, 1e-6, Kq8, cs), 'cam_rms_mul_q8_1')), Rq, 'rows_per_s')
     del xq, yq8, q8o
+    xq1 = rnd(8192 * 5120, scale=2.0)
+    line('gg_quantize_q8_1_f32_41943040', 8192 * 5120 * 4 + 8192 * 5120 // 32 * 36, timed(lambda i: gguf.quantize_q8_1(xq1)), 8192, 'rows_per_s')
+    uq1 = rnd(8192 * 5120, scale=2.0); hq1 = torch.empty_like(xq1)
+    line('gg_silu_mul_f32_41943040', 8192 * 5120 * 12, timed(lambda i: gguf.silu_mul(xq1, uq1)), 8192, 'rows_per_s')
+    del xq1, uq1, hq1
     # the one-kernel tensor-parallel norm run by a single rank (its own partial is the only word it waits for): the kernel's HBM side
     from caminus_b200 import dist as DD
     for Ns_ in (640, 2560):

@@ -212,7 +212,72 @@ __global__ void __launch_bounds__(32) q8_1_tail_kernel(const T * __restrict__ g,
     if (lane == 0) *reinterpret_cast<uint32_t *>(o) = f2_to_h2(d, s);
 }
 
-// FAST: the two-pass fused kernel (SwiGLU only); otherwise the exact statements for every value
+// The plain quantiser (gg_quantize_q8_1) at memory speed, every byte the exact statements': the values are given, so amax, d and
+// the block sum are exact as they stand; only the 32 divisions x / d are replaced, where that provably changes nothing: x * rcp(d)
+// is within 1.8e-7 |t| of the IEEE quotient t; if its two ends t (1 -+ 4.8e-7) round to one integer, no rounding boundary lies
+// between them and that integer is roundf(t). A lane whose test fails (or whose block has a zero, tiny, huge or NaN scale or sum)
+// divides its 16 values. Mapping as swiglu_q8_step: 16 values per lane, two lanes per block.
+template <typename T, bool FULL>
+CAM_DEV void q8_plain_step(const T * __restrict__ x, uint8_t * __restrict__ y, int base, int npairs, int lane) {
+    const int pi = base + lane, q = lane & 1;
+    const bool on = FULL || pi < npairs;
+    float h[16];
+    if (on) {
+        float t[8];
+        Load8<T>::get(x + (size_t)pi * 16, t);
+#pragma unroll
+        for (int k = 0; k < 8; k++) h[k] = t[k];
+        Load8<T>::get(x + (size_t)pi * 16 + 8, t);
+#pragma unroll
+        for (int k = 0; k < 8; k++) h[8 + k] = t[k];
+    } else {
+#pragma unroll
+        for (int k = 0; k < 16; k++) h[k] = 0.0f;
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 16; k++) amax = fmaxf(amax, fabsf(h[k]));
+    amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 1));
+    float sg[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        sg[j] = fadd(fadd(h[4 * j], h[4 * j + 1]), fadd(h[4 * j + 2], h[4 * j + 3]));
+        sg[j] = fadd(sg[j], __shfl_xor_sync(CAM_FULL, sg[j], 1));                                         // partner 4
+    }
+    const float sum = fadd(fadd(sg[0], sg[2]), fadd(sg[1], sg[3]));                                        // partners 2, 1
+    const float d = fdiv(amax, 127.0f);
+    const float inv = rcp_approx(d);
+    const float inv_hi = fmul(inv, 0x1.000008p+0f), inv_lo = fmul(inv, 0x1.fffff0p-1f);
+    uint32_t v[16], differ = 0;
+#pragma unroll
+    for (int k = 0; k < 16; k++) {
+        v[k] = __float_as_uint(ffma(h[k], inv_hi, 12582912.0f));
+        differ |= v[k] ^ __float_as_uint(ffma(h[k], inv_lo, 12582912.0f));
+    }
+    if (differ != 0 || !(d >= 1.0e-30f && d < 3.0e38f) || !(fabsf(sum) < 3.0e38f)) {
+#pragma unroll
+        for (int k = 0; k < 16; k++) v[k] = (uint32_t)q8_code(h[k], d, amax);
+    }
+    if (on) {
+        uint32_t * o = reinterpret_cast<uint32_t *>(y + (size_t)(pi >> 1) * 36);
+        if (q == 0) __stcs(o, f2_to_h2(d, sum));
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            __stcs(o + 1 + 4 * q + j, __byte_perm(__byte_perm(v[4 * j], v[4 * j + 1], 0x0040), __byte_perm(v[4 * j + 2], v[4 * j + 3], 0x0040), 0x5410));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(Q8_THREADS) q8_plain_kernel(const T * __restrict__ x, uint8_t * __restrict__ y, int nb) {
+    const int lane = threadIdx.x & 31;
+    const int npairs = nb * 2;
+    const int stride = gridDim.x * Q8_THREADS;
+    int base = blockIdx.x * Q8_THREADS + (threadIdx.x & ~31);
+    for (; base + 32 <= npairs; base += stride) q8_plain_step<T, true>(x, y, base, npairs, lane);
+    if (base < npairs) q8_plain_step<T, false>(x, y, base, npairs, lane);
+}
+
+// FAST: the two-pass fused kernel (SwiGLU only). Plain quantisation: q8_plain_kernel. Strict SwiGLU: the exact statements for every value
 template <typename T, bool SWIGLU, bool FAST = false>
 int launch_q8(const T * g, const T * u, void * y, long n, cudaStream_t stream) {
     if (n < 0 || !g || !y || (SWIGLU && !u)) return CAM_ERR_ARG;
@@ -228,6 +293,13 @@ int launch_q8(const T * g, const T * u, void * y, long n, cudaStream_t stream) {
                 const long w = (m * 2 + Q8_THREADS - 1) / Q8_THREADS;
                 swiglu_q8_fast_kernel<T><<<cam_resident_grid(swiglu_q8_fast_kernel<T>, Q8_THREADS, 0, w), Q8_THREADS, 0, stream>>>(
                     g + b0 * 32, u + b0 * 32, (uint8_t *)y + b0 * 36, (int)m);
+            }
+        } else if (!SWIGLU) {
+            const long piece = 1L << 28;
+            for (long b0 = 0; b0 < nb; b0 += piece) {
+                const long m = nb - b0 < piece ? nb - b0 : piece;
+                const long w = (m * 2 + Q8_THREADS - 1) / Q8_THREADS;
+                q8_plain_kernel<T><<<cam_resident_grid(q8_plain_kernel<T>, Q8_THREADS, 0, w), Q8_THREADS, 0, stream>>>(g + b0 * 32, (uint8_t *)y + b0 * 36, (int)m);
             }
         } else q8_1_kernel<T, SWIGLU><<<cam_resident_grid(q8_1_kernel<T, SWIGLU>, Q8_THREADS, 0, want), Q8_THREADS, 0, stream>>>(g, u, (uint8_t *)y, nb);
     }

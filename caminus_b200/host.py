@@ -4,21 +4,55 @@ HostLayerGlue owns pinned host buffers for one batch of token rows and runs, per
 on the device: the rows are cut into chunks, each chunk's inputs are copied in on one stream, computed on a second and its
 outputs copied back on a third, two chunks in flight, so the copies of one chunk overlap the kernels of another. All bytes
 cross the host link in both directions on every call; device memory holds two chunks, not the batch."""
+import contextlib
+import os
+
 import torch
 
 from . import glue
+
+
+@contextlib.contextmanager
+def near_gpu(dev):
+    """Inside the block the calling thread runs on the CPUs next to GPU `dev` (NVML's CPU affinity of the device), so that pinned
+    host memory allocated there lands on that GPU's NUMA node and its copies do not cross the socket interconnect; the thread's
+    previous affinity is restored afterwards. Changes nothing on the GPU; without NVML, or where the call fails, it does nothing."""
+    old = None
+    try:
+        import pynvml as nv
+        nv.nvmlInit()
+        index = torch.device(dev).index or 0
+        vis = os.environ.get('CUDA_VISIBLE_DEVICES')
+        idx = int(vis.split(',')[index]) if vis and all(v.strip().isdigit() for v in vis.split(',')) else index
+        h = nv.nvmlDeviceGetHandleByIndex(idx)
+        ncpu = os.cpu_count() or 1
+        words = nv.nvmlDeviceGetCpuAffinity(h, (ncpu + 63) // 64)
+        cpus = {64 * w + b for w, m in enumerate(words) for b in range(64) if (int(m) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        if cpus & allowed:
+            old = allowed
+            os.sched_setaffinity(0, cpus & allowed)
+    except Exception:
+        old = None
+    try:
+        yield
+    finally:
+        if old is not None:
+            try: os.sched_setaffinity(0, old)
+            except Exception: pass
 
 
 class HostLayerGlue:
     def __init__(self, T, hidden, nh, nkv, inter, nw, par, dev, chunk=1024, eps=1e-6, yarn=False):
         self.T, self.dev, self.chunk = int(T), torch.device(dev), int(min(chunk, T))
         self.layer = glue.LayerGlue(nw, par, eps, yarn)
-        pin = lambda *s, dt=torch.float16: torch.empty(*s, dtype=dt, pin_memory=True)
-        self.x, self.resid = pin(T, hidden), pin(T, hidden)
-        self.q, self.k = pin(T, nh, 128), pin(T, nkv, 128)
-        self.gate, self.up = pin(T, inter), pin(T, inter)
-        self.h16 = pin(T, hidden)
-        self.yq = pin(T, inter // 32 * 36, dt=torch.uint8)
+        pin = lambda *s, dt=torch.float16: torch.empty(*s, dtype=dt, pin_memory=True).zero_()      # (touched where it is allocated)
+        with near_gpu(self.dev):
+            self.x, self.resid = pin(T, hidden), pin(T, hidden)
+            self.q, self.k = pin(T, nh, 128), pin(T, nkv, 128)
+            self.gate, self.up = pin(T, inter), pin(T, inter)
+            self.h16 = pin(T, hidden)
+            self.yq = pin(T, inter // 32 * 36, dt=torch.uint8)
         C = self.chunk
         dv = lambda *s, dt=torch.float16: torch.empty(*s, dtype=dt, device=self.dev)
         self.bufs = [dict(x=dv(C, hidden), resid=dv(C, hidden), q=dv(C, nh, 128), k=dv(C, nkv, 128), gate=dv(C, inter), up=dv(C, inter),

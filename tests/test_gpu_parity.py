@@ -131,6 +131,21 @@ def test_q8_1_golden(golden):
         assert same(y, oracle.q8_1(x, sum_order=1))                              # every byte, the block sums included
 
 
+def test_q8_1_plain_every_byte_on_hard_inputs():
+    """the plain quantiser's division-free codes: all 36 bytes of every block are the exact statements' on scales from 1e-35 to
+    1e35, quotients on exact .5 boundaries, zero blocks, infinities and NaNs, and a ragged tail"""
+    g_ = np.random.default_rng(5); n = (1 << 20) + 19
+    x = (g_.standard_normal(n) * 2.0).astype(np.float32)
+    x[:32768] *= (10.0 ** g_.integers(-35, 35, 32768 // 32).repeat(32)).astype(np.float32)      # a scale per block
+    blk = x[32768:65536].reshape(-1, 32); blk[:] = np.round(blk * 8) / 8; blk[:, 0] = 127.0 / 8 * 8    # amax 127: d = 1, codes = values: ties at .5
+    x[65536:65536 + 64] = 0.0
+    x[70000] = np.inf; x[70100] = -np.inf; x[70200] = np.nan; x[80000:80032] = 3e38
+    y = gguf.quantize_q8_1(cu(x)).cpu().numpy(); want = oracle.q8_1(x, sum_order=1)
+    d, s_, q = oracle.q8_split(y); d1, s1, q1 = oracle.q8_split(want)
+    ok = ~np.isnan(d1.astype(np.float32)) & ~np.isnan(s1.astype(np.float32))        # (a NaN has no fixed bit pattern)
+    assert np.array_equal(q, q1) and np.array_equal(d.view(np.uint16)[ok], d1.view(np.uint16)[ok]) and np.array_equal(s_.view(np.uint16)[ok], s1.view(np.uint16)[ok])
+
+
 def sums_close(y, want, h):
     """the block sums of the fast pass: within one fp16 ulp of the exact statements' sum, or 2e-6 sum |h| when the values cancel"""
     _, s, _ = oracle.q8_split(y); _, s0, _ = oracle.q8_split(want)
