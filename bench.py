@@ -235,6 +235,7 @@ def single_op_lines(torch, dev, peak, only=()):
     line('pf_rms_mul_R32768_K2560_f32', R * D * 8, timed(lambda i: gl.rms_mul(x, w, y, R, 1e-6)), R, 'rows_per_s')
     b = rnd(T, D); inj = rnd(T, HC, scale=3.0)
     line('pf_hc_post_rms_T8192_HC4_bf16_scale', R * D * (8 + 2) + T * D * 4, timed(lambda i: gl.hc_post_rms(b, inj, x, w, T, HC, 1e-6, xnbf=ybf, scale=scl)), T, 'tokens_per_s')
+    line('pf_hc_post_T8192_HC4', T * D * 4 + R * D * 8, timed(lambda i: gl.hc_post(b, inj, x, T, HC)), T, 'tokens_per_s')
     gate = rnd(R, D); outm = torch.empty(T, D, device=dev)
     line('pf_hc_mean_T8192_HC4', R * D * 8 + T * D * 4, timed(lambda i: gl.hc_mean(x, gate, outm, T, HC, scale=scl, w=w)), T, 'tokens_per_s')
     del x, y, ybf, gate, outm, b
@@ -250,6 +251,12 @@ def single_op_lines(torch, dev, peak, only=()):
     F16 = q3m_ops.Ops(dev); c16 = torch.zeros(T * 2 * M, dtype=torch.float16, device=dev)
     line('qk_rope_f32_cache_T4096', T * (ldq * 4 + nh * 256 + 2 * M * 2), timed(lambda i: F16.qk_rope(qkv[i], ldq, nh, nkv, par, 0, q16, c16, T), rot=2), T, 'tokens_per_s')
     del qkv, cache, c16
+    T2 = 32768                                               # the same two forms on a batch that fills the device for longer
+    qkv2 = rnd(T2 * ldq, scale=3.0); q16b = torch.empty(T2, nh, 128, dtype=torch.float16, device=dev)
+    cache2 = torch.zeros(T2 * rowb, dtype=torch.uint8, device=dev); c16b = torch.zeros(T2 * 2 * M, dtype=torch.float16, device=dev)
+    line('qk_rope_q8_f32_T32768', T2 * (ldq * 4 + nh * 256 + rowb), timed(lambda i: Q8.qk_rope(qkv2, ldq, nh, nkv, par, 0, q16b, cache2, T2, err=err)), T2, 'tokens_per_s')
+    line('qk_rope_f32_cache_T32768', T2 * (ldq * 4 + nh * 256 + 2 * M * 2), timed(lambda i: F16.qk_rope(qkv2, ldq, nh, nkv, par, 0, q16b, c16b, T2)), T2, 'tokens_per_s')
+    del qkv2, cache2, c16b, q16b
     Mr, Kq = 32768, 1024
     xa = rnd(Mr, Kq, scale=2.0).bfloat16()
     line('actq_codes_bf16_M32768_K1024', Mr * Kq * (2 + 2 + 0.5) + Mr * 4, timed(lambda i: A.actq_codes(xa, 4, 1.0)), Mr, 'rows_per_s')

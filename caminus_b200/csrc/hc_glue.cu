@@ -120,38 +120,68 @@ __global__ void __launch_bounds__(256) hc_mean_kernel(const float * __restrict__
 }
 
 // the two stream kernels, four consecutive elements per thread (D a multiple of 4, 16-byte aligned buffers)
+// (a block per token, looping over tokens: no index is divided, and a token's HC gate factors are computed once, not once per thread)
 __global__ void __launch_bounds__(256) hc_post_vec_kernel(const float * __restrict__ b, const float * __restrict__ inj, float * res, int T, int HC, int D, float rs) {
-    const int D4 = D >> 2; const long n = (long)T * D4;
-    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {
-        const int tt = (int)(i / D4), i4 = (int)(i - (long)tt * D4);
-        const float4 bv = __ldg(reinterpret_cast<const float4 *>(b) + i);
-        for (int h = 0; h < HC; h++) {
-            const float ph = fmul(cam_sigmoid(fmul(__ldg(inj + tt * HC + h), rs)), 2.0f);
-            float4 * o = reinterpret_cast<float4 *>(res + (size_t)(tt * HC + h) * D) + i4;
-            const float4 r = *o;
-            *o = make_float4(ffma(bv.x, ph, r.x), ffma(bv.y, ph, r.y), ffma(bv.z, ph, r.z), ffma(bv.w, ph, r.w));
+    __shared__ float ph_s[32];
+    const int D4 = D >> 2;
+    for (int tt = blockIdx.x; tt < T; tt += gridDim.x) {
+        __syncthreads();                                     // (the previous token's readers are done with ph_s)
+        if (threadIdx.x < HC && threadIdx.x < 32) ph_s[threadIdx.x] = fmul(cam_sigmoid(fmul(__ldg(inj + tt * HC + threadIdx.x), rs)), 2.0f);
+        __syncthreads();
+        for (int i4 = threadIdx.x; i4 < D4; i4 += 256) {
+            const float4 bv = __ldg(reinterpret_cast<const float4 *>(b) + (size_t)tt * D4 + i4);
+            for (int h = 0; h < HC; h++) {
+                const float ph = h < 32 ? ph_s[h] : fmul(cam_sigmoid(fmul(__ldg(inj + tt * HC + h), rs)), 2.0f);
+                float4 * o = reinterpret_cast<float4 *>(res + (size_t)(tt * HC + h) * D) + i4;
+                const float4 r = *o;
+                *o = make_float4(ffma(bv.x, ph, r.x), ffma(bv.y, ph, r.y), ffma(bv.z, ph, r.z), ffma(bv.w, ph, r.w));
+            }
         }
     }
 }
+// (a block per token, looping over tokens: no index is divided; HCT > 0: the stream count at compile time, all streams' loads
+// issued before the first sigmoid)
+template <int HCT>
 __global__ void __launch_bounds__(256) hc_mean_vec_kernel(const float * __restrict__ x, const float * __restrict__ scl, const float * __restrict__ w,
                                                           const float * __restrict__ g, float * __restrict__ out, int T, int HC, int D, float rs) {
-    const int D4 = D >> 2; const long n = (long)T * D4;
-    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {
-        const int tt = (int)(i / D4), i4 = (int)(i - (long)tt * D4);
-        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (int h = 0; h < HC; h++) {
-            const size_t o = (size_t)(tt * HC + h) * D4 + i4;
-            float4 xv = __ldg(reinterpret_cast<const float4 *>(x) + o);
-            const float4 gv = __ldg(reinterpret_cast<const float4 *>(g) + o);
-            if (scl) {
-                const float sc = __ldg(scl + tt * HC + h);
-                const float4 wv = __ldg(reinterpret_cast<const float4 *>(w) + (size_t)h * D4 + i4);
-                xv = make_float4(fmul(fmul(xv.x, sc), wv.x), fmul(fmul(xv.y, sc), wv.y), fmul(fmul(xv.z, sc), wv.z), fmul(fmul(xv.w, sc), wv.w));
+    const int D4 = D >> 2, nh = HCT ? HCT : HC;
+    constexpr int HM = HCT ? HCT : 1;
+    for (int tt = blockIdx.x; tt < T; tt += gridDim.x) {
+        for (int i4 = threadIdx.x; i4 < D4; i4 += 256) {
+            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (HCT) {
+                float4 xv[HM], gv[HM];
+#pragma unroll
+                for (int h = 0; h < HM; h++) {
+                    const size_t o = (size_t)(tt * HM + h) * D4 + i4;
+                    xv[h] = __ldg(reinterpret_cast<const float4 *>(x) + o); gv[h] = __ldg(reinterpret_cast<const float4 *>(g) + o);
+                }
+#pragma unroll
+                for (int h = 0; h < HM; h++) {
+                    if (scl) {
+                        const float sc = __ldg(scl + tt * HM + h);
+                        const float4 wv = __ldg(reinterpret_cast<const float4 *>(w) + (size_t)h * D4 + i4);
+                        xv[h] = make_float4(fmul(fmul(xv[h].x, sc), wv.x), fmul(fmul(xv[h].y, sc), wv.y), fmul(fmul(xv[h].z, sc), wv.z), fmul(fmul(xv[h].w, sc), wv.w));
+                    }
+                    sum = make_float4(ffma(xv[h].x, cam_sigmoid(gv[h].x), sum.x), ffma(xv[h].y, cam_sigmoid(gv[h].y), sum.y),
+                                      ffma(xv[h].z, cam_sigmoid(gv[h].z), sum.z), ffma(xv[h].w, cam_sigmoid(gv[h].w), sum.w));
+                }
+            } else {
+                for (int h = 0; h < nh; h++) {
+                    const size_t o = (size_t)(tt * nh + h) * D4 + i4;
+                    float4 xv = __ldg(reinterpret_cast<const float4 *>(x) + o);
+                    const float4 gv = __ldg(reinterpret_cast<const float4 *>(g) + o);
+                    if (scl) {
+                        const float sc = __ldg(scl + tt * nh + h);
+                        const float4 wv = __ldg(reinterpret_cast<const float4 *>(w) + (size_t)h * D4 + i4);
+                        xv = make_float4(fmul(fmul(xv.x, sc), wv.x), fmul(fmul(xv.y, sc), wv.y), fmul(fmul(xv.z, sc), wv.z), fmul(fmul(xv.w, sc), wv.w));
+                    }
+                    sum = make_float4(ffma(xv.x, cam_sigmoid(gv.x), sum.x), ffma(xv.y, cam_sigmoid(gv.y), sum.y), ffma(xv.z, cam_sigmoid(gv.z), sum.z),
+                                      ffma(xv.w, cam_sigmoid(gv.w), sum.w));
+                }
             }
-            sum = make_float4(ffma(xv.x, cam_sigmoid(gv.x), sum.x), ffma(xv.y, cam_sigmoid(gv.y), sum.y), ffma(xv.z, cam_sigmoid(gv.z), sum.z),
-                              ffma(xv.w, cam_sigmoid(gv.w), sum.w));
+            __stcs(reinterpret_cast<float4 *>(out) + (size_t)tt * D4 + i4, make_float4(fmul(rs, sum.x), fmul(rs, sum.y), fmul(rs, sum.z), fmul(rs, sum.w)));
         }
-        __stcs(reinterpret_cast<float4 *>(out) + i, make_float4(fmul(rs, sum.x), fmul(rs, sum.y), fmul(rs, sum.z), fmul(rs, sum.w)));
     }
 }
 
@@ -299,7 +329,7 @@ extern "C" int pf_hc_post_rms(const float * b, const float * inj, float * res, c
 extern "C" int pf_hc_post(const float * b, const float * inj, float * res, int T, int HC, int D, float rs, void * stream) {
     if (T < 0 || HC < 1 || D < 1 || !b || !inj || !res) return CAM_ERR_ARG;
     if (T == 0) return CAM_OK;
-    if (!(D & 3) && cam_aligned16(b) && cam_aligned16(res)) hc_post_vec_kernel<<<grid_for((long)T * D / 4), 256, 0, CAM_STREAM>>>(b, inj, res, T, HC, D, rs);
+    if (!(D & 3) && cam_aligned16(b) && cam_aligned16(res)) hc_post_vec_kernel<<<cam_resident_grid(hc_post_vec_kernel, 256, 0, T), 256, 0, CAM_STREAM>>>(b, inj, res, T, HC, D, rs);
     else hc_post_kernel<<<grid_for((long)T * D), 256, 0, CAM_STREAM>>>(b, inj, res, T, HC, D, rs);
     return (int)cudaGetLastError();
 }
@@ -307,7 +337,11 @@ extern "C" int pf_hc_mean(const float * x, const float * scl, const float * w, c
     if (T < 0 || HC < 1 || D < 1 || !x || !g || !out || (scl && !w)) return CAM_ERR_ARG;
     if (T == 0) return CAM_OK;
     if (!(D & 3) && cam_aligned16(x) && cam_aligned16(g) && cam_aligned16(out) && (!w || cam_aligned16(w)))
-        hc_mean_vec_kernel<<<grid_for((long)T * D / 4), 256, 0, CAM_STREAM>>>(x, scl, w, g, out, T, HC, D, rs);
+    {
+        if (HC == 4) hc_mean_vec_kernel<4><<<cam_resident_grid(hc_mean_vec_kernel<4>, 256, 0, T), 256, 0, CAM_STREAM>>>(x, scl, w, g, out, T, HC, D, rs);
+        else if (HC == 2) hc_mean_vec_kernel<2><<<cam_resident_grid(hc_mean_vec_kernel<2>, 256, 0, T), 256, 0, CAM_STREAM>>>(x, scl, w, g, out, T, HC, D, rs);
+        else hc_mean_vec_kernel<0><<<cam_resident_grid(hc_mean_vec_kernel<0>, 256, 0, T), 256, 0, CAM_STREAM>>>(x, scl, w, g, out, T, HC, D, rs);
+    }
     else hc_mean_kernel<<<grid_for((long)T * D), 256, 0, CAM_STREAM>>>(x, scl, w, g, out, T, HC, D, rs);
     return (int)cudaGetLastError();
 }
