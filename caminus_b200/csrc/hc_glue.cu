@@ -200,24 +200,28 @@ __global__ void __launch_bounds__(256) ew_kernel(const void * __restrict__ a, co
 
 template <bool SILU>
 __global__ void __launch_bounds__(256) to_bf16_kernel(const float * __restrict__ x, int ldx, uint16_t * __restrict__ y, int T, int Tpad, int K, float rs) {
-    const long n = (long)Tpad * K;
-    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {
-        const int t = (int)(i / K), j = (int)(i - (long)t * K);
-        uint16_t v = 0;
-        if (t < T) {
-            const float xv = __ldg(x + (size_t)t * ldx + j);
-            v = bf16_rne(SILU ? cam_silu(ffma(rs, xv, 0.0f)) : xv);
+    for (int t = blockIdx.x; t < Tpad; t += gridDim.x)                 // (a block per row: no index is divided)
+        for (int j = threadIdx.x; j < K; j += 256) {
+            uint16_t v = 0;
+            if (t < T) {
+                const float xv = __ldg(x + (size_t)t * ldx + j);
+                v = bf16_rne(SILU ? cam_silu(ffma(rs, xv, 0.0f)) : xv);
+            }
+            y[(size_t)t * K + j] = v;
         }
-        y[i] = v;
-    }
 }
 
 __global__ void __launch_bounds__(256) silu_mul_bf16_kernel(const uint16_t * __restrict__ gu, uint16_t * __restrict__ act, int H, long n) {
-    for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {
-        const long r = i / H, c = i - r * H;
-        const float g = bf16_f(__ldg(gu + r * 2 * H + c)), u = bf16_f(__ldg(gu + r * 2 * H + H + c));
-        const float s = bf16_f(bf16_nan(cam_silu(g)));
-        act[i] = bf16_nan(fmul(s, u));
+    const long rows = n / H;                                           // (whole rows; a block per row: no index is divided per element)
+    for (long r = blockIdx.x; r < rows; r += gridDim.x)
+        for (int c = threadIdx.x; c < H; c += 256) {
+            const float g = bf16_f(__ldg(gu + r * 2 * H + c)), u = bf16_f(__ldg(gu + r * 2 * H + H + c));
+            const float s = bf16_f(bf16_nan(cam_silu(g)));
+            act[r * H + c] = bf16_nan(fmul(s, u));
+        }
+    for (long i = rows * H + (long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long)gridDim.x * 256) {      // a last, partial row
+        const float g = bf16_f(__ldg(gu + rows * 2 * H + (i - rows * H))), u = bf16_f(__ldg(gu + rows * 2 * H + H + (i - rows * H)));
+        act[i] = bf16_nan(fmul(bf16_f(bf16_nan(cam_silu(g))), u));
     }
 }
 
@@ -362,13 +366,13 @@ extern "C" int pf_swiglu(const float * g, const float * u, float * y, long n, vo
 extern "C" int pf_silu_bf16(const float * x, int ldx, void * y, int T, int Tpad, int K, float rs, void * stream) {
     if (T < 0 || Tpad < T || K < 1 || ldx < K || !x || !y) return CAM_ERR_ARG;
     if (Tpad == 0) return CAM_OK;
-    to_bf16_kernel<true><<<grid_for((long)Tpad * K), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, T, Tpad, K, rs);
+    to_bf16_kernel<true><<<cam_resident_grid(to_bf16_kernel<true>, 256, 0, Tpad), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, T, Tpad, K, rs);
     return (int)cudaGetLastError();
 }
 extern "C" int pf_to_bf16(const float * x, int ldx, void * y, int T, int Tpad, int K, void * stream) {
     if (T < 0 || Tpad < T || K < 1 || ldx < K || !x || !y) return CAM_ERR_ARG;
     if (Tpad == 0) return CAM_OK;
-    to_bf16_kernel<false><<<grid_for((long)Tpad * K), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, T, Tpad, K, 0.0f);
+    to_bf16_kernel<false><<<cam_resident_grid(to_bf16_kernel<false>, 256, 0, Tpad), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, T, Tpad, K, 0.0f);
     return (int)cudaGetLastError();
 }
 // pf_qk_nr: kernels/prefill_attn.hip:105-106 (= op_qk_nr, kernels/k3_gguf_ops.h:1490-1518); nblocks = rows * heads is the reference's grid.x
