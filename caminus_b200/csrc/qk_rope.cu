@@ -71,8 +71,6 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
     unsigned char * stage = smem + (128 + 128 + 64 + 2 * 64 * ROPE_STAGES) * 4;
     const float eps = __ldg(A.par + 257);
 
-    if (tid < 128) { wq[tid] = __ldg(A.par + tid); wk[tid] = __ldg(A.par + 128 + tid); }
-    if (tid < 64) freq[tid] = A.yarn ? __ldg(A.par + 258 + tid) : cam_powi(__ldg(A.par + 256), tid);
     const float mscale = A.yarn ? __ldg(A.par + 322) : 1.0f;
 
     auto issue = [&](int t, int st) {
@@ -114,9 +112,13 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
 
     const int t0 = blockIdx.x, g = gridDim.x;
 #pragma unroll
-    for (int k = 0; k < ROPE_STAGES - 1; k++) {
-        issue(t0 + k * g, k);
-        if (tid < 64 && t0 + k * g < A.n) tables(t0 + k * g, k);
+    for (int k = 0; k < ROPE_STAGES - 1; k++) issue(t0 + k * g, k);        // (the first tokens' copies fly while the parameters are read)
+    if (tid < 128) { wq[tid] = __ldg(A.par + tid); wk[tid] = __ldg(A.par + 128 + tid); }
+    if (tid < 64) {
+        freq[tid] = A.yarn ? __ldg(A.par + 258 + tid) : cam_powi(__ldg(A.par + 256), tid);
+#pragma unroll
+        for (int k = 0; k < ROPE_STAGES - 1; k++)
+            if (t0 + k * g < A.n) tables(t0 + k * g, k);
     }
     int st = 0;
     for (int t = t0; t < A.n; t += g, st = st + 1 == ROPE_STAGES ? 0 : st + 1) {
