@@ -285,7 +285,10 @@ def single_op_lines(torch, dev, peak, only=()):
     bpr = 64; raw = torch.randint(0, 256, (vocab, bpr, 18), device=dev, dtype=torch.uint8, generator=g)
     raw[:, :, 0:2] = (torch.randn(vocab, bpr, 1, device=dev, generator=g) * 1e-3).abs().half().view(torch.uint8).view(vocab, bpr, 2)
     line('ple_rows_iq4nl_16384x2048', nt * (4 + bpr * 18 + bpr * 128), timed(lambda i: feed.ple_rows_iq4nl((1,), (256,), raw.view(-1), tk, I(vocab), I(nt), I(bpr), xo[i], er), rot=2), nt, 'rows_per_s')
-    del tab, raw, xo
+    tq6 = torch.randint(0, 256, (vocab, nblk, 210), device=dev, dtype=torch.uint8, generator=g)
+    tq6[:, :, 208:210] = (torch.randn(vocab, nblk, 1, device=dev, generator=g) * 1e-3).half().view(torch.uint8).view(vocab, nblk, 2)
+    line('emb_rows_q6k_16384x2048', nt * (4 + nblk * 210 + nblk * 1024), timed(lambda i: O.emb_q6k(tq6.view(-1), nblk * 210, vocab, tk, xo[i], nt, nblk * 256), rot=2), nt, 'rows_per_s')
+    del tab, raw, xo, tq6
     from caminus_b200 import lib as LB
     Rq, Kq8 = 32768, 2560
     xq = rnd(Rq, Kq8, scale=3.0); wq8 = 0.5 + torch.rand(1, Kq8, device=dev, generator=g); yq8 = torch.empty(Rq, Kq8, device=dev)

@@ -104,6 +104,45 @@ __global__ void __launch_bounds__(256) ple_rows_iq4nl_kernel(const uint8_t * __r
     }
 }
 
+// ---- Q6_K rows (no kernel of the reference gathers them; its host decoder python/caminus/own_dequant.py:40-53 is the definition) -----
+// 210-byte blocks of 256 values: ql[128] | qh[64] | int8 sc[16] | fp16 d. Per half n of 128 and group qd of 32, lane l:
+// q = nibble of ql[n][(qd & 1) 32 + l] (high for qd >= 2) | ((qh[n][l] >> 2 qd) & 3) << 4; y = (d * sc[8 n + 2 qd + (l >= 16)]) * (q - 32).
+// A thread takes four consecutive l of a half and writes their values of all four groups (16 outputs, four 16-byte stores) from
+// 12 bytes of the block (2-byte aligned: six 16-bit loads).
+__global__ void __launch_bounds__(256) emb_rows_q6k_kernel(const uint8_t * __restrict__ W, int rb, int vocab, const int * __restrict__ toks,
+                                                           float * __restrict__ x, int n, int N) {
+    const int units = (N >> 8) * 16;
+    for (int p = blockIdx.x; p < n; p += gridDim.x) {
+        const int t = min(max(__ldg(toks + p), 0), vocab - 1);
+        const uint8_t * row = W + (size_t)t * rb;
+        float * orow = x + (size_t)p * N;
+        for (int q = threadIdx.x; q < units; q += 256) {
+            const int bl = q >> 4, nn = (q >> 3) & 1, l = (q & 7) * 4;
+            const uint8_t * b = row + (size_t)bl * 210;
+            const uint16_t * b16 = reinterpret_cast<const uint16_t *>(b);
+            const int lo_at = (nn * 64 + l) >> 1, hi_at = (128 + nn * 32 + l) >> 1;
+            const uint32_t qa = (uint32_t)__ldg(b16 + lo_at) | ((uint32_t)__ldg(b16 + lo_at + 1) << 16);             // ql[n][l .. l + 3]
+            const uint32_t qb = (uint32_t)__ldg(b16 + lo_at + 16) | ((uint32_t)__ldg(b16 + lo_at + 17) << 16);       // ql[n][32 + l ..]
+            const uint32_t qh = (uint32_t)__ldg(b16 + hi_at) | ((uint32_t)__ldg(b16 + hi_at + 1) << 16);             // qh[n][l ..]
+            const float d = __half2float(__ushort_as_half(__ldg(b16 + 104)));
+            const int8_t * sc = reinterpret_cast<const int8_t *>(b + 192 + nn * 8 + (l >= 16));
+#pragma unroll
+            for (int qd = 0; qd < 4; qd++) {
+                const float ds = fmul(d, (float)(int)sc[2 * qd]);
+                const uint32_t src = (qd & 1) ? qb : qa;
+                float v[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const uint32_t byte = (src >> (8 * e)) & 0xffu, hb = (qh >> (8 * e)) & 0xffu;
+                    const int qv = (int)((qd >= 2 ? byte >> 4 : byte & 15u) | (((hb >> (2 * qd)) & 3u) << 4)) - 32;
+                    v[e] = fmul(ds, (float)qv);
+                }
+                __stcs(reinterpret_cast<float4 *>(orow + bl * 256 + nn * 128 + qd * 32 + l), make_float4(v[0], v[1], v[2], v[3]));
+            }
+        }
+    }
+}
+
 }   // namespace
 
 // embd_rows_iq4xs / ple_rows_iq4nl: kernels/prefill_feed.hip:40-41, 24-25 (one thread per output float there)
@@ -125,5 +164,16 @@ extern "C" int ple_rows_iq4nl(const void * raw, const int * inv, int nuniq, int 
     if (reinterpret_cast<uintptr_t>(raw) & 1u)
         ple_rows_iq4nl_bytes_kernel<<<cam_resident_grid(ple_rows_iq4nl_bytes_kernel, 256, 0, want), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)raw, inv, nuniq, nrows, bpr, out, err);
     else ple_rows_iq4nl_kernel<<<cam_resident_grid(ple_rows_iq4nl_kernel, 256, 0, nrows), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)raw, inv, nuniq, nrows, bpr, out, err);
+    return (int)cudaGetLastError();
+}
+
+// cam_emb_rows_q6k: x [n][N] fp32 = the Q6_K rows toks[i] of a table (vocab rows of rb = N / 256 * 210 bytes), ids clamped to the
+// vocabulary; the floats of the reference's host decoder (python/caminus/own_dequant.py:40-53, bitwise gguf-py). N a multiple of 256,
+// W 2-byte aligned, x 16-byte aligned.
+extern "C" int cam_emb_rows_q6k(int n, const void * W, int rb, int vocab, const int * toks, float * x, int N, void * stream) {
+    if (n < 0 || vocab < 1 || N < 256 || (N & 255) || rb < N / 256 * 210 || !W || !toks || !x) return CAM_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(W) & 1u) || (rb & 1) || !cam_aligned16(x)) return CAM_ERR_ALIGN;
+    if (n == 0) return CAM_OK;
+    emb_rows_q6k_kernel<<<cam_resident_grid(emb_rows_q6k_kernel, 256, 0, n), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)W, rb, vocab, toks, x, n, N);
     return (int)cudaGetLastError();
 }

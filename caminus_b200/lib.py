@@ -51,6 +51,7 @@ SIGNATURES = {
     'block_entry_fwd': [I, P, P, P, I, F, P, P, P, P, P, I, F, I, P],
     'embd_rows_iq4xs': [P, P, I, I, I, P, P, P],
     'ple_rows_iq4nl': [P, P, I, I, I, P, P, P],
+    'cam_emb_rows_q6k': [I, P, I, I, P, P, I, P],
     'q3p_router': [I, P, P, I, I, P, P],
     'q3p_topk': [I, P, I, I, F, P, P, P, P],
     'q3p_group': [P, I, I, I, P, P, P, P, P, P],

@@ -54,6 +54,13 @@ class Ops:
         with _On(self.dev):
             self.mod.q3p_emb((n,), (256,), W, I(rb), I(vocab), toks, x, I(N))
 
+    def emb_q6k(self, W, rb, vocab, toks, x, n, N):
+        """as emb for a Q6_K table (rows of N / 256 * 210 bytes): the floats of own_dequant.q6_k (python/caminus/own_dequant.py:40-53)"""
+        from .. import lib as _lib
+        if N % 256 or rb < N // 256 * 210: raise ValueError(f'q3m emb_q6k: N {N} (a multiple of 256), rb {rb}')
+        with _On(self.dev):
+            _lib.check(_lib.load().cam_emb_rows_q6k(n, W.data_ptr(), rb, vocab, toks.data_ptr(), x.data_ptr(), N, torch.cuda.current_stream().cuda_stream), 'cam_emb_rows_q6k')
+
     def add_rms16(self, x, nw, eps, h16, n, N, d=None, w=None, S=0, h=None):
         if N % 256 or N > 2048: raise ValueError(f'q3m add_rms16: N {N} (a multiple of 256, <= 2048)')
         with _On(self.dev):

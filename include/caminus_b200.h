@@ -142,6 +142,9 @@ int cam_qk_rope_f16(int n, const void * q, const void * k, int nh, int nkv, cons
  *   index outside [0, nuniq) is clamped and sets err |= 1. ---- */
 int embd_rows_iq4xs(const void * table, const int * tok, int nvocab, int n, int nblk, float * out, int * err, void * stream);
 int ple_rows_iq4nl(const void * raw, const int * inv, int nuniq, int nrows, int bpr, float * out, int * err, void * stream);
+/* cam_emb_rows_q6k: the Q6_K row gather (210-byte blocks; the reference decodes this format on the host only:
+ *   python/caminus/own_dequant.py:40-53, whose floats these are). x [n][N] = rows toks[i] (clamped to [0, vocab)) of a table of rb-byte rows. */
+int cam_emb_rows_q6k(int n, const void * W, int rb, int vocab, const int * toks, float * x, int N, void * stream);
 
 /* ---- the router glue of the Qwen3-MoE prefill: kernels/q3m_prefill.hip:417-513; wrappers python/caminus/prefill/q3m_ops.py:94-104 ----
  * q3p_router: logits [n][E] = h [n][K] . Wr [E][K] in fp32 (n = grid.x; K a multiple of 128).

@@ -437,3 +437,9 @@ def ple_rows_iq4nl(raw, inv, nuniq, bpr):
     raw = _c(raw, np.uint8).reshape(-1); inv = _c(inv, np.int32); out = np.empty((inv.size, bpr * 32), np.float32); err = np.zeros(1, np.int32)
     lib().orc_ple_rows_iq4nl(_p(raw), _p(inv), I(nuniq), I(inv.size), I(bpr), _p(out), _p(err))
     return out, int(err[0])
+
+
+def emb_rows_q6k(W, rb, vocab, toks, N):
+    W = _c(W, np.uint8).reshape(-1); toks = _c(toks, np.int32); x = np.empty((toks.size, N), np.float32)
+    lib().orc_emb_rows_q6k(_p(W), I(rb), I(vocab), _p(toks), _p(x), I(toks.size), I(N))
+    return x

@@ -837,3 +837,23 @@ void orc_embd_rows_iq4xs(const uint8_t * table, const int32_t * tok, int nvocab,
         out[i] = dl * kIQ4NL[j < 16 ? (q & 15) : (q >> 4)];
     }
 }
+
+/* Q6_K row gather (no kernel of the reference does this; its host decoder python/caminus/own_dequant.py:40-53 is the definition, bitwise
+ * gguf-py): 210-byte blocks of 256 = ql[128] | qh[64] | int8 sc[16] | fp16 d; per half n of 128 and group qd of 32, lane l:
+ * q = nibble (ql[n][(qd & 1) 32 + l], high for qd >= 2) | ((qh[n][l] >> 2 qd) & 3) << 4; y = (d * sc[8 n + 2 qd + (l >= 16)]) * (q - 32),
+ * two roundings. Token ids are clamped to the vocabulary. */
+void orc_emb_rows_q6k(const uint8_t * W, int rb, int vocab, const int32_t * toks, float * x, int n, int N) {
+    for (int p = 0; p < n; p++) {
+        int t = toks[p]; t = t < 0 ? 0 : t >= vocab ? vocab - 1 : t;
+        const uint8_t * row = W + (size_t)t * rb;
+        for (int i = 0; i < N; i++) {
+            const uint8_t * b = row + (size_t)(i >> 8) * 210;
+            const int w = i & 255, nn = w >> 7, qd = (w >> 5) & 3, l = w & 31;
+            const uint8_t qlb = b[nn * 64 + (qd & 1) * 32 + l], qhb = b[128 + nn * 32 + l];
+            const int q = ((qd >= 2 ? qlb >> 4 : qlb & 15) | (((qhb >> (2 * qd)) & 3) << 4)) - 32;
+            const float d = h2f((uint16_t)(b[208] | (b[209] << 8)));
+            const float ds = d * (float)(int8_t)b[192 + nn * 8 + 2 * qd + (l >= 16)];
+            x[(size_t)p * N + i] = ds * (float)q;
+        }
+    }
+}

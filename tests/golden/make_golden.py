@@ -162,7 +162,17 @@ def make_iq4():
     np.savez_compressed(os.path.join(OUT, 'iq4_rows.npz'), T=T, xs=xs, R=R, nl=nl)
 
 
+def make_q6k():
+    """Q6_K rows: own_dequant.q6_k (python/caminus/own_dequant.py:40-53), bitwise the vendored gguf-py dequantiser; small finite scales"""
+    g = np.random.default_rng(20261125); vocab, nblk = 19, 3
+    T = g.integers(0, 256, (vocab, nblk, 210), dtype=np.uint8)
+    T[:, :, 208:210] = (g.standard_normal((vocab, nblk, 1)) * 1e-3).astype(np.float16).view(np.uint8).reshape(vocab, nblk, 2)
+    rows = np.stack([own_dequant.q6_k(T[t].reshape(-1)) for t in range(vocab)]).astype(np.float32)
+    assert np.array_equal(rows.view(np.uint32), np.stack([gq.dequantize(T[t].reshape(1, -1), QT.Q6_K).reshape(-1) for t in range(vocab)]).astype(np.float32).view(np.uint32))
+    np.savez_compressed(os.path.join(OUT, 'q6k_rows.npz'), T=T, rows=rows)
+
+
 if __name__ == '__main__':
-    make_iq4(); make_q4k(); make_q8(); make_swiglu(); make_rms(); make_rope(); make_q8_kv()
+    make_q6k(); make_iq4(); make_q4k(); make_q8(); make_swiglu(); make_rms(); make_rope(); make_q8_kv()
     for f in sorted(os.listdir(OUT)):
         if f.endswith('.npz'): print(f, os.path.getsize(os.path.join(OUT, f)), 'bytes')

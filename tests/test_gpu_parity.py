@@ -506,3 +506,20 @@ def test_tp_rms_fused_wait_runs_out_and_reports():
     assert int(status.item()) == 1 and not h.any().item()
     assert float((x + 1).sum().item()) == 2.0 * T * Ns                 # (the context still runs kernels)
     assert L.cam_tp_rms_norm_f16(T + 1, x.data_ptr(), 0, nw.data_ptr(), 1e-6, h.data_ptr(), Ns, 2 * Ns, peers.data_ptr(), 0, world, T, 1, status.data_ptr(), 0) == -4
+
+
+def test_q6k_rows(golden):
+    """cam_emb_rows_q6k: the fixture's rows (the reference's host decoder) bit for bit, clamped ids; a larger random table against the oracle"""
+    f = golden('q6k_rows'); T = f['T']; vocab, nblk = T.shape[:2]; N = nblk * 256
+    O = q3m_ops.Ops(DEV)
+    toks = np.concatenate([[0, 18, -4, 77], np.random.default_rng(3).integers(0, vocab, 200)]).astype(np.int32)
+    x = torch.zeros(len(toks), N, device=DEV)
+    O.emb_q6k(cu(T.reshape(-1)), nblk * 210, vocab, cu(toks), x, len(toks), N)
+    assert same(x, f['rows'][np.clip(toks, 0, vocab - 1)])
+    g_ = np.random.default_rng(8); vocab2, nblk2 = 300, 8
+    W = g_.integers(0, 256, (vocab2, nblk2, 210), dtype=np.uint8)
+    W[:, :, 208:210] = (g_.standard_normal((vocab2, nblk2, 1)) * 1e-3).astype(np.float16).view(np.uint8).reshape(vocab2, nblk2, 2)
+    toks2 = g_.integers(0, vocab2, 1000).astype(np.int32); x2 = torch.zeros(1000, nblk2 * 256, device=DEV)
+    O.emb_q6k(cu(W.reshape(-1)), nblk2 * 210, vocab2, cu(toks2), x2, 1000, nblk2 * 256)
+    assert same(x2, oracle.emb_rows_q6k(W, nblk2 * 210, vocab2, toks2, nblk2 * 256))
+    with pytest.raises(ValueError): O.emb_q6k(cu(W.reshape(-1)), 100, vocab2, cu(toks2), x2, 1000, nblk2 * 256)

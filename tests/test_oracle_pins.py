@@ -184,3 +184,11 @@ def test_iq4_rows_bitwise(golden):
     inv = np.array([3, 0, 10, 11, -2, 4], np.int32)
     out, err = oracle.ple_rows_iq4nl(R, inv, nuniq, bpr)
     assert err == 1 and np.array_equal(out.view(np.uint32), f['nl'][np.clip(inv, 0, nuniq - 1)].view(np.uint32))
+
+
+def test_q6k_rows_bitwise(golden):
+    """the Q6_K decoder of the oracle == the reference's own_dequant.q6_k (== gguf-py) on the fixture, clamped ids included"""
+    f = golden('q6k_rows'); T = f['T']; vocab, nblk = T.shape[:2]
+    toks = np.array([0, 7, 18, -2, 50, 3], np.int32)
+    x = oracle.emb_rows_q6k(T, nblk * 210, vocab, toks, nblk * 256)
+    assert np.array_equal(x.view(np.uint32), f['rows'][np.clip(toks, 0, vocab - 1)].view(np.uint32))
