@@ -466,9 +466,10 @@ def test_tp_rms_fused_single_rank_is_the_unsharded_norm():
             assert same(x, xo) and same(h, ho)
 
 
-def test_tp_rms_fused_two_ranks_with_the_peer_words_in_place():
+@pytest.mark.parametrize('N', [2560, 1024, 1296])                      # shards of 1280 (a warp per row), 512 and 648 (a half-warp per row)
+def test_tp_rms_fused_two_ranks_with_the_peer_words_in_place(N):
     from caminus_b200 import lib
-    T, N, world, tag = 300, 2560, 2, 5
+    T, world, tag = 300, 2, 5
     x0, r0, w = synth.add_rms_inputs(T, N, seed=12, dtype=np.float16)
     Ns = N // world; L = lib.load(); words = L.cam_tp_rms_words(T, world)
     parts = [oracle.rms_partial_f16(x0[:, r * Ns:(r + 1) * Ns], r0[:, r * Ns:(r + 1) * Ns]) for r in range(world)]
