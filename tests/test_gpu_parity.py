@@ -362,6 +362,44 @@ def test_layer_glue_sequence():
     assert same(d, d1) and np.array_equal(q_, q1)
 
 
+def test_config5_full_size_properties():
+    """BASELINE config 5 at its full per-GPU size (T = 65536 rows, 13.7 GB per pass), through size-independent properties:
+    chunk-split invariance (one launch == three launches over row ranges, bit for bit: the reference's own gate for its prefill),
+    the updated residual == fp16(x + r) computed by torch, fast == strict SwiGLU blocks (d and codes) over all 52 M blocks,
+    and rows sampled across the batch == the oracle"""
+    T, N, nh, nkv, I = 65536, 5120, 64, 8, 25600
+    gen = torch.Generator(device=DEV); gen.manual_seed(55)
+    rn = lambda *sh, sc=1.0: (torch.randn(*sh, device=DEV, generator=gen) * sc).half()
+    x0, r0 = rn(T, N), rn(T, N); q0, k0 = rn(T, nh, 128), rn(T, nkv, 128)
+    w = (1 + 0.05 * torch.randn(N, device=DEV, generator=gen)); par = cu(synth.rope_par(seed=55))
+    L = glue.LayerGlue(w, par)
+    g0, u0 = rn(T, I, sc=1.5), rn(T, I, sc=1.5)
+    def run(cuts):
+        x, q, k = x0.clone(), q0.clone(), k0.clone()
+        h16 = torch.empty_like(x); yq = torch.empty(T * I // 32 * 36, dtype=torch.uint8, device=DEV); rb = I // 32 * 36
+        for a, b in zip(cuts[:-1], cuts[1:]):
+            L(x[a:b], r0[a:b], q[a:b], k[a:b], g0[a:b], u0[a:b], h16[a:b], yq[a * rb:b * rb], pos0=7 + a)
+        return x, h16, q, k, yq
+    one = run([0, T]); three = run([0, 20001, 20002, T])
+    for a, b in zip(one, three): assert torch.equal(a, b)
+    x, h16, q, k, yq = one
+    del three
+    assert torch.equal(x, (x0.float() + r0.float()).half())
+    strict = gguf.swiglu_q8_1(g0.view(-1), u0.view(-1), strict=True).view(-1, 36); fast = yq.view(-1, 36)
+    assert torch.equal(fast[:, :2], strict[:, :2]) and torch.equal(fast[:, 4:], strict[:, 4:])
+    del strict
+    rows = np.unique(np.concatenate([[0, 1, T - 1], np.random.default_rng(9).integers(0, T, 29)]))
+    xs, rs = x0[rows].cpu().numpy(), r0[rows].cpu().numpy()
+    xo, ho = oracle.add_rms_f16(xs, w.cpu().numpy(), 1e-6, rs)
+    assert same(x[rows], xo) and same(h16[rows], ho)
+    for i, t in enumerate(rows):
+        qo, ko = oracle.qk_rope_f16(q0[t:t + 1].cpu().numpy(), k0[t:t + 1].cpu().numpy(), par.cpu().numpy(), 7 + int(t), sum_order=1)
+        assert same(q[t:t + 1], qo) and same(k[t:t + 1], ko)
+    want = oracle.swiglu_q8_1(g0[rows].cpu().numpy().reshape(-1), u0[rows].cpu().numpy().reshape(-1), sum_order=1).reshape(len(rows), -1, 36)
+    got = yq.view(T, -1, 36)[rows].cpu().numpy()
+    assert np.array_equal(got[:, :, :2], want[:, :, :2]) and np.array_equal(got[:, :, 4:], want[:, :, 4:])
+
+
 # ---- tensor-parallel RMSNorm (hidden sharded) ---------------------------------------------------------------------------------
 @pytest.mark.parametrize('T,N,G', [(300, 5120, 8), (64, 2048, 2), (1000, 5120, 4)])
 @pytest.mark.parametrize('add', [True, False])
