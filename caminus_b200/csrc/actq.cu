@@ -136,7 +136,6 @@ CAM_DEV void actq_fwd_src(Src src, uint16_t * __restrict__ y, float * __restrict
         const int ch = wave + c * AQ_WAVES;
         if (ch < nch) {
             float q[4];
-#pragma unroll
             bool slow = !fast;
 #pragma unroll
             for (int e = 0; e < 4; e++) {       // (the division-free rint of actq_emit below)
@@ -218,7 +217,6 @@ CAM_DEV void actq_emit(const uint2 (&up)[MAXC], float amax, int nch, int row, in
         if (c < nch) {
             float q[4], u[4];
             unpack4(up[c], u);
-#pragma unroll
             bool slow = !fast;
 #pragma unroll
             for (int e = 0; e < 4; e++) {
