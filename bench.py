@@ -301,6 +301,33 @@ def single_op_lines(torch, dev, peak, only=()):
     uq1 = rnd(8192 * 5120, scale=2.0); hq1 = torch.empty_like(xq1)
     line('gg_silu_mul_f32_41943040', 8192 * 5120 * 12, timed(lambda i: gguf.silu_mul(xq1, uq1)), 8192, 'rows_per_s')
     del xq1, uq1, hq1
+    # ---- the remaining small ops of the path (per-head norm + partial rotation, the training line's elementwise forwards) ----
+    L_ = ctypes.c_long; Fc = ctypes.c_float
+    rows_h, heads_h, Dh = 8192, 16, 256                          # pf_qk_nr: 8192 tokens x 16 heads of 256, 64 rotated dims
+    xh = rnd(rows_h * heads_h, Dh, scale=1.5); wh = 0.5 + torch.rand(Dh, device=dev, generator=g); oh = torch.empty_like(xh)
+    attn = CU.Module('prefill_attn'); ts_h = float(np.float32(np.float32(1e7) ** np.float32(-2.0 / 64)))
+    line('pf_qk_nr_T8192_16heads_D256', rows_h * heads_h * Dh * 8, timed(lambda i: attn.pf_qk_nr((rows_h * heads_h,), (256,), xh, I(Dh), I(heads_h), wh, I(Dh), I(64), Fc(ts_h), Fc(1e-6), I(0), oh)), rows_h, 'tokens_per_s')
+    del xh, oh
+    core, fuse = CU.Module('core'), CU.Module('fuse'); ne, de = 65536, 896; nel = ne * de
+    xe_ = rnd(ne, de); we_ = 0.5 + torch.rand(de, device=dev, generator=g); oe_ = torch.empty_like(xe_)
+    line('rmsnorm_f32_65536x896', nel * 8, timed(lambda i: core.rmsnorm_f32((ne,), (256,), xe_, we_, oe_, I(de), Fc(1e-5))), ne, 'rows_per_s')
+    mb = rnd(ne, de).bfloat16(); lb = rnd(ne, de).bfloat16()
+    line('residual3_65536x896', nel * 12, timed(lambda i: core.residual3(((nel + 255) // 256,), (256,), xe_, mb, lb, oe_, ctypes.c_int64(nel))), ne, 'rows_per_s')
+    line('residual_slices_fwd_65536x896', nel * 12, timed(lambda i: fuse.residual_slices_fwd(((nel // 4 + 255) // 256,), (256,), xe_, mb, lb, ctypes.c_void_p(None), ctypes.c_void_p(None), oe_, I(de), L_(nel // 4))), ne, 'rows_per_s')
+    cb_ = torch.empty(ne, de, dtype=torch.bfloat16, device=dev)
+    line('cast_bf16_65536x896', nel * 6, timed(lambda i: core.cast_bf16(((nel + 255) // 256,), (256,), xe_, cb_, ctypes.c_int64(nel))), ne, 'rows_per_s')
+    gub = rnd(ne, 2 * de, scale=2.0).bfloat16(); ab_ = torch.empty(ne, de, dtype=torch.bfloat16, device=dev)
+    line('silu_mul_bf16_65536x896', nel * 6, timed(lambda i: core.silu_mul_bf16(((nel + 255) // 256,), (256,), gub, ab_, I(de), ctypes.c_int64(nel))), ne, 'rows_per_s')
+    ya_ = rnd(ne, de)
+    line('pf_add_sum_65536x896', nel * 16, timed(lambda i: gl.add_sum(xe_, oe_, ya_, nel)), ne, 'rows_per_s')
+    yb_ = torch.empty(PG.tpad(ne), de, dtype=torch.bfloat16, device=dev)
+    line('pf_silu_bf16_65536x896', nel * 6, timed(lambda i: gl.silu_bf16(xe_, yb_, ne, de, 0.5)), ne, 'rows_per_s')
+    line('pf_to_bf16_65536x896', nel * 6, timed(lambda i: gl.to_bf16(xe_, yb_, ne, de)), ne, 'rows_per_s')
+    tp_ = CU.Module('prefill_tp')
+    line('pf_swiglu_f32_65536x896', nel * 12, timed(lambda i: tp_.pf_swiglu(((nel + 255) // 256,), (256,), xe_, oe_, ya_, L_(nel))), ne, 'rows_per_s')
+    toks_e = torch.randint(0, ne, (ne,), device=dev, dtype=torch.int32, generator=g)
+    line('embedding_f32_65536x896', nel * 8, timed(lambda i: core.embedding_f32((ne,), (256,), toks_e, xe_, oe_, I(de))), ne, 'rows_per_s')
+    del xe_, oe_, mb, lb, cb_, gub, ab_, ya_, yb_
     # the one-kernel tensor-parallel norm run by a single rank (its own partial is the only word it waits for): the kernel's HBM side
     from caminus_b200 import dist as DD
     for Ns_ in (640, 2560):

@@ -190,11 +190,7 @@ __global__ void __launch_bounds__(256) add_rms_f32_row_kernel(float * __restrict
 
 // ---- the hyper-connection line's row norms on the warp-per-row mapping (pf_rms_mul, pf_hc_post_rms; K = 128 CH) -----------------
 // The same reference-order reduction as above. POST: the row is res[t, h], first updated in place to fma(b[t], p, res) with
-// p = 2 sigmoid(inj[t, h] rs). Outputs optional: y fp32, ybf bf16 (round to nearest even, no NaN case: prefill_glue.hip's to_bf16), scl.
-CAM_DEV uint32_t bf16x2_rne(float a, float b) {
-    const uint32_t ua = __float_as_uint(a), ub = __float_as_uint(b);
-    return ((ua + 0x7FFFu + ((ua >> 16) & 1u)) >> 16) | ((ub + 0x7FFFu + ((ub >> 16) & 1u)) & 0xffff0000u);
-}
+// p = 2 sigmoid(inj[t, h] rs). Outputs optional: y fp32, ybf bf16 (round to nearest even as prefill_glue.hip's to_bf16; a NaN result stays a NaN, 0x7fc0: see bf16_soft), scl.
 // Q8: also the Q8_1 copy of the normed row (yq: 36-byte blocks, the bytes of gg_quantize_q8_1 on y). 8 adjacent lanes hold a block
 // of 32. The block sum follows the quantiser's 32-lane butterfly (partners 16, 8, 4 are lanes l ^ 4, 2, 1 here, partners 2, 1
 // are inside the lane). The codes roundf(v / d) come from v * rcp(d) where that provably rounds the same way: the product is
@@ -238,7 +234,7 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) rms_rows_vec_kernel(float * x,
             const float4 v = make_float4(fmul(fmul(xv[m].x, scale), ww.x), fmul(fmul(xv[m].y, scale), ww.y), fmul(fmul(xv[m].z, scale), ww.z),
                                          fmul(fmul(xv[m].w, scale), ww.w));
             if (y) *reinterpret_cast<float4 *>(y + (size_t)t * K + 4 * lane + 128 * m) = v;
-            if (ybf) st64_stream(ybf + (size_t)t * K + 4 * lane + 128 * m, make_uint2(bf16x2_rne(v.x, v.y), bf16x2_rne(v.z, v.w)));
+            if (ybf) st64_stream(ybf + (size_t)t * K + 4 * lane + 128 * m, make_uint2(bf16x2<true>(v.x, v.y), bf16x2<true>(v.z, v.w)));
             if (Q8) {
                 float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
                 float s0 = v.x, s1 = v.y, s2 = v.z, s3 = v.w;
@@ -605,7 +601,7 @@ extern "C" int cam_rms_norm_f16_static(int n, void * x, const void * d, const fl
     return launch_f16<2>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, nullptr, ss, N, N, n, (cudaStream_t)stream);
 }
 
-// The vector path of pf_rms_mul / pf_hc_post_rms (csrc/hc_glue.cu): K in {2048, 2560, 5120}, 16-byte aligned buffers, enough rows to
+// The vector path of pf_rms_mul / pf_hc_post_rms / rmsnorm_f32 (csrc/hc_glue.cu): K in {2048, 2560, 5120} (the plain norm: more multiples of 128), 16-byte aligned buffers, enough rows to
 // fill the device. Returns CAM_ERR_SHAPE when it does not apply (the caller then uses its block-per-row kernel).
 int cam_rms_rows_vec(float * x, const float * w, float * y, void * ybf, float * scl, int R, int wr, float eps, int K, const float * b,
                      const float * inj, int HC, float rs, void * stream, void * yq) {
@@ -625,6 +621,14 @@ int cam_rms_rows_vec(float * x, const float * w, float * y, void * ybf, float * 
         case 2048: return b ? launch_rows_vec<16, true>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st) : launch_rows_vec<16, false>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st);
         case 2560: return b ? launch_rows_vec<20, true>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st) : launch_rows_vec<20, false>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st);
         case 5120: return b ? launch_rows_vec<40, true>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st) : launch_rows_vec<40, false>(x, w, y, yb, scl, R, wr, eps, b, inj, HC, rs, st);
+        default: break;
+    }
+    if (b) return CAM_ERR_SHAPE;
+    switch (K) {    // the plain norm (rmsnorm_f32's row lengths among them): any multiple of 128 follows the same lane-to-thread mapping
+#define CAM_ROWS_CASE(CH) case 128 * CH: return launch_rows_vec<CH, false>(x, w, y, yb, scl, R, wr, eps, nullptr, nullptr, 1, 0.0f, st)
+        CAM_ROWS_CASE(4); CAM_ROWS_CASE(5); CAM_ROWS_CASE(6); CAM_ROWS_CASE(7); CAM_ROWS_CASE(8); CAM_ROWS_CASE(10); CAM_ROWS_CASE(12);
+        CAM_ROWS_CASE(14); CAM_ROWS_CASE(24); CAM_ROWS_CASE(28); CAM_ROWS_CASE(32);
+#undef CAM_ROWS_CASE
         default: return CAM_ERR_SHAPE;
     }
 }

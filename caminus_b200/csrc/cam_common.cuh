@@ -89,6 +89,9 @@ CAM_DEV uint16_t f_to_h(float a) { return __half_as_ushort(__float2half_rn(a)); 
 // The reference's integer statements, u + 0x7fff + ((u >> 16) & 1), are IEEE round-to-nearest-even for every number, which is what
 // the conversion instruction does. For a NaN operand the integer statements decide the bits: NANQ true: 0x7fc0 (the training
 // line's f2bf, kernels/actq.hip:23-28, kernels/core.hip); false: the carry may turn a NaN into an infinity (prefill_glue's to_bf16).
+// The false form is for bits a caller stored (a plain conversion of an input). A NaN this device COMPUTED is 0x7fffffff, which the
+// integer statements would carry into 0x8000, a zero, where the reference's hardware returns the operand's quieted payload (0x7fc0 for
+// the usual NaN) that they keep a NaN: computed values under prefill_glue's rule therefore use the true form, so a NaN stays a NaN.
 template <bool NANQ> CAM_DEV uint32_t bf16_soft(float f) {
     uint32_t u = __float_as_uint(f);
     if (NANQ && (u & 0x7fffffffu) > 0x7f800000u) return 0x7fc0u;

@@ -12,7 +12,7 @@ namespace {
 
 constexpr int ROW_MAX_NI = 32;       // row lengths up to 8192
 
-CAM_DEV uint16_t bf16_rne(float v) {       // prefill_glue.hip's to_bf16: round to nearest even, no NaN case
+CAM_DEV uint16_t bf16_rne(float v) {       // prefill_glue.hip's to_bf16: round to nearest even, no NaN case (for stored inputs; computed values: bf16_nan)
     const uint32_t u = __float_as_uint(v);
     return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
 }
@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(256) rms_rows_kernel(const float * x, const fl
             if (tid + 256 * j < K) {
                 const float v = fmul(fmul(xv[j], scale), __ldg(wv + tid + 256 * j));
                 if (y) y[(size_t)t * K + tid + 256 * j] = v;
-                if (ybf) ybf[(size_t)t * K + tid + 256 * j] = bf16_rne(v);
+                if (ybf) ybf[(size_t)t * K + tid + 256 * j] = bf16_nan(v);
                 if (yq) {      // the Q8_1 copy (q8_emit: the warp's 32 consecutive values are one block; K a multiple of 32 keeps a warp whole)
                     float amax = fabsf(v), sum = v;
 #pragma unroll
@@ -198,6 +198,116 @@ __global__ void __launch_bounds__(256) ew_kernel(const void * __restrict__ a, co
     }
 }
 
+// the same ops, four consecutive elements per item and two items in flight per thread (16-byte aligned fp32 buffers, 8-byte
+// aligned bf16 buffers); the n % 4 last elements go to the first threads of block 0
+CAM_DEV float2 bf16x2_f(uint32_t w) { return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u)); }
+template <int OP>
+CAM_DEV void ew_item(const void * a, const void * b, const void * c, void * y, long i, float4 av, uint2 bw, uint2 cw, float4 bv, float4 yv) {
+    if (OP == EW_ADD_SUM)
+        *(reinterpret_cast<float4 *>(y) + i) = make_float4(fadd(yv.x, fadd(av.x, bv.x)), fadd(yv.y, fadd(av.y, bv.y)), fadd(yv.z, fadd(av.z, bv.z)), fadd(yv.w, fadd(av.w, bv.w)));
+    if (OP == EW_SWIGLU)
+        __stcs(reinterpret_cast<float4 *>(y) + i, make_float4(fmul(cam_silu(av.x), bv.x), fmul(cam_silu(av.y), bv.y), fmul(cam_silu(av.z), bv.z), fmul(cam_silu(av.w), bv.w)));
+    if (OP == EW_RESIDUAL3) {
+        const float2 m0 = bf16x2_f(bw.x), m1 = bf16x2_f(bw.y), l0 = bf16x2_f(cw.x), l1 = bf16x2_f(cw.y);
+        __stcs(reinterpret_cast<float4 *>(y) + i, make_float4(fadd(fadd(av.x, m0.x), l0.x), fadd(fadd(av.y, m0.y), l0.y), fadd(fadd(av.z, m1.x), l1.x), fadd(fadd(av.w, m1.y), l1.y)));
+    }
+    if (OP == EW_CAST_BF16) __stcs(reinterpret_cast<uint2 *>(y) + i, make_uint2(bf16x2<true>(av.x, av.y), bf16x2<true>(av.z, av.w)));
+}
+template <int OP>
+__global__ void __launch_bounds__(256) ew_vec_kernel(const void * __restrict__ a, const void * __restrict__ b, const void * __restrict__ c, void * y, long n) {
+    const long n4 = n >> 2, stride = (long)gridDim.x * 256;
+    for (long i0 = (long)blockIdx.x * 256 + threadIdx.x; i0 < n4; i0 += 2 * stride) {
+        float4 av[2], bv[2], yv[2]; uint2 bw[2], cw[2];
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const long i = i0 + k * stride;
+            if (i >= n4) continue;
+            av[k] = __ldg(reinterpret_cast<const float4 *>(a) + i);
+            if (OP == EW_ADD_SUM || OP == EW_SWIGLU) bv[k] = __ldg(reinterpret_cast<const float4 *>(b) + i);
+            if (OP == EW_ADD_SUM) yv[k] = *(reinterpret_cast<const float4 *>(y) + i);
+            if (OP == EW_RESIDUAL3) { bw[k] = __ldg(reinterpret_cast<const uint2 *>(b) + i); cw[k] = __ldg(reinterpret_cast<const uint2 *>(c) + i); }
+        }
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const long i = i0 + k * stride;
+            if (i < n4) ew_item<OP>(a, b, c, y, i, av[k], bw[k], cw[k], bv[k], yv[k]);
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (int)(n & 3)) {
+        const long i = (n4 << 2) + threadIdx.x;
+        if (OP == EW_ADD_SUM) { float * yy = (float *)y; yy[i] = fadd(yy[i], fadd(__ldg((const float *)a + i), __ldg((const float *)b + i))); }
+        if (OP == EW_SWIGLU) ((float *)y)[i] = fmul(cam_silu(__ldg((const float *)a + i)), __ldg((const float *)b + i));
+        if (OP == EW_RESIDUAL3)
+            ((float *)y)[i] = fadd(fadd(__ldg((const float *)a + i), bf16_f(__ldg((const uint16_t *)b + i))), bf16_f(__ldg((const uint16_t *)c + i)));
+        if (OP == EW_CAST_BF16) ((uint16_t *)y)[i] = bf16_nan(__ldg((const float *)a + i));
+    }
+}
+// bf16(silu(g)) without the exact statements' two divisions and polynomial where that provably gives the same 16 bits: the
+// special-function evaluation s^ = g rcp(1 + ex2(-g log2 e)) is within 1.35e-6 |s| of cam_silu(g) for g >= -8 and 3e-38 <= |g| < 3e38
+// (the analysis at the fused SwiGLU + Q8_1 kernel, csrc/swiglu_q8.cu, without its last product). If s^ (1 - 1.55e-6) and s^ (1 + 1.55e-6) round to the same
+// bf16, no rounding boundary and no tie lies in the interval that holds cam_silu(g), and that bf16 is its rounding. Anything
+// else (1 value in about 1400, NaN and infinities among them) evaluates the exact statements. g = +-0 gives +-0 both ways.
+// NANQ: the NaN rule of the rounding (see bf16_soft).
+template <bool NANQ> CAM_DEV uint32_t silu_bf16_bits(float g) {
+    const float e = ex2_approx(fmul(g, -0x1.715476p+0f));
+    const float s = fmul(g, rcp_approx(fadd(1.0f, e)));
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(fmul(s, 0x1.00001ap+0f)), "f"(fmul(s, 0x1.ffffccp-1f)));
+    const float ag = fabsf(g);
+    const bool proven = (r >> 16) == (r & 0xffffu) && g >= -8.0f && ag < 3.0e38f && (ag >= 3.0e-38f || g == 0.0f);
+    if (!proven) r = bf16_soft<NANQ>(cam_silu(g));
+    return r & 0xffffu;
+}
+
+// pf_silu_bf16 / pf_to_bf16 over items of four elements: item i is row i / K4, columns 4 (i % K4) .. (K4 = K / 4; the division only when
+// the rows are strided); items of the padding rows store zeros
+template <bool SILU>
+__global__ void __launch_bounds__(256) to_bf16_vec_kernel(const float * __restrict__ x, int ldx, uint16_t * __restrict__ y, unsigned live, unsigned all, unsigned K4, float rs) {
+    const unsigned stride = gridDim.x * 256u;
+    const bool dense = (unsigned)ldx == 4u * K4;
+    for (unsigned i0 = blockIdx.x * 256u + threadIdx.x; i0 < all; i0 += 2 * stride) {
+        float4 v[2];
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const unsigned i = i0 + k * stride;
+            if (i >= live) continue;
+            size_t src = (size_t)i * 4;
+            if (!dense) { const unsigned r = i / K4; src = (size_t)r * ldx + (size_t)(i - r * K4) * 4; }
+            v[k] = __ldg(reinterpret_cast<const float4 *>(x + src));
+        }
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const unsigned i = i0 + k * stride;
+            if (i >= all) continue;
+            uint2 o = make_uint2(0u, 0u);
+            if (i < live) {
+                if (SILU) o = make_uint2(silu_bf16_bits<true>(ffma(rs, v[k].x, 0.0f)) | (silu_bf16_bits<true>(ffma(rs, v[k].y, 0.0f)) << 16),
+                                         silu_bf16_bits<true>(ffma(rs, v[k].z, 0.0f)) | (silu_bf16_bits<true>(ffma(rs, v[k].w, 0.0f)) << 16));
+                else o = make_uint2(bf16x2<false>(v[k].x, v[k].y), bf16x2<false>(v[k].z, v[k].w));
+            }
+            __stcs(reinterpret_cast<uint2 *>(y) + i, o);
+        }
+    }
+}
+
+// silu_mul_bf16 over items of eight elements: item i is row i / H8, columns 8 (i % H8) .. of the rows [g | u] (H8 = H / 8)
+__global__ void __launch_bounds__(256) silu_mul_bf16_vec_kernel(const uint16_t * __restrict__ gu, uint16_t * __restrict__ act, unsigned H8, unsigned items) {
+    const unsigned stride = gridDim.x * 256u;
+    for (unsigned i = blockIdx.x * 256u + threadIdx.x; i < items; i += stride) {
+        const unsigned r = i / H8, c8 = i - r * H8;
+        const uint4 gw = ldg128(gu + ((size_t)r * 2 * H8 + c8) * 8), uw = ldg128(gu + ((size_t)r * 2 * H8 + H8 + c8) * 8);
+        const uint32_t gs[4] = {gw.x, gw.y, gw.z, gw.w}, us[4] = {uw.x, uw.y, uw.z, uw.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float2 g = bf16x2_f(gs[k]), u = bf16x2_f(us[k]);
+            const float s0 = __uint_as_float(silu_bf16_bits<true>(g.x) << 16), s1 = __uint_as_float(silu_bf16_bits<true>(g.y) << 16);
+            o[k] = bf16x2<true>(fmul(s0, u.x), fmul(s1, u.y));
+        }
+        st128_stream(act + (size_t)i * 8, make_uint4(o[0], o[1], o[2], o[3]));
+    }
+}
+
 template <bool SILU>
 __global__ void __launch_bounds__(256) to_bf16_kernel(const float * __restrict__ x, int ldx, uint16_t * __restrict__ y, int T, int Tpad, int K, float rs) {
     for (int t = blockIdx.x; t < Tpad; t += gridDim.x)                 // (a block per row: no index is divided)
@@ -205,7 +315,7 @@ __global__ void __launch_bounds__(256) to_bf16_kernel(const float * __restrict__
             uint16_t v = 0;
             if (t < T) {
                 const float xv = __ldg(x + (size_t)t * ldx + j);
-                v = bf16_rne(SILU ? cam_silu(ffma(rs, xv, 0.0f)) : xv);
+                v = SILU ? bf16_nan(cam_silu(ffma(rs, xv, 0.0f))) : bf16_rne(xv);
             }
             y[(size_t)t * K + j] = v;
         }
@@ -252,6 +362,98 @@ __global__ void __launch_bounds__(256) embedding_f32_kernel(const int * __restri
     const int t = blockIdx.x;
     const float * src = emb + (size_t)__ldg(tok + t) * D;
     for (int j = threadIdx.x; j < D; j += 256) out[(size_t)t * D + j] = __ldg(src + j);
+}
+
+// a warp per token row, 16 bytes per lane and load (D a multiple of 4, 16-byte aligned table and output)
+__global__ void __launch_bounds__(256) embedding_f32_vec_kernel(const int * __restrict__ tok, const float * __restrict__ emb, float * __restrict__ out, int D4, int T) {
+    const int lane = threadIdx.x & 31;
+    for (int t = blockIdx.x * 8 + (threadIdx.x >> 5); t < T; t += gridDim.x * 8) {
+        const float4 * src = reinterpret_cast<const float4 *>(emb) + (size_t)__ldg(tok + t) * D4;
+        float4 * dst = reinterpret_cast<float4 *>(out) + (size_t)t * D4;
+#pragma unroll 8
+        for (int j = lane; j < D4; j += 32) __stcs(dst + j, __ldg(src + j));
+    }
+}
+
+// pf_qk_nr, a warp per token row looping over the row's heads (D and head_stride multiples of 4, 16-byte aligned buffers, whole token
+// rows; NCH = chunks of 128 values per head). The powers theta_scale^j are computed once per block and a token's sines and cosines
+// once per token, by the warp that owns it, instead of once per head (the same statements on the same operands give the same bits);
+// the sum of squares is the 256-thread order above (ref_total_f32), lane l holding elements 128 m + 4 l .. + 3. The normed head is
+// staged in the warp's slice of shared memory, where the rotation reads its partners; the next head's values are loaded before the
+// current head is reduced. No barrier after the table of powers.
+constexpr int NR_WARPS = 8;
+template <int NCH>
+__global__ void __launch_bounds__(NR_WARPS * 32) qk_nr_vec_kernel(const float * __restrict__ xin, int head_stride, int heads, const float * __restrict__ w, int D, int nrot,
+                                                                  float theta_scale, float eps, int pos0, float * __restrict__ out, int rows) {
+    __shared__ float pw[64 * NCH];
+    __shared__ float sn_s[NR_WARPS][64 * NCH], cs_s[NR_WARPS][64 * NCH];
+    __shared__ __align__(16) float nrm_s[NR_WARPS][128 * NCH];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, half = nrot >> 1;
+    for (int j = tid; j < half; j += NR_WARPS * 32) pw[j] = cam_powi(theta_scale, j);
+    __syncthreads();
+    float * nrm = nrm_s[warp]; float * sns = sn_s[warp]; float * css = cs_s[warp];
+    const float4 zero4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 wv[NCH];
+#pragma unroll
+    for (int m = 0; m < NCH; m++) wv[m] = 128 * m + 4 * lane < D ? __ldg(reinterpret_cast<const float4 *>(w + 128 * m + 4 * lane)) : zero4;
+    for (int row = blockIdx.x * NR_WARPS + warp; row < rows; row += gridDim.x * NR_WARPS) {
+        const float * x = xin + (size_t)row * heads * head_stride + 4 * lane;
+        float4 nx[NCH];
+#pragma unroll
+        for (int m = 0; m < NCH; m++) nx[m] = 128 * m + 4 * lane < D ? __ldg(reinterpret_cast<const float4 *>(x + 128 * m)) : zero4;
+        const float pos = (float)(pos0 + row);
+        for (int j = lane; j < half; j += 32) cam_sincos(fmul(pos, pw[j]), sns[j], css[j]);
+        __syncwarp();
+        for (int h = 0; h < heads; h++) {
+            float4 xv[NCH];
+#pragma unroll
+            for (int m = 0; m < NCH; m++) xv[m] = nx[m];
+            if (h + 1 < heads) {
+                const float * xn = x + (size_t)(h + 1) * head_stride;
+#pragma unroll
+                for (int m = 0; m < NCH; m++) nx[m] = 128 * m + 4 * lane < D ? __ldg(reinterpret_cast<const float4 *>(xn + 128 * m)) : zero4;
+            }
+            float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int m = 0; m < NCH; m++) {
+                const int q = 4 * (m & 1);
+                a[q + 0] = ffma(xv[m].x, xv[m].x, a[q + 0]); a[q + 1] = ffma(xv[m].y, xv[m].y, a[q + 1]);
+                a[q + 2] = ffma(xv[m].z, xv[m].z, a[q + 2]); a[q + 3] = ffma(xv[m].w, xv[m].w, a[q + 3]);
+            }
+            const float tot = ref_total_f32(a, lane);
+            const float scale = cam_rsqrt(fadd(fdiv(tot, (float)D), eps));
+#pragma unroll
+            for (int m = 0; m < NCH; m++) {
+                xv[m] = make_float4(fmul(fmul(scale, xv[m].x), wv[m].x), fmul(fmul(scale, xv[m].y), wv[m].y), fmul(fmul(scale, xv[m].z), wv[m].z),
+                                    fmul(fmul(scale, xv[m].w), wv[m].w));
+                if (128 * m < nrot) *reinterpret_cast<float4 *>(nrm + 128 * m + 4 * lane) = xv[m];
+            }
+            __syncwarp();
+            float * y = out + ((size_t)row * heads + h) * D + 4 * lane;
+#pragma unroll
+            for (int m = 0; m < NCH; m++) {
+                const int e = 128 * m + 4 * lane;
+                if (e >= D) continue;
+                float o[4] = {xv[m].x, xv[m].y, xv[m].z, xv[m].w};
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int i = e + c;
+                    if (i >= nrot) continue;
+                    const int j = i < half ? i : i - half;
+                    const float x0 = nrm[j], x1 = nrm[j + half], sn = sns[j], cs = css[j];
+                    o[c] = i < half ? ffma(x0, cs, -fmul(x1, sn)) : ffma(x0, sn, fmul(x1, cs));
+                }
+                __stcs(reinterpret_cast<float4 *>(y + 128 * m), make_float4(o[0], o[1], o[2], o[3]));
+            }
+            __syncwarp();     // the next head overwrites the slice, the next token the table
+        }
+    }
+}
+template <int NCH>
+void launch_qk_nr_vec(const float * xin, int head_stride, int heads, const float * w, int D, int nrot, float theta_scale, float eps, int pos0, float * out, int rows,
+                      cudaStream_t stream) {
+    const int grid = cam_resident_grid(qk_nr_vec_kernel<NCH>, NR_WARPS * 32, 0, (rows + NR_WARPS - 1) / NR_WARPS);
+    qk_nr_vec_kernel<NCH><<<grid, NR_WARPS * 32, 0, stream>>>(xin, head_stride, heads, w, D, nrot, theta_scale, eps, pos0, out, rows);
 }
 
 // pf_qk_nr: block t = row * heads + head; D <= 512
@@ -352,27 +554,37 @@ extern "C" int pf_hc_mean(const float * x, const float * scl, const float * w, c
 extern "C" int pf_add_sum(const float * a, const float * b, float * y, long n, void * stream) {
     if (n < 0 || !a || !b || !y) return CAM_ERR_ARG;
     if (n == 0) return CAM_OK;
-    ew_kernel<EW_ADD_SUM><<<grid_for(n), 256, 0, CAM_STREAM>>>(a, b, nullptr, y, n);
+    if (n >= 4 && cam_aligned16(a) && cam_aligned16(b) && cam_aligned16(y))
+        ew_vec_kernel<EW_ADD_SUM><<<cam_resident_grid(ew_vec_kernel<EW_ADD_SUM>, 256, 0, ((n >> 2) + 511) / 512), 256, 0, CAM_STREAM>>>(a, b, nullptr, y, n);
+    else ew_kernel<EW_ADD_SUM><<<grid_for(n), 256, 0, CAM_STREAM>>>(a, b, nullptr, y, n);
     return (int)cudaGetLastError();
 }
 // pf_swiglu: kernels/prefill_tp.hip:37-43
 extern "C" int pf_swiglu(const float * g, const float * u, float * y, long n, void * stream) {
     if (n < 0 || !g || !u || !y) return CAM_ERR_ARG;
     if (n == 0) return CAM_OK;
-    ew_kernel<EW_SWIGLU><<<grid_for(n), 256, 0, CAM_STREAM>>>(g, u, nullptr, y, n);
+    if (n >= 4 && cam_aligned16(g) && cam_aligned16(u) && cam_aligned16(y))
+        ew_vec_kernel<EW_SWIGLU><<<cam_resident_grid(ew_vec_kernel<EW_SWIGLU>, 256, 0, ((n >> 2) + 511) / 512), 256, 0, CAM_STREAM>>>(g, u, nullptr, y, n);
+    else ew_kernel<EW_SWIGLU><<<grid_for(n), 256, 0, CAM_STREAM>>>(g, u, nullptr, y, n);
     return (int)cudaGetLastError();
 }
 // pf_silu_bf16 / pf_to_bf16: kernels/prefill_glue.hip:554, 561
 extern "C" int pf_silu_bf16(const float * x, int ldx, void * y, int T, int Tpad, int K, float rs, void * stream) {
     if (T < 0 || Tpad < T || K < 1 || ldx < K || !x || !y) return CAM_ERR_ARG;
     if (Tpad == 0) return CAM_OK;
-    to_bf16_kernel<true><<<cam_resident_grid(to_bf16_kernel<true>, 256, 0, Tpad), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, T, Tpad, K, rs);
+    if (!(K & 3) && !(ldx & 3) && (long)Tpad * (K >> 2) < 0x7fffffffL && cam_aligned16(x) && !(reinterpret_cast<uintptr_t>(y) & 7u)) {
+        const unsigned K4 = (unsigned)(K >> 2), live = (unsigned)T * K4, all = (unsigned)Tpad * K4;
+        to_bf16_vec_kernel<true><<<cam_resident_grid(to_bf16_vec_kernel<true>, 256, 0, ((long)all + 511) / 512), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, live, all, K4, rs);
+    } else to_bf16_kernel<true><<<cam_resident_grid(to_bf16_kernel<true>, 256, 0, Tpad), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, T, Tpad, K, rs);
     return (int)cudaGetLastError();
 }
 extern "C" int pf_to_bf16(const float * x, int ldx, void * y, int T, int Tpad, int K, void * stream) {
     if (T < 0 || Tpad < T || K < 1 || ldx < K || !x || !y) return CAM_ERR_ARG;
     if (Tpad == 0) return CAM_OK;
-    to_bf16_kernel<false><<<cam_resident_grid(to_bf16_kernel<false>, 256, 0, Tpad), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, T, Tpad, K, 0.0f);
+    if (!(K & 3) && !(ldx & 3) && (long)Tpad * (K >> 2) < 0x7fffffffL && cam_aligned16(x) && !(reinterpret_cast<uintptr_t>(y) & 7u)) {
+        const unsigned K4 = (unsigned)(K >> 2), live = (unsigned)T * K4, all = (unsigned)Tpad * K4;
+        to_bf16_vec_kernel<false><<<cam_resident_grid(to_bf16_vec_kernel<false>, 256, 0, ((long)all + 511) / 512), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, live, all, K4, 0.0f);
+    } else to_bf16_kernel<false><<<cam_resident_grid(to_bf16_kernel<false>, 256, 0, Tpad), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, T, Tpad, K, 0.0f);
     return (int)cudaGetLastError();
 }
 // pf_qk_nr: kernels/prefill_attn.hip:105-106 (= op_qk_nr, kernels/k3_gguf_ops.h:1490-1518); nblocks = rows * heads is the reference's grid.x
@@ -381,7 +593,12 @@ extern "C" int pf_qk_nr(int nblocks, const float * xin, int head_stride, int hea
     if (nblocks < 0 || heads < 1 || D < 1 || D > 512 || nrot < 0 || nrot > D || (nrot & 1) || head_stride < D || pos0 < 0 || !xin || !w || !out) return CAM_ERR_ARG;
     if ((long)pos0 + nblocks / heads > (1L << 22)) return CAM_ERR_SHAPE;
     if (nblocks == 0) return CAM_OK;
-    qk_nr_kernel<<<nblocks, 256, 0, CAM_STREAM>>>(xin, head_stride, heads, w, D, nrot, theta_scale, eps, pos0, out);
+    if (!(D & 3) && !(head_stride & 3) && nblocks % heads == 0 && cam_aligned16(xin) && cam_aligned16(w) && cam_aligned16(out)) {
+        const int rows = nblocks / heads;
+        if (D <= 128) launch_qk_nr_vec<1>(xin, head_stride, heads, w, D, nrot, theta_scale, eps, pos0, out, rows, CAM_STREAM);
+        else if (D <= 256) launch_qk_nr_vec<2>(xin, head_stride, heads, w, D, nrot, theta_scale, eps, pos0, out, rows, CAM_STREAM);
+        else launch_qk_nr_vec<4>(xin, head_stride, heads, w, D, nrot, theta_scale, eps, pos0, out, rows, CAM_STREAM);
+    } else qk_nr_kernel<<<nblocks, 256, 0, CAM_STREAM>>>(xin, head_stride, heads, w, D, nrot, theta_scale, eps, pos0, out);
     return (int)cudaGetLastError();
 }
 // embedding_f32 / rmsnorm_f32 / silu_mul_bf16 / residual3 / cast_bf16: kernels/core.hip:23-66 (T, rows = the reference's grid.x);
@@ -389,31 +606,48 @@ extern "C" int pf_qk_nr(int nblocks, const float * xin, int head_stride, int hea
 extern "C" int embedding_f32(int T, const int * tok, const float * emb, float * out, int D, void * stream) {
     if (T < 0 || D < 1 || !tok || !emb || !out) return CAM_ERR_ARG;
     if (T == 0) return CAM_OK;
-    embedding_f32_kernel<<<T, 256, 0, CAM_STREAM>>>(tok, emb, out, D);
+    if (!(D & 3) && cam_aligned16(emb) && cam_aligned16(out))
+        embedding_f32_vec_kernel<<<cam_resident_grid(embedding_f32_vec_kernel, 256, 0, (T + 7) / 8), 256, 0, CAM_STREAM>>>(tok, emb, out, D >> 2, T);
+    else embedding_f32_kernel<<<T, 256, 0, CAM_STREAM>>>(tok, emb, out, D);
     return (int)cudaGetLastError();
 }
 extern "C" int rmsnorm_f32(int rows, const float * x, const float * w, float * out, int D, float eps, void * stream) {
     if (rows < 0 || D < 1 || D > 256 * ROW_MAX_NI || !x || !w || !out) return CAM_ERR_ARG;
     if (rows == 0) return CAM_OK;
+    {
+        const int r = cam_rms_rows_vec(const_cast<float *>(x), w, out, nullptr, nullptr, rows, 1, eps, D, nullptr, nullptr, 1, 0.0f, stream);
+        if (r != CAM_ERR_SHAPE) return r;
+    }
     rms_rows_kernel<2><<<rows < cam_sm_count() * 8 ? rows : cam_sm_count() * 8, 256, 0, CAM_STREAM>>>(x, w, out, nullptr, nullptr, rows, 1, eps, D, nullptr, nullptr, 1, 0.0f, nullptr);
     return (int)cudaGetLastError();
 }
 extern "C" int silu_mul_bf16(const void * gu, void * act, int H, long n, void * stream) {
     if (n < 0 || H < 1 || !gu || !act) return CAM_ERR_ARG;
     if (n == 0) return CAM_OK;
-    silu_mul_bf16_kernel<<<grid_for(n), 256, 0, CAM_STREAM>>>((const uint16_t *)gu, (uint16_t *)act, H, n);
+    const long rows = n / H;
+    if (!(H & 7) && rows > 0 && rows * (H >> 3) < 0x7fffffffL && cam_aligned16(gu) && cam_aligned16(act)) {     // whole rows by vectors, a last partial row by elements
+        const unsigned items = (unsigned)(rows * (H >> 3));
+        silu_mul_bf16_vec_kernel<<<cam_resident_grid(silu_mul_bf16_vec_kernel, 256, 0, (items + 255) / 256), 256, 0, CAM_STREAM>>>((const uint16_t *)gu, (uint16_t *)act,
+                                                                                                                        (unsigned)(H >> 3), items);
+        const long rest = n - rows * H;
+        if (rest) silu_mul_bf16_kernel<<<grid_for(rest), 256, 0, CAM_STREAM>>>((const uint16_t *)gu + rows * 2 * H, (uint16_t *)act + rows * H, H, rest);
+    } else silu_mul_bf16_kernel<<<grid_for(n), 256, 0, CAM_STREAM>>>((const uint16_t *)gu, (uint16_t *)act, H, n);
     return (int)cudaGetLastError();
 }
 extern "C" int residual3(const float * x, const void * m, const void * y, float * out, long n, void * stream) {
     if (n < 0 || !x || !m || !y || !out) return CAM_ERR_ARG;
     if (n == 0) return CAM_OK;
-    ew_kernel<EW_RESIDUAL3><<<grid_for(n), 256, 0, CAM_STREAM>>>(x, m, y, out, n);
+    if (n >= 4 && cam_aligned16(x) && cam_aligned16(out) && !(reinterpret_cast<uintptr_t>(m) & 7u) && !(reinterpret_cast<uintptr_t>(y) & 7u))
+        ew_vec_kernel<EW_RESIDUAL3><<<cam_resident_grid(ew_vec_kernel<EW_RESIDUAL3>, 256, 0, ((n >> 2) + 511) / 512), 256, 0, CAM_STREAM>>>(x, m, y, out, n);
+    else ew_kernel<EW_RESIDUAL3><<<grid_for(n), 256, 0, CAM_STREAM>>>(x, m, y, out, n);
     return (int)cudaGetLastError();
 }
 extern "C" int cast_bf16(const float * x, void * out, long n, void * stream) {
     if (n < 0 || !x || !out) return CAM_ERR_ARG;
     if (n == 0) return CAM_OK;
-    ew_kernel<EW_CAST_BF16><<<grid_for(n), 256, 0, CAM_STREAM>>>(x, nullptr, nullptr, out, n);
+    if (n >= 4 && cam_aligned16(x) && !(reinterpret_cast<uintptr_t>(out) & 7u))
+        ew_vec_kernel<EW_CAST_BF16><<<cam_resident_grid(ew_vec_kernel<EW_CAST_BF16>, 256, 0, ((n >> 2) + 511) / 512), 256, 0, CAM_STREAM>>>(x, nullptr, nullptr, out, n);
+    else ew_kernel<EW_CAST_BF16><<<grid_for(n), 256, 0, CAM_STREAM>>>(x, nullptr, nullptr, out, n);
     return (int)cudaGetLastError();
 }
 // residual_slices_fwd: kernels/fuse.hip:19-20; wrapper python/caminus/train/fuse.py:19-30. d a multiple of 4.

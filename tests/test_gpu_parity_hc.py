@@ -129,6 +129,107 @@ def test_training_line_forwards():
     assert same(ro, r3)
 
 
+def specials32():
+    """fp32 values the fast evaluations must hand to the exact statements or get right: zeros, denormals, the -8 gate bound, the
+    exp clamps, huge values, infinities, NaNs"""
+    v = np.array([0.0, -0.0, 1e-45, -1e-45, 1e-39, -3e-39, 2.9e-38, 3.1e-38, -8.0, -8.000001, -7.999999, -20.0, -87.0, -88.5, -104.0, 87.0, 88.0, 89.0,
+                  1e30, -1e30, 3.3e38, -3.3e38, np.inf, -np.inf, np.nan, 1.0, -1.0, 0.5, 65504.0], np.float32)
+    nan2 = np.array([0x7fa00001, 0xffc12345, 0x7f800001], np.uint32).view(np.float32)       # signalling and payload NaNs
+    return np.concatenate([v, nan2])
+
+
+def same_but_nan(a, b):
+    """bit-equal where the oracle's value is a number; where it is a NaN the device's must be one too (the payload of a computed NaN
+    is the arithmetic unit's: 0x7fffffff on this device, the operand's quieted payload on the CPU)"""
+    a, b = bits(a), bits(b)
+    if a.dtype == np.uint32: na, nb = (a & 0x7fffffff) > 0x7f800000, (b & 0x7fffffff) > 0x7f800000
+    else: na, nb = (a & 0x7fff) > 0x7f80, (b & 0x7fff) > 0x7f80
+    return np.array_equal(na, nb) and np.array_equal(a[~nb], b[~nb])
+
+
+def test_silu_mul_bf16_every_gate():
+    """every one of the 65536 bf16 gate patterns through the vector kernel (its proof-or-exact rounding), against a few ups"""
+    core = hip.Module('core'); H = 65536
+    gpat = np.arange(H, dtype=np.uint16); g = np.random.default_rng(40)
+    ups = [np.full(H, 0x3f80, np.uint16), (g.standard_normal(H) * 2).astype(np.float32).view(np.uint32) >> 16,
+           np.resize(np.array([0x7f80, 0xff80, 0x7fc0, 0x0000, 0x8000, 0x0001, 0x7f7f, 0xc2f0], np.uint16), H)]
+    gu = np.concatenate([np.concatenate([gpat, np.asarray(u, np.uint16)]) for u in ups]).reshape(3, 2 * H)
+    gd = torch.from_numpy(gu.view(np.int16)).to(DEV).view(torch.bfloat16); act = bfz(3 * H)
+    core.silu_mul_bf16(((3 * H + 255) // 256,), (256,), gd, act, I(H), ctypes.c_int64(3 * H))
+    assert same(act, oracle.silu_mul_bf16(gu, H))
+    n = 2 * H + 1000                                                       # whole rows by vectors, the partial third row by elements
+    act2 = bfz(3 * H)
+    core.silu_mul_bf16(((n + 255) // 256,), (256,), gd, act2, I(H), ctypes.c_int64(n))
+    assert same(act2[:n], bits(act)[:n]) and not bits(act2)[n:].any()
+    H2 = 100                                                               # a row length the vector kernel does not take
+    gu2 = gu.reshape(-1)[:40 * 2 * H2].copy(); a3 = bfz(40 * H2)
+    core.silu_mul_bf16(((40 * H2 + 255) // 256,), (256,), torch.from_numpy(gu2.view(np.int16)).to(DEV).view(torch.bfloat16), a3, I(H2), ctypes.c_int64(40 * H2))
+    assert same(a3, oracle.silu_mul_bf16(gu2, H2))
+
+
+@pytest.mark.parametrize('T,K,ldx,rs', [(1500, 1024, 1024, 1.0), (700, 896, 1000, 0.5), (130, 322, 322, 0.25)])
+def test_bf16_operands_hard_inputs(T, K, ldx, rs):
+    """pf_silu_bf16 / pf_to_bf16 on wide-ranging inputs and the special values: dense rows, strided rows, a width without the vector path"""
+    gl = G.Glue(DEV); g = np.random.default_rng(T)
+    x = (g.standard_normal((T, ldx)) * np.exp(g.uniform(-6, 4, (T, ldx)))).astype(np.float32)
+    sp = specials32()
+    with np.errstate(all='ignore'):
+        x.reshape(-1)[: 40 * sp.size] = np.tile(sp, 40) / np.float32(rs) * np.repeat(np.linspace(0.999, 1.001, 40, dtype=np.float32), sp.size)
+    x.reshape(-1)[40 * sp.size: 41 * sp.size] = sp
+    Tp = G.tpad(T); y = torch.full((Tp, K), 7.0, dtype=torch.bfloat16, device=DEV)
+    gl.silu_bf16(cu(x), y, T, K, rs, ldx=ldx)
+    assert same_but_nan(y, oracle.pf_to_bf16(x, ldx, T, Tp, K, rs=rs))
+    y.fill_(7.0); gl.to_bf16(cu(x), y, T, K, ldx=ldx)
+    assert same(y, oracle.pf_to_bf16(x, ldx, T, Tp, K))
+
+
+def test_elementwise_tails_and_unaligned():
+    """the four-element kernels with n % 4 != 0 and the special values; buffers offset by one element take the element kernels"""
+    g = np.random.default_rng(41); n = 4 * 70001 + 3; sp = specials32()
+    core, tp, gl = hip.Module('core'), hip.Module('prefill_tp'), G.Glue(DEV)
+    a = acts(g, (n + 1,), 3.0); b = acts(g, (n + 1,)); c = acts(g, (n + 1,))
+    a[: sp.size] = sp; a[-sp.size:] = sp; b[5: 5 + sp.size] = sp
+    mb = torch.from_numpy(b).bfloat16().to(DEV); lb = torch.from_numpy(c).bfloat16().to(DEV)
+    grid = ((n + 255) // 256,)
+    for off in (0, 1):
+        av, bv, cv = a[off: off + n], b[off: off + n], c[off: off + n]
+        ad, bd = cu(a)[off: off + n], cu(b)[off: off + n]
+        y = cu(c)[off: off + n]
+        gl.add_sum(ad, bd, y, n)
+        assert same_but_nan(y, oracle.pf_add_sum(av, bv, cv))
+        out = torch.zeros(n + 1, device=DEV)[off: off + n]
+        tp.pf_swiglu(grid, (256,), ad, bd, out, L(n))
+        assert same_but_nan(out, oracle.pf_swiglu(av, bv))
+        core.residual3(grid, (256,), ad, mb[off: off + n], lb[off: off + n], out, ctypes.c_int64(n))
+        assert same_but_nan(out, oracle.residual3(av, bits(mb)[off: off + n], bits(lb)[off: off + n]))
+        cb = bfz(n + 1)[off: off + n]
+        core.cast_bf16(grid, (256,), ad, cb, ctypes.c_int64(n))
+        assert same(cb, oracle.cast_bf16(av))
+
+
+@pytest.mark.parametrize('rows,d', [(1000, 512), (600, 1024), (400, 3584), (333, 4096), (300, 704), (20, 896)])
+def test_rmsnorm_f32_row_lengths(rows, d):
+    """the warp-per-row path (multiples of 128 with enough rows) and the block-per-row path give the oracle's bits"""
+    g = np.random.default_rng(d); x = acts(g, (rows, d), 2.0); w = (g.random(d) + 0.5).astype(np.float32)
+    out = torch.zeros(rows, d, device=DEV)
+    hip.Module('core').rmsnorm_f32((rows,), (256,), cu(x), cu(w), out, I(d), F(1e-5))
+    assert same(out, oracle.rmsnorm_f32(x, w, 1e-5))
+
+
+def test_embedding_f32_and_qk_nr_other_paths():
+    g = np.random.default_rng(42); core = hip.Module('core')
+    for V, d, T in ((500, 896, 3000), (64, 30, 100)):
+        emb = acts(g, (V, d)); tok = g.integers(0, V, T).astype(np.int32); eo = torch.zeros(T, d, device=DEV)
+        core.embedding_f32((T,), (256,), cu(tok), cu(emb), eo, I(d))
+        assert same(eo, emb[tok])
+    for rows, heads, D, nrot, stride in ((300, 16, 256, 64, 256), (50, 5, 384, 384, 400), (9, 2, 130, 64, 131), (64, 8, 64, 32, 64), (33, 4, 512, 512, 512)):
+        x = acts(g, (rows * heads, stride), 1.5); w = (g.random(D) + 0.5).astype(np.float32)
+        ts = float(np.float32(np.float32(1e6) ** np.float32(-2.0 / nrot))); pos0 = 70000
+        out = torch.zeros(rows * heads, D, device=DEV)
+        hip.Module('prefill_attn').pf_qk_nr((rows * heads,), (256,), cu(x), I(stride), I(heads), cu(w), I(D), I(nrot), F(ts), F(1e-6), I(pos0), out)
+        assert same(out, oracle.pf_qk_nr(x, stride, heads, w, D, nrot, ts, 1e-6, pos0, rows * heads)), (rows, heads, D, nrot)
+
+
 @pytest.mark.parametrize('layout', ['D4', 'DS4'])
 @pytest.mark.parametrize('rows,K', [(1, 128), (37, 768), (150, 2560), (9, 300)])
 def test_mmq_q8_1(layout, rows, K):
