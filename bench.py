@@ -288,7 +288,13 @@ def single_op_lines(torch, dev, peak, only=()):
     tq6 = torch.randint(0, 256, (vocab, nblk, 210), device=dev, dtype=torch.uint8, generator=g)
     tq6[:, :, 208:210] = (torch.randn(vocab, nblk, 1, device=dev, generator=g) * 1e-3).half().view(torch.uint8).view(vocab, nblk, 2)
     line('emb_rows_q6k_16384x2048', nt * (4 + nblk * 210 + nblk * 1024), timed(lambda i: O.emb_q6k(tq6.view(-1), nblk * 210, vocab, tk, xo[i], nt, nblk * 256), rot=2), nt, 'rows_per_s')
-    del tab, raw, xo, tq6
+    ti2 = torch.randint(0, 256, (vocab, nblk, 82), device=dev, dtype=torch.uint8, generator=g)
+    ti2[:, :, 0:2] = (torch.randn(vocab, nblk, 1, device=dev, generator=g) * 1e-2).half().view(torch.uint8).view(vocab, nblk, 2)
+    CU.set_iq2s_grid(np.array([8, 25, 43], np.uint8)[np.random.default_rng(5).integers(0, 3, (1024, 8))])     # a stand-in grid: the timing does not depend on its entries
+    from caminus_b200.prefill import q35own
+    OT = q35own.Ops(dev, module=q35own.MODULE_TCAP)
+    line('emb_rows_iq2s_16384x2048', nt * (4 + nblk * 82 + nblk * 1024), timed(lambda i: OT.emb_iq2s(ti2.view(-1), nblk * 82, vocab, tk, xo[i], nt, nblk * 256), rot=2), nt, 'rows_per_s')
+    del tab, raw, xo, tq6, ti2
     from caminus_b200 import lib as LB
     Rq, Kq8 = 32768, 2560
     xq = rnd(Rq, Kq8, scale=3.0); wq8 = 0.5 + torch.rand(1, Kq8, device=dev, generator=g); yq8 = torch.empty(Rq, Kq8, device=dev)

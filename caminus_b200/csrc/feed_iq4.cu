@@ -143,6 +143,59 @@ __global__ void __launch_bounds__(256) emb_rows_q6k_kernel(const uint8_t * __res
     }
 }
 
+// ---- IQ2_S rows: q35t_emb_iq2s (kernels/q35_prefill_tcap.hip:94-113) = q35t_op_emb (kernels/k3_q35t_ops.h:147-175) --------------------
+// 82-byte blocks of 256 values: fp16 d | qs[32] | signs[32] | qh[8] | scales[8]. A thread decodes one group of 8 values (one 10-bit grid
+// index, one byte of signs): five 16-bit loads in, two 16-byte stores out. The grid (1024 entries of eight 2-bit magnitude codes, packed
+// two to a word as the reference's kernels hold it) is GGUF's format constant; the caller supplies it and each block stages it once.
+constexpr int IQ2S_ROWS = 4;      // token rows a block decodes together: a thread's loads of the four rows are issued before the first decode
+__global__ void __launch_bounds__(256) emb_rows_iq2s_kernel(const uint8_t * __restrict__ W, int rb, int vocab, const int * __restrict__ toks, float * __restrict__ x,
+                                                            int n, int N, const uint32_t * __restrict__ grid) {
+    __shared__ uint32_t gs[512];
+    for (int i = threadIdx.x; i < 512; i += 256) gs[i] = __ldg(grid + i);
+    __syncthreads();
+    const int units = N >> 3;
+    for (int p0 = blockIdx.x * IQ2S_ROWS; p0 < n; p0 += gridDim.x * IQ2S_ROWS) {
+        const uint8_t * row[IQ2S_ROWS];
+#pragma unroll
+        for (int r = 0; r < IQ2S_ROWS; r++) {
+            int t = __ldg(toks + (p0 + r < n ? p0 + r : n - 1)); t = t < 0 ? 0 : t >= vocab ? vocab - 1 : t;
+            row[r] = W + (size_t)t * rb;
+        }
+        for (int q = threadIdx.x; q < units; q += 256) {
+            const int j8 = q & 31, ib = j8 >> 2, g = j8 & 3;
+            uint32_t raw[IQ2S_ROWS][5];
+#pragma unroll
+            for (int r = 0; r < IQ2S_ROWS; r++) {
+                const uint16_t * b16 = reinterpret_cast<const uint16_t *>(row[r] + (size_t)(q >> 5) * 82);
+                raw[r][0] = __ldg(b16); raw[r][1] = __ldg(b16 + 1 + (j8 >> 1)); raw[r][2] = __ldg(b16 + 33 + (ib >> 1));
+                raw[r][3] = __ldg(b16 + 37 + (ib >> 1)); raw[r][4] = __ldg(b16 + 17 + (j8 >> 1));
+            }
+#pragma unroll
+            for (int r = 0; r < IQ2S_ROWS; r++) {
+                if (p0 + r >= n) break;
+                const float d = __half2float(__ushort_as_half((unsigned short)raw[r][0]));
+                const uint32_t lo = (raw[r][1] >> (8 * (j8 & 1))) & 0xffu;                 // qs[j8]
+                const uint32_t qh = (raw[r][2] >> (8 * (ib & 1))) & 0xffu;                 // qh[ib]
+                const uint32_t sb = (raw[r][3] >> (8 * (ib & 1))) & 0xffu;                 // scales[ib]
+                const uint32_t sg = (raw[r][4] >> (8 * (j8 & 1))) & 0xffu;                 // signs[j8]
+                const uint32_t idx = lo | (((qh >> (2 * g)) & 3u) << 8);
+                const uint32_t codes = (gs[idx >> 1] >> (16 * (idx & 1u))) & 0xffffu;
+                const float db = fmul(fmul(d, fadd(0.5f, (float)((sb >> (4 * ((j8 >> 1) & 1))) & 15u))), 0.25f);
+                float v[8];
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const uint32_t c = (codes >> (2 * k)) & 3u;
+                    const float m = fmul(db, c == 0 ? 8.0f : c == 1 ? 25.0f : 43.0f);
+                    v[k] = ((sg >> k) & 1u) ? -m : m;
+                }
+                float * o = x + (size_t)(p0 + r) * N + 8 * q;
+                __stcs(reinterpret_cast<float4 *>(o), make_float4(v[0], v[1], v[2], v[3]));
+                __stcs(reinterpret_cast<float4 *>(o + 4), make_float4(v[4], v[5], v[6], v[7]));
+            }
+        }
+    }
+}
+
 }   // namespace
 
 // embd_rows_iq4xs / ple_rows_iq4nl: kernels/prefill_feed.hip:40-41, 24-25 (one thread per output float there)
@@ -175,5 +228,16 @@ extern "C" int cam_emb_rows_q6k(int n, const void * W, int rb, int vocab, const 
     if ((reinterpret_cast<uintptr_t>(W) & 1u) || (rb & 1) || !cam_aligned16(x)) return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
     emb_rows_q6k_kernel<<<cam_resident_grid(emb_rows_q6k_kernel, 256, 0, n), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)W, rb, vocab, toks, x, n, N);
+    return (int)cudaGetLastError();
+}
+
+// q35t_emb_iq2s: x [n][N] fp32 = the IQ2_S rows toks[i] of a table (vocab rows of rb >= N / 256 * 82 bytes), ids clamped to the vocabulary:
+// kernels/q35_prefill_tcap.hip:94-113 (n = the reference's grid.x). grid: 512 words on the device, the packed IQ2_S grid of the reference's
+// kernels/iq2s_grid.h (a constant of its code object; here the caller's). N a multiple of 256, W and rb 2-byte aligned, x 16-byte aligned.
+extern "C" int q35t_emb_iq2s(int n, const void * W, int rb, int vocab, const int * toks, float * x, int N, const unsigned int * grid, void * stream) {
+    if (n < 0 || vocab < 1 || N < 256 || (N & 255) || rb < N / 256 * 82 || !W || !toks || !x || !grid) return CAM_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(W) & 1u) || (rb & 1) || !cam_aligned16(x) || (reinterpret_cast<uintptr_t>(grid) & 3u)) return CAM_ERR_ALIGN;
+    if (n == 0) return CAM_OK;
+    emb_rows_iq2s_kernel<<<cam_resident_grid(emb_rows_iq2s_kernel, 256, 0, (n + IQ2S_ROWS - 1) / IQ2S_ROWS), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)W, rb, vocab, toks, x, n, N, grid);
     return (int)cudaGetLastError();
 }

@@ -242,22 +242,33 @@ __global__ void __launch_bounds__(256) ew_vec_kernel(const void * __restrict__ a
         if (OP == EW_CAST_BF16) ((uint16_t *)y)[i] = bf16_nan(__ldg((const float *)a + i));
     }
 }
-// bf16(silu(g)) without the exact statements' two divisions and polynomial where that provably gives the same 16 bits: the
+// bf16(silu(g)) for N values without the exact statements' two divisions and polynomial where that provably gives the same bits: the
 // special-function evaluation s^ = g rcp(1 + ex2(-g log2 e)) is within 1.35e-6 |s| of cam_silu(g) for g >= -8 and 3e-38 <= |g| < 3e38
 // (the analysis at the fused SwiGLU + Q8_1 kernel, csrc/swiglu_q8.cu, without its last product). If s^ (1 - 1.55e-6) and s^ (1 + 1.55e-6) round to the same
-// bf16, no rounding boundary and no tie lies in the interval that holds cam_silu(g), and that bf16 is its rounding. Anything
-// else (1 value in about 1400, NaN and infinities among them) evaluates the exact statements. g = +-0 gives +-0 both ways.
-// NANQ: the NaN rule of the rounding (see bf16_soft).
-template <bool NANQ> CAM_DEV uint32_t silu_bf16_bits(float g) {
-    const float e = ex2_approx(fmul(g, -0x1.715476p+0f));
-    const float s = fmul(g, rcp_approx(fadd(1.0f, e)));
-    uint32_t r;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(fmul(s, 0x1.00001ap+0f)), "f"(fmul(s, 0x1.ffffccp-1f)));
-    const float ag = fabsf(g);
-    const bool proven = (r >> 16) == (r & 0xffffu) && g >= -8.0f && ag < 3.0e38f && (ag >= 3.0e-38f || g == 0.0f);
-    if (!proven) r = bf16_soft<NANQ>(cam_silu(g));
-    return r & 0xffffu;
+// bf16, no rounding boundary and no tie lies in the interval that holds cam_silu(g), and that bf16 is its rounding. The conditions are
+// ranges are gathered over the N values (minimum, largest and smallest magnitude) and tested once: an item with a value outside the
+// range, a zero or an infinity evaluates the exact statements for all N, a pair with an interval that holds a boundary (1 value in
+// about 1400) for its two. A NaN gate passes the gathered tests (minimum and maximum skip it) and gives the conversion's NaN, 0x7fff:
+// the callers' NaN test of the result sends such an item to the exact statements too. out[k] = values 2 k (low half), 2 k + 1.
+// Returns the pairs to redo with the exact statements, bit k for out[k] (0: none): a pair whose two roundings differ, every pair
+// when a range test fails. (A warp runs the redo when one of its lanes asks: per pair that is 1 step in 22, per item it was 1 in 6.)
+template <int N> CAM_DEV uint32_t silu_bf16_fast(const float (&g)[N], uint32_t (&out)[N / 2]) {
+    float gmin = g[0], amax = fabsf(g[0]), amin = fabsf(g[0]);
+    uint32_t redo = 0;
+#pragma unroll
+    for (int k = 0; k < N; k += 2) {
+        const float s0 = fmul(g[k], rcp_approx(fadd(1.0f, ex2_approx(fmul(g[k], -0x1.715476p+0f)))));
+        const float s1 = fmul(g[k + 1], rcp_approx(fadd(1.0f, ex2_approx(fmul(g[k + 1], -0x1.715476p+0f)))));
+        uint32_t lo;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(out[k >> 1]) : "f"(fmul(s1, 0x1.00001ap+0f)), "f"(fmul(s0, 0x1.00001ap+0f)));
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(fmul(s1, 0x1.ffffccp-1f)), "f"(fmul(s0, 0x1.ffffccp-1f)));
+        if (out[k >> 1] != lo) redo |= 1u << (k >> 1);
+        if (k) { gmin = fminf(gmin, g[k]); amax = fmaxf(amax, fabsf(g[k])); amin = fminf(amin, fabsf(g[k])); }
+        gmin = fminf(gmin, g[k + 1]); amax = fmaxf(amax, fabsf(g[k + 1])); amin = fminf(amin, fabsf(g[k + 1]));
+    }
+    return (gmin >= -8.0f && amax < 3.0e38f && amin >= 3.0e-38f) ? redo : (1u << (N / 2)) - 1u;
 }
+CAM_DEV bool bf16_pair_has_nan(uint32_t w) { return (w & 0x7fffu) > 0x7f80u || (w & 0x7fff0000u) > 0x7f800000u; }
 
 // pf_silu_bf16 / pf_to_bf16 over items of four elements: item i is row i / K4, columns 4 (i % K4) .. (K4 = K / 4; the division only when
 // the rows are strided); items of the padding rows store zeros
@@ -281,8 +292,15 @@ __global__ void __launch_bounds__(256) to_bf16_vec_kernel(const float * __restri
             if (i >= all) continue;
             uint2 o = make_uint2(0u, 0u);
             if (i < live) {
-                if (SILU) o = make_uint2(silu_bf16_bits<true>(ffma(rs, v[k].x, 0.0f)) | (silu_bf16_bits<true>(ffma(rs, v[k].y, 0.0f)) << 16),
-                                         silu_bf16_bits<true>(ffma(rs, v[k].z, 0.0f)) | (silu_bf16_bits<true>(ffma(rs, v[k].w, 0.0f)) << 16));
+                if (SILU) {
+                    const float gv[4] = {ffma(rs, v[k].x, 0.0f), ffma(rs, v[k].y, 0.0f), ffma(rs, v[k].z, 0.0f), ffma(rs, v[k].w, 0.0f)};
+                    uint32_t w2[2];
+                    if (silu_bf16_fast<4>(gv, w2) || bf16_pair_has_nan(w2[0]) || bf16_pair_has_nan(w2[1])) {      // (one redo for the item's four: measured faster than one per pair here)
+                        w2[0] = bf16_soft<true>(cam_silu(gv[0])) | (bf16_soft<true>(cam_silu(gv[1])) << 16);
+                        w2[1] = bf16_soft<true>(cam_silu(gv[2])) | (bf16_soft<true>(cam_silu(gv[3])) << 16);
+                    }
+                    o = make_uint2(w2[0], w2[1]);
+                }
                 else o = make_uint2(bf16x2<false>(v[k].x, v[k].y), bf16x2<false>(v[k].z, v[k].w));
             }
             __stcs(reinterpret_cast<uint2 *>(y) + i, o);
@@ -297,12 +315,20 @@ __global__ void __launch_bounds__(256) silu_mul_bf16_vec_kernel(const uint16_t *
         const unsigned r = i / H8, c8 = i - r * H8;
         const uint4 gw = ldg128(gu + ((size_t)r * 2 * H8 + c8) * 8), uw = ldg128(gu + ((size_t)r * 2 * H8 + H8 + c8) * 8);
         const uint32_t gs[4] = {gw.x, gw.y, gw.z, gw.w}, us[4] = {uw.x, uw.y, uw.z, uw.w};
-        uint32_t o[4];
+        float gv[8];
+#pragma unroll
+        for (int k = 0; k < 4; k++) { const float2 g = bf16x2_f(gs[k]); gv[2 * k] = g.x; gv[2 * k + 1] = g.y; }
+        uint32_t sw[4], o[4];
+        const uint32_t redo = silu_bf16_fast<8>(gv, sw);
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-            const float2 g = bf16x2_f(gs[k]), u = bf16x2_f(us[k]);
-            const float s0 = __uint_as_float(silu_bf16_bits<true>(g.x) << 16), s1 = __uint_as_float(silu_bf16_bits<true>(g.y) << 16);
-            o[k] = bf16x2<true>(fmul(s0, u.x), fmul(s1, u.y));
+            const float2 sv = bf16x2_f(sw[k]), u = bf16x2_f(us[k]);
+            const float p0 = fmul(sv.x, u.x), p1 = fmul(sv.y, u.y);
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[k]) : "f"(p1), "f"(p0));
+            if (((redo >> k) & 1u) || p0 != p0 || p1 != p1) {            // the exact statements for the pair (a NaN: f2bf's 0x7fc0)
+                const float s0 = __uint_as_float(bf16_soft<true>(cam_silu(gv[2 * k])) << 16), s1 = __uint_as_float(bf16_soft<true>(cam_silu(gv[2 * k + 1])) << 16);
+                o[k] = bf16_soft<true>(fmul(s0, u.x)) | (bf16_soft<true>(fmul(s1, u.y)) << 16);
+            }
         }
         st128_stream(act + (size_t)i * 8, make_uint4(o[0], o[1], o[2], o[3]));
     }

@@ -43,6 +43,8 @@ MODULES = {
     'q3m_prefill_kvq8': {'q3p_qk_rope_q8': ('q3p_qk_rope_q8', 1)},
     'q3m_prefill_kvq8_yarn': {'q3p_qk_rope_q8': ('q3p_qk_rope_q8_yarn', 1)},
     'q35_prefill': {'q35p_add_rms16': ('q35p_add_rms16', 1)},
+    'q35_prefill_tcap': {'q35p_add_rms16': ('q35p_add_rms16', 1), 'q35t_emb_iq2s': ('q35t_emb_iq2s', 1, (lambda: _iq2s_grid(),))},
+    'q35_prefill_gsq': {'q35p_add_rms16': ('q35p_add_rms16', 1), 'q35t_emb_iq2s': ('q35t_emb_iq2s', 1, (lambda: _iq2s_grid(),))},
     'k3_gguf': {'gg_quantize_q8_1': ('gg_quantize_q8_1', 0), 'gg_silu_mul': ('gg_silu_mul', 0)},
     'k3_gguf_gsq': {'gg_quantize_q8_1': ('gg_quantize_q8_1', 0), 'gg_silu_mul': ('gg_silu_mul', 0)},
 }
@@ -50,6 +52,37 @@ MODULES = {
 
 def check(err):
     _lib.check(err)
+
+
+# GGUF's IQ2_S grid, a constant of the reference's q35_prefill_tcap / _gsq code objects (kernels/iq2s_grid.h, generated from
+# python/caminus/iq_tables.py:747-768). This library does not carry the table: the caller hands it over once per device.
+_IQ2S = {}
+
+
+def set_iq2s_grid(grid, device=None):
+    """grid: the reference's iq_tables.GRID_IQ2_S (uint8 [1024, 8], magnitudes 8 / 25 / 43) or its packed form (uint32 / int32 [512]:
+    2-bit codes 0 / 1 / 2 at bits 2 k, entry 2 w in word w's low half), as a numpy array or tensor; kept on `device` (default: current)"""
+    import numpy as np
+    import torch
+    g = grid.detach().cpu().numpy() if torch.is_tensor(grid) else np.asarray(grid)
+    if g.size == 8192:
+        m = g.astype(np.uint8).reshape(1024, 8)
+        if not np.isin(m, (8, 25, 43)).all(): raise ValueError('set_iq2s_grid: magnitudes other than 8 / 25 / 43')
+        code = np.where(m == 8, 0, np.where(m == 25, 1, 2)).astype(np.uint32)
+        e = (code << (2 * np.arange(8, dtype=np.uint32))).sum(axis=1).astype(np.uint32)
+        g = e[0::2] | (e[1::2] << 16)
+    elif g.size != 512 or g.dtype.itemsize != 4:
+        raise ValueError(f'set_iq2s_grid: {g.size} values of {g.dtype}; expected uint8 [1024, 8] or 512 packed words')
+    dev = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    _IQ2S[idx] = torch.from_numpy(np.ascontiguousarray(g).view(np.int32).reshape(512).copy()).to(torch.device('cuda', idx))
+
+
+def _iq2s_grid():
+    import torch
+    t = _IQ2S.get(torch.cuda.current_device())
+    if t is None: raise RuntimeError('caminus_b200: q35t_emb_iq2s needs the IQ2_S grid: call caminus_b200.device.cuda.set_iq2s_grid(iq_tables.GRID_IQ2_S) once per device')
+    return ctypes.c_void_p(t.data_ptr())
 
 
 _torch = None
@@ -87,7 +120,8 @@ class Kernel:
             nh, nkv = int(getattr(vals[2], 'value', vals[2])), int(getattr(vals[3], 'value', vals[3]))
             if grid[1] != nh + nkv: raise ValueError(f'{self.name}: grid.y {grid[1]} is not nh + nkv = {nh + nkv}')
         lead = [ctypes.c_int(int(grid[i])) for i in range(self.ngrid)]
-        _lib.check(self.fn(*lead, *vals, *self.tail, ctypes.c_void_p(s)), self.name)
+        tail = [t() if callable(t) else t for t in self.tail]      # (a callable: a per-device constant looked up at the launch)
+        _lib.check(self.fn(*lead, *vals, *tail, ctypes.c_void_p(s)), self.name)
         if r is not None: r.launched(self, grid, block, vals, shmem, s)
 
 

@@ -52,6 +52,7 @@ SIGNATURES = {
     'embd_rows_iq4xs': [P, P, I, I, I, P, P, P],
     'ple_rows_iq4nl': [P, P, I, I, I, P, P, P],
     'cam_emb_rows_q6k': [I, P, I, I, P, P, I, P],
+    'q35t_emb_iq2s': [I, P, I, I, P, P, I, P, P],
     'q3p_router': [I, P, P, I, I, P, P],
     'q3p_topk': [I, P, I, I, F, P, P, P, P],
     'q3p_group': [P, I, I, I, P, P, P, P, P, P],

@@ -145,6 +145,11 @@ int ple_rows_iq4nl(const void * raw, const int * inv, int nuniq, int nrows, int 
 /* cam_emb_rows_q6k: the Q6_K row gather (210-byte blocks; the reference decodes this format on the host only:
  *   python/caminus/own_dequant.py:40-53, whose floats these are). x [n][N] = rows toks[i] (clamped to [0, vocab)) of a table of rb-byte rows. */
 int cam_emb_rows_q6k(int n, const void * W, int rb, int vocab, const int * toks, float * x, int N, void * stream);
+/* x [n][N] fp32 = the IQ2_S rows toks[i] of a table (82-byte blocks of 256; vocab rows of rb bytes), ids clamped to the vocabulary.
+ * grid: 512 words on the device, GGUF's IQ2_S grid packed as the reference's kernels hold it (kernels/iq2s_grid.h: entry e = eight 2-bit
+ * magnitude codes, entries 2 w and 2 w + 1 in word w); a constant of the reference's code object, the caller's argument here.
+ * Replaces q35t_emb_iq2s, kernels/q35_prefill_tcap.hip:94-113 (= q35t_op_emb, kernels/k3_q35t_ops.h:147-175); n = grid.x. */
+int q35t_emb_iq2s(int n, const void * W, int rb, int vocab, const int * toks, float * x, int N, const unsigned int * grid, void * stream);
 
 /* ---- the router glue of the Qwen3-MoE prefill: kernels/q3m_prefill.hip:417-513; wrappers python/caminus/prefill/q3m_ops.py:94-104 ----
  * q3p_router: logits [n][E] = h [n][K] . Wr [E][K] in fp32 (n = grid.x; K a multiple of 128).

@@ -439,6 +439,21 @@ def ple_rows_iq4nl(raw, inv, nuniq, bpr):
     return out, int(err[0])
 
 
+def pack_iq2s_grid(mags):
+    """uint8 [1024, 8] magnitudes (8 / 25 / 43: the form of the reference's iq_tables.GRID_IQ2_S) -> uint32 [512], the packing of the
+    reference's kernels/iq2s_grid.h (python/caminus/iq_tables.py:747-768): 2-bit codes 0 / 1 / 2 at bits 2 k, entry 2 w in word w's low half"""
+    m = np.asarray(mags, np.uint8).reshape(1024, 8)
+    code = np.where(m == 8, 0, np.where(m == 25, 1, 2)).astype(np.uint32)
+    e = (code << (2 * np.arange(8, dtype=np.uint32))).sum(axis=1).astype(np.uint32)
+    return (e[0::2] | (e[1::2] << 16)).astype(np.uint32)
+
+
+def emb_rows_iq2s(W, rb, vocab, toks, N, grid):
+    W = _c(W, np.uint8).reshape(-1); toks = _c(toks, np.int32); grid = _c(grid, np.uint32); x = np.empty((toks.size, N), np.float32)
+    lib().orc_emb_rows_iq2s(_p(W), I(rb), I(vocab), _p(toks), _p(x), I(toks.size), I(N), _p(grid))
+    return x
+
+
 def emb_rows_q6k(W, rb, vocab, toks, N):
     W = _c(W, np.uint8).reshape(-1); toks = _c(toks, np.int32); x = np.empty((toks.size, N), np.float32)
     lib().orc_emb_rows_q6k(_p(W), I(rb), I(vocab), _p(toks), _p(x), I(toks.size), I(N))

@@ -857,3 +857,28 @@ void orc_emb_rows_q6k(const uint8_t * W, int rb, int vocab, const int32_t * toks
         }
     }
 }
+
+/* IQ2_S row gather: q35t_emb_iq2s (kernels/q35_prefill_tcap.hip:94-113) = q35t_op_emb (kernels/k3_q35t_ops.h:147-175), the floats of the host
+ * decoder python/caminus/own_dequant.py:128-137. 82-byte blocks of 256 = fp16 d | qs[32] | signs[32] | qh[8] | scales[8]; value j of a block:
+ * group j >> 3 has the 10-bit grid index qs[j >> 3] | ((qh[j >> 5] >> 2 ((j >> 3) & 3)) & 3) << 8, its magnitude k = j & 7 is the 2-bit code at
+ * bits 2 k of the grid's 16-bit entry (0: 8, 1: 25, else 43); y = +-(((d (0.5 + s)) 0.25) mag) with s the nibble j >> 4 of scales and the sign
+ * bit j & 7 of signs[j >> 3]. grid: the 1024 entries packed two to a 32-bit word (entry 2 w in word w's low half), GGUF's format constant,
+ * which the caller supplies. Token ids are clamped to the vocabulary. */
+void orc_emb_rows_iq2s(const uint8_t * W, int rb, int vocab, const int32_t * toks, float * x, int n, int N, const uint32_t * grid) {
+    for (int p = 0; p < n; p++) {
+        int t = toks[p]; t = t < 0 ? 0 : t >= vocab ? vocab - 1 : t;
+        const uint8_t * row = W + (size_t)t * rb;
+        for (int i = 0; i < N; i++) {
+            const uint8_t * b = row + (size_t)(i >> 8) * 82;
+            const int j = i & 255, ib = j >> 5, g = (j >> 3) & 3, k = j & 7;
+            const float d = h2f((uint16_t)(b[0] | (b[1] << 8)));
+            const uint32_t idx = b[2 + 4 * ib + g] | ((((uint32_t)b[66 + ib] >> (2 * g)) & 3u) << 8);
+            const uint32_t code = ((grid[idx >> 1] >> (16 * (idx & 1u))) >> (2 * k)) & 3u;
+            const float mag = code == 0 ? 8.0f : code == 1 ? 25.0f : 43.0f;
+            const float sc = (float)((b[74 + ib] >> (4 * ((j >> 4) & 1))) & 15);
+            const float db = (d * (0.5f + sc)) * 0.25f;
+            const float v = db * mag;
+            x[(size_t)p * N + i] = ((b[34 + (j >> 3)] >> k) & 1) ? -v : v;
+        }
+    }
+}

@@ -172,7 +172,34 @@ def make_q6k():
     np.savez_compressed(os.path.join(OUT, 'q6k_rows.npz'), T=T, rows=rows)
 
 
+def make_iq2s():
+    """IQ2_S rows: own_dequant.iq2_s (python/caminus/own_dequant.py:128-137), the decoder the reference gates q35t_emb_iq2s against.
+    The 1024-entry grid is ggml's data and is not carried by this repository: for the stored fixture the decoder runs over a seeded
+    stand-in grid (magnitudes drawn from 8 / 25 / 43, as the real entries are), which pins every statement of the decoder (index
+    assembly, scales, signs, the order of the float32 products). With the checkout present this function also checks, without storing
+    anything, that the oracle over the reference's real grid equals the decoder and gguf-py on the same bytes."""
+    from caminus import iq_tables
+    sys.path.insert(0, os.path.join(OUT, '..', '..'))
+    import oracle
+    g = np.random.default_rng(20261126); vocab, nblk = 23, 3
+    T = g.integers(0, 256, (vocab, nblk, 82), dtype=np.uint8)
+    T[:, :, 0:2] = (g.standard_normal((vocab, nblk, 1)) * 1e-2).astype(np.float16).view(np.uint8).reshape(vocab, nblk, 2)
+    T[3, 0, 0:2] = 0; T[4, 1, 0:2] = np.array([0x8000], np.uint16).view(np.uint8); T[5, 2, 0:2] = np.array([0x7bff], np.uint16).view(np.uint8)
+    real = iq_tables.GRID_IQ2_S
+    toks = np.arange(vocab, dtype=np.int32)
+    rows_real = np.stack([own_dequant.iq2_s(T[t].reshape(-1)) for t in range(vocab)]).astype(np.float32)
+    assert np.array_equal(rows_real.view(np.uint32), np.stack([gq.dequantize(T[t].reshape(1, -1), QT.IQ2_S).reshape(-1) for t in range(vocab)]).astype(np.float32).view(np.uint32))
+    assert np.array_equal(rows_real.view(np.uint32), oracle.emb_rows_iq2s(T, nblk * 82, vocab, toks, nblk * 256, oracle.pack_iq2s_grid(real)).view(np.uint32))
+    grid = np.array([8, 25, 43], np.uint8)[g.integers(0, 3, (1024, 8))]
+    iq_tables.GRID_IQ2_S = grid
+    try:
+        rows = np.stack([own_dequant.iq2_s(T[t].reshape(-1)) for t in range(vocab)]).astype(np.float32)
+    finally:
+        iq_tables.GRID_IQ2_S = real
+    np.savez_compressed(os.path.join(OUT, 'iq2s_rows.npz'), T=T, rows=rows, grid=grid)
+
+
 if __name__ == '__main__':
-    make_q6k(); make_iq4(); make_q4k(); make_q8(); make_swiglu(); make_rms(); make_rope(); make_q8_kv()
+    make_iq2s(); make_q6k(); make_iq4(); make_q4k(); make_q8(); make_swiglu(); make_rms(); make_rope(); make_q8_kv()
     for f in sorted(os.listdir(OUT)):
         if f.endswith('.npz'): print(f, os.path.getsize(os.path.join(OUT, f)), 'bytes')

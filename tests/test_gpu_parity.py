@@ -562,3 +562,30 @@ def test_q6k_rows(golden):
     O.emb_q6k(cu(W.reshape(-1)), nblk2 * 210, vocab2, cu(toks2), x2, 1000, nblk2 * 256)
     assert same(x2, oracle.emb_rows_q6k(W, nblk2 * 210, vocab2, toks2, nblk2 * 256))
     with pytest.raises(ValueError): O.emb_q6k(cu(W.reshape(-1)), 100, vocab2, cu(toks2), x2, 1000, nblk2 * 256)
+
+
+def test_iq2s_rows(golden):
+    """q35t_emb_iq2s: the fixture's rows (the reference's host decoder over the fixture's grid) bit for bit, clamped ids; a larger random
+    table against the oracle; the grid handed over in either form; refused without one"""
+    from caminus_b200.prefill import q35own
+    from caminus_b200.device import cuda as hip
+    f = golden('iq2s_rows'); T = f['T']; vocab, nblk = T.shape[:2]; N = nblk * 256
+    O = q35own.Ops(DEV, module=q35own.MODULE_TCAP)
+    toks = np.concatenate([[0, 22, -4, 77], np.random.default_rng(3).integers(0, vocab, 200)]).astype(np.int32)
+    x = torch.zeros(len(toks), N, device=DEV)
+    hip._IQ2S.clear()
+    with pytest.raises(RuntimeError): O.emb_iq2s(cu(T.reshape(-1)), nblk * 82, vocab, cu(toks), x, len(toks), N)
+    hip.set_iq2s_grid(f['grid'])                                        # the magnitudes, [1024, 8]
+    O.emb_iq2s(cu(T.reshape(-1)), nblk * 82, vocab, cu(toks), x, len(toks), N)
+    assert same(x, f['rows'][np.clip(toks, 0, vocab - 1)])
+    g_ = np.random.default_rng(9); vocab2, nblk2 = 300, 20
+    grid2 = np.array([8, 25, 43], np.uint8)[g_.integers(0, 3, (1024, 8))]
+    hip.set_iq2s_grid(oracle.pack_iq2s_grid(grid2))                     # the packed words
+    W = g_.integers(0, 256, (vocab2, nblk2, 82), dtype=np.uint8)
+    W[:, :, 0:2] = (g_.standard_normal((vocab2, nblk2, 1)) * 1e-2).astype(np.float16).view(np.uint8).reshape(vocab2, nblk2, 2)
+    toks2 = g_.integers(-3, vocab2 + 3, 1000).astype(np.int32); x2 = torch.zeros(1000, nblk2 * 256, device=DEV)
+    O.emb_iq2s(cu(W.reshape(-1)), nblk2 * 82, vocab2, cu(toks2), x2, 1000, nblk2 * 256)
+    assert same(x2, oracle.emb_rows_iq2s(W, nblk2 * 82, vocab2, toks2, nblk2 * 256, oracle.pack_iq2s_grid(grid2)))
+    with pytest.raises(ValueError): O.emb_iq2s(cu(W.reshape(-1)), 100, vocab2, cu(toks2), x2, 1000, nblk2 * 256)
+    with pytest.raises(ValueError): q35own.Ops(DEV).emb_iq2s(cu(W.reshape(-1)), nblk2 * 82, vocab2, cu(toks2), x2, 1000, nblk2 * 256)
+    with pytest.raises(ValueError): hip.set_iq2s_grid(np.zeros((1024, 8), np.uint8))

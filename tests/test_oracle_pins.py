@@ -192,3 +192,12 @@ def test_q6k_rows_bitwise(golden):
     toks = np.array([0, 7, 18, -2, 50, 3], np.int32)
     x = oracle.emb_rows_q6k(T, nblk * 210, vocab, toks, nblk * 256)
     assert np.array_equal(x.view(np.uint32), f['rows'][np.clip(toks, 0, vocab - 1)].view(np.uint32))
+
+
+def test_iq2s_rows_bitwise(golden):
+    """the IQ2_S decoder of the oracle == the reference's own_dequant.iq2_s on the fixture (decoded over the fixture's stand-in grid:
+    the real grid is ggml's data and not carried here; the generator also checks the real grid, unstored), clamped ids included"""
+    f = golden('iq2s_rows'); T = f['T']; vocab, nblk = T.shape[:2]
+    toks = np.array([0, 7, 22, -2, 50, 3], np.int32)
+    x = oracle.emb_rows_iq2s(T, nblk * 82, vocab, toks, nblk * 256, oracle.pack_iq2s_grid(f['grid']))
+    assert np.array_equal(x.view(np.uint32), f['rows'][np.clip(toks, 0, vocab - 1)].view(np.uint32))
