@@ -412,7 +412,7 @@ template <int NCH>
 __global__ void __launch_bounds__(NR_WARPS * 32) qk_nr_vec_kernel(const float * __restrict__ xin, int head_stride, int heads, const float * __restrict__ w, int D, int nrot,
                                                                   float theta_scale, float eps, int pos0, float * __restrict__ out, int rows) {
     __shared__ float pw[64 * NCH];
-    __shared__ float sn_s[NR_WARPS][64 * NCH], cs_s[NR_WARPS][64 * NCH];
+    __shared__ __align__(16) float sn_s[NR_WARPS][64 * NCH], cs_s[NR_WARPS][64 * NCH];
     __shared__ __align__(16) float nrm_s[NR_WARPS][128 * NCH];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, half = nrot >> 1;
     for (int j = tid; j < half; j += NR_WARPS * 32) pw[j] = cam_powi(theta_scale, j);
@@ -446,7 +446,7 @@ __global__ void __launch_bounds__(NR_WARPS * 32) qk_nr_vec_kernel(const float * 
                 a[q + 0] = ffma(xv[m].x, xv[m].x, a[q + 0]); a[q + 1] = ffma(xv[m].y, xv[m].y, a[q + 1]);
                 a[q + 2] = ffma(xv[m].z, xv[m].z, a[q + 2]); a[q + 3] = ffma(xv[m].w, xv[m].w, a[q + 3]);
             }
-            const float tot = ref_total_f32(a, lane);
+            const float tot = ref_total_f32_rs(a, lane);
             const float scale = cam_rsqrt(fadd(fdiv(tot, (float)D), eps));
 #pragma unroll
             for (int m = 0; m < NCH; m++) {
@@ -461,13 +461,24 @@ __global__ void __launch_bounds__(NR_WARPS * 32) qk_nr_vec_kernel(const float * 
                 const int e = 128 * m + 4 * lane;
                 if (e >= D) continue;
                 float o[4] = {xv[m].x, xv[m].y, xv[m].z, xv[m].w};
+                if (e + 3 < nrot && !(half & 3)) {       // the four elements rotate and lie on one side of the half: partners and tables by 16-byte reads
+                    const bool low = e < half;
+                    const int j = low ? e : e - half;
+                    const float4 x0 = *reinterpret_cast<const float4 *>(nrm + j), x1 = *reinterpret_cast<const float4 *>(nrm + j + half);
+                    const float4 sn = *reinterpret_cast<const float4 *>(sns + j), cs = *reinterpret_cast<const float4 *>(css + j);
+                    o[0] = low ? ffma(x0.x, cs.x, -fmul(x1.x, sn.x)) : ffma(x0.x, sn.x, fmul(x1.x, cs.x));
+                    o[1] = low ? ffma(x0.y, cs.y, -fmul(x1.y, sn.y)) : ffma(x0.y, sn.y, fmul(x1.y, cs.y));
+                    o[2] = low ? ffma(x0.z, cs.z, -fmul(x1.z, sn.z)) : ffma(x0.z, sn.z, fmul(x1.z, cs.z));
+                    o[3] = low ? ffma(x0.w, cs.w, -fmul(x1.w, sn.w)) : ffma(x0.w, sn.w, fmul(x1.w, cs.w));
+                } else if (e < nrot) {
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const int i = e + c;
-                    if (i >= nrot) continue;
-                    const int j = i < half ? i : i - half;
-                    const float x0 = nrm[j], x1 = nrm[j + half], sn = sns[j], cs = css[j];
-                    o[c] = i < half ? ffma(x0, cs, -fmul(x1, sn)) : ffma(x0, sn, fmul(x1, cs));
+                    for (int c = 0; c < 4; c++) {
+                        const int i = e + c;
+                        if (i >= nrot) continue;
+                        const int j = i < half ? i : i - half;
+                        const float x0 = nrm[j], x1 = nrm[j + half], sn = sns[j], cs = css[j];
+                        o[c] = i < half ? ffma(x0, cs, -fmul(x1, sn)) : ffma(x0, sn, fmul(x1, cs));
+                    }
                 }
                 __stcs(reinterpret_cast<float4 *>(y + 128 * m), make_float4(o[0], o[1], o[2], o[3]));
             }

@@ -222,7 +222,7 @@ def test_embedding_f32_and_qk_nr_other_paths():
         emb = acts(g, (V, d)); tok = g.integers(0, V, T).astype(np.int32); eo = torch.zeros(T, d, device=DEV)
         core.embedding_f32((T,), (256,), cu(tok), cu(emb), eo, I(d))
         assert same(eo, emb[tok])
-    for rows, heads, D, nrot, stride in ((300, 16, 256, 64, 256), (50, 5, 384, 384, 400), (9, 2, 130, 64, 131), (64, 8, 64, 32, 64), (33, 4, 512, 512, 512)):
+    for rows, heads, D, nrot, stride in ((300, 16, 256, 64, 256), (50, 5, 384, 384, 400), (9, 2, 130, 64, 131), (64, 8, 64, 32, 64), (33, 4, 512, 512, 512), (17, 3, 128, 20, 128), (21, 2, 256, 250, 260)):
         x = acts(g, (rows * heads, stride), 1.5); w = (g.random(D) + 0.5).astype(np.float32)
         ts = float(np.float32(np.float32(1e6) ** np.float32(-2.0 / nrot))); pos0 = 70000
         out = torch.zeros(rows * heads, D, device=DEV)
