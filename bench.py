@@ -193,7 +193,7 @@ def single_op_lines(torch, dev, peak, only=()):
 
     g = torch.Generator(device=dev); g.manual_seed(0)
     # config 1: add + RMSNorm fp32, hidden 2048: T = 1 (latency) and a T sweep
-    for T in (1, 4096, 65536):
+    for T in (1, 64, 4096, 65536):
         rot = 8 if T <= 4096 else 1
         xs = [torch.randn(T, 2048, device=dev, generator=g) for _ in range(rot)]; d = torch.randn(T, 2048, device=dev, generator=g)
         nw = 1 + 0.05 * torch.randn(2048, device=dev, generator=g); h = torch.empty(T, 2048, device=dev); h16 = torch.empty(T, 2048, dtype=torch.float16, device=dev)

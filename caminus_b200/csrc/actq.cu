@@ -89,9 +89,12 @@ struct SiluMulSrc {
         const uint16_t * r = gu + (size_t)row * ld;
         float g[4], u[4];
         bf4(__ldg(reinterpret_cast<const uint2 *>(r + k)), g); bf4(__ldg(reinterpret_cast<const uint2 *>(r + F + k)), u);
+        uint32_t w2[2];                       // bf16(silu(g)): the special-function value where its bits are proven, else the exact statements (silu_bf16_fast)
+        const uint32_t redo = silu_bf16_fast<4>(g, w2);
 #pragma unroll
-        for (int e = 0; e < 4; e++) v[e] = cam_silu(g[e]);
-        rbf4(v);
+        for (int p = 0; p < 2; p++)
+            if (((redo >> p) & 1u) || bf16_pair_has_nan(w2[p])) w2[p] = bf16_soft<true>(cam_silu(g[2 * p])) | (bf16_soft<true>(cam_silu(g[2 * p + 1])) << 16);
+        unpack4(make_uint2(w2[0], w2[1]), v);
 #pragma unroll
         for (int e = 0; e < 4; e++) v[e] = fmul(v[e], u[e]);
         rbf4(v);
@@ -103,7 +106,8 @@ struct RmsSrc {
     CAM_DEV float operator()(int row, int k) const { return fmul(fmul(__ldg(x + (size_t)row * d + k), rstd), __ldg(w + k)); }
 };
 
-template <typename Src>
+// VEC: the source is read four values at a time (get4; rows aligned for it)
+template <typename Src, bool VEC = false>
 CAM_DEV void actq_fwd_src(Src src, uint16_t * __restrict__ y, float * __restrict__ s_out, int K, float clip, int qmax, uint16_t * __restrict__ codes,
                           float * lds) {
     const int row = blockIdx.x, wave = threadIdx.x >> 5, lane = threadIdx.x & 31, nch = K / 128;
@@ -113,9 +117,14 @@ CAM_DEV void actq_fwd_src(Src src, uint16_t * __restrict__ y, float * __restrict
     for (int c = 0; c < AQ_MAXC; c++) {
         const int ch = wave + c * AQ_WAVES;
         if (ch < nch) {                                            // (uniform per warp)
+            if constexpr (VEC) {
+                src.get4(row, ch * 128 + lane * 4, u[c]);
+                if (!Src::kBf16) rbf4(u[c]);
+            } else {
 #pragma unroll
-            for (int e = 0; e < 4; e++) u[c][e] = src(row, ch * 128 + lane * 4 + e);
-            rbf4(u[c]);
+                for (int e = 0; e < 4; e++) u[c][e] = src(row, ch * 128 + lane * 4 + e);
+                rbf4(u[c]);
+            }
             fwht128(u[c], lane);
 #pragma unroll
             for (int e = 0; e < 4; e++) u[c][e] = fmul(u[c][e], 0.08837890625f);
@@ -156,10 +165,10 @@ CAM_DEV void actq_fwd_src(Src src, uint16_t * __restrict__ y, float * __restrict
     }
 }
 
-template <typename Src>
+template <typename Src, bool VEC = false>
 __global__ void __launch_bounds__(256) actq_kernel(Src src, uint16_t * y, float * s, int K, float clip, int qmax, uint16_t * codes) {
     __shared__ float lds[AQ_WAVES];
-    actq_fwd_src(src, y, s, K, clip, qmax, codes, lds);
+    actq_fwd_src<Src, VEC>(src, y, s, K, clip, qmax, codes, lds);
 }
 
 __global__ void __launch_bounds__(256) block_entry_kernel(const float * __restrict__ x, const float * __restrict__ nw, const uint16_t * __restrict__ wab, int nab,
@@ -352,15 +361,19 @@ bool misaligned8(const void * p) { return p && (reinterpret_cast<uintptr_t>(p) &
 extern "C" int actq_fwd_codes_bf16(int M, const void * x, void * y, float * s, void * codes, int K, float clip, int qmax, void * stream) {
     const int r = check_actq(M, K, qmax, x, s); if (r || M == 0) return r;
     if (misaligned8(y)) return CAM_ERR_ALIGN;
-    if (!launch_actq_rows(PlainBf16{(const uint16_t *)x, K}, !misaligned8(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST))
-        actq_kernel<<<M, 256, 0, CAM_ST>>>(PlainBf16{(const uint16_t *)x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
+    if (!launch_actq_rows(PlainBf16{(const uint16_t *)x, K}, !misaligned8(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST)) {
+        if (!misaligned8(x)) actq_kernel<PlainBf16, true><<<M, 256, 0, CAM_ST>>>(PlainBf16{(const uint16_t *)x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
+        else actq_kernel<<<M, 256, 0, CAM_ST>>>(PlainBf16{(const uint16_t *)x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
+    }
     return (int)cudaGetLastError();
 }
 extern "C" int actq_fwd_codes_f32(int M, const float * x, void * y, float * s, void * codes, int K, float clip, int qmax, void * stream) {
     const int r = check_actq(M, K, qmax, x, s); if (r || M == 0) return r;
     if (misaligned8(y)) return CAM_ERR_ALIGN;
-    if (!launch_actq_rows(PlainF32{x, K}, cam_aligned16(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST))
-        actq_kernel<<<M, 256, 0, CAM_ST>>>(PlainF32{x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
+    if (!launch_actq_rows(PlainF32{x, K}, cam_aligned16(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST)) {
+        if (cam_aligned16(x)) actq_kernel<PlainF32, true><<<M, 256, 0, CAM_ST>>>(PlainF32{x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
+        else actq_kernel<<<M, 256, 0, CAM_ST>>>(PlainF32{x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
+    }
     return (int)cudaGetLastError();
 }
 extern "C" int actq_fwd_bf16(int M, const void * x, void * y, float * s, int K, float clip, int qmax, void * stream) {
@@ -375,8 +388,11 @@ extern "C" int silu_mul_actq_fwd(int M, const void * gu, int ld, int F, void * y
     if (ld < 2 * F) return CAM_ERR_ARG;
     if (misaligned8(y)) return CAM_ERR_ALIGN;
     if (M == 0) return CAM_OK;
-    if (!launch_actq_rows(SiluMulSrc{(const uint16_t *)gu, ld, F}, !misaligned8(gu) && !(ld & 3), M, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes, CAM_ST))
-        actq_kernel<<<M, 256, 0, CAM_ST>>>(SiluMulSrc{(const uint16_t *)gu, ld, F}, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes);
+    const bool vec = !misaligned8(gu) && !(ld & 3);
+    if (!launch_actq_rows(SiluMulSrc{(const uint16_t *)gu, ld, F}, vec, M, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes, CAM_ST)) {
+        if (vec) actq_kernel<SiluMulSrc, true><<<M, 256, 0, CAM_ST>>>(SiluMulSrc{(const uint16_t *)gu, ld, F}, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes);
+        else actq_kernel<<<M, 256, 0, CAM_ST>>>(SiluMulSrc{(const uint16_t *)gu, ld, F}, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes);
+    }
     return (int)cudaGetLastError();
 }
 // block_entry_fwd: kernels/actq.hip:247-249 (M = grid.x); wrapper python/caminus/train/actq.py:131-151. d <= 1024 in the reference's

@@ -242,34 +242,6 @@ __global__ void __launch_bounds__(256) ew_vec_kernel(const void * __restrict__ a
         if (OP == EW_CAST_BF16) ((uint16_t *)y)[i] = bf16_nan(__ldg((const float *)a + i));
     }
 }
-// bf16(silu(g)) for N values without the exact statements' two divisions and polynomial where that provably gives the same bits: the
-// special-function evaluation s^ = g rcp(1 + ex2(-g log2 e)) is within 1.35e-6 |s| of cam_silu(g) for g >= -8 and 3e-38 <= |g| < 3e38
-// (the analysis at the fused SwiGLU + Q8_1 kernel, csrc/swiglu_q8.cu, without its last product). If s^ (1 - 1.55e-6) and s^ (1 + 1.55e-6) round to the same
-// bf16, no rounding boundary and no tie lies in the interval that holds cam_silu(g), and that bf16 is its rounding. The conditions are
-// ranges are gathered over the N values (minimum, largest and smallest magnitude) and tested once: an item with a value outside the
-// range, a zero or an infinity evaluates the exact statements for all N, a pair with an interval that holds a boundary (1 value in
-// about 1400) for its two. A NaN gate passes the gathered tests (minimum and maximum skip it) and gives the conversion's NaN, 0x7fff:
-// the callers' NaN test of the result sends such an item to the exact statements too. out[k] = values 2 k (low half), 2 k + 1.
-// Returns the pairs to redo with the exact statements, bit k for out[k] (0: none): a pair whose two roundings differ, every pair
-// when a range test fails. (A warp runs the redo when one of its lanes asks: per pair that is 1 step in 22, per item it was 1 in 6.)
-template <int N> CAM_DEV uint32_t silu_bf16_fast(const float (&g)[N], uint32_t (&out)[N / 2]) {
-    float gmin = g[0], amax = fabsf(g[0]), amin = fabsf(g[0]);
-    uint32_t redo = 0;
-#pragma unroll
-    for (int k = 0; k < N; k += 2) {
-        const float s0 = fmul(g[k], rcp_approx(fadd(1.0f, ex2_approx(fmul(g[k], -0x1.715476p+0f)))));
-        const float s1 = fmul(g[k + 1], rcp_approx(fadd(1.0f, ex2_approx(fmul(g[k + 1], -0x1.715476p+0f)))));
-        uint32_t lo;
-        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(out[k >> 1]) : "f"(fmul(s1, 0x1.00001ap+0f)), "f"(fmul(s0, 0x1.00001ap+0f)));
-        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(fmul(s1, 0x1.ffffccp-1f)), "f"(fmul(s0, 0x1.ffffccp-1f)));
-        if (out[k >> 1] != lo) redo |= 1u << (k >> 1);
-        if (k) { gmin = fminf(gmin, g[k]); amax = fmaxf(amax, fabsf(g[k])); amin = fminf(amin, fabsf(g[k])); }
-        gmin = fminf(gmin, g[k + 1]); amax = fmaxf(amax, fabsf(g[k + 1])); amin = fminf(amin, fabsf(g[k + 1]));
-    }
-    return (gmin >= -8.0f && amax < 3.0e38f && amin >= 3.0e-38f) ? redo : (1u << (N / 2)) - 1u;
-}
-CAM_DEV bool bf16_pair_has_nan(uint32_t w) { return (w & 0x7fffu) > 0x7f80u || (w & 0x7fff0000u) > 0x7f800000u; }
-
 // pf_silu_bf16 / pf_to_bf16 over items of four elements: item i is row i / K4, columns 4 (i % K4) .. (K4 = K / 4; the division only when
 // the rows are strided); items of the padding rows store zeros
 template <bool SILU>
