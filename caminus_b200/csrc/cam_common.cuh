@@ -186,33 +186,6 @@ CAM_DEV float ref_total_f32(float (&a)[8], int lane) {
     return tot;
 }
 
-// The same total with fewer exchanges, for kernels that take it once per few hundred values: the three exchange stages halve the
-// accumulators a lane carries instead of duplicating them (a lane keeps a[k] + partner's a[k] for half of its k and hands the other
-// half over), which gives every sum the butterfly gives since fadd commutes; lane bits 2, 1, 0 end up selecting b, c bit 1, c bit 0 of
-// the one S[c + 4 b] a lane holds, so partners 2 and 1 are two more single-value exchanges. 9 shuffles instead of 24.
-CAM_DEV float ref_total_f32_rs(const float (&a)[8], int lane) {
-    const bool b2 = lane & 4, b1 = lane & 2, b0 = lane & 1;
-    float v4[4], v2[2];
-#pragma unroll
-    for (int c = 0; c < 4; c++) {                                   // partner 16 (lane ^ 4): keep b = bit 2
-        const float keep = b2 ? a[4 + c] : a[c], give = b2 ? a[c] : a[4 + c];
-        v4[c] = fadd(keep, __shfl_xor_sync(CAM_FULL, give, 4));
-    }
-#pragma unroll
-    for (int c = 0; c < 2; c++) {                                   // partner 8 (lane ^ 2): keep c bit 1 = bit 1
-        const float keep = b1 ? v4[2 + c] : v4[c], give = b1 ? v4[c] : v4[2 + c];
-        v2[c] = fadd(keep, __shfl_xor_sync(CAM_FULL, give, 2));
-    }
-    const float keep = b0 ? v2[1] : v2[0], give = b0 ? v2[0] : v2[1];
-    float S = fadd(keep, __shfl_xor_sync(CAM_FULL, give, 1));      // partner 4 (lane ^ 1): S[c + 4 b], c = 2 bit 1 + bit 0
-    S = fadd(S, __shfl_xor_sync(CAM_FULL, S, 2));                   // partner 2: S[c] + S[c ^ 2]
-    S = fadd(S, __shfl_xor_sync(CAM_FULL, S, 1));                   // partner 1: P[b] in every lane with bit 2 = b
-    float tot = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 8; w++) tot = fadd(tot, __shfl_sync(CAM_FULL, S, 8 * (w & 3) + 4 * (w >> 2)));
-    return tot;
-}
-
 // the same sum for fp16 rows, where lane l holds the 8 halves at 8 l + 256 m: accumulator c is thread 8 l + c with j = m; wave l >> 2,
 // wave lane 8 (l & 3) + c: partners 16, 8 are lanes l ^ 2, l ^ 1; partners 4, 2, 1 are inside the lane
 CAM_DEV float ref_total_f16(float (&a)[8], int lane) {

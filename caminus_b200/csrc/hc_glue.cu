@@ -418,7 +418,7 @@ __global__ void __launch_bounds__(NR_WARPS * 32) qk_nr_vec_kernel(const float * 
                 a[q + 0] = ffma(xv[m].x, xv[m].x, a[q + 0]); a[q + 1] = ffma(xv[m].y, xv[m].y, a[q + 1]);
                 a[q + 2] = ffma(xv[m].z, xv[m].z, a[q + 2]); a[q + 3] = ffma(xv[m].w, xv[m].w, a[q + 3]);
             }
-            const float tot = ref_total_f32_rs(a, lane);
+            const float tot = ref_total_f32(a, lane);
             const float scale = cam_rsqrt(fadd(fdiv(tot, (float)D), eps));
 #pragma unroll
             for (int m = 0; m < NCH; m++) {
