@@ -12,7 +12,8 @@ import sys
 
 import numpy as np
 
-REF = sys.argv[1] if len(sys.argv) > 1 else '/root/reference'
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get('CAMINUS_REFERENCE', '')
+if not os.path.isdir(os.path.join(REF, 'python', 'caminus')): sys.exit('usage: python tests/golden/make_golden.py /path/to/caminus   (or CAMINUS_REFERENCE=...)')
 sys.path.insert(0, os.path.join(REF, 'python'))
 sys.path.insert(0, os.path.join(REF, 'python', 'caminus', '_vendor'))
 sys.path.insert(0, os.path.join(REF, 'tests', 'engine'))
