@@ -91,6 +91,7 @@ class TPRmsNormFused:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.tag = 0
         self._mapped = []                                        # bases of the peers' allocations mapped into this process
+        self._export = None
         ptrs = [0] * self.world
         if self.world > 1:
             import ctypes
@@ -103,6 +104,7 @@ class TPRmsNormFused:
             if len(raw) < 64 or (len(raw) > 64 and raw[-65:-64] != b'c'):
                 raise RuntimeError(f'TPRmsNormFused: the allocator exported a handle this code does not map ({len(raw)} bytes, kind {raw[-65:-64]!r}): '
                                    'expandable segments are not supported')
+            self._export = (shared[4], shared[5])                # the allocator's count of importers for this export (released in close)
             mine = (raw[-64:], int(shared[3]))
             everyone = [None] * self.world
             dist.all_gather_object(everyone, mine, group=group)
@@ -144,11 +146,20 @@ class TPRmsNormFused:
         return h16
 
     def close(self):
-        """unmap the peers' buffers (after the last call has finished on every rank)"""
+        """unmap the peers' buffers (after the last call has finished on every rank). With more than one rank this is a collective
+        call: every rank of the group makes it (it waits until all have unmapped before this rank's block counts as unshared)"""
         torch.cuda.synchronize(self.dev)
         with torch.cuda.device(self.dev):
             for base in self._mapped: _lib.load().cam_ipc_close(base)
         self._mapped = []
+        if self._export is not None:
+            if self.world > 1 and dist.is_initialized(): dist.barrier(group=self.group)      # every peer has unmapped this rank's block
+            # the export counted one importer that the allocator expects to report back; the peers map the block through this library
+            # instead, so the exporter reports for them (else the allocator warns at exit that the block was still shared)
+            handle, offset = self._export
+            self._export = None
+            try: torch.UntypedStorage._release_ipc_counter(handle, offset, device=self.dev)
+            except Exception: pass                               # (bookkeeping only)
 
     def check(self):
         torch.cuda.synchronize(self.dev)
