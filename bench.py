@@ -214,6 +214,8 @@ def single_op_lines(torch, dev, peak, only=()):
     gt = (torch.randn(T * INTER, device=dev, generator=g) * 1.5).half(); up = (torch.randn(T * INTER, device=dev, generator=g) * 1.5).half()
     yq = torch.empty(T * INTER // 32 * 36, dtype=torch.uint8, device=dev)
     line('swiglu_q8_1_f16_T8192', T * BYTES_PER_TOKEN['swiglu_q8_1_f16'], timed(lambda i: gguf.swiglu_q8_1(gt, up, yq)), T, 'tokens_per_s')
+    line('swiglu_q8_1_f16_sums_T8192', T * BYTES_PER_TOKEN['swiglu_q8_1_f16'], timed(lambda i: gguf.swiglu_q8_1(gt, up, yq, sums=True)), T, 'tokens_per_s')
+    line('swiglu_q8_1_f16_strict_T8192', T * BYTES_PER_TOKEN['swiglu_q8_1_f16'], timed(lambda i: gguf.swiglu_q8_1(gt, up, yq, strict=True)), T, 'tokens_per_s')
     del gt, up, yq
     # config 4: Q4_K rows, vocab 151936 x 2048, 16384 ids (output 134 MB: 2 rotating outputs)
     vocab, N, n = 151936, 2048, 16384

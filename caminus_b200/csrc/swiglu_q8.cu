@@ -84,20 +84,25 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_1_kernel(const T * __restrict__
 //          from the fp16 rounding tie (0x1000) and d^ is in fp16's normal range, fp16(d^) = fp16(d): the stored scale is exact.
 //   codes: t^ = h^ / d^ is within 3.06e-6 |t| of the exact fp32 quotient t. If t^ (1 - 3.2e-6) and t^ (1 + 3.2e-6) round to the
 //          same integer, no rounding boundary and no tie lies in the interval that holds t, and that integer is roundf(t).
+//   sum (SUMS): the fast pass adds the h^ in the exact statements' order. Its sum S^ is within 1.95e-6 A of theirs, A = sum |h^| (1.35e-6 A
+//          from the values, 3e-7 A from the five levels of fp32 additions of either tree). If S^ - 2.2e-6 A and S^ + 2.2e-6 A round
+//          to the same fp16, no fp16 rounding boundary lies in the interval that holds the exact sum: the stored sum is exact.
 // A block (32 values) where any of this fails: some g < -8, an interval that holds a rounding boundary, d^ near an fp16
 // tie or outside [6.2e-5, 6e4), a sum that is not finite (NaN or infinite input): is recomputed by the whole warp with
-// the exact statements, one lane per value. About 2 % of the blocks of Gaussian inputs take that path.
-// The stored scale d and the 32 codes are therefore always the exact statements' bytes. The block sum of a block on the
-// fast pass is the fp16 rounding of the same-order sum of the h^: it can differ from the exact statements' sum by one fp16
-// ulp (or by 1.6e-6 sum |h| when the values cancel). The reference reports that field and does not gate it
-// (tests/engine/golden_util.py:145-146); the strict kernel above gives its exact bytes too.
+// the exact statements, one lane per value. About 2 % of the blocks of Gaussian inputs take that path (4 % with the sum test).
+// The stored scale d and the 32 codes are therefore always the exact statements' bytes. With SUMS so is the block sum: all 36 bytes.
+// Without it the sum of a block on the fast pass is the fp16 rounding of S^: it can differ from the exact statements' sum by one fp16
+// ulp (or by 2e-6 A when the values cancel). The reference reports that field and does not gate it (tests/engine/golden_util.py:145-146).
+// The sum test costs a quarter of the throughput (the recomputation of twice as many blocks no longer hides behind the memory system),
+// so it is a separate entry.
 // One warp-wide step over 16 blocks (512 values) starting at pair `base` (a multiple of 32): 16 values per lane, two lanes per block.
 // (With 8 values per lane and four lanes per block the same pass ran at 88 % of the copy bandwidth: the work that does not depend on
 // the number of values (loop, indices, margins, ballots, store addresses) was a third of its instructions; spent once per 16 values
 // the kernel is memory-bound.) FULL: all 32 lanes have a pair.
 // Block sum in aq_fill's order: a lane holds groups 4 q .. 4 q + 3 (q its place in the pair): partner 4 is the other lane, partners 2
 // and 1 are the lane's own groups.
-template <typename T, bool FULL>
+// SUMS: also prove the block sum (else it is the fp16 rounding of the fast pass's own sum, within one fp16 ulp of the exact one)
+template <typename T, bool FULL, bool SUMS>
 CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y, int base, int npairs, int lane) {
     const int pi = base + lane, q = lane & 1;
     const bool on = FULL || pi < npairs;
@@ -120,7 +125,7 @@ CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, 
 #pragma unroll
         for (int k = 0; k < 16; k++) { gv[k] = 0.0f; uv[k] = 0.0f; }
     }
-    float gmin = gv[0], amax = 0.0f, gsm = fabsf(gv[0]);
+    float gmin = gv[0], amax = 0.0f, gsm = fabsf(gv[0]), sabs0 = 0.0f, sabs1 = 0.0f;
 #pragma unroll
     for (int k = 1; k < 16; k++) { gmin = fminf(gmin, gv[k]); if (sizeof(T) == 4) gsm = fminf(gsm, fabsf(gv[k])); }
 #pragma unroll
@@ -128,8 +133,11 @@ CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, 
         const float e = ex2_approx(fmul(gv[k], -0x1.715476p+0f));
         h[k] = fmul(fmul(gv[k], rcp_approx(fadd(1.0f, e))), uv[k]);
         amax = fmaxf(amax, fabsf(h[k]));
+        if (SUMS) { if (k & 1) sabs1 = fadd(sabs1, fabsf(h[k])); else sabs0 = fadd(sabs0, fabsf(h[k])); }
     }
     amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, 1));
+    float sabs = fadd(sabs0, sabs1);
+    if (SUMS) sabs = fadd(sabs, __shfl_xor_sync(CAM_FULL, sabs, 1));                                      // sum |h^| of the block
     float sg[4];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
@@ -147,7 +155,9 @@ CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, 
         differ |= v[k] ^ __float_as_uint(ffma(h[k], inv_lo, 12582912.0f));
     }
     const int low = (int)(__float_as_uint(d) & 0x1fffu) - 0x1000;
-    const bool redo = differ != 0 || !(gmin >= -8.0f) || !(d >= 6.2e-5f && d < 6.0e4f) || (low >= -40 && low <= 40) || !(fabsf(sum) < 3.0e38f) ||
+    const float smargin = fmul(sabs, 2.2e-6f);
+    const bool sum_open = SUMS && __half_as_ushort(__float2half_rn(fsub(sum, smargin))) != __half_as_ushort(__float2half_rn(fadd(sum, smargin)));
+    const bool redo = differ != 0 || sum_open || !(gmin >= -8.0f) || !(d >= 6.2e-5f && d < 6.0e4f) || (low >= -40 && low <= 40) || !(fabsf(sum) < 3.0e38f) ||
                       (sizeof(T) == 4 && on && !(gsm >= 3.0e-38f));
     const uint32_t mask = __ballot_sync(CAM_FULL, redo && on);
     const uint32_t pairs = (mask | (mask >> 1)) & 0x55555555u;              // bit 2 j: block j of this warp
@@ -177,15 +187,15 @@ CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, 
     }
 }
 
-template <typename T>
+template <typename T, bool SUMS>
 __global__ void __launch_bounds__(Q8_THREADS) swiglu_q8_fast_kernel(const T * __restrict__ g, const T * __restrict__ u,
                                                                       uint8_t * __restrict__ y, int nb) {
     const int lane = threadIdx.x & 31;
     const int npairs = nb * 2;
     const int stride = gridDim.x * Q8_THREADS;
     int base = blockIdx.x * Q8_THREADS + (threadIdx.x & ~31);
-    for (; base + 32 <= npairs; base += stride) swiglu_q8_step<T, true>(g, u, y, base, npairs, lane);
-    if (base < npairs) swiglu_q8_step<T, false>(g, u, y, base, npairs, lane);
+    for (; base + 32 <= npairs; base += stride) swiglu_q8_step<T, true, SUMS>(g, u, y, base, npairs, lane);
+    if (base < npairs) swiglu_q8_step<T, false, SUMS>(g, u, y, base, npairs, lane);
 }
 
 // the last, partial block (n % 32 values, the rest 0): one warp, one lane per value
@@ -277,8 +287,9 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_plain_kernel(const T * __restri
     if (base < npairs) q8_plain_step<T, false>(x, y, base, npairs, lane);
 }
 
-// FAST: the two-pass fused kernel (SwiGLU only). Plain quantisation: q8_plain_kernel. Strict SwiGLU: the exact statements for every value
-template <typename T, bool SWIGLU, bool FAST = false>
+// FAST 1: the two-pass fused kernel (SwiGLU only); 2: the same with the block sums proven too. Plain quantisation: q8_plain_kernel.
+// Strict SwiGLU (FAST 0): the exact statements for every value
+template <typename T, bool SWIGLU, int FAST = 0>
 int launch_q8(const T * g, const T * u, void * y, long n, cudaStream_t stream) {
     if (n < 0 || !g || !y || (SWIGLU && !u)) return CAM_ERR_ARG;
     if (n == 0) return CAM_OK;
@@ -291,7 +302,7 @@ int launch_q8(const T * g, const T * u, void * y, long n, cudaStream_t stream) {
             for (long b0 = 0; b0 < nb; b0 += piece) {
                 const long m = nb - b0 < piece ? nb - b0 : piece;
                 const long w = (m * 2 + Q8_THREADS - 1) / Q8_THREADS;
-                swiglu_q8_fast_kernel<T><<<cam_resident_grid(swiglu_q8_fast_kernel<T>, Q8_THREADS, 0, w), Q8_THREADS, 0, stream>>>(
+                swiglu_q8_fast_kernel<T, FAST == 2><<<cam_resident_grid(swiglu_q8_fast_kernel<T, FAST == 2>, Q8_THREADS, 0, w), Q8_THREADS, 0, stream>>>(
                     g + b0 * 32, u + b0 * 32, (uint8_t *)y + b0 * 36, (int)m);
             }
         } else if (!SWIGLU) {
@@ -355,11 +366,19 @@ extern "C" int gg_quantize_q8_1(const float * x, void * y, int n, void * stream)
 // gg_swiglu_q8_1: Q8_1 blocks of silu(x[i]) mul[i]: the tape op OP_GG_Q8_1 with work = 2 as one launch.
 // Reference: kernels/k3_gguf_ops.h:55-77 (semantics); python/caminus/engine/k3.py:649-659 (Engine.gg_q8_1(x, yq, mul=u)).
 extern "C" int gg_swiglu_q8_1(const float * x, const float * mul, void * y, long n, void * stream) {
-    return launch_q8<float, true, true>(x, mul, y, n, (cudaStream_t)stream);
+    return launch_q8<float, true, 1>(x, mul, y, n, (cudaStream_t)stream);
 }
 // the same with fp16 gate and up (widened exactly to fp32 before the same statements)
 extern "C" int gg_swiglu_q8_1_f16(const void * g, const void * u, void * y, long n, void * stream) {
-    return launch_q8<uint16_t, true, true>((const uint16_t *)g, (const uint16_t *)u, y, n, (cudaStream_t)stream);
+    return launch_q8<uint16_t, true, 1>((const uint16_t *)g, (const uint16_t *)u, y, n, (cudaStream_t)stream);
+}
+// The _sums forms: the fast pass with the block sum proven as well: all 36 bytes are the exact statements' bytes, at about 70 % of
+// the copy bandwidth (one block in 25 is recomputed instead of one in 50).
+extern "C" int gg_swiglu_q8_1_sums(const float * x, const float * mul, void * y, long n, void * stream) {
+    return launch_q8<float, true, 2>(x, mul, y, n, (cudaStream_t)stream);
+}
+extern "C" int gg_swiglu_q8_1_f16_sums(const void * g, const void * u, void * y, long n, void * stream) {
+    return launch_q8<uint16_t, true, 2>((const uint16_t *)g, (const uint16_t *)u, y, n, (cudaStream_t)stream);
 }
 // The strict forms: every value through the exact statements, so the block sums are the exact statements' bytes as well as
 // d and the codes (which the entries above already guarantee). About half the throughput.

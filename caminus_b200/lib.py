@@ -31,6 +31,8 @@ SIGNATURES = {
     'gg_quantize_q8_1': [P, P, I, P],
     'gg_swiglu_q8_1': [P, P, P, L, P],
     'gg_swiglu_q8_1_f16': [P, P, P, L, P],
+    'gg_swiglu_q8_1_sums': [P, P, P, L, P],
+    'gg_swiglu_q8_1_f16_sums': [P, P, P, L, P],
     'gg_swiglu_q8_1_strict': [P, P, P, L, P],
     'gg_swiglu_q8_1_f16_strict': [P, P, P, L, P],
     'q3p_qk_rope': [I, P, I, I, I, P, I, P, P, P],

@@ -163,6 +163,7 @@ def test_swiglu_q8_1_vs_oracle(dtype, n):
     want = oracle.swiglu_q8_1(g, u, sum_order=1)
     ys = gguf.swiglu_q8_1(cu(g), cu(u), strict=True)
     assert same(ys, want)                                                        # strict: every byte
+    assert same(gguf.swiglu_q8_1(cu(g), cu(u), sums=True), want)                 # the fast pass with the sum test: every byte too
     y = gguf.swiglu_q8_1(cu(g), cu(u)).cpu().numpy()
     d, s, q = oracle.q8_split(y); d1, s1, q1 = oracle.q8_split(want)
     assert np.array_equal(q, q1) and same(d, d1)                                 # the fused kernel: d and codes exact, always
@@ -194,6 +195,7 @@ def test_swiglu_q8_1_hard_inputs(kind):
     ok = ~(np.isnan(d1.astype(np.float32)))                                      # (a NaN scale has no fixed bit pattern)
     assert np.array_equal(q, q1) and np.array_equal(d.view(np.uint16)[ok], d1.view(np.uint16)[ok]) and np.isnan(d.astype(np.float32)[~ok]).all()
     if kind != 'nonfinite': assert sums_close(y, want, oracle.swiglu_f32_from_f16(gate, up))
+    if kind != 'nonfinite': assert np.array_equal(gguf.swiglu_q8_1(cu(gate), cu(up), sums=True).cpu().numpy(), want)     # all 36 bytes
 
 
 def test_swiglu_q8_1_f32_denormal_gates():
@@ -211,6 +213,7 @@ def test_swiglu_q8_1_f32_denormal_gates():
         d, s_, q = oracle.q8_split(y); d1, s1, q1 = oracle.q8_split(want)
         assert np.array_equal(q, q1) and np.array_equal(d.view(np.uint16), d1.view(np.uint16))
         if strict: assert np.array_equal(y, want)
+    assert np.array_equal(gguf.swiglu_q8_1(cu(gate), cu(up), sums=True).cpu().numpy(), want)
 
 
 def test_swiglu_golden_reference_host_path(golden):
@@ -240,6 +243,7 @@ def test_swiglu_q8_1_full_size_config():
     rows = np.arange(0, T, 61)
     want = oracle.swiglu_q8_1(g[rows].reshape(-1), u[rows].reshape(-1), sum_order=1).reshape(len(rows), I // 32, 36)
     assert np.array_equal(ysb[torch.from_numpy(rows).to(DEV)].cpu().numpy(), want)     # the exact statements: the oracle's bytes
+    assert torch.equal(gguf.swiglu_q8_1(gd.reshape(-1), ud.reshape(-1), sums=True), ystrict)       # the sum test: all 36 bytes of all 6.5 M blocks
     # the fused kernel against the exact statements over ALL 6.5 M blocks: d and the 32 codes identical, sums within one fp16 ulp
     assert torch.equal(yb[:, :, 0:2], ysb[:, :, 0:2]) and torch.equal(yb[:, :, 4:], ysb[:, :, 4:])
     sf, ss_ = yb[:, :, 2:4].contiguous().view(torch.float16).float(), ysb[:, :, 2:4].contiguous().view(torch.float16).float()
