@@ -443,7 +443,7 @@ def main():
             t = torch.tensor([tf], device=dev, dtype=torch.float64); torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX); tf = float(t.item())
             tp['fused'] = {'us_per_step': tf * 1e6, 'tokens_per_s': T / tf, 'hbm_gbs_per_gpu': T * 4 * Ns * 2 / tf / 1e9,
                            'nvlink_bytes_per_rank': T * 8 * (world - 1), 'note': 'one launch per rank: per-row partials stored into every peer, rows normalised as they complete'}
-            barrier(); fused.close()
+            barrier(); fused.close(); barrier()              # (every rank has unmapped before any buffer can go)
         except Exception as e:      # (peer mapping refused on this box: keep the collective form's number)
             tp['fused'] = {'unavailable': f'{type(e).__name__}: {e}'[:200]}
         del xs, ds, hs

@@ -146,14 +146,13 @@ class TPRmsNormFused:
         return h16
 
     def close(self):
-        """unmap the peers' buffers (after the last call has finished on every rank). With more than one rank this is a collective
-        call: every rank of the group makes it (it waits until all have unmapped before this rank's block counts as unshared)"""
+        """unmap the peers' buffers (after the last call has finished on every rank: the caller's barrier). Keep this object (its
+        buffer) alive until every rank has closed"""
         torch.cuda.synchronize(self.dev)
         with torch.cuda.device(self.dev):
             for base in self._mapped: _lib.load().cam_ipc_close(base)
         self._mapped = []
         if self._export is not None:
-            if self.world > 1 and dist.is_initialized(): dist.barrier(group=self.group)      # every peer has unmapped this rank's block
             # the export counted one importer that the allocator expects to report back; the peers map the block through this library
             # instead, so the exporter reports for them (else the allocator warns at exit that the block was still shared)
             handle, offset = self._export

@@ -46,6 +46,7 @@ def _rank(rank, world, port, T, N, out):
             fused_ok = fused_ok and torch.equal(h_f, h_ref) and torch.equal(xa, xb)
         dist.barrier()
         fused.close()
+        dist.barrier()
         # the unsharded kernel on this rank's rows of the full-width batch (row sharding: no collective)
         ra, rb = D.row_shard(T, rank, world)
         xr = torch.from_numpy(x0[ra:rb].copy()).to(dev)
