@@ -59,23 +59,31 @@ def check(err):
 _IQ2S = {}
 
 
-def set_iq2s_grid(grid, device=None):
-    """grid: the reference's iq_tables.GRID_IQ2_S (uint8 [1024, 8], magnitudes 8 / 25 / 43) or its packed form (uint32 / int32 [512]:
-    2-bit codes 0 / 1 / 2 at bits 2 k, entry 2 w in word w's low half), as a numpy array or tensor; kept on `device` (default: current)"""
+def pack_iq2s_grid(grid):
+    """grid: the reference's iq_tables.GRID_IQ2_S (uint8 [1024, 8], magnitudes 8 / 25 / 43) or its packed form (uint32 / int32 [512]);
+    returns the packed words (uint32 [512]: 2-bit codes 0 / 1 / 2 at bits 2 k, entry 2 w in word w's low half, kernels/iq2s_grid.h)"""
     import numpy as np
-    import torch
-    g = grid.detach().cpu().numpy() if torch.is_tensor(grid) else np.asarray(grid)
+    g = np.asarray(grid)
     if g.size == 8192:
         m = g.astype(np.uint8).reshape(1024, 8)
-        if not np.isin(m, (8, 25, 43)).all(): raise ValueError('set_iq2s_grid: magnitudes other than 8 / 25 / 43')
+        if not np.isin(m, (8, 25, 43)).all(): raise ValueError('IQ2_S grid: magnitudes other than 8 / 25 / 43')
         code = np.where(m == 8, 0, np.where(m == 25, 1, 2)).astype(np.uint32)
         e = (code << (2 * np.arange(8, dtype=np.uint32))).sum(axis=1).astype(np.uint32)
-        g = e[0::2] | (e[1::2] << 16)
-    elif g.size != 512 or g.dtype.itemsize != 4:
-        raise ValueError(f'set_iq2s_grid: {g.size} values of {g.dtype}; expected uint8 [1024, 8] or 512 packed words')
+        return (e[0::2] | (e[1::2] << 16)).astype(np.uint32)
+    if g.size != 512 or g.dtype.itemsize != 4:
+        raise ValueError(f'IQ2_S grid: {g.size} values of {g.dtype}; expected uint8 [1024, 8] or 512 packed words')
+    return np.ascontiguousarray(g).view(np.uint32).reshape(512).copy()
+
+
+def set_iq2s_grid(grid, device=None):
+    """hands the IQ2_S grid (either form pack_iq2s_grid takes, as a numpy array or tensor) to the library's launches on `device`
+    (default: the current one)"""
+    import numpy as np
+    import torch
+    g = pack_iq2s_grid(grid.detach().cpu().numpy() if torch.is_tensor(grid) else grid)
     dev = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
     idx = dev.index if dev.index is not None else torch.cuda.current_device()
-    _IQ2S[idx] = torch.from_numpy(np.ascontiguousarray(g).view(np.int32).reshape(512).copy()).to(torch.device('cuda', idx))
+    _IQ2S[idx] = torch.from_numpy(g.view(np.int32)).to(torch.device('cuda', idx))
 
 
 def _iq2s_grid():

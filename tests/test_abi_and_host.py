@@ -112,3 +112,17 @@ def test_mmq_buffer_arithmetic_matches_the_reference():
     assert [mmq.k_pad(k) for k in (1, 512, 513, 2048, 2560, 25600)] == [512, 512, 1024, 2048, 2560, 25600]
     assert mmq.y_bytes(2048, 10) == 2048 // 128 * 10 * 144 + 18432 and mmq.y_bytes(600, 3) == 1024 // 128 * 3 * 144 + 18432
     assert (mmq.D4, mmq.DS4) == (0, 1)
+
+
+def test_iq2s_grid_packing():
+    """the packed IQ2_S grid (the layout of the reference's kernels/iq2s_grid.h): the shim's packing == the oracle's, both input forms, refusals"""
+    import oracle
+    from caminus_b200.device import cuda as hip
+    g = np.array([8, 25, 43], np.uint8)[np.random.default_rng(1).integers(0, 3, (1024, 8))]
+    w = hip.pack_iq2s_grid(g)
+    assert w.dtype == np.uint32 and w.shape == (512,) and np.array_equal(w, oracle.pack_iq2s_grid(g))
+    e5 = (w[2] >> 16) & 0xffff                                            # entry 5 = word 2, high half
+    assert [(int(e5) >> (2 * k)) & 3 for k in range(8)] == [{8: 0, 25: 1, 43: 2}[int(v)] for v in g[5]]
+    assert np.array_equal(hip.pack_iq2s_grid(w), w) and np.array_equal(hip.pack_iq2s_grid(w.view(np.int32)), w)
+    with pytest.raises(ValueError): hip.pack_iq2s_grid(np.zeros((1024, 8), np.uint8))
+    with pytest.raises(ValueError): hip.pack_iq2s_grid(np.zeros(100, np.uint32))
