@@ -262,6 +262,10 @@ def single_op_lines(torch, dev, peak, only=()):
     Mr, Kq = 32768, 1024
     xa = rnd(Mr, Kq, scale=2.0).bfloat16()
     line('actq_codes_bf16_M32768_K1024', Mr * Kq * (2 + 2 + 0.5) + Mr * 4, timed(lambda i: A.actq_codes(xa, 4, 1.0)), Mr, 'rows_per_s')
+    for Kq2, Mr2 in ((2048, 16384), (4096, 8192)):
+        xa2 = rnd(Mr2, Kq2, scale=2.0).bfloat16()
+        line(f'actq_codes_bf16_M{Mr2}_K{Kq2}', Mr2 * Kq2 * (2 + 2 + 0.5) + Mr2 * 4, timed(lambda i: A.actq_codes(xa2, 4, 1.0)), Mr2, 'rows_per_s')
+        del xa2
     gu = rnd(8192, 2 * 4096, scale=2.0).bfloat16()
     line('silu_mul_actq_M8192_F4096', 8192 * 4096 * (4 + 2 + 0.5) + 8192 * 4, timed(lambda i: A.silu_mul_actq(gu, 4, 1.0)), 8192, 'rows_per_s')
     xe = rnd(Mr, 896, scale=2.0); nwe = 0.5 + torch.rand(896, device=dev, generator=g); wab = rnd(8, 896, scale=0.05).bfloat16()

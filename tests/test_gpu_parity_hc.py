@@ -313,7 +313,7 @@ def test_mmq_quantize_ids_and_scatter(layout):
     with pytest.raises(ValueError): M.quantize(xd, K, ncols, torch.zeros(100, dtype=torch.uint8, device=DEV), layout)
 
 
-@pytest.mark.parametrize('M,K', [(1, 128), (37, 896), (300, 1024), (5, 8192), (20, 2048), (9, 4096), (3, 384)])
+@pytest.mark.parametrize('M,K', [(1, 128), (37, 896), (300, 1024), (5, 8192), (20, 2048), (9, 4096), (3, 384), (11, 4224), (6, 2304), (70, 6144)])
 def test_actq_family(M, K):
     """actq_fwd_*, silu_mul_actq_fwd, block_entry_fwd: values, scales and packed codes are the oracle's bytes; silu extremes and a
     row-strided view as tests/train/test_silu_mul_actq.py:21-47"""
