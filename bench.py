@@ -244,6 +244,7 @@ def single_op_lines(torch, dev, peak, only=()):
     rows, K = 8192, 25600
     gh = (rnd(rows, K, scale=1.5)).half(); uh = (rnd(rows, K, scale=1.5)).half(); ym = torch.empty(K // 128, rows, 144, dtype=torch.uint8, device=dev)
     line('swiglu_mmq_q8_1_f16_T8192_K25600_D4', rows * K * 4 + rows * K // 128 * 144, timed(lambda i: gguf.quantize_mmq_q8_1(gh, 'D4', u=uh, y=ym)), rows, 'tokens_per_s')
+    line('swiglu_mmq_q8_1_f16_T8192_K25600_DS4', rows * K * 4 + rows * K // 128 * 144, timed(lambda i: gguf.quantize_mmq_q8_1(gh, 'DS4', u=uh, y=ym)), rows, 'tokens_per_s')
     del gh, uh, ym
     T, nh, nkv = 4096, 32, 4; M = nkv * 128; ldq = nh * 128 + 2 * M; rowb = 2 * (M // 32) * 34
     Q8 = q3m_ops.Ops(dev, q8=True)

@@ -162,7 +162,7 @@ static dim3 mmq_grid(K kernel, long nx, long ny) {
     return dim3((unsigned)gx, (unsigned)gy);
 }
 
-// ---- SwiGLU into D4 blocks at memory speed: a fast pass with proof margins, exact recomputation where a margin is not met ---
+// ---- SwiGLU into D4 / DS4 blocks: a fast pass with proof margins, exact recomputation where a margin is not met ---
 //
 // The scale of this layout is a full fp32 number, d = 1.0f / (127.0f / amax), so it needs the exact statements' amax bit for bit.
 // The fast pass evaluates h^ = g * rcp(1 + ex2(-g log2 e)) * u on the special-function unit; with h the exact statements' value
@@ -239,7 +239,13 @@ CAM_DEV void mmq_fetch(const T * __restrict__ g, const T * __restrict__ u, const
 }
 
 // PF: the next task's values are loaded before this task's arithmetic (fp16: 32 more registers)
-template <typename T, bool PF>
+// LAYOUT 1 (DS4: the header word of a group is (fp16 d, fp16 sum)) needs no exact amax: d^ = amax^ / 127 is within 27 fp32 ulps of the
+// exact statements' d; where its low 13 bits are more than 44 from the fp16 rounding tie and d^ is in fp16's normal range, fp16(d^) is
+// the stored scale. Codes: t^ = h^ (127 rcp(amax^)) is within 3.06e-6 |t| of the exact product; the two-ended test with 1 -+ 3.2e-6.
+// Sum: the fast pass adds the h^ in the reference's order (((x0 + x1) + x2) + x3 per four, then partners 4, 2, 1: six levels); its sum is
+// within 2.07e-6 A of the exact statements', A = sum |h^|; where S^ - 2.3e-6 A and S^ + 2.3e-6 A round to one fp16, that is the stored sum.
+// Groups that fail any of it (about 7 % of Gaussian groups, most of them by the sum) are recomputed exactly as for D4.
+template <typename T, bool PF, int LAYOUT>
 __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y,
                                                                  int kvalid, int nkb, long ld, int rows) {
     const int lane = threadIdx.x & 31, pb = lane & 30, pi = lane & 1;      // a group of 32 values = the lane pair pb, pb + 1
@@ -258,6 +264,7 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
         if (!PF) mmq_fetch(g, u, t, ld, rows, rg, ru);
         else if (kq < nkq) mmq_fetch(g, u, MmqTask(kq, rp, lane, nkb, kvalid), ld, rows, ng, nu);
         float h[2][16], eg = 1.0f, eu = 0.0f;
+        float am2[2] = {0.0f, 0.0f}, sum2[2] = {0.0f, 0.0f}, sab2[2] = {0.0f, 0.0f};      // DS4: the chunks' amax^, S^, A
         uint32_t bad = 0;                                             // bit c: chunk c of this lane fails a margin
 #pragma unroll
         for (int c = 0; c < 2; c++) {
@@ -287,27 +294,58 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
                 if (sizeof(T) == 4) gsm = fminf(gsm, fabsf(gv[e]));
             }
             amax = max_nan(amax, __shfl_xor_sync(CAM_FULL, amax, 1));
-            const float thr = fmul(amax, 0.999997f);
-            uint32_t bits = 0;
+            if constexpr (LAYOUT == 0) {
+                const float thr = fmul(amax, 0.999997f);
+                uint32_t bits = 0;
 #pragma unroll
-            for (int e = 0; e < 16; e++) or_if_ge(bits, h[c][e], thr, 1u << e);
-            const uint32_t ball = (__ballot_sync(CAM_FULL, bits != 0) >> pb) & 0x3u;
-            if ((bits & (bits - 1)) != 0 || ball == 3u || ball == 0 || !(gmin >= -8.0f) || !(amax >= 1.0e-30f && amax < 3.0e38f) ||
-                (sizeof(T) == 4 && !(gsm >= 3.0e-38f))) bad |= 1u << c;
-            const int idx = (__ffs(bits) - 1) & 15, src = pb + ((ball >> 1) & 1u);
-            const float cg = idx < 8 ? rg[c][0].pick(idx) : rg[c][1].pick(idx - 8), cu = idx < 8 ? ru[c][0].pick(idx) : ru[c][1].pick(idx - 8);
-            const float tg = __shfl_sync(CAM_FULL, cg, src), tu = __shfl_sync(CAM_FULL, cu, src);
-            if (pi == c) { eg = tg; eu = tu; }
+                for (int e = 0; e < 16; e++) or_if_ge(bits, h[c][e], thr, 1u << e);
+                const uint32_t ball = (__ballot_sync(CAM_FULL, bits != 0) >> pb) & 0x3u;
+                if ((bits & (bits - 1)) != 0 || ball == 3u || ball == 0 || !(gmin >= -8.0f) || !(amax >= 1.0e-30f && amax < 3.0e38f) ||
+                    (sizeof(T) == 4 && !(gsm >= 3.0e-38f))) bad |= 1u << c;
+                const int idx = (__ffs(bits) - 1) & 15, src = pb + ((ball >> 1) & 1u);
+                const float cg = idx < 8 ? rg[c][0].pick(idx) : rg[c][1].pick(idx - 8), cu = idx < 8 ? ru[c][0].pick(idx) : ru[c][1].pick(idx - 8);
+                const float tg = __shfl_sync(CAM_FULL, cg, src), tu = __shfl_sync(CAM_FULL, cu, src);
+                if (pi == c) { eg = tg; eu = tu; }
+            } else {
+                float ts[4], sab = 0.0f;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; q4++) {
+                    ts[q4] = fadd(fadd(fadd(h[c][4 * q4], h[c][4 * q4 + 1]), h[c][4 * q4 + 2]), h[c][4 * q4 + 3]);
+                    sab = fadd(sab, fadd(fadd(fabsf(h[c][4 * q4]), fabsf(h[c][4 * q4 + 1])), fadd(fabsf(h[c][4 * q4 + 2]), fabsf(h[c][4 * q4 + 3]))));
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; q4++) ts[q4] = fadd(ts[q4], __shfl_xor_sync(CAM_FULL, ts[q4], 1));      // partner 4
+                sum2[c] = fadd(fadd(ts[0], ts[2]), fadd(ts[1], ts[3]));                                          // partners 2, 1
+                sab2[c] = fadd(sab, __shfl_xor_sync(CAM_FULL, sab, 1));
+                am2[c] = amax;
+                if (!(gmin >= -8.0f) || (sizeof(T) == 4 && !(gsm >= 3.0e-38f))) bad |= 1u << c;
+            }
         }
-        // the exact statements for the pair's two candidates, one per lane
-        const float am = fabsf(fmul(cam_silu(eg), eu));
-        const float d_inv = fdiv(127.0f, am), d = fdiv(1.0f, d_inv);
+        // D4: the exact statements for the pair's two candidates, one per lane
+        float d_inv = 0.0f, d = 0.0f;
+        if constexpr (LAYOUT == 0) {
+            const float am = fabsf(fmul(cam_silu(eg), eu));
+            d_inv = fdiv(127.0f, am); d = fdiv(1.0f, d_inv);
+        }
+        uint32_t hdr2[2] = {0u, 0u};
         uint8_t * const yb = y + ((size_t)t.kb * rows + t.r0) * 144;           // row r0's block of this lane's K-block
         uint32_t redo = 0;                                            // bit 2 j + c: group j (of the warp's 16) of chunk c is recomputed
 #pragma unroll
         for (int c = 0; c < 2; c++) {
-            const float di = __shfl_sync(CAM_FULL, d_inv, pb + c);
-            const float inv_hi = fmul(di, 0x1.00001cp+0f), inv_lo = fmul(di, 0x1.ffffc8p-1f);      // 1 +- 1.67e-6
+            float inv_hi, inv_lo;
+            bool open = (bad >> c) & 1u;
+            if constexpr (LAYOUT == 0) {
+                const float di = __shfl_sync(CAM_FULL, d_inv, pb + c);
+                inv_hi = fmul(di, 0x1.00001cp+0f); inv_lo = fmul(di, 0x1.ffffc8p-1f);              // 1 +- 1.67e-6
+            } else {
+                const float dh = fmul(am2[c], 0x1.020408p-7f), di = fmul(127.0f, rcp_approx(am2[c]));
+                inv_hi = fmul(di, 0x1.000036p+0f); inv_lo = fmul(di, 0x1.ffff94p-1f);              // 1 +- 3.2e-6
+                const int low = (int)(__float_as_uint(dh) & 0x1fffu) - 0x1000;
+                const float margin = fmul(sab2[c], 2.3e-6f);
+                open = open || !(dh >= 6.2e-5f && dh < 6.0e4f) || (low >= -44 && low <= 44) || !(fabsf(sum2[c]) < 3.0e38f) ||
+                       __half_as_ushort(__float2half_rn(fsub(sum2[c], margin))) != __half_as_ushort(__float2half_rn(fadd(sum2[c], margin)));
+                hdr2[c] = f2_to_h2(dh, sum2[c]);
+            }
             uint32_t v[16], differ = 0;
 #pragma unroll
             for (int e = 0; e < 16; e++) {
@@ -315,7 +353,7 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
                 differ |= v[e] ^ __float_as_uint(ffma(h[c][e], inv_lo, 12582912.0f));
             }
             const bool on = t.kon && t.r0 + c < rows;
-            const uint32_t mask = __ballot_sync(CAM_FULL, (differ != 0 || ((bad >> c) & 1u)) && on);
+            const uint32_t mask = __ballot_sync(CAM_FULL, (differ != 0 || open) && on);
             const uint32_t pair = (mask | (mask >> 1)) & 0x55555555u;
             redo |= pair << c;
             if (on && !((pair >> pb) & 1u)) {
@@ -328,7 +366,8 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
             }
         }
         // the scale of chunk pi, group (lane / 2) % 4 of this lane's K-block (this lane evaluated it)
-        if (t.kon && t.r0 + pi < rows && !((redo >> (pb + pi)) & 1u)) reinterpret_cast<float *>(yb + pi * 144)[(lane >> 1) & 3] = d;
+        if (t.kon && t.r0 + pi < rows && !((redo >> (pb + pi)) & 1u))
+            reinterpret_cast<uint32_t *>(yb + pi * 144)[(lane >> 1) & 3] = LAYOUT == 0 ? __float_as_uint(d) : (pi ? hdr2[1] : hdr2[0]);
         // exact recomputation of the flagged groups: the whole warp, one lane per value (uniform: redo is the same in every lane)
         for (uint32_t m = redo; m; m &= m - 1) {
             const int bit = __ffs(m) - 1, j = bit >> 1, c = bit & 1;     // group j of the warp's 16: K-block j / 4, group j % 4
@@ -350,7 +389,16 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
                 de = fdiv(1.0f, di);
             }
             blk[16 + (j & 3) * 32 + lane] = (uint8_t)code;
-            if (lane == 0) reinterpret_cast<float *>(blk)[j & 3] = de;
+            if constexpr (LAYOUT == 0) { if (lane == 0) reinterpret_cast<float *>(blk)[j & 3] = de; }
+            else {      // the sum in the reference's order: ((x0 + x1) + x2) + x3 in the first lane of four, then the eight quads' partners 4, 2, 1
+                float sq = fadd(x, __shfl_down_sync(CAM_FULL, x, 1));
+                sq = fadd(sq, __shfl_down_sync(CAM_FULL, x, 2));
+                sq = fadd(sq, __shfl_down_sync(CAM_FULL, x, 3));
+                sq = fadd(sq, __shfl_xor_sync(CAM_FULL, sq, 16));
+                sq = fadd(sq, __shfl_xor_sync(CAM_FULL, sq, 8));
+                sq = fadd(sq, __shfl_xor_sync(CAM_FULL, sq, 4));
+                if (lane == 0) reinterpret_cast<uint32_t *>(blk)[j & 3] = f2_to_h2(de, sq);
+            }
         }
         if (PF) {
 #pragma unroll
@@ -368,12 +416,13 @@ int launch_mmq(const void * x, const void * u, void * y, int kvalid, int Kpad, l
     const int elt = MODE == 2 ? 8 : 16;
     if ((reinterpret_cast<uintptr_t>(x) & (elt - 1)) || (u && (reinterpret_cast<uintptr_t>(u) & (elt - 1))) || !cam_aligned16(y)) return CAM_ERR_ALIGN;
     if (rows == 0) return CAM_OK;
-    if (MODE != 0 && layout == 0 && !(kvalid & 15) && !(ld & 7) && cam_aligned16(x) && cam_aligned16(u)) {
+    if (MODE != 0 && !(kvalid & 15) && !(ld & 7) && cam_aligned16(x) && cam_aligned16(u)) {
         const long nx = ((rows + 1) / 2 + 7) / 8, ny = (Kpad / 128 + 3) / 4;
-        if (MODE == 2) mmq_swiglu_fast_kernel<uint16_t, true><<<mmq_grid(mmq_swiglu_fast_kernel<uint16_t, true>, nx, ny), 256, 0, stream>>>(
-                (const uint16_t *)x, (const uint16_t *)u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
-        else mmq_swiglu_fast_kernel<float, false><<<mmq_grid(mmq_swiglu_fast_kernel<float, false>, nx, ny), 256, 0, stream>>>(
-                (const float *)x, (const float *)u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
+#define CAM_MMQ_FAST(TT, PF, LAY) mmq_swiglu_fast_kernel<TT, PF, LAY><<<mmq_grid(mmq_swiglu_fast_kernel<TT, PF, LAY>, nx, ny), 256, 0, stream>>>( \
+                (const TT *)x, (const TT *)u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows)
+        if (MODE == 2) { if (layout == 0) CAM_MMQ_FAST(uint16_t, true, 0); else CAM_MMQ_FAST(uint16_t, true, 1); }
+        else { if (layout == 0) CAM_MMQ_FAST(float, false, 0); else CAM_MMQ_FAST(float, false, 1); }
+#undef CAM_MMQ_FAST
         return (int)cudaGetLastError();
     }
     const long ny = (Kpad / 128 + 31) / 32;

@@ -249,10 +249,11 @@ def test_mmq_q8_1(layout, rows, K):
     assert same(fused, gguf.quantize_mmq_q8_1(cu(h), layout))
 
 
+@pytest.mark.parametrize('layout', ['D4', 'DS4'])
 @pytest.mark.parametrize('dt', [np.float16, np.float32])
 @pytest.mark.parametrize('rows,K,kvalid', [(1, 128, 128), (3, 384, 384), (6, 640, 592), (13, 1024, 1024), (5, 896, 888), (64, 2560, 2560)])
-def test_swiglu_mmq_hard_inputs(dt, rows, K, kvalid):
-    """the D4 fast pass: every byte is the exact statements' byte on inputs built to sit on its margins: duplicated and nearly
+def test_swiglu_mmq_hard_inputs(layout, dt, rows, K, kvalid):
+    """the D4 and DS4 fast passes: every byte is the exact statements' byte on inputs built to sit on its margins: duplicated and nearly
     equal maxima, products on rounding boundaries, gates below -8, zero groups, tiny and huge values, NaN and infinities; odd
     K-block counts, row counts that do not fill a warp's four rows, kvalid below K"""
     from caminus_b200.engine import gguf
@@ -270,21 +271,28 @@ def test_swiglu_mmq_hard_inputs(dt, rows, K, kvalid):
     # halves of the maximum: codes on the .5 boundaries
     h = oracle.swiglu_f32_from_f16(g.reshape(-1), u.reshape(-1)).reshape(rows, K) if dt == np.float16 else None
     Kp = (K + 127) // 128 * 128
-    got = gguf.quantize_mmq_q8_1(cu(g), 'D4', u=cu(u), kvalid=kvalid)
-    assert same(got, oracle.mmq_q8_1(g, kvalid, Kp, 0, u=u))
-    if h is not None and kvalid == K: assert same(got, gguf.quantize_mmq_q8_1(cu(h), 'D4'))
+    got = gguf.quantize_mmq_q8_1(cu(g), layout, u=cu(u), kvalid=kvalid)
+    want = oracle.mmq_q8_1(g, kvalid, Kp, gguf.MMQ_LAYOUTS[layout], u=u)
+    if layout == 'DS4':                                                            # (a NaN sum or scale has the arithmetic unit's payload)
+        gb, wb = bits(got).reshape(-1, 144), bits(want).reshape(-1, 144)
+        gh, wh = gb[:, :16].copy().view(np.uint16), wb[:, :16].copy().view(np.uint16)
+        nan = (wh & 0x7fff) > 0x7c00
+        assert np.array_equal(gb[:, 16:], wb[:, 16:]) and np.array_equal(gh[~nan], wh[~nan]) and ((gh[nan] & 0x7fff) > 0x7c00).all()
+    else: assert same(got, want)
+    if h is not None and kvalid == K and not np.isnan(h).any(): assert same(got, gguf.quantize_mmq_q8_1(cu(h), layout))
 
 
-def test_swiglu_mmq_fast_equals_unfused_large():
-    """2048 x 25600 fp16 values: the fused D4 blocks equal the plain quantiser's over gg_silu_mul's fp32 products (both the exact
+@pytest.mark.parametrize('layout', ['D4', 'DS4'])
+def test_swiglu_mmq_fast_equals_unfused_large(layout):
+    """2048 x 25600 fp16 values: the fused D4 / DS4 blocks equal the plain quantiser's over gg_silu_mul's fp32 products (both the exact
     statements for every value), byte for byte"""
     from caminus_b200.engine import gguf
     gen = torch.Generator(device=DEV); gen.manual_seed(5)
     T, K = 2048, 25600
     g = (torch.randn(T, K, device=DEV, generator=gen) * 1.5).half(); u = torch.randn(T, K, device=DEV, generator=gen).half()
-    fused = gguf.quantize_mmq_q8_1(g, 'D4', u=u)
+    fused = gguf.quantize_mmq_q8_1(g, layout, u=u)
     h = gguf.silu_mul(g.float().reshape(-1), u.float().reshape(-1)).reshape(T, K)
-    assert torch.equal(fused, gguf.quantize_mmq_q8_1(h, 'D4'))
+    assert torch.equal(fused, gguf.quantize_mmq_q8_1(h, layout))
 
 
 @pytest.mark.parametrize('layout', [0, 1])
