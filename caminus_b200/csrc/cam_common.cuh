@@ -100,7 +100,10 @@ template <bool NANQ> CAM_DEV uint32_t bf16_soft(float f) {
 template <bool NANQ> CAM_DEV uint32_t bf16x2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    if (lo != lo || hi != hi) r = bf16_soft<NANQ>(lo) | (bf16_soft<NANQ>(hi) << 16);
+    if (NANQ) {      // (two predicated selects, no branch: a branch per pair kept the compiler from batching a row's loads and stores)
+        if (lo != lo) r = (r & 0xffff0000u) | 0x7fc0u;
+        if (hi != hi) r = (r & 0x0000ffffu) | 0x7fc00000u;
+    } else if (lo != lo || hi != hi) r = bf16_soft<NANQ>(lo) | (bf16_soft<NANQ>(hi) << 16);
     return r;
 }
 
