@@ -217,6 +217,7 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) rms_rows_vec_kernel(float * x,
                 *reinterpret_cast<float4 *>(xr + 128 * m) = xv[m];
             }
         }
+        unsigned long long redo = 0;                           // Q8: bit m: this lane's four values of chunk m take the exact statements
         float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
         for (int m = 0; m < CH; m++) {
@@ -255,20 +256,39 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) rms_rows_vec_kernel(float * x,
                     c[e] = __float_as_uint(ffma(vv[e], inv_hi, 12582912.0f));
                     differ |= c[e] ^ __float_as_uint(ffma(vv[e], inv_lo, 12582912.0f));
                 }
-                uint32_t word = __byte_perm(__byte_perm(c[0], c[1], 0x0040), __byte_perm(c[2], c[3], 0x0040), 0x5410);
+                const uint32_t word = __byte_perm(__byte_perm(c[0], c[1], 0x0040), __byte_perm(c[2], c[3], 0x0040), 0x5410);
                 const float mag = fadd(fadd(fabsf(v.x), fabsf(v.y)), fadd(fabsf(v.z), fabsf(v.w)));
-                if (differ != 0 || !(d >= 1.0e-30f) || !(mag < 3.0e38f)) {      // the exact statements for this lane's four values
-                    word = 0;
+                if (differ != 0 || !(d >= 1.0e-30f) || !(mag < 3.0e38f)) redo |= 1ull << m;      // (settled after the row: no branch among the row's loads and stores)
+                uint32_t * blk = reinterpret_cast<uint32_t *>(yq + ((size_t)t * (K / 32) + 4 * m + (lane >> 3)) * 36);
+                blk[1 + (lane & 7)] = word;
+                if ((lane & 7) == 0) __stcs(blk, f2_to_h2(d, sum));
+            }
+        }
+        if (Q8) {      // the exact statements for a flagged lane's four values of a chunk (about one row in ten has one), stored over the fast word
+            unsigned long long any = __reduce_or_sync(CAM_FULL, (uint32_t)redo);
+            if (CH > 32) any |= (unsigned long long)__reduce_or_sync(CAM_FULL, (uint32_t)(redo >> 32)) << 32;
+            while (any) {                                       // (uniform: the chunk's eight lanes find its amax together)
+                const int m = __ffsll((long long)any) - 1;
+                any &= any - 1;
+                float4 xm = xv[0];
+#pragma unroll
+                for (int k = 1; k < CH; k++) if (k == m) xm = xv[k];
+                const float4 ww = __ldg(reinterpret_cast<const float4 *>(wv + 128 * m));
+                const float vv[4] = {fmul(fmul(xm.x, scale), ww.x), fmul(fmul(xm.y, scale), ww.y), fmul(fmul(xm.z, scale), ww.z), fmul(fmul(xm.w, scale), ww.w)};
+                float amax = fmaxf(fmaxf(fabsf(vv[0]), fabsf(vv[1])), fmaxf(fabsf(vv[2]), fabsf(vv[3])));
+#pragma unroll
+                for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, o));
+                if ((redo >> m) & 1ull) {
+                    const float d = fdiv(amax, 127.0f);
+                    uint32_t word = 0;
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
                         const float qv = fdiv(vv[e], d);
                         const int q = (amax != 0.0f && fabsf(qv) < 127.5f) ? __float2int_rn(roundf(qv)) : 0;
                         word |= (uint32_t)(q & 0xff) << (8 * e);
                     }
+                    reinterpret_cast<uint32_t *>(yq + ((size_t)t * (K / 32) + 4 * m + (lane >> 3)) * 36)[1 + (lane & 7)] = word;
                 }
-                uint32_t * blk = reinterpret_cast<uint32_t *>(yq + ((size_t)t * (K / 32) + 4 * m + (lane >> 3)) * 36);
-                __stcs(blk + 1 + (lane & 7), word);
-                if ((lane & 7) == 0) __stcs(blk, f2_to_h2(d, sum));
             }
         }
     }
