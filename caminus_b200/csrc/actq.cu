@@ -207,6 +207,15 @@ __global__ void __launch_bounds__(256) block_entry_kernel(const float * __restri
 }
 
 // ---- a warp per row (K <= 128 MAXC) ---------------------------------------------------------------------------------------------
+// one lane's four quantised values of chunk ch: clamped, packed to a 16-bit code word, dequantised to bf16
+CAM_DEV void actq_store(float (&q)[4], float s, float lo, float hi, int row, int ch, int lane, uint16_t * __restrict__ y, int K, uint16_t * __restrict__ codes) {
+#pragma unroll
+    for (int e = 0; e < 4; e++) q[e] = fminf(fmaxf(q[e], lo), hi);
+    const uint32_t pk = ((uint32_t)(int)q[0] & 0xFu) | (((uint32_t)(int)q[1] & 0xFu) << 4) | (((uint32_t)(int)q[2] & 0xFu) << 8) | (((uint32_t)(int)q[3] & 0xFu) << 12);
+    if (y) st64(y + (size_t)row * K + ch * 128 + lane * 4, make_uint2(bf16x2<true>(fmul(q[0], s), fmul(q[1], s)), bf16x2<true>(fmul(q[2], s), fmul(q[3], s))));
+    if (codes) codes[(size_t)row * (K / 4) + ch * 32 + lane] = (uint16_t)pk;
+}
+
 // the codes, values and scale of a row whose transformed chunks u[c] (c < nch) are in the warp's registers
 template <int MAXC>
 CAM_DEV void actq_emit(const uint2 (&up)[MAXC], float amax, int nch, int row, int lane, uint16_t * __restrict__ y, float * __restrict__ s_out, int K,
@@ -221,7 +230,8 @@ CAM_DEV void actq_emit(const uint2 (&up)[MAXC], float amax, int nch, int row, in
     const float inv = rcp_approx(s);
     const float inv_hi = fmul(inv, 0x1.000008p+0f), inv_lo = fmul(inv, 0x1.fffff0p-1f);
     const bool fast = s < 3.0e38f && fmul(amax, inv) < 4.0e6f;                 // (s >= 1e-8; false for a NaN)
-#pragma unroll
+    uint32_t redo = 0;                                   // bit c: this lane's four values of chunk c take the division (settled after the loop:
+#pragma unroll                                           //  a branch per chunk kept the compiler from batching the row's stores)
     for (int c = 0; c < MAXC; c++)
         if (c < nch) {
             float q[4], u[4];
@@ -233,16 +243,21 @@ CAM_DEV void actq_emit(const uint2 (&up)[MAXC], float amax, int nch, int row, in
                 q[e] = __uint_as_float(__float_as_uint(fsub(vh, 12582912.0f)) | (__float_as_uint(u[e]) & 0x80000000u));     // (rint keeps the sign of a zero)
                 slow |= vh != vl;
             }
-            if (slow) {                              // (one branch for the lane's four values)
-#pragma unroll
-                for (int e = 0; e < 4; e++) q[e] = rintf(fdiv(u[e], s));
-            }
-#pragma unroll
-            for (int e = 0; e < 4; e++) q[e] = fminf(fmaxf(q[e], lo), hi);
-            const uint32_t pk = ((uint32_t)(int)q[0] & 0xFu) | (((uint32_t)(int)q[1] & 0xFu) << 4) | (((uint32_t)(int)q[2] & 0xFu) << 8) | (((uint32_t)(int)q[3] & 0xFu) << 12);
-            if (y) st64_stream(y + (size_t)row * K + c * 128 + lane * 4, make_uint2(bf16x2<true>(fmul(q[0], s), fmul(q[1], s)), bf16x2<true>(fmul(q[2], s), fmul(q[3], s))));
-            if (codes) codes[(size_t)row * (K / 4) + c * 32 + lane] = (uint16_t)pk;
+            if (slow) redo |= 1u << c;
+            actq_store(q, s, lo, hi, row, c, lane, y, K, codes);
         }
+    while (redo) {                                       // (rare: the lane's four values divided, stored over the fast ones)
+        const int c = __ffs(redo) - 1;
+        redo &= redo - 1;
+        uint2 pk = up[0];
+#pragma unroll
+        for (int k = 1; k < MAXC; k++) if (k == c) pk = up[k];
+        float q[4], u[4];
+        unpack4(pk, u);
+#pragma unroll
+        for (int e = 0; e < 4; e++) q[e] = rintf(fdiv(u[e], s));
+        actq_store(q, s, lo, hi, row, c, lane, y, K, codes);
+    }
 }
 
 template <typename Src, int MAXC>
