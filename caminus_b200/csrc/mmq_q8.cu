@@ -329,11 +329,11 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
         }
         uint32_t hdr2[2] = {0u, 0u};
         uint8_t * const yb = y + ((size_t)t.kb * rows + t.r0) * 144;           // row r0's block of this lane's K-block
-        uint32_t redo = 0;                                            // bit 2 j + c: group j (of the warp's 16) of chunk c is recomputed
+        uint32_t redo = 0, resum = 0;                                 // bit 2 j + c: group j (of the warp's 16) of chunk c is recomputed / only its sum is
 #pragma unroll
         for (int c = 0; c < 2; c++) {
             float inv_hi, inv_lo;
-            bool open = (bad >> c) & 1u;
+            bool open = (bad >> c) & 1u, sum_open = false;       // (sum_open alone: scale and codes are proven, only the sum is recomputed)
             if constexpr (LAYOUT == 0) {
                 const float di = __shfl_sync(CAM_FULL, d_inv, pb + c);
                 inv_hi = fmul(di, 0x1.00001cp+0f); inv_lo = fmul(di, 0x1.ffffc8p-1f);              // 1 +- 1.67e-6
@@ -342,8 +342,8 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
                 inv_hi = fmul(di, 0x1.000036p+0f); inv_lo = fmul(di, 0x1.ffff94p-1f);              // 1 +- 3.2e-6
                 const int low = (int)(__float_as_uint(dh) & 0x1fffu) - 0x1000;
                 const float margin = fmul(sab2[c], 2.3e-6f);
-                open = open || !(dh >= 6.2e-5f && dh < 6.0e4f) || (low >= -44 && low <= 44) || !(fabsf(sum2[c]) < 3.0e38f) ||
-                       __half_as_ushort(__float2half_rn(fsub(sum2[c], margin))) != __half_as_ushort(__float2half_rn(fadd(sum2[c], margin)));
+                open = open || !(dh >= 6.2e-5f && dh < 6.0e4f) || (low >= -44 && low <= 44) || !(fabsf(sum2[c]) < 3.0e38f);
+                sum_open = __half_as_ushort(__float2half_rn(fsub(sum2[c], margin))) != __half_as_ushort(__float2half_rn(fadd(sum2[c], margin)));
                 hdr2[c] = f2_to_h2(dh, sum2[c]);
             }
             uint32_t v[16], differ = 0;
@@ -356,6 +356,10 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
             const uint32_t mask = __ballot_sync(CAM_FULL, (differ != 0 || open) && on);
             const uint32_t pair = (mask | (mask >> 1)) & 0x55555555u;
             redo |= pair << c;
+            if constexpr (LAYOUT == 1) {
+                const uint32_t ms = __ballot_sync(CAM_FULL, sum_open && on);
+                resum |= ((ms | (ms >> 1)) & 0x55555555u & ~pair) << c;
+            }
             if (on && !((pair >> pb) & 1u)) {
                 uint4 w;
                 w.x = __byte_perm(__byte_perm(v[0], v[1], 0x0040), __byte_perm(v[2], v[3], 0x0040), 0x5410);
@@ -366,8 +370,26 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
             }
         }
         // the scale of chunk pi, group (lane / 2) % 4 of this lane's K-block (this lane evaluated it)
-        if (t.kon && t.r0 + pi < rows && !((redo >> (pb + pi)) & 1u))
+        if (t.kon && t.r0 + pi < rows && !(((redo | resum) >> (pb + pi)) & 1u))
             reinterpret_cast<uint32_t *>(yb + pi * 144)[(lane >> 1) & 3] = LAYOUT == 0 ? __float_as_uint(d) : (pi ? hdr2[1] : hdr2[0]);
+        // DS4 groups whose scale and codes are proven and whose sum is not: the exact values' sum in the reference's order, one lane per value
+        for (uint32_t m = resum; m; m &= m - 1) {
+            const int bit = __ffs(m) - 1, j = bit >> 1, c = bit & 1;
+            const int kbj = kq_now * 4 + (j >> 2), kj = kbj * 128 + (j & 3) * 32 + lane;
+            float x = 0.0f;
+            if (kj < kvalid) {
+                const size_t at = (size_t)(t.r0 + c) * ld + kj;
+                x = fmul(cam_silu(Load8<T>::one(g + at)), Load8<T>::one(u + at));
+            }
+            float sq = fadd(x, __shfl_down_sync(CAM_FULL, x, 1));
+            sq = fadd(sq, __shfl_down_sync(CAM_FULL, x, 2));
+            sq = fadd(sq, __shfl_down_sync(CAM_FULL, x, 3));
+            sq = fadd(sq, __shfl_xor_sync(CAM_FULL, sq, 16));
+            sq = fadd(sq, __shfl_xor_sync(CAM_FULL, sq, 8));
+            sq = fadd(sq, __shfl_xor_sync(CAM_FULL, sq, 4));
+            const uint32_t hd = __shfl_sync(CAM_FULL, c ? hdr2[1] : hdr2[0], 2 * j);      // the group's proven fp16 scale (its pair's even lane)
+            if (lane == 0) reinterpret_cast<uint32_t *>(y + ((size_t)kbj * rows + t.r0 + c) * 144)[j & 3] = (hd & 0xffffu) | ((uint32_t)__half_as_ushort(__float2half_rn(sq)) << 16);
+        }
         // exact recomputation of the flagged groups: the whole warp, one lane per value (uniform: redo is the same in every lane)
         for (uint32_t m = redo; m; m &= m - 1) {
             const int bit = __ffs(m) - 1, j = bit >> 1, c = bit & 1;     // group j of the warp's 16: K-block j / 4, group j % 4
