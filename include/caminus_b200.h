@@ -107,7 +107,7 @@ int gg_quantize_q8_1(const float * x, void * y, int n, void * stream);
  * statements for every value (the sums are exact too) at about half the throughput. */
 int gg_swiglu_q8_1(const float * x, const float * mul, void * y, long n, void * stream);
 int gg_swiglu_q8_1_f16(const void * g, const void * u, void * y, long n, void * stream);
-/* the same with the block sum proven as well: all 36 bytes of every block are the exact statements', at about 70 % of the copy bandwidth */
+/* the same with the block sum proven as well: all 36 bytes of every block are the exact statements', at about three quarters of the copy bandwidth */
 int gg_swiglu_q8_1_sums(const float * x, const float * mul, void * y, long n, void * stream);
 int gg_swiglu_q8_1_f16_sums(const void * g, const void * u, void * y, long n, void * stream);
 int gg_swiglu_q8_1_strict(const float * x, const float * mul, void * y, long n, void * stream);
