@@ -282,11 +282,18 @@ __global__ void __launch_bounds__(256) to_bf16_vec_kernel(const float * __restri
 
 // silu_mul_bf16 over items of eight elements: item i is row i / H8, columns 8 (i % H8) .. of the rows [g | u] (H8 = H / 8)
 __global__ void __launch_bounds__(256) silu_mul_bf16_vec_kernel(const uint16_t * __restrict__ gu, uint16_t * __restrict__ act, unsigned H8, unsigned items) {
-    const unsigned stride = gridDim.x * 256u;
-    for (unsigned i = blockIdx.x * 256u + threadIdx.x; i < items; i += stride) {
-        const unsigned r = i / H8, c8 = i - r * H8;
-        const uint4 gw = ldg128(gu + ((size_t)r * 2 * H8 + c8) * 8), uw = ldg128(gu + ((size_t)r * 2 * H8 + H8 + c8) * 8);
+    const unsigned stride = gridDim.x * 256u, sdiv = stride / H8, smod = stride - sdiv * H8;
+    unsigned i = blockIdx.x * 256u + threadIdx.x;
+    if (i >= items) return;
+    unsigned r = i / H8, c8 = i - r * H8;                              // (divided once: the next item's row and column follow by addition)
+    uint4 gw = ldg128(gu + ((size_t)r * 2 * H8 + c8) * 8), uw = ldg128(gu + ((size_t)r * 2 * H8 + H8 + c8) * 8);
+    for (; i < items; i += stride) {
         const uint32_t gs[4] = {gw.x, gw.y, gw.z, gw.w}, us[4] = {uw.x, uw.y, uw.z, uw.w};
+        r += sdiv; c8 += smod;
+        if (c8 >= H8) { c8 -= H8; r++; }
+        if (i + stride < items) {                                      // the next item's loads fly during this item's arithmetic
+            gw = ldg128(gu + ((size_t)r * 2 * H8 + c8) * 8); uw = ldg128(gu + ((size_t)r * 2 * H8 + H8 + c8) * 8);
+        }
         float gv[8];
 #pragma unroll
         for (int k = 0; k < 4; k++) { const float2 g = bf16x2_f(gs[k]); gv[2 * k] = g.x; gv[2 * k + 1] = g.y; }
