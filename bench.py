@@ -8,8 +8,11 @@ launches. Every rank (one process per GPU; torchrun for N > 1) processes T = 655
 so there is no data-path collective and the scaling is weak. `value` = rows of all ranks / the slowest rank's device time
 with inputs resident in HBM; `e2e` = the same through the host-buffer call (pinned host inputs copied in, outputs copied
 back, inside the timed region). `roofline` is for the dominant kernel (SwiGLU + Q8_1) from CUDA events recorded around it in
-the timed steps. `cpu_baseline` is the CPU oracle on a bounded sample of rows on this box's host cores.
---impl reference times the CPU implementation alone. --ops adds one line per single-op config to stderr-free JSON key "ops".
+the timed steps. `cpu_baseline` is the CPU oracle on a bounded sample of rows on this box's host cores. `ops` holds the four
+single-op workloads (add + RMSNorm fp32 at hidden 2048 for T = 1 and T = 65536, q/k norm + RoPE at T = 4096, SwiGLU + Q8_1 at
+T = 8192, Q4_K rows 16384 x 2048) with their GB/s; --ops adds one entry per further op of the library.
+--impl reference times the CPU implementations alone: the C restatement of the kernels on all host threads (the line's value) and
+the NumPy restatement of the reference's host path, op by op, on one core (`cpu_baseline_numpy`).
 """
 import argparse
 import json
@@ -27,8 +30,8 @@ import numpy as np   # noqa: E402
 
 T_PER_GPU, HIDDEN, NH, NKV, INTER = 65536, 5120, 64, 8, 25600
 BYTES_PER_TOKEN = {'add_rms_f16': 4 * HIDDEN * 2, 'qk_rope_f16': (NH + NKV) * 128 * 2 * 2, 'swiglu_q8_1_f16': 2 * INTER * 2 + INTER // 32 * 36}
-# DRAM bytes per token row of the dominant kernel, from one ncu capture at T = 8192 (profiles/swiglu_q8_fast_kernel_T8192_I25600.md:
-# dram__bytes_read.sum + dram__bytes_write.sum = 838.95 + 217.91 MB); the traffic grows in proportion to the rows, so a launch
+# DRAM bytes per token row of the dominant kernel, from one ncu capture of swiglu_q8_fast_kernel at T = 8192, I = 25600
+# (dram__bytes_read.sum + dram__bytes_write.sum = 838.95 + 217.91 MB); the traffic grows in proportion to the rows, so a launch
 # of T rows is scaled from it
 SWIGLU_DRAM_BYTES_PER_TOKEN = (838_906_880 + 216_342_016) / 8192
 METRIC = 'per-layer glue throughput (residual add + RMSNorm -> q/k norm + RoPE -> SwiGLU + Q8_1), tokens/s'
@@ -109,6 +112,26 @@ class Clocks:
         return {'sm_mhz': float(np.median(sm)), 'sm_max_mhz': float(max(mx)), 'reasons': sorted(reasons), 'samples': len(sm), 'via': 'nvidia-smi'}
 
 
+def host_mem_available():
+    """bytes of host memory the kernel counts as available (/proc/meminfo MemAvailable), capped by the cgroup's limit when one is set; 0 if unknown"""
+    avail = 0
+    try:
+        for ln in open('/proc/meminfo'):
+            if ln.startswith('MemAvailable:'): avail = int(ln.split()[1]) * 1024
+    except OSError:
+        return 0
+    for pth, used in (('/sys/fs/cgroup/memory.max', '/sys/fs/cgroup/memory.current'),
+                      ('/sys/fs/cgroup/memory/memory.limit_in_bytes', '/sys/fs/cgroup/memory/memory.usage_in_bytes')):
+        try:
+            lim = open(pth).read().strip()
+            if lim.isdigit() and int(lim) < 1 << 60:
+                left = int(lim) - int(open(used).read().strip())
+                avail = min(avail, left) if avail else left
+        except (OSError, ValueError):
+            pass
+    return max(avail, 0)
+
+
 def cpu_layer_glue(sample, threads):
     """the CPU oracle over `sample` rows of the same workload: seconds for one pass"""
     import oracle
@@ -123,9 +146,35 @@ def cpu_layer_glue(sample, threads):
     return time.perf_counter() - t0
 
 
+def numpy_path_times(rows=64, reps=3):
+    """the NumPy restatement of the reference's host path (oracle/numpy_path.py), op by op on one core: tokens/s (rows/s) of each op
+    on `rows` token rows of the benchmarked shapes, best of `reps`"""
+    from oracle import numpy_path as NP
+    from caminus_b200 import synth
+    def best(fn):
+        fn(); ts = []
+        for _ in range(reps): t0 = time.perf_counter(); fn(); ts.append(time.perf_counter() - t0)
+        return min(ts)
+    x0, r0, w = synth.add_rms_inputs(rows, HIDDEN, dtype=np.float16); q0, k0 = synth.qk_inputs(rows, NH, NKV); g0, u0 = synth.swiglu_inputs(rows, INTER)
+    par = synth.rope_par(); pos = np.arange(rows)
+    t_add = best(lambda: NP.add_rms_f32(x0, r0, w)); t_swi = best(lambda: NP.swiglu_q8_1(g0.reshape(-1), u0.reshape(-1)))
+    t_qk = best(lambda: (NP.qk_norm_rope_f64(q0, par[:128], pos), NP.qk_norm_rope_f64(k0, par[128:256], pos)))
+    g = np.random.default_rng(0); vocab, nrow = 4096, 1024
+    W = g.integers(0, 256, (vocab, 8, 144), dtype=np.uint8); W[:, :, 0:4] = np.abs(g.standard_normal((vocab, 8, 2)) * 1e-3).astype(np.float16).view(np.uint8).reshape(vocab, 8, 4)
+    ids = g.integers(0, vocab, nrow).astype(np.int32)
+    t_q4k = best(lambda: NP.q4k_rows(W, ids))
+    x1 = g.standard_normal((1, 2048)).astype(np.float32); d1 = g.standard_normal((1, 2048)).astype(np.float32); w1 = (1 + 0.05 * g.standard_normal(2048)).astype(np.float32)
+    t_one = best(lambda: NP.add_rms_f32(x1, d1, w1))
+    return {'value': rows / (t_add + t_qk + t_swi), 'unit': 'tokens/s', 'cores': 1, 'kind': 'reference host path restated in NumPy (float32 norm, float64 rotation, Q8_1 and Q4_K as its decoders define them)',
+            'sample': f'{rows} token rows per op ({nrow} rows for the Q4_K gather), best of {reps}',
+            'per_op': {'add_rms_f16_h5120_tokens_per_s': rows / t_add, 'qk_rope_72heads_tokens_per_s': rows / t_qk, 'swiglu_q8_1_I25600_tokens_per_s': rows / t_swi,
+                       'q4k_get_rows_2048_rows_per_s': nrow / t_q4k, 'add_rms_f32_h2048_T1_us': t_one * 1e6}}
+
+
 def run_reference(args, rank):
-    """the reference arm: the path's CPU implementation (the C restatement of the reference's kernels: its HIP sources do not
-    compile for a CPU) on this box's host cores, all threads, a bounded sample of the workload per step"""
+    """the reference arm: the path's CPU implementations on this box's host cores, a bounded sample of the workload per step. The
+    line's value is the C restatement of the reference's kernels (its HIP sources do not compile for a CPU) on all host threads;
+    `cpu_baseline_numpy` is the NumPy restatement of the reference's own host path on one core"""
     if rank != 0: return
     import oracle
     oracle.build()
@@ -134,20 +183,26 @@ def run_reference(args, rank):
     for _ in range(args.warmup): cpu_layer_glue(sample, threads)
     ts = [cpu_layer_glue(sample, threads) for _ in range(args.steps)]
     sec = float(np.mean(ts)); val = sample / sec
+    try: npy = numpy_path_times()
+    except Exception as e: npy = {'unavailable': f'{type(e).__name__}: {e}'[:200]}
     print(json.dumps({
         'impl': 'reference', 'metric': METRIC, 'value': val, 'unit': 'tokens/s', 'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup,
         'ms_per_step': sec * 1e3, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-        'config': {'workload': f'per-layer glue, Qwen3-32B shape (BASELINE config 5): hidden {HIDDEN}, {NH} q + {NKV} kv heads x 128, '
+        'config': {'workload': f'per-layer glue, Qwen3-32B shape: hidden {HIDDEN}, {NH} q + {NKV} kv heads x 128, '
                                f'intermediate {INTER}, fp16 storage', 'rows_per_step': sample},
         'cpu_baseline': {'value': val, 'unit': 'tokens/s', 'cores': threads, 'kind': 'port',
                          'sample': f'{sample} token rows per step through all three ops (the C oracle, rows split over {threads} host threads)'},
+        'cpu_baseline_numpy': npy,
         'e2e': {'value': val, 'unit': 'tokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0}), flush=True)
 
 
-def single_op_lines(torch, dev, peak, only=()):
-    """device-resident GB/s of the single-op configs 1-4 (median of 20 event-timed launches; buffers rotated where a
-    config's data would fit in L2)"""
+HEADLINE_OPS = ('add_rms16_f32_h2048_T1', 'add_rms16_f32_h2048_T65536', 'qk_rope_f16_T4096', 'swiglu_q8_1_f16_T8192', 'q4k_get_rows_16384x2048')
+
+
+def single_op_lines(torch, dev, peak, only=(), headline=False):
+    """device-resident GB/s of the single-op workloads (median over batches of event-timed launches; buffers rotated where a
+    workload's data would fit in L2). headline: only the four workloads the metric is quoted on (HEADLINE_OPS)"""
     from caminus_b200 import glue, synth
     from caminus_b200.engine import gguf
     from caminus_b200.prefill import q3m_ops
@@ -186,6 +241,7 @@ def single_op_lines(torch, dev, peak, only=()):
             return f'{type(e).__name__}: {e}'[:160]
 
     def line(name, nbytes, sec, units, unit):
+        if headline and name not in HEADLINE_OPS: return
         if only and not any(o in name for o in only): return
         med, mn = sec()
         out[name] = {'bytes': nbytes, 'us_median': med * 1e6, 'us_min': mn * 1e6, 'gbs': nbytes / med / 1e9, 'frac_of_peak': nbytes / med / 1e9 / peak,
@@ -193,7 +249,7 @@ def single_op_lines(torch, dev, peak, only=()):
 
     g = torch.Generator(device=dev); g.manual_seed(0)
     # config 1: add + RMSNorm fp32, hidden 2048: T = 1 (latency) and a T sweep
-    for T in (1, 64, 4096, 65536):
+    for T in ((1, 65536) if headline else (1, 64, 4096, 65536)):
         rot = 8 if T <= 4096 else 1
         xs = [torch.randn(T, 2048, device=dev, generator=g) for _ in range(rot)]; d = torch.randn(T, 2048, device=dev, generator=g)
         nw = 1 + 0.05 * torch.randn(2048, device=dev, generator=g); h = torch.empty(T, 2048, device=dev); h16 = torch.empty(T, 2048, dtype=torch.float16, device=dev)
@@ -202,6 +258,10 @@ def single_op_lines(torch, dev, peak, only=()):
         if T == 1 and f'add_rms16_f32_h2048_T{T}' in out:
             gs = graphed(lambda i: O.add_rms16(xs[i % rot], nw, 1e-6, h16, T, 2048, d=d, S=1, h=h))
             out[f'add_rms16_f32_h2048_T{T}']['us_in_cuda_graph'] = gs * 1e6 if isinstance(gs, float) else gs
+            torch.cuda.synchronize(dev); t0 = time.perf_counter()            # the host's cost of one call through the loader interface
+            for i in range(2000): O.add_rms16(xs[i % rot], nw, 1e-6, h16, T, 2048, d=d, S=1, h=h)
+            host_s = (time.perf_counter() - t0) / 2000; torch.cuda.synchronize(dev)
+            out[f'add_rms16_f32_h2048_T{T}']['us_per_call_host'] = host_s * 1e6
         del xs, d, h, h16
     # config 2: q/k norm + RoPE fp16, T = 4096, 32 + 4 heads (75 MB: 4 rotating copies)
     T = 4096
@@ -225,6 +285,7 @@ def single_op_lines(torch, dev, peak, only=()):
     xo = [torch.empty(n, N, device=dev) for _ in range(2)]
     line('q4k_get_rows_16384x2048', n * (4 + 1152 + 8192), timed(lambda i: O.emb(W.view(-1), 1152, vocab, toks, xo[i], n, N), rot=2), n, 'rows_per_s')
     del W, toks, xo
+    if headline: return out
     # ---- the later rows of the path (hyper-connection glue, MMQ layout, Q8_0 KV form, the training line's quantiser) ----
     import ctypes
     from caminus_b200.prefill import glue as PG
@@ -359,12 +420,12 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--rows', type=int, default=T_PER_GPU, help='token rows per GPU (the configured workload is 65536)')
     ap.add_argument('--e2e-chunk', type=int, default=1024, help='rows per chunk of the host-buffer pass (two chunks in flight)')
-    ap.add_argument('--ops', action='store_true', help='also time the single-op configs 1-4 on rank 0')
+    ap.add_argument('--ops', action='store_true', help='time every op of the library on rank 0, not only the four headline workloads')
     ap.add_argument('--only', default='', help='with --ops: comma-separated substrings of the op names to time (default: all)')
     ap.add_argument('--cpu-sample', type=int, default=512)
     ap.add_argument('--skip-e2e', action='store_true', help='leave out the host-buffer leg (profiling runs)')
     ap.add_argument('--skip-cpu', action='store_true', help='leave out the CPU baseline leg (profiling runs)')
-    ap.add_argument('--e2e-rows', type=int, default=16384, help='token rows per GPU of the host-buffer leg (pinned host memory: 209 KB per row)')
+    ap.add_argument('--e2e-rows', type=int, default=0, help='token rows per GPU of the host-buffer leg (0: the whole batch if the host can pin it, 229 KB per row and rank)')
     args = ap.parse_args()
     rank, world, local = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1)), int(os.environ.get('LOCAL_RANK', 0))
     if args.impl == 'reference': return run_reference(args, rank)
@@ -416,62 +477,115 @@ def main():
     ms_per_step = total / args.steps * 1e3
     value = T * world / (total / args.steps)
 
-    # end to end through host buffers (pinned): inputs copied in, the three launches, outputs copied back, every step
     # the hidden-sharded RMSNorm (N > 1 only): this rank's hidden / N columns of all T rows, partial -> NCCL all-reduce of [T] fp32 -> apply
     tp = None
     if world > 1 and HIDDEN % (8 * world) == 0:
         from caminus_b200 import dist as D
         Ns = HIDDEN // world
-        xs = rn(T, Ns); ds = rn(T, Ns); hs = torch.empty_like(xs)
-        norm = D.TPRmsNorm(nw[:Ns].contiguous(), HIDDEN, 1e-6)
-        for _ in range(3): norm(xs, ds, hs)
-        barrier()
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-        ev[0].record()
-        for _ in range(args.steps): norm(xs, ds, hs)
-        ev[1].record(); barrier()
-        tps = ev[0].elapsed_time(ev[1]) * 1e-3 / args.steps
-        t = torch.tensor([tps], device=dev, dtype=torch.float64); torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX); tps = float(t.item())
-        tp = {'us_per_step': tps * 1e6, 'tokens_per_s': T / tps, 'hbm_gbs_per_gpu': T * 4 * Ns * 2 / tps / 1e9,
-              'nvlink_bytes_per_rank': T * 4, 'note': f'hidden {HIDDEN} in {world} shards of {Ns}; every rank holds all {T} rows'}
+        xs0 = rn(T, Ns); ds = rn(T, Ns); hs = torch.empty_like(xs0); xs = xs0.clone()
+        norm = D.TPRmsNorm(nw[rank * Ns:(rank + 1) * Ns].contiguous(), HIDDEN, 1e-6)
+
+        def all_true(flag):
+            t = torch.tensor([1 if flag else 0], device=dev, dtype=torch.int32); torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN)
+            return bool(t.item())
+
+        def timed_norm(fn):
+            for _ in range(3): fn()
+            barrier()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            ev[0].record()
+            for _ in range(args.steps): fn()
+            ev[1].record(); barrier()
+            t = torch.tensor([ev[0].elapsed_time(ev[1]) * 1e-3 / args.steps], device=dev, dtype=torch.float64)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            return float(t.item())
+
+        # the value check's reference: this rank's apply kernel on all ranks' partials added in rank order from 0.0f
+        xa = xs0.clone()
+        parts = [torch.empty(T, device=dev) for _ in range(world)]
+        torch.distributed.all_gather(parts, norm.partial(xa, ds).clone())
+        tot = torch.zeros(T, device=dev)
+        for p_ in parts: tot = tot + p_
+        h_ref = norm.apply(xa, tot, d=ds).clone()                     # (xa is now fp16(x + d))
+        xb = xs0.clone(); h_nccl = norm(xb, ds).clone()
+        rel = float(((h_nccl.float() - h_ref.float()).abs().max() / h_ref.float().abs().max()).item())
+        nccl_ok = all_true(torch.equal(xb, xa) and rel <= 1e-3)      # (fp16 outputs: one rounding step of 2^-11; the sums differ only in order)
+        tps = timed_norm(lambda: norm(xs, ds, hs))
+        tp = {'us_per_step': tps * 1e6, 'tokens_per_s': T / tps, 'hbm_gbs_per_gpu': T * 4 * Ns * 2 / tps / 1e9, 'frac_of_peak': T * 4 * Ns * 2 / tps / 1e9 / peaks()[0],
+              'nvlink_bytes_per_rank': T * 4, 'vs_rank_ordered_sum': {'x_bitwise': nccl_ok, 'h16_max_rel': rel},
+              'note': f'hidden {HIDDEN} in {world} shards of {Ns}; every rank holds all {T} rows'}
         # the same norm as one kernel per rank (partials by peer stores over NVLink, no collective call)
         try:
             fused = D.TPRmsNormFused(norm.nw, HIDDEN, T, 1e-6)
-            for _ in range(3): fused(xs, ds, hs)
-            fused.check(); barrier()
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-            ev[0].record()
-            for _ in range(args.steps): fused(xs, ds, hs)
-            ev[1].record(); barrier()
+            xc = xs0.clone(); h_f = fused(xc, ds); fused.check()
+            bitwise = all_true(torch.equal(h_f, h_ref) and torch.equal(xc, xa))
+            xc.copy_(xs0); h_f2 = fused(xc, ds); fused.check()           # the next call (the other half of the exchange buffer)
+            bitwise = all_true(torch.equal(h_f2, h_ref) and torch.equal(xc, xa)) and bitwise
+            rel_f = float(((h_f.float() - h_nccl.float()).abs().max() / h_nccl.float().abs().max()).item())
+            tf = timed_norm(lambda: fused(xs, ds, hs))
             fused.check()
-            tf = ev[0].elapsed_time(ev[1]) * 1e-3 / args.steps
-            t = torch.tensor([tf], device=dev, dtype=torch.float64); torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX); tf = float(t.item())
-            tp['fused'] = {'us_per_step': tf * 1e6, 'tokens_per_s': T / tf, 'hbm_gbs_per_gpu': T * 4 * Ns * 2 / tf / 1e9,
-                           'nvlink_bytes_per_rank': T * 8 * (world - 1), 'note': 'one launch per rank: per-row partials stored into every peer, rows normalised as they complete'}
+            tp['fused'] = {'us_per_step': tf * 1e6, 'tokens_per_s': T / tf, 'hbm_gbs_per_gpu': T * 4 * Ns * 2 / tf / 1e9, 'frac_of_peak': T * 4 * Ns * 2 / tf / 1e9 / peaks()[0],
+                           'nvlink_bytes_per_rank': T * 8 * (world - 1), 'parity': 'bitwise' if bitwise else 'MISMATCH',
+                           'vs_nccl_form_max_rel': rel_f, 'note': 'one launch per rank: per-row partials stored into every peer, rows normalised as they complete; '
+                           'parity = h16 and x equal, on every rank and on two consecutive calls, to the apply kernel on the rank-ordered sum of the all-gathered partials'}
             barrier(); fused.close(); barrier()              # (every rank has unmapped before any buffer can go)
         except Exception as e:      # (peer mapping refused on this box: keep the collective form's number)
             tp['fused'] = {'unavailable': f'{type(e).__name__}: {e}'[:200]}
-        del xs, ds, hs
+        # the fused kernel run by this rank alone on the same shard (world = 1: it waits for its own partial only): the kernel's HBM side
+        try:
+            one = D.TPRmsNormFused(norm.nw, Ns, T, 1e-6, group=D.SOLO)
+            for _ in range(3): one(xs, ds, hs)
+            torch.cuda.synchronize(dev)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            ev[0].record()
+            for _ in range(args.steps): one(xs, ds, hs)
+            ev[1].record(); ev[1].synchronize(); one.check()
+            t1 = ev[0].elapsed_time(ev[1]) * 1e-3 / args.steps
+            tp['fused_one_rank'] = {'us_per_step': t1 * 1e6, 'frac_of_peak': T * 4 * Ns * 2 / t1 / 1e9 / peaks()[0]}
+        except Exception as e:
+            tp['fused_one_rank'] = {'unavailable': f'{type(e).__name__}: {e}'[:200]}
+        barrier()
+        del xs, xs0, ds, hs, xa, xb, h_ref, h_nccl, parts, tot
 
     from caminus_b200 import host
-    Te = min(T, args.e2e_rows)
+    # rows of the host-buffer leg: the whole workload when the host can pin it for every rank (209 KB per row and rank, twice: the
+    # batch and the plain-copy check below share the buffers), else as many as a third of the available host memory holds
+    row_bytes = sum(BYTES_PER_TOKEN.values()) + HIDDEN * 2           # (the residual comes in too)
+    avail = host_mem_available()
+    fit = int(avail / 3 / world / row_bytes) // 1024 * 1024 if avail else 16384
+    Te = min(T, args.e2e_rows if args.e2e_rows > 0 else max(1024, fit))
+    rows_note = 'the whole batch' if Te == T else (f'--e2e-rows {args.e2e_rows}' if args.e2e_rows > 0 else
+                                                   f'{Te} rows: a third of the {avail / 2**30:.0f} GiB of available host memory over {world} ranks at {row_bytes} pinned bytes per row')
     e2e = None
     if not args.skip_e2e:
         Hrun = host.HostLayerGlue(Te, HIDDEN, NH, NKV, INTER, nw, par, dev, chunk=args.e2e_chunk)
         Hrun.fill_from(x, resid, q, k, gate, up)
         del gate, up, yq, h16, x, q, k, resid
         torch.cuda.empty_cache()
-        for _ in range(3): Hrun.run()
+        for _ in range(3 if Te <= 16384 else 2): Hrun.run()
         barrier()
-        e2e_steps = max(2, min(args.steps, 5))
+        e2e_steps = max(2, min(args.steps, 5 if Te <= 16384 else 3))
         t0 = time.perf_counter()
         for _ in range(e2e_steps): Hrun.run()
         barrier()
         e2e_s = (time.perf_counter() - t0) / e2e_steps
+        # the host link alone: the same pinned buffers, the same bytes, plain copies in both directions at once (no kernel), every rank
+        # at the same time: what the copies of one step cost on this box at this N
+        link_s = Hrun.copies_only()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(2): Hrun.copies_only()
+        barrier()
+        link_s = (time.perf_counter() - t0) / 2
         if world > 1:
-            t = torch.tensor([e2e_s], device=dev, dtype=torch.float64); torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX); e2e_s = float(t.item())
-        e2e = {'value': Te * world / e2e_s, 'unit': 'tokens/s', 'rows_per_gpu': Te, 'h2d_bytes_per_step': Hrun.h2d_bytes,
-               'd2h_bytes_per_step': Hrun.d2h_bytes, 'ms_per_step': e2e_s * 1e3}
+            t = torch.tensor([e2e_s, link_s], device=dev, dtype=torch.float64); torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            e2e_s, link_s = float(t[0].item()), float(t[1].item())
+        e2e = {'value': Te * world / e2e_s, 'unit': 'tokens/s', 'rows_per_gpu': Te, 'rows_note': rows_note, 'h2d_bytes_per_step': Hrun.h2d_bytes,
+               'd2h_bytes_per_step': Hrun.d2h_bytes, 'ms_per_step': e2e_s * 1e3,
+               'host_link': {'ms_copies_only': link_s * 1e3, 'h2d_gbs_per_gpu': Hrun.h2d_bytes / link_s / 1e9, 'd2h_gbs_per_gpu': Hrun.d2h_bytes / link_s / 1e9,
+                             'gbs_all_gpus_both_ways': (Hrun.h2d_bytes + Hrun.d2h_bytes) * world / link_s / 1e9,
+                             'tokens_per_s_if_only_copies': Te * world / link_s, 'frac_of_copies_only': link_s / e2e_s,
+                             'note': 'the same pinned buffers and bytes as a step, copied in and out concurrently with no kernel between, all ranks at once'}}
 
     if rank == 0:
         peak, which = peaks()
@@ -492,13 +606,13 @@ def main():
             'metric': METRIC, 'value': value, 'unit': 'tokens/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
             'ms_per_step': ms_per_step, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
             'data': 'synthetic',
-            'config': {'workload': f'per-layer glue, Qwen3-32B shape (BASELINE config 5): T = {T} token rows per GPU, hidden {HIDDEN}, {NH} q + {NKV} kv '
+            'config': {'workload': f'per-layer glue, Qwen3-32B shape: T = {T} token rows per GPU, hidden {HIDDEN}, {NH} q + {NKV} kv '
                                    f'heads x 128, intermediate {INTER}, fp16 storage, fp32 arithmetic', 'rows_per_gpu': T,
                        'parallelism': f'token rows x {world} (no collective)', 'l2': 'inputs (13.7 GB per step) larger than L2',
                        'bytes_per_token': sum(BYTES_PER_TOKEN.values())},
             'clocks': clk,
             'e2e': e2e,
-            'gpu_launches': 3 * args.steps,
+            'gpu_launches': 3 * args.steps, 'gpu_launches_note': 'the three glue kernels per timed step (the e2e, ops and tensor-parallel legs launch more, outside the timed region)',
             'roofline': {'bound': 'hbm', 'kernel': 'swiglu_q8_fast_kernel<fp16> (SwiGLU + Q8_1)', 'achieved': ach, 'peak': peak, 'unit': 'GB/s',
                          'frac': ach / peak, 'peak_source': which, 'frac_of_8tbs': ach / 8000.0, 'traffic': SWIGLU_DRAM_BYTES_PER_TOKEN * T,
                          'traffic_note': 'bytes per launch, scaled by rows from an ncu capture at T = 8192', 'algorithmic_bytes': T * BYTES_PER_TOKEN[dom]},
@@ -507,7 +621,7 @@ def main():
             'cpu_baseline': cpu,
             'tp_rmsnorm': tp,
         }
-        if args.ops: line['ops'] = single_op_lines(torch, dev, peak, tuple(o for o in args.only.split(',') if o))
+        line['ops'] = single_op_lines(torch, dev, peak, tuple(o for o in args.only.split(',') if o), headline=not args.ops)
         print(json.dumps(line), flush=True)
     if world > 1: torch.distributed.destroy_process_group()
 

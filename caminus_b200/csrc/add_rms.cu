@@ -483,7 +483,8 @@ int launch_f16(uint16_t * x, const uint16_t * d, const float * nw, float eps, ui
     if (n < 4 * warps) nw_smem = 0;                               // (a handful of rows: staging the weights costs more than it saves)
     const size_t smem = (size_t)nw_smem * 4 + per_warp * warps;
     if (smem > budget) return CAM_ERR_SHAPE;
-    const cudaError_t e = cudaFuncSetAttribute(add_rms_f16_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    static unsigned long long allowed = 0;
+    const cudaError_t e = cam_allow_smem(add_rms_f16_kernel<MODE>, 227 * 1024, allowed);
     if (e != cudaSuccess) return (int)e;
     const int grid = cam_resident_grid(add_rms_f16_kernel<MODE>, warps * 32, smem, ((long)n + warps - 1) / warps);
     add_rms_f16_kernel<MODE><<<grid, warps * 32, smem, stream>>>(x, d, nw, eps, h16, ss, tot, N, Nfull, n, warps, nw_smem);

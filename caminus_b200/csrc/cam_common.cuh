@@ -77,6 +77,17 @@ CAM_DEV void cam_sincos(float theta, float & sn, float & cs) {
     cs = ((q + 1u) & 2u) ? -c0 : c0;
 }
 
+// ---- two fp32 operations in one instruction (sm_100: fma / mul / add .f32x2 on a 64-bit register pair) ---------------------------------
+// Each half is the IEEE round-to-nearest operation of the scalar instruction (no flush to zero), so a packed statement stores the
+// bits of the two scalar statements it stands for; what changes is the instruction count of a kernel that the issue rate bounds.
+typedef unsigned long long f32x2;
+CAM_DEV f32x2 pk2(float lo, float hi) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+CAM_DEV float lo2(f32x2 v) { float a, b; asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); return a; }
+CAM_DEV float hi2(f32x2 v) { float a, b; asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); return b; }
+CAM_DEV f32x2 mul2(f32x2 a, f32x2 b) { f32x2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+CAM_DEV f32x2 add2(f32x2 a, f32x2 b) { f32x2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+CAM_DEV f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r; }
+
 // ---- fp16 <-> fp32 (the widening is exact; the narrowing rounds to nearest even) --------------------------------------------
 CAM_DEV float2 h2_to_f2(uint32_t v) { return __half22float2(*reinterpret_cast<const __half2 *>(&v)); }
 CAM_DEV uint32_t f2_to_h2(float a, float b) {
@@ -227,6 +238,18 @@ static inline int cam_resident_grid(K kernel, int threads, size_t smem, long wan
     const int per_sm = cam_blocks_per_sm(reinterpret_cast<const void *>(kernel), threads, smem);
     const long cap = (long)cam_sm_count() * per_sm;
     return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
+}
+
+// One-time, per device: a kernel's opt-in to more dynamic shared memory than the default limit. `done` is the caller's static word,
+// one bit per device ordinal: after the first launch on a device the attribute call (a driver call) is skipped.
+template <typename Kn> static inline cudaError_t cam_allow_smem(Kn kernel, size_t bytes, unsigned long long & done) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && ((__atomic_load_n(&done, __ATOMIC_ACQUIRE) >> dev) & 1ull)) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < 64) __atomic_fetch_or(&done, 1ull << dev, __ATOMIC_RELEASE);
+    return e;
 }
 
 // csrc/add_rms.cu: the warp-per-row path of the hyper-connection norms (CAM_ERR_SHAPE: does not apply to this call)

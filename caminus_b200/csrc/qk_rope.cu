@@ -231,6 +231,109 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
     cp_async_wait<0>();
 }
 
+// ---- the fp16-storage form (cam_qk_rope_f16) without a block-wide step per token -----------------------------------------------------
+// A warp owns a token and walks its heads 2 P at a time (a half-warp per head, as above), straight from global memory into registers:
+// the next round's 16 P bytes per lane are requested before the current round is computed, so a warp keeps two rounds of loads in flight
+// and nothing in the token loop waits on another warp (the staged kernel above holds a block at two barriers per token, which a batch
+// of a few thousand tokens, four or five per block, never amortises). The 64 frequencies are formed once per block (the only
+// barrier); a token's cosines and sines are formed by its warp: each half-warp computes two of a lane's four angles and the halves
+// swap. The arithmetic is written with the packed fp32 instructions where two statements run on neighbouring dims (the norm's two
+// products, the rotation): the same IEEE operations, half the instructions. Sums and statement order are the staged kernel's.
+// In place (qo = q, ko = k) is safe: a lane stores exactly the addresses it loaded, after loading them.
+template <int P>
+__global__ void __launch_bounds__(128) qk_rope_f16_warp_kernel(const RopeArgs A, int rounds) {
+    __shared__ __align__(16) float wq[128], wk[128], freq[64];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nh = A.nh, nkv = A.nkv, H = nh + nkv;
+    wq[tid] = __ldg(A.par + tid); wk[tid] = __ldg(A.par + 128 + tid);
+    if (tid < 64) freq[tid] = A.yarn ? __ldg(A.par + 258 + tid) : cam_powi(__ldg(A.par + 256), tid);
+    const float eps = __ldg(A.par + 257), mscale = A.yarn ? __ldg(A.par + 322) : 1.0f;
+    __syncthreads();
+    const int hw = lane >> 4, l16 = lane & 15;
+    const float f0 = freq[4 * l16 + 2 * hw], f1 = freq[4 * l16 + 2 * hw + 1];      // this half-warp's two of the lane's four angles
+    const uint16_t * const qin = reinterpret_cast<const uint16_t *>(A.in0), * const kin = reinterpret_cast<const uint16_t *>(A.in1);
+    const int tw = blockIdx.x * 4 + warp, stride = gridDim.x * 4;
+    const int ntok = tw < A.n ? (A.n - tw + stride - 1) / stride : 0;
+    uint2 cur[P][2], nxt[P][2];
+    auto request = [&](int kk, int rr, uint2 (&v)[P][2]) {               // round rr of this warp's token kk (nothing past its last token)
+        const int t = tw + kk * stride, h0 = rr * 2 * P;
+#pragma unroll
+        for (int p = 0; p < P; p++) {
+            const int hy = h0 + 2 * p + hw;
+            if (kk < ntok && hy < H) {
+                const uint16_t * src = (hy < nh ? qin + ((size_t)t * nh + hy) * 128 : kin + ((size_t)t * nkv + (hy - nh)) * 128) + 4 * l16;
+                v[p][0] = *reinterpret_cast<const uint2 *>(src); v[p][1] = *reinterpret_cast<const uint2 *>(src + 64);
+            } else { v[p][0] = make_uint2(0u, 0u); v[p][1] = make_uint2(0u, 0u); }
+        }
+    };
+    request(0, 0, cur);
+    f32x2 cc[2], sn[2], nsn[2];                                          // cos, sin, -sin of dims (4 l16, + 1) and (+ 2, + 3)
+    int r = 0, k = 0;
+    while (k < ntok) {
+        const int rn = r + 1 == rounds ? 0 : r + 1, kn = rn ? k : k + 1;
+        request(kn, rn, nxt);
+        const int t = tw + k * stride;
+        if (r == 0) {
+            const float pos = (float)(A.pos0 + t);
+            float s0, c0, s1, c1;
+            cam_sincos(fmul(pos, f0), s0, c0); cam_sincos(fmul(pos, f1), s1, c1);
+            if (A.yarn) { c0 = fmul(c0, mscale); s0 = fmul(s0, mscale); c1 = fmul(c1, mscale); s1 = fmul(s1, mscale); }
+            const float oc0 = __shfl_xor_sync(CAM_FULL, c0, 16), os0 = __shfl_xor_sync(CAM_FULL, s0, 16);
+            const float oc1 = __shfl_xor_sync(CAM_FULL, c1, 16), os1 = __shfl_xor_sync(CAM_FULL, s1, 16);
+            const float ca = hw ? oc0 : c0, cb = hw ? oc1 : c1, cc_ = hw ? c0 : oc0, cd = hw ? c1 : oc1;      // dims 0, 1 come from the lower half-warp
+            const float sa = hw ? os0 : s0, sb = hw ? os1 : s1, sc = hw ? s0 : os0, sd = hw ? s1 : os1;
+            cc[0] = pk2(ca, cb); cc[1] = pk2(cc_, cd); sn[0] = pk2(sa, sb); sn[1] = pk2(sc, sd); nsn[0] = pk2(-sa, -sb); nsn[1] = pk2(-sc, -sd);
+        }
+        const int h0 = r * 2 * P;
+        f32x2 xl[P][2], xh[P][2]; float tot[P];
+#pragma unroll
+        for (int p = 0; p < P; p++) {
+            const float2 a = h2_to_f2(cur[p][0].x), b = h2_to_f2(cur[p][0].y), c = h2_to_f2(cur[p][1].x), e = h2_to_f2(cur[p][1].y);
+            // the head's sum of squares: per lane an fma chain over its 4 low and its 4 high dims, then the half-warp butterfly
+            float sl = ffma(a.x, a.x, 0.0f), sh = ffma(c.x, c.x, 0.0f);
+            sl = ffma(a.y, a.y, sl); sh = ffma(c.y, c.y, sh); sl = ffma(b.x, b.x, sl); sh = ffma(e.x, e.x, sh); sl = ffma(b.y, b.y, sl); sh = ffma(e.y, e.y, sh);
+            float ss = fadd(sl, sh);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) ss = fadd(ss, __shfl_xor_sync(CAM_FULL, ss, o));
+            tot[p] = ss;
+            xl[p][0] = pk2(a.x, a.y); xl[p][1] = pk2(b.x, b.y); xh[p][0] = pk2(c.x, c.y); xh[p][1] = pk2(e.x, e.y);
+        }
+        // lane j < 2 P computes the scale of head h0 + j (pass j >> 1, half-warp j & 1); then every lane fetches its heads' scales
+        float mine = 1.0f;
+#pragma unroll
+        for (int p = 0; p < P; p++) {
+            const float v = __shfl_sync(CAM_FULL, tot[p], 16 * (lane & 1));
+            if ((lane >> 1) == p) mine = v;
+        }
+        const float scale_mine = cam_rsqrt(fadd(fmul(mine, 0.0078125f), eps));      // tot / 128: the same bits as the division
+#pragma unroll
+        for (int p = 0; p < P; p++) {
+            const float scale = __shfl_sync(CAM_FULL, scale_mine, 2 * p + hw);
+            const int hy = h0 + 2 * p + hw;
+            if (hy < H) {
+                const bool isq = hy < nh;
+                const float * wn = (isq ? wq : wk) + 4 * l16;
+                const float4 wlo = *reinterpret_cast<const float4 *>(wn), whi = *reinterpret_cast<const float4 *>(wn + 64);
+                const f32x2 s2 = pk2(scale, scale);
+                uint16_t * o = (isq ? A.out0 + ((size_t)t * nh + hy) * 128 : A.out1 + ((size_t)t * nkv + (hy - nh)) * 128) + 4 * l16;
+                uint32_t olo[2], ohi[2];
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    const f32x2 x0 = mul2(mul2(s2, xl[p][c]), c ? pk2(wlo.z, wlo.w) : pk2(wlo.x, wlo.y));
+                    const f32x2 x1 = mul2(mul2(s2, xh[p][c]), c ? pk2(whi.z, whi.w) : pk2(whi.x, whi.y));
+                    const f32x2 ylo = fma2(x0, cc[c], mul2(x1, nsn[c])), yhi = fma2(x1, cc[c], mul2(x0, sn[c]));
+                    olo[c] = f2_to_h2(lo2(ylo), hi2(ylo)); ohi[c] = f2_to_h2(lo2(yhi), hi2(yhi));
+                }
+                st64_stream(o, make_uint2(olo[0], olo[1]));
+                st64_stream(o + 64, make_uint2(ohi[0], ohi[1]));
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < P; p++) { cur[p][0] = nxt[p][0]; cur[p][1] = nxt[p][1]; }
+        r = rn; k = kn;
+    }
+}
+
 // warps per block (4 .. 12) and heads per half-warp and round (1 .. 4): the pair with the fewest idle half-warp slots over a
 // token's H heads; among equals the most heads per round (one scale computation serves 2 P heads), then the most warps
 void pick_shape(int H, int & warps, int & P) {
@@ -250,7 +353,8 @@ void pick_shape(int H, int & warps, int & P) {
 
 template <typename T, bool CACHE, int P, bool ONE, bool Q8>
 int launch_rope_p(const RopeArgs & A, int warps, size_t smem, cudaStream_t stream) {
-    const cudaError_t e = cudaFuncSetAttribute(qk_rope_kernel<T, CACHE, P, ONE, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    static unsigned long long allowed = 0;
+    const cudaError_t e = cam_allow_smem(qk_rope_kernel<T, CACHE, P, ONE, Q8>, 227 * 1024, allowed);
     if (e != cudaSuccess) return (int)e;
     const int grid = cam_resident_grid(qk_rope_kernel<T, CACHE, P, ONE, Q8>, warps * 32, smem, A.n);
     qk_rope_kernel<T, CACHE, P, ONE, Q8><<<grid, warps * 32, smem, stream>>>(A);
@@ -341,5 +445,11 @@ extern "C" int cam_qk_rope_f16(int n, const void * q, const void * k, int nh, in
     if (!cam_aligned16(q) || !cam_aligned16(qo) || (nkv > 0 && (!cam_aligned16(k) || !cam_aligned16(ko)))) return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
     const RopeArgs A = {q, k, par, (uint16_t *)qo, (uint16_t *)ko, 0, nh, nkv, pos0, n, yarn, nullptr};
-    return launch_rope<uint16_t, false>(A, (cudaStream_t)stream);
+    if (const char * e = getenv("CAMINUS_B200_ROPE_STAGED")) { if (e[0] == '1') return launch_rope<uint16_t, false>(A, (cudaStream_t)stream); }      // (tuning: the staged kernel)
+    // a warp per token, heads 6 at a time; as many blocks of four warps as the device holds at once, or as the tokens need
+    constexpr int P = 3;
+    const int rounds = (nh + nkv + 2 * P - 1) / (2 * P);
+    const int grid = cam_resident_grid(qk_rope_f16_warp_kernel<P>, 128, 0, ((long)n + 3) / 4);
+    qk_rope_f16_warp_kernel<P><<<grid, 128, 0, (cudaStream_t)stream>>>(A, rounds);
+    return (int)cudaGetLastError();
 }

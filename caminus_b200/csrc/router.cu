@@ -1,13 +1,20 @@
 // The router glue of the Qwen3-MoE prefill (the reference's q3p_router, q3p_topk, q3p_group, kernels/q3m_prefill.hip:417-513;
-// wrappers python/caminus/prefill/q3m_ops.py:94-104): fp32 router logits, softmax + rank-based top-k with lower-index-first
-// ties, and the grouping of (token, slot) pairs by expert into work items of at most 64 pairs. The mappings are the
-// reference's (a warp per logit row; a warp per token; one block of 1024 threads for the grouping), so every sum has its order.
+// wrappers python/caminus/prefill/q3m_ops.py:94-104) and the hyper-connection line's pf_router (kernels/prefill_glue.hip:208-308):
+// fp32 router logits, softmax + rank-based top-k with lower-index-first ties, and the grouping of (token, slot) pairs by expert into
+// work items of at most 64 pairs. What the reference fixes is the order of every floating-point sum (stated at each kernel); the
+// mappings onto the device are this library's: logits by shared-memory tiles (many tokens) or one warp per expert (few tokens), the
+// softmax and top-k by one warp per token, the grouping by a thread-block cluster that counts, scans through distributed shared
+// memory and scatters in pair order.
 #include "cam_common.cuh"
+
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 namespace {
 
-struct MMItem { int e, off, cnt, pad; };
-constexpr int MM_M = 64;
+struct WorkItem { int expert, first, count, zero; };       // the reference's 16-byte work item { e, off, cnt, pad } (q3m_prefill.hip MMItem)
+constexpr int ITEM_PAIRS = 64;                             // pairs per work item (python/caminus/prefill/q3m_ops.py:21 MM_M)
 
 CAM_DEV float wsum(float v) {
 #pragma unroll
@@ -20,20 +27,31 @@ CAM_DEV float wmax(float v) {
     return v;
 }
 CAM_DEV bool finite_f(float x) { return fabsf(x) <= 3.402823466e38f; }
+CAM_DEV float dot4(const float4 w, const float4 x) {        // the reference's per-step expression w.x x.x + w.y x.y + .. as it contracts: one product, three fma
+    float d = fmul(w.x, x.x); d = ffma(w.y, x.y, d); d = ffma(w.z, x.z, d); return ffma(w.w, x.w, d);
+}
 
-__global__ void __launch_bounds__(256) router_kernel(const float * __restrict__ h, const float * __restrict__ Wr, int E, int K, float * __restrict__ logits) {
-    const int lane = threadIdx.x & 31, wave = threadIdx.x >> 5, t = blockIdx.x;
-    const float * x = h + (size_t)t * K;
-    for (int e = wave; e < E; e += 8) {
-        const float * wr = Wr + (size_t)e * K;
-        float acc = 0.0f;
-        for (int k0 = lane * 4; k0 < K; k0 += 128) {
-            const float4 wv = __ldg(reinterpret_cast<const float4 *>(wr + k0)), xv = __ldg(reinterpret_cast<const float4 *>(x + k0));
-            float d = fmul(wv.x, xv.x); d = ffma(wv.y, xv.y, d); d = ffma(wv.z, xv.z, d); d = ffma(wv.w, xv.w, d);
-            acc = fadd(acc, d);
+// Few tokens (n < 64): the weights are what is read (E K floats), the tokens fit in cache. A warp owns one expert and walks the tokens
+// two at a time, so an expert's row comes from DRAM once and the grid is E warps wide whatever n is (a block per token would leave
+// most of the device idle at n = 1). Per (token, expert) the statements are the reference's: lane l adds the float4 products of
+// k = 4 l + 128 i in the order of i, then the xor butterfly 16, 8, 4, 2, 1.
+__global__ void __launch_bounds__(256) router_few_kernel(const float * __restrict__ h, const float * __restrict__ Wr, int E, int K,
+                                                         float * __restrict__ logits, int n) {
+    const int lane = threadIdx.x & 31, e = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (e >= E) return;                                                    // (whole warps; no block-wide barrier below)
+    const float4 * wr = reinterpret_cast<const float4 *>(Wr + (size_t)e * K) + lane;
+    const int steps = K >> 7;
+    for (int t = 0; t < n; t += 2) {
+        const int t1 = min(t + 1, n - 1);
+        const float4 * x0 = reinterpret_cast<const float4 *>(h + (size_t)t * K) + lane, * x1 = reinterpret_cast<const float4 *>(h + (size_t)t1 * K) + lane;
+        float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll 4
+        for (int i = 0; i < steps; i++) {
+            const float4 wv = __ldg(wr + 32 * i);
+            a0 = fadd(a0, dot4(wv, __ldg(x0 + 32 * i))); a1 = fadd(a1, dot4(wv, __ldg(x1 + 32 * i)));
         }
-        acc = wsum(acc);
-        if (lane == 0) logits[(size_t)t * E + e] = acc;
+        a0 = wsum(a0); a1 = wsum(a1);
+        if (lane == 0) { logits[(size_t)t * E + e] = a0; if (t1 != t) logits[(size_t)t1 * E + e] = a1; }
     }
 }
 
@@ -41,7 +59,7 @@ __global__ void __launch_bounds__(256) router_kernel(const float * __restrict__ 
 // accumulator per pair in every lane, the lanes splitting K as above). Steps of 128 values of K are brought into shared memory
 // with cp.async, three stages deep (32 rows of h and 16 of Wr, 512 bytes each), so a step costs a warp 16 16-byte shared-memory
 // loads for 64 pairs instead of two global loads per pair, and no load waits on DRAM. Per pair the statements and their order
-// are router_kernel's.
+// are the ones stated above router_few_kernel.
 constexpr int RT_TOK = 32, RT_EXP = 16, RT_STAGES = 3, RT_STAGE_FLOATS = (RT_TOK + RT_EXP) * 128;
 
 __global__ void __launch_bounds__(256) router_tile_kernel(const float * __restrict__ h, const float * __restrict__ Wr, int E, int K,
@@ -85,10 +103,7 @@ __global__ void __launch_bounds__(256) router_tile_kernel(const float * __restri
 #pragma unroll
         for (int i = 0; i < 8; i++)
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                float d = fmul(wv[j].x, xv[i].x); d = ffma(wv[j].y, xv[i].y, d); d = ffma(wv[j].z, xv[i].z, d); d = ffma(wv[j].w, xv[i].w, d);
-                acc[i][j] = fadd(acc[i][j], d);
-            }
+            for (int j = 0; j < 8; j++) acc[i][j] = fadd(acc[i][j], dot4(wv[j], xv[i]));
     }
     cp_async_wait<0>();
     float mine[2] = {0.0f, 0.0f};                                          // lane l stores pairs (token l / 8 and 4 + l / 8, expert l % 8)
@@ -156,32 +171,200 @@ __global__ void __launch_bounds__(256) topk_kernel(const float * __restrict__ lo
     if (bad) atomicOr(err, 1);
 }
 
-__global__ void __launch_bounds__(1024) group_kernel(const int * __restrict__ ids, int npairs, int k, int E, int * __restrict__ xs, int * __restrict__ yd,
-                                                     MMItem * __restrict__ items, int * __restrict__ nitems, int * __restrict__ err) {
-    __shared__ int cnt[1024], off[1024], cur[1024], ioff[1024];
-    const int tid = threadIdx.x;
-    if (tid < E) { cnt[tid] = 0; cur[tid] = 0; }
-    __syncthreads();
-    for (int p = tid; p < npairs; p += 1024) {
-        int e = ids[p];
+// ---- pf_router: softmax over E <= 1024 logits and the k <= 64 most probable experts of a token ----------------------------------------
+// The reference runs a workgroup of 256 per token: thread tid owns logits tid + 256 j (j < 4), its sum is the chain over j from 0.0f, a
+// wave adds by the butterfly 16, 8, 4, 2, 1 and the eight wave sums are added in wave order (kernels/prefill_glue.hip:251-268). Here a
+// warp owns the token: lane l holds, for every wave w of the reference, the values of that wave's lane l (logits 32 w + l + 256 j), so
+// a wave's butterfly is a warp butterfly and the eight totals are added in a register. The k experts come from k rounds of a warp-wide
+// argmax over (probability bits as a signed integer, lower index first): the r-th round's winner is the element of rank r under the
+// reference's order (rank = how many are larger, or equal with a lower index), so ids and weights are slot for slot the reference's.
+// Each pick is masked out before the next round: the k ids are distinct and below E by construction, also for a token whose logits are
+// not finite (err |= 1; the reference's further flags 2 and 4, an id out of range or repeated, cannot arise).
+template <int NJ>
+__global__ void __launch_bounds__(256) softmax_topk_rows_kernel(const float * __restrict__ logits, int E, int k, float clamp, int * __restrict__ ids,
+                                                                float * __restrict__ wts, int * __restrict__ err, int n) {
+    const int lane = threadIdx.x & 31, t = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (t >= n) return;                                                    // (whole warps; no block-wide barrier below)
+    const float * lg = logits + (size_t)t * E;
+    const float ninf = -__int_as_float(0x7f800000);
+    float v[8][NJ]; bool bad = false; float m = ninf;
+#pragma unroll
+    for (int j = 0; j < NJ; j++)
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const int e = 32 * w + lane + 256 * j;
+            v[w][j] = e < E ? __ldg(lg + e) : ninf;
+            if (e < E) { bad |= !finite_f(v[w][j]); m = fmaxf(m, v[w][j]); }
+        }
+    m = wmax(m);
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+        float s = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NJ; j++)
+            if (32 * w + lane + 256 * j < E) { v[w][j] = cam_expf(fsub(v[w][j], m)); s = fadd(s, v[w][j]); }
+        s = wsum(s);
+        total = w == 0 ? s : fadd(total, s);
+    }
+    const float inv = fdiv(1.0f, total);
+    const long long none = (long long)0x8000000000000000ull;               // below every key of a real element (a probability's bits are never 0x80000000)
+    long long key[8][NJ];
+#pragma unroll
+    for (int w = 0; w < 8; w++)
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const int e = 32 * w + lane + 256 * j;
+            const unsigned pb = __float_as_uint(fmul(v[w][j], inv));
+            key[w][j] = e < E ? (long long)(((unsigned long long)pb << 32) | (unsigned)(0x7fffffff - e)) : none;
+        }
+    int sel_e[2] = {0, 0}; float sel_p[2] = {0.0f, 0.0f};                  // lane l keeps slots l and l + 32
+    for (int r = 0; r < k; r++) {
+        long long best = none;
+#pragma unroll
+        for (int w = 0; w < 8; w++)
+#pragma unroll
+            for (int j = 0; j < NJ; j++) best = key[w][j] > best ? key[w][j] : best;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) { const long long q = __shfl_xor_sync(CAM_FULL, best, o); best = q > best ? q : best; }
+        const int e = 0x7fffffff - (int)(unsigned)(best & 0xffffffffll);
+        if (lane == (r & 31)) { sel_e[r >> 5] = e; sel_p[r >> 5] = __uint_as_float((unsigned)((unsigned long long)best >> 32)); }
+        if (lane == (e & 31)) {
+#pragma unroll
+            for (int w = 0; w < 8; w++)
+#pragma unroll
+                for (int j = 0; j < NJ; j++) if (((e >> 5) & 7) == w && (e >> 8) == j) key[w][j] = none;
+        }
+    }
+    float ws = 0.0f;
+    for (int j = 0; j < k; j++) ws = fadd(ws, __shfl_sync(CAM_FULL, j < 32 ? sel_p[0] : sel_p[1], j & 31));
+    ws = fmaxf(ws, clamp);
+#pragma unroll
+    for (int q = 0; q < 2; q++) {
+        const int slot = lane + 32 * q;
+        if (slot < k) { ids[(size_t)t * k + slot] = sel_e[q]; wts[(size_t)t * k + slot] = fdiv(sel_p[q], ws); }
+    }
+    if (bad) atomicOr(err, 1);
+}
+
+// ---- q3p_group: the (token, slot) pairs of a chunk listed by expert, and the experts' lists cut into work items of at most 64 pairs ------
+// One thread-block cluster of up to 8 blocks x 32 warps; no global scratch. A warp takes a contiguous run of pairs, 32 at a time:
+//   count    lanes holding the same expert find each other (match.any); the first of them adds their number to the warp's own row of
+//            counters in shared memory (a row per warp: no atomics);
+//   scan     a block adds its warps' rows, the blocks read one another's totals through distributed shared memory, and every block
+//            derives the same expert offsets (an exclusive scan over the experts) and its own start inside every expert's list; the
+//            warps' counter rows become their write cursors;
+//   scatter  the second pass over the same pairs (kept in registers when a warp has at most 8 steps) writes pair p at cursor + its
+//            rank among the step's equal lanes.
+// A warp's pairs are ascending and the cursors follow (block, warp) order, so every expert's list is in ascending pair order: the
+// result does not depend on timing (the reference's order follows its atomics; it states that the order inside a list changes no bit
+// downstream), and the rows a GEMM gathers through xs ascend. An id outside [0, E) counts as expert 0 and sets err |= 2.
+constexpr int GR_WARPS = 32, GR_KEEP = 8;
+
+__global__ void __launch_bounds__(1024) group_cluster_kernel(const int * __restrict__ ids, int npairs, int k, int E, int * __restrict__ xs,
+                                                             int * __restrict__ yd, WorkItem * __restrict__ items, int * __restrict__ nitems,
+                                                             int * __restrict__ err) {
+    extern __shared__ int gr_smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int nblk = (int)cluster.num_blocks(), blk = (int)cluster.block_rank();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int * rows = gr_smem;                        // [GR_WARPS][E]: a warp's counts, later its cursors
+    int * mine = rows + GR_WARPS * E;            // [E]: this block's count per expert (read by the other blocks)
+    int * first = mine + E;                      // [E]: where an expert's list starts
+    int * ifirst = first + E;                    // [E]: where an expert's work items start
+    int * total = ifirst + E;                    // [E]: pairs of an expert over all blocks
+    int * wsum_ = total + E;                     // [2][32]: the scan's per-warp sums
+    // this warp's run of pairs: `per` (a multiple of 32) consecutive pairs per warp, warps in (block, warp) order
+    const int nw = nblk * GR_WARPS;
+    const int per = ((npairs + nw - 1) / nw + 31) & ~31;
+    const long lo = (long)(blk * GR_WARPS + warp) * per;
+    const int steps = lo >= npairs ? 0 : (int)((min((long)npairs, lo + per) - lo + 31) >> 5);
+    int * row = rows + warp * E;
+    for (int e = lane; e < E; e += 32) row[e] = 0;
+    __syncwarp();
+    const unsigned below = (1u << lane) - 1u;
+    int kept[GR_KEEP];
+    auto expert_of = [&](int s) {                // the expert of this lane's pair in step s (-1: past the end), range-checked
+        const long p = lo + 32 * s + lane;
+        if (p >= npairs) return -1;
+        int e = __ldg(ids + p);
         if (e < 0 || e >= E) { atomicOr(err, 2); e = 0; }
-        atomicAdd(&cnt[e], 1);
+        return e;
+    };
+    for (int s = 0; s < steps; s++) {
+        const int e = expert_of(s);
+        if (s < GR_KEEP) {
+#pragma unroll
+            for (int q = 0; q < GR_KEEP; q++) if (q == s) kept[q] = e;
+        }
+        const unsigned same = __match_any_sync(CAM_FULL, e);
+        if (e >= 0 && (same & below) == 0) row[e] += __popc(same);
+        __syncwarp();
     }
     __syncthreads();
-    if (tid == 0) {
-        int o = 0, io = 0;
-        for (int e = 0; e < E; e++) { off[e] = o; ioff[e] = io; o += cnt[e]; io += (cnt[e] + MM_M - 1) / MM_M; }
-        *nitems = io;
+    for (int e = tid; e < E; e += 1024) {
+        int c = 0;
+        for (int w = 0; w < GR_WARPS; w++) c += rows[w * E + e];
+        mine[e] = c;
     }
-    __syncthreads();
-    for (int p = tid; p < npairs; p += 1024) {
-        int e = ids[p]; if (e < 0 || e >= E) e = 0;
-        const int sl = off[e] + atomicAdd(&cur[e], 1);
-        xs[sl] = p / k; yd[sl] = p;
-    }
+    cluster.sync();
+    // E <= 1024: thread e owns expert e from here on
+    int before = 0, tot = 0;
     if (tid < E) {
-        const int c = cnt[tid];
-        for (int j = 0; j * MM_M < c; j++) { MMItem it; it.e = tid; it.off = off[tid] + j * MM_M; it.cnt = min(MM_M, c - j * MM_M); it.pad = 0; items[ioff[tid] + j] = it; }
+        for (int b = 0; b < nblk; b++) {
+            const int c = cluster.map_shared_rank(mine, b)[tid];
+            tot += c; if (b < blk) before += c;
+        }
+        total[tid] = tot;
+    }
+    cluster.sync();                              // (no block leaves, or goes on to reuse anything, while another still reads its counts)
+    // exclusive scans over the experts of the pair counts and of the item counts: a warp scan, then the 32 warp sums
+    const int nit = (tot + ITEM_PAIRS - 1) / ITEM_PAIRS;
+    int sc = tot, si = nit;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int a = __shfl_up_sync(CAM_FULL, sc, o), b = __shfl_up_sync(CAM_FULL, si, o);
+        if (lane >= o) { sc += a; si += b; }
+    }
+    if (lane == 31) { wsum_[warp] = sc; wsum_[32 + warp] = si; }
+    __syncthreads();
+    int base_c = 0, base_i = 0;
+    for (int w = 0; w < warp; w++) { base_c += wsum_[w]; base_i += wsum_[32 + w]; }
+    const int my_first = base_c + sc - tot, my_ifirst = base_i + si - nit;
+    if (tid < E) {
+        first[tid] = my_first; ifirst[tid] = my_ifirst;
+        int cur = my_first + before;
+        for (int w = 0; w < GR_WARPS; w++) { const int c = rows[w * E + tid]; rows[w * E + tid] = cur; cur += c; }
+    }
+    __syncthreads();
+    int all_items = 0;
+    for (int w = 0; w < GR_WARPS; w++) all_items += wsum_[32 + w];
+    if (blk == 0 && tid == 0) *nitems = all_items;
+    for (int s = 0; s < steps; s++) {
+        int e = -1;
+        if (s < GR_KEEP) {
+#pragma unroll
+            for (int q = 0; q < GR_KEEP; q++) if (q == s) e = kept[q];
+        } else {
+            const long p = lo + 32 * s + lane;
+            if (p < npairs) { e = __ldg(ids + p); if (e < 0 || e >= E) e = 0; }
+        }
+        const unsigned same = __match_any_sync(CAM_FULL, e);
+        if (e >= 0) {
+            const int p = (int)(lo + 32 * s + lane), at = row[e] + __popc(same & below);
+            xs[at] = p / k; yd[at] = p;
+        }
+        __syncwarp();
+        if (e >= 0 && (same & below) == 0) row[e] += __popc(same);
+        __syncwarp();
+    }
+    // the work items, spread over all threads of the cluster: item i belongs to the last expert whose items start at or before i
+    for (int i = blk * 1024 + tid; i < all_items; i += nblk * 1024) {
+        int a = 0, b = E - 1;
+        while (a < b) { const int mid = (a + b + 1) >> 1; if (ifirst[mid] <= i) a = mid; else b = mid - 1; }
+        const int j = i - ifirst[a];
+        WorkItem it; it.expert = a; it.first = first[a] + j * ITEM_PAIRS; it.count = min(ITEM_PAIRS, total[a] - j * ITEM_PAIRS); it.zero = 0;
+        items[i] = it;
     }
 }
 
@@ -193,11 +376,12 @@ extern "C" int q3p_router(int n, const float * h, const float * Wr, int E, int K
     if (!cam_aligned16(h) || !cam_aligned16(Wr)) return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
     if (n >= 64) {
-        const size_t smem = (size_t)RT_STAGES * RT_STAGE_FLOATS * 4;
-        const cudaError_t e = cudaFuncSetAttribute(router_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     // (72 KB: above the default limit)
+        static unsigned long long allowed = 0;
+        const size_t smem = (size_t)RT_STAGES * RT_STAGE_FLOATS * 4;                 // (72 KB: above the default limit)
+        const cudaError_t e = cam_allow_smem(router_tile_kernel, smem, allowed);
         if (e != cudaSuccess) return (int)e;
         router_tile_kernel<<<dim3((n + RT_TOK - 1) / RT_TOK, (E + RT_EXP - 1) / RT_EXP), 256, smem, (cudaStream_t)stream>>>(h, Wr, E, K, logits, n);
-    } else router_kernel<<<n, 256, 0, (cudaStream_t)stream>>>(h, Wr, E, K, logits);
+    } else router_few_kernel<<<(E + 7) / 8, 256, 0, (cudaStream_t)stream>>>(h, Wr, E, K, logits, n);
     return (int)cudaGetLastError();
 }
 // q3p_topk: kernels/q3m_prefill.hip:440-441 (n = grid.x); E <= 128, k <= 32
@@ -207,9 +391,32 @@ extern "C" int q3p_topk(int n, const float * logits, int E, int k, float floor_,
     topk_kernel<<<(n + 7) / 8, 256, 0, (cudaStream_t)stream>>>(logits, E, k, floor_, ids, wts, err, n);
     return (int)cudaGetLastError();
 }
+// pf_router: kernels/prefill_glue.hip:242-243 (T = grid.x); E <= 1024, k <= min(64, E)
+extern "C" int pf_router(int T, const float * logits, int E, int k, float clamp, int * ids, float * wts, int * err, void * stream) {
+    if (T < 0 || E < 1 || E > 1024 || k < 1 || k > 64 || k > E || !logits || !ids || !wts || !err) return CAM_ERR_ARG;
+    if (T == 0) return CAM_OK;
+    const dim3 grid((T + 7) / 8);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch ((E + 255) / 256) {
+        case 1: softmax_topk_rows_kernel<1><<<grid, 256, 0, st>>>(logits, E, k, clamp, ids, wts, err, T); break;
+        case 2: softmax_topk_rows_kernel<2><<<grid, 256, 0, st>>>(logits, E, k, clamp, ids, wts, err, T); break;
+        case 3: softmax_topk_rows_kernel<3><<<grid, 256, 0, st>>>(logits, E, k, clamp, ids, wts, err, T); break;
+        default: softmax_topk_rows_kernel<4><<<grid, 256, 0, st>>>(logits, E, k, clamp, ids, wts, err, T); break;
+    }
+    return (int)cudaGetLastError();
+}
 // q3p_group: kernels/q3m_prefill.hip:490-492; items are { int e, off, cnt, pad }; E <= 1024
 extern "C" int q3p_group(const int * ids, int npairs, int k, int E, int * xs, int * yd, void * items, int * nitems, int * err, void * stream) {
     if (npairs < 0 || k < 1 || E < 1 || E > 1024 || !ids || !xs || !yd || !items || !nitems || !err) return CAM_ERR_ARG;
-    group_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(ids, npairs, k, E, xs, yd, (MMItem *)items, nitems, err);
-    return (int)cudaGetLastError();
+    static unsigned long long allowed = 0;
+    const size_t smem = ((size_t)(GR_WARPS + 4) * E + 64) * sizeof(int);             // (E = 1024: 144 KB)
+    if (smem > 48 * 1024) { const cudaError_t e = cam_allow_smem(group_cluster_kernel, smem, allowed); if (e != cudaSuccess) return (int)e; }
+    int nblk = 1;
+    while (nblk < 8 && (long)nblk * 8192 < npairs) nblk *= 2;                         // 8 steps of 32 pairs per warp before the cluster grows
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nblk); cfg.blockDim = dim3(1024); cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = nblk; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, group_cluster_kernel, ids, npairs, k, E, xs, yd, (WorkItem *)items, nitems, err);
 }

@@ -26,7 +26,7 @@
 
 namespace {
 
-constexpr unsigned long long CAM_TP_WAIT_NS = 2000000000ull;      // 2 s
+constexpr unsigned long long CAM_TP_WAIT_NS = 2000000000ull;      // 2 s: the default limit of a wait (CAMINUS_B200_TP_WAIT_MS overrides it)
 
 CAM_DEV void st_sys_u64(unsigned long long * p, unsigned long long v) { asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory"); }
 CAM_DEV unsigned long long ld_sys_u64(const unsigned long long * p) {
@@ -44,7 +44,7 @@ CAM_DEV void widen8(const uint4 v, float (&f)[8]) {
 template <int DEPTH>
 __global__ void __launch_bounds__(128) tp_rms_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d, const float * __restrict__ nw, float eps,
                                                      uint16_t * __restrict__ h16, int Ns, int Nfull, int n, unsigned long long * const * __restrict__ peers,
-                                                     int rank, int world, int cap, unsigned tag, int * status) {
+                                                     int rank, int world, int cap, unsigned tag, int * status, unsigned long long wait_ns) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nch = (Ns + 255) >> 8;                                     // 16-byte chunks per lane and row (the last may be short)
     const int t0 = blockIdx.x * 4 + warp, stride = gridDim.x * 4;
@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(128) tp_rms_kernel(uint16_t * __restrict__ x, 
                         __nanosleep(64);
                         w = ld_sys_u64(from + t);
                         late = (unsigned)(w >> 32) != tag;
-                    } while (late && global_ns() - start < CAM_TP_WAIT_NS);
+                    } while (late && global_ns() - start < wait_ns);
                 }
                 part = __uint_as_float((unsigned)w);
             }
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(128) tp_rms_kernel(uint16_t * __restrict__ x, 
 template <int LA, int DEPTH>
 __global__ void __launch_bounds__(256) tp_rms_staged_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d, const float * __restrict__ nw, float eps,
                                                             uint16_t * __restrict__ h16, int Ns, int Nfull, int n, unsigned long long * const * __restrict__ peers,
-                                                            int rank, int world, int cap, unsigned tag, int * status, int warps) {
+                                                            int rank, int world, int cap, unsigned tag, int * status, int warps, unsigned long long wait_ns) {
     constexpr int S = LA + DEPTH + 1;
     extern __shared__ __align__(16) unsigned char tp_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(256) tp_rms_staged_kernel(uint16_t * __restric
                         __nanosleep(64);
                         w = ld_sys_u64(from + t);
                         late = (unsigned)(w >> 32) != tag;
-                    } while (late && global_ns() - start < CAM_TP_WAIT_NS);
+                    } while (late && global_ns() - start < wait_ns);
                 }
                 part = __uint_as_float((unsigned)w);
             }
@@ -241,12 +241,13 @@ __global__ void __launch_bounds__(256) tp_rms_staged_kernel(uint16_t * __restric
 
 template <int LA, int DEPTH>
 int launch_tp_staged(int warps, size_t smem, int n, void * x, const void * d, const float * nw, float eps, void * h16, int Ns, int Nfull, const void * peers,
-                     int rank, int world, int cap, unsigned tag, int * status, cudaStream_t stream) {
-    const cudaError_t e = cudaFuncSetAttribute(tp_rms_staged_kernel<LA, DEPTH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+                     int rank, int world, int cap, unsigned tag, int * status, unsigned long long wait_ns, cudaStream_t stream) {
+    static unsigned long long allowed = 0;
+    const cudaError_t e = cam_allow_smem(tp_rms_staged_kernel<LA, DEPTH>, 227 * 1024, allowed);
     if (e != cudaSuccess) return (int)e;
     const int grid = cam_resident_grid(tp_rms_staged_kernel<LA, DEPTH>, warps * 32, smem, ((long)n + warps - 1) / warps);
     tp_rms_staged_kernel<LA, DEPTH><<<grid, warps * 32, smem, stream>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Ns, Nfull, n,
-                                                                        (unsigned long long * const *)peers, rank, world, cap, tag, status, warps);
+                                                                        (unsigned long long * const *)peers, rank, world, cap, tag, status, warps, wait_ns);
     return (int)cudaGetLastError();
 }
 
@@ -262,8 +263,10 @@ extern "C" int cam_tp_rms_words(int cap, int world) {
 // nw fp32 [Ns] = this rank's weights, h16 fp16 [n][Ns] out; Nfull = the row length over all ranks. peers: device array of `world`
 // pointers, entry r = rank r's exchange buffer as mapped in this process (entry `rank` = this rank's own), each
 // cam_tp_rms_words(cap, world) words; n <= cap (CAM_ERR_CAPACITY beyond). tag: the call's sequence number, not 0, the same on
-// every rank, consecutive calls differing in parity (1, 2, 3, ..). status: an int32 word in this rank's memory; bit 0 is set when
-// a wait ran out (some rank did not take part, or not with the same n and tag), in which case rows are left unnormalised.
+// every rank, consecutive LAUNCHES differing in parity (1, 2, 3, ..: a call with n = 0 launches nothing and must not use one up).
+// status: an int32 word in this rank's memory; bit 0 is set when a wait ran out (some rank did not take part, or not with the same n
+// and tag; the limit is 2 s, or CAMINUS_B200_TP_WAIT_MS milliseconds). The call's rows are then partly updated: the rows normalised
+// before the wait ran out hold x = fp16(x + d) and their h16, the others are untouched, so a retry needs x restored from a copy.
 // Every rank must make the matching call; no rank's call may share a GPU with another's. Ns a multiple of 8, world <= 32.
 extern "C" int cam_tp_rms_norm_f16(int n, void * x, const void * d, const float * nw, float eps, void * h16, int Ns, int Nfull,
                                    const void * peers, int rank, int world, int cap, unsigned tag, int * status, void * stream) {
@@ -272,8 +275,10 @@ extern "C" int cam_tp_rms_norm_f16(int n, void * x, const void * d, const float 
     if (n > cap) return CAM_ERR_CAPACITY;
     if (!cam_aligned16(x) || (d && !cam_aligned16(d)) || !cam_aligned16(nw) || !cam_aligned16(h16) || (reinterpret_cast<uintptr_t>(peers) & 7u) ||
         (reinterpret_cast<uintptr_t>(status) & 3u)) return CAM_ERR_ALIGN;
-    if (n == 0) return CAM_OK;
+    if (n == 0) return CAM_OK;                      // (the caller must not advance its tag for such a call: nothing was stamped with it)
     cudaStream_t st = (cudaStream_t)stream;
+    unsigned long long wait_ns = CAM_TP_WAIT_NS;    // CAMINUS_B200_TP_WAIT_MS: the limit of a wait in milliseconds (1 .. 600000)
+    if (const char * e = getenv("CAMINUS_B200_TP_WAIT_MS")) { const long ms = atol(e); if (ms >= 1 && ms <= 600000) wait_ns = (unsigned long long)ms * 1000000ull; }
     // Rows staged in shared memory. Measured on B200 (T = 65536, shards of 640 / 1280 / 2560 columns): resident warps matter more than
     // rows in flight per warp: two slots per warp (one row waiting for its partials while the next is loaded and reduced) where
     // that still leaves 20 warps per multiprocessor, else one slot. CAMINUS_B200_TP_CFG="slots,warps" overrides (tuning).
@@ -287,7 +292,7 @@ extern "C" int cam_tp_rms_norm_f16(int n, void * x, const void * d, const float 
         while (warps > 1 && (size_t)slots * warps * row_bytes > budget) warps--;
         const size_t smem = (size_t)slots * warps * row_bytes;
         if (smem <= budget) {
-#define CAM_TP_STAGED(LAV, DV) return launch_tp_staged<LAV, DV>(warps, smem, n, x, d, nw, eps, h16, Ns, Nfull, peers, rank, world, cap, tag, status, st);
+#define CAM_TP_STAGED(LAV, DV) return launch_tp_staged<LAV, DV>(warps, smem, n, x, d, nw, eps, h16, Ns, Nfull, peers, rank, world, cap, tag, status, wait_ns, st);
             switch (slots) {
                 case 1: CAM_TP_STAGED(0, 0)
                 case 2: CAM_TP_STAGED(0, 1)
@@ -300,7 +305,7 @@ extern "C" int cam_tp_rms_norm_f16(int n, void * x, const void * d, const float 
     // longer rows: two passes over the row, four rows apart
     const int grid = cam_resident_grid(tp_rms_kernel<4>, 128, 0, ((long)n + 3) / 4);
     tp_rms_kernel<4><<<grid, 128, 0, st>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Ns, Nfull, n,
-                                           (unsigned long long * const *)peers, rank, world, cap, tag, status);
+                                           (unsigned long long * const *)peers, rank, world, cap, tag, status, wait_ns);
     return (int)cudaGetLastError();
 }
 

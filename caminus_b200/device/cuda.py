@@ -26,7 +26,7 @@ _Q3M = {'q3p_emb': ('q3p_emb', 1), 'q3p_add_rms16': ('q3p_add_rms16', 1), 'q3p_s
 def _glue(K):
     """the hyper-connection glue object of row width K (the reference bakes K into the code object: GLUE_NI x 256)"""
     return {'pf_rms_mul': ('pf_rms_mul', 0, (K,)), 'pf_hc_post_rms': ('pf_hc_post_rms', 0, (K,)), 'pf_hc_post': ('pf_hc_post', 0),
-            'pf_hc_mean': ('pf_hc_mean', 0), 'pf_add_sum': ('pf_add_sum', 0), 'pf_silu_bf16': ('pf_silu_bf16', 0), 'pf_to_bf16': ('pf_to_bf16', 0)}
+            'pf_hc_mean': ('pf_hc_mean', 0), 'pf_router': ('pf_router', 1), 'pf_add_sum': ('pf_add_sum', 0), 'pf_silu_bf16': ('pf_silu_bf16', 0), 'pf_to_bf16': ('pf_to_bf16', 0)}
 
 
 MODULES = {
@@ -94,42 +94,62 @@ def _iq2s_grid():
 
 
 _torch = None
+_Tensor = None
+
+
+def _bind_torch():
+    global _torch, _Tensor
+    import torch
+    _torch, _Tensor = torch, torch.Tensor
 
 
 def _current_stream():
-    global _torch
-    if _torch is None:
-        import torch
-        _torch = torch
+    if _torch is None: _bind_torch()
     return _torch.cuda.current_stream().cuda_stream
 
 
-def _arg(a):
-    if hasattr(a, 'data_ptr'):
-        if getattr(a, 'is_cuda', True) is False: raise ValueError('caminus_b200: a kernel argument is a CPU tensor')
-        return ctypes.c_void_p(a.data_ptr())
-    return a
-
-
 class Kernel:
+    """one kernel of a code object: __call__(grid, block, *args, shmem=0, stream=None) as the reference's hip.Kernel. The call is the
+    whole host cost of a decode-sized launch, so its path is short: tensors go down as their device addresses (plain integers),
+    ctypes scalars as they are, and nothing is built that the launch does not need."""
+
     def __init__(self, module, name, entry, ngrid, tail=()):
         """tail: constants the reference bakes into the code object, passed as the entry's last arguments before the stream"""
         self.module, self.name, self.entry, self.ngrid, self.tail = module, name, entry, ngrid, tuple(tail)
         self.fn = getattr(_lib.load(), entry)
+        self._heads = name in ('q3p_qk_rope', 'q3p_qk_rope_q8')      # grid.y is the reference's nh + nkv: checked against the arguments
+        self._lazy_tail = any(callable(t) for t in self.tail)
+        if _Tensor is None: _bind_torch()
 
     def __call__(self, grid, block, *args, shmem=0, stream=None):
         """args: torch tensors (passed as device pointers) or ctypes scalars (c_int, c_float, c_void_p(0) for null)"""
-        vals = [_arg(a) for a in args]
-        grid = (tuple(grid) + (1, 1))[:3]
-        s = _current_stream() if stream is None else stream
+        T = _Tensor
+        vals = []
+        for a in args:
+            if type(a) is T:
+                if not a.is_cuda: raise ValueError('caminus_b200: a kernel argument is a CPU tensor')
+                vals.append(a.data_ptr())
+            elif hasattr(a, 'data_ptr'):                             # (a tensor subclass or another array with a device address)
+                if getattr(a, 'is_cuda', True) is False: raise ValueError('caminus_b200: a kernel argument is a CPU tensor')
+                vals.append(a.data_ptr())
+            else:
+                vals.append(a)
+        s = _torch.cuda.current_stream().cuda_stream if stream is None else stream
         r = RECORD
-        if r is not None and r.intercept(self, grid, block, vals, shmem, s): return
-        if self.name in ('q3p_qk_rope', 'q3p_qk_rope_q8'):   # grid.y is the reference's nh + nkv: it must agree with the kernel's own arguments
+        if r is not None:                                            # the recorder sees what the reference's loader hands it: c_void_p for tensors, 3-tuples
+            vals = [ctypes.c_void_p(v) if type(v) is int else v for v in vals]
+            grid, block = (tuple(grid) + (1, 1))[:3], (tuple(block) + (1, 1))[:3]
+            if r.intercept(self, grid, block, vals, shmem, s): return
+        if self._heads:
             nh, nkv = int(getattr(vals[2], 'value', vals[2])), int(getattr(vals[3], 'value', vals[3]))
-            if grid[1] != nh + nkv: raise ValueError(f'{self.name}: grid.y {grid[1]} is not nh + nkv = {nh + nkv}')
-        lead = [ctypes.c_int(int(grid[i])) for i in range(self.ngrid)]
-        tail = [t() if callable(t) else t for t in self.tail]      # (a callable: a per-device constant looked up at the launch)
-        _lib.check(self.fn(*lead, *vals, *tail, ctypes.c_void_p(s)), self.name)
+            gy = grid[1] if len(grid) > 1 else 1
+            if gy != nh + nkv: raise ValueError(f'{self.name}: grid.y {gy} is not nh + nkv = {nh + nkv}')
+        tail = [t() if callable(t) else t for t in self.tail] if self._lazy_tail else self.tail      # (a callable: a per-device constant looked up at the launch)
+        n = self.ngrid
+        if n == 0: rc = self.fn(*vals, *tail, s)
+        elif n == 1: rc = self.fn(int(grid[0]), *vals, *tail, s)
+        else: rc = self.fn(*[int(grid[i]) for i in range(n)], *vals, *tail, s)
+        if rc: _lib.check(rc, self.name)
         if r is not None: r.launched(self, grid, block, vals, shmem, s)
 
 

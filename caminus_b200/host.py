@@ -89,3 +89,17 @@ class HostLayerGlue:
                 self.yq[a:b].copy_(B['yq'][:n * self.yq.shape[1]].view(n, -1), non_blocking=True)
                 f = torch.cuda.Event(); f.record(self.s_out); free[i & 1] = f
         self.s_out.synchronize()
+
+    def copies_only(self):
+        """the copies of one pass without its kernels: every input chunk host -> device on one stream while every output chunk goes
+        device -> host on another (the bytes and buffers of run()). Returns when all of it has finished. What the host link alone
+        costs for a pass: the floor under run()'s time"""
+        C, T = self.chunk, self.T
+        for i, a in enumerate(range(0, T, C)):
+            b = min(T, a + C); n = b - a; B = self.bufs[i & 1]
+            with torch.cuda.stream(self.s_in):
+                for name in ('x', 'resid', 'q', 'k', 'gate', 'up'): B[name][:n].copy_(getattr(self, name)[a:b], non_blocking=True)
+            with torch.cuda.stream(self.s_out):
+                for name in ('x', 'h16', 'q', 'k'): getattr(self, name)[a:b].copy_(B[name][:n], non_blocking=True)
+                self.yq[a:b].copy_(B['yq'][:n * self.yq.shape[1]].view(n, -1), non_blocking=True)
+        self.s_in.synchronize(); self.s_out.synchronize()

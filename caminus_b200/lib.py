@@ -58,6 +58,7 @@ SIGNATURES = {
     'q3p_router': [I, P, P, I, I, P, P],
     'q3p_topk': [I, P, I, I, F, P, P, P, P],
     'q3p_group': [P, I, I, I, P, P, P, P, P, P],
+    'pf_router': [I, P, I, I, F, P, P, P, P],
     'pf_rms_mul': [P, P, P, P, P, I, I, F, I, P],
     'cam_rms_mul_q8_1': [P, P, P, P, I, I, F, I, P],
     'pf_hc_post_rms': [P, P, P, P, P, P, P, I, I, F, F, I, P],

@@ -1,6 +1,6 @@
-"""Host side of the hyper-connection ("Coder") glue: the methods rms_mul, hc_post_rms, hc_post, hc_mean, add_sum, silu_bf16 and
-to_bf16 of the reference's class Glue (python/caminus/prefill/glue.py:96-313) with its names, argument meaning and refusals,
-over the B200 kernels. The router, GDN, PLE and BF16-matrix methods of that class are outside this library's path."""
+"""Host side of the hyper-connection ("Coder") glue: the methods rms_mul, hc_post_rms, hc_post, hc_mean, router, add_sum, silu_bf16
+and to_bf16 of the reference's class Glue (python/caminus/prefill/glue.py:96-313) with its names, argument meaning and refusals,
+over the B200 kernels. The router-logit matrices, GDN, PLE and BF16-matrix methods of that class are outside this library's path."""
 import ctypes
 
 import torch
@@ -10,7 +10,7 @@ from ..device.cuda import Module
 TPAD = 128                                         # rows of the GEMM operands come in multiples of this
 GLUE_MODULES = {'prefill_glue': 2560, 'prefill_glue_q35': 2048, 'prefill_glue_q35d': 5120}     # code object -> row width
 D_GLUE = GLUE_MODULES['prefill_glue']
-F32, BF16 = torch.float32, torch.bfloat16
+F32, BF16, I32 = torch.float32, torch.bfloat16, torch.int32
 _i, _f, _l = ctypes.c_int, ctypes.c_float, ctypes.c_long
 _NULL = ctypes.c_void_p(0)
 
@@ -83,6 +83,15 @@ class Glue:
         _check(self.dev, 'hc_mean', {'xn': (xn, F32, T * HC * D), 'gate': (gate, F32, T * HC * D), 'out': (out, F32, T * D),
                                      'scale': (scale, F32, T * HC), 'w': (w, F32, HC * D)}, opt=('scale', 'w'))
         self._go('pf_hc_mean', T * D, xn, self._nul(scale), self._nul(w), gate, out, _i(T), _i(HC), _i(D), _f(rs))
+
+    # ---- the router: softmax + top-k of a token's expert logits ---------------------------------------------------------------
+    def router(self, logits, T, E, k, ids, wts, err, clamp=6.103515625e-5):
+        """logits [T, E] -> ids [T, k] int32 and wts [T, k] = p / max(sum of the k, clamp), in rank order (most probable first, ties
+        to the lower index); err: the sticky routing flag word (bit 0: a logit was NaN or infinite)"""
+        T, E, k = int(T), int(E), int(k)
+        if T < 1 or not (1 <= E <= 1024 and 1 <= k <= min(64, E)): raise ValueError(f'router: T {T}, E {E}, k {k}')
+        _check(self.dev, 'router', {'logits': (logits, F32, T * E), 'ids': (ids, I32, T * k), 'wts': (wts, F32, T * k), 'err': (err, I32, 1)})
+        with torch.cuda.device(self.dev): self.m.pf_router((T,), (256,), logits, _i(E), _i(k), _f(clamp), ids, wts, err)
 
     def add_sum(self, a, b, y, n):
         """y[i] += a[i] + b[i] for n values"""

@@ -51,7 +51,10 @@ class Ops:
             with torch.cuda.device(self.dev): yield
 
     def _go(self, mod, kernel, grid, block, *args):
-        with self._here(): getattr(mod, kernel)(grid, block, *args)
+        idx = self.dev.index
+        if idx is None or torch.cuda.current_device() == idx: getattr(mod, kernel)(grid, block, *args)      # (the usual case: no context to enter)
+        else:
+            with torch.cuda.device(self.dev): getattr(mod, kernel)(grid, block, *args)
 
     # ---- embedding rows ---------------------------------------------------------------------------------------------------
     def emb(self, W, rb, vocab, toks, x, n, N):

@@ -159,10 +159,15 @@ int q35t_emb_iq2s(int n, const void * W, int rb, int vocab, const int * toks, fl
  * q3p_topk: per token softmax over E <= 128 logits, the k <= 32 most probable (ties: lower index first), ids int32 [n][k], wts =
  *   p / max(sum of the k, floor_); err |= 1 for a logit that is not finite (n = grid.x).
  * q3p_group: the n * k (token, slot) pairs grouped by expert: xs[i] = token, yd[i] = pair, work items { int e, off, cnt, pad } of at
- *   most 64 pairs, their count in *nitems; an id outside [0, E) sets err |= 2 and counts as expert 0. */
+ *   most 64 pairs, their count in *nitems; an id outside [0, E) sets err |= 2 and counts as expert 0. Every expert's list is in
+ *   ascending pair order (the reference's follows its atomics). One cluster of at most 8 blocks; E <= 1024.
+ * pf_router: the hyper-connection line's softmax + top-k, kernels/prefill_glue.hip:242-308 (T = grid.x); wrapper Glue.router,
+ *   python/caminus/prefill/glue.py:182-192: E <= 1024 logits per token, k <= min(64, E) ids and weights p / max(sum of the k, clamp) in
+ *   rank order; err |= 1 for a logit that is not finite (the ids of such a token are still k distinct experts below E). */
 int q3p_router(int n, const float * h, const float * Wr, int E, int K, float * logits, void * stream);
 int q3p_topk(int n, const float * logits, int E, int k, float floor_, int * ids, float * wts, int * err, void * stream);
 int q3p_group(const int * ids, int npairs, int k, int E, int * xs, int * yd, void * items, int * nitems, int * err, void * stream);
+int pf_router(int T, const float * logits, int E, int k, float clamp, int * ids, float * wts, int * err, void * stream);
 
 /* ---- Q8_1 in the MMQ layout (block_q8_1_mmq, kernels/ggml_mmq/mmq.cuh:63-82): blocks [Kpad / 128][rows] of 144 bytes = 16 bytes of
  * per-32 scales + 128 int8; d_inv = 127 / amax, q = roundf(x * d_inv), d = 1 / d_inv. layout 0 = D4 (four fp32 d), 1 = DS4 (four

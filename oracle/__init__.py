@@ -427,6 +427,27 @@ def topk(logits, k, floor_):
     return ids, wts, int(err[0])
 
 
+def pf_router(logits, k, clamp):
+    """softmax + top-k of the hyper-connection line's router (kernels/prefill_glue.hip:242-308): ids [n, k], wts [n, k], the error word"""
+    lg = _f32(logits); n, E = lg.shape
+    ids = np.empty((n, k), np.int32); wts = np.empty((n, k), np.float32); err = np.zeros(1, np.int32)
+    lib().orc_pf_router(_p(lg), I(E), I(k), F(clamp), _p(ids), _p(wts), _p(err), I(n))
+    return ids, wts, int(err[0])
+
+
+def group(ids, k, E):
+    """the grouping of the (token, slot) pairs by expert (kernels/q3m_prefill.hip:490-513) with every expert's list in ascending pair
+    order (the reference leaves the order inside a list to its atomics and states that it changes no bit downstream):
+    xs, yd [npairs], items [nitems, 4] = (expert, first, count, 0) of at most 64 pairs, the error word (2: an id outside [0, E), which
+    counts as expert 0)"""
+    ids = _c(ids, np.int32).reshape(-1); bad = (ids < 0) | (ids >= E)
+    e = np.where(bad, 0, ids)
+    yd = np.argsort(e, kind='stable').astype(np.int32); xs = (yd // k).astype(np.int32)
+    cnt = np.bincount(e, minlength=E); first = np.concatenate([[0], np.cumsum(cnt)[:-1]])
+    items = [(x, int(first[x]) + 64 * j, min(64, int(cnt[x]) - 64 * j), 0) for x in range(E) for j in range(-(-int(cnt[x]) // 64))]
+    return xs, yd, np.array(items, np.int32).reshape(-1, 4), 2 if bad.any() else 0
+
+
 def embd_rows_iq4xs(table, tok, nvocab, nblk):
     table = _c(table, np.uint8).reshape(-1); tok = _c(tok, np.int32); out = np.empty((tok.size, nblk * 256), np.float32); err = np.zeros(1, np.int32)
     lib().orc_embd_rows_iq4xs(_p(table), _p(tok), I(nvocab), I(tok.size), I(nblk), _p(out), _p(err))

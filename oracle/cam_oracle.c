@@ -806,6 +806,40 @@ void orc_topk(const float * logits, int E, int k, float floor_, int32_t * ids, f
     }
 }
 
+/* pf_router (kernels/prefill_glue.hip:242-308): softmax over E <= 1024 logits by a workgroup of 256 (thread tid owns logits tid + 256 j:
+ * the maximum; v = exp(v - m); the thread's sum over j from 0.0f, the wave butterfly, the eight wave sums in wave order; p = v (1 / sum)),
+ * rank = #{bits(p_j) > bits(p_i) as signed integers, or equal and j < i}, the k <= 64 lowest ranks in rank order, weights
+ * p / max(sum of the k in slot order, clamp); err |= 1 for a logit that is not finite */
+void orc_pf_router(const float * logits, int E, int k, float clamp, int32_t * ids, float * wts, int32_t * err, int n) {
+    for (int t = 0; t < n; t++) {
+        const float * lg = logits + (size_t)t * E; float v[1024]; float m = -INFINITY;
+        for (int e = 0; e < E; e++) { if (!isfinite(lg[e])) *err |= 1; m = fmaxf(m, lg[e]); }
+        float sum = 0.0f;
+        for (int w = 0; w < 8; w++) {
+            float lane_sum[32];
+            for (int l = 0; l < 32; l++) {
+                float s = 0.0f;
+                for (int j = 0; j < 4; j++) { const int e = 32 * w + l + 256 * j; if (e < E) { v[e] = orc_expf(lg[e] - m); s += v[e]; } }
+                lane_sum[l] = s;
+            }
+            const float ws = wave_sum(lane_sum);
+            sum = w == 0 ? ws : sum + ws;
+        }
+        const float inv = 1.0f / sum;
+        for (int e = 0; e < E; e++) v[e] = v[e] * inv;
+        int sel[64];
+        for (int i = 0; i < E; i++) {
+            int rk = 0; const int32_t pi = (int32_t)f2u(v[i]);
+            for (int j = 0; j < E; j++) { const int32_t pj = (int32_t)f2u(v[j]); rk += (pj > pi) || (pj == pi && j < i); }
+            if (rk < k) sel[rk] = i;
+        }
+        float ws = 0.0f;
+        for (int j = 0; j < k; j++) ws = ws + v[sel[j]];
+        ws = fmaxf(ws, clamp);
+        for (int j = 0; j < k; j++) { ids[(size_t)t * k + j] = sel[j]; wts[(size_t)t * k + j] = v[sel[j]] / ws; }
+    }
+}
+
 /* ==== the IQ4 row gathers of the host feed (kernels/prefill_feed.hip:24-54; host decoders python/caminus/own_dequant.py iq4_xs) ====
  * The 16 values of a 4-bit index are ggml's IQ4_NL codebook (part of the format's definition). IQ4_NL block: f16 d, 16 bytes of
  * nibbles (low nibble = value j, high = value j + 16), y = d * kvalue. IQ4_XS block (136 bytes, 256 values): f16 d, u16 scales_h,

@@ -47,6 +47,23 @@ def _rank(rank, world, port, T, N, out):
         dist.barrier()
         fused.close()
         dist.barrier()
+        # one exchange per rank serving two norms (a model's layers): one exported buffer, one tag sequence, calls alternating
+        ex = D.TPExchange(T, device=dev)
+        na, nb = D.TPRmsNormFused(norm.nw, N, exchange=ex), D.TPRmsNormFused((norm.nw * 0.5).contiguous(), N, exchange=ex)
+        norm_b = D.TPRmsNorm(nb.nw, N, 1e-6)
+        for rep in range(4):
+            fn, two = (na, norm) if rep % 2 == 0 else (nb, norm_b)
+            xa = x_in.clone(); xb = xa.clone()
+            parts = [torch.empty(T, device=dev) for _ in range(world)]
+            dist.all_gather(parts, two.partial(xa, rs).clone())
+            tot = torch.zeros(T, device=dev)
+            for p_ in parts: tot = tot + p_
+            h_ref = two.apply(xa, tot, d=rs)
+            h_f = fn(xb, rs); fn.check()
+            fused_ok = fused_ok and torch.equal(h_f, h_ref) and torch.equal(xa, xb) and ex.tag == rep + 1
+        dist.barrier()
+        ex.close()
+        dist.barrier()
         # the unsharded kernel on this rank's rows of the full-width batch (row sharding: no collective)
         ra, rb = D.row_shard(T, rank, world)
         xr = torch.from_numpy(x0[ra:rb].copy()).to(dev)

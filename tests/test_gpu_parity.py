@@ -498,6 +498,17 @@ def test_tp_rms_fused_single_rank_is_the_unsharded_norm():
         xo, ho = oracle.add_rms_f16(x0, w, 1e-6, r0)
         assert same(x, xo) and same(h, ho)
     with pytest.raises(ValueError): F_(cu(np.zeros((T + 1, N), np.float16)))
+    # a call without rows launches nothing and leaves the tag alone (two launches in a row must not share a half of the buffer)
+    before = F_.tag; F_(torch.zeros(0, N, dtype=torch.float16, device=DEV)); assert F_.tag == before
+    # two norms over one exchange (one buffer, one tag sequence), called alternately
+    ex = D.TPExchange(T, group=D.SOLO, device=DEV)
+    wa, wb = cu(w), cu((w * 0.5).astype(np.float32)); Fa, Fb = D.TPRmsNormFused(wa, N, exchange=ex), D.TPRmsNormFused(wb, N, exchange=ex)
+    for rep in range(4):
+        Fn, wn = (Fa, w) if rep % 2 == 0 else (Fb, (w * 0.5).astype(np.float32))
+        x = cu(x0); h = Fn(x, cu(r0)); Fn.check()
+        xo, ho = oracle.add_rms_f16(x0, wn, 1e-6, r0)
+        assert same(x, xo) and same(h, ho) and ex.tag == rep + 1
+    ex.close()
     for N2 in (2048, 640, 1288):                                       # rows held in registers (one row / two rows deep), a short last chunk
         x0, r0, w = synth.add_rms_inputs(T, N2, seed=N2, dtype=np.float16)
         F2 = D.TPRmsNormFused(cu(w), N2, T, 1e-6, device=DEV)

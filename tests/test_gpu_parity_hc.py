@@ -361,7 +361,7 @@ def test_router_topk_group():
     O.router(cu(hh), cu(Wr), E, D, lg, n)
     lo = oracle.router(hh, Wr)
     assert same(lg, lo)
-    for n2, E2, D2 in ((5, 128, 2048), (70, 61, 256), (64, 4, 128)):          # few tokens (a block per token); tiles that overhang n and E
+    for n2, E2, D2 in ((5, 128, 2048), (70, 61, 256), (64, 4, 128), (1, 128, 2048), (63, 13, 384), (2, 1, 128)):          # few tokens (a block per token); tiles that overhang n and E
         h2 = g.standard_normal((n2, D2)).astype(np.float32); W2 = g.standard_normal((E2, D2)).astype(np.float32)
         l2 = torch.zeros(n2, E2, device=DEV); hd, wd = cu(h2), cu(W2)
         O.router(hd, wd, E2, D2, l2, n2)
@@ -380,16 +380,63 @@ def test_router_topk_group():
     O.check_flags(err)
     use = g.choice(E, 12, replace=False)
     ids_np = np.stack([g.choice(use, k, replace=False) for _ in range(n)]).astype(np.int32)
-    bound = q3m_ops.items_bound(n * k, E)
-    xs, yd = (torch.zeros(n * k, dtype=torch.int32, device=DEV) for _ in range(2))
-    items = torch.zeros(bound, 4, dtype=torch.int32, device=DEV); nitems = torch.zeros(1, dtype=torch.int32, device=DEV); err.zero_()
-    O.group(cu(ids_np.reshape(-1)), n * k, k, E, xs, yd, items, nitems, err)
-    it = items[:int(nitems.item())].cpu().numpy(); cnt = np.bincount(ids_np.reshape(-1), minlength=E); ydn = yd.cpu().numpy()
-    assert int(err.item()) == 0 and int(nitems.item()) == sum(-(-c // 64) for c in cnt) and sorted(ydn.tolist()) == list(range(n * k))
-    assert all(ids_np.reshape(-1)[ydn[i0:i0 + c]].tolist() == [e] * c for e, i0, c, _ in it) and np.array_equal(xs.cpu().numpy(), ydn // k)
-    bad = ids_np.reshape(-1).copy(); bad[10] = E + 5; err.zero_()
-    O.group(cu(bad), n * k, k, E, xs, yd, items, nitems, err)
-    assert int(err.item()) & 2
+    _group_case(O, ids_np.reshape(-1), k, E)
+    bad = ids_np.reshape(-1).copy(); bad[10] = E + 5; bad[77] = -3
+    assert _group_case(O, bad, k, E) & 2
+
+
+def _group_case(O, ids_np, k, E):
+    """one grouping launch held to the oracle on every word: xs, yd, the items and their count, the error word (returned)"""
+    from caminus_b200.prefill import q3m_ops
+    npairs = ids_np.size; bound = q3m_ops.items_bound(npairs, E)
+    xs, yd = (torch.full((max(npairs, 1),), -7, dtype=torch.int32, device=DEV) for _ in range(2))
+    items = torch.full((bound + 1, 4), -7, dtype=torch.int32, device=DEV); nitems = torch.full((1,), -7, dtype=torch.int32, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    idd = cu(ids_np) if npairs else torch.zeros(1, dtype=torch.int32, device=DEV)
+    O.group(idd, npairs, k, E, xs, yd, items, nitems, err)
+    xo, yo, io, eo = oracle.group(ids_np, k, E)
+    ni = int(nitems.item())
+    assert ni == len(io) <= bound and int(err.item()) == eo
+    assert np.array_equal(xs.cpu().numpy()[:npairs], xo) and np.array_equal(yd.cpu().numpy()[:npairs], yo)
+    assert np.array_equal(items.cpu().numpy()[:ni], io) and (items.cpu().numpy()[ni:] == -7).all()      # nothing written past the count
+    return int(err.item())
+
+
+@pytest.mark.parametrize('npairs,k,E', [(0, 8, 128), (1, 8, 128), (31, 1, 7), (65536, 8, 128), (65537, 8, 1024), (8191, 7, 1000),
+                                        (200000, 8, 128), (300001, 10, 256), (4096, 8, 1)])
+def test_group_sizes(npairs, k, E):
+    """the grouping over its launch shapes: no pair, one pair, odd counts, one to eight blocks in the cluster, runs longer than the
+    eight steps a warp keeps in registers, 1 to 1024 experts, lists skewed to a few experts and lists that stay empty"""
+    from caminus_b200.prefill import q3m_ops
+    O = q3m_ops.Ops(DEV); g = np.random.default_rng(npairs + E)
+    ids = g.integers(0, E, npairs).astype(np.int32)
+    if npairs > 100: ids[g.random(npairs) < 0.5] = E // 3                       # half of all pairs under one expert: hundreds of items for it
+    if E > 16: ids[ids == 5] = 6                                                 # an expert nobody routes to
+    assert _group_case(O, ids, k, E) == 0
+    assert _group_case(O, ids, k, E) == 0                                        # and again: nothing is carried between launches
+
+
+@pytest.mark.parametrize('T,E,k', [(777, 256, 10), (5, 128, 8), (64, 1000, 64), (33, 33, 5), (2048, 512, 12), (9, 1024, 33), (3, 8, 8)])
+def test_pf_router(T, E, k):
+    """the hyper-connection line's softmax + top-k (a warp per token here, a workgroup per token in the reference): ids and weights are
+    the oracle's bytes, with exact ties, equal rows and a row of large logits; a row with a logit that is not finite sets bit 0 and
+    still carries k distinct experts below E"""
+    gl = G.Glue(DEV); g = np.random.default_rng(T + E + k)
+    lg = (g.standard_normal((T, E)) * 3).astype(np.float32)
+    lg[0, min(7, E - 1)] = lg[0, 2] = lg[0].max() + 1.0; lg[1, :] = 0.5; lg[2] *= 40
+    ids = torch.full((T, k), -1, dtype=torch.int32, device=DEV); wts = torch.zeros(T, k, device=DEV); err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    gl.router(cu(lg), T, E, k, ids, wts, err)
+    io, wo, eo = oracle.pf_router(lg, k, 6.103515625e-5)
+    assert int(err.item()) == 0 == eo and np.array_equal(ids.cpu().numpy(), io) and same(wts, wo)
+    if T > 4:
+        lg[3, 1] = np.nan; lg[4, 0] = -np.inf
+        gl.router(cu(lg), T, E, k, ids, wts, err)
+        got = ids.cpu().numpy()
+        assert int(err.item()) == 1 and all(len(set(r.tolist())) == k and r.min() >= 0 and r.max() < E for r in got)
+        keep = np.ones(T, bool); keep[3:5] = False
+        assert np.array_equal(got[keep], io[keep]) and same(wts[torch.from_numpy(keep).to(DEV)], wo[keep])
+    with pytest.raises(ValueError): gl.router(cu(lg), T, E, E + 1, ids, wts, err)
+    with pytest.raises(ValueError): gl.router(cu(lg), T, E, k, ids[:-1], wts, err)
 
 
 def test_iq4_row_gathers(golden):

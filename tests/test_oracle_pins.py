@@ -201,3 +201,28 @@ def test_iq2s_rows_bitwise(golden):
     toks = np.array([0, 7, 22, -2, 50, 3], np.int32)
     x = oracle.emb_rows_iq2s(T, nblk * 82, vocab, toks, nblk * 256, oracle.pack_iq2s_grid(f['grid']))
     assert np.array_equal(x.view(np.uint32), f['rows'][np.clip(toks, 0, vocab - 1)].view(np.uint32))
+
+
+def test_numpy_path_against_the_fixtures(golden):
+    """the NumPy restatement of the reference's host path (the benchmark's second CPU leg) against what the reference's own code
+    produced: Q4_K rows and Q8_1 scales / codes bit for bit, the norms and the rotation within float32 rounding of float64"""
+    from oracle import numpy_path as NP
+    f = golden('q4k_rows')
+    assert np.array_equal(NP.q4k_rows(f['W'], f['toks']).view(np.uint32), f['want'].view(np.uint32))
+    f = golden('q8_1')
+    d, s, q = NP.q8_1_blocks(f['x'])
+    assert np.array_equal(d.view(np.uint16), f['d16'].view(np.uint16)) and np.array_equal(q, f['q'])
+    d, s, q = NP.q8_1_blocks(f['x'][:int(f['n_odd'])])
+    assert np.array_equal(d.view(np.uint16), f['d16_odd'].view(np.uint16)) and np.array_equal(q, f['q_odd'])
+    f = golden('swiglu')
+    h = NP.silu(f['gate']) * f['up'].astype(np.float32)
+    assert np.abs(h - f['h64']).max() <= 1e-6 * np.abs(f['h64']).max()
+    d, s, q = NP.swiglu_q8_1(f['gate'], f['up'])
+    assert (np.abs(q.astype(int) - f['q'].astype(int)) <= 1).all() and (q != f['q']).mean() < 2e-3      # the reference's flip rule: a code may move by one at a .5 boundary
+    f = golden('add_rms')
+    xs, hh = NP.add_rms_f32(f['x1'], f['r1'], f['w1'])
+    assert np.abs(xs - f['s1']).max() <= 1e-6 * np.abs(f['s1']).max() and np.abs(hh - f['h1']).max() <= 2e-6 * np.sqrt((f['h1'] ** 2).mean()) * 10
+    f = golden('qk_rope'); nh, nkv = int(f['nh']), int(f['nkv']); par = f['par']
+    q = f['qkv'][:, :nh * 128].reshape(-1, nh, 128)
+    got = NP.qk_norm_rope_f64(q, par[:128], f['pos'], theta=1e6, eps=float(par[257]))
+    assert np.abs(got - f['q_plain']).max() <= 1e-12

@@ -154,3 +154,43 @@ def test_router_glue_as_the_reference_tests_it():
     assert np.array_equal(ids[~near], rid[~near]) and np.abs(wts - rw)[~near].max() < 1e-6
     lg[5, 2] = np.nan
     assert oracle.topk(lg, 8, 6.103515625e-5)[2] & 1
+
+
+@pytest.mark.parametrize('E,k', [(256, 10), (128, 8), (1000, 64), (33, 5), (1024, 32)])
+def test_pf_router_float64_and_rank_order(E, k):
+    """the hyper-connection line's softmax + top-k against a float64 softmax: the k most probable experts in rank order (the lower
+    index first among equal probabilities, which the planted ties exercise), weights within 1e-5 of p / sum of the k"""
+    g = np.random.default_rng(E + k); n = 40
+    lg = (g.standard_normal((n, E)) * 3).astype(np.float32)
+    lg[3, 7] = lg[3, 2] = lg[3].max() + 1.0                        # an exact tie at the top: index 2 before index 7
+    lg[4, :] = 0.5                                                   # all equal: experts 0 .. k - 1 in order
+    ids, wts, err = oracle.pf_router(lg, k, 6.103515625e-5)
+    assert err == 0 and ids[3, 0] == 2 and ids[3, 1] == 7 and ids[4].tolist() == list(range(k))
+    p = np.exp(lg.astype(np.float64) - lg.max(-1, keepdims=True)); p /= p.sum(-1, keepdims=True)
+    for t in range(n):
+        assert len(set(ids[t].tolist())) == k and ids[t].min() >= 0 and ids[t].max() < E
+        order = np.lexsort((np.arange(E), -p[t]))[:k]
+        agree = ids[t] == order
+        assert agree.all() or np.abs(p[t][ids[t][~agree]] / p[t][order[~agree]] - 1).max() < 1e-6     # float32 may swap near-equal neighbours
+        w64 = p[t][ids[t]] / max(p[t][ids[t]].sum(), 6.103515625e-5)
+        assert np.abs(wts[t] / w64 - 1).max() < 1e-5
+    lg[9, 5] = np.inf
+    assert oracle.pf_router(lg, k, 6.103515625e-5)[2] == 1
+    if E <= 128 and k <= 32:                                          # a workgroup per token or a wave per token: the same experts
+        i2, w2, _ = oracle.topk(lg[:9], k, 6.103515625e-5)
+        assert np.array_equal(i2, ids[:9]) and np.abs(w2 / wts[:9] - 1).max() < 1e-6
+
+
+def test_group_lists_and_items():
+    """the grouping restated with numpy: every pair once under its expert, lists in ascending pair order, items of at most 64"""
+    g = np.random.default_rng(3); n, k, E = 300, 8, 128
+    ids = np.stack([g.choice(E // 4, k, replace=False) for _ in range(n)]).astype(np.int32).reshape(-1)
+    xs, yd, items, err = oracle.group(ids, k, E)
+    assert err == 0 and sorted(yd.tolist()) == list(range(n * k)) and np.array_equal(xs, yd // k)
+    cnt = np.bincount(ids, minlength=E)
+    assert len(items) == sum(-(-c // 64) for c in cnt) and items[:, 2].max() <= 64 and items[:, 2].sum() == n * k
+    for e, first, c, z in items:
+        assert z == 0 and (ids[yd[first:first + c]] == e).all() and (np.diff(yd[first:first + c]) > 0).all()
+    bad = ids.copy(); bad[5] = -1; bad[6] = E
+    xs2, yd2, items2, err2 = oracle.group(bad, k, E)
+    assert err2 == 2 and items2[0, 0] == 0 and 5 in yd2[:items2[0, 2]].tolist()
