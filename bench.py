@@ -240,12 +240,24 @@ def single_op_lines(torch, dev, peak, only=(), headline=False):
         except Exception as e:     # (capture refused: report why, keep the bench alive)
             return f'{type(e).__name__}: {e}'[:160]
 
-    def line(name, nbytes, sec, units, unit):
+    def line(name, nbytes, sec, units, unit, copy_ref=False, graph_fn=None):
         if headline and name not in HEADLINE_OPS: return
         if only and not any(o in name for o in only): return
         med, mn = sec()
         out[name] = {'bytes': nbytes, 'us_median': med * 1e6, 'us_min': mn * 1e6, 'gbs': nbytes / med / 1e9, 'frac_of_peak': nbytes / med / 1e9 / peak,
                      'frac_of_8tbs': nbytes / med / 8e12, unit: units / med}
+        if graph_fn is not None:      # a launch this short can be bounded by the host's launch rate: the same launches replayed from a CUDA graph
+            gs = graphed(graph_fn, 40)
+            out[name]['us_in_cuda_graph'] = gs * 1e6 if isinstance(gs, float) else gs
+            if isinstance(gs, float): out[name]['frac_of_peak_in_cuda_graph'] = nbytes / gs / 1e9 / peak
+        if copy_ref:      # a launch this short does not reach the bandwidth of a long copy: a plain device copy moving the same bytes, timed the same way
+            half = nbytes // 2 // 16 * 16
+            srcs = [torch.empty(half, dtype=torch.uint8, device=dev) for _ in range(4)]; dsts = [torch.empty(half, dtype=torch.uint8, device=dev) for _ in range(4)]
+            cmed, _ = timed(lambda i: dsts[i].copy_(srcs[i]), rot=4)()
+            out[name]['us_plain_copy_same_bytes'] = cmed * 1e6; out[name]['frac_of_plain_copy_same_bytes'] = cmed / med
+            if graph_fn is not None:
+                cg = graphed(lambda i: dsts[i % 4].copy_(srcs[i % 4]), 40)
+                if isinstance(cg, float): out[name]['us_plain_copy_in_cuda_graph'] = cg * 1e6
 
     g = torch.Generator(device=dev); g.manual_seed(0)
     # config 1: add + RMSNorm fp32, hidden 2048: T = 1 (latency) and a T sweep
@@ -267,7 +279,8 @@ def single_op_lines(torch, dev, peak, only=(), headline=False):
     T = 4096
     qs = [torch.randn(T, 32, 128, device=dev, generator=g).half() for _ in range(4)]; ks = [torch.randn(T, 4, 128, device=dev, generator=g).half() for _ in range(4)]
     par = torch.from_numpy(synth.rope_par()).to(dev)
-    line('qk_rope_f16_T4096', T * 36 * 128 * 4 + 1032, timed(lambda i: glue.qk_rope_f16(qs[i], ks[i], par, 0), rot=4), T, 'tokens_per_s')
+    line('qk_rope_f16_T4096', T * 36 * 128 * 4 + 1032, timed(lambda i: glue.qk_rope_f16(qs[i], ks[i], par, 0), rot=4), T, 'tokens_per_s', copy_ref=True,
+         graph_fn=lambda i: glue.qk_rope_f16(qs[i % 4], ks[i % 4], par, 0))
     del qs, ks
     # config 3: SwiGLU + Q8_1, T = 8192, I = 25600
     T = 8192
@@ -283,7 +296,8 @@ def single_op_lines(torch, dev, peak, only=(), headline=False):
     W[:, :, 0:4] = (torch.randn(vocab, 8, 2, device=dev, generator=g) * 1e-3).abs().half().view(torch.uint8).view(vocab, 8, 4)
     toks = torch.randint(0, vocab, (n,), device=dev, dtype=torch.int32, generator=g)
     xo = [torch.empty(n, N, device=dev) for _ in range(2)]
-    line('q4k_get_rows_16384x2048', n * (4 + 1152 + 8192), timed(lambda i: O.emb(W.view(-1), 1152, vocab, toks, xo[i], n, N), rot=2), n, 'rows_per_s')
+    line('q4k_get_rows_16384x2048', n * (4 + 1152 + 8192), timed(lambda i: O.emb(W.view(-1), 1152, vocab, toks, xo[i], n, N), rot=2), n, 'rows_per_s', copy_ref=True,
+         graph_fn=lambda i: O.emb(W.view(-1), 1152, vocab, toks, xo[i % 2], n, N))
     del W, toks, xo
     if headline: return out
     # ---- the later rows of the path (hyper-connection glue, MMQ layout, Q8_0 KV form, the training line's quantiser) ----

@@ -14,6 +14,8 @@
 // a butterfly step hold the same bits), without a block-wide barrier.
 #include "cam_common.cuh"
 
+#include <cstdlib>
+
 #include <mutex>
 
 namespace {
@@ -466,7 +468,11 @@ __global__ void __launch_bounds__(128, 2) add_rms_f16_reg_kernel(uint16_t * __re
 
 template <int CH>
 int launch_f16_reg(uint16_t * x, const uint16_t * d, const float * nw, float eps, uint16_t * h16, int n, cudaStream_t stream) {
-    const int grid = cam_resident_grid(add_rms_f16_reg_kernel<CH>, 128, 0, ((long)n + 3) / 4);
+    // eight times the resident blocks (or a block per four rows, if fewer): a finished block's successor starts with its rows' loads
+    // at once, which measured 424 us against 437 us for exactly the resident blocks looping over rows (65536 rows of 5120)
+    const long want = ((long)n + 3) / 4;
+    const long cap = 8L * cam_resident_grid(add_rms_f16_reg_kernel<CH>, 128, 0, want);
+    const int grid = (int)(want < cap ? want : cap);
     add_rms_f16_reg_kernel<CH><<<grid, 128, 0, stream>>>(x, d, nw, eps, h16, n);
     return (int)cudaGetLastError();
 }

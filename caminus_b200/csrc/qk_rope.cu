@@ -232,47 +232,75 @@ __global__ void __launch_bounds__(384) qk_rope_kernel(const RopeArgs A) {
 }
 
 // ---- the fp16-storage form (cam_qk_rope_f16) without a block-wide step per token -----------------------------------------------------
-// A warp owns a token and walks its heads 2 P at a time (a half-warp per head, as above), straight from global memory into registers:
-// the next round's 16 P bytes per lane are requested before the current round is computed, so a warp keeps two rounds of loads in flight
-// and nothing in the token loop waits on another warp (the staged kernel above holds a block at two barriers per token, which a batch
-// of a few thousand tokens, four or five per block, never amortises). The 64 frequencies are formed once per block (the only
-// barrier); a token's cosines and sines are formed by its warp: each half-warp computes two of a lane's four angles and the halves
-// swap. The arithmetic is written with the packed fp32 instructions where two statements run on neighbouring dims (the norm's two
-// products, the rotation): the same IEEE operations, half the instructions. Sums and statement order are the staged kernel's.
-// In place (qo = q, ko = k) is safe: a lane stores exactly the addresses it loaded, after loading them.
+// A warp owns a token and walks first its q heads, then its k heads, 2 P at a time (a half-warp per head, as above; nh and nkv even,
+// so a round is all q or all k and a pair of heads is whole). Every lane copies exactly the two 8-byte pieces of a head that it will
+// read (dims 4 l .. 4 l + 3 and 64 + 4 l ..) into the warp's own ring in shared memory with cp.async, RING - 1 rounds ahead, so its own
+// copy groups are the only synchronisation: nothing in the token loop waits on another warp (the staged kernel above holds a block at
+// two barriers per token, which a batch of a few thousand tokens, four or five per block, never amortises), and a warp keeps RING - 1
+// rounds of loads in flight without holding them in registers. A round's addresses are one base (q or k of the token) plus constants.
+// The 64 frequencies are formed once per block (the only barrier; the first rounds' copies are already flying); a token's cosines and
+// sines are formed by its warp: each half-warp computes two of a lane's four angles and the halves swap. The arithmetic is written
+// with the packed fp32 instructions where two statements run on neighbouring dims (the norm's two products, the rotation): the same
+// IEEE operations, half the instructions. Sums and statement order are the staged kernel's. In place (qo = q, ko = k) is safe: a lane
+// stores exactly the addresses it copied, after its copy has landed.
+constexpr int ROPE_RING = 4;
+
+CAM_DEV void cp_async8_s(uint32_t smem_addr, const void * gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(smem_addr), "l"(gmem) : "memory");
+}
+CAM_DEV void cp_async16_s(uint32_t smem_addr, const void * gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gmem) : "memory");
+}
+CAM_DEV uint2 lds64(uint32_t smem_addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(smem_addr));
+    return v;
+}
+
 template <int P>
-__global__ void __launch_bounds__(128) qk_rope_f16_warp_kernel(const RopeArgs A, int rounds) {
+__global__ void __launch_bounds__(128) qk_rope_f16_warp_kernel(const RopeArgs A) {
     __shared__ __align__(16) float wq[128], wk[128], freq[64];
+    __shared__ __align__(16) unsigned char ring_all[4 * ROPE_RING * P * 512];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int nh = A.nh, nkv = A.nkv, H = nh + nkv;
+    const int nh = A.nh, nkv = A.nkv;
+    const int rq_n = (nh + 2 * P - 1) / (2 * P), rounds = rq_n + (nkv + 2 * P - 1) / (2 * P);      // q rounds, then k rounds
+    const int hw = lane >> 4, l16 = lane & 15;
+    const int lane_off = hw * 256 + l16 * 8;                             // bytes: this lane's low piece inside a pair of heads (the high piece: + 128)
+    const unsigned char * const qin = reinterpret_cast<const unsigned char *>(A.in0), * const kin = reinterpret_cast<const unsigned char *>(A.in1);
+    unsigned char * const qout = reinterpret_cast<unsigned char *>(A.out0), * const kout = reinterpret_cast<unsigned char *>(A.out1);
+    const int tw = blockIdx.x * 4 + warp, stride = gridDim.x * 4;
+    const int ntok = tw < A.n ? (A.n - tw + stride - 1) / stride : 0;
+    const size_t qrow = (size_t)nh * 256, krow = (size_t)nkv * 256;      // bytes per token
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_all) + warp * (ROPE_RING * P * 512) + lane_off;
+    // the round to request next: token kq (its q and k rows), round rq, ring slot sq
+    int rq = 0, kq = 0, sq = 0;
+    const unsigned char * rq_q = qin + (size_t)tw * qrow + lane_off, * rq_k = kin + (size_t)tw * krow + lane_off;
+    auto request = [&]() {                                               // one copy group per call (empty past the warp's last token)
+        if (kq < ntok) {
+            const bool isq = rq < rq_n;
+            const int h0 = isq ? rq * 2 * P : (rq - rq_n) * 2 * P, np = min(P, ((isq ? nh : nkv) - h0) >> 1);
+            const unsigned char * src = (isq ? rq_q : rq_k) + h0 * 256;
+            const uint32_t dst = ring + sq * (P * 512);
+#pragma unroll
+            for (int p = 0; p < P; p++)
+                if (p < np) { cp_async8_s(dst + p * 512, src + p * 512); cp_async8_s(dst + p * 512 + 128, src + p * 512 + 128); }
+        }
+        cp_async_commit();
+        if (++rq == rounds) { rq = 0; kq++; rq_q += (size_t)stride * qrow; rq_k += (size_t)stride * krow; }
+        sq = sq + 1 == ROPE_RING ? 0 : sq + 1;
+    };
+#pragma unroll
+    for (int i = 0; i < ROPE_RING - 1; i++) request();
     wq[tid] = __ldg(A.par + tid); wk[tid] = __ldg(A.par + 128 + tid);
     if (tid < 64) freq[tid] = A.yarn ? __ldg(A.par + 258 + tid) : cam_powi(__ldg(A.par + 256), tid);
     const float eps = __ldg(A.par + 257), mscale = A.yarn ? __ldg(A.par + 322) : 1.0f;
     __syncthreads();
-    const int hw = lane >> 4, l16 = lane & 15;
     const float f0 = freq[4 * l16 + 2 * hw], f1 = freq[4 * l16 + 2 * hw + 1];      // this half-warp's two of the lane's four angles
-    const uint16_t * const qin = reinterpret_cast<const uint16_t *>(A.in0), * const kin = reinterpret_cast<const uint16_t *>(A.in1);
-    const int tw = blockIdx.x * 4 + warp, stride = gridDim.x * 4;
-    const int ntok = tw < A.n ? (A.n - tw + stride - 1) / stride : 0;
-    uint2 cur[P][2], nxt[P][2];
-    auto request = [&](int kk, int rr, uint2 (&v)[P][2]) {               // round rr of this warp's token kk (nothing past its last token)
-        const int t = tw + kk * stride, h0 = rr * 2 * P;
-#pragma unroll
-        for (int p = 0; p < P; p++) {
-            const int hy = h0 + 2 * p + hw;
-            if (kk < ntok && hy < H) {
-                const uint16_t * src = (hy < nh ? qin + ((size_t)t * nh + hy) * 128 : kin + ((size_t)t * nkv + (hy - nh)) * 128) + 4 * l16;
-                v[p][0] = *reinterpret_cast<const uint2 *>(src); v[p][1] = *reinterpret_cast<const uint2 *>(src + 64);
-            } else { v[p][0] = make_uint2(0u, 0u); v[p][1] = make_uint2(0u, 0u); }
-        }
-    };
-    request(0, 0, cur);
     f32x2 cc[2], sn[2], nsn[2];                                          // cos, sin, -sin of dims (4 l16, + 1) and (+ 2, + 3)
-    int r = 0, k = 0;
-    while (k < ntok) {
-        const int rn = r + 1 == rounds ? 0 : r + 1, kn = rn ? k : k + 1;
-        request(kn, rn, nxt);
-        const int t = tw + k * stride;
+    int r = 0, sc = 0, t = tw;
+    unsigned char * out_q = qout + (size_t)tw * qrow + lane_off, * out_k = kout + (size_t)tw * krow + lane_off;
+    for (int k = 0; k < ntok;) {
+        request();
         if (r == 0) {
             const float pos = (float)(A.pos0 + t);
             float s0, c0, s1, c1;
@@ -281,14 +309,19 @@ __global__ void __launch_bounds__(128) qk_rope_f16_warp_kernel(const RopeArgs A,
             const float oc0 = __shfl_xor_sync(CAM_FULL, c0, 16), os0 = __shfl_xor_sync(CAM_FULL, s0, 16);
             const float oc1 = __shfl_xor_sync(CAM_FULL, c1, 16), os1 = __shfl_xor_sync(CAM_FULL, s1, 16);
             const float ca = hw ? oc0 : c0, cb = hw ? oc1 : c1, cc_ = hw ? c0 : oc0, cd = hw ? c1 : oc1;      // dims 0, 1 come from the lower half-warp
-            const float sa = hw ? os0 : s0, sb = hw ? os1 : s1, sc = hw ? s0 : os0, sd = hw ? s1 : os1;
-            cc[0] = pk2(ca, cb); cc[1] = pk2(cc_, cd); sn[0] = pk2(sa, sb); sn[1] = pk2(sc, sd); nsn[0] = pk2(-sa, -sb); nsn[1] = pk2(-sc, -sd);
+            const float sa = hw ? os0 : s0, sb = hw ? os1 : s1, sc_ = hw ? s0 : os0, sd = hw ? s1 : os1;
+            cc[0] = pk2(ca, cb); cc[1] = pk2(cc_, cd); sn[0] = pk2(sa, sb); sn[1] = pk2(sc_, sd); nsn[0] = pk2(-sa, -sb); nsn[1] = pk2(-sc_, -sd);
         }
-        const int h0 = r * 2 * P;
+        cp_async_wait<ROPE_RING - 1>();                                  // this round's pieces have landed (the later ones may still fly)
+        const bool isq = r < rq_n;
+        const int h0 = isq ? r * 2 * P : (r - rq_n) * 2 * P, np = min(P, ((isq ? nh : nkv) - h0) >> 1);
+        const uint32_t src = ring + sc * (P * 512);
         f32x2 xl[P][2], xh[P][2]; float tot[P];
 #pragma unroll
         for (int p = 0; p < P; p++) {
-            const float2 a = h2_to_f2(cur[p][0].x), b = h2_to_f2(cur[p][0].y), c = h2_to_f2(cur[p][1].x), e = h2_to_f2(cur[p][1].y);
+            uint2 vlo = make_uint2(0u, 0u), vhi = make_uint2(0u, 0u);
+            if (p < np) { vlo = lds64(src + p * 512); vhi = lds64(src + p * 512 + 128); }
+            const float2 a = h2_to_f2(vlo.x), b = h2_to_f2(vlo.y), c = h2_to_f2(vhi.x), e = h2_to_f2(vhi.y);
             // the head's sum of squares: per lane an fma chain over its 4 low and its 4 high dims, then the half-warp butterfly
             float sl = ffma(a.x, a.x, 0.0f), sh = ffma(c.x, c.x, 0.0f);
             sl = ffma(a.y, a.y, sl); sh = ffma(c.y, c.y, sh); sl = ffma(b.x, b.x, sl); sh = ffma(e.x, e.x, sh); sl = ffma(b.y, b.y, sl); sh = ffma(e.y, e.y, sh);
@@ -299,39 +332,174 @@ __global__ void __launch_bounds__(128) qk_rope_f16_warp_kernel(const RopeArgs A,
             xl[p][0] = pk2(a.x, a.y); xl[p][1] = pk2(b.x, b.y); xh[p][0] = pk2(c.x, c.y); xh[p][1] = pk2(e.x, e.y);
         }
         // lane j < 2 P computes the scale of head h0 + j (pass j >> 1, half-warp j & 1); then every lane fetches its heads' scales
-        float mine = 1.0f;
+        float own = 1.0f;
 #pragma unroll
         for (int p = 0; p < P; p++) {
             const float v = __shfl_sync(CAM_FULL, tot[p], 16 * (lane & 1));
-            if ((lane >> 1) == p) mine = v;
+            if ((lane >> 1) == p) own = v;
         }
-        const float scale_mine = cam_rsqrt(fadd(fmul(mine, 0.0078125f), eps));      // tot / 128: the same bits as the division
+        const float scale_own = cam_rsqrt(fadd(fmul(own, 0.0078125f), eps));      // tot / 128: the same bits as the division
+        const float * wn = (isq ? wq : wk) + 4 * l16;
+        const float4 wlo = *reinterpret_cast<const float4 *>(wn), whi = *reinterpret_cast<const float4 *>(wn + 64);
+        const f32x2 wl2[2] = {pk2(wlo.x, wlo.y), pk2(wlo.z, wlo.w)}, wh2[2] = {pk2(whi.x, whi.y), pk2(whi.z, whi.w)};
+        unsigned char * const o = (isq ? out_q : out_k) + h0 * 256;
 #pragma unroll
         for (int p = 0; p < P; p++) {
-            const float scale = __shfl_sync(CAM_FULL, scale_mine, 2 * p + hw);
-            const int hy = h0 + 2 * p + hw;
-            if (hy < H) {
-                const bool isq = hy < nh;
-                const float * wn = (isq ? wq : wk) + 4 * l16;
-                const float4 wlo = *reinterpret_cast<const float4 *>(wn), whi = *reinterpret_cast<const float4 *>(wn + 64);
+            const float scale = __shfl_sync(CAM_FULL, scale_own, 2 * p + hw);
+            if (p < np) {
                 const f32x2 s2 = pk2(scale, scale);
-                uint16_t * o = (isq ? A.out0 + ((size_t)t * nh + hy) * 128 : A.out1 + ((size_t)t * nkv + (hy - nh)) * 128) + 4 * l16;
                 uint32_t olo[2], ohi[2];
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
-                    const f32x2 x0 = mul2(mul2(s2, xl[p][c]), c ? pk2(wlo.z, wlo.w) : pk2(wlo.x, wlo.y));
-                    const f32x2 x1 = mul2(mul2(s2, xh[p][c]), c ? pk2(whi.z, whi.w) : pk2(whi.x, whi.y));
+                    const f32x2 x0 = mul2(mul2(s2, xl[p][c]), wl2[c]), x1 = mul2(mul2(s2, xh[p][c]), wh2[c]);
                     const f32x2 ylo = fma2(x0, cc[c], mul2(x1, nsn[c])), yhi = fma2(x1, cc[c], mul2(x0, sn[c]));
                     olo[c] = f2_to_h2(lo2(ylo), hi2(ylo)); ohi[c] = f2_to_h2(lo2(yhi), hi2(yhi));
                 }
-                st64_stream(o, make_uint2(olo[0], olo[1]));
-                st64_stream(o + 64, make_uint2(ohi[0], ohi[1]));
+                st64_stream(o + p * 512, make_uint2(olo[0], olo[1]));
+                st64_stream(o + p * 512 + 128, make_uint2(ohi[0], ohi[1]));
             }
         }
-#pragma unroll
-        for (int p = 0; p < P; p++) { cur[p][0] = nxt[p][0]; cur[p][1] = nxt[p][1]; }
-        r = rn; k = kn;
+        sc = sc + 1 == ROPE_RING ? 0 : sc + 1;
+        if (++r == rounds) { r = 0; k++; t += stride; out_q += (size_t)stride * qrow; out_k += (size_t)stride * krow; }
     }
+    cp_async_wait<0>();
+}
+
+// ---- the same mapping with the token's shape fixed at compile time ----------------------------------------------------------------------
+// NQ2 pairs of q heads and NK2 pairs of k heads per token (NQ2 a multiple of 4, NK2 <= 4 or a multiple of 4): the token's rounds of four
+// pairs are unrolled, so every address is a token base plus a constant and nothing is counted or selected at run time. A pair of heads
+// is 512 contiguous bytes, copied by the warp as one 16-byte cp.async per lane (a warp barrier then stands between the copies and the
+// lanes' reads of their own 8-byte pieces; 8-byte copies, which need none, were measured slower: four times the requests). The ring
+// has one slot per round: as soon as a round of this token has been read, the same round of the warp's next token is requested into
+// its slot, so almost a whole token of copies is in flight per warp. The four heads' sums of squares of a half-warp are reduced
+// together: after the exchange with partner 8 a lane keeps two of the four sums, after partner 4 one (the sums a butterfly forms at
+// those lanes, addition being commutative), and partners 2 and 1 finish it: 5 exchanges for four heads instead of 16. Instruction
+// count is what bounds this op on a batch of a few thousand tokens (the output of such a batch stays in L2).
+template <int NQ2, int NK2>
+__global__ void __launch_bounds__(128) qk_rope_f16_tok_kernel(const RopeArgs A) {
+    constexpr int RQ = NQ2 / 4, RK = (NK2 + 3) / 4, R = RQ + RK;
+    static_assert(NQ2 % 4 == 0 && (NK2 <= 4 || NK2 % 4 == 0), "rounds of four pairs of heads");
+    __shared__ __align__(16) float wsm[256], freq[64];
+    extern __shared__ __align__(16) unsigned char ring_all[];            // [4 warps][R rounds][2048]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int hw = lane >> 4, l16 = lane & 15;
+    const int lane_off = hw * 256 + l16 * 8;                             // bytes: this lane's low piece inside a pair of heads (the high piece: + 128)
+    constexpr size_t qrow = (size_t)NQ2 * 512, krow = (size_t)NK2 * 512;  // bytes per token
+    const int tw = blockIdx.x * 4 + warp, stride = gridDim.x * 4;
+    const int ntok = tw < A.n ? (A.n - tw + stride - 1) / stride : 0;
+    const uint32_t slots = (uint32_t)__cvta_generic_to_shared(ring_all) + warp * (R * 2048) + lane * 16;      // where this lane copies to
+    const uint32_t ring = slots - lane * 16 + lane_off;                                                          // where it reads its pieces
+    const unsigned char * in_q = reinterpret_cast<const unsigned char *>(A.in0) + (size_t)tw * qrow + lane * 16;
+    const unsigned char * in_k = reinterpret_cast<const unsigned char *>(A.in1) + (size_t)tw * krow + lane * 16;
+    unsigned char * out_q = reinterpret_cast<unsigned char *>(A.out0) + (size_t)tw * qrow + lane_off;
+    unsigned char * out_k = reinterpret_cast<unsigned char *>(A.out1) + (size_t)tw * krow + lane_off;
+    const size_t qstep = (size_t)stride * qrow, kstep = (size_t)stride * krow;
+    auto request = [&](int i, const unsigned char * bq, const unsigned char * bk, bool on) {      // round i (a constant after unrolling) of the token at bq / bk
+        if (on) {
+            const bool isq = i < RQ;
+            const int np = isq ? 4 : (NK2 - 4 * (i - RQ) < 4 ? NK2 - 4 * (i - RQ) : 4);
+            const unsigned char * src = isq ? bq + i * 2048 : bk + (i - RQ) * 2048;
+#pragma unroll
+            for (int p = 0; p < 4; p++)                                  // a pair of heads is 512 contiguous bytes: 16 per lane
+                if (p < np) cp_async16_s(slots + i * 2048 + p * 512, src + p * 512);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int i = 0; i < R; i++) request(i, in_q, in_k, ntok > 0);
+    wsm[tid] = __ldg(A.par + tid); wsm[128 + tid] = __ldg(A.par + 128 + tid);
+    if (tid < 64) freq[tid] = A.yarn ? __ldg(A.par + 258 + tid) : cam_powi(__ldg(A.par + 256), tid);
+    const float eps = __ldg(A.par + 257), mscale = A.yarn ? __ldg(A.par + 322) : 1.0f;
+    __syncthreads();
+    const float f0 = freq[4 * l16 + 2 * hw], f1 = freq[4 * l16 + 2 * hw + 1];      // this half-warp's two of the lane's four angles
+    f32x2 wq2[4], wk2[4];                                                // the lane's weights: dims (0, 1), (2, 3), (64, 65), (66, 67) + 4 l16
+    {
+        const float4 a = *reinterpret_cast<const float4 *>(wsm + 4 * l16), b = *reinterpret_cast<const float4 *>(wsm + 64 + 4 * l16);
+        const float4 c = *reinterpret_cast<const float4 *>(wsm + 128 + 4 * l16), e = *reinterpret_cast<const float4 *>(wsm + 192 + 4 * l16);
+        wq2[0] = pk2(a.x, a.y); wq2[1] = pk2(a.z, a.w); wq2[2] = pk2(b.x, b.y); wq2[3] = pk2(b.z, b.w);
+        wk2[0] = pk2(c.x, c.y); wk2[1] = pk2(c.z, c.w); wk2[2] = pk2(e.x, e.y); wk2[3] = pk2(e.z, e.w);
+    }
+    const bool up8 = l16 & 8, up4 = l16 & 4;
+    int t = tw;
+    for (int k = 0; k < ntok; k++, t += stride) {
+        f32x2 cc[2], sn[2], nsn[2];                                      // cos, sin, -sin of dims (4 l16, + 1) and (+ 2, + 3)
+        {
+            const float pos = (float)(A.pos0 + t);
+            float s0, c0, s1, c1;
+            cam_sincos(fmul(pos, f0), s0, c0); cam_sincos(fmul(pos, f1), s1, c1);
+            if (A.yarn) { c0 = fmul(c0, mscale); s0 = fmul(s0, mscale); c1 = fmul(c1, mscale); s1 = fmul(s1, mscale); }
+            const float oc0 = __shfl_xor_sync(CAM_FULL, c0, 16), os0 = __shfl_xor_sync(CAM_FULL, s0, 16);
+            const float oc1 = __shfl_xor_sync(CAM_FULL, c1, 16), os1 = __shfl_xor_sync(CAM_FULL, s1, 16);
+            const float ca = hw ? oc0 : c0, cb = hw ? oc1 : c1, cc_ = hw ? c0 : oc0, cd = hw ? c1 : oc1;      // dims 0, 1 come from the lower half-warp
+            const float sa = hw ? os0 : s0, sb = hw ? os1 : s1, sc_ = hw ? s0 : os0, sd = hw ? s1 : os1;
+            cc[0] = pk2(ca, cb); cc[1] = pk2(cc_, cd); sn[0] = pk2(sa, sb); sn[1] = pk2(sc_, sd); nsn[0] = pk2(-sa, -sb); nsn[1] = pk2(-sc_, -sd);
+        }
+        const bool more = k + 1 < ntok;
+        const unsigned char * nq = in_q + qstep, * nk = in_k + kstep;      // the warp's next token
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            cp_async_wait<R - 1>();                                      // this lane's copies of round i have landed (R groups are always outstanding)
+            __syncwarp();                                                // .. and every other lane's
+            const bool isq = i < RQ;
+            const int np = isq ? 4 : (NK2 - 4 * (i - RQ) < 4 ? NK2 - 4 * (i - RQ) : 4);
+            f32x2 xl[4][2], xh[4][2]; float ss[4];
+#pragma unroll
+            for (int p = 0; p < 4; p++) {
+                if (p < np) {
+                    const uint2 vlo = lds64(ring + i * 2048 + p * 512), vhi = lds64(ring + i * 2048 + p * 512 + 128);
+                    const float2 a = h2_to_f2(vlo.x), b = h2_to_f2(vlo.y), c = h2_to_f2(vhi.x), e = h2_to_f2(vhi.y);
+                    // the head's sum of squares: per lane an fma chain over its 4 low and its 4 high dims, added
+                    float sl = ffma(a.x, a.x, 0.0f), sh = ffma(c.x, c.x, 0.0f);
+                    sl = ffma(a.y, a.y, sl); sh = ffma(c.y, c.y, sh); sl = ffma(b.x, b.x, sl); sh = ffma(e.x, e.x, sh); sl = ffma(b.y, b.y, sl); sh = ffma(e.y, e.y, sh);
+                    ss[p] = fadd(sl, sh);
+                    xl[p][0] = pk2(a.x, a.y); xl[p][1] = pk2(b.x, b.y); xh[p][0] = pk2(c.x, c.y); xh[p][1] = pk2(e.x, e.y);
+                } else ss[p] = 0.0f;
+            }
+            __syncwarp();                                                // every lane has read its pieces of the slot
+            request(i, nq, nk, more);                                    // this round of the next token into it
+            // the half-warp sums of the four heads: partner 8 (a lane keeps heads 0, 1 or 2, 3), partner 4 (one head), partners 2, 1
+            float scale[4];
+            if (np > 2) {
+                const float g0 = __shfl_xor_sync(CAM_FULL, up8 ? ss[0] : ss[2], 8), g1 = __shfl_xor_sync(CAM_FULL, up8 ? ss[1] : ss[3], 8);
+                const float k0 = fadd(up8 ? ss[2] : ss[0], g0), k1 = fadd(up8 ? ss[3] : ss[1], g1);      // heads (0, 1) or (2, 3)
+                const float g2 = __shfl_xor_sync(CAM_FULL, up4 ? k0 : k1, 4);
+                float tot = fadd(up4 ? k1 : k0, g2);                         // head 2 up8 + up4 of the four
+                tot = fadd(tot, __shfl_xor_sync(CAM_FULL, tot, 2));
+                tot = fadd(tot, __shfl_xor_sync(CAM_FULL, tot, 1));
+                const float sc = cam_rsqrt(fadd(fmul(tot, 0.0078125f), eps));      // tot / 128: the same bits as the division
+#pragma unroll
+                for (int p = 0; p < 4; p++) scale[p] = __shfl_sync(CAM_FULL, sc, 16 * hw + 4 * p);      // head p's lanes: l16 = 4 p ..
+            } else {
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                    if (p < np) {
+                        float tot = ss[p];
+#pragma unroll
+                        for (int o = 8; o > 0; o >>= 1) tot = fadd(tot, __shfl_xor_sync(CAM_FULL, tot, o));
+                        scale[p] = cam_rsqrt(fadd(fmul(tot, 0.0078125f), eps));
+                    }
+                }
+            }
+            unsigned char * const o = isq ? out_q + i * 2048 : out_k + (i - RQ) * 2048;
+#pragma unroll
+            for (int p = 0; p < 4; p++) {
+                if (p < np) {
+                    const f32x2 s2 = pk2(scale[p], scale[p]);
+                    uint32_t olo[2], ohi[2];
+#pragma unroll
+                    for (int c = 0; c < 2; c++) {
+                        const f32x2 x0 = mul2(mul2(s2, xl[p][c]), isq ? wq2[c] : wk2[c]), x1 = mul2(mul2(s2, xh[p][c]), isq ? wq2[2 + c] : wk2[2 + c]);
+                        const f32x2 ylo = fma2(x0, cc[c], mul2(x1, nsn[c])), yhi = fma2(x1, cc[c], mul2(x0, sn[c]));
+                        olo[c] = f2_to_h2(lo2(ylo), hi2(ylo)); ohi[c] = f2_to_h2(lo2(yhi), hi2(yhi));
+                    }
+                    st64_stream(o + p * 512, make_uint2(olo[0], olo[1]));
+                    st64_stream(o + p * 512 + 128, make_uint2(ohi[0], ohi[1]));
+                }
+            }
+        }
+        in_q = nq; in_k = nk; out_q += qstep; out_k += kstep;
+    }
+    cp_async_wait<0>();
 }
 
 // warps per block (4 .. 12) and heads per half-warp and round (1 .. 4): the pair with the fewest idle half-warp slots over a
@@ -446,10 +614,36 @@ extern "C" int cam_qk_rope_f16(int n, const void * q, const void * k, int nh, in
     if (n == 0) return CAM_OK;
     const RopeArgs A = {q, k, par, (uint16_t *)qo, (uint16_t *)ko, 0, nh, nkv, pos0, n, yarn, nullptr};
     if (const char * e = getenv("CAMINUS_B200_ROPE_STAGED")) { if (e[0] == '1') return launch_rope<uint16_t, false>(A, (cudaStream_t)stream); }      // (tuning: the staged kernel)
-    // a warp per token, heads 6 at a time; as many blocks of four warps as the device holds at once, or as the tokens need
-    constexpr int P = 3;
-    const int rounds = (nh + nkv + 2 * P - 1) / (2 * P);
-    const int grid = cam_resident_grid(qk_rope_f16_warp_kernel<P>, 128, 0, ((long)n + 3) / 4);
-    qk_rope_f16_warp_kernel<P><<<grid, 128, 0, (cudaStream_t)stream>>>(A, rounds);
+    // a warp per token, heads 8 at a time; as many blocks of four warps as the device holds at once, or as the tokens need
+    if ((nh & 1) || (nkv & 1)) return launch_rope<uint16_t, false>(A, (cudaStream_t)stream);       // (a pair of heads must be whole: odd counts take the staged kernel)
+    const long blocks = ((long)n + 3) / 4;
+    cudaStream_t st = (cudaStream_t)stream;
+    const char * pick = getenv("CAMINUS_B200_ROPE_P");               // (tuning: 2 / 4 = the generic warp kernel with that many pairs per round)
+    // the shapes with a compile-time token layout (Qwen3: 32 + 4, 64 + 8, 40 + 8 and 32 + 8 heads)
+    // Grid: a block per four tokens when that is more than twice what the device holds at once (measured at 65536 tokens: 358 us against
+    // 409 us for a resident grid whose warps loop over tokens; a finished block's successor starts with a whole token of copies in
+    // flight), else exactly the resident blocks, the warps taking a second token where there are more tokens than warps (measured at
+    // 4096 tokens of 36 heads: 16.5 us against 18.8 us).
+#define CAM_ROPE_TOK(NQ2V, NK2V)                                                                                                   \
+    if (!pick && nh == 2 * NQ2V && nkv == 2 * NK2V) {                                                                              \
+        static unsigned long long allowed = 0;                                                                                     \
+        constexpr size_t smem = 4 * (NQ2V / 4 + (NK2V + 3) / 4) * 2048;                                                            \
+        const cudaError_t e = cam_allow_smem(qk_rope_f16_tok_kernel<NQ2V, NK2V>, smem, allowed);                                   \
+        if (e != cudaSuccess) return (int)e;                                                                                       \
+        const int cap = cam_resident_grid(qk_rope_f16_tok_kernel<NQ2V, NK2V>, 128, smem, blocks);                                  \
+        const bool full = grid_mode ? grid_mode[0] == 'f' : blocks > 2L * cap;                                                     \
+        qk_rope_f16_tok_kernel<NQ2V, NK2V><<<full ? (int)blocks : cap, 128, smem, st>>>(A);                                        \
+        return (int)cudaGetLastError();                                                                                            \
+    }
+    const char * grid_mode = getenv("CAMINUS_B200_ROPE_GRID");       // (tuning: "full" / "resident")
+    CAM_ROPE_TOK(16, 2) CAM_ROPE_TOK(32, 4) CAM_ROPE_TOK(20, 4) CAM_ROPE_TOK(16, 4)
+#undef CAM_ROPE_TOK
+    // other shapes: heads per round 8 (one scale computation per four pairs of heads, 20 resident warps per multiprocessor) when every
+    // warp gets many tokens, else 4 (32 resident warps: a batch of a few thousand tokens is one token per warp in a single wave)
+    const int g4 = cam_resident_grid(qk_rope_f16_warp_kernel<4>, 128, 0, blocks);
+    int P = blocks >= 8L * g4 ? 4 : 2;
+    if (pick && (pick[0] == '2' || pick[0] == '4')) P = pick[0] - '0';
+    if (P == 4) qk_rope_f16_warp_kernel<4><<<g4, 128, 0, st>>>(A);
+    else qk_rope_f16_warp_kernel<2><<<cam_resident_grid(qk_rope_f16_warp_kernel<2>, 128, 0, blocks), 128, 0, st>>>(A);
     return (int)cudaGetLastError();
 }
