@@ -59,7 +59,7 @@ CAM_DEV void mmq_values(const MmqRaw<2> & raw, float (&v)[16]) {
 // thread), then the quads' partners 4 (the other lane), 2 and 1 (inside the lane).
 template <int LAYOUT>
 CAM_DEV void mmq_quant(const float (&v)[16], uint4 & w, uint32_t & hdr) {
-    float amax = 0.0f, ts[4];
+    float amax = fabsf(v[0]), ts[4];       // (the reference's thread starts from its first value: 32 NaNs give a NaN maximum and scale; fmaxf skips a NaN among numbers)
 #pragma unroll
     for (int s = 0; s < 4; s++) {
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[4 * s]), fabsf(v[4 * s + 1])), fmaxf(fabsf(v[4 * s + 2]), fabsf(v[4 * s + 3]))));

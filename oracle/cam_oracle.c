@@ -552,8 +552,8 @@ void orc_pf_qk_nr(const float * xin, int head_stride, int heads, const float * w
  * four values, then partners 4, 2, 1 over the group's eight fours. An all-zero group stores d = 0 and codes 0 (the reference's
  * arithmetic yields 0 * inf = NaN there, whose int8 conversion is 0 on its GPUs). Values at k >= kvalid are 0 (row padding). */
 static void mmq_group(const float * x, int8_t * q, float * d_out, float * sum_out) {
-    float amax = 0.0f;
-    for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(x[i]));
+    float amax = fabsf(x[0]);                     /* (as the reference's thread starts from its first value: a group of 32 NaNs has a NaN for a maximum and a scale; */
+    for (int i = 1; i < 32; i++) amax = fmaxf(amax, fabsf(x[i]));      /*  a NaN among numbers is skipped by fmaxf) */
     float p[8], t[8];
     for (int l = 0; l < 8; l++) p[l] = ((x[4 * l] + x[4 * l + 1]) + x[4 * l + 2]) + x[4 * l + 3];
     for (int m = 4; m >= 1; m >>= 1) { for (int l = 0; l < 8; l++) t[l] = p[l] + p[l ^ m]; memcpy(p, t, sizeof p); }
