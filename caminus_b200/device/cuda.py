@@ -19,6 +19,7 @@ from .. import lib as _lib
 # caminus.prefill.graph's recorder hook of the reference (device/hip.py:12-14): an object with intercept(...) / launched(...)
 RECORD = None
 LOADED = []    # module names this process asked for, in order (the reference's LOADED, device/hip.py:16)
+CHECK_DEVICE = True   # refuse host tensors as kernel arguments (a test that records launches without a GPU clears it)
 
 # kernel -> (C entry, how many leading counts come from the launch grid)
 _Q3M = {'q3p_emb': ('q3p_emb', 1), 'q3p_add_rms16': ('q3p_add_rms16', 1), 'q3p_swiglu': ('q3p_swiglu', 0),
@@ -127,10 +128,10 @@ class Kernel:
         vals = []
         for a in args:
             if type(a) is T:
-                if not a.is_cuda: raise ValueError('caminus_b200: a kernel argument is a CPU tensor')
+                if CHECK_DEVICE and not a.is_cuda: raise ValueError('caminus_b200: a kernel argument is a CPU tensor')
                 vals.append(a.data_ptr())
             elif hasattr(a, 'data_ptr'):                             # (a tensor subclass or another array with a device address)
-                if getattr(a, 'is_cuda', True) is False: raise ValueError('caminus_b200: a kernel argument is a CPU tensor')
+                if CHECK_DEVICE and getattr(a, 'is_cuda', True) is False: raise ValueError('caminus_b200: a kernel argument is a CPU tensor')
                 vals.append(a.data_ptr())
             else:
                 vals.append(a)
