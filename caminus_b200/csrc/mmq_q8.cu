@@ -126,9 +126,10 @@ __global__ void __launch_bounds__(256) mmq_q8_1_rows_kernel(const float * __rest
 
 // grid.x walks the rows, grid.y groups of 32 K-blocks (four per warp): a block reads 16 KB of a row; two rows per pass, both rows'
 // loads issued before either is used. (No index is divided: a 64-bit division per task costs more than the task's arithmetic.)
+// ids (nullable): column r of y holds row ids[r] of the inputs, clamped to the rows there are
 template <int MODE, int LAYOUT>
 __global__ void __launch_bounds__(256) mmq_q8_1_kernel(const void * __restrict__ xv, const void * __restrict__ uv, uint8_t * __restrict__ y,
-                                                       int kvalid, int nkb, long ld, int rows) {
+                                                       int kvalid, int nkb, long ld, int rows, const int * __restrict__ ids) {
     const int lane = threadIdx.x & 31;
     for (int kb0 = (blockIdx.y * 8 + (threadIdx.x >> 5)) * 4; kb0 < nkb; kb0 += gridDim.y * 32) {
         const int kb = kb0 + (lane >> 3), k = kb * 128 + (lane & 7) * 16;
@@ -137,8 +138,9 @@ __global__ void __launch_bounds__(256) mmq_q8_1_kernel(const void * __restrict__
         for (int r = blockIdx.x; r < rows; r += 2 * gridDim.x) {
             const int r2 = r + gridDim.x;
             MmqRaw<MODE> a0, a1;
-            mmq_load<MODE>(a0, xv, uv, k, (size_t)r * ld, kv);
-            if (r2 < rows) mmq_load<MODE>(a1, xv, uv, k, (size_t)r2 * ld, kv);
+            const int s0 = ids ? min(max(__ldg(ids + r), 0), rows - 1) : r, s1 = ids && r2 < rows ? min(max(__ldg(ids + r2), 0), rows - 1) : r2;
+            mmq_load<MODE>(a0, xv, uv, k, (size_t)s0 * ld, kv);
+            if (r2 < rows) mmq_load<MODE>(a1, xv, uv, k, (size_t)s1 * ld, kv);
             float v[16];
             uint4 w; uint32_t hdr;
             mmq_values(a0, v);
@@ -216,26 +218,32 @@ template <> struct Raw8<float> {
 
 // a warp's task: K-blocks 4 kq .. 4 kq + 3 (8 lanes each, 16 values per lane) of rows r0, r0 + 1
 struct MmqTask {
-    int r0, kb, k;
+    int r0, kb, k, s0, s1;                       // s0, s1: the input rows of output columns r0, r0 + 1 (the columns themselves without an index)
     bool kon, kin;
-    CAM_DEV MmqTask(int kq, int rp, int lane, int nkb, int kvalid) {
+    CAM_DEV MmqTask(int kq, int rp, int lane, int nkb, int kvalid, const int * __restrict__ ids, int rows) {
         r0 = rp * 2;
         kb = kq * 4 + (lane >> 3); k = kb * 128 + (lane & 7) * 16;
         kon = kb < nkb; kin = kon && k < kvalid;
+        s0 = r0; s1 = r0 + 1;
+        if (ids) {
+            if (r0 < rows) s0 = min(max(__ldg(ids + r0), 0), rows - 1);
+            if (r0 + 1 < rows) s1 = min(max(__ldg(ids + r0 + 1), 0), rows - 1);
+        }
     }
 };
 
 // chunk c (row r0 + c) of a task: a lane's 16 values as two loads of 8
 template <typename T>
 CAM_DEV void mmq_fetch(const T * __restrict__ g, const T * __restrict__ u, const MmqTask & t, long ld, int rows, Raw8<T> (&rg)[2][2], Raw8<T> (&ru)[2][2]) {
-    const T * gp = g + (size_t)t.r0 * ld + t.k, * up = u + (size_t)t.r0 * ld + t.k;
 #pragma unroll
-    for (int c = 0; c < 2; c++)
+    for (int c = 0; c < 2; c++) {
+        const size_t at = (size_t)(c ? t.s1 : t.s0) * ld + t.k;
 #pragma unroll
         for (int hf = 0; hf < 2; hf++) {
-            if (t.kin && t.r0 + c < rows) { rg[c][hf].load(gp + c * ld + 8 * hf); ru[c][hf].load(up + c * ld + 8 * hf); }
+            if (t.kin && t.r0 + c < rows) { rg[c][hf].load(g + at + 8 * hf); ru[c][hf].load(u + at + 8 * hf); }
             else { rg[c][hf].fill(1.0f); ru[c][hf].fill(0.0f); }      // h = 0 on both passes
         }
+    }
 }
 
 // PF: the next task's values are loaded before this task's arithmetic (fp16: 32 more registers)
@@ -247,7 +255,7 @@ CAM_DEV void mmq_fetch(const T * __restrict__ g, const T * __restrict__ u, const
 // Groups that fail any of it (about 7 % of Gaussian groups, most of them by the sum) are recomputed exactly as for D4.
 template <typename T, bool PF, int LAYOUT>
 __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y,
-                                                                 int kvalid, int nkb, long ld, int rows) {
+                                                                 int kvalid, int nkb, long ld, int rows, const int * __restrict__ ids) {
     const int lane = threadIdx.x & 31, pb = lane & 30, pi = lane & 1;      // a group of 32 values = the lane pair pb, pb + 1
     // grid.x walks pairs of rows (8 per block, one per warp), grid.y the quads of K-blocks; no index is divided
     const int nrp = (rows + 1) >> 1, nkq = (nkb + 3) >> 2;
@@ -255,14 +263,14 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
     if (rp0 >= nrp) return;
     int kq = blockIdx.y, rp = rp0;
     Raw8<T> rg[2][2], ru[2][2], ng[2][2], nu[2][2];
-    if (PF && kq < nkq) mmq_fetch(g, u, MmqTask(kq, rp, lane, nkb, kvalid), ld, rows, rg, ru);
+    if (PF && kq < nkq) mmq_fetch(g, u, MmqTask(kq, rp, lane, nkb, kvalid, ids, rows), ld, rows, rg, ru);
     while (kq < nkq) {
-        const MmqTask t(kq, rp, lane, nkb, kvalid);
+        const MmqTask t(kq, rp, lane, nkb, kvalid, ids, rows);
         const int kq_now = kq;
         rp += rstride;                                                // the next task
         if (rp >= nrp) { rp = rp0; kq += gridDim.y; }
         if (!PF) mmq_fetch(g, u, t, ld, rows, rg, ru);
-        else if (kq < nkq) mmq_fetch(g, u, MmqTask(kq, rp, lane, nkb, kvalid), ld, rows, ng, nu);
+        else if (kq < nkq) mmq_fetch(g, u, MmqTask(kq, rp, lane, nkb, kvalid, ids, rows), ld, rows, ng, nu);
         float h[2][16], eg = 1.0f, eu = 0.0f;
         float am2[2] = {0.0f, 0.0f}, sum2[2] = {0.0f, 0.0f}, sab2[2] = {0.0f, 0.0f};      // DS4: the chunks' amax^, S^, A
         uint32_t bad = 0;                                             // bit c: chunk c of this lane fails a margin
@@ -378,7 +386,7 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
             const int kbj = kq_now * 4 + (j >> 2), kj = kbj * 128 + (j & 3) * 32 + lane;
             float x = 0.0f;
             if (kj < kvalid) {
-                const size_t at = (size_t)(t.r0 + c) * ld + kj;
+                const size_t at = (size_t)(c ? t.s1 : t.s0) * ld + kj;
                 x = fmul(cam_silu(Load8<T>::one(g + at)), Load8<T>::one(u + at));
             }
             float sq = fadd(x, __shfl_down_sync(CAM_FULL, x, 1));
@@ -396,7 +404,7 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
             const int kbj = kq_now * 4 + (j >> 2), kj = kbj * 128 + (j & 3) * 32 + lane;
             float x = 0.0f;
             if (kj < kvalid) {
-                const size_t at = (size_t)(t.r0 + c) * ld + kj;
+                const size_t at = (size_t)(c ? t.s1 : t.s0) * ld + kj;
                 x = fmul(cam_silu(Load8<T>::one(g + at)), Load8<T>::one(u + at));
             }
             float a = fabsf(x);
@@ -432,24 +440,25 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
 }
 
 template <int MODE>
-int launch_mmq(const void * x, const void * u, void * y, int kvalid, int Kpad, long ld, int rows, int layout, cudaStream_t stream) {
+int launch_mmq(const void * x, const void * u, void * y, int kvalid, int Kpad, long ld, int rows, int layout, cudaStream_t stream, const int * ids = nullptr) {
     if (rows < 0 || Kpad < 128 || (Kpad & 127) || kvalid < 0 || kvalid > Kpad || (kvalid & 3) || ld < kvalid || (ld & 3) || !x || !y ||
         (MODE != 0 && !u) || (layout != 0 && layout != 1)) return CAM_ERR_ARG;
     const int elt = MODE == 2 ? 8 : 16;
-    if ((reinterpret_cast<uintptr_t>(x) & (elt - 1)) || (u && (reinterpret_cast<uintptr_t>(u) & (elt - 1))) || !cam_aligned16(y)) return CAM_ERR_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(x) & (elt - 1)) || (u && (reinterpret_cast<uintptr_t>(u) & (elt - 1))) || !cam_aligned16(y) ||
+        (ids && (reinterpret_cast<uintptr_t>(ids) & 3u))) return CAM_ERR_ALIGN;
     if (rows == 0) return CAM_OK;
     if (MODE != 0 && !(kvalid & 15) && !(ld & 7) && cam_aligned16(x) && cam_aligned16(u)) {
         const long nx = ((rows + 1) / 2 + 7) / 8, ny = (Kpad / 128 + 3) / 4;
 #define CAM_MMQ_FAST(TT, PF, LAY) mmq_swiglu_fast_kernel<TT, PF, LAY><<<mmq_grid(mmq_swiglu_fast_kernel<TT, PF, LAY>, nx, ny), 256, 0, stream>>>( \
-                (const TT *)x, (const TT *)u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows)
+                (const TT *)x, (const TT *)u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows, ids)
         if (MODE == 2) { if (layout == 0) CAM_MMQ_FAST(uint16_t, true, 0); else CAM_MMQ_FAST(uint16_t, true, 1); }
         else { if (layout == 0) CAM_MMQ_FAST(float, false, 0); else CAM_MMQ_FAST(float, false, 1); }
 #undef CAM_MMQ_FAST
         return (int)cudaGetLastError();
     }
     const long ny = (Kpad / 128 + 31) / 32;
-    if (layout == 0) mmq_q8_1_kernel<MODE, 0><<<mmq_grid(mmq_q8_1_kernel<MODE, 0>, rows, ny), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
-    else mmq_q8_1_kernel<MODE, 1><<<mmq_grid(mmq_q8_1_kernel<MODE, 1>, rows, ny), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows);
+    if (layout == 0) mmq_q8_1_kernel<MODE, 0><<<mmq_grid(mmq_q8_1_kernel<MODE, 0>, rows, ny), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows, ids);
+    else mmq_q8_1_kernel<MODE, 1><<<mmq_grid(mmq_q8_1_kernel<MODE, 1>, rows, ny), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows, ids);
     return (int)cudaGetLastError();
 }
 
@@ -468,6 +477,17 @@ extern "C" int cam_swiglu_mmq_q8_1(const float * g, const float * u, void * y, i
 }
 extern "C" int cam_swiglu_mmq_q8_1_f16(const void * g, const void * u, void * y, int kvalid, int Kpad, long ld, int rows, int layout, void * stream) {
     return launch_mmq<2>(g, u, y, kvalid, Kpad, ld, rows, layout, (cudaStream_t)stream);
+}
+
+// cam_swiglu_mmq_q8_1[_f16]_ids: column c of y (ncols columns) = the blocks of silu(g) * u of row ids[c] of gate and up (ids null: row c;
+// an index outside [0, ncols) is clamped): the fused producer for expert-grouped columns, where the reference's gate / up kernel writes
+// column c0 + j of its work item (kernels/prefill_moe.hip:389-394) and its unfused path gathers rows through quantize_mmq_q8_1's index
+// (python/caminus/prefill/mmq.py:245-262). gate and up hold ncols rows of stride s01.
+extern "C" int cam_swiglu_mmq_q8_1_ids(const float * g, const float * u, const int * ids, void * y, int K, int Kpad, long s01, int ncols, int layout, void * stream) {
+    return launch_mmq<1>(g, u, y, K, Kpad, s01, ncols, layout, (cudaStream_t)stream, ids);
+}
+extern "C" int cam_swiglu_mmq_q8_1_f16_ids(const void * g, const void * u, const int * ids, void * y, int K, int Kpad, long s01, int ncols, int layout, void * stream) {
+    return launch_mmq<2>(g, u, y, K, Kpad, s01, ncols, layout, (cudaStream_t)stream, ids);
 }
 
 // cam_quantize_mmq_q8_1_ids: column c of y (ncols columns) = row ids[c] of x (ids null: row c); x fp32 with row stride s01 floats,

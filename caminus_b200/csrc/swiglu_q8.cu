@@ -102,8 +102,9 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_1_kernel(const T * __restrict__
 // Block sum in aq_fill's order: a lane holds groups 4 q .. 4 q + 3 (q its place in the pair): partner 4 is the other lane, partners 2
 // and 1 are the lane's own groups.
 // SUMS: also prove the block sum (else it is the fp16 rounding of the fast pass's own sum, within one fp16 ulp of the exact one)
-template <typename T, bool FULL, bool SUMS>
-CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y, int base, int npairs, int lane) {
+// SCALED: the values are silu(g rs), with no second operand (u is not read): the tape op's work = 1, ggml_scale then ggml_silu
+template <typename T, bool FULL, bool SUMS, bool SCALED = false>
+CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y, int base, int npairs, int lane, float rs = 1.0f) {
     const int pi = base + lane, q = lane & 1;
     const bool on = FULL || pi < npairs;
     float gv[16], uv[16], h[16];
@@ -115,12 +116,17 @@ CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, 
         Load8<T>::get(g + (size_t)pi * 16 + 8, t);
 #pragma unroll
         for (int k = 0; k < 8; k++) gv[8 + k] = t[k];
-        Load8<T>::get(u + (size_t)pi * 16, t);
+        if (SCALED) {
 #pragma unroll
-        for (int k = 0; k < 8; k++) uv[k] = t[k];
-        Load8<T>::get(u + (size_t)pi * 16 + 8, t);
+            for (int k = 0; k < 16; k++) { gv[k] = fmul(gv[k], rs); uv[k] = 1.0f; }      // (the product with 1 is exact: h = silu(g rs))
+        } else {
+            Load8<T>::get(u + (size_t)pi * 16, t);
 #pragma unroll
-        for (int k = 0; k < 8; k++) uv[8 + k] = t[k];
+            for (int k = 0; k < 8; k++) uv[k] = t[k];
+            Load8<T>::get(u + (size_t)pi * 16 + 8, t);
+#pragma unroll
+            for (int k = 0; k < 8; k++) uv[8 + k] = t[k];
+        }
     } else {
 #pragma unroll
         for (int k = 0; k < 16; k++) { gv[k] = 0.0f; uv[k] = 0.0f; }
@@ -174,7 +180,7 @@ CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, 
     for (uint32_t m = resum; m; m &= m - 1) {
         const int j2 = __ffs(m) - 1;
         const size_t blk = (size_t)(base >> 1) + (j2 >> 1);
-        const float x = fmul(cam_silu(Load8<T>::one(g + blk * 32 + lane)), Load8<T>::one(u + blk * 32 + lane));
+        const float x = SCALED ? cam_silu(fmul(Load8<T>::one(g + blk * 32 + lane), rs)) : fmul(cam_silu(Load8<T>::one(g + blk * 32 + lane)), Load8<T>::one(u + blk * 32 + lane));
         float sx = fadd(x, __shfl_xor_sync(CAM_FULL, x, 1));
         sx = fadd(sx, __shfl_xor_sync(CAM_FULL, sx, 2));
         sx = fadd(sx, __shfl_xor_sync(CAM_FULL, sx, 16));
@@ -186,7 +192,7 @@ CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, 
     // exact recomputation of the flagged blocks: the whole warp, one lane per value (uniform: pairs is the same in every lane)
     for (uint32_t m = pairs; m; m &= m - 1) {
         const size_t blk = (size_t)(base >> 1) + ((__ffs(m) - 1) >> 1);
-        const float x = fmul(cam_silu(Load8<T>::one(g + blk * 32 + lane)), Load8<T>::one(u + blk * 32 + lane));
+        const float x = SCALED ? cam_silu(fmul(Load8<T>::one(g + blk * 32 + lane), rs)) : fmul(cam_silu(Load8<T>::one(g + blk * 32 + lane)), Load8<T>::one(u + blk * 32 + lane));
         float am = fabsf(x);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(CAM_FULL, am, o));
@@ -202,26 +208,27 @@ CAM_DEV void swiglu_q8_step(const T * __restrict__ g, const T * __restrict__ u, 
     }
 }
 
-template <typename T, bool SUMS>
+template <typename T, bool SUMS, bool SCALED = false>
 __global__ void __launch_bounds__(Q8_THREADS) swiglu_q8_fast_kernel(const T * __restrict__ g, const T * __restrict__ u,
-                                                                      uint8_t * __restrict__ y, int nb) {
+                                                                      uint8_t * __restrict__ y, int nb, float rs = 1.0f) {
     const int lane = threadIdx.x & 31;
     const int npairs = nb * 2;
     const int stride = gridDim.x * Q8_THREADS;
     int base = blockIdx.x * Q8_THREADS + (threadIdx.x & ~31);
-    for (; base + 32 <= npairs; base += stride) swiglu_q8_step<T, true, SUMS>(g, u, y, base, npairs, lane);
-    if (base < npairs) swiglu_q8_step<T, false, SUMS>(g, u, y, base, npairs, lane);
+    for (; base + 32 <= npairs; base += stride) swiglu_q8_step<T, true, SUMS, SCALED>(g, u, y, base, npairs, lane, rs);
+    if (base < npairs) swiglu_q8_step<T, false, SUMS, SCALED>(g, u, y, base, npairs, lane, rs);
 }
 
 // the last, partial block (n % 32 values, the rest 0): one warp, one lane per value
-template <typename T, bool SWIGLU>
+template <typename T, bool SWIGLU, bool SCALED = false>
 __global__ void __launch_bounds__(32) q8_1_tail_kernel(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y,
-                                                       long first, int rem) {
+                                                       long first, int rem, float rs = 1.0f) {
     const int lane = threadIdx.x;
     float x = 0.0f;
     if (lane < rem) {
         x = Load8<T>::one(g + first + lane);
         if (SWIGLU) x = fmul(cam_silu(x), Load8<T>::one(u + first + lane));
+        if (SCALED) x = cam_silu(fmul(x, rs));
     }
     float amax = fabsf(x);
 #pragma unroll
@@ -333,6 +340,23 @@ int launch_q8(const T * g, const T * u, void * y, long n, cudaStream_t stream) {
     return (int)cudaGetLastError();
 }
 
+// the tape op's work = 1: Q8_1 blocks of silu(x rs) (SUMS: all 36 bytes the exact statements'; else the scale and the codes)
+template <bool SUMS>
+int launch_q8_scaled(const float * x, float rs, void * y, long n, cudaStream_t stream) {
+    if (n < 0 || !x || !y) return CAM_ERR_ARG;
+    if (n == 0) return CAM_OK;
+    if (!cam_aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 3u)) return CAM_ERR_ALIGN;
+    const long nb = n >> 5, piece = 1L << 28;
+    for (long b0 = 0; b0 < nb; b0 += piece) {
+        const long m = nb - b0 < piece ? nb - b0 : piece;
+        const long w = (m * 2 + Q8_THREADS - 1) / Q8_THREADS;
+        swiglu_q8_fast_kernel<float, SUMS, true><<<cam_resident_grid(swiglu_q8_fast_kernel<float, SUMS, true>, Q8_THREADS, 0, w), Q8_THREADS, 0, stream>>>(
+            x + b0 * 32, nullptr, (uint8_t *)y + b0 * 36, (int)m, rs);
+    }
+    if (n & 31) q8_1_tail_kernel<float, false, true><<<1, 32, 0, stream>>>(x, nullptr, (uint8_t *)y, nb << 5, (int)(n & 31), rs);
+    return (int)cudaGetLastError();
+}
+
 // y = silu(g) u elementwise: fp16 (q3p_swiglu) or fp32 (gg_silu_mul) out
 template <bool HALF_OUT>
 __global__ void __launch_bounds__(256) silu_mul_kernel(const float * __restrict__ g, const float * __restrict__ u, void * __restrict__ y,
@@ -394,6 +418,16 @@ extern "C" int gg_swiglu_q8_1_sums(const float * x, const float * mul, void * y,
 }
 extern "C" int gg_swiglu_q8_1_f16_sums(const void * g, const void * u, void * y, long n, void * stream) {
     return launch_q8<uint16_t, true, 2>((const uint16_t *)g, (const uint16_t *)u, y, n, (cudaStream_t)stream);
+}
+// gg_silu_scale_q8_1: Q8_1 blocks of silu(x[i] * rs): the tape op OP_GG_Q8_1 with work = 1 (ggml_scale, then ggml_silu, then the
+// quantiser: the hyper-connection down output) as one launch. Reference: kernels/k3_gguf_ops.h:70 (semantics);
+// python/caminus/engine/k3.py:649-659 (Engine.gg_q8_1(x, yq, silu_scale=rs)). d and the codes are the exact statements' bytes, the sum
+// as for gg_swiglu_q8_1; the _sums form proves the sum too.
+extern "C" int gg_silu_scale_q8_1(const float * x, float rs, void * y, long n, void * stream) {
+    return launch_q8_scaled<false>(x, rs, y, n, (cudaStream_t)stream);
+}
+extern "C" int gg_silu_scale_q8_1_sums(const float * x, float rs, void * y, long n, void * stream) {
+    return launch_q8_scaled<true>(x, rs, y, n, (cudaStream_t)stream);
 }
 // The strict forms: every value through the exact statements, so the block sums are the exact statements' bytes as well as
 // d and the codes (which the entries above already guarantee). About half the throughput.

@@ -50,6 +50,19 @@ def swiglu_q8_1(g, u, yq=None, strict=False, sums=False):
     return yq
 
 
+def silu_scale_q8_1(x, rs, yq=None, sums=False):
+    """q8_1 blocks of silu(x * rs) in one launch (x fp32, cuda): the decode tape's Engine.gg_q8_1(x, yq, silu_scale=rs)
+    (python/caminus/engine/k3.py:649-659). sums=True proves the block sums too (all 36 bytes the exact statements')"""
+    if x.dtype != torch.float32 or not x.is_contiguous(): raise ValueError(f'silu_scale_q8_1: x must be contiguous fp32, not {x.dtype}')
+    n = x.numel(); nb = (n + 31) // 32
+    if yq is None: yq = torch.empty(nb * Q8_1_BYTES, dtype=torch.uint8, device=x.device)
+    elif yq.dtype != torch.uint8 or yq.numel() < nb * Q8_1_BYTES or not yq.is_contiguous(): raise ValueError(f'silu_scale_q8_1: yq needs {nb * Q8_1_BYTES} contiguous uint8')
+    fn = _lib.load().gg_silu_scale_q8_1_sums if sums else _lib.load().gg_silu_scale_q8_1
+    with torch.cuda.device(x.device):
+        _lib.check(fn(x.data_ptr(), float(rs), yq.data_ptr(), n, torch.cuda.current_stream().cuda_stream), 'gg_silu_scale_q8_1')
+    return yq
+
+
 MMQ_BLOCK_BYTES = 144     # block_q8_1_mmq: 16 bytes of scales + 128 int8
 MMQ_LAYOUTS = {'D4': 0, 'DS4': 1}
 

@@ -35,6 +35,8 @@ SIGNATURES = {
     'gg_swiglu_q8_1_f16_sums': [P, P, P, L, P],
     'gg_swiglu_q8_1_strict': [P, P, P, L, P],
     'gg_swiglu_q8_1_f16_strict': [P, P, P, L, P],
+    'gg_silu_scale_q8_1': [P, F, P, L, P],
+    'gg_silu_scale_q8_1_sums': [P, F, P, L, P],
     'q3p_qk_rope': [I, P, I, I, I, P, I, P, P, P],
     'q3p_qk_rope_yarn': [I, P, I, I, I, P, I, P, P, P],
     'cam_qk_rope_f16': [I, P, P, I, I, P, I, P, P, I, P],
@@ -43,6 +45,8 @@ SIGNATURES = {
     'cam_quantize_mmq_q8_1': [P, P, I, I, L, I, I, P],
     'cam_swiglu_mmq_q8_1': [P, P, P, I, I, L, I, I, P],
     'cam_swiglu_mmq_q8_1_f16': [P, P, P, I, I, L, I, I, P],
+    'cam_swiglu_mmq_q8_1_ids': [P, P, P, P, I, I, L, I, I, P],
+    'cam_swiglu_mmq_q8_1_f16_ids': [P, P, P, P, I, I, L, I, I, P],
     'cam_quantize_mmq_q8_1_ids': [P, P, P, I, I, L, I, I, P],
     'cam_quantize_mmq_q8_1_scatter': [P, P, P, I, I, L, I, I, I, P],
     'actq_fwd_bf16': [I, P, P, P, I, F, I, P],

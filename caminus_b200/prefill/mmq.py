@@ -53,6 +53,27 @@ class Mmq:
             r = _lib.load().cam_quantize_mmq_q8_1_ids(x.data_ptr(), 0 if ids is None else ids.data_ptr(), y.data_ptr(), K, k_pad(K), s01, ncols, layout, s)
         _lib.check(r, 'mmq.quantize')
 
+    def swiglu_quantize(self, g, u, K, ncols, y, layout, s01=None, ids=None, stream=None):
+        """quantize() of silu(g) * u without storing the products: column c of y = the blocks of row (ids[c] if ids else c) of gate and
+        up (both fp32 or both fp16, row stride s01 values). The bytes the reference's fused gate / up kernel writes for its down
+        projection (kernels/prefill_moe.hip:339-396), here from stored gate and up rows"""
+        K, ncols = int(K), int(ncols); s01 = K if s01 is None else int(s01)
+        self._chk(g, 'gate'); self._chk(u, 'up', g.dtype); self._chk(y, 'y')
+        if g.dtype not in (torch.float32, torch.float16): raise ValueError(f'mmq.swiglu_quantize: gate and up fp32 or fp16, not {g.dtype}')
+        if K % 4 or ncols < 1 or s01 < K: raise ValueError(f'mmq.swiglu_quantize: K {K} (a multiple of 4), ncols {ncols}, s01 {s01}')
+        if layout not in (D4, DS4): raise ValueError(f'mmq.swiglu_quantize: layout {layout}')
+        if _view_bytes(y) < y_bytes(K, ncols): raise ValueError(f'mmq.swiglu_quantize: y holds {_view_bytes(y)} B < {y_bytes(K, ncols)}')
+        need = g.element_size() * ((ncols - 1) * s01 + K)
+        if _view_bytes(g) < need or _view_bytes(u) < need: raise ValueError(f'mmq.swiglu_quantize: gate / up hold fewer than {ncols} rows ({need} B)')
+        if ids is not None:
+            self._chk(ids, 'ids', torch.int32)
+            if ids.numel() < ncols: raise ValueError(f'mmq.swiglu_quantize: ids holds {ids.numel()} < {ncols}')
+        fn = _lib.load().cam_swiglu_mmq_q8_1_f16_ids if g.dtype == torch.float16 else _lib.load().cam_swiglu_mmq_q8_1_ids
+        with torch.cuda.device(self.dev):
+            s = torch.cuda.current_stream().cuda_stream if stream is None else int(stream)
+            r = fn(g.data_ptr(), u.data_ptr(), 0 if ids is None else ids.data_ptr(), y.data_ptr(), K, k_pad(K), s01, ncols, layout, s)
+        _lib.check(r, 'mmq.swiglu_quantize')
+
     def quantize_scatter(self, x, K, ntok, ids_inv, k, y, layout, s_tok=None, stream=None):
         """each token's row of x quantised once and written to its k compact columns ids_inv[t * k + slot] of y
         ([K_pad / 128][ntok * k])"""

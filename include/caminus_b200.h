@@ -112,6 +112,15 @@ int gg_swiglu_q8_1_sums(const float * x, const float * mul, void * y, long n, vo
 int gg_swiglu_q8_1_f16_sums(const void * g, const void * u, void * y, long n, void * stream);
 int gg_swiglu_q8_1_strict(const float * x, const float * mul, void * y, long n, void * stream);
 int gg_swiglu_q8_1_f16_strict(const void * g, const void * u, void * y, long n, void * stream);
+/* The same tape op with work = 1: blocks of silu(x[i] * rs) (ggml_scale, then ggml_silu, then the quantiser; kernels/k3_gguf_ops.h:70;
+ * built by Engine.gg_q8_1(x, yq, silu_scale=rs), python/caminus/engine/k3.py:649-659). d and the codes are the exact statements' bytes;
+ * the _sums form proves the block sum as well. */
+int gg_silu_scale_q8_1(const float * x, float rs, void * y, long n, void * stream);
+int gg_silu_scale_q8_1_sums(const float * x, float rs, void * y, long n, void * stream);
+/* Block sums of the Q8_1 entries above (gg_quantize_q8_1, gg_swiglu_q8_1*, gg_silu_scale_q8_1*): added in the order of the reference's
+ * eight-lane quantiser aq_fill (kernels/k3_gguf_ops.h:83-120: four values per lane, then partners 4, 2, 1), which the reference itself
+ * uses beside the lane butterfly of gg_op_q8_1 (kernels/k3_gguf_ops.h:55-77) and documents as bitwise-equivalent for every consumer:
+ * the two orders can differ by one fp16 ulp in that field, never in d or the codes. cam_rms_mul_q8_1 uses the lane butterfly. */
 
 /* Per-head q/k RMSNorm + NeoX RoPE. qkv fp32 [n][ldq] = q (nh heads of 128) | k (nkv) | v (nkv); q16 fp16 [n][nh][128];
  * cache fp16: row pos0 + t = K [nkv][128] | V [nkv][128] (V copied). par = q_norm[128] | k_norm[128] | theta_scale | eps
@@ -179,6 +188,12 @@ int pf_router(int T, const float * logits, int E, int k, float clamp, int * ids,
 int cam_quantize_mmq_q8_1(const float * x, void * y, int kvalid, int Kpad, long ld, int rows, int layout, void * stream);
 int cam_swiglu_mmq_q8_1(const float * g, const float * u, void * y, int kvalid, int Kpad, long ld, int rows, int layout, void * stream);
 int cam_swiglu_mmq_q8_1_f16(const void * g, const void * u, void * y, int kvalid, int Kpad, long ld, int rows, int layout, void * stream);
+/* The fused producer with a row index: column c of y (ncols columns) = the blocks of silu(g) * u of row ids[c] of gate and up (ids null:
+ * row c; an index outside [0, ncols) is clamped): expert-grouped columns, as the reference's fused gate / up kernel writes column
+ * c0 + j of its work item (kernels/prefill_moe.hip:389-394) and its unfused path gathers rows through the quantiser's index
+ * (python/caminus/prefill/mmq.py:245-262). gate and up hold ncols rows of stride s01; K values per row (a multiple of 4). */
+int cam_swiglu_mmq_q8_1_ids(const float * g, const float * u, const int * ids, void * y, int K, int Kpad, long s01, int ncols, int layout, void * stream);
+int cam_swiglu_mmq_q8_1_f16_ids(const void * g, const void * u, const int * ids, void * y, int K, int Kpad, long s01, int ncols, int layout, void * stream);
 /* The indexed forms of quantize_mmq_q8_1 (kernels/ggml_mmq/quantize_mmq.cuh:41-140; instances kernels/prefill_mmq.hip:101-107; wrappers
  * Mmq.quantize / Mmq.quantize_scatter, python/caminus/prefill/mmq.py:245-281). _ids: column c of y (ncols columns) = row ids[c] of x
  * (ids null: row c; x holds ncols rows of stride s01). _scatter: row t of x (ntok rows of stride s_tok) is quantised once and written

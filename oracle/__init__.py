@@ -201,6 +201,14 @@ def swiglu_q8_1(g, u, sum_order=0, threads=None):
     return y
 
 
+def silu_scale_q8_1(x, rs, sum_order=0):
+    """silu(x * rs) quantised to Q8_1 (the tape op OP_GG_Q8_1 with work = 1, kernels/k3_gguf_ops.h:70): uint8 [ceil(n / 32) * 36]"""
+    x = _c(x, np.float32).reshape(-1); n = x.size
+    y = np.empty((n + 31) // 32 * 36, np.uint8)
+    lib().orc_silu_scale_q8_1(_p(x), F(rs), _p(y), L_(n), I(sum_order))
+    return y
+
+
 def swiglu_f32_from_f16(g, u, threads=None):
     g = _c(g, np.float16).reshape(-1); u = _c(u, np.float16).reshape(-1); n = g.size
     h = np.empty(n, np.float32); f = lib().orc_swiglu_f32_from_f16

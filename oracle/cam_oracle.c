@@ -288,6 +288,14 @@ void orc_swiglu_q8_1(const float * g, const float * u, uint8_t * y, long n, int 
     }
 }
 /* the same with fp16 gate / up (converted exactly to fp32 first) */
+/* the tape op's work = 1 (kernels/k3_gguf_ops.h:70): xi = gg_silu(x * rs), ggml_scale then ggml_silu, then the quantiser */
+void orc_silu_scale_q8_1(const float * x, float rs, uint8_t * y, long n, int sum_order) {
+    for (long b = 0; b * 32 < n; b++) {
+        float xi[32];
+        for (int i = 0; i < 32; i++) { const long k = b * 32 + i; xi[i] = k < n ? orc_silu(x[k] * rs) : 0.0f; }
+        q8_1_block(xi, y + b * 36, sum_order);
+    }
+}
 void orc_swiglu_q8_1_f16(const uint16_t * g, const uint16_t * u, uint8_t * y, long n, int sum_order) {
     const long nb = (n + 31) / 32;
     for (long b = 0; b < nb; b++) {

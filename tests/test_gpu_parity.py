@@ -198,6 +198,20 @@ def test_swiglu_q8_1_hard_inputs(kind):
     if kind != 'nonfinite': assert np.array_equal(gguf.swiglu_q8_1(cu(gate), cu(up), sums=True).cpu().numpy(), want)     # all 36 bytes
 
 
+@pytest.mark.parametrize('n', [32, 1, 4096 + 7, 1 << 20])
+@pytest.mark.parametrize('rs', [1.0, 0.25, -3.0, 1e-3, 40.0])
+def test_silu_scale_q8_1(n, rs):
+    """gg_silu_scale_q8_1 (the tape op's work = 1: ggml_scale, ggml_silu, the quantiser): scale and codes are the oracle's bytes, the
+    _sums form all 36 bytes; gates scaled below -8 and above the exponential's range, zeros, a zero block, a ragged tail"""
+    g_ = np.random.default_rng(n + int(abs(rs) * 7)); x = (g_.standard_normal(n) * 4).astype(np.float32)
+    if n >= 64: x[:8] = np.array([30, -30, 0, -0.0, 1e-3, -88, 88, 3], np.float32); x[32:64] = 0
+    want = oracle.silu_scale_q8_1(x, rs, sum_order=1)
+    assert same(gguf.silu_scale_q8_1(cu(x), rs, sums=True), want)
+    d, s, q = oracle.q8_split(gguf.silu_scale_q8_1(cu(x), rs).cpu().numpy()); d1, s1, q1 = oracle.q8_split(want)
+    assert np.array_equal(q, q1) and same(d, d1)
+    assert (np.abs(s.astype(np.float64) - s1.astype(np.float64)) <= ulp16(s1.astype(np.float64)) + 1e-5).all()
+
+
 def test_swiglu_q8_1_f32_denormal_gates():
     """fp32 gates so small that the exact statements' g / (1 + e) is a denormal (its rounding is not the fast product's), next to
     huge ups that bring the product back to the block's scale; zero gates; the fused entries still give the exact statements' bytes"""

@@ -321,6 +321,31 @@ def test_mmq_quantize_ids_and_scatter(layout):
     with pytest.raises(ValueError): M.quantize(xd, K, ncols, torch.zeros(100, dtype=torch.uint8, device=DEV), layout)
 
 
+@pytest.mark.parametrize('layout', [0, 1])
+@pytest.mark.parametrize('dt', [np.float16, np.float32])
+@pytest.mark.parametrize('ncols,K,s01', [(37, 600, 640), (150, 2560, 2560), (5, 128, 128), (64, 1000, 1008)])
+def test_swiglu_mmq_with_a_row_index(layout, dt, ncols, K, s01):
+    """Mmq.swiglu_quantize: the fused SwiGLU blocks gathered through a row index: column c holds the oracle's block of row ids[c]
+    (with and without an index, aligned rows on the fast pass and odd strides on the exact kernel, ids out of range clamped)"""
+    from caminus_b200.prefill import mmq
+    g = np.random.default_rng(ncols + K + layout); M = mmq.Mmq(DEV); Kp = mmq.k_pad(K)
+    gt = acts(g, (ncols, s01), 1.5).astype(dt); up = acts(g, (ncols, s01)).astype(dt)
+    gt[1, :40] = 0; gt[2 % ncols, 5] = -9.5
+    plain = oracle.mmq_q8_1(gt, K, Kp, layout, u=up)                             # [Kp / 128, rows, 144] of the rows in order
+    gd, ud = cu(gt.reshape(-1)), cu(up.reshape(-1))
+    def run(ids):
+        y = torch.zeros(mmq.y_bytes(K, ncols), dtype=torch.uint8, device=DEV)
+        M.swiglu_quantize(gd, ud, K, ncols, y, layout, s01=s01, ids=ids)
+        return y[:Kp // 128 * ncols * 144].cpu().numpy().reshape(Kp // 128, ncols, 144)
+    assert np.array_equal(run(None), plain)
+    ids = g.permutation(ncols).astype(np.int32); ids[0] = ids[-1]                # a row used twice
+    assert np.array_equal(run(cu(ids)), plain[:, ids])
+    wild = ids.copy(); wild[1 % ncols] = -4; wild[2 % ncols] = ncols + 9
+    assert np.array_equal(run(cu(wild)), plain[:, np.clip(wild, 0, ncols - 1)])
+    with pytest.raises(ValueError): M.swiglu_quantize(gd, ud, K + 2, ncols, torch.zeros(mmq.y_bytes(K, ncols), dtype=torch.uint8, device=DEV), layout)
+    with pytest.raises(ValueError): M.swiglu_quantize(gd, ud.float() if dt == np.float16 else ud.half(), K, ncols, torch.zeros(mmq.y_bytes(K, ncols), dtype=torch.uint8, device=DEV), layout)
+
+
 @pytest.mark.parametrize('M,K', [(1, 128), (37, 896), (300, 1024), (5, 8192), (20, 2048), (9, 4096), (3, 384), (11, 4224), (6, 2304), (70, 6144)])
 def test_actq_family(M, K):
     """actq_fwd_*, silu_mul_actq_fwd, block_entry_fwd: values, scales and packed codes are the oracle's bytes; silu extremes and a

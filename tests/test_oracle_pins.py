@@ -226,3 +226,16 @@ def test_numpy_path_against_the_fixtures(golden):
     q = f['qkv'][:, :nh * 128].reshape(-1, nh, 128)
     got = NP.qk_norm_rope_f64(q, par[:128], f['pos'], theta=1e6, eps=float(par[257]))
     assert np.abs(got - f['q_plain']).max() <= 1e-12
+
+
+def test_silu_scale_q8_1_against_the_host_path():
+    """the tape op's work = 1, silu(x * rs) then Q8_1, against the NumPy host path under the reference's flip rule (a code may move by
+    one where the quotient sits on a .5 boundary, tests/engine/golden_util.py:132-173); rs = 1 with u = 1 is the SwiGLU form's bytes"""
+    from oracle import numpy_path as NP
+    g = np.random.default_rng(8); x = (g.standard_normal(4096 + 19) * 3).astype(np.float32); rs = 0.37
+    y = oracle.silu_scale_q8_1(x, rs, sum_order=1)
+    d, s, q = oracle.q8_split(y)
+    dn, sn, qn = NP.q8_1_blocks(NP.silu((x * np.float32(rs)).astype(np.float32)))
+    assert (np.abs(q.astype(int) - qn.astype(int)) <= 1).all() and (q != qn).mean() < 2e-3
+    assert np.abs(d.view(np.int16).astype(int) - dn.view(np.int16).astype(int)).max() <= 1
+    assert np.array_equal(oracle.silu_scale_q8_1(x, 1.0, sum_order=1), oracle.swiglu_q8_1(x, np.ones_like(x), sum_order=1))
