@@ -413,6 +413,65 @@ __global__ void __launch_bounds__(128) add_rms_f16_kernel(uint16_t * __restrict_
     cp_async_wait<0>();
 }
 
+// ---- fp16 rows too long to stage (2 stages x (x and d) x N x 2 bytes beyond a block's shared memory: N above about 28 900 with d,
+// 57 800 without): a warp per row, the row read twice from global memory: for the sum of squares and, a few microseconds later, for the
+// normalisation (the second read of a row of at most 256 KB comes from L2, not from HBM). Modes as the staged kernel's.
+template <int MODE>
+__global__ void __launch_bounds__(128) add_rms_f16_long_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d, const float * __restrict__ nw, float eps,
+                                                               uint16_t * __restrict__ h16, float * __restrict__ ss, const float * __restrict__ tot_in,
+                                                               int N, int Nfull, int n) {
+    const int lane = threadIdx.x & 31;
+    const int nch = (N + 255) >> 8;
+    for (int t = blockIdx.x * 4 + (threadIdx.x >> 5); t < n; t += gridDim.x * 4) {
+        uint16_t * xr = x + (size_t)t * N;
+        const uint16_t * dr = d ? d + (size_t)t * N : nullptr;
+        float tot;
+        if (MODE != 2) {
+            float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+            for (int m = 0; m < nch; m++) {
+                const int i = 8 * lane + 256 * m;
+                if (i >= N) break;
+                float xs[8];
+                load8(ld128(xr + i), xs);
+                if (dr) {
+                    float dv[8];
+                    load8(ldg128(dr + i), dv);
+#pragma unroll
+                    for (int c = 0; c < 8; c++) xs[c] = fadd(xs[c], dv[c]);
+                }
+#pragma unroll
+                for (int c = 0; c < 8; c++) a[c] = ffma(xs[c], xs[c], a[c]);
+            }
+            tot = ref_total_f16(a, lane);
+        } else tot = __ldg(tot_in + t);
+        if (MODE == 1) { if (lane == 0) ss[t] = tot; continue; }
+        const float scale = cam_rsqrt(fadd(fdiv(tot, (float)(MODE == 2 ? Nfull : N)), eps));
+        uint16_t * hr = h16 + (size_t)t * N;
+#pragma unroll 2
+        for (int m = 0; m < nch; m++) {
+            const int i = 8 * lane + 256 * m;
+            if (i >= N) break;
+            float xs[8];
+            load8(ld128(xr + i), xs);
+            if (dr) {
+                float dv[8];
+                load8(ldg128(dr + i), dv);
+#pragma unroll
+                for (int c = 0; c < 8; c++) xs[c] = fadd(xs[c], dv[c]);
+                st128(xr + i, make_uint4(f2_to_h2(xs[0], xs[1]), f2_to_h2(xs[2], xs[3]), f2_to_h2(xs[4], xs[5]), f2_to_h2(xs[6], xs[7])));
+            }
+            const float4 w0 = __ldg(reinterpret_cast<const float4 *>(nw + i)), w1 = __ldg(reinterpret_cast<const float4 *>(nw + i + 4));
+            float v[8];
+            v[0] = fmul(fmul(xs[0], scale), w0.x); v[1] = fmul(fmul(xs[1], scale), w0.y);
+            v[2] = fmul(fmul(xs[2], scale), w0.z); v[3] = fmul(fmul(xs[3], scale), w0.w);
+            v[4] = fmul(fmul(xs[4], scale), w1.x); v[5] = fmul(fmul(xs[5], scale), w1.y);
+            v[6] = fmul(fmul(xs[6], scale), w1.z); v[7] = fmul(fmul(xs[7], scale), w1.w);
+            st128_stream(hr + i, make_uint4(f2_to_h2(v[0], v[1]), f2_to_h2(v[2], v[3]), f2_to_h2(v[4], v[5]), f2_to_h2(v[6], v[7])));
+        }
+    }
+}
+
 // ---- fp16 rows held in registers -----------------------------------------------------------------------------------------
 // N = 256 CH: a warp loads its whole row (x and d: 2 CH 16-byte loads per lane, all issued before any is used, so a warp
 // keeps 4 N bytes in flight), keeps xs in fp32 registers between the sum of squares and the normalisation, and reads the
@@ -488,7 +547,11 @@ int launch_f16(uint16_t * x, const uint16_t * d, const float * nw, float eps, ui
     while (warps > 1 && (size_t)nw_smem * 4 + per_warp * warps > budget) warps >>= 1;
     if (n < 4 * warps) nw_smem = 0;                               // (a handful of rows: staging the weights costs more than it saves)
     const size_t smem = (size_t)nw_smem * 4 + per_warp * warps;
-    if (smem > budget) return CAM_ERR_SHAPE;
+    if (smem > budget) {                                          // a row that one warp cannot stage: the two-pass kernel
+        const int grid = cam_resident_grid(add_rms_f16_long_kernel<MODE>, 128, 0, ((long)n + 3) / 4);
+        add_rms_f16_long_kernel<MODE><<<grid, 128, 0, stream>>>(x, d, nw, eps, h16, ss, tot, N, Nfull, n);
+        return (int)cudaGetLastError();
+    }
     static unsigned long long allowed = 0;
     const cudaError_t e = cam_allow_smem(add_rms_f16_kernel<MODE>, 227 * 1024, allowed);
     if (e != cudaSuccess) return (int)e;

@@ -68,7 +68,10 @@ int cam_rms_apply_f16(int n, void * x, const void * d, const float * tot, const 
  * cam_tp_rms_words(cap, world) 64-bit words, zeroed once, and is mapped into every rank's process; peers is a device array of `world`
  * pointers to them (entry `rank` = the caller's own). A rank writes its per-row partial sums into every buffer by peer stores and
  * normalises a row when all ranks' partials have arrived; tag = the call's sequence number (1, 2, 3, ..: never 0, the same on every
- * rank). Waits are bounded (2 s): on expiry bit 0 of *status is set and rows are left unnormalised. n <= cap. */
+ * rank; a call with n = 0 launches nothing and must not use a tag up). Waits are bounded (2 s, or CAMINUS_B200_TP_WAIT_MS milliseconds):
+ * on expiry bit 0 of *status is set and the warp takes no more rows, so the call's rows are PARTLY updated: those normalised before
+ * hold x = fp16(x + d) and their h16, the others are untouched; a retry needs x restored from the caller's copy. n <= cap.
+ * One exchange buffer serves every norm of a model: the buffer does not depend on the weights (caminus_b200.dist.TPExchange). */
 int cam_ipc_open(const void * handle64, void ** base);      /* map another process's exported allocation (its 64-byte cudaIpcMemHandle_t) for the current device, peer access included */
 int cam_ipc_close(void * base);
 int cam_tp_rms_words(int cap, int world);
@@ -81,8 +84,9 @@ int cam_tp_rms_norm_f16(int n, void * x, const void * d, const float * nw, float
  * sized at start-up, or a process whose device memory is already fully handed out. x [n][N] fp16 (updated in place when d is
  * given), d fp16 (nullable), nw fp32 [N], h16 fp16 [n][N]; N a multiple of 8; same bytes as the pair with Ns = Nfull = N.
  * n > 65536 returns CAM_ERR_CAPACITY (split the batch). The first call on a device resolves the array's address: make it
- * before any stream capture. All calls on a device share the array: calls that can overlap on the GPU race; order them.
- * This entry has no counterpart in the reference. */
+ * before any stream capture. The address is kept per device ordinal for the life of the process: it does not survive a
+ * cudaDeviceReset (a process that resets a device must not call this entry on it again). All calls on a device share the
+ * array: calls that can overlap on the GPU race; order them. This entry has no counterpart in the reference. */
 int cam_rms_norm_f16_static(int n, void * x, const void * d, const float * nw, float eps, void * h16, int N, void * stream);
 
 /* y16[i] = fp16(silu(g[i]) * u[i]), i < n.

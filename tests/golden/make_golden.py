@@ -99,7 +99,7 @@ def make_rms():
     ww = g.random((n, S)).astype(np.float32); nw = (g.random(D) + 0.5).astype(np.float32)
     xr = x0.astype(np.float64) + np.einsum('ns,nsd->nd', ww.astype(np.float64), dd.astype(np.float64))
     hr = xr / np.sqrt((xr ** 2).mean(-1, keepdims=True) + 1e-6) * nw
-    # BASELINE config 1: hidden 2048, T = 1, seed 0, one generator per tensor in the listed order
+    # the decode-token case of the benchmark: hidden 2048, T = 1, seed 0, one generator per tensor in the listed order
     x1 = np.random.default_rng(0).standard_normal((1, 2048)).astype(np.float32)
     r1 = np.random.default_rng(0).standard_normal((1, 2048)).astype(np.float32)
     w1 = (1 + 0.05 * np.random.default_rng(0).standard_normal(2048)).astype(np.float32)

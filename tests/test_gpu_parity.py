@@ -67,7 +67,7 @@ def test_add_rms16_golden(O, golden):
     rel = lambda a, b: float(np.abs(a - b).max() / np.sqrt((b ** 2).mean()))
     assert rel(x.cpu().numpy(), f['xr']) < 1e-6 and rel(h.cpu().numpy(), f['hr']) < 2e-6        # tests/prefill/test_q3m_ops.py:162
     assert rel(h16.float().cpu().numpy(), f['hr']) < 2e-3
-    # BASELINE config 1: T = 1, hidden 2048, one added row
+    # the decode-token case: T = 1, hidden 2048, one added row
     x = cu(f['x1']); h = torch.zeros(1, 2048, device=DEV); h16 = torch.zeros(1, 2048, dtype=torch.float16, device=DEV)
     O.add_rms16(x, cu(f['w1']), 1e-6, h16, 1, 2048, d=cu(f['r1']), S=1, h=h)
     xo, ho, h16o = oracle.add_rms16(f['x1'], f['w1'], 1e-6, d=f['r1'].reshape(1, 1, -1), S=1)
@@ -119,6 +119,30 @@ def test_add_rms_f16(T, N, add):
     s = x0.astype(np.float64) + (r0.astype(np.float64) if add else 0)
     ref = oracle.rms_f64(s, w, 1e-6)
     assert (np.abs(h16.float().cpu().numpy() - ref) <= 2 * ulp16(ref) + 1e-5 * np.abs(ref).max()).all()   # 2 fp16 ulp / 1e-5
+
+
+@pytest.mark.parametrize('N', [28672, 29184, 57600, 58112, 65536])
+@pytest.mark.parametrize('add', [True, False])
+def test_add_rms_f16_rows_around_the_staging_limit(N, add):
+    """row lengths on both sides of what a warp can stage in shared memory (two stages of x and d: about 28 900 values with an addend,
+    57 800 without): the staged kernel below, the two-pass kernel above, one set of bytes; through the direct entry, the partial / apply
+    pair and the entry that keeps the sums in the library's static array"""
+    from caminus_b200 import lib
+    T = 5
+    x0, r0, w = synth.add_rms_inputs(T, N, seed=N, dtype=np.float16)
+    xo, ho = oracle.add_rms_f16(x0, w, 1e-6, r0 if add else None)
+    x = cu(x0); d = cu(r0) if add else None; nw = cu(w)
+    h16 = glue.add_rms_f16(x, nw, 1e-6, d=d)
+    assert same(x, xo) and same(h16, ho)
+    L = lib.load(); s = torch.cuda.current_stream().cuda_stream
+    x2 = cu(x0); ss = torch.zeros(T, device=DEV); h2 = torch.zeros_like(x2); dp = 0 if d is None else d.data_ptr()
+    lib.check(L.cam_rms_partial_f16(T, x2.data_ptr(), dp, ss.data_ptr(), N, s))
+    assert same(ss, oracle.rms_partial_f16(x0, r0 if add else None))
+    lib.check(L.cam_rms_apply_f16(T, x2.data_ptr(), dp, ss.data_ptr(), nw.data_ptr(), 1e-6, h2.data_ptr(), N, N, s))
+    assert same(x2, xo) and same(h2, ho)
+    x3 = cu(x0); h3 = torch.zeros_like(x3)
+    lib.check(L.cam_rms_norm_f16_static(T, x3.data_ptr(), dp, nw.data_ptr(), 1e-6, h3.data_ptr(), N, s))
+    assert same(x3, xo) and same(h3, ho)
 
 
 # ---- SwiGLU and Q8_1 ------------------------------------------------------------------------------------------------------
@@ -246,7 +270,7 @@ def test_swiglu_golden_reference_host_path(golden):
 
 
 def test_swiglu_q8_1_full_size_config():
-    """BASELINE config 3 (T = 8192, I = 25600): the whole output against the oracle on a strided sample of rows, and
+    """The SwiGLU + Q8_1 benchmark workload (T = 8192, I = 25600): the whole output against the oracle on a strided sample of rows, and
     size-independent properties of all of it: |q| <= 127, d >= 0, |x - d q| <= d / 2 up to fp16 rounding of d."""
     T, I = 8192, 25600
     g, u = synth.swiglu_inputs(T, I, seed=0)
@@ -315,7 +339,7 @@ def test_qk_rope_chunk(O, n, nh, nkv, pos0):
 
 @pytest.mark.parametrize('yarn', [False, True])
 def test_qk_rope_f16_config(yarn):
-    """BASELINE config 2: T = 4096, 32 q + 4 kv heads, positions 0 .. 4095; in place and out of place"""
+    """The q/k norm + RoPE benchmark workload: T = 4096, 32 q + 4 kv heads, positions 0 .. 4095; in place and out of place"""
     T, nh, nkv = 4096, 32, 4
     q, k = synth.qk_inputs(T, nh, nkv, seed=0)
     par = synth.rope_par(seed=0, yarn_table=synth.yarn_table() if yarn else None)
@@ -366,7 +390,7 @@ def test_module_interface():
 
 
 def test_layer_glue_sequence():
-    """the per-layer order of BASELINE config 5 at a small T: each op's bytes are the oracle's"""
+    """the per-layer order of the benchmarked sequence (Qwen3-32B shape) at a small T: each op's bytes are the oracle's"""
     T, N, nh, nkv, I = 96, 5120, 64, 8, 25600
     x0, r0, w = synth.add_rms_inputs(T, N, seed=5, dtype=np.float16)
     q0, k0 = synth.qk_inputs(T, nh, nkv, seed=5); g0, u0 = synth.swiglu_inputs(T, I, seed=5); par = synth.rope_par(seed=5)
@@ -381,7 +405,7 @@ def test_layer_glue_sequence():
 
 
 def test_config5_full_size_properties():
-    """BASELINE config 5 at its full per-GPU size (T = 65536 rows, 13.7 GB per pass), through size-independent properties:
+    """The benchmarked per-layer sequence at its full per-GPU size (T = 65536 rows, 13.7 GB per pass), through size-independent properties:
     chunk-split invariance (one launch == three launches over row ranges, bit for bit: the reference's own gate for its prefill),
     the updated residual == fp16(x + r) computed by torch, fast == strict SwiGLU blocks (d and codes) over all 52 M blocks,
     and rows sampled across the batch == the oracle"""

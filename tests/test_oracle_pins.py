@@ -85,7 +85,7 @@ def test_add_rms_against_float64(golden):
     rel = lambda a, b: float(np.abs(a - b).max() / np.sqrt((np.asarray(b, np.float64) ** 2).mean()))
     x, h, h16 = oracle.add_rms16(f['x0'], f['nw'], 1e-6, d=f['dd'], w=f['ww'], S=8)
     assert rel(x, f['xr']) < 1e-6 and rel(h, f['hr']) < 2e-6 and rel(h16.astype(np.float64), f['hr']) < 2e-3   # test_q3m_ops.py:162
-    # BASELINE config 1: one added row, the q3p (S = 1, no weights) and q35p forms agree bit for bit here
+    # the decode-token case: one added row, the q3p (S = 1, no weights) and q35p forms agree bit for bit here
     x1, h1, h116 = oracle.add_rms16(f['x1'], f['w1'], 1e-6, d=f['r1'].reshape(1, 1, -1), S=1)
     x2, h2, h216 = oracle.add_rms16_q35(f['x1'], f['w1'], 1e-6, d=f['r1'])
     assert np.abs(h1 - f['h1']).max() <= 1e-5 * np.abs(f['h1']).max() and np.array_equal(x1, f['s1'].astype(np.float32))
