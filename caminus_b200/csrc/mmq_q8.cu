@@ -184,6 +184,28 @@ static dim3 mmq_grid(K kernel, long nx, long ny) {
 // (one per chunk) are moved one to each of its lanes, so that the exact evaluation and the two IEEE divisions run once per
 // two chunks; that lane also stores the group's scale. (16 values per lane: the per-step work that does not depend on the
 // number of values is spent half as often as with 8.)
+// The margins of the proofs above: fp32 gates the analytic EPS = 1.35e-6; fp16 gates the bound enumerated over all 65 536 of them,
+// |h^ - h| <= 7.0e-7 |h| (csrc/swiglu_q8.cu, Q8Margins). D4: candidates for the maximum are the elements within 2 EPS (+ slack) of
+// amax^; codes t^ = h^ d_inv (exact d_inv) within EPS + 6e-8. DS4: d^ within EPS + 1.3e-7 of d (27 / 14 fp32 ulps: the tie test keeps
+// 44 / 24 clear); codes within 2 EPS + 3.0e-7; the sum within EPS + 7.2e-7 of the exact one, in units of A = sum |h^|.
+template <typename T> struct MmqMargins {
+    static constexpr int TIE = 44;
+    static CAM_DEV float candidates() { return 0.999997f; }
+    static CAM_DEV float d4_hi() { return 0x1.00001cp+0f; }      // 1 +- 1.67e-6
+    static CAM_DEV float d4_lo() { return 0x1.ffffc8p-1f; }
+    static CAM_DEV float ds4_hi() { return 0x1.000036p+0f; }     // 1 +- 3.2e-6
+    static CAM_DEV float ds4_lo() { return 0x1.ffff94p-1f; }
+    static CAM_DEV float sum() { return 2.3e-6f; }
+};
+template <> struct MmqMargins<uint16_t> {
+    static constexpr int TIE = 24;
+    static CAM_DEV float candidates() { return 0.9999984f; }     // 1 - 1.6e-6
+    static CAM_DEV float d4_hi() { return 0x1.000010p+0f; }      // 1 +- 9.5e-7
+    static CAM_DEV float d4_lo() { return 0x1.ffffe0p-1f; }
+    static CAM_DEV float ds4_hi() { return 0x1.000020p+0f; }     // 1 +- 1.91e-6
+    static CAM_DEV float ds4_lo() { return 0x1.ffffc0p-1f; }
+    static CAM_DEV float sum() { return 1.6e-6f; }
+};
 CAM_DEV float max_nan(float a, float b) { float r; asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
 // bits |= bit where |h| >= thr (a compare and a predicated OR)
 CAM_DEV void or_if_ge(uint32_t & bits, float h, float thr, uint32_t bit) {
@@ -217,15 +239,15 @@ template <> struct Raw8<float> {
 };
 
 // a warp's task: K-blocks 4 kq .. 4 kq + 3 (8 lanes each, 16 values per lane) of rows r0, r0 + 1
-struct MmqTask {
-    int r0, kb, k, s0, s1;                       // s0, s1: the input rows of output columns r0, r0 + 1 (the columns themselves without an index)
+template <bool IDS> struct MmqTask {
+    int r0, kb, k, s0, s1;                       // s0, s1: the input rows of output columns r0, r0 + 1 (IDS false: the columns themselves)
     bool kon, kin;
     CAM_DEV MmqTask(int kq, int rp, int lane, int nkb, int kvalid, const int * __restrict__ ids, int rows) {
         r0 = rp * 2;
         kb = kq * 4 + (lane >> 3); k = kb * 128 + (lane & 7) * 16;
         kon = kb < nkb; kin = kon && k < kvalid;
         s0 = r0; s1 = r0 + 1;
-        if (ids) {
+        if (IDS) {
             if (r0 < rows) s0 = min(max(__ldg(ids + r0), 0), rows - 1);
             if (r0 + 1 < rows) s1 = min(max(__ldg(ids + r0 + 1), 0), rows - 1);
         }
@@ -233,8 +255,8 @@ struct MmqTask {
 };
 
 // chunk c (row r0 + c) of a task: a lane's 16 values as two loads of 8
-template <typename T>
-CAM_DEV void mmq_fetch(const T * __restrict__ g, const T * __restrict__ u, const MmqTask & t, long ld, int rows, Raw8<T> (&rg)[2][2], Raw8<T> (&ru)[2][2]) {
+template <typename T, bool IDS>
+CAM_DEV void mmq_fetch(const T * __restrict__ g, const T * __restrict__ u, const MmqTask<IDS> & t, long ld, int rows, Raw8<T> (&rg)[2][2], Raw8<T> (&ru)[2][2]) {
 #pragma unroll
     for (int c = 0; c < 2; c++) {
         const size_t at = (size_t)(c ? t.s1 : t.s0) * ld + t.k;
@@ -253,7 +275,7 @@ CAM_DEV void mmq_fetch(const T * __restrict__ g, const T * __restrict__ u, const
 // Sum: the fast pass adds the h^ in the reference's order (((x0 + x1) + x2) + x3 per four, then partners 4, 2, 1: six levels); its sum is
 // within 2.07e-6 A of the exact statements', A = sum |h^|; where S^ - 2.3e-6 A and S^ + 2.3e-6 A round to one fp16, that is the stored sum.
 // Groups that fail any of it (about 7 % of Gaussian groups, most of them by the sum) are recomputed exactly as for D4.
-template <typename T, bool PF, int LAYOUT>
+template <typename T, bool PF, int LAYOUT, bool IDS>
 __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __restrict__ g, const T * __restrict__ u, uint8_t * __restrict__ y,
                                                                  int kvalid, int nkb, long ld, int rows, const int * __restrict__ ids) {
     const int lane = threadIdx.x & 31, pb = lane & 30, pi = lane & 1;      // a group of 32 values = the lane pair pb, pb + 1
@@ -263,14 +285,14 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
     if (rp0 >= nrp) return;
     int kq = blockIdx.y, rp = rp0;
     Raw8<T> rg[2][2], ru[2][2], ng[2][2], nu[2][2];
-    if (PF && kq < nkq) mmq_fetch(g, u, MmqTask(kq, rp, lane, nkb, kvalid, ids, rows), ld, rows, rg, ru);
+    if (PF && kq < nkq) mmq_fetch(g, u, MmqTask<IDS>(kq, rp, lane, nkb, kvalid, ids, rows), ld, rows, rg, ru);
     while (kq < nkq) {
-        const MmqTask t(kq, rp, lane, nkb, kvalid, ids, rows);
+        const MmqTask<IDS> t(kq, rp, lane, nkb, kvalid, ids, rows);
         const int kq_now = kq;
         rp += rstride;                                                // the next task
         if (rp >= nrp) { rp = rp0; kq += gridDim.y; }
         if (!PF) mmq_fetch(g, u, t, ld, rows, rg, ru);
-        else if (kq < nkq) mmq_fetch(g, u, MmqTask(kq, rp, lane, nkb, kvalid, ids, rows), ld, rows, ng, nu);
+        else if (kq < nkq) mmq_fetch(g, u, MmqTask<IDS>(kq, rp, lane, nkb, kvalid, ids, rows), ld, rows, ng, nu);
         float h[2][16], eg = 1.0f, eu = 0.0f;
         float am2[2] = {0.0f, 0.0f}, sum2[2] = {0.0f, 0.0f}, sab2[2] = {0.0f, 0.0f};      // DS4: the chunks' amax^, S^, A
         uint32_t bad = 0;                                             // bit c: chunk c of this lane fails a margin
@@ -293,17 +315,21 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
                 for (int e = 0; e < 8; e++) uv[8 + e] = t8[e];
             }
             float amax = 0.0f, gmin = gv[0], gsm = fabsf(gv[0]);
+            const f32x2 nlog2e = pk2(-0x1.715476p+0f, -0x1.715476p+0f), one2 = pk2(1.0f, 1.0f);      // two values per instruction: the same roundings
 #pragma unroll
-            for (int e = 0; e < 16; e++) {
-                const float ex = ex2_approx(fmul(gv[e], -0x1.715476p+0f));
-                h[c][e] = fmul(fmul(gv[e], rcp_approx(fadd(1.0f, ex))), uv[e]);
-                amax = max_nan(amax, fabsf(h[c][e]));
-                gmin = fminf(gmin, gv[e]);
-                if (sizeof(T) == 4) gsm = fminf(gsm, fabsf(gv[e]));
+            for (int e = 0; e < 16; e += 2) {
+                const f32x2 g2 = pk2(gv[e], gv[e + 1]);
+                const f32x2 a2 = mul2(g2, nlog2e);
+                const f32x2 den = add2(one2, pk2(ex2_approx(lo2(a2)), ex2_approx(hi2(a2))));
+                const f32x2 hh = mul2(mul2(g2, pk2(rcp_approx(lo2(den)), rcp_approx(hi2(den)))), pk2(uv[e], uv[e + 1]));
+                h[c][e] = lo2(hh); h[c][e + 1] = hi2(hh);
+                amax = max_nan(amax, max_nan(fabsf(h[c][e]), fabsf(h[c][e + 1])));
+                gmin = fminf(gmin, fminf(gv[e], gv[e + 1]));
+                if (sizeof(T) == 4) gsm = fminf(gsm, fminf(fabsf(gv[e]), fabsf(gv[e + 1])));
             }
             amax = max_nan(amax, __shfl_xor_sync(CAM_FULL, amax, 1));
             if constexpr (LAYOUT == 0) {
-                const float thr = fmul(amax, 0.999997f);
+                const float thr = fmul(amax, MmqMargins<T>::candidates());
                 uint32_t bits = 0;
 #pragma unroll
                 for (int e = 0; e < 16; e++) or_if_ge(bits, h[c][e], thr, 1u << e);
@@ -344,21 +370,23 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
             bool open = (bad >> c) & 1u, sum_open = false;       // (sum_open alone: scale and codes are proven, only the sum is recomputed)
             if constexpr (LAYOUT == 0) {
                 const float di = __shfl_sync(CAM_FULL, d_inv, pb + c);
-                inv_hi = fmul(di, 0x1.00001cp+0f); inv_lo = fmul(di, 0x1.ffffc8p-1f);              // 1 +- 1.67e-6
+                inv_hi = fmul(di, MmqMargins<T>::d4_hi()); inv_lo = fmul(di, MmqMargins<T>::d4_lo());
             } else {
                 const float dh = fmul(am2[c], 0x1.020408p-7f), di = fmul(127.0f, rcp_approx(am2[c]));
-                inv_hi = fmul(di, 0x1.000036p+0f); inv_lo = fmul(di, 0x1.ffff94p-1f);              // 1 +- 3.2e-6
+                inv_hi = fmul(di, MmqMargins<T>::ds4_hi()); inv_lo = fmul(di, MmqMargins<T>::ds4_lo());
                 const int low = (int)(__float_as_uint(dh) & 0x1fffu) - 0x1000;
-                const float margin = fmul(sab2[c], 2.3e-6f);
-                open = open || !(dh >= 6.2e-5f && dh < 6.0e4f) || (low >= -44 && low <= 44) || !(fabsf(sum2[c]) < 3.0e38f);
+                const float margin = fmul(sab2[c], MmqMargins<T>::sum());
+                open = open || !(dh >= 6.2e-5f && dh < 6.0e4f) || (low >= -MmqMargins<T>::TIE && low <= MmqMargins<T>::TIE) || !(fabsf(sum2[c]) < 3.0e38f);
                 sum_open = __half_as_ushort(__float2half_rn(fsub(sum2[c], margin))) != __half_as_ushort(__float2half_rn(fadd(sum2[c], margin)));
                 hdr2[c] = f2_to_h2(dh, sum2[c]);
             }
             uint32_t v[16], differ = 0;
+            const f32x2 ih2 = pk2(inv_hi, inv_hi), il2 = pk2(inv_lo, inv_lo), magic2 = pk2(12582912.0f, 12582912.0f);
 #pragma unroll
-            for (int e = 0; e < 16; e++) {
-                v[e] = __float_as_uint(ffma(h[c][e], inv_hi, 12582912.0f));
-                differ |= v[e] ^ __float_as_uint(ffma(h[c][e], inv_lo, 12582912.0f));
+            for (int e = 0; e < 16; e += 2) {
+                const f32x2 hh = pk2(h[c][e], h[c][e + 1]), a = fma2(hh, ih2, magic2), b = fma2(hh, il2, magic2);
+                v[e] = __float_as_uint(lo2(a)); v[e + 1] = __float_as_uint(hi2(a));
+                differ |= (v[e] ^ __float_as_uint(lo2(b))) | (v[e + 1] ^ __float_as_uint(hi2(b)));
             }
             const bool on = t.kon && t.r0 + c < rows;
             const uint32_t mask = __ballot_sync(CAM_FULL, (differ != 0 || open) && on);
@@ -449,10 +477,12 @@ int launch_mmq(const void * x, const void * u, void * y, int kvalid, int Kpad, l
     if (rows == 0) return CAM_OK;
     if (MODE != 0 && !(kvalid & 15) && !(ld & 7) && cam_aligned16(x) && cam_aligned16(u)) {
         const long nx = ((rows + 1) / 2 + 7) / 8, ny = (Kpad / 128 + 3) / 4;
-#define CAM_MMQ_FAST(TT, PF, LAY) mmq_swiglu_fast_kernel<TT, PF, LAY><<<mmq_grid(mmq_swiglu_fast_kernel<TT, PF, LAY>, nx, ny), 256, 0, stream>>>( \
+#define CAM_MMQ_FAST1(TT, PF, LAY, IDSV) mmq_swiglu_fast_kernel<TT, PF, LAY, IDSV><<<mmq_grid(mmq_swiglu_fast_kernel<TT, PF, LAY, IDSV>, nx, ny), 256, 0, stream>>>( \
                 (const TT *)x, (const TT *)u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows, ids)
+#define CAM_MMQ_FAST(TT, PF, LAY) do { if (ids) CAM_MMQ_FAST1(TT, PF, LAY, true); else CAM_MMQ_FAST1(TT, PF, LAY, false); } while (0)
         if (MODE == 2) { if (layout == 0) CAM_MMQ_FAST(uint16_t, true, 0); else CAM_MMQ_FAST(uint16_t, true, 1); }
         else { if (layout == 0) CAM_MMQ_FAST(float, false, 0); else CAM_MMQ_FAST(float, false, 1); }
+#undef CAM_MMQ_FAST1
 #undef CAM_MMQ_FAST
         return (int)cudaGetLastError();
     }

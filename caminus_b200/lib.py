@@ -36,6 +36,7 @@ SIGNATURES = {
     'gg_swiglu_q8_1_strict': [P, P, P, L, P],
     'gg_swiglu_q8_1_f16_strict': [P, P, P, L, P],
     'gg_silu_scale_q8_1': [P, F, P, L, P],
+    'cam_probe_silu_f16': [P, P, P, I, P],
     'gg_silu_scale_q8_1_sums': [P, F, P, L, P],
     'q3p_qk_rope': [I, P, I, I, I, P, I, P, P, P],
     'q3p_qk_rope_yarn': [I, P, I, I, I, P, I, P, P, P],

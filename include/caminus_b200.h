@@ -121,6 +121,10 @@ int gg_swiglu_q8_1_f16_strict(const void * g, const void * u, void * y, long n, 
  * the _sums form proves the block sum as well. */
 int gg_silu_scale_q8_1(const float * x, float rs, void * y, long n, void * stream);
 int gg_silu_scale_q8_1_sums(const float * x, float rs, void * y, long n, void * stream);
+/* For tests: exact[i] = the exact statements' silu of fp16 gate g[i], fast[i] = the special-function evaluation the fused entries' fast
+ * passes use. The fp16 entries' proofs rest on max |fast - exact| / |exact| <= 5.6e-7 over all gates >= -8 (measured: 5.43e-7 on sm_100a);
+ * tests/test_gpu_enumerated.py checks it on the device it runs on. No counterpart in the reference. */
+int cam_probe_silu_f16(const void * g, float * fast, float * exact, int n, void * stream);
 /* Block sums of the Q8_1 entries above (gg_quantize_q8_1, gg_swiglu_q8_1*, gg_silu_scale_q8_1*): added in the order of the reference's
  * eight-lane quantiser aq_fill (kernels/k3_gguf_ops.h:83-120: four values per lane, then partners 4, 2, 1), which the reference itself
  * uses beside the lane butterfly of gg_op_q8_1 (kernels/k3_gguf_ops.h:55-77) and documents as bitwise-equivalent for every consumer:

@@ -113,3 +113,18 @@ def test_silu_mul_actq_every_bf16_gate():
     assert int(fin.sum()) > M // 2
     assert torch.equal(s.view(torch.int32)[fin], s2.view(torch.int32)[fin])
     assert torch.equal(y.view(torch.int16)[fin], y2.view(torch.int16)[fin]) and torch.equal(c[fin], c2[fin])
+
+
+def test_fast_silu_bound_over_every_fp16_gate():
+    """the bound the fp16 entries' proofs rest on, measured on this device: over every fp16 gate >= -8 (zeros aside) the special-function
+    evaluation of silu is within 5.6e-7 of the exact statements' value (5.43e-7 on sm_100a; the proofs allow 7.0e-7 after the product)"""
+    from caminus_b200 import lib
+    pat = torch.arange(65536, device=DEV, dtype=torch.int32).to(torch.int16)
+    fast = torch.empty(65536, device=DEV); exact = torch.empty(65536, device=DEV)
+    lib.check(lib.load().cam_probe_silu_f16(pat.data_ptr(), fast.data_ptr(), exact.data_ptr(), 65536, torch.cuda.current_stream().cuda_stream))
+    g = pat.view(torch.float16).double()
+    ok = torch.isfinite(g) & (g >= -8.0) & (g != 0)
+    rel = ((fast.double() - exact.double()).abs() / exact.double().abs())[ok]
+    assert int(ok.sum()) == 50175 and float(rel.max()) <= 5.6e-7, float(rel.max())
+    true = g[ok] / (1 + torch.exp(-g[ok]))
+    assert float(((exact.double()[ok] - true).abs() / true.abs()).max()) <= 2.5e-7      # the exact statements against float64
