@@ -249,114 +249,136 @@ __global__ void __launch_bounds__(256) softmax_topk_rows_kernel(const float * __
 
 // ---- q3p_group: the (token, slot) pairs of a chunk listed by expert, and the experts' lists cut into work items of at most 64 pairs ------
 // One thread-block cluster of up to 8 blocks x 32 warps; no global scratch. A warp takes a contiguous run of pairs, 32 at a time:
-//   count    lanes holding the same expert find each other (match.any); the first of them adds their number to the warp's own row of
-//            counters in shared memory (a row per warp: no atomics);
-//   scan     a block adds its warps' rows, the blocks read one another's totals through distributed shared memory, and every block
-//            derives the same expert offsets (an exclusive scan over the experts) and its own start inside every expert's list; the
-//            warps' counter rows become their write cursors;
+//   count    lanes holding the same expert find each other (match.any); the first of them adds their number to the warp's own
+//            counter of that expert in shared memory (a cell per warp and expert: no atomics);
+//   scan     a block adds its warps' cells (a warp per expert, by shuffles), the blocks read one another's totals through distributed
+//            shared memory, and every block derives the same expert offsets (an exclusive scan over the experts) and its own start
+//            inside every expert's list; the warps' cells become their write cursors (a warp scan per expert);
 //   scatter  the second pass over the same pairs (kept in registers when a warp has at most 8 steps) writes pair p at cursor + its
 //            rank among the step's equal lanes.
 // A warp's pairs are ascending and the cursors follow (block, warp) order, so every expert's list is in ascending pair order: the
 // result does not depend on timing (the reference's order follows its atomics; it states that the order inside a list changes no bit
 // downstream), and the rows a GEMM gathers through xs ascend. An id outside [0, E) counts as expert 0 and sets err |= 2.
-constexpr int GR_WARPS = 32, GR_KEEP = 8;
+constexpr int GR_WARPS = 32, GR_KEEP = 8, GR_PITCH = GR_WARPS + 1;
 
+CAM_DEV int wscan_excl(int v, int lane) {            // exclusive prefix sum over the warp's lanes
+    int s = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(CAM_FULL, s, o); if (lane >= o) s += t; }
+    return s - v;
+}
+
+// kmul, kshift: p / k = (p * kmul) >> kshift for every 0 <= p < 2^31 (the host's round-up reciprocal of k)
 __global__ void __launch_bounds__(1024) group_cluster_kernel(const int * __restrict__ ids, int npairs, int k, int E, int * __restrict__ xs,
                                                              int * __restrict__ yd, WorkItem * __restrict__ items, int * __restrict__ nitems,
-                                                             int * __restrict__ err) {
+                                                             int * __restrict__ err, unsigned long long kmul, int kshift) {
     extern __shared__ int gr_smem[];
     cg::cluster_group cluster = cg::this_cluster();
     const int nblk = (int)cluster.num_blocks(), blk = (int)cluster.block_rank();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    int * rows = gr_smem;                        // [GR_WARPS][E]: a warp's counts, later its cursors
-    int * mine = rows + GR_WARPS * E;            // [E]: this block's count per expert (read by the other blocks)
+    int * cells = gr_smem;                       // [E][GR_PITCH]: cell (e, w) = warp w's count of expert e, later its cursor (a scan walks a row conflict-free)
+    int * mine = cells + E * GR_PITCH;           // [E]: this block's count per expert (read by the other blocks)
     int * first = mine + E;                      // [E]: where an expert's list starts
     int * ifirst = first + E;                    // [E]: where an expert's work items start
     int * total = ifirst + E;                    // [E]: pairs of an expert over all blocks
-    int * wsum_ = total + E;                     // [2][32]: the scan's per-warp sums
+    int * before = total + E;                    // [E]: pairs of an expert in the blocks before this one
+    int * wsum_ = before + E;                    // [3][32]: the expert scan's per-warp sums, then their prefixes; [96]: the number of items
     // this warp's run of pairs: `per` (a multiple of 32) consecutive pairs per warp, warps in (block, warp) order
     const int nw = nblk * GR_WARPS;
     const int per = ((npairs + nw - 1) / nw + 31) & ~31;
     const long lo = (long)(blk * GR_WARPS + warp) * per;
     const int steps = lo >= npairs ? 0 : (int)((min((long)npairs, lo + per) - lo + 31) >> 5);
-    int * row = rows + warp * E;
-    for (int e = lane; e < E; e += 32) row[e] = 0;
-    __syncwarp();
-    const unsigned below = (1u << lane) - 1u;
+    // the first GR_KEEP steps' ids are requested at once and stay in registers for the second pass
     int kept[GR_KEEP];
-    auto expert_of = [&](int s) {                // the expert of this lane's pair in step s (-1: past the end), range-checked
+    bool bad = false;
+#pragma unroll
+    for (int q = 0; q < GR_KEEP; q++) {
+        const long p = lo + 32 * q + lane;
+        kept[q] = q < steps && p < npairs ? __ldg(ids + p) : -1;
+    }
+#pragma unroll
+    for (int q = 0; q < GR_KEEP; q++)
+        if (q < steps && lo + 32 * q + lane < npairs && (kept[q] < 0 || kept[q] >= E)) { bad = true; kept[q] = 0; }
+    for (int i = tid; i < E * GR_PITCH; i += 1024) cells[i] = 0;
+    __syncthreads();
+    const unsigned below = (1u << lane) - 1u;
+    int * const col = cells + warp;              // + e GR_PITCH: this warp's cell of expert e
+    auto later = [&](int s) {                    // the expert of this lane's pair in a step past the kept ones (-1: past the end), range-checked
         const long p = lo + 32 * s + lane;
         if (p >= npairs) return -1;
         int e = __ldg(ids + p);
-        if (e < 0 || e >= E) { atomicOr(err, 2); e = 0; }
+        if (e < 0 || e >= E) { bad = true; e = 0; }
         return e;
     };
-    for (int s = 0; s < steps; s++) {
-        const int e = expert_of(s);
-        if (s < GR_KEEP) {
 #pragma unroll
-            for (int q = 0; q < GR_KEEP; q++) if (q == s) kept[q] = e;
+    for (int q = 0; q < GR_KEEP; q++)
+        if (q < steps) {
+            const int e = kept[q];
+            const unsigned same = __match_any_sync(CAM_FULL, e);
+            if (e >= 0 && (same & below) == 0) col[e * GR_PITCH] += __popc(same);
+            __syncwarp();
         }
+    for (int s = GR_KEEP; s < steps; s++) {
+        const int e = later(s);
         const unsigned same = __match_any_sync(CAM_FULL, e);
-        if (e >= 0 && (same & below) == 0) row[e] += __popc(same);
+        if (e >= 0 && (same & below) == 0) col[e * GR_PITCH] += __popc(same);
         __syncwarp();
     }
+    if (__any_sync(CAM_FULL, bad) && lane == 0) atomicOr(err, 2);
     __syncthreads();
-    for (int e = tid; e < E; e += 1024) {
-        int c = 0;
-        for (int w = 0; w < GR_WARPS; w++) c += rows[w * E + e];
-        mine[e] = c;
+    for (int e = warp; e < E; e += GR_WARPS) {   // a warp adds an expert's 32 cells
+        int c = cells[e * GR_PITCH + lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(CAM_FULL, c, o);
+        if (lane == 0) mine[e] = c;
     }
     cluster.sync();
-    // E <= 1024: thread e owns expert e from here on
-    int before = 0, tot = 0;
+    // E <= 1024: thread e owns expert e for the scan over the experts
+    int bef = 0, tot = 0;
     if (tid < E) {
         for (int b = 0; b < nblk; b++) {
             const int c = cluster.map_shared_rank(mine, b)[tid];
-            tot += c; if (b < blk) before += c;
+            tot += c; if (b < blk) bef += c;
         }
-        total[tid] = tot;
+        total[tid] = tot; before[tid] = bef;
     }
-    cluster.sync();                              // (no block leaves, or goes on to reuse anything, while another still reads its counts)
-    // exclusive scans over the experts of the pair counts and of the item counts: a warp scan, then the 32 warp sums
     const int nit = (tot + ITEM_PAIRS - 1) / ITEM_PAIRS;
-    int sc = tot, si = nit;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int a = __shfl_up_sync(CAM_FULL, sc, o), b = __shfl_up_sync(CAM_FULL, si, o);
-        if (lane >= o) { sc += a; si += b; }
-    }
-    if (lane == 31) { wsum_[warp] = sc; wsum_[32 + warp] = si; }
+    const int ex_c = wscan_excl(tot, lane), ex_i = wscan_excl(nit, lane);
+    if (lane == 31) { wsum_[warp] = ex_c + tot; wsum_[32 + warp] = ex_i + nit; }
     __syncthreads();
-    int base_c = 0, base_i = 0;
-    for (int w = 0; w < warp; w++) { base_c += wsum_[w]; base_i += wsum_[32 + w]; }
-    const int my_first = base_c + sc - tot, my_ifirst = base_i + si - nit;
-    if (tid < E) {
-        first[tid] = my_first; ifirst[tid] = my_ifirst;
-        int cur = my_first + before;
-        for (int w = 0; w < GR_WARPS; w++) { const int c = rows[w * E + tid]; rows[w * E + tid] = cur; cur += c; }
+    if (warp == 0) {                             // the 32 warp sums' prefixes
+        const int a = wsum_[lane], b = wsum_[32 + lane];
+        const int pa = wscan_excl(a, lane), pb = wscan_excl(b, lane);
+        wsum_[lane] = pa; wsum_[32 + lane] = pb;
+        if (lane == 31) wsum_[96] = pb + b;
     }
     __syncthreads();
-    int all_items = 0;
-    for (int w = 0; w < GR_WARPS; w++) all_items += wsum_[32 + w];
+    if (tid < E) { first[tid] = wsum_[warp] + ex_c; ifirst[tid] = wsum_[32 + warp] + ex_i; }
+    const int all_items = wsum_[96];
     if (blk == 0 && tid == 0) *nitems = all_items;
-    for (int s = 0; s < steps; s++) {
-        int e = -1;
-        if (s < GR_KEEP) {
-#pragma unroll
-            for (int q = 0; q < GR_KEEP; q++) if (q == s) e = kept[q];
-        } else {
-            const long p = lo + 32 * s + lane;
-            if (p < npairs) { e = __ldg(ids + p); if (e < 0 || e >= E) e = 0; }
-        }
-        const unsigned same = __match_any_sync(CAM_FULL, e);
+    __syncthreads();
+    for (int e = warp; e < E; e += GR_WARPS) {   // an expert's cells become its warps' cursors: the list's start, the earlier blocks, the earlier warps
+        const int c = cells[e * GR_PITCH + lane];
+        cells[e * GR_PITCH + lane] = first[e] + before[e] + wscan_excl(c, lane);
+    }
+    __syncthreads();
+    auto place = [&](int e, int s, unsigned same) {
         if (e >= 0) {
-            const int p = (int)(lo + 32 * s + lane), at = row[e] + __popc(same & below);
-            xs[at] = p / k; yd[at] = p;
+            const int p = (int)(lo + 32 * s + lane), at = col[e * GR_PITCH] + __popc(same & below);
+            xs[at] = (int)(((unsigned long long)(unsigned)p * kmul) >> kshift); yd[at] = p;
         }
         __syncwarp();
-        if (e >= 0 && (same & below) == 0) row[e] += __popc(same);
+        if (e >= 0 && (same & below) == 0) col[e * GR_PITCH] += __popc(same);
         __syncwarp();
+    };
+#pragma unroll
+    for (int q = 0; q < GR_KEEP; q++)
+        if (q < steps) place(kept[q], q, __match_any_sync(CAM_FULL, kept[q]));
+    for (int s = GR_KEEP; s < steps; s++) {
+        const long p = lo + 32 * s + lane;
+        int e = -1;
+        if (p < npairs) { e = __ldg(ids + p); if (e < 0 || e >= E) e = 0; }
+        place(e, s, __match_any_sync(CAM_FULL, e));
     }
     // the work items, spread over all threads of the cluster: item i belongs to the last expert whose items start at or before i
     for (int i = blk * 1024 + tid; i < all_items; i += nblk * 1024) {
@@ -366,6 +388,7 @@ __global__ void __launch_bounds__(1024) group_cluster_kernel(const int * __restr
         WorkItem it; it.expert = a; it.first = first[a] + j * ITEM_PAIRS; it.count = min(ITEM_PAIRS, total[a] - j * ITEM_PAIRS); it.zero = 0;
         items[i] = it;
     }
+    cluster.sync();                              // (no block leaves while another may still read its counts)
 }
 
 }   // namespace
@@ -409,8 +432,12 @@ extern "C" int pf_router(int T, const float * logits, int E, int k, float clamp,
 extern "C" int q3p_group(const int * ids, int npairs, int k, int E, int * xs, int * yd, void * items, int * nitems, int * err, void * stream) {
     if (npairs < 0 || k < 1 || E < 1 || E > 1024 || !ids || !xs || !yd || !items || !nitems || !err) return CAM_ERR_ARG;
     static unsigned long long allowed = 0;
-    const size_t smem = ((size_t)(GR_WARPS + 4) * E + 64) * sizeof(int);             // (E = 1024: 144 KB)
+    const size_t smem = ((size_t)(GR_PITCH + 5) * E + 128) * sizeof(int);             // (E = 1024: 152 KB)
     if (smem > 48 * 1024) { const cudaError_t e = cam_allow_smem(group_cluster_kernel, smem, allowed); if (e != cudaSuccess) return (int)e; }
+    // p / k as a multiplication: kshift = 32 + ceil(log2 k), kmul = ceil(2^kshift / k): exact for every p below 2^32
+    int l = 0; while ((1LL << l) < k) l++;
+    const int kshift = 32 + l;
+    const unsigned long long kmul = (unsigned long long)((((unsigned __int128)1 << kshift) + (unsigned)k - 1) / (unsigned)k);
     int nblk = 1;
     while (nblk < 8 && (long)nblk * 8192 < npairs) nblk *= 2;                         // 8 steps of 32 pairs per warp before the cluster grows
     cudaLaunchConfig_t cfg = {};
@@ -418,5 +445,5 @@ extern "C" int q3p_group(const int * ids, int npairs, int k, int E, int * xs, in
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = nblk; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, group_cluster_kernel, ids, npairs, k, E, xs, yd, (WorkItem *)items, nitems, err);
+    return (int)cudaLaunchKernelEx(&cfg, group_cluster_kernel, ids, npairs, k, E, xs, yd, (WorkItem *)items, nitems, err, kmul, kshift);
 }

@@ -134,14 +134,15 @@ __global__ void __launch_bounds__(128) tp_rms_kernel(uint16_t * __restrict__ x, 
 // partials have had DEPTH rows of time to cross NVLink, is gathered, normalised from shared memory and stored. No row is read from
 // HBM twice. A warp's wait (for its row, for the partials) is covered by the other warps of the multiprocessor: the launcher
 // trades slots per warp for resident warps.
-template <int LA, int DEPTH>
+// NCHT: the 16-byte chunks per lane and row fixed at compile time (0: computed from Ns): the chunk loops unroll, nothing is counted
+template <int LA, int DEPTH, int NCHT = 0>
 __global__ void __launch_bounds__(256) tp_rms_staged_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d, const float * __restrict__ nw, float eps,
                                                             uint16_t * __restrict__ h16, int Ns, int Nfull, int n, unsigned long long * const * __restrict__ peers,
                                                             int rank, int world, int cap, unsigned tag, int * status, int warps, unsigned long long wait_ns) {
     constexpr int S = LA + DEPTH + 1;
     extern __shared__ __align__(16) unsigned char tp_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nch = (Ns + 255) >> 8;
+    const int nch = NCHT ? NCHT : (Ns + 255) >> 8;
     const size_t half_bytes = (size_t)nch * 512, row_bytes = (d ? 2 : 1) * half_bytes;
     unsigned char * const slots = tp_smem + (size_t)warp * S * row_bytes;
     const int t0 = blockIdx.x * warps + warp, stride = gridDim.x * warps;
@@ -154,7 +155,8 @@ __global__ void __launch_bounds__(256) tp_rms_staged_kernel(uint16_t * __restric
         if (k < rows) {
             unsigned char * sx = slots + (size_t)(k % S) * row_bytes;
             const size_t at = (size_t)(t0 + k * stride) * Ns + 8 * lane;
-            for (int m = 0; m < nch; m++)
+#pragma unroll
+            for (int m = 0; m < (NCHT ? NCHT : nch); m++)
                 if (8 * lane + 256 * m < Ns) {
                     cp_async16(sx + (size_t)(m * 32 + lane) * 16, x + at + 256 * m);
                     if (d) cp_async16(sx + half_bytes + (size_t)(m * 32 + lane) * 16, d + at + 256 * m);
@@ -162,13 +164,16 @@ __global__ void __launch_bounds__(256) tp_rms_staged_kernel(uint16_t * __restric
         }
         cp_async_commit();
     };
-    auto row_values = [&](const unsigned char * sx, int m, float (&xs)[8]) {   // xs = x + d of this lane's chunk m
-        widen8(*reinterpret_cast<const uint4 *>(sx + (size_t)(m * 32 + lane) * 16), xs);
+    auto row_values = [&](const unsigned char * sx, int m, f32x2 (&xs)[4]) {   // xs = x + d of this lane's chunk m, two values per register pair
+        float xv[8];
+        widen8(*reinterpret_cast<const uint4 *>(sx + (size_t)(m * 32 + lane) * 16), xv);
+#pragma unroll
+        for (int c = 0; c < 4; c++) xs[c] = pk2(xv[2 * c], xv[2 * c + 1]);
         if (d) {
             float dv[8];
             widen8(*reinterpret_cast<const uint4 *>(sx + half_bytes + (size_t)(m * 32 + lane) * 16), dv);
 #pragma unroll
-            for (int c = 0; c < 8; c++) xs[c] = fadd(xs[c], dv[c]);
+            for (int c = 0; c < 4; c++) xs[c] = add2(xs[c], pk2(dv[2 * c], dv[2 * c + 1]));
         }
     };
 
@@ -180,15 +185,19 @@ __global__ void __launch_bounds__(256) tp_rms_staged_kernel(uint16_t * __restric
         cp_async_wait<LA>();                                             // row k has landed (later rows may still fly)
         if (k < rows && !dead) {                                         // ---- row k: this shard's sum of squares, sent to every rank
             const unsigned char * sx = slots + (size_t)(k % S) * row_bytes;
-            float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 4
-            for (int m = 0; m < nch; m++) {
-                if (8 * lane + 256 * m >= Ns) break;
-                float xs[8];
-                row_values(sx, m, xs);
+            f32x2 a2[4] = {pk2(0.0f, 0.0f), pk2(0.0f, 0.0f), pk2(0.0f, 0.0f), pk2(0.0f, 0.0f)};
 #pragma unroll
-                for (int c = 0; c < 8; c++) a[c] = ffma(xs[c], xs[c], a[c]);
+            for (int m = 0; m < (NCHT ? NCHT : nch); m++) {
+                if (8 * lane + 256 * m < Ns) {
+                    f32x2 xs[4];
+                    row_values(sx, m, xs);
+#pragma unroll
+                    for (int c = 0; c < 4; c++) a2[c] = fma2(xs[c], xs[c], a2[c]);
+                }
             }
+            float a[8];
+#pragma unroll
+            for (int c = 0; c < 4; c++) { a[2 * c] = lo2(a2[c]); a[2 * c + 1] = hi2(a2[c]); }
             const float part = ref_total_f16(a, lane);                   // (the bits of cam_rms_partial_f16)
             if (mine) st_sys_u64(mine + (t0 + k * stride), ((unsigned long long)tag << 32) | __float_as_uint(part));
         }
@@ -219,34 +228,34 @@ __global__ void __launch_bounds__(256) tp_rms_staged_kernel(uint16_t * __restric
             const float scale = cam_rsqrt(fadd(fdiv(tot, (float)Nfull), eps));
             const unsigned char * sx = slots + (size_t)(kd % S) * row_bytes;
             const size_t at = (size_t)t * Ns + 8 * lane;
-#pragma unroll 2
-            for (int m = 0; m < nch; m++) {
+            const f32x2 s2 = pk2(scale, scale);
+#pragma unroll
+            for (int m = 0; m < (NCHT ? NCHT : nch); m++) {
                 const int i = 8 * lane + 256 * m;
-                if (i >= Ns) break;
-                float xs[8];
-                row_values(sx, m, xs);
-                if (d) st128(x + at + 256 * m, make_uint4(f2_to_h2(xs[0], xs[1]), f2_to_h2(xs[2], xs[3]), f2_to_h2(xs[4], xs[5]), f2_to_h2(xs[6], xs[7])));
-                const float4 w0 = __ldg(reinterpret_cast<const float4 *>(nw + i)), w1 = __ldg(reinterpret_cast<const float4 *>(nw + i + 4));
-                float v[8];
-                v[0] = fmul(fmul(xs[0], scale), w0.x); v[1] = fmul(fmul(xs[1], scale), w0.y);
-                v[2] = fmul(fmul(xs[2], scale), w0.z); v[3] = fmul(fmul(xs[3], scale), w0.w);
-                v[4] = fmul(fmul(xs[4], scale), w1.x); v[5] = fmul(fmul(xs[5], scale), w1.y);
-                v[6] = fmul(fmul(xs[6], scale), w1.z); v[7] = fmul(fmul(xs[7], scale), w1.w);
-                st128_stream(h16 + at + 256 * m, make_uint4(f2_to_h2(v[0], v[1]), f2_to_h2(v[2], v[3]), f2_to_h2(v[4], v[5]), f2_to_h2(v[6], v[7])));
+                if (i < Ns) {
+                    f32x2 xs[4];
+                    row_values(sx, m, xs);
+                    if (d) st128(x + at + 256 * m, make_uint4(f2_to_h2(lo2(xs[0]), hi2(xs[0])), f2_to_h2(lo2(xs[1]), hi2(xs[1])), f2_to_h2(lo2(xs[2]), hi2(xs[2])),
+                                                              f2_to_h2(lo2(xs[3]), hi2(xs[3]))));
+                    const float4 w0 = __ldg(reinterpret_cast<const float4 *>(nw + i)), w1 = __ldg(reinterpret_cast<const float4 *>(nw + i + 4));
+                    const f32x2 v0 = mul2(mul2(xs[0], s2), pk2(w0.x, w0.y)), v1 = mul2(mul2(xs[1], s2), pk2(w0.z, w0.w));
+                    const f32x2 v2 = mul2(mul2(xs[2], s2), pk2(w1.x, w1.y)), v3 = mul2(mul2(xs[3], s2), pk2(w1.z, w1.w));
+                    st128_stream(h16 + at + 256 * m, make_uint4(f2_to_h2(lo2(v0), hi2(v0)), f2_to_h2(lo2(v1), hi2(v1)), f2_to_h2(lo2(v2), hi2(v2)), f2_to_h2(lo2(v3), hi2(v3))));
+                }
             }
         }
     }
     cp_async_wait<0>();
 }
 
-template <int LA, int DEPTH>
+template <int LA, int DEPTH, int NCHT = 0>
 int launch_tp_staged(int warps, size_t smem, int n, void * x, const void * d, const float * nw, float eps, void * h16, int Ns, int Nfull, const void * peers,
                      int rank, int world, int cap, unsigned tag, int * status, unsigned long long wait_ns, cudaStream_t stream) {
     static unsigned long long allowed = 0;
-    const cudaError_t e = cam_allow_smem(tp_rms_staged_kernel<LA, DEPTH>, 227 * 1024, allowed);
+    const cudaError_t e = cam_allow_smem(tp_rms_staged_kernel<LA, DEPTH, NCHT>, 227 * 1024, allowed);
     if (e != cudaSuccess) return (int)e;
-    const int grid = cam_resident_grid(tp_rms_staged_kernel<LA, DEPTH>, warps * 32, smem, ((long)n + warps - 1) / warps);
-    tp_rms_staged_kernel<LA, DEPTH><<<grid, warps * 32, smem, stream>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Ns, Nfull, n,
+    const int grid = cam_resident_grid(tp_rms_staged_kernel<LA, DEPTH, NCHT>, warps * 32, smem, ((long)n + warps - 1) / warps);
+    tp_rms_staged_kernel<LA, DEPTH, NCHT><<<grid, warps * 32, smem, stream>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Ns, Nfull, n,
                                                                         (unsigned long long * const *)peers, rank, world, cap, tag, status, warps, wait_ns);
     return (int)cudaGetLastError();
 }
@@ -279,7 +288,9 @@ extern "C" int cam_tp_rms_norm_f16(int n, void * x, const void * d, const float 
     cudaStream_t st = (cudaStream_t)stream;
     unsigned long long wait_ns = CAM_TP_WAIT_NS;    // CAMINUS_B200_TP_WAIT_MS: the limit of a wait in milliseconds (1 .. 600000)
     if (const char * e = getenv("CAMINUS_B200_TP_WAIT_MS")) { const long ms = atol(e); if (ms >= 1 && ms <= 600000) wait_ns = (unsigned long long)ms * 1000000ull; }
-    // Rows staged in shared memory. Measured on B200 (T = 65536, shards of 640 / 1280 / 2560 columns): resident warps matter more than
+    // Rows staged in shared memory. (Tried and not kept: rows converted once and held in fp32 registers, a half-warp per row of a 640-column
+    // shard: 200 instructions per row instead of 575, but 16 warps of 128 registers per multiprocessor hold too few rows in flight to
+    // cover the load and the exchange: 73.5 us against 67.4 us for 65536 rows on one rank.) Measured on B200 (T = 65536, shards of 640 / 1280 / 2560 columns): resident warps matter more than
     // rows in flight per warp: two slots per warp (one row waiting for its partials while the next is loaded and reduced) where
     // that still leaves 20 warps per multiprocessor, else one slot. CAMINUS_B200_TP_CFG="slots,warps" overrides (tuning).
     {
@@ -293,6 +304,11 @@ extern "C" int cam_tp_rms_norm_f16(int n, void * x, const void * d, const float 
         const size_t smem = (size_t)slots * warps * row_bytes;
         if (smem <= budget) {
 #define CAM_TP_STAGED(LAV, DV) return launch_tp_staged<LAV, DV>(warps, smem, n, x, d, nw, eps, h16, Ns, Nfull, peers, rank, world, cap, tag, status, wait_ns, st);
+#define CAM_TP_FIXED(LAV, DV, NCHV) return launch_tp_staged<LAV, DV, NCHV>(warps, smem, n, x, d, nw, eps, h16, Ns, Nfull, peers, rank, world, cap, tag, status, wait_ns, st);
+            // the usual shards (5120 or 4096 columns over 2, 4 or 8 ranks): the chunk count is a compile-time constant
+            const int nch_ = (Ns + 255) >> 8;
+            if (slots == 2) { switch (nch_) { case 2: CAM_TP_FIXED(0, 1, 2) case 3: CAM_TP_FIXED(0, 1, 3) case 4: CAM_TP_FIXED(0, 1, 4) case 5: CAM_TP_FIXED(0, 1, 5) default: break; } }
+            if (slots == 1) { switch (nch_) { case 8: CAM_TP_FIXED(0, 0, 8) case 10: CAM_TP_FIXED(0, 0, 10) default: break; } }
             switch (slots) {
                 case 1: CAM_TP_STAGED(0, 0)
                 case 2: CAM_TP_STAGED(0, 1)
@@ -300,6 +316,7 @@ extern "C" int cam_tp_rms_norm_f16(int n, void * x, const void * d, const float 
                 default: CAM_TP_STAGED(1, 2)
             }
 #undef CAM_TP_STAGED
+#undef CAM_TP_FIXED
         }
     }
     // longer rows: two passes over the row, four rows apart
