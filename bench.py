@@ -255,9 +255,6 @@ def single_op_lines(torch, dev, peak, only=(), headline=False):
             srcs = [torch.empty(half, dtype=torch.uint8, device=dev) for _ in range(4)]; dsts = [torch.empty(half, dtype=torch.uint8, device=dev) for _ in range(4)]
             cmed, _ = timed(lambda i: dsts[i].copy_(srcs[i]), rot=4)()
             out[name]['us_plain_copy_same_bytes'] = cmed * 1e6; out[name]['frac_of_plain_copy_same_bytes'] = cmed / med
-            if graph_fn is not None:
-                cg = graphed(lambda i: dsts[i % 4].copy_(srcs[i % 4]), 40)
-                if isinstance(cg, float): out[name]['us_plain_copy_in_cuda_graph'] = cg * 1e6
 
     g = torch.Generator(device=dev); g.manual_seed(0)
     # config 1: add + RMSNorm fp32, hidden 2048: T = 1 (latency) and a T sweep
@@ -352,10 +349,15 @@ def single_op_lines(torch, dev, peak, only=(), headline=False):
     line('q3p_router_T8192_E128_K2048', n * K * 4 + E * K * 4 + n * E * 4, timed(lambda i: O.router(hh, Wr, E, K, lg, n)), n, 'tokens_per_s')
     if 'q3p_router_T8192_E128_K2048' in out: out['q3p_router_T8192_E128_K2048']['gflops'] = 2.0 * n * E * K / out['q3p_router_T8192_E128_K2048']['us_median'] / 1e3
     ids = torch.zeros(n * k, dtype=torch.int32, device=dev); wts = torch.zeros(n * k, device=dev); er = torch.zeros(1, dtype=torch.int32, device=dev)
-    line('q3p_topk_T8192_E128_k8', n * E * 4 + n * k * 8, timed(lambda i: O.topk(lg, E, k, 6.103515625e-5, ids, wts, er, n)), n, 'tokens_per_s')
+    line('q3p_topk_T8192_E128_k8', n * E * 4 + n * k * 8, timed(lambda i: O.topk(lg, E, k, 6.103515625e-5, ids, wts, er, n)), n, 'tokens_per_s',
+         graph_fn=lambda i: O.topk(lg, E, k, 6.103515625e-5, ids, wts, er, n))
     xs_, yd_ = (torch.zeros(n * k, dtype=torch.int32, device=dev) for _ in range(2))
     items = torch.zeros(q3m_ops.items_bound(n * k, E), 4, dtype=torch.int32, device=dev); nit = torch.zeros(1, dtype=torch.int32, device=dev)
-    line('q3p_group_65536_pairs_E128', n * k * 12, timed(lambda i: O.group(ids, n * k, k, E, xs_, yd_, items, nit, er)), n, 'tokens_per_s')
+    line('q3p_group_65536_pairs_E128', n * k * 12, timed(lambda i: O.group(ids, n * k, k, E, xs_, yd_, items, nit, er)), n, 'tokens_per_s',
+         graph_fn=lambda i: O.group(ids, n * k, k, E, xs_, yd_, items, nit, er))
+    lg256 = rnd(2048, 256, scale=3.0); ids10 = torch.zeros(2048 * 10, dtype=torch.int32, device=dev); wts10 = torch.zeros(2048 * 10, device=dev)
+    line('pf_router_T2048_E256_k10', 2048 * 256 * 4 + 2048 * 10 * 8, timed(lambda i: gl.router(lg256, 2048, 256, 10, ids10, wts10, er)), 2048, 'tokens_per_s',
+         graph_fn=lambda i: gl.router(lg256, 2048, 256, 10, ids10, wts10, er))
     del hh, Wr, lg
     from caminus_b200.device import cuda as CU
     feed = CU.Module('prefill_feed'); I = ctypes.c_int

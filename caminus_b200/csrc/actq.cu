@@ -351,6 +351,153 @@ __global__ void __launch_bounds__(256) block_entry_rows_kernel(const float * __r
     }
 }
 
+// ---- sixteen values per lane --------------------------------------------------------------------------------------------------------
+// The kernels above give a lane 4 values of a chunk of 128, so five of the seven butterfly stages cross lanes: a shuffle and an fma per
+// value and stage. Here a lane holds 16 consecutive values (8 lanes a chunk, four chunks per warp step): stages 1 .. 8 stay inside the
+// lane, stages 16, 32, 64 exchange with lanes l ^ 1, l ^ 2, l ^ 4, and the arithmetic of neighbouring values runs two at a time (packed
+// fp32 add, sub, fma, mul: the same roundings). A stage's statements are the reference's whatever lane holds a value: the element
+// whose index has the stage's bit clear becomes own + partner, the other partner - own. Per 32 values 24 warp instructions instead of
+// 44. A row's transformed values stay in registers as bf16 pairs between the amax and the codes; rows longer than 2048 take two or four
+// warps (at most 2048 values each: 80 registers) that exchange their maxima through shared memory.
+CAM_DEV void fwht_wide(f32x2 (&p)[8], int l8) {
+    // stage 1: the two values of a pair
+#pragma unroll
+    for (int i = 0; i < 8; i++) { const float a = lo2(p[i]), b = hi2(p[i]); p[i] = pk2(fadd(a, b), fsub(a, b)); }
+    // stages 2, 4, 8: pairs of register pairs
+#pragma unroll
+    for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            if (!(i & h)) { const f32x2 a = p[i], b = p[i + h]; p[i] = add2(a, b); p[i + h] = sub2(a, b); }
+    // stages 16, 32, 64: lanes l ^ 1, l ^ 2, l ^ 4 of the chunk's eight
+#pragma unroll
+    for (int m = 1; m < 8; m <<= 1) {
+        const float sg = (l8 & m) ? -1.0f : 1.0f;        // the upper lane of a pair holds partner - own: fma(own, -1, partner), one rounding
+        const f32x2 sg2 = pk2(sg, sg);
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            p[i] = fma2(p[i], sg2, pk2(__shfl_xor_sync(CAM_FULL, lo2(p[i]), m), __shfl_xor_sync(CAM_FULL, hi2(p[i]), m)));
+    }
+}
+CAM_DEV bool bf16_word_has_nan(uint32_t w) { return (((w & 0x7fff7fffu) + 0x007f007fu) & 0x80008000u) != 0; }
+
+// STEPS: warp steps of 512 values per row and warp; WPR: warps per row (1, 2 or 4)
+template <typename Src, int STEPS, int WPR>
+__global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __restrict__ y, float * __restrict__ s_out, int K, float clip, int qmax,
+                                                        uint16_t * __restrict__ codes, int M) {
+    __shared__ float wmax[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g8 = lane >> 3, l8 = lane & 7;
+    const int nch = K >> 7;
+    constexpr int RPB = 8 / WPR;                                         // rows per block and pass
+    const int part = WPR == 1 ? 0 : (warp & (WPR - 1));                  // this warp's part of the row: chunks part STEPS 4 ..
+    for (int r0 = blockIdx.x * RPB; r0 < M; r0 += gridDim.x * RPB) {     // (block-uniform: every warp takes part in the barrier below)
+        const int row = r0 + warp / WPR;
+        const bool row_on = row < M;
+        uint32_t up[STEPS][8];                                           // the transformed values, bf16 pairs
+        float amax = 0.f;
+#pragma unroll
+        for (int st = 0; st < STEPS; st++) {
+            const int ch = (part * STEPS + st) * 4 + g8;
+            const bool on = row_on && ch < nch;
+            float v[16];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                float t4[4] = {0.f, 0.f, 0.f, 0.f};
+                if (on) src.get4(row, ch * 128 + l8 * 16 + 4 * q, t4);
+                if (!Src::kBf16) rbf4(t4);
+#pragma unroll
+                for (int e = 0; e < 4; e++) v[4 * q + e] = t4[e];
+            }
+            f32x2 p[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) p[i] = pk2(v[2 * i], v[2 * i + 1]);
+            fwht_wide(p, l8);
+            const f32x2 c2 = pk2(0.08837890625f, 0.08837890625f);
+            bool nan = false;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const f32x2 t = mul2(p[i], c2);
+                uint32_t w;
+                asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi2(t)), "f"(lo2(t)));
+                up[st][i] = w;
+                nan |= bf16_word_has_nan(w);
+                amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w << 16)), fabsf(__uint_as_float(w & 0xffff0000u))));
+            }
+            if (nan) {                                                   // (a NaN is stored as 0x7fc0, the reference's f2bf; the conversion gives 0x7fff)
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    uint32_t w = up[st][i];
+                    if ((w & 0x7fffu) > 0x7f80u) w = (w & 0xffff0000u) | 0x7fc0u;
+                    if ((w & 0x7fff0000u) > 0x7f800000u) w = (w & 0x0000ffffu) | 0x7fc00000u;
+                    up[st][i] = w;
+                }
+            }
+        }
+        amax = wave_max(amax);
+        if (WPR > 1) {
+            if (lane == 0) wmax[warp] = amax;
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < WPR; i++) amax = fmaxf(amax, wmax[(warp & ~(WPR - 1)) + i]);
+            __syncthreads();
+        }
+        const float s = fmaxf(fdiv(fmul(amax, clip), (float)qmax), 1e-8f);
+        if (lane == 0 && part == 0 && row_on && s_out) s_out[row] = s;
+        const float lo = (float)(-qmax - 1), hi = (float)qmax;
+        // rint(u / s) without the division where that is provably the same integer (actq_emit above): two-ended rounding test per value
+        const float inv = rcp_approx(s);
+        const f32x2 ih2 = pk2(fmul(inv, 0x1.000008p+0f), fmul(inv, 0x1.000008p+0f)), il2 = pk2(fmul(inv, 0x1.fffff0p-1f), fmul(inv, 0x1.fffff0p-1f));
+        const f32x2 magic2 = pk2(12582912.0f, 12582912.0f), s2 = pk2(s, s);
+        const bool fast = s < 3.0e38f && fmul(amax, inv) < 4.0e6f;       // (s >= 1e-8; false for a NaN)
+#pragma unroll
+        for (int st = 0; st < STEPS; st++) {
+            const int ch = (part * STEPS + st) * 4 + g8;
+            if (!(row_on && ch < nch)) continue;
+            uint32_t yw[8], cw[2] = {0u, 0u};
+            f32x2 q2[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t w = up[st][i];
+                const float u0 = __uint_as_float(w << 16), u1 = __uint_as_float(w & 0xffff0000u);
+                const f32x2 u = pk2(u0, u1);
+                const f32x2 vh = fma2(u, ih2, magic2), vl = fma2(u, il2, magic2);
+                const f32x2 r = sub2(vh, magic2);
+                q2[i] = pk2(copysignf(lo2(r), u0), copysignf(hi2(r), u1));                                   // (rint keeps the sign of a zero)
+                // a pair whose two ends differ (a quotient on or next to a .5 boundary: bf16 operands make exact ties common) is divided
+                if ((((__float_as_uint(lo2(vh)) ^ __float_as_uint(lo2(vl))) | (__float_as_uint(hi2(vh)) ^ __float_as_uint(hi2(vl)))) != 0) || !fast)
+                    q2[i] = pk2(rintf(fdiv(u0, s)), rintf(fdiv(u1, s)));
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float a = fminf(fmaxf(lo2(q2[i]), lo), hi), b = fminf(fmaxf(hi2(q2[i]), lo), hi);
+                // the code's low four bits from the clamped integer's place under 1.5 * 2^23
+                const uint32_t na = __float_as_uint(fadd(a, 12582912.0f)) & 0xFu, nb = __float_as_uint(fadd(b, 12582912.0f)) & 0xFu;
+                cw[i >> 2] |= (na | (nb << 4)) << (8 * (i & 3));
+                const f32x2 d2 = mul2(pk2(a, b), s2);
+                yw[i] = bf16x2<true>(lo2(d2), hi2(d2));
+            }
+            const size_t at = (size_t)row * K + ch * 128 + l8 * 16;
+            if (y) { st128(y + at, make_uint4(yw[0], yw[1], yw[2], yw[3])); st128(y + at + 8, make_uint4(yw[4], yw[5], yw[6], yw[7])); }
+            if (codes) st64(codes + (at >> 2), make_uint2(cw[0], cw[1]));
+        }
+    }
+}
+
+// the sixteen-values-per-lane launch: rows of up to 8192 values whose loads and stores are 16-byte aligned; false: the caller's other kernels
+template <typename Src>
+bool launch_actq_wide(Src src, bool aligned, int M, uint16_t * y, float * s, int K, float clip, int qmax, uint16_t * codes, cudaStream_t stream) {
+    if (!aligned || (y && !cam_aligned16(y)) || (codes && (reinterpret_cast<uintptr_t>(codes) & 7u))) return false;
+    const long want8 = ((long)M + 7) / 8, want4 = ((long)M + 3) / 4, want2 = ((long)M + 1) / 2;
+#define CAM_AQ_WIDE(STV, WPRV, WANT) actq_wide_kernel<Src, STV, WPRV><<<cam_resident_grid(actq_wide_kernel<Src, STV, WPRV>, 256, 0, WANT), 256, 0, stream>>>(src, y, s, K, clip, qmax, codes, M)
+    if (K <= 512) CAM_AQ_WIDE(1, 1, want8);
+    else if (K <= 1024) CAM_AQ_WIDE(2, 1, want8);
+    else if (K <= 2048) CAM_AQ_WIDE(4, 1, want8);
+    else if (K <= 4096) CAM_AQ_WIDE(4, 2, want4);
+    else CAM_AQ_WIDE(4, 4, want2);
+#undef CAM_AQ_WIDE
+    return true;
+}
+
 // the warp-per-row launch when the row fits (K <= 2048) and its loads are aligned; false: the caller uses the block-per-row kernel
 template <typename Src>
 bool launch_actq_rows(Src src, bool aligned, int M, uint16_t * y, float * s, int K, float clip, int qmax, uint16_t * codes, cudaStream_t stream) {
@@ -376,7 +523,8 @@ bool misaligned8(const void * p) { return p && (reinterpret_cast<uintptr_t>(p) &
 extern "C" int actq_fwd_codes_bf16(int M, const void * x, void * y, float * s, void * codes, int K, float clip, int qmax, void * stream) {
     const int r = check_actq(M, K, qmax, x, s); if (r || M == 0) return r;
     if (misaligned8(y)) return CAM_ERR_ALIGN;
-    if (!launch_actq_rows(PlainBf16{(const uint16_t *)x, K}, !misaligned8(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST)) {
+    if (!launch_actq_wide(PlainBf16{(const uint16_t *)x, K}, !misaligned8(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST) &&
+        !launch_actq_rows(PlainBf16{(const uint16_t *)x, K}, !misaligned8(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST)) {
         if (!misaligned8(x)) actq_kernel<PlainBf16, true><<<M, 256, 0, CAM_ST>>>(PlainBf16{(const uint16_t *)x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
         else actq_kernel<<<M, 256, 0, CAM_ST>>>(PlainBf16{(const uint16_t *)x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
     }
@@ -385,7 +533,8 @@ extern "C" int actq_fwd_codes_bf16(int M, const void * x, void * y, float * s, v
 extern "C" int actq_fwd_codes_f32(int M, const float * x, void * y, float * s, void * codes, int K, float clip, int qmax, void * stream) {
     const int r = check_actq(M, K, qmax, x, s); if (r || M == 0) return r;
     if (misaligned8(y)) return CAM_ERR_ALIGN;
-    if (!launch_actq_rows(PlainF32{x, K}, cam_aligned16(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST)) {
+    if (!launch_actq_wide(PlainF32{x, K}, cam_aligned16(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST) &&
+        !launch_actq_rows(PlainF32{x, K}, cam_aligned16(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST)) {
         if (cam_aligned16(x)) actq_kernel<PlainF32, true><<<M, 256, 0, CAM_ST>>>(PlainF32{x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
         else actq_kernel<<<M, 256, 0, CAM_ST>>>(PlainF32{x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
     }
@@ -404,7 +553,8 @@ extern "C" int silu_mul_actq_fwd(int M, const void * gu, int ld, int F, void * y
     if (misaligned8(y)) return CAM_ERR_ALIGN;
     if (M == 0) return CAM_OK;
     const bool vec = !misaligned8(gu) && !(ld & 3);
-    if (!launch_actq_rows(SiluMulSrc{(const uint16_t *)gu, ld, F}, vec, M, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes, CAM_ST)) {
+    if (!launch_actq_wide(SiluMulSrc{(const uint16_t *)gu, ld, F}, vec, M, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes, CAM_ST) &&
+        !launch_actq_rows(SiluMulSrc{(const uint16_t *)gu, ld, F}, vec, M, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes, CAM_ST)) {
         if (vec) actq_kernel<SiluMulSrc, true><<<M, 256, 0, CAM_ST>>>(SiluMulSrc{(const uint16_t *)gu, ld, F}, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes);
         else actq_kernel<<<M, 256, 0, CAM_ST>>>(SiluMulSrc{(const uint16_t *)gu, ld, F}, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes);
     }
