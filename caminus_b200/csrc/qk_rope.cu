@@ -502,6 +502,180 @@ __global__ void __launch_bounds__(128) qk_rope_f16_tok_kernel(const RopeArgs A) 
     cp_async_wait<0>();
 }
 
+// ---- the reference's signature (fp32 qkv rows in; q16 and the KV cache row out) with the token-shaped mapping --------------------------
+// As qk_rope_f16_tok_kernel: a warp owns a token and walks its q rounds, its k rounds and then its v rounds of four pairs of heads,
+// unrolled. A pair of fp32 heads is 1024 bytes (two 16-byte cp.async per lane); the ring has two slots of a round each, the next round
+// requested while this one is computed. q heads go to q16, k heads into the K half of cache row pos0 + t, v heads are rounded to fp16
+// into its V half. Q8: the Q8_0 cache form (csrc/kv_q8.cuh): every q and k head is rounded to fp16, transformed (Hadamard-128) and
+// stored as fp16 (q16) or as four Q8_0 blocks (K); V as four Q8_0 blocks of its fp16-rounded values.
+CAM_DEV float4 lds128f(uint32_t smem_addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_addr));
+    return v;
+}
+
+template <int NQ2, int NK2, bool Q8>
+__global__ void __launch_bounds__(128) qk_rope_cache_tok_kernel(const RopeArgs A) {
+    constexpr int RQ = NQ2 / 4, RK = (NK2 + 3) / 4, R = RQ + 2 * RK;
+    static_assert(NQ2 % 4 == 0 && (NK2 <= 4 || NK2 % 4 == 0), "rounds of four pairs of heads");
+    __shared__ __align__(16) float wsm[256], freq[64];
+    __shared__ __align__(16) unsigned char ring_all[4 * 2 * 4096];       // [4 warps][2 slots][a round: 4 pairs x 1024 bytes]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int hw = lane >> 4, l16 = lane & 15;
+    const int tw = blockIdx.x * 4 + warp, stride = gridDim.x * 4;
+    const int ntok = tw < A.n ? (A.n - tw + stride - 1) / stride : 0;
+    const uint32_t slots = (uint32_t)__cvta_generic_to_shared(ring_all) + warp * 8192 + lane * 16;      // where this lane copies to
+    const uint32_t mine = slots - lane * 16 + hw * 512 + l16 * 16;                                      // where it reads its low piece (the high piece: + 256)
+    const size_t tstep = (size_t)stride * A.ldq * 4;                                                    // bytes between this warp's tokens
+    const unsigned char * in = reinterpret_cast<const unsigned char *>(A.in0) + (size_t)tw * A.ldq * 4 + lane * 16;
+    auto np_of = [&](int i) { return i < RQ ? 4 : ((i - RQ) % RK == RK - 1 && (NK2 & 3) ? (NK2 & 3) : 4); };      // pairs in round i
+    auto src_of = [&](int i) { return i < RQ ? i * 4096 : (i < RQ + RK ? NQ2 * 1024 + (i - RQ) * 4096 : (NQ2 + NK2) * 1024 + (i - RQ - RK) * 4096); };
+    auto request = [&](int i, const unsigned char * tok, uint32_t slot, bool on) {      // round i (a constant after unrolling) of the token at `tok`
+        if (on) {
+            const int np = np_of(i);
+            const unsigned char * src = tok + src_of(i);
+#pragma unroll
+            for (int p = 0; p < 4; p++)
+                if (p < np) { cp_async16_s(slots + slot + p * 1024, src + p * 1024); cp_async16_s(slots + slot + p * 1024 + 512, src + p * 1024 + 512); }
+        }
+        cp_async_commit();
+    };
+    request(0, in, 0, ntok > 0);
+    wsm[tid] = __ldg(A.par + tid); wsm[128 + tid] = __ldg(A.par + 128 + tid);
+    if (tid < 64) freq[tid] = A.yarn ? __ldg(A.par + 258 + tid) : cam_powi(__ldg(A.par + 256), tid);
+    const float eps = __ldg(A.par + 257), mscale = A.yarn ? __ldg(A.par + 322) : 1.0f;
+    __syncthreads();
+    const float f0 = freq[4 * l16 + 2 * hw], f1 = freq[4 * l16 + 2 * hw + 1];
+    f32x2 wq2[4], wk2[4];
+    {
+        const float4 a = *reinterpret_cast<const float4 *>(wsm + 4 * l16), b = *reinterpret_cast<const float4 *>(wsm + 64 + 4 * l16);
+        const float4 c = *reinterpret_cast<const float4 *>(wsm + 128 + 4 * l16), e = *reinterpret_cast<const float4 *>(wsm + 192 + 4 * l16);
+        wq2[0] = pk2(a.x, a.y); wq2[1] = pk2(a.z, a.w); wq2[2] = pk2(b.x, b.y); wq2[3] = pk2(b.z, b.w);
+        wk2[0] = pk2(c.x, c.y); wk2[1] = pk2(c.z, c.w); wk2[2] = pk2(e.x, e.y); wk2[3] = pk2(e.z, e.w);
+    }
+    const bool up8 = l16 & 8, up4 = l16 & 4;
+    uint32_t cur = 0;                                                    // the ring slot (byte offset 0 / 4096) that holds the round being computed
+    int t = tw;
+    for (int k = 0; k < ntok; k++, t += stride) {
+        f32x2 cc[2], sn[2], nsn[2];
+        {
+            const float pos = (float)(A.pos0 + t);
+            float s0, c0, s1, c1;
+            cam_sincos(fmul(pos, f0), s0, c0); cam_sincos(fmul(pos, f1), s1, c1);
+            if (A.yarn) { c0 = fmul(c0, mscale); s0 = fmul(s0, mscale); c1 = fmul(c1, mscale); s1 = fmul(s1, mscale); }
+            const float oc0 = __shfl_xor_sync(CAM_FULL, c0, 16), os0 = __shfl_xor_sync(CAM_FULL, s0, 16);
+            const float oc1 = __shfl_xor_sync(CAM_FULL, c1, 16), os1 = __shfl_xor_sync(CAM_FULL, s1, 16);
+            const float ca = hw ? oc0 : c0, cb = hw ? oc1 : c1, cc_ = hw ? c0 : oc0, cd = hw ? c1 : oc1;
+            const float sa = hw ? os0 : s0, sb = hw ? os1 : s1, sc_ = hw ? s0 : os0, sd = hw ? s1 : os1;
+            cc[0] = pk2(ca, cb); cc[1] = pk2(cc_, cd); sn[0] = pk2(sa, sb); sn[1] = pk2(sc_, sd); nsn[0] = pk2(-sa, -sb); nsn[1] = pk2(-sc_, -sd);
+        }
+        const bool more = k + 1 < ntok;
+        const unsigned char * nxt = in + tstep;
+        const int pos = A.pos0 + t;
+        uint16_t * const qrow = A.out0 + (size_t)t * NQ2 * 256 + hw * 128 + 4 * l16;
+        uint16_t * const krow = A.out1 + (size_t)pos * NK2 * 512 + hw * 128 + 4 * l16;                      // F16 cache: K [nkv][128] | V [nkv][128]
+        uint8_t * const cw = reinterpret_cast<uint8_t *>(A.out1) + (size_t)pos * (NK2 * 4 * 4 * 34) + (size_t)hw * 4 * 34 + (size_t)(l16 >> 3) * 34;   // Q8: K blocks | V blocks
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            // the next round (of this token, or the first of the next) into the other slot, then wait for this round's copies
+            if (i + 1 < R) request(i + 1, in, cur ^ 4096u, true); else request(0, nxt, cur ^ 4096u, more);
+            cp_async_wait<1>();
+            __syncwarp();
+            const int np = np_of(i);
+            const bool isq = i < RQ, isk = !isq && i < RQ + RK;
+            const int h0 = isq ? 8 * i : (isk ? 8 * (i - RQ) : 8 * (i - RQ - RK));      // the round's first head within its kind
+            if (isq || isk) {
+                f32x2 xl[4][2], xh[4][2]; float ss[4];
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                    if (p < np) {
+                        const float4 a = lds128f(mine + cur + p * 1024), c = lds128f(mine + cur + p * 1024 + 256);
+                        float sl = ffma(a.x, a.x, 0.0f), sh = ffma(c.x, c.x, 0.0f);
+                        sl = ffma(a.y, a.y, sl); sh = ffma(c.y, c.y, sh); sl = ffma(a.z, a.z, sl); sh = ffma(c.z, c.z, sh); sl = ffma(a.w, a.w, sl); sh = ffma(c.w, c.w, sh);
+                        ss[p] = fadd(sl, sh);
+                        xl[p][0] = pk2(a.x, a.y); xl[p][1] = pk2(a.z, a.w); xh[p][0] = pk2(c.x, c.y); xh[p][1] = pk2(c.z, c.w);
+                    } else ss[p] = 0.0f;
+                }
+                float scale[4];
+                if (np > 2) {
+                    const float g0 = __shfl_xor_sync(CAM_FULL, up8 ? ss[0] : ss[2], 8), g1 = __shfl_xor_sync(CAM_FULL, up8 ? ss[1] : ss[3], 8);
+                    const float k0 = fadd(up8 ? ss[2] : ss[0], g0), k1 = fadd(up8 ? ss[3] : ss[1], g1);
+                    const float g2 = __shfl_xor_sync(CAM_FULL, up4 ? k0 : k1, 4);
+                    float tot = fadd(up4 ? k1 : k0, g2);
+                    tot = fadd(tot, __shfl_xor_sync(CAM_FULL, tot, 2));
+                    tot = fadd(tot, __shfl_xor_sync(CAM_FULL, tot, 1));
+                    const float sc = cam_rsqrt(fadd(fmul(tot, 0.0078125f), eps));
+#pragma unroll
+                    for (int p = 0; p < 4; p++) scale[p] = __shfl_sync(CAM_FULL, sc, 16 * hw + 4 * p);
+                } else {
+#pragma unroll
+                    for (int p = 0; p < 4; p++)
+                        if (p < np) {
+                            float tot = ss[p];
+#pragma unroll
+                            for (int o = 8; o > 0; o >>= 1) tot = fadd(tot, __shfl_xor_sync(CAM_FULL, tot, o));
+                            scale[p] = cam_rsqrt(fadd(fmul(tot, 0.0078125f), eps));
+                        }
+                }
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                    if (p < np) {
+                        const f32x2 s2 = pk2(scale[p], scale[p]);
+                        f32x2 ylo[2], yhi[2];
+#pragma unroll
+                        for (int c = 0; c < 2; c++) {
+                            const f32x2 x0 = mul2(mul2(s2, xl[p][c]), isq ? wq2[c] : wk2[c]), x1 = mul2(mul2(s2, xh[p][c]), isq ? wq2[2 + c] : wk2[2 + c]);
+                            ylo[c] = fma2(x0, cc[c], mul2(x1, nsn[c])); yhi[c] = fma2(x1, cc[c], mul2(x0, sn[c]));
+                        }
+                        const int head = h0 + 2 * p;                     // (+ hw: inside the row pointers)
+                        if (!Q8) {
+                            uint16_t * o = (isq ? qrow : krow) + head * 128;
+                            st64_stream(o, make_uint2(f2_to_h2(lo2(ylo[0]), hi2(ylo[0])), f2_to_h2(lo2(ylo[1]), hi2(ylo[1]))));
+                            st64_stream(o + 64, make_uint2(f2_to_h2(lo2(yhi[0]), hi2(yhi[0])), f2_to_h2(lo2(yhi[1]), hi2(yhi[1]))));
+                        } else {
+                            float y[8] = {f16r(lo2(ylo[0])), f16r(hi2(ylo[0])), f16r(lo2(ylo[1])), f16r(hi2(ylo[1])),
+                                          f16r(lo2(yhi[0])), f16r(hi2(yhi[0])), f16r(lo2(yhi[1])), f16r(hi2(yhi[1]))};
+                            hadamard128(y, l16);
+                            if (isq) {
+                                uint16_t * o = qrow + head * 128;
+                                st64_stream(o, make_uint2(f2_to_h2(y[0], y[1]), f2_to_h2(y[2], y[3])));
+                                st64_stream(o + 64, make_uint2(f2_to_h2(y[4], y[5]), f2_to_h2(y[6], y[7])));
+                            } else {
+                                uint8_t * kb = cw + (size_t)head * 4 * 34;
+                                const float klo[4] = {y[0], y[1], y[2], y[3]}, khi[4] = {y[4], y[5], y[6], y[7]};
+                                q8_0_store(klo, kb, l16 & 7, A.err, true);
+                                q8_0_store(khi, kb + 2 * 34, l16 & 7, A.err, true);
+                            }
+                        }
+                    }
+                }
+            } else {                                                     // v heads: rounded to fp16 (Q8: then Q8_0 blocks)
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                    if (p < np) {
+                        const float4 a = lds128f(mine + cur + p * 1024), c = lds128f(mine + cur + p * 1024 + 256);
+                        const int head = h0 + 2 * p;
+                        if (!Q8) {
+                            uint16_t * o = krow + NK2 * 256 + head * 128;
+                            st64_stream(o, make_uint2(f2_to_h2(a.x, a.y), f2_to_h2(a.z, a.w)));
+                            st64_stream(o + 64, make_uint2(f2_to_h2(c.x, c.y), f2_to_h2(c.z, c.w)));
+                        } else {
+                            uint8_t * vb = cw + (size_t)NK2 * 2 * 4 * 34 + (size_t)head * 4 * 34;
+                            const float vlo[4] = {f16r(a.x), f16r(a.y), f16r(a.z), f16r(a.w)}, vhi[4] = {f16r(c.x), f16r(c.y), f16r(c.z), f16r(c.w)};
+                            q8_0_store(vlo, vb, l16 & 7, A.err, true);
+                            q8_0_store(vhi, vb + 2 * 34, l16 & 7, A.err, true);
+                        }
+                    }
+                }
+            }
+            __syncwarp();                                                // every lane has read the slot before the next request overwrites it
+            cur ^= 4096u;
+        }
+        in = nxt;
+    }
+    cp_async_wait<0>();
+}
+
 // warps per block (4 .. 12) and heads per half-warp and round (1 .. 4): the pair with the fewest idle half-warp slots over a
 // token's H heads; among equals the most heads per round (one scale computation serves 2 P heads), then the most warps
 void pick_shape(int H, int & warps, int & P) {
@@ -547,6 +721,24 @@ int launch_rope(const RopeArgs & A, cudaStream_t stream) {
 #undef CAM_ROPE_CASE
 }
 
+// the token-shaped kernel of the reference's signature for the head counts it is built for; CAM_ERR_SHAPE: the caller's staged kernel
+template <bool Q8>
+int launch_cache_tok(const RopeArgs & A, cudaStream_t stream) {
+    if (const char * e = getenv("CAMINUS_B200_ROPE_STAGED")) { if (e[0] == '1') return CAM_ERR_SHAPE; }      // (tuning: the staged kernel)
+    const long blocks = ((long)A.n + 3) / 4;
+    const char * grid_mode = getenv("CAMINUS_B200_ROPE_GRID");       // (tuning: "full" / "resident")
+#define CAM_ROPE_CTOK(NQ2V, NK2V)                                                                                                  \
+    if (A.nh == 2 * NQ2V && A.nkv == 2 * NK2V) {                                                                                   \
+        const int cap = cam_resident_grid(qk_rope_cache_tok_kernel<NQ2V, NK2V, Q8>, 128, 0, blocks);                               \
+        const bool full = grid_mode ? grid_mode[0] == 'f' : blocks > 2L * cap;                                                     \
+        qk_rope_cache_tok_kernel<NQ2V, NK2V, Q8><<<full ? (int)blocks : cap, 128, 0, stream>>>(A);                                 \
+        return (int)cudaGetLastError();                                                                                            \
+    }
+    CAM_ROPE_CTOK(16, 2) CAM_ROPE_CTOK(32, 4) CAM_ROPE_CTOK(20, 4) CAM_ROPE_CTOK(16, 4)
+#undef CAM_ROPE_CTOK
+    return CAM_ERR_SHAPE;
+}
+
 int check_common(int n, int nh, int nkv, const void * par, int pos0) {
     if (n < 0 || nh < 1 || nkv < 0 || !par || pos0 < 0) return CAM_ERR_ARG;
     if ((long)pos0 + n > (1L << 22)) return CAM_ERR_SHAPE;      // the angle's range reduction holds below 2^22 radians
@@ -569,7 +761,8 @@ static int qk_rope_entry(int n, const float * qkv, int ldq, int nh, int nkv, con
         return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
     const RopeArgs A = {qkv, nullptr, par, (uint16_t *)q16, (uint16_t *)cache, ldq, nh, nkv, pos0, n, yarn, nullptr};
-    return launch_rope<float, true>(A, (cudaStream_t)stream);
+    const int r2 = launch_cache_tok<false>(A, (cudaStream_t)stream);
+    return r2 != CAM_ERR_SHAPE ? r2 : launch_rope<float, true>(A, (cudaStream_t)stream);
 }
 extern "C" int q3p_qk_rope(int n, const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, void * q16, void * cache,
                            void * stream) {
@@ -591,7 +784,8 @@ static int rope_q8_entry(int n, const float * qkv, int ldq, int nh, int nkv, con
         (reinterpret_cast<uintptr_t>(err) & 3u)) return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
     const RopeArgs A = {qkv, nullptr, par, (uint16_t *)q16, (uint16_t *)cache, ldq, nh, nkv, pos0, n, yarn, err};
-    return launch_rope<float, true, true>(A, (cudaStream_t)stream);
+    const int r2 = launch_cache_tok<true>(A, (cudaStream_t)stream);
+    return r2 != CAM_ERR_SHAPE ? r2 : launch_rope<float, true, true>(A, (cudaStream_t)stream);
 }
 extern "C" int q3p_qk_rope_q8(int n, const float * qkv, int ldq, int nh, int nkv, const float * par, int pos0, void * q16, void * cache, int * err,
                               void * stream) {

@@ -314,7 +314,8 @@ def test_qk_rope_golden(golden, yarn):
         assert (np.abs(q16[0].float().cpu().numpy() - ref) <= bound).all()     # tests/engine/test_q3m_yarn_rope.py:132-135
 
 
-@pytest.mark.parametrize('n,nh,nkv,pos0', [(75, 32, 4, 1000), (1, 32, 4, 0), (130, 64, 8, 7), (19, 5, 1, 3), (40, 16, 2, 131000)])
+@pytest.mark.parametrize('n,nh,nkv,pos0', [(75, 32, 4, 1000), (1, 32, 4, 0), (130, 64, 8, 7), (19, 5, 1, 3), (40, 16, 2, 131000), (5000, 32, 4, 3), (77, 40, 8, 0),
+                                           (33, 32, 8, 9), (2500, 64, 8, 1)])
 def test_qk_rope_chunk(O, n, nh, nkv, pos0):
     """a chunk at pos0 as tests/prefill/test_q3m_ops.py:189-217 runs it, with a padded row stride"""
     g = np.random.default_rng(n); M = nkv * 128; ldq = nh * 128 + 2 * M + 64; rows = 9 if pos0 > 100000 else pos0 + n + 2
@@ -489,7 +490,7 @@ def test_add_rms16_single_row_kernel_and_many_rows_agree(O):
 
 # ---- the Q8_0 KV cache form ---------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize('yarn', [False, True])
-@pytest.mark.parametrize('n,nh,nkv,pos0', [(75, 32, 4, 1000), (1, 32, 4, 0), (33, 16, 2, 5), (20, 5, 3, 2)])
+@pytest.mark.parametrize('n,nh,nkv,pos0', [(75, 32, 4, 1000), (1, 32, 4, 0), (33, 16, 2, 5), (20, 5, 3, 2), (5000, 32, 4, 3), (130, 64, 8, 7), (41, 40, 8, 2), (9, 32, 8, 0)])
 def test_qk_rope_q8(n, nh, nkv, pos0, yarn):
     """q3p_qk_rope_q8: q16 and the Q8_0 row bytes are the oracle's; the row is encode(hadamard(K16), V16) of the F16 object's
     halves (tests/engine/test_q3m_yarn_rope.py:121-123); rows below the chunk untouched; a refused block sets bit 2 of err"""
