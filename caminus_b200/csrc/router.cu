@@ -8,6 +8,7 @@
 #include "cam_common.cuh"
 
 #include <cooperative_groups.h>
+#include <cstdlib>
 
 namespace cg = cooperative_groups;
 
@@ -249,7 +250,7 @@ __global__ void __launch_bounds__(256) softmax_topk_rows_kernel(const float * __
 
 // ---- q3p_group: the (token, slot) pairs of a chunk listed by expert, and the experts' lists cut into work items of at most 64 pairs ------
 // One thread-block cluster of up to 8 blocks x 32 warps; no global scratch. A warp takes a contiguous run of pairs, 32 at a time:
-//   count    lanes holding the same expert find each other (match.any); the first of them adds their number to the warp's own
+//   count    lanes holding the same expert find each other (a ballot per bit of the expert's number); the first of them adds their number to the warp's own
 //            counter of that expert in shared memory (a cell per warp and expert: no atomics);
 //   scan     a block adds its warps' cells (a warp per expert, by shuffles), the blocks read one another's totals through distributed
 //            shared memory, and every block derives the same expert offsets (an exclusive scan over the experts) and its own start
@@ -260,6 +261,17 @@ __global__ void __launch_bounds__(256) softmax_topk_rows_kernel(const float * __
 // result does not depend on timing (the reference's order follows its atomics; it states that the order inside a list changes no bit
 // downstream), and the rows a GEMM gathers through xs ascend. An id outside [0, E) counts as expert 0 and sets err |= 2.
 constexpr int GR_WARPS = 32, GR_KEEP = 8, GR_PITCH = GR_WARPS + 1;
+
+// the lanes whose v equals this lane's (v < 2^nbits): one ballot per bit. (match.any gives the same mask, but takes a step per distinct
+// value in the warp: 28 of them for 32 pairs spread over 128 experts, against 7 ballots.)
+CAM_DEV unsigned same_lanes(unsigned v, int nbits) {
+    unsigned same = CAM_FULL;
+    for (int b = 0; b < nbits; b++) {
+        const unsigned set = __ballot_sync(CAM_FULL, (v >> b) & 1u);
+        same &= ((v >> b) & 1u) ? set : ~set;
+    }
+    return same;
+}
 
 CAM_DEV int wscan_excl(int v, int lane) {            // exclusive prefix sum over the warp's lanes
     int s = v;
@@ -302,6 +314,7 @@ __global__ void __launch_bounds__(1024) group_cluster_kernel(const int * __restr
     for (int i = tid; i < E * GR_PITCH; i += 1024) cells[i] = 0;
     __syncthreads();
     const unsigned below = (1u << lane) - 1u;
+    int nbits = 1; while ((1 << nbits) <= E) nbits++;             // an expert + 1 (0: no pair) in nbits bits
     int * const col = cells + warp;              // + e GR_PITCH: this warp's cell of expert e
     auto later = [&](int s) {                    // the expert of this lane's pair in a step past the kept ones (-1: past the end), range-checked
         const long p = lo + 32 * s + lane;
@@ -314,13 +327,13 @@ __global__ void __launch_bounds__(1024) group_cluster_kernel(const int * __restr
     for (int q = 0; q < GR_KEEP; q++)
         if (q < steps) {
             const int e = kept[q];
-            const unsigned same = __match_any_sync(CAM_FULL, e);
+            const unsigned same = same_lanes((unsigned)(e + 1), nbits);
             if (e >= 0 && (same & below) == 0) col[e * GR_PITCH] += __popc(same);
             __syncwarp();
         }
     for (int s = GR_KEEP; s < steps; s++) {
         const int e = later(s);
-        const unsigned same = __match_any_sync(CAM_FULL, e);
+        const unsigned same = same_lanes((unsigned)(e + 1), nbits);
         if (e >= 0 && (same & below) == 0) col[e * GR_PITCH] += __popc(same);
         __syncwarp();
     }
@@ -373,12 +386,12 @@ __global__ void __launch_bounds__(1024) group_cluster_kernel(const int * __restr
     };
 #pragma unroll
     for (int q = 0; q < GR_KEEP; q++)
-        if (q < steps) place(kept[q], q, __match_any_sync(CAM_FULL, kept[q]));
+        if (q < steps) place(kept[q], q, same_lanes((unsigned)(kept[q] + 1), nbits));
     for (int s = GR_KEEP; s < steps; s++) {
         const long p = lo + 32 * s + lane;
         int e = -1;
         if (p < npairs) { e = __ldg(ids + p); if (e < 0 || e >= E) e = 0; }
-        place(e, s, __match_any_sync(CAM_FULL, e));
+        place(e, s, same_lanes((unsigned)(e + 1), nbits));
     }
     // the work items, spread over all threads of the cluster: item i belongs to the last expert whose items start at or before i
     for (int i = blk * 1024 + tid; i < all_items; i += nblk * 1024) {
@@ -440,6 +453,7 @@ extern "C" int q3p_group(const int * ids, int npairs, int k, int E, int * xs, in
     const unsigned long long kmul = (unsigned long long)((((unsigned __int128)1 << kshift) + (unsigned)k - 1) / (unsigned)k);
     int nblk = 1;
     while (nblk < 8 && (long)nblk * 8192 < npairs) nblk *= 2;                         // 8 steps of 32 pairs per warp before the cluster grows
+    if (const char * e = getenv("CAMINUS_B200_GROUP_BLOCKS")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4 || v == 8) nblk = v; }      // (tuning)
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(nblk); cfg.blockDim = dim3(1024); cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)stream;
     cudaLaunchAttribute at[1];
