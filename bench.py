@@ -31,9 +31,9 @@ import numpy as np   # noqa: E402
 T_PER_GPU, HIDDEN, NH, NKV, INTER = 65536, 5120, 64, 8, 25600
 BYTES_PER_TOKEN = {'add_rms_f16': 4 * HIDDEN * 2, 'qk_rope_f16': (NH + NKV) * 128 * 2 * 2, 'swiglu_q8_1_f16': 2 * INTER * 2 + INTER // 32 * 36}
 # DRAM bytes per token row of the dominant kernel, from one ncu capture of swiglu_q8_fast_kernel at T = 8192, I = 25600
-# (dram__bytes_read.sum + dram__bytes_write.sum = 838.95 + 217.91 MB); the traffic grows in proportion to the rows, so a launch
+# (dram__bytes_read.sum + dram__bytes_write.sum = 838.89 + 216.15 MB); the traffic grows in proportion to the rows, so a launch
 # of T rows is scaled from it
-SWIGLU_DRAM_BYTES_PER_TOKEN = (838_906_880 + 216_342_016) / 8192
+SWIGLU_DRAM_BYTES_PER_TOKEN = (838_888_448 + 216_150_272) / 8192
 METRIC = 'per-layer glue throughput (residual add + RMSNorm -> q/k norm + RoPE -> SwiGLU + Q8_1), tokens/s'
 
 

@@ -9,6 +9,8 @@
 // aligned take the byte-wise kernels.
 #include "cam_common.cuh"
 
+#include <cstdlib>
+
 namespace {
 
 __constant__ float kIQ4NL[16] = {-127.f, -104.f, -83.f, -65.f, -49.f, -35.f, -22.f, -10.f, 1.f, 13.f, 25.f, 38.f, 53.f, 69.f, 89.f, 113.f};
@@ -151,7 +153,13 @@ constexpr int IQ2S_ROWS = 4;      // token rows a block decodes together: a thre
 __global__ void __launch_bounds__(256) emb_rows_iq2s_kernel(const uint8_t * __restrict__ W, int rb, int vocab, const int * __restrict__ toks, float * __restrict__ x,
                                                             int n, int N, const uint32_t * __restrict__ grid) {
     __shared__ uint32_t gs[512];
+    __shared__ __align__(8) float2 mag2[64];     // two neighbouring values at once: entry (c0 | c1 << 2 | s0 << 4 | s1 << 5) = (+-mag(c0), +-mag(c1)), mag = 8, 25, 43
     for (int i = threadIdx.x; i < 512; i += 256) gs[i] = __ldg(grid + i);
+    if (threadIdx.x < 64) {
+        const int i = threadIdx.x, c0 = i & 3, c1 = (i >> 2) & 3;
+        const float m0 = c0 == 0 ? 8.0f : c0 == 1 ? 25.0f : 43.0f, m1 = c1 == 0 ? 8.0f : c1 == 1 ? 25.0f : 43.0f;
+        mag2[i] = make_float2((i & 16) ? -m0 : m0, (i & 32) ? -m1 : m1);
+    }
     __syncthreads();
     const int units = N >> 3;
     for (int p0 = blockIdx.x * IQ2S_ROWS; p0 < n; p0 += gridDim.x * IQ2S_ROWS) {
@@ -181,16 +189,17 @@ __global__ void __launch_bounds__(256) emb_rows_iq2s_kernel(const uint8_t * __re
                 const uint32_t idx = lo | (((qh >> (2 * g)) & 3u) << 8);
                 const uint32_t codes = (gs[idx >> 1] >> (16 * (idx & 1u))) & 0xffffu;
                 const float db = fmul(fmul(d, fadd(0.5f, (float)((sb >> (4 * ((j8 >> 1) & 1))) & 15u))), 0.25f);
-                float v[8];
+                // db times the signed magnitude: the product's bits are those of -(db mag) or db mag (the sign of an IEEE product is exact)
+                const f32x2 db2 = pk2(db, db);
+                f32x2 v[4];
 #pragma unroll
-                for (int k = 0; k < 8; k++) {
-                    const uint32_t c = (codes >> (2 * k)) & 3u;
-                    const float m = fmul(db, c == 0 ? 8.0f : c == 1 ? 25.0f : 43.0f);
-                    v[k] = ((sg >> k) & 1u) ? -m : m;
+                for (int k = 0; k < 4; k++) {
+                    const float2 m = mag2[((codes >> (4 * k)) & 15u) | (((sg >> (2 * k)) & 3u) << 4)];
+                    v[k] = mul2(db2, pk2(m.x, m.y));
                 }
                 float * o = x + (size_t)(p0 + r) * N + 8 * q;
-                __stcs(reinterpret_cast<float4 *>(o), make_float4(v[0], v[1], v[2], v[3]));
-                __stcs(reinterpret_cast<float4 *>(o + 4), make_float4(v[4], v[5], v[6], v[7]));
+                __stcs(reinterpret_cast<float4 *>(o), make_float4(lo2(v[0]), hi2(v[0]), lo2(v[1]), hi2(v[1])));
+                __stcs(reinterpret_cast<float4 *>(o + 4), make_float4(lo2(v[2]), hi2(v[2]), lo2(v[3]), hi2(v[3])));
             }
         }
     }
@@ -238,6 +247,8 @@ extern "C" int q35t_emb_iq2s(int n, const void * W, int rb, int vocab, const int
     if (n < 0 || vocab < 1 || N < 256 || (N & 255) || rb < N / 256 * 82 || !W || !toks || !x || !grid) return CAM_ERR_ARG;
     if ((reinterpret_cast<uintptr_t>(W) & 1u) || (rb & 1) || !cam_aligned16(x) || (reinterpret_cast<uintptr_t>(grid) & 3u)) return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
-    emb_rows_iq2s_kernel<<<cam_resident_grid(emb_rows_iq2s_kernel, 256, 0, (n + IQ2S_ROWS - 1) / IQ2S_ROWS), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)W, rb, vocab, toks, x, n, N, grid);
+    const long want = ((long)n + IQ2S_ROWS - 1) / IQ2S_ROWS;
+    long g = cam_resident_grid(emb_rows_iq2s_kernel, 256, 0, want);
+    emb_rows_iq2s_kernel<<<(int)g, 256, 0, (cudaStream_t)stream>>>((const uint8_t *)W, rb, vocab, toks, x, n, N, grid);
     return (int)cudaGetLastError();
 }
