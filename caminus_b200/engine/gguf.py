@@ -34,7 +34,7 @@ def silu_mul(g, u):
 
 def swiglu_q8_1(g, u, yq=None, strict=False, sums=False):
     """q8_1 blocks of silu(g) * u in one launch; g, u both fp32 or both fp16 (cuda), same numel. d and the codes are always
-    the exact statements' bytes; sums=True proves the block sums as well (all 36 bytes exact, about three quarters of the default's
+    the exact statements' bytes; sums=True proves the block sums as well (all 36 bytes exact, about four fifths of the default's
     throughput); strict=True runs the exact statements for every value (the same bytes as sums=True, slower still)"""
     if g.dtype != u.dtype or g.dtype not in (torch.float32, torch.float16) or g.numel() != u.numel() or g.device != u.device:
         raise ValueError(f'swiglu_q8_1: gate {g.dtype} [{g.numel()}] and up {u.dtype} [{u.numel()}] (both fp32 or both fp16, one size)')

@@ -108,10 +108,10 @@ int gg_quantize_q8_1(const float * x, void * y, int n, void * stream);
  * d and the 32 codes of every block are the bytes of the exact statements (a fast pass is used only where that is proven,
  * the rest is recomputed exactly: csrc/swiglu_q8.cu). The block sum may differ from the exact statements' by one fp16 ulp; the
  * reference reports that field and does not gate it (tests/engine/golden_util.py:145-146). The _strict forms run the exact
- * statements for every value (the sums are exact too) at about half the throughput. */
+ * statements for every value (the sums are exact too) at about a third of the throughput. */
 int gg_swiglu_q8_1(const float * x, const float * mul, void * y, long n, void * stream);
 int gg_swiglu_q8_1_f16(const void * g, const void * u, void * y, long n, void * stream);
-/* the same with the block sum proven as well: all 36 bytes of every block are the exact statements', at about three quarters of the copy bandwidth */
+/* the same with the block sum proven as well: all 36 bytes of every block are the exact statements', at about four fifths of the copy bandwidth */
 int gg_swiglu_q8_1_sums(const float * x, const float * mul, void * y, long n, void * stream);
 int gg_swiglu_q8_1_f16_sums(const void * g, const void * u, void * y, long n, void * stream);
 int gg_swiglu_q8_1_strict(const float * x, const float * mul, void * y, long n, void * stream);
