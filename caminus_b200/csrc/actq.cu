@@ -70,6 +70,14 @@ struct PlainBf16 {
     CAM_DEV float operator()(int row, int k) const { return bf2f(__ldg(x + (size_t)row * K + k)); }
     CAM_DEV void get4(int row, int k, float (&v)[4]) const { bf4(__ldg(reinterpret_cast<const uint2 *>(x + (size_t)row * K + k)), v); }
     static constexpr bool kBf16 = true;            // get4's values are bf16 numbers already
+    // sixteen consecutive values at k (a multiple of 16; rows 16-byte aligned) as pairs; zeros when off
+    CAM_DEV void get16(bool on, int row, int k, f32x2 (&p)[8]) const {
+        uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
+        if (on) { const uint4 * r = reinterpret_cast<const uint4 *>(x + (size_t)row * K + k); a = __ldg(r); b = __ldg(r + 1); }
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) p[i] = pk2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+    }
 };
 struct PlainF32 {
     const float * x; int K;
@@ -78,7 +86,19 @@ struct PlainF32 {
         const float4 a = __ldg(reinterpret_cast<const float4 *>(x + (size_t)row * K + k)); v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
     }
     static constexpr bool kBf16 = false;
+    CAM_DEV void get16(bool on, int row, int k, f32x2 (&p)[8]) const {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (on) a = __ldg(reinterpret_cast<const float4 *>(x + (size_t)row * K + k) + q);
+            const uint32_t w0 = bf16x2<true>(a.x, a.y), w1 = bf16x2<true>(a.z, a.w);
+            p[2 * q] = pk2(__uint_as_float(w0 << 16), __uint_as_float(w0 & 0xffff0000u));
+            p[2 * q + 1] = pk2(__uint_as_float(w1 << 16), __uint_as_float(w1 & 0xffff0000u));
+        }
+    }
 };
+// the exact statements' bf16(silu(g)) of two gates (out of line: the fast passes call it for one pair in some hundreds)
+__device__ __noinline__ uint32_t silu_pair_bf16_exact(float g0, float g1) { return bf16_soft<true>(cam_silu(g0)) | (bf16_soft<true>(cam_silu(g1)) << 16); }
 struct SiluMulSrc {
     const uint16_t * gu; int ld, F;
     CAM_DEV float operator()(int row, int k) const {
@@ -100,6 +120,54 @@ struct SiluMulSrc {
         rbf4(v);
     }
     static constexpr bool kBf16 = true;
+    // sixteen consecutive activations at k as pairs (rows and F 16-byte aligned: ld and F multiples of 8, checked by the launcher)
+    CAM_DEV void get16(bool on, int row, int k, f32x2 (&p)[8]) const {
+        if (!on) {                               // (no gates: zeros, and no visit to the exact statements that a zero gate asks for)
+#pragma unroll
+            for (int i = 0; i < 8; i++) p[i] = pk2(0.f, 0.f);
+            return;
+        }
+        const uint4 * r = reinterpret_cast<const uint4 *>(gu + (size_t)row * ld + k);
+        const uint4 * q = reinterpret_cast<const uint4 *>(gu + (size_t)row * ld + F + k);
+        const uint4 ga = __ldg(r), gb = __ldg(r + 1), ua = __ldg(q), ub = __ldg(q + 1);
+        const uint32_t gw[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w}, uw[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+        float g[16];
+        const f32x2 zero2 = pk2(0.f, 0.f);
+        f32x2 zg = zero2;                        // 0 g summed: a NaN iff a gate is a NaN or an infinity
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            g[2 * i] = __uint_as_float(gw[i] << 16); g[2 * i + 1] = __uint_as_float(gw[i] & 0xffff0000u);
+            zg = fma2(pk2(g[2 * i], g[2 * i + 1]), zero2, zg);
+        }
+        uint32_t sw[8];                          // bf16(silu(g)): the special-function value where its bits are proven, else the exact statements
+        uint32_t redo = silu_bf16_fast<16>(g, sw);
+        const float zs = fadd(lo2(zg), hi2(zg));
+        if (zs != zs) redo = 0xffu;
+        if (redo) {
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                if ((redo >> i) & 1u) sw[i] = silu_pair_bf16_exact(g[2 * i], g[2 * i + 1]);
+        }
+        f32x2 zp = zero2;
+        uint32_t hw[8];                          // bf16(bf16(silu(g)) u)
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const f32x2 h = mul2(pk2(__uint_as_float(sw[i] << 16), __uint_as_float(sw[i] & 0xffff0000u)),
+                                 pk2(__uint_as_float(uw[i] << 16), __uint_as_float(uw[i] & 0xffff0000u)));
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hw[i]) : "f"(hi2(h)), "f"(lo2(h)));
+            zp = fma2(h, zero2, zp);
+        }
+        const float zq = fadd(lo2(zp), hi2(zp));
+        if (zq != zq) {                          // a product that is a NaN is stored as 0x7fc0 (the conversion gives 0x7fff)
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                if ((hw[i] & 0x7fffu) > 0x7f80u) hw[i] = (hw[i] & 0xffff0000u) | 0x7fc0u;
+                if ((hw[i] & 0x7fff0000u) > 0x7f800000u) hw[i] = (hw[i] & 0x0000ffffu) | 0x7fc00000u;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) p[i] = pk2(__uint_as_float(hw[i] << 16), __uint_as_float(hw[i] & 0xffff0000u));
+    }
 };
 struct RmsSrc {
     const float * x; const float * w; float rstd; int d;
@@ -381,6 +449,33 @@ CAM_DEV void fwht_wide(f32x2 (&p)[8], int l8) {
 }
 CAM_DEV bool bf16_word_has_nan(uint32_t w) { return (((w & 0x7fff7fffu) + 0x007f007fu) & 0x80008000u) != 0; }
 
+// the codes, dequantised values and stores of one warp step in general: every value clamped (a clip below 1 lets quotients pass qmax; a
+// NaN or an infinity among the values needs fminf / fmaxf's treatment of a NaN)
+CAM_DEV void actq_wide_emit_clamped(const uint32_t (&up)[8], float s, float inv, bool fast, float lo, float hi, size_t at, uint16_t * __restrict__ y,
+                                    uint16_t * __restrict__ codes) {
+    const f32x2 ih2 = pk2(fmul(inv, 0x1.000008p+0f), fmul(inv, 0x1.000008p+0f)), il2 = pk2(fmul(inv, 0x1.fffff0p-1f), fmul(inv, 0x1.fffff0p-1f));
+    const f32x2 magic2 = pk2(12582912.0f, 12582912.0f), s2 = pk2(s, s);
+    uint32_t yw[8], cw[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t w = up[i];
+        const float u0 = __uint_as_float(w << 16), u1 = __uint_as_float(w & 0xffff0000u);
+        const f32x2 u = pk2(u0, u1);
+        const f32x2 vh = fma2(u, ih2, magic2), vl = fma2(u, il2, magic2);
+        const f32x2 r = sub2(vh, magic2);
+        f32x2 q2 = pk2(copysignf(lo2(r), u0), copysignf(hi2(r), u1));                                   // (rint keeps the sign of a zero)
+        if ((((__float_as_uint(lo2(vh)) ^ __float_as_uint(lo2(vl))) | (__float_as_uint(hi2(vh)) ^ __float_as_uint(hi2(vl)))) != 0) || !fast)
+            q2 = pk2(rintf(fdiv(u0, s)), rintf(fdiv(u1, s)));
+        const float a = fminf(fmaxf(lo2(q2), lo), hi), b = fminf(fmaxf(hi2(q2), lo), hi);
+        const uint32_t na = __float_as_uint(fadd(a, 12582912.0f)) & 0xFu, nb = __float_as_uint(fadd(b, 12582912.0f)) & 0xFu;
+        cw[i >> 2] |= (na | (nb << 4)) << (8 * (i & 3));
+        const f32x2 d2 = mul2(pk2(a, b), s2);
+        yw[i] = bf16x2<true>(lo2(d2), hi2(d2));
+    }
+    if (y) { st128(y + at, make_uint4(yw[0], yw[1], yw[2], yw[3])); st128(y + at + 8, make_uint4(yw[4], yw[5], yw[6], yw[7])); }
+    if (codes) st64(codes + (at >> 2), make_uint2(cw[0], cw[1]));
+}
+
 // STEPS: warp steps of 512 values per row and warp; WPR: warps per row (1, 2 or 4)
 template <typename Src, int STEPS, int WPR>
 __global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __restrict__ y, float * __restrict__ s_out, int K, float clip, int qmax,
@@ -394,36 +489,29 @@ __global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __re
         const int row = r0 + warp / WPR;
         const bool row_on = row < M;
         uint32_t up[STEPS][8];                                           // the transformed values, bf16 pairs
-        float amax = 0.f;
+        float amax = 0.f;                                                // over the values before their rounding to bf16 (rounded below: rounding is monotone)
+        bool odd = false;                                                // a NaN or an infinity among this lane's transformed values
 #pragma unroll
         for (int st = 0; st < STEPS; st++) {
             const int ch = (part * STEPS + st) * 4 + g8;
             const bool on = row_on && ch < nch;
-            float v[16];
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                float t4[4] = {0.f, 0.f, 0.f, 0.f};
-                if (on) src.get4(row, ch * 128 + l8 * 16 + 4 * q, t4);
-                if (!Src::kBf16) rbf4(t4);
-#pragma unroll
-                for (int e = 0; e < 4; e++) v[4 * q + e] = t4[e];
-            }
             f32x2 p[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) p[i] = pk2(v[2 * i], v[2 * i + 1]);
+            src.get16(on, row, ch * 128 + l8 * 16, p);
             fwht_wide(p, l8);
-            const f32x2 c2 = pk2(0.08837890625f, 0.08837890625f);
-            bool nan = false;
+            const f32x2 c2 = pk2(0.08837890625f, 0.08837890625f), zero2 = pk2(0.f, 0.f);
+            f32x2 z2 = zero2;                                            // 0 t summed: a NaN iff some t is a NaN or an infinity (one packed fma per pair)
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 const f32x2 t = mul2(p[i], c2);
                 uint32_t w;
                 asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi2(t)), "f"(lo2(t)));
                 up[st][i] = w;
-                nan |= bf16_word_has_nan(w);
-                amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w << 16)), fabsf(__uint_as_float(w & 0xffff0000u))));
+                z2 = fma2(t, zero2, z2);
+                amax = fmaxf(amax, fmaxf(fabsf(lo2(t)), fabsf(hi2(t))));
             }
-            if (nan) {                                                   // (a NaN is stored as 0x7fc0, the reference's f2bf; the conversion gives 0x7fff)
+            const float zs = fadd(lo2(z2), hi2(z2));
+            if (zs != zs) {                                              // (a NaN is stored as 0x7fc0, the reference's f2bf; the conversion gives 0x7fff)
+                odd = true;
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                     uint32_t w = up[st][i];
@@ -441,44 +529,48 @@ __global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __re
             for (int i = 0; i < WPR; i++) amax = fmaxf(amax, wmax[(warp & ~(WPR - 1)) + i]);
             __syncthreads();
         }
+        amax = __uint_as_float(bf16x2<false>(amax, 0.f) << 16);          // the largest rounded magnitude = the largest magnitude, rounded (never a NaN)
         const float s = fmaxf(fdiv(fmul(amax, clip), (float)qmax), 1e-8f);
         if (lane == 0 && part == 0 && row_on && s_out) s_out[row] = s;
         const float lo = (float)(-qmax - 1), hi = (float)qmax;
         // rint(u / s) without the division where that is provably the same integer (actq_emit above): two-ended rounding test per value
         const float inv = rcp_approx(s);
-        const f32x2 ih2 = pk2(fmul(inv, 0x1.000008p+0f), fmul(inv, 0x1.000008p+0f)), il2 = pk2(fmul(inv, 0x1.fffff0p-1f), fmul(inv, 0x1.fffff0p-1f));
-        const f32x2 magic2 = pk2(12582912.0f, 12582912.0f), s2 = pk2(s, s);
         const bool fast = s < 3.0e38f && fmul(amax, inv) < 4.0e6f;       // (s >= 1e-8; false for a NaN)
+        // No value passes the clamp when clip >= 1 and every value is a number: |u| <= amax and s >= fl(amax / qmax) put the quotient
+        // below qmax + 0.5. The warp then skips the clamp, takes the code from the rounded sum's own low bits (1.5 2^23 + 8 + q holds
+        // q + 8 in its last four bits) and the zero's sign from the source word.
+        const bool plain = clip >= 1.0f && amax < 3.0e38f && s < 3.0e38f && !__any_sync(CAM_FULL, odd);
+        const f32x2 ih2 = pk2(fmul(inv, 0x1.000008p+0f), fmul(inv, 0x1.000008p+0f)), il2 = pk2(fmul(inv, 0x1.fffff0p-1f), fmul(inv, 0x1.fffff0p-1f));
+        const f32x2 magic2 = pk2(12582920.0f, 12582920.0f), s2 = pk2(s, s);
 #pragma unroll
         for (int st = 0; st < STEPS; st++) {
             const int ch = (part * STEPS + st) * 4 + g8;
             if (!(row_on && ch < nch)) continue;
-            uint32_t yw[8], cw[2] = {0u, 0u};
-            f32x2 q2[8];
+            const size_t at = (size_t)row * K + ch * 128 + l8 * 16;
+            if (!plain) { actq_wide_emit_clamped(up[st], s, inv, fast, lo, hi, at, y, codes); continue; }
+            uint32_t yw[8], nb[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 const uint32_t w = up[st][i];
                 const float u0 = __uint_as_float(w << 16), u1 = __uint_as_float(w & 0xffff0000u);
                 const f32x2 u = pk2(u0, u1);
-                const f32x2 vh = fma2(u, ih2, magic2), vl = fma2(u, il2, magic2);
-                const f32x2 r = sub2(vh, magic2);
-                q2[i] = pk2(copysignf(lo2(r), u0), copysignf(hi2(r), u1));                                   // (rint keeps the sign of a zero)
+                f32x2 vh = fma2(u, ih2, magic2);
+                const f32x2 vl = fma2(u, il2, magic2);
                 // a pair whose two ends differ (a quotient on or next to a .5 boundary: bf16 operands make exact ties common) is divided
                 if ((((__float_as_uint(lo2(vh)) ^ __float_as_uint(lo2(vl))) | (__float_as_uint(hi2(vh)) ^ __float_as_uint(hi2(vl)))) != 0) || !fast)
-                    q2[i] = pk2(rintf(fdiv(u0, s)), rintf(fdiv(u1, s)));
+                    vh = pk2(fadd(rintf(fdiv(u0, s)), 12582920.0f), fadd(rintf(fdiv(u1, s)), 12582920.0f));
+                const f32x2 d2 = mul2(sub2(vh, magic2), s2);
+                uint32_t yv;
+                asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(yv) : "f"(hi2(d2)), "f"(lo2(d2)));
+                yw[i] = yv | (w & 0x80008000u);                          // (rint keeps the sign of a zero; elsewhere the signs agree already)
+                nb[i] = __float_as_uint(hi2(vh)) * 16u + __float_as_uint(lo2(vh));        // low byte: (q1 + 8) << 4 | (q0 + 8)
             }
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const float a = fminf(fmaxf(lo2(q2[i]), lo), hi), b = fminf(fmaxf(hi2(q2[i]), lo), hi);
-                // the code's low four bits from the clamped integer's place under 1.5 * 2^23
-                const uint32_t na = __float_as_uint(fadd(a, 12582912.0f)) & 0xFu, nb = __float_as_uint(fadd(b, 12582912.0f)) & 0xFu;
-                cw[i >> 2] |= (na | (nb << 4)) << (8 * (i & 3));
-                const f32x2 d2 = mul2(pk2(a, b), s2);
-                yw[i] = bf16x2<true>(lo2(d2), hi2(d2));
-            }
-            const size_t at = (size_t)row * K + ch * 128 + l8 * 16;
             if (y) { st128(y + at, make_uint4(yw[0], yw[1], yw[2], yw[3])); st128(y + at + 8, make_uint4(yw[4], yw[5], yw[6], yw[7])); }
-            if (codes) st64(codes + (at >> 2), make_uint2(cw[0], cw[1]));
+            if (codes) {
+                const uint32_t c0 = __byte_perm(__byte_perm(nb[0], nb[1], 0x0040), __byte_perm(nb[2], nb[3], 0x0040), 0x5410);
+                const uint32_t c1 = __byte_perm(__byte_perm(nb[4], nb[5], 0x0040), __byte_perm(nb[6], nb[7], 0x0040), 0x5410);
+                st64(codes + (at >> 2), make_uint2(c0 ^ 0x88888888u, c1 ^ 0x88888888u));
+            }
         }
     }
 }
@@ -523,7 +615,7 @@ bool misaligned8(const void * p) { return p && (reinterpret_cast<uintptr_t>(p) &
 extern "C" int actq_fwd_codes_bf16(int M, const void * x, void * y, float * s, void * codes, int K, float clip, int qmax, void * stream) {
     const int r = check_actq(M, K, qmax, x, s); if (r || M == 0) return r;
     if (misaligned8(y)) return CAM_ERR_ALIGN;
-    if (!launch_actq_wide(PlainBf16{(const uint16_t *)x, K}, !misaligned8(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST) &&
+    if (!launch_actq_wide(PlainBf16{(const uint16_t *)x, K}, cam_aligned16(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST) &&
         !launch_actq_rows(PlainBf16{(const uint16_t *)x, K}, !misaligned8(x), M, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes, CAM_ST)) {
         if (!misaligned8(x)) actq_kernel<PlainBf16, true><<<M, 256, 0, CAM_ST>>>(PlainBf16{(const uint16_t *)x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
         else actq_kernel<<<M, 256, 0, CAM_ST>>>(PlainBf16{(const uint16_t *)x, K}, (uint16_t *)y, s, K, clip, qmax, (uint16_t *)codes);
@@ -553,7 +645,7 @@ extern "C" int silu_mul_actq_fwd(int M, const void * gu, int ld, int F, void * y
     if (misaligned8(y)) return CAM_ERR_ALIGN;
     if (M == 0) return CAM_OK;
     const bool vec = !misaligned8(gu) && !(ld & 3);
-    if (!launch_actq_wide(SiluMulSrc{(const uint16_t *)gu, ld, F}, vec, M, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes, CAM_ST) &&
+    if (!launch_actq_wide(SiluMulSrc{(const uint16_t *)gu, ld, F}, cam_aligned16(gu) && !(ld & 7), M, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes, CAM_ST) &&
         !launch_actq_rows(SiluMulSrc{(const uint16_t *)gu, ld, F}, vec, M, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes, CAM_ST)) {
         if (vec) actq_kernel<SiluMulSrc, true><<<M, 256, 0, CAM_ST>>>(SiluMulSrc{(const uint16_t *)gu, ld, F}, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes);
         else actq_kernel<<<M, 256, 0, CAM_ST>>>(SiluMulSrc{(const uint16_t *)gu, ld, F}, (uint16_t *)y, s, F, clip, qmax, (uint16_t *)codes);

@@ -361,11 +361,18 @@ def test_actq_family(M, K):
         yo, so, co = oracle.actq_fwd(ref, 1.0, 7)
         assert same(y, yo) and same(s, so) and np.array_equal(c.cpu().numpy().view(np.uint16).reshape(-1), co.reshape(-1))
         assert same(A.actq(xin, 4, 1.0), yo)
+        for nbits, clip in ((3, 1.5), (4, 0.7), (2, 1.0)):           # clips on both sides of 1 (above it no quotient passes qmax), other code widths
+            y, c, s = A.actq_codes(xin, nbits, clip)
+            yo2, so2, co2 = oracle.actq_fwd(ref, clip, 2 ** (nbits - 1) - 1)
+            assert same(y, yo2) and same(s, so2) and np.array_equal(c.cpu().numpy().view(np.uint16).reshape(-1), co2.reshape(-1))
     wide = torch.from_numpy(acts(g, (M, 2 * K + 64), 2.0)).bfloat16().to(DEV)
     wide[0, :8] = torch.tensor([30, -30, 0, -0.0, 1e-3, -88, 88, 3]).bfloat16()
     gu = wide[:, :2 * K]                                              # a row-strided view
     y, c, s = A.silu_mul_actq(gu, 4, 0.9)
     yo, so, co = oracle.silu_mul_actq_fwd(bits(wide.cpu()).reshape(M, -1), K, 0.9, 7)
+    assert same(y, yo) and same(s, so) and np.array_equal(c.cpu().numpy().view(np.uint16).reshape(-1), co.reshape(-1))
+    y, c, s = A.silu_mul_actq(wide[:, 64:], 4, 1.0)                   # (16-byte aligned rows of the same stride, no clamp)
+    yo, so, co = oracle.silu_mul_actq_fwd(bits(wide[:, 64:].contiguous().cpu()).reshape(M, -1), K, 1.0, 7)
     assert same(y, yo) and same(s, so) and np.array_equal(c.cpu().numpy().view(np.uint16).reshape(-1), co.reshape(-1))
     if K <= 1024:
         nw = (g.random(K) + 0.5).astype(np.float32); wab = torch.from_numpy(acts(g, (6, K), 0.05)).bfloat16().to(DEV)
