@@ -70,6 +70,7 @@ struct PlainBf16 {
     CAM_DEV float operator()(int row, int k) const { return bf2f(__ldg(x + (size_t)row * K + k)); }
     CAM_DEV void get4(int row, int k, float (&v)[4]) const { bf4(__ldg(reinterpret_cast<const uint2 *>(x + (size_t)row * K + k)), v); }
     static constexpr bool kBf16 = true;            // get4's values are bf16 numbers already
+    static constexpr bool kHeavy = false;          // (a source whose loads carry arithmetic of their own keeps the transformed row in shared memory sooner)
     // sixteen consecutive values at k (a multiple of 16; rows 16-byte aligned) as pairs; zeros when off
     CAM_DEV void get16(bool on, int row, int k, f32x2 (&p)[8]) const {
         uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
@@ -86,6 +87,7 @@ struct PlainF32 {
         const float4 a = __ldg(reinterpret_cast<const float4 *>(x + (size_t)row * K + k)); v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
     }
     static constexpr bool kBf16 = false;
+    static constexpr bool kHeavy = false;
     CAM_DEV void get16(bool on, int row, int k, f32x2 (&p)[8]) const {
 #pragma unroll
         for (int q = 0; q < 4; q++) {
@@ -120,6 +122,7 @@ struct SiluMulSrc {
         rbf4(v);
     }
     static constexpr bool kBf16 = true;
+    static constexpr bool kHeavy = true;
     // sixteen consecutive activations at k as pairs (rows and F 16-byte aligned: ld and F multiples of 8, checked by the launcher)
     CAM_DEV void get16(bool on, int row, int k, f32x2 (&p)[8]) const {
         if (!on) {                               // (no gates: zeros, and no visit to the exact statements that a zero gate asks for)
@@ -451,8 +454,9 @@ CAM_DEV bool bf16_word_has_nan(uint32_t w) { return (((w & 0x7fff7fffu) + 0x007f
 
 // the codes, dequantised values and stores of one warp step in general: every value clamped (a clip below 1 lets quotients pass qmax; a
 // NaN or an infinity among the values needs fminf / fmaxf's treatment of a NaN)
-CAM_DEV void actq_wide_emit_clamped(const uint32_t (&up)[8], float s, float inv, bool fast, float lo, float hi, size_t at, uint16_t * __restrict__ y,
-                                    uint16_t * __restrict__ codes) {
+__device__ __noinline__ void actq_wide_emit_clamped(uint4 ua, uint4 ub, float s, float inv, bool fast, float lo, float hi, size_t at, uint16_t * __restrict__ y,
+                                                    uint16_t * __restrict__ codes) {
+    const uint32_t up[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
     const f32x2 ih2 = pk2(fmul(inv, 0x1.000008p+0f), fmul(inv, 0x1.000008p+0f)), il2 = pk2(fmul(inv, 0x1.fffff0p-1f), fmul(inv, 0x1.fffff0p-1f));
     const f32x2 magic2 = pk2(12582912.0f, 12582912.0f), s2 = pk2(s, s);
     uint32_t yw[8], cw[2] = {0u, 0u};
@@ -476,25 +480,36 @@ CAM_DEV void actq_wide_emit_clamped(const uint32_t (&up)[8], float s, float inv,
     if (codes) st64(codes + (at >> 2), make_uint2(cw[0], cw[1]));
 }
 
+// one pair by the division (no clamp: the caller's row needs none): its two bf16 values and its code byte
+__device__ __noinline__ void actq_wide_divided_pair(uint32_t w, float s, uint16_t * __restrict__ y2, uint8_t * __restrict__ code) {
+    const float u0 = __uint_as_float(w << 16), u1 = __uint_as_float(w & 0xffff0000u);
+    const float q0 = rintf(fdiv(u0, s)), q1 = rintf(fdiv(u1, s));
+    if (y2) *reinterpret_cast<uint32_t *>(y2) = bf16x2<true>(fmul(q0, s), fmul(q1, s));
+    if (code) *code = (uint8_t)(((uint32_t)(int)q0 & 0xFu) | (((uint32_t)(int)q1 & 0xFu) << 4));
+}
+
 // STEPS: warp steps of 512 values per row and warp; WPR: warps per row (1, 2 or 4)
-template <typename Src, int STEPS, int WPR>
+template <typename Src, int STEPS, int WPR, bool SM>
 __global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __restrict__ y, float * __restrict__ s_out, int K, float clip, int qmax,
                                                         uint16_t * __restrict__ codes, int M) {
     __shared__ float wmax[8];
+    extern __shared__ uint4 aq_sm[];                                     // SM: [warp][step][2][lane], a lane reads back its own words only (no barrier)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g8 = lane >> 3, l8 = lane & 7;
     const int nch = K >> 7;
+    uint4 * const mine = aq_sm + (SM ? warp * (STEPS * 64) + lane : 0);
     constexpr int RPB = 8 / WPR;                                         // rows per block and pass
     const int part = WPR == 1 ? 0 : (warp & (WPR - 1));                  // this warp's part of the row: chunks part STEPS 4 ..
     for (int r0 = blockIdx.x * RPB; r0 < M; r0 += gridDim.x * RPB) {     // (block-uniform: every warp takes part in the barrier below)
         const int row = r0 + warp / WPR;
         const bool row_on = row < M;
-        uint32_t up[STEPS][8];                                           // the transformed values, bf16 pairs
+        uint32_t upr[SM ? 1 : STEPS][8];                                 // the transformed values, bf16 pairs (SM: in shared memory instead)
         float amax = 0.f;                                                // over the values before their rounding to bf16 (rounded below: rounding is monotone)
         bool odd = false;                                                // a NaN or an infinity among this lane's transformed values
-#pragma unroll
+#pragma unroll (SM ? 1 : STEPS)
         for (int st = 0; st < STEPS; st++) {
             const int ch = (part * STEPS + st) * 4 + g8;
             const bool on = row_on && ch < nch;
+            uint32_t w8[8];
             f32x2 p[8];
             src.get16(on, row, ch * 128 + l8 * 16, p);
             fwht_wide(p, l8);
@@ -505,7 +520,7 @@ __global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __re
                 const f32x2 t = mul2(p[i], c2);
                 uint32_t w;
                 asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi2(t)), "f"(lo2(t)));
-                up[st][i] = w;
+                w8[i] = w;
                 z2 = fma2(t, zero2, z2);
                 amax = fmaxf(amax, fmaxf(fabsf(lo2(t)), fabsf(hi2(t))));
             }
@@ -514,11 +529,16 @@ __global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __re
                 odd = true;
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    uint32_t w = up[st][i];
+                    uint32_t w = w8[i];
                     if ((w & 0x7fffu) > 0x7f80u) w = (w & 0xffff0000u) | 0x7fc0u;
                     if ((w & 0x7fff0000u) > 0x7f800000u) w = (w & 0x0000ffffu) | 0x7fc00000u;
-                    up[st][i] = w;
+                    w8[i] = w;
                 }
+            }
+            if constexpr (SM) { mine[st * 64] = make_uint4(w8[0], w8[1], w8[2], w8[3]); mine[st * 64 + 32] = make_uint4(w8[4], w8[5], w8[6], w8[7]); }
+            else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) upr[st][i] = w8[i];
             }
         }
         amax = wave_max(amax);
@@ -542,23 +562,32 @@ __global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __re
         const bool plain = clip >= 1.0f && amax < 3.0e38f && s < 3.0e38f && !__any_sync(CAM_FULL, odd);
         const f32x2 ih2 = pk2(fmul(inv, 0x1.000008p+0f), fmul(inv, 0x1.000008p+0f)), il2 = pk2(fmul(inv, 0x1.fffff0p-1f), fmul(inv, 0x1.fffff0p-1f));
         const f32x2 magic2 = pk2(12582920.0f, 12582920.0f), s2 = pk2(s, s);
-#pragma unroll
+#pragma unroll (SM ? 1 : STEPS)
         for (int st = 0; st < STEPS; st++) {
             const int ch = (part * STEPS + st) * 4 + g8;
             if (!(row_on && ch < nch)) continue;
             const size_t at = (size_t)row * K + ch * 128 + l8 * 16;
-            if (!plain) { actq_wide_emit_clamped(up[st], s, inv, fast, lo, hi, at, y, codes); continue; }
+            uint32_t w8[8];
+            if constexpr (SM) {
+                const uint4 a = mine[st * 64], b = mine[st * 64 + 32];
+                w8[0] = a.x; w8[1] = a.y; w8[2] = a.z; w8[3] = a.w; w8[4] = b.x; w8[5] = b.y; w8[6] = b.z; w8[7] = b.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) w8[i] = upr[st][i];
+            }
+            if (!plain) {                                                // (out of line: rare, and the straight-line code below stays short)
+                actq_wide_emit_clamped(make_uint4(w8[0], w8[1], w8[2], w8[3]), make_uint4(w8[4], w8[5], w8[6], w8[7]), s, inv, fast, lo, hi, at, y, codes);
+                continue;
+            }
             uint32_t yw[8], nb[8];
+            uint32_t bad = fast ? 0u : 0xffu;                            // pairs to divide
 #pragma unroll
             for (int i = 0; i < 8; i++) {
-                const uint32_t w = up[st][i];
-                const float u0 = __uint_as_float(w << 16), u1 = __uint_as_float(w & 0xffff0000u);
-                const f32x2 u = pk2(u0, u1);
-                f32x2 vh = fma2(u, ih2, magic2);
-                const f32x2 vl = fma2(u, il2, magic2);
-                // a pair whose two ends differ (a quotient on or next to a .5 boundary: bf16 operands make exact ties common) is divided
-                if ((((__float_as_uint(lo2(vh)) ^ __float_as_uint(lo2(vl))) | (__float_as_uint(hi2(vh)) ^ __float_as_uint(hi2(vl)))) != 0) || !fast)
-                    vh = pk2(fadd(rintf(fdiv(u0, s)), 12582920.0f), fadd(rintf(fdiv(u1, s)), 12582920.0f));
+                const uint32_t w = w8[i];
+                const f32x2 u = pk2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+                const f32x2 vh = fma2(u, ih2, magic2), vl = fma2(u, il2, magic2);
+                // a pair whose two ends differ (a quotient on or next to a .5 boundary: bf16 operands make exact ties common) is divided below
+                if (((__float_as_uint(lo2(vh)) ^ __float_as_uint(lo2(vl))) | (__float_as_uint(hi2(vh)) ^ __float_as_uint(hi2(vl)))) != 0) bad |= 1u << i;
                 const f32x2 d2 = mul2(sub2(vh, magic2), s2);
                 uint32_t yv;
                 asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(yv) : "f"(hi2(d2)), "f"(lo2(d2)));
@@ -571,6 +600,14 @@ __global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __re
                 const uint32_t c1 = __byte_perm(__byte_perm(nb[4], nb[5], 0x0040), __byte_perm(nb[6], nb[7], 0x0040), 0x5410);
                 st64(codes + (at >> 2), make_uint2(c0 ^ 0x88888888u, c1 ^ 0x88888888u));
             }
+            while (bad) {                                                // a divided pair's word and code byte, stored over the ones above (one pair in 250)
+                const int i = __ffs(bad) - 1;
+                bad &= bad - 1;
+                uint32_t w = w8[0];
+#pragma unroll
+                for (int k = 1; k < 8; k++) if (k == i) w = w8[k];
+                actq_wide_divided_pair(w, s, y ? y + at + 2 * i : nullptr, codes ? reinterpret_cast<uint8_t *>(codes) + (at >> 1) + i : nullptr);
+            }
         }
     }
 }
@@ -580,12 +617,18 @@ template <typename Src>
 bool launch_actq_wide(Src src, bool aligned, int M, uint16_t * y, float * s, int K, float clip, int qmax, uint16_t * codes, cudaStream_t stream) {
     if (!aligned || (y && !cam_aligned16(y)) || (codes && (reinterpret_cast<uintptr_t>(codes) & 7u))) return false;
     const long want8 = ((long)M + 7) / 8, want4 = ((long)M + 3) / 4, want2 = ((long)M + 1) / 2;
-#define CAM_AQ_WIDE(STV, WPRV, WANT) actq_wide_kernel<Src, STV, WPRV><<<cam_resident_grid(actq_wide_kernel<Src, STV, WPRV>, 256, 0, WANT), 256, 0, stream>>>(src, y, s, K, clip, qmax, codes, M)
-    if (K <= 512) CAM_AQ_WIDE(1, 1, want8);
-    else if (K <= 1024) CAM_AQ_WIDE(2, 1, want8);
-    else if (K <= 2048) CAM_AQ_WIDE(4, 1, want8);
-    else if (K <= 4096) CAM_AQ_WIDE(4, 2, want4);
-    else CAM_AQ_WIDE(4, 4, want2);
+    // SMV: the row's transformed values wait in shared memory (1 KB per warp and step) and the step loops are loops: a third of the
+    // registers and a quarter of the code of the unrolled form, which long rows pay for in resident warps and instruction fetches
+    static const char * force = getenv("CAMINUS_B200_ACTQ_SM");            // (tuning: "0" / "1" overrides the choice)
+#define CAM_AQ_WIDE(STV, WPRV, WANT, SMV) do { \
+        const bool sm = force ? force[0] == '1' : (SMV || (Src::kHeavy && STV > 1)); \
+        if (sm) actq_wide_kernel<Src, STV, WPRV, true><<<cam_resident_grid(actq_wide_kernel<Src, STV, WPRV, true>, 256, 8 * STV * 1024, WANT), 256, 8 * STV * 1024, stream>>>(src, y, s, K, clip, qmax, codes, M); \
+        else actq_wide_kernel<Src, STV, WPRV, false><<<cam_resident_grid(actq_wide_kernel<Src, STV, WPRV, false>, 256, 0, WANT), 256, 0, stream>>>(src, y, s, K, clip, qmax, codes, M); } while (0)
+    if (K <= 512) CAM_AQ_WIDE(1, 1, want8, false);
+    else if (K <= 1024) CAM_AQ_WIDE(2, 1, want8, false);
+    else if (K <= 2048) CAM_AQ_WIDE(4, 1, want8, true);
+    else if (K <= 4096) CAM_AQ_WIDE(4, 2, want4, true);
+    else CAM_AQ_WIDE(4, 4, want2, true);
 #undef CAM_AQ_WIDE
     return true;
 }
