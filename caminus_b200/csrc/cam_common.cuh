@@ -124,6 +124,22 @@ CAM_DEV uint4 ldg128(const void * p) { return __ldg(reinterpret_cast<const uint4
 CAM_DEV uint4 ld128(const void * p) { return *reinterpret_cast<const uint4 *>(p); }                 // data this kernel also writes
 CAM_DEV void st128(void * p, uint4 v) { *reinterpret_cast<uint4 *>(p) = v; }
 CAM_DEV void st64(void * p, uint2 v) { *reinterpret_cast<uint2 *>(p) = v; }
+// 256-bit accesses (sm_100: one request per lane covers a whole 32-byte sector; two 16-byte stores at a 32-byte lane stride write every
+// sector of the warp's span twice, half at a time, and the second level sees twice the write requests). p 32-byte aligned.
+CAM_DEV void st256_cs(float * p, float4 a, float4 b) {
+    asm volatile("st.global.cs.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(a.x), "f"(a.y), "f"(a.z), "f"(a.w), "f"(b.x), "f"(b.y), "f"(b.z),
+                 "f"(b.w) : "memory");
+}
+CAM_DEV void st256_cs(void * p, uint4 a, uint4 b) {
+    asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z),
+                 "r"(b.w) : "memory");
+}
+// eight floats at p: one 256-bit store when `wide` (p 32-byte aligned), else two 128-bit ones
+CAM_DEV void st8f_cs(float * p, float4 a, float4 b, bool wide) {
+    if (wide) st256_cs(p, a, b);
+    else { __stcs(reinterpret_cast<float4 *>(p), a); __stcs(reinterpret_cast<float4 *>(p) + 1, b); }
+}
+static inline bool cam_aligned32(const void * p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 CAM_DEV void st128_stream(void * p, uint4 v) { __stcs(reinterpret_cast<uint4 *>(p), v); }           // written once, not re-read here
 CAM_DEV void st64_stream(void * p, uint2 v) { __stcs(reinterpret_cast<uint2 *>(p), v); }
 

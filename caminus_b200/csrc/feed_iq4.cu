@@ -153,12 +153,14 @@ constexpr int IQ2S_ROWS = 4;      // token rows a block decodes together: a thre
 __global__ void __launch_bounds__(256) emb_rows_iq2s_kernel(const uint8_t * __restrict__ W, int rb, int vocab, const int * __restrict__ toks, float * __restrict__ x,
                                                             int n, int N, const uint32_t * __restrict__ grid) {
     __shared__ uint32_t gs[512];
-    __shared__ __align__(8) float2 mag2[64];     // two neighbouring values at once: entry (c0 | c1 << 2 | s0 << 4 | s1 << 5) = (+-mag(c0), +-mag(c1)), mag = 8, 25, 43
+    // two neighbouring values at once: entry (c0 | c1 << 2 | s0 << 4 | s1 << 5) = (+-mag(c0), +-mag(c1)), mag = 8, 25, 43; sixteen copies, one per
+    // lane of a 64-bit shared-memory pass (copy j in bank pair j): a warp's lookup is two conflict-free passes whatever the codes are
+    __shared__ __align__(8) float2 mag2[64 * 16];
     for (int i = threadIdx.x; i < 512; i += 256) gs[i] = __ldg(grid + i);
-    if (threadIdx.x < 64) {
-        const int i = threadIdx.x, c0 = i & 3, c1 = (i >> 2) & 3;
+    for (int t = threadIdx.x; t < 64 * 16; t += 256) {
+        const int i = t >> 4, c0 = i & 3, c1 = (i >> 2) & 3;
         const float m0 = c0 == 0 ? 8.0f : c0 == 1 ? 25.0f : 43.0f, m1 = c1 == 0 ? 8.0f : c1 == 1 ? 25.0f : 43.0f;
-        mag2[i] = make_float2((i & 16) ? -m0 : m0, (i & 32) ? -m1 : m1);
+        mag2[t] = make_float2((i & 16) ? -m0 : m0, (i & 32) ? -m1 : m1);
     }
     __syncthreads();
     const int units = N >> 3;
@@ -194,15 +196,98 @@ __global__ void __launch_bounds__(256) emb_rows_iq2s_kernel(const uint8_t * __re
                 f32x2 v[4];
 #pragma unroll
                 for (int k = 0; k < 4; k++) {
-                    const float2 m = mag2[((codes >> (4 * k)) & 15u) | (((sg >> (2 * k)) & 3u) << 4)];
+                    const float2 m = mag2[((((codes >> (4 * k)) & 15u) | (((sg >> (2 * k)) & 3u) << 4)) << 4) | (threadIdx.x & 15u)];
                     v[k] = mul2(db2, pk2(m.x, m.y));
                 }
                 float * o = x + (size_t)(p0 + r) * N + 8 * q;
-                __stcs(reinterpret_cast<float4 *>(o), make_float4(lo2(v[0]), hi2(v[0]), lo2(v[1]), hi2(v[1])));
+                __stcs(reinterpret_cast<float4 *>(o), make_float4(lo2(v[0]), hi2(v[0]), lo2(v[1]), hi2(v[1])));      // (one 256-bit store here measured slower: 40.8 us against 32.6 us)
                 __stcs(reinterpret_cast<float4 *>(o + 4), make_float4(lo2(v[2]), hi2(v[2]), lo2(v[3]), hi2(v[3])));
             }
         }
     }
+}
+
+// The same rows with the table's bytes staged: a warp per token row copies the row's blocks into its own shared-memory slice by 16-byte
+// cp.async (the next row's copy in flight while this one is decoded: the id, the row and its bytes are three dependent loads otherwise;
+// the first copy is issued before the block builds its tables) and decodes from there: block bl's group `lane` per step, byte reads
+// that cost no global request. Rows 16-byte aligned (table and rb).
+// The magnitudes come from byte permutes: the grid entry is held as eight 4-bit selectors (the 2-bit code, bit 2 = the value's sign bit,
+// spread from the signs byte by a 256-entry table); one permute over the pools 128 + {8, 25, 43, 43} and 128 - {8, 25, 43, 43} yields
+// four biased signed bytes, a second one per value puts the byte under the bits of 1.5 2^23, and a packed subtraction leaves the signed
+// magnitude as a float, exactly. The group's eight floats leave as ONE 256-bit store: two 16-byte stores at a 32-byte lane stride write
+// every 32-byte sector twice, half at a time (the second level saw 7.8 M sector writes for 4.2 M sectors, and the kernel 45 us
+// whatever its arithmetic cost: 30 us with the one store).
+CAM_DEV void iq2s_copy_row(uint8_t * dst, const uint8_t * src, int chunks, int lane) {
+    for (int c = lane; c < chunks; c += 32) cp_async16(dst + 16 * c, src + 16 * c);
+}
+CAM_DEV uint32_t spread2to4(uint32_t e) {         // sixteen bits as eight 2-bit fields -> eight nibbles
+    e = (e | (e << 8)) & 0x00ff00ffu; e = (e | (e << 4)) & 0x0f0f0f0fu; e = (e | (e << 2)) & 0x33333333u;
+    return e;
+}
+template <int NBLK, int WPB>
+__global__ void __launch_bounds__(32 * WPB) emb_rows_iq2s_staged_kernel(const uint8_t * __restrict__ W, int rb, int vocab, const int * __restrict__ toks,
+                                                                   float * __restrict__ x, int n, int N, const uint32_t * __restrict__ grid) {
+    __shared__ uint32_t sel[1024];                                        // grid entry -> selectors (code per nibble)
+    __shared__ uint32_t sgn[256];                                         // signs byte -> bit 2 of nibble j = bit j
+    extern __shared__ __align__(16) uint8_t iq2s_stage[];                 // [warp][2][chunks * 16]
+    const bool wide = (reinterpret_cast<uintptr_t>(x) & 31u) == 0;       // (rows are multiples of 1 KB: every group's eight floats are 32-byte aligned then)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nblk = NBLK ? NBLK : N >> 8, chunks = (nblk * 82 + 15) >> 4, stride = gridDim.x * WPB;
+    uint8_t * const mine = iq2s_stage + (size_t)warp * 2 * chunks * 16;
+    auto clamp_id = [&](int t) { return t < 0 ? 0 : t >= vocab ? vocab - 1 : t; };
+    // a warp per row; the ids of this warp's first three rows are loaded before anything waits for one
+    int p = blockIdx.x * WPB + warp;
+    const int id0 = p < n ? __ldg(toks + p) : 0, id1 = p + stride < n ? __ldg(toks + p + stride) : 0;
+    int id2 = p + 2 * stride < n ? __ldg(toks + p + 2 * stride) : 0;
+    if (p < n) iq2s_copy_row(mine, W + (size_t)clamp_id(id0) * rb, chunks, lane);
+    cp_async_commit();
+    for (int i = threadIdx.x; i < 512; i += 32 * WPB) {
+        const uint32_t w = __ldg(grid + i);
+        sel[2 * i] = spread2to4(w & 0xffffu); sel[2 * i + 1] = spread2to4(w >> 16);
+    }
+    for (uint32_t v = threadIdx.x; v < 256; v += 32 * WPB) {
+        uint32_t t = (v | (v << 12)) & 0x000f000fu; t = (t | (t << 6)) & 0x03030303u; t = (t | (t << 3)) & 0x11111111u;
+        sgn[v] = t << 2;
+    }
+    __syncthreads();
+    if (p >= n) return;
+    const int qsh = 2 * (lane & 3), ssh = 4 * ((lane >> 1) & 1);
+    int idn = id1;                                                        // the next row's id (loaded a pass ago)
+    for (int buf = 0;; buf ^= 1) {
+        const int pn = p + stride;
+        if (pn < n) iq2s_copy_row(mine + (buf ^ 1) * chunks * 16, W + (size_t)clamp_id(idn) * rb, chunks, lane);
+        cp_async_commit();
+        idn = id2;
+        if (pn + 2 * stride < n) id2 = __ldg(toks + pn + 2 * stride);   // (used two passes from now)
+        cp_async_wait<1>();
+        __syncwarp();
+        const uint8_t * bq = mine + buf * chunks * 16 + lane, * bh = mine + buf * chunks * 16 + (lane >> 2);
+        float * orow = x + (size_t)p * N + 8 * lane;
+#pragma unroll
+        for (int bl = 0; bl < nblk; bl++) {
+            const int off = 82 * bl;
+            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(mine + buf * chunks * 16 + off)));
+            const uint32_t lo = bq[off + 2], sg = bq[off + 34], qh = bh[off + 66], sb = bh[off + 74];
+            const uint32_t s8 = sel[lo + (((qh >> qsh) & 3u) << 8)] | sgn[sg];
+            const float db = fmul(fmul(d, fadd(0.5f, (float)((sb >> ssh) & 15u))), 0.25f);
+            const f32x2 db2 = pk2(db, db);
+            // four signed magnitudes each, as bytes biased by 128: 128 + {8, 25, 43, 43} and 128 - {8, 25, 43, 43}
+            const uint32_t m0 = __byte_perm(0xabab9988u, 0x55556778u, s8), m1 = __byte_perm(0xabab9988u, 0x55556778u, s8 >> 16);
+            // a byte under the bits of 1.5 2^23 is the float 12582912 + byte: minus 12583040 it is the signed magnitude, exactly (a
+            // permute and half a packed subtraction per value, against a shift, a sign extension and a conversion)
+            const f32x2 bias = pk2(-12583040.0f, -12583040.0f);
+            const f32x2 f0 = add2(pk2(__uint_as_float(__byte_perm(m0, 0x4b400000u, 0x7650)), __uint_as_float(__byte_perm(m0, 0x4b400000u, 0x7651))), bias);
+            const f32x2 f1 = add2(pk2(__uint_as_float(__byte_perm(m0, 0x4b400000u, 0x7652)), __uint_as_float(__byte_perm(m0, 0x4b400000u, 0x7653))), bias);
+            const f32x2 f2 = add2(pk2(__uint_as_float(__byte_perm(m1, 0x4b400000u, 0x7650)), __uint_as_float(__byte_perm(m1, 0x4b400000u, 0x7651))), bias);
+            const f32x2 f3 = add2(pk2(__uint_as_float(__byte_perm(m1, 0x4b400000u, 0x7652)), __uint_as_float(__byte_perm(m1, 0x4b400000u, 0x7653))), bias);
+            // db times the signed magnitude: the product's bits are those of -(db mag) or db mag (the sign of an IEEE product is exact)
+            const f32x2 v0 = mul2(db2, f0), v1 = mul2(db2, f1), v2 = mul2(db2, f2), v3 = mul2(db2, f3);
+            st8f_cs(orow + bl * 256, make_float4(lo2(v0), hi2(v0), lo2(v1), hi2(v1)), make_float4(lo2(v2), hi2(v2), lo2(v3), hi2(v3)), wide);
+        }
+        __syncwarp();                                                    // (the slice read here is the one the copy after next writes)
+        if (pn >= n) break;
+        p = pn;
+    }
+    cp_async_wait<0>();
 }
 
 }   // namespace
@@ -247,6 +332,16 @@ extern "C" int q35t_emb_iq2s(int n, const void * W, int rb, int vocab, const int
     if (n < 0 || vocab < 1 || N < 256 || (N & 255) || rb < N / 256 * 82 || !W || !toks || !x || !grid) return CAM_ERR_ARG;
     if ((reinterpret_cast<uintptr_t>(W) & 1u) || (rb & 1) || !cam_aligned16(x) || (reinterpret_cast<uintptr_t>(grid) & 3u)) return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
+    const size_t stage = (size_t)8 * 2 * ((N / 256 * 82 + 15) / 16) * 16;
+    if (cam_aligned16(W) && !(rb & 15) && stage <= 36 * 1024) {         // (rows of up to 15616 values; longer ones take the kernel below)
+        // a warp per row, a block per eight rows; more blocks than are resident (measured: 29.1 us against 30.7 us for resident blocks that
+        // loop; blocks of four or two warps 30.6-33.9 us), up to a grid the loop in the kernel then covers
+        long g8 = ((long)n + 7) / 8;
+        if (g8 > (1L << 20)) g8 = 1L << 20;
+        if (N == 2048) emb_rows_iq2s_staged_kernel<8, 8><<<(int)g8, 256, stage, (cudaStream_t)stream>>>((const uint8_t *)W, rb, vocab, toks, x, n, N, grid);
+        else emb_rows_iq2s_staged_kernel<0, 8><<<(int)g8, 256, stage, (cudaStream_t)stream>>>((const uint8_t *)W, rb, vocab, toks, x, n, N, grid);
+        return (int)cudaGetLastError();
+    }
     const long want = ((long)n + IQ2S_ROWS - 1) / IQ2S_ROWS;
     long g = cam_resident_grid(emb_rows_iq2s_kernel, 256, 0, want);
     emb_rows_iq2s_kernel<<<(int)g, 256, 0, (cudaStream_t)stream>>>((const uint8_t *)W, rb, vocab, toks, x, n, N, grid);

@@ -640,6 +640,12 @@ def test_iq2s_rows(golden):
     toks2 = g_.integers(-3, vocab2 + 3, 1000).astype(np.int32); x2 = torch.zeros(1000, nblk2 * 256, device=DEV)
     O.emb_iq2s(cu(W.reshape(-1)), nblk2 * 82, vocab2, cu(toks2), x2, 1000, nblk2 * 256)
     assert same(x2, oracle.emb_rows_iq2s(W, nblk2 * 82, vocab2, toks2, nblk2 * 256, oracle.pack_iq2s_grid(grid2)))
+    for nblk3, n3 in ((8, 20011), (16, 700), (24, 9)):                  # row strides that are multiples of 16 bytes: the staged kernel, several rows per warp
+        W3 = g_.integers(0, 256, (vocab2, nblk3, 82), dtype=np.uint8)
+        W3[:, :, 0:2] = (g_.standard_normal((vocab2, nblk3, 1)) * 1e-2).astype(np.float16).view(np.uint8).reshape(vocab2, nblk3, 2)
+        toks3 = g_.integers(-3, vocab2 + 3, n3).astype(np.int32); x3 = torch.zeros(n3, nblk3 * 256, device=DEV)
+        O.emb_iq2s(cu(W3.reshape(-1)), nblk3 * 82, vocab2, cu(toks3), x3, n3, nblk3 * 256)
+        assert same(x3, oracle.emb_rows_iq2s(W3, nblk3 * 82, vocab2, toks3, nblk3 * 256, oracle.pack_iq2s_grid(grid2)))
     with pytest.raises(ValueError): O.emb_iq2s(cu(W.reshape(-1)), 100, vocab2, cu(toks2), x2, 1000, nblk2 * 256)
     with pytest.raises(ValueError): q35own.Ops(DEV).emb_iq2s(cu(W.reshape(-1)), nblk2 * 82, vocab2, cu(toks2), x2, 1000, nblk2 * 256)
     with pytest.raises(ValueError): hip.set_iq2s_grid(np.zeros((1024, 8), np.uint8))
