@@ -496,6 +496,7 @@ __global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __re
     extern __shared__ uint4 aq_sm[];                                     // SM: [warp][step][2][lane], a lane reads back its own words only (no barrier)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g8 = lane >> 3, l8 = lane & 7;
     const int nch = K >> 7;
+    const bool y32 = (reinterpret_cast<uintptr_t>(y) & 31u) == 0;
     uint4 * const mine = aq_sm + (SM ? warp * (STEPS * 64) + lane : 0);
     constexpr int RPB = 8 / WPR;                                         // rows per block and pass
     const int part = WPR == 1 ? 0 : (warp & (WPR - 1));                  // this warp's part of the row: chunks part STEPS 4 ..
@@ -594,7 +595,10 @@ __global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __re
                 yw[i] = yv | (w & 0x80008000u);                          // (rint keeps the sign of a zero; elsewhere the signs agree already)
                 nb[i] = __float_as_uint(hi2(vh)) * 16u + __float_as_uint(lo2(vh));        // low byte: (q1 + 8) << 4 | (q0 + 8)
             }
-            if (y) { st128(y + at, make_uint4(yw[0], yw[1], yw[2], yw[3])); st128(y + at + 8, make_uint4(yw[4], yw[5], yw[6], yw[7])); }
+            if (y) {                                                     // (a lane's 32 bytes as one store where they are a whole sector: two 16-byte stores write each sector twice)
+                if (y32) st256(y + at, make_uint4(yw[0], yw[1], yw[2], yw[3]), make_uint4(yw[4], yw[5], yw[6], yw[7]));
+                else { st128(y + at, make_uint4(yw[0], yw[1], yw[2], yw[3])); st128(y + at + 8, make_uint4(yw[4], yw[5], yw[6], yw[7])); }
+            }
             if (codes) {
                 const uint32_t c0 = __byte_perm(__byte_perm(nb[0], nb[1], 0x0040), __byte_perm(nb[2], nb[3], 0x0040), 0x5410);
                 const uint32_t c1 = __byte_perm(__byte_perm(nb[4], nb[5], 0x0040), __byte_perm(nb[6], nb[7], 0x0040), 0x5410);

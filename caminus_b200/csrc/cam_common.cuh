@@ -134,6 +134,13 @@ CAM_DEV void st256_cs(void * p, uint4 a, uint4 b) {
     asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z),
                  "r"(b.w) : "memory");
 }
+CAM_DEV void st256(void * p, uint4 a, uint4 b) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z),
+                 "r"(b.w) : "memory");
+}
+CAM_DEV void ldg256(const void * p, uint4 & a, uint4 & b) {          // read-only data, 32-byte aligned
+    asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p));
+}
 // eight floats at p: one 256-bit store when `wide` (p 32-byte aligned), else two 128-bit ones
 CAM_DEV void st8f_cs(float * p, float4 a, float4 b, bool wide) {
     if (wide) st256_cs(p, a, b);
