@@ -70,7 +70,8 @@ int cam_rms_apply_f16(int n, void * x, const void * d, const float * tot, const 
  * normalises a row when all ranks' partials have arrived; tag = the call's sequence number (1, 2, 3, ..: never 0, the same on every
  * rank; a call with n = 0 launches nothing and must not use a tag up). Waits are bounded (2 s, or CAMINUS_B200_TP_WAIT_MS milliseconds):
  * on expiry bit 0 of *status is set and the warp takes no more rows, so the call's rows are PARTLY updated: those normalised before
- * hold x = fp16(x + d) and their h16, the others are untouched; a retry needs x restored from the caller's copy. n <= cap.
+ * hold x = fp16(x + d) and their h16, a row whose partial had been sent may hold x = fp16(x + d) without its h16, the others are
+ * untouched; a retry needs x restored from the caller's copy. n <= cap.
  * One exchange buffer serves every norm of a model: the buffer does not depend on the weights (caminus_b200.dist.TPExchange). */
 int cam_ipc_open(const void * handle64, void ** base);      /* map another process's exported allocation (its 64-byte cudaIpcMemHandle_t) for the current device, peer access included */
 int cam_ipc_close(void * base);

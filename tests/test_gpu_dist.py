@@ -90,8 +90,10 @@ def test_tp_rmsnorm_over_nccl_matches_the_unsharded_rows():
     ctx = mp.get_context('spawn')
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank, args=(r, world, port, 512, 5120, out)) for r in range(world)]
-    for p in procs: p.start()
-    for p in procs: p.join(300)
-    assert all(p.exitcode == 0 for p in procs)
-    assert out.get(timeout=10)
+    for N in (5120, 640 * world):                                      # shards the staged kernel takes (two ranks) and the lean one
+        port = _free_port()
+        procs = [ctx.Process(target=_rank, args=(r, world, port, 512, N, out)) for r in range(world)]
+        for p in procs: p.start()
+        for p in procs: p.join(300)
+        assert all(p.exitcode == 0 for p in procs)
+        assert out.get(timeout=10)

@@ -585,10 +585,11 @@ def test_tp_rms_fused_two_ranks_with_the_peer_words_in_place(N):
         assert np.array_equal(own_d.cpu().numpy().view(np.uint64)[half + rank * T: half + rank * T + T], _tp_words(parts[rank], tag))
 
 
-def test_tp_rms_fused_wait_runs_out_and_reports():
+@pytest.mark.parametrize('Ns', [256, 640])                             # the staged kernel and the lean one
+def test_tp_rms_fused_wait_runs_out_and_reports(Ns):
     """a peer that never writes: every wait ends at its limit, the status word says so, the rows are left alone, the context lives on"""
     from caminus_b200 import lib
-    T, Ns, world = 16, 256, 2
+    T, world = 16, 2
     L = lib.load(); words = L.cam_tp_rms_words(T, world)
     own = torch.zeros(words, dtype=torch.int64, device=DEV); peer = torch.zeros(words, dtype=torch.int64, device=DEV)
     peers = torch.tensor([own.data_ptr(), peer.data_ptr()], dtype=torch.int64, device=DEV); status = torch.zeros(1, dtype=torch.int32, device=DEV)
