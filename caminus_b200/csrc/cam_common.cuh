@@ -187,13 +187,17 @@ CAM_DEV float rcp_approx(float a) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : 
 template <int N> CAM_DEV uint32_t silu_bf16_fast(const float (&g)[N], uint32_t (&out)[N / 2]) {
     float gmin = g[0], amax = fabsf(g[0]), amin = fabsf(g[0]);
     uint32_t redo = 0;
+    const f32x2 nl2 = pk2(-0x1.715476p+0f, -0x1.715476p+0f), one2 = pk2(1.0f, 1.0f), up2 = pk2(0x1.00001ap+0f, 0x1.00001ap+0f), dn2 = pk2(0x1.ffffccp-1f, 0x1.ffffccp-1f);
 #pragma unroll
-    for (int k = 0; k < N; k += 2) {
-        const float s0 = fmul(g[k], rcp_approx(fadd(1.0f, ex2_approx(fmul(g[k], -0x1.715476p+0f)))));
-        const float s1 = fmul(g[k + 1], rcp_approx(fadd(1.0f, ex2_approx(fmul(g[k + 1], -0x1.715476p+0f)))));
+    for (int k = 0; k < N; k += 2) {                   // (two values per instruction: the same roundings as one by one)
+        const f32x2 g2 = pk2(g[k], g[k + 1]);
+        const f32x2 a2 = mul2(g2, nl2);
+        const f32x2 den = add2(one2, pk2(ex2_approx(lo2(a2)), ex2_approx(hi2(a2))));
+        const f32x2 s2 = mul2(g2, pk2(rcp_approx(lo2(den)), rcp_approx(hi2(den))));
+        const f32x2 hi_ = mul2(s2, up2), lo_ = mul2(s2, dn2);
         uint32_t lo;
-        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(out[k >> 1]) : "f"(fmul(s1, 0x1.00001ap+0f)), "f"(fmul(s0, 0x1.00001ap+0f)));
-        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(fmul(s1, 0x1.ffffccp-1f)), "f"(fmul(s0, 0x1.ffffccp-1f)));
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(out[k >> 1]) : "f"(hi2(hi_)), "f"(lo2(hi_)));
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(hi2(lo_)), "f"(lo2(lo_)));
         if (out[k >> 1] != lo) redo |= 1u << (k >> 1);
         if (k) { gmin = fminf(gmin, g[k]); amax = fmaxf(amax, fabsf(g[k])); amin = fminf(amin, fabsf(g[k])); }
         gmin = fminf(gmin, g[k + 1]); amax = fmaxf(amax, fabsf(g[k + 1])); amin = fminf(amin, fabsf(g[k + 1]));
