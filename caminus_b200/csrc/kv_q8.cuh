@@ -45,18 +45,20 @@ CAM_DEV void hadamard128(float (&x)[8], int l16) {
         float a0 = fadd(x[b], x[b + 1]), a1 = fsub(x[b], x[b + 1]), a2 = fadd(x[b + 2], x[b + 3]), a3 = fsub(x[b + 2], x[b + 3]);
         x[b] = fadd(a0, a2); x[b + 2] = fsub(a0, a2); x[b + 1] = fadd(a1, a3); x[b + 3] = fsub(a1, a3);
     }
+    f32x2 p2[4] = {pk2(x[0], x[1]), pk2(x[2], x[3]), pk2(x[4], x[5]), pk2(x[6], x[7])};      // (two values per instruction below: the same roundings)
 #pragma unroll
     for (int m = 1; m < 16; m <<= 1) {               // h = 4, 8, 16, 32: lanes l ^ 1, 2, 4, 8
         const float sg = (l16 & m) ? -1.0f : 1.0f;      // the upper lane of a pair holds partner - own: fma(own, -1, partner), one rounding
+        const f32x2 sg2 = pk2(sg, sg);
 #pragma unroll
-        for (int c = 0; c < 8; c++) {
-            const float p = __shfl_xor_sync(CAM_FULL, x[c], m);
-            x[c] = ffma(x[c], sg, p);
-        }
+        for (int c = 0; c < 4; c++)
+            p2[c] = fma2(p2[c], sg2, pk2(__shfl_xor_sync(CAM_FULL, lo2(p2[c]), m), __shfl_xor_sync(CAM_FULL, hi2(p2[c]), m)));
     }
+    const f32x2 r2 = pk2(0x1.6a09e6p-4f, 0x1.6a09e6p-4f);
 #pragma unroll
-    for (int c = 0; c < 4; c++) {                    // h = 64, then the scale
-        const float a = x[c], b = x[4 + c];
-        x[c] = fmul(fadd(a, b), 0x1.6a09e6p-4f); x[4 + c] = fmul(fsub(a, b), 0x1.6a09e6p-4f);
+    for (int c = 0; c < 2; c++) {                    // h = 64, then the scale
+        const f32x2 a = p2[c], b = p2[2 + c];
+        const f32x2 lo = mul2(add2(a, b), r2), hi = mul2(sub2(a, b), r2);
+        x[2 * c] = lo2(lo); x[2 * c + 1] = hi2(lo); x[4 + 2 * c] = lo2(hi); x[4 + 2 * c + 1] = hi2(hi);
     }
 }
