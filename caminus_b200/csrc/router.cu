@@ -323,11 +323,12 @@ __global__ void __launch_bounds__(1024) group_cluster_kernel(const int * __restr
         if (e < 0 || e >= E) { bad = true; e = 0; }
         return e;
     };
+    unsigned keptsame[GR_KEEP];                  // (the kept steps' equal-lane masks serve both passes)
 #pragma unroll
     for (int q = 0; q < GR_KEEP; q++)
         if (q < steps) {
             const int e = kept[q];
-            const unsigned same = same_lanes((unsigned)(e + 1), nbits);
+            const unsigned same = keptsame[q] = same_lanes((unsigned)(e + 1), nbits);
             if (e >= 0 && (same & below) == 0) col[e * GR_PITCH] += __popc(same);
             __syncwarp();
         }
@@ -386,7 +387,7 @@ __global__ void __launch_bounds__(1024) group_cluster_kernel(const int * __restr
     };
 #pragma unroll
     for (int q = 0; q < GR_KEEP; q++)
-        if (q < steps) place(kept[q], q, same_lanes((unsigned)(kept[q] + 1), nbits));
+        if (q < steps) place(kept[q], q, keptsame[q]);
     for (int s = GR_KEEP; s < steps; s++) {
         const long p = lo + 32 * s + lane;
         int e = -1;
@@ -451,9 +452,28 @@ extern "C" int q3p_group(const int * ids, int npairs, int k, int E, int * xs, in
     int l = 0; while ((1LL << l) < k) l++;
     const int kshift = 32 + l;
     const unsigned long long kmul = (unsigned long long)((((unsigned __int128)1 << kshift) + (unsigned)k - 1) / (unsigned)k);
+    // A cluster of 16 (beyond the portable 8) where the device schedules one: asked once per device
+    static int max16[64] = {};                                                         // 0: not asked, 1: no, 2: yes
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && max16[dev] == 0) {
+        int ok = 1;
+        if (cudaFuncSetAttribute(group_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+            cudaLaunchConfig_t q = {};
+            q.gridDim = dim3(16); q.blockDim = dim3(1024); q.dynamicSmemBytes = smem;
+            cudaLaunchAttribute qa[1];
+            qa[0].id = cudaLaunchAttributeClusterDimension; qa[0].val.clusterDim.x = 16; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+            q.attrs = qa; q.numAttrs = 1;
+            int nclusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&nclusters, group_cluster_kernel, &q) == cudaSuccess && nclusters >= 1) ok = 2;
+        }
+        (void)cudaGetLastError();
+        max16[dev] = ok;
+    }
+    const int cap = dev >= 0 && dev < 64 && max16[dev] == 2 && smem <= 48 * 1024 ? 16 : 8;
     int nblk = 1;
-    while (nblk < 8 && (long)nblk * 8192 < npairs) nblk *= 2;                         // 8 steps of 32 pairs per warp before the cluster grows
-    if (const char * e = getenv("CAMINUS_B200_GROUP_BLOCKS")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4 || v == 8) nblk = v; }      // (tuning)
+    while (nblk < cap && (long)nblk * 4096 < npairs) nblk *= 2;                       // 4 steps of 32 pairs per warp before the cluster grows
+    if (const char * e = getenv("CAMINUS_B200_GROUP_BLOCKS")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4 || v == 8 || (v == 16 && cap == 16)) nblk = v; }      // (tuning)
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(nblk); cfg.blockDim = dim3(1024); cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)stream;
     cudaLaunchAttribute at[1];
