@@ -431,8 +431,8 @@ extern "C" int cam_tp_rms_norm_f16(int n, void * x, const void * d, const float 
     cudaStream_t st = (cudaStream_t)stream;
     unsigned long long wait_ns = CAM_TP_WAIT_NS;    // CAMINUS_B200_TP_WAIT_MS: the limit of a wait in milliseconds (1 .. 600000)
     if (const char * e = getenv("CAMINUS_B200_TP_WAIT_MS")) { const long ms = atol(e); if (ms >= 1 && ms <= 600000) wait_ns = (unsigned long long)ms * 1000000ull; }
-    // Measured around the lean kernel (65536 rows of 640 columns, one rank: 63.0 us) and not kept: the next rows' loads issued before the
-    // previous rows are normalised (126 registers: 63.1 us); the rows read a second time from the second-level cache instead of parked in
+    // The lean kernel requests the next rows' loads before it normalises the previous rows (126 registers; on one rank the same 63 us as
+    // without: 65536 rows of 640 columns). Measured around it and not kept: the rows read a second time from the second-level cache instead of parked in
     // shared memory, one or two rows per lane group and step (67.8 / 72.7 us); the partials' words asked for a phase early (64.4 us);
     // blocks of 6 or 4 warps (64.4 / 76.4 us).
     if (world <= 16 && !getenv("CAMINUS_B200_TP_CFG")) {                // the usual shards: the lean kernel (a row on 16 or 32 lanes, chunks counted at compile time)
