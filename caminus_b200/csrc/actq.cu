@@ -71,6 +71,7 @@ struct PlainBf16 {
     CAM_DEV void get4(int row, int k, float (&v)[4]) const { bf4(__ldg(reinterpret_cast<const uint2 *>(x + (size_t)row * K + k)), v); }
     static constexpr bool kBf16 = true;            // get4's values are bf16 numbers already
     static constexpr bool kHeavy = false;          // (a source whose loads carry arithmetic of their own keeps the transformed row in shared memory sooner)
+    static constexpr bool kPrologue = false;       // (no work per row before the steps)
     // sixteen consecutive values at k (a multiple of 16; rows 16-byte aligned) as pairs; zeros when off
     CAM_DEV void get16(bool on, int row, int k, f32x2 (&p)[8]) const {
         uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
@@ -87,7 +88,7 @@ struct PlainF32 {
         const float4 a = __ldg(reinterpret_cast<const float4 *>(x + (size_t)row * K + k)); v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
     }
     static constexpr bool kBf16 = false;
-    static constexpr bool kHeavy = false;
+    static constexpr bool kHeavy = false, kPrologue = false;
     CAM_DEV void get16(bool on, int row, int k, f32x2 (&p)[8]) const {
 #pragma unroll
         for (int q = 0; q < 4; q++) {
@@ -122,7 +123,7 @@ struct SiluMulSrc {
         rbf4(v);
     }
     static constexpr bool kBf16 = true;
-    static constexpr bool kHeavy = true;
+    static constexpr bool kHeavy = true, kPrologue = false;
     // sixteen consecutive activations at k as pairs (rows and F 16-byte aligned: ld and F multiples of 8, checked by the launcher)
     CAM_DEV void get16(bool on, int row, int k, f32x2 (&p)[8]) const {
         if (!on) {                               // (no gates: zeros, and no visit to the exact statements that a zero gate asks for)
@@ -452,6 +453,81 @@ CAM_DEV void fwht_wide(f32x2 (&p)[8], int l8) {
 }
 CAM_DEV bool bf16_word_has_nan(uint32_t w) { return (((w & 0x7fff7fffu) + 0x007f007fu) & 0x80008000u) != 0; }
 
+// The block entry as a source of the sixteen-values-per-lane kernel: a prologue per row on the warp (lane l holds the four values 4 l ..
+// of every chunk of 128, the layout in which the reference's ordered sums are in-lane fma chains) forms rstd, stores
+// hb = bf16((x rstd) w) into the warp's shared-memory slice and the thin projections ab = bf16(hb . wab[j]); the quantiser's steps then
+// read hb back sixteen values per lane. Sums: thread tid owns tid + 256 j, wave butterflies, 8 wave sums in order (ref_total_f32's
+// statements, the butterfly's additions two accumulators per instruction).
+CAM_DEV float ref_total_f32_pairs(f32x2 (&a2)[4], int lane) {            // a2[c] = accumulators 2 c, 2 c + 1 of ref_total_f32's a[8]
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1)
+#pragma unroll
+        for (int c = 0; c < 4; c++) a2[c] = add2(a2[c], pk2(__shfl_xor_sync(CAM_FULL, lo2(a2[c]), o), __shfl_xor_sync(CAM_FULL, hi2(a2[c]), o)));
+    const f32x2 t0 = add2(a2[0], a2[1]), t1 = add2(a2[2], a2[3]);        // partner 2: (a0 + a2, a1 + a3), (a4 + a6, a5 + a7)
+    const float P0 = fadd(lo2(t0), hi2(t0)), P1 = fadd(lo2(t1), hi2(t1));   // partner 1
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) tot = fadd(tot, __shfl_sync(CAM_FULL, w < 4 ? P0 : P1, 8 * (w & 3)));
+    return tot;
+}
+// NCH: the row's chunks of 128 when known at compile time (0: counted from d, up to 8)
+template <int NCH>
+struct BlockEntrySrc {
+    static constexpr int MAXC = NCH ? NCH : 8;
+    const float * x; const float * nw; const uint16_t * wab; int nab; float eps; uint16_t * ab; float * rstd_out; int d;
+    uint16_t * stage;                              // this warp's slice of shared memory (set by the kernel): d bf16 values
+    static constexpr bool kBf16 = true, kHeavy = false, kPrologue = true;
+    CAM_DEV void begin_row(bool on, int row, int lane) const {
+        const int nch = NCH ? NCH : d >> 7;
+        f32x2 u[MAXC][2];                          // chunk c: (v0, v1), (v2, v3) of this lane's four
+        const float * xr = x + (size_t)(on ? row : 0) * d + lane * 4;
+#pragma unroll
+        for (int c = 0; c < MAXC; c++) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (on && c < nch) a = __ldg(reinterpret_cast<const float4 *>(xr + c * 128));
+            u[c][0] = pk2(a.x, a.y); u[c][1] = pk2(a.z, a.w);
+        }
+        f32x2 a2[4] = {pk2(0.f, 0.f), pk2(0.f, 0.f), pk2(0.f, 0.f), pk2(0.f, 0.f)};
+#pragma unroll
+        for (int c = 0; c < MAXC; c++)
+            if (c < nch) { a2[2 * (c & 1)] = fma2(u[c][0], u[c][0], a2[2 * (c & 1)]); a2[2 * (c & 1) + 1] = fma2(u[c][1], u[c][1], a2[2 * (c & 1) + 1]); }
+        const float rstd = cam_rsqrt(fadd(fdiv(ref_total_f32_pairs(a2, lane), (float)d), eps));
+        if (lane == 0 && on) rstd_out[row] = rstd;
+        const f32x2 r2 = pk2(rstd, rstd);
+#pragma unroll
+        for (int c = 0; c < MAXC; c++)
+            if (c < nch) {                         // hb = bf16((x rstd) w): the quantiser's source and the projections' operand
+                const float4 w4 = __ldg(reinterpret_cast<const float4 *>(nw + c * 128 + lane * 4));
+                const f32x2 h0 = mul2(mul2(u[c][0], r2), pk2(w4.x, w4.y)), h1 = mul2(mul2(u[c][1], r2), pk2(w4.z, w4.w));
+                const uint32_t b0 = bf16x2<true>(lo2(h0), hi2(h0)), b1 = bf16x2<true>(lo2(h1), hi2(h1));
+                *reinterpret_cast<uint2 *>(stage + c * 128 + lane * 4) = make_uint2(b0, b1);
+                u[c][0] = pk2(__uint_as_float(b0 << 16), __uint_as_float(b0 & 0xffff0000u));
+                u[c][1] = pk2(__uint_as_float(b1 << 16), __uint_as_float(b1 & 0xffff0000u));
+            }
+        for (int j = 0; j < nab; j++) {
+            const uint16_t * wr = wab + (size_t)j * d + lane * 4;
+            f32x2 p2[4] = {pk2(0.f, 0.f), pk2(0.f, 0.f), pk2(0.f, 0.f), pk2(0.f, 0.f)};
+#pragma unroll
+            for (int c = 0; c < MAXC; c++)
+                if (c < nch) {
+                    const uint2 wv = __ldg(reinterpret_cast<const uint2 *>(wr + c * 128));
+                    p2[2 * (c & 1)] = fma2(u[c][0], pk2(__uint_as_float(wv.x << 16), __uint_as_float(wv.x & 0xffff0000u)), p2[2 * (c & 1)]);
+                    p2[2 * (c & 1) + 1] = fma2(u[c][1], pk2(__uint_as_float(wv.y << 16), __uint_as_float(wv.y & 0xffff0000u)), p2[2 * (c & 1) + 1]);
+                }
+            const float tot = ref_total_f32_pairs(p2, lane);
+            if (lane == 0 && on) ab[(size_t)row * nab + j] = f2bf(tot);
+        }
+        __syncwarp();                              // (hb is read back by other lanes)
+    }
+    CAM_DEV void get16(bool on, int row, int k, f32x2 (&p)[8]) const {
+        uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
+        if (on) { const uint4 * r = reinterpret_cast<const uint4 *>(stage + k); a = r[0]; b = r[1]; }
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) p[i] = pk2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+    }
+};
+
 // the codes, dequantised values and stores of one warp step in general: every value clamped (a clip below 1 lets quotients pass qmax; a
 // NaN or an infinity among the values needs fminf / fmaxf's treatment of a NaN)
 __device__ __noinline__ void actq_wide_emit_clamped(uint4 ua, uint4 ub, float s, float inv, bool fast, float lo, float hi, size_t at, uint16_t * __restrict__ y,
@@ -498,6 +574,7 @@ __global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __re
     const int nch = K >> 7;
     const bool y32 = (reinterpret_cast<uintptr_t>(y) & 31u) == 0;
     uint4 * const mine = aq_sm + (SM ? warp * (STEPS * 64) + lane : 0);
+    if constexpr (Src::kPrologue) src.stage = reinterpret_cast<uint16_t *>(aq_sm + (SM ? 8 * STEPS * 64 : 0)) + warp * (STEPS * 512);      // (K bf16 values per warp)
     constexpr int RPB = 8 / WPR;                                         // rows per block and pass
     const int part = WPR == 1 ? 0 : (warp & (WPR - 1));                  // this warp's part of the row: chunks part STEPS 4 ..
     for (int r0 = blockIdx.x * RPB; r0 < M; r0 += gridDim.x * RPB) {     // (block-uniform: every warp takes part in the barrier below)
@@ -505,6 +582,7 @@ __global__ void __launch_bounds__(256) actq_wide_kernel(Src src, uint16_t * __re
         const bool row_on = row < M;
         uint32_t upr[SM ? 1 : STEPS][8];                                 // the transformed values, bf16 pairs (SM: in shared memory instead)
         float amax = 0.f;                                                // over the values before their rounding to bf16 (rounded below: rounding is monotone)
+        if constexpr (Src::kPrologue) src.begin_row(row_on, row, lane);
         bool odd = false;                                                // a NaN or an infinity among this lane's transformed values
 #pragma unroll (SM ? 1 : STEPS)
         for (int st = 0; st < STEPS; st++) {
@@ -626,8 +704,9 @@ bool launch_actq_wide(Src src, bool aligned, int M, uint16_t * y, float * s, int
     static const char * force = getenv("CAMINUS_B200_ACTQ_SM");            // (tuning: "0" / "1" overrides the choice)
 #define CAM_AQ_WIDE(STV, WPRV, WANT, SMV) do { \
         const bool sm = force ? force[0] == '1' : (SMV || (Src::kHeavy && STV > 1)); \
-        if (sm) actq_wide_kernel<Src, STV, WPRV, true><<<cam_resident_grid(actq_wide_kernel<Src, STV, WPRV, true>, 256, 8 * STV * 1024, WANT), 256, 8 * STV * 1024, stream>>>(src, y, s, K, clip, qmax, codes, M); \
-        else actq_wide_kernel<Src, STV, WPRV, false><<<cam_resident_grid(actq_wide_kernel<Src, STV, WPRV, false>, 256, 0, WANT), 256, 0, stream>>>(src, y, s, K, clip, qmax, codes, M); } while (0)
+        const size_t pro = Src::kPrologue ? (size_t)8 * STV * 1024 : 0;      /* (a prologue's staged row: STV * 512 bf16 per warp) */ \
+        if (sm) actq_wide_kernel<Src, STV, WPRV, true><<<cam_resident_grid(actq_wide_kernel<Src, STV, WPRV, true>, 256, 8 * STV * 1024 + pro, WANT), 256, 8 * STV * 1024 + pro, stream>>>(src, y, s, K, clip, qmax, codes, M); \
+        else actq_wide_kernel<Src, STV, WPRV, false><<<cam_resident_grid(actq_wide_kernel<Src, STV, WPRV, false>, 256, pro, WANT), 256, pro, stream>>>(src, y, s, K, clip, qmax, codes, M); } while (0)
     if (K <= 512) CAM_AQ_WIDE(1, 1, want8, false);
     else if (K <= 1024) CAM_AQ_WIDE(2, 1, want8, false);
     else if (K <= 2048) CAM_AQ_WIDE(4, 1, want8, true);
@@ -707,6 +786,13 @@ extern "C" int block_entry_fwd(int M, const float * x, const float * nw, const v
     if (!nw || !rstd_out || nab < 0 || nab > AQ_NAB || (nab && (!wab || !ab))) return CAM_ERR_ARG;
     if (misaligned8(y)) return CAM_ERR_ALIGN;
     if (M == 0) return CAM_OK;
+    if (d <= 1024 && cam_aligned16(x) && cam_aligned16(nw) && !misaligned8(wab)) {
+#define CAM_BE_WIDE(NCHV) launch_actq_wide(BlockEntrySrc<NCHV>{x, nw, (const uint16_t *)wab, nab, eps, (uint16_t *)ab, rstd_out, d, nullptr}, true, M, (uint16_t *)y, s, d, \
+                                           clip, qmax, (uint16_t *)codes, CAM_ST)
+        const bool done = d == 896 ? CAM_BE_WIDE(7) : d == 1024 ? CAM_BE_WIDE(8) : d == 512 ? CAM_BE_WIDE(4) : CAM_BE_WIDE(0);
+#undef CAM_BE_WIDE
+        if (done) return (int)cudaGetLastError();
+    }
     if (d <= 1024 && cam_aligned16(x) && cam_aligned16(nw) && !misaligned8(wab)) {
         const long want = ((long)M + 7) / 8;
         block_entry_rows_kernel<8><<<cam_resident_grid(block_entry_rows_kernel<8>, 256, 0, want), 256, 0, CAM_ST>>>(
