@@ -470,6 +470,28 @@ CAM_DEV float ref_total_f32_pairs(f32x2 (&a2)[4], int lane) {            // a2[c
     for (int w = 0; w < 8; w++) tot = fadd(tot, __shfl_sync(CAM_FULL, w < 4 ? P0 : P1, 8 * (w & 3)));
     return tot;
 }
+// two such sums at once, a[] and b[]: in the first butterfly stage a lane keeps one of the two (lanes with bit 2 clear a's, the others b's) and
+// sends the other, so each stage costs one set of shuffles for both; the additions and their order are ref_total_f32's. Returns the
+// total of the lane's own sum (a's where lane & 4 is clear).
+CAM_DEV float ref_total_f32_two(const f32x2 (&a)[4], const f32x2 (&b)[4], int lane) {
+    const bool up = (lane & 4) != 0;
+    f32x2 v[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const f32x2 keep = up ? b[c] : a[c], send = up ? a[c] : b[c];
+        v[c] = add2(keep, pk2(__shfl_xor_sync(CAM_FULL, lo2(send), 4), __shfl_xor_sync(CAM_FULL, hi2(send), 4)));
+    }
+#pragma unroll
+    for (int o = 2; o > 0; o >>= 1)
+#pragma unroll
+        for (int c = 0; c < 4; c++) v[c] = add2(v[c], pk2(__shfl_xor_sync(CAM_FULL, lo2(v[c]), o), __shfl_xor_sync(CAM_FULL, hi2(v[c]), o)));
+    const f32x2 t0 = add2(v[0], v[1]), t1 = add2(v[2], v[3]);
+    const float P0 = fadd(lo2(t0), hi2(t0)), P1 = fadd(lo2(t1), hi2(t1));
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) tot = fadd(tot, __shfl_sync(CAM_FULL, w < 4 ? P0 : P1, 8 * (w & 3) + (lane & 4)));
+    return tot;
+}
 // NCH: the row's chunks of 128 when known at compile time (0: counted from d, up to 8)
 template <int NCH>
 struct BlockEntrySrc {
@@ -504,18 +526,21 @@ struct BlockEntrySrc {
                 u[c][0] = pk2(__uint_as_float(b0 << 16), __uint_as_float(b0 & 0xffff0000u));
                 u[c][1] = pk2(__uint_as_float(b1 << 16), __uint_as_float(b1 & 0xffff0000u));
             }
-        for (int j = 0; j < nab; j++) {
-            const uint16_t * wr = wab + (size_t)j * d + lane * 4;
-            f32x2 p2[4] = {pk2(0.f, 0.f), pk2(0.f, 0.f), pk2(0.f, 0.f), pk2(0.f, 0.f)};
+        for (int j = 0; j < nab; j += 2) {         // two projections at a time (an odd count's last one beside a row of zeros)
+            const bool two = j + 1 < nab;
+            const uint16_t * wr = wab + (size_t)j * d + lane * 4, * wr1 = wr + (two ? d : 0);
+            f32x2 pa[4] = {pk2(0.f, 0.f), pk2(0.f, 0.f), pk2(0.f, 0.f), pk2(0.f, 0.f)}, pb[4] = {pk2(0.f, 0.f), pk2(0.f, 0.f), pk2(0.f, 0.f), pk2(0.f, 0.f)};
 #pragma unroll
             for (int c = 0; c < MAXC; c++)
                 if (c < nch) {
-                    const uint2 wv = __ldg(reinterpret_cast<const uint2 *>(wr + c * 128));
-                    p2[2 * (c & 1)] = fma2(u[c][0], pk2(__uint_as_float(wv.x << 16), __uint_as_float(wv.x & 0xffff0000u)), p2[2 * (c & 1)]);
-                    p2[2 * (c & 1) + 1] = fma2(u[c][1], pk2(__uint_as_float(wv.y << 16), __uint_as_float(wv.y & 0xffff0000u)), p2[2 * (c & 1) + 1]);
+                    const uint2 wv = __ldg(reinterpret_cast<const uint2 *>(wr + c * 128)), wz = __ldg(reinterpret_cast<const uint2 *>(wr1 + c * 128));
+                    pa[2 * (c & 1)] = fma2(u[c][0], pk2(__uint_as_float(wv.x << 16), __uint_as_float(wv.x & 0xffff0000u)), pa[2 * (c & 1)]);
+                    pa[2 * (c & 1) + 1] = fma2(u[c][1], pk2(__uint_as_float(wv.y << 16), __uint_as_float(wv.y & 0xffff0000u)), pa[2 * (c & 1) + 1]);
+                    pb[2 * (c & 1)] = fma2(u[c][0], pk2(__uint_as_float(wz.x << 16), __uint_as_float(wz.x & 0xffff0000u)), pb[2 * (c & 1)]);
+                    pb[2 * (c & 1) + 1] = fma2(u[c][1], pk2(__uint_as_float(wz.y << 16), __uint_as_float(wz.y & 0xffff0000u)), pb[2 * (c & 1) + 1]);
                 }
-            const float tot = ref_total_f32_pairs(p2, lane);
-            if (lane == 0 && on) ab[(size_t)row * nab + j] = f2bf(tot);
+            const float tot = ref_total_f32_two(pa, pb, lane);
+            if (on && (lane == 0 || (lane == 4 && two))) ab[(size_t)row * nab + j + (lane >> 2)] = f2bf(tot);
         }
         __syncwarp();                              // (hb is read back by other lanes)
     }

@@ -381,6 +381,15 @@ def test_actq_family(M, K):
             yo, so, co, abo, ro = oracle.block_entry_fwd(x, nw, None if w_ is None else bits(w_).reshape(6, K), 1e-6, 1.0, 7)
             assert same(y, yo) and same(s, so) and same(rstd, ro) and np.array_equal(c.cpu().numpy().view(np.uint16).reshape(-1), co.reshape(-1))
             if w_ is not None: assert same(ab, abo)
+        # an odd number of projections (the wrapper takes even counts as upstream; the entry itself takes any up to 16)
+        import ctypes
+        from caminus_b200.device import cuda as hip
+        w5 = torch.from_numpy(acts(g, (5, K), 0.05)).bfloat16().to(DEV); xd = cu(x); nwd = cu(nw)
+        y5 = torch.empty(M, K, dtype=torch.bfloat16, device=DEV); s5 = torch.empty(M, device=DEV); c5 = torch.empty(M, K // 4, dtype=torch.int16, device=DEV)
+        ab5 = torch.empty(M, 5, dtype=torch.bfloat16, device=DEV); r5 = torch.empty(M, device=DEV)
+        hip.Module('actq').block_entry_fwd((M,), (256,), xd, nwd, w5, ctypes.c_int(5), ctypes.c_float(1e-6), y5, s5, c5, ab5, r5, ctypes.c_int(K), ctypes.c_float(1.0), ctypes.c_int(7))
+        yo, so, co, abo, ro = oracle.block_entry_fwd(x, nw, bits(w5).reshape(5, K), 1e-6, 1.0, 7)
+        assert same(y5, yo) and same(s5, so) and same(r5, ro) and same(ab5, abo)
 
 
 def test_router_topk_group():
