@@ -612,6 +612,10 @@ extern "C" int cam_add_rms_f16(int n, void * x, const void * d, const float * nw
     if (!cam_aligned16(x) || !cam_aligned16(nw) || (d && !cam_aligned16(d)) || !cam_aligned16(h16)) return CAM_ERR_ALIGN;
     if (n >= 64) {      // (a handful of rows: the staged kernel, which does not stage the weights first)
         switch (N) {
+            case 512: return launch_f16_reg<2>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
+            case 768: return launch_f16_reg<3>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
+            case 1280: return launch_f16_reg<5>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
+            case 1536: return launch_f16_reg<6>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
             case 1024: return launch_f16_reg<4>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
             case 2048: return launch_f16_reg<8>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
             case 2560: return launch_f16_reg<10>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);

@@ -2,9 +2,9 @@
 // columns of a row to one fp32 sum of squares, writes it straight into every rank's exchange buffer over NVLink (plain peer
 // stores), and normalises its columns once all ranks' partials of that row have arrived in its own buffer. The two-kernel form
 // (cam_rms_partial_f16 -> all-reduce of [T] floats -> cam_rms_apply_f16, csrc/add_rms.cu) reads every row twice from HBM and pays a
-// collective's launch between the kernels; here a warp keeps its rows in shared memory from the sum of squares to the
-// normalisation (rows too long for that are read a second time, a few rows later), and the exchange overlaps the arithmetic row
-// by row. The reference has no counterpart (it replicates its norms,
+// collective's launch between the kernels; here a warp keeps its rows in registers (the usual shard widths) or in shared memory from
+// the sum of squares to the normalisation (rows too long for that are read a second time, a few rows later), and the exchange
+// overlaps the arithmetic row by row. The reference has no counterpart (it replicates its norms,
 // python/caminus/engine/q3moe_tp.py:18-20).
 //
 // Exchange buffer of a rank (the caller allocates it and maps every rank's into every process): 64-bit words
@@ -248,13 +248,10 @@ __global__ void __launch_bounds__(256) tp_rms_staged_kernel(uint16_t * __restric
     cp_async_wait<0>();
 }
 
-// The lean form for the usual shards (Ns = G x 8 x CH with G = 16 or 32 lanes per row and CH <= 5 chunks per lane: 512 / 640 columns on a
-// half-warp, two rows per warp; 1024 / 1280 on a warp): every lane of every instruction is busy, nothing is counted or tested per chunk, and
-// the row is converted once. Per step a warp loads its row(s) straight into registers, forms x + d, stores fp16(x + d), the sum of squares
-// in the reference's order and the fp32 sums into its own shared-memory slot, sends the partial; then takes the row(s) of one step ago out
-// of the other slot, whose partials have had a step to cross NVLink, and normalises them. 170-180 warp instructions per row against 575.
-// Element of lane l, chunk q, value c: G = 32: 256 q + 8 l + c (thread 8 l + c of the reference's 256, its j = q); G = 16, lane h of the
-// half-warp: 128 q + 8 h + c (thread 128 (q & 1) + 8 h + c, j = q >> 1).
+// The form for the usual shards (Ns = G x 8 x CH with G = 16 or 32 lanes per row: 512 / 640 columns on a half-warp, two rows per warp;
+// 1024 / 1280 / 2048 / 2560 on a warp): every lane of every instruction is busy, nothing is counted or tested per chunk, and the row is
+// converted once. Element of lane l, chunk q, value c: G = 32: 256 q + 8 l + c (thread 8 l + c of the reference's 256, its j = q);
+// G = 16, lane h of the half-warp: 128 q + 8 h + c (thread 128 (q & 1) + 8 h + c, j = q >> 1).
 template <int G> CAM_DEV float tp_row_total(float (&a)[2][8], int lane) {
     // a[g][c]: thread 128 g + 8 h + c (G = 16; g = 0 only for G = 32, thread 8 l + c). Wave butterfly 16, 8 = lanes ^ 2, ^ 1; 4, 2, 1 inside
     // the lane; then the 8 wave sums in order: wave w = thread >> 5 sits in lane 4 (w & 3) of the row's lanes (G = 16: its g = w >> 2)
@@ -275,71 +272,74 @@ template <int G> CAM_DEV float tp_row_total(float (&a)[2][8], int lane) {
     return tot;
 }
 
+// The next block number of this call, in the order blocks actually start: word = (tag << 32) | blocks started. The first block of a call
+// finds another tag there and replaces it. With numbers handed out this way the lowest unfinished number on every rank belongs to a
+// running block, so the rank that is behind always holds the block whose partials the others wait for, whatever order the hardware
+// starts blocks in (each block sends its partials before it waits).
+CAM_DEV unsigned tp_take_number(unsigned long long * counter, unsigned tag) {
+    for (;;) {
+        const unsigned long long w = *reinterpret_cast<volatile unsigned long long *>(counter);
+        if ((unsigned)(w >> 32) == tag) return (unsigned)atomicAdd(counter, 1ull);
+        if (atomicCAS(counter, w, ((unsigned long long)tag << 32) | 1ull) == w) return 0u;
+    }
+}
+
+// Nothing is parked: a warp loads its row(s) straight into registers, stores fp16(x + d), sends the partial, waits for the others' and
+// normalises from the fp32 sums it still holds. Blocks of four warps, a block per 4 or 8 rows, so more blocks than are resident (a finished
+// block's successor starts with its loads at once, and the blocks' load, arithmetic and store phases drift apart instead of running in
+// step): the shape of add_rms_f16_reg_kernel. 65536 rows of 640 columns on one rank: 57 us (0.89); the pipelined kernels that parked rows
+// in shared memory on resident, looping blocks: 63-68 us, and this kernel itself on resident blocks that loop: 63.8 us.
 template <int G, int CH>
-__global__ void __launch_bounds__(256, 2) tp_rms_lean_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d, const float * __restrict__ nw, float eps,
-                                                             uint16_t * __restrict__ h16, int Nfull, int n, unsigned long long * const * __restrict__ peers,
-                                                             int rank, int world, int cap, unsigned tag, int * status, int warps, unsigned long long wait_ns) {
-    constexpr int RPW = 32 / G, Ns = G * 8 * CH;                          // rows per warp and step; the shard's columns
-    extern __shared__ __align__(16) unsigned char tp_smem[];
+__global__ void __launch_bounds__(128) tp_rms_direct_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d, const float * __restrict__ nw, float eps,
+                                                            uint16_t * __restrict__ h16, int Nfull, int n, unsigned long long * const * __restrict__ peers,
+                                                            int rank, int world, int cap, unsigned tag, int * status, unsigned long long wait_ns) {
+    constexpr int RPW = 32 / G, Ns = G * 8 * CH;
+    __shared__ unsigned number;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, h = lane & (G - 1), sub = lane / G;
-    float4 * const slots = reinterpret_cast<float4 *>(tp_smem) + (size_t)warp * 2 * CH * 64 + lane;        // [slot][chunk][half][lane]
-    const int g0 = (blockIdx.x * warps + warp) * RPW + sub, stride = gridDim.x * warps * RPW;             // this lane's rows: g0, g0 + stride, ..
-    const int first = (blockIdx.x * warps + warp) * RPW;
-    const int steps = first < n ? (n - first + stride - 1) / stride : 0;                                   // (warp-uniform)
+    if (threadIdx.x == 0) number = tp_take_number(peers[rank] + (size_t)2 * world * cap, tag);      // (the word after this rank's exchange words)
+    __syncthreads();
     const size_t slot0 = (size_t)(tag & 1u) * world * cap;
     unsigned long long * const mine = h < world ? peers[h] + slot0 + (size_t)rank * cap : nullptr;
     const unsigned long long * const from = h < world ? peers[rank] + slot0 + (size_t)h * cap : nullptr;
-    bool dead = false;
-    uint4 xv[CH], dv[CH];                                                // the row being loaded: requested a phase ahead of its use
-    auto request = [&](int k) {
-        const int t = g0 + k * stride;
-        const bool on = k < steps && t < n;
+    {                                                                    // one block = 4 RPW rows (the grid covers n)
+        const int first = ((int)number * 4 + warp) * RPW;                // (warp-uniform)
+        if (first >= n) return;
+        const int t = first + sub;
+        const bool on = t < n;
         const size_t at = (size_t)(on ? t : 0) * Ns + 8 * h;
+        uint4 xv[CH], dv[CH];
 #pragma unroll
         for (int q = 0; q < CH; q++) {
             xv[q] = on ? ld128(x + at + G * 8 * q) : make_uint4(0u, 0u, 0u, 0u);
             dv[q] = on && d ? ldg128(d + at + G * 8 * q) : make_uint4(0u, 0u, 0u, 0u);
         }
-    };
-    request(0);
-    for (int k = 0; k <= steps; k++) {
-        if (k < steps && !dead) {                                        // ---- step k: this shard's sum of squares of row t, sent to every rank
-            const int t = g0 + k * stride;
-            const bool on = t < n;
-            const size_t at = (size_t)(on ? t : 0) * Ns + 8 * h;
-            float a[2][8];
+        f32x2 xs[CH][4];
+        float a[2][8];
 #pragma unroll
-            for (int c = 0; c < 8; c++) a[0][c] = a[1][c] = 0.0f;
-            float4 * const sl = slots + (size_t)(k & 1) * CH * 64;
+        for (int c = 0; c < 8; c++) a[0][c] = a[1][c] = 0.0f;
 #pragma unroll
-            for (int q = 0; q < CH; q++) {
-                const uint32_t xw[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w}, dw[4] = {dv[q].x, dv[q].y, dv[q].z, dv[q].w};
-                f32x2 xs[4];
+        for (int q = 0; q < CH; q++) {
+            const uint32_t xw[4] = {xv[q].x, xv[q].y, xv[q].z, xv[q].w}, dw[4] = {dv[q].x, dv[q].y, dv[q].z, dv[q].w};
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const float2 xf = h2_to_f2(xw[c]);
-                    xs[c] = pk2(xf.x, xf.y);
-                    if (d) { const float2 df = h2_to_f2(dw[c]); xs[c] = add2(xs[c], pk2(df.x, df.y)); }
-                }
-                if (d && on) st128(x + at + G * 8 * q, make_uint4(f2_to_h2(lo2(xs[0]), hi2(xs[0])), f2_to_h2(lo2(xs[1]), hi2(xs[1])), f2_to_h2(lo2(xs[2]), hi2(xs[2])),
-                                                                  f2_to_h2(lo2(xs[3]), hi2(xs[3]))));
-                constexpr int NGq = G == 16 ? 2 : 1;
-                float (&ag)[8] = a[q % NGq];
-#pragma unroll
-                for (int c = 0; c < 4; c++) { ag[2 * c] = ffma(lo2(xs[c]), lo2(xs[c]), ag[2 * c]); ag[2 * c + 1] = ffma(hi2(xs[c]), hi2(xs[c]), ag[2 * c + 1]); }
-                sl[(2 * q) * 32] = make_float4(lo2(xs[0]), hi2(xs[0]), lo2(xs[1]), hi2(xs[1]));
-                sl[(2 * q + 1) * 32] = make_float4(lo2(xs[2]), hi2(xs[2]), lo2(xs[3]), hi2(xs[3]));
+            for (int c = 0; c < 4; c++) {
+                const float2 xf = h2_to_f2(xw[c]);
+                xs[q][c] = pk2(xf.x, xf.y);
+                if (d) { const float2 df = h2_to_f2(dw[c]); xs[q][c] = add2(xs[q][c], pk2(df.x, df.y)); }
             }
-            const float part = tp_row_total<G>(a, lane);                 // (the bits of cam_rms_partial_f16)
-            if (mine && on) st_sys_u64(mine + t, ((unsigned long long)tag << 32) | __float_as_uint(part));
-            request(k + 1);                                              // (in flight while the row of a step ago is normalised)
+            if (d && on) st128(x + at + G * 8 * q, make_uint4(f2_to_h2(lo2(xs[q][0]), hi2(xs[q][0])), f2_to_h2(lo2(xs[q][1]), hi2(xs[q][1])),
+                                                              f2_to_h2(lo2(xs[q][2]), hi2(xs[q][2])), f2_to_h2(lo2(xs[q][3]), hi2(xs[q][3]))));
+            constexpr int NGq = G == 16 ? 2 : 1;
+            float (&ag)[8] = a[q % NGq];
+#pragma unroll
+            for (int c = 0; c < 4; c++) { ag[2 * c] = ffma(lo2(xs[q][c]), lo2(xs[q][c]), ag[2 * c]); ag[2 * c + 1] = ffma(hi2(xs[q][c]), hi2(xs[q][c]), ag[2 * c + 1]); }
         }
-        if (k >= 1 && !dead) {                                           // ---- the row of a step ago: gather the partials, normalise, store
-            const int t = g0 + (k - 1) * stride;
-            const bool on = t < n;
-            float part = 0.0f;
-            bool late = false;
-            if (from && on) {
+        const float own = tp_row_total<G>(a, lane);                      // (the bits of cam_rms_partial_f16)
+        if (mine && on) st_sys_u64(mine + t, ((unsigned long long)tag << 32) | __float_as_uint(own));
+        float part = 0.0f;
+        bool late = false;
+        if (from && on) {
+            if (h == rank) part = own;                                   // (this rank's own partial needs no trip through memory)
+            else {
                 unsigned long long w = ld_sys_u64(from + t);
                 if ((unsigned)(w >> 32) != tag) {
                     const unsigned long long start = global_ns();
@@ -351,42 +351,33 @@ __global__ void __launch_bounds__(256, 2) tp_rms_lean_kernel(uint16_t * __restri
                 }
                 part = __uint_as_float((unsigned)w);
             }
-            if (__any_sync(CAM_FULL, late)) {                            // a source never arrived: report, take no more rows
-                if (lane == 0) atomicOr(status, 1);
-                dead = true;
-                continue;
-            }
-            float tot = 0.0f;
-            for (int r = 0; r < world; r++) tot = fadd(tot, __shfl_sync(CAM_FULL, part, r, G));
-            const float scale = cam_rsqrt(fadd(fdiv(tot, (float)Nfull), eps));
-            const f32x2 s2 = pk2(scale, scale);
-            const float4 * const sl = slots + (size_t)((k - 1) & 1) * CH * 64;
-            const size_t at = (size_t)(on ? t : 0) * Ns + 8 * h;
+        }
+        if (__any_sync(CAM_FULL, late)) {                                // a source never arrived: report, take no more rows
+            if (lane == 0) atomicOr(status, 1);
+            return;
+        }
+        float tot = 0.0f;
+        for (int r = 0; r < world; r++) tot = fadd(tot, __shfl_sync(CAM_FULL, part, r, G));
+        const float scale = cam_rsqrt(fadd(fdiv(tot, (float)Nfull), eps));
+        const f32x2 s2 = pk2(scale, scale);
 #pragma unroll
-            for (int q = 0; q < CH; q++) {
-                const float4 lo = sl[(2 * q) * 32], hi = sl[(2 * q + 1) * 32];
-                const float4 w0 = __ldg(reinterpret_cast<const float4 *>(nw + 8 * h + G * 8 * q)), w1 = __ldg(reinterpret_cast<const float4 *>(nw + 8 * h + G * 8 * q + 4));
-                const f32x2 v0 = mul2(mul2(pk2(lo.x, lo.y), s2), pk2(w0.x, w0.y)), v1 = mul2(mul2(pk2(lo.z, lo.w), s2), pk2(w0.z, w0.w));
-                const f32x2 v2 = mul2(mul2(pk2(hi.x, hi.y), s2), pk2(w1.x, w1.y)), v3 = mul2(mul2(pk2(hi.z, hi.w), s2), pk2(w1.z, w1.w));
-                if (on) st128_stream(h16 + at + G * 8 * q, make_uint4(f2_to_h2(lo2(v0), hi2(v0)), f2_to_h2(lo2(v1), hi2(v1)), f2_to_h2(lo2(v2), hi2(v2)), f2_to_h2(lo2(v3), hi2(v3))));
-            }
+        for (int q = 0; q < CH; q++) {
+            const float4 w0 = __ldg(reinterpret_cast<const float4 *>(nw + 8 * h + G * 8 * q)), w1 = __ldg(reinterpret_cast<const float4 *>(nw + 8 * h + G * 8 * q + 4));
+            const f32x2 v0 = mul2(mul2(xs[q][0], s2), pk2(w0.x, w0.y)), v1 = mul2(mul2(xs[q][1], s2), pk2(w0.z, w0.w));
+            const f32x2 v2 = mul2(mul2(xs[q][2], s2), pk2(w1.x, w1.y)), v3 = mul2(mul2(xs[q][3], s2), pk2(w1.z, w1.w));
+            if (on) st128_stream(h16 + at + G * 8 * q, make_uint4(f2_to_h2(lo2(v0), hi2(v0)), f2_to_h2(lo2(v1), hi2(v1)), f2_to_h2(lo2(v2), hi2(v2)), f2_to_h2(lo2(v3), hi2(v3))));
         }
     }
 }
 
 template <int G, int CH>
-int launch_tp_lean(int n, void * x, const void * d, const float * nw, float eps, void * h16, int Nfull, const void * peers, int rank, int world, int cap,
-                   unsigned tag, int * status, unsigned long long wait_ns, cudaStream_t stream) {
-    static unsigned long long allowed = 0;
-    const cudaError_t e = cam_allow_smem(tp_rms_lean_kernel<G, CH>, 227 * 1024, allowed);
-    if (e != cudaSuccess) return (int)e;
-    int warps = 8;
-    if (const char * ev = getenv("CAMINUS_B200_TP_WARPS")) { const int v = atoi(ev); if (v >= 1 && v <= 8) warps = v; }      // (tuning)
-    const size_t smem = (size_t)warps * 2 * CH * 64 * 16;
-    const int rpb = warps * (32 / G);
-    const int grid = cam_resident_grid(tp_rms_lean_kernel<G, CH>, warps * 32, smem, ((long)n + rpb - 1) / rpb);
-    tp_rms_lean_kernel<G, CH><<<grid, warps * 32, smem, stream>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Nfull, n,
-                                                                 (unsigned long long * const *)peers, rank, world, cap, tag, status, warps, wait_ns);
+int launch_tp_direct(int n, void * x, const void * d, const float * nw, float eps, void * h16, int Nfull, const void * peers, int rank, int world, int cap,
+                     unsigned tag, int * status, unsigned long long wait_ns, cudaStream_t stream) {
+    const int rpb = 4 * (32 / G);
+    // a block per 4 or 8 rows, so more blocks than are resident: 56.0 us against 63.8 us for resident blocks that loop (65536 rows of 640, one rank)
+    const int grid = (n + rpb - 1) / rpb;
+    tp_rms_direct_kernel<G, CH><<<grid, 128, 0, stream>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Nfull, n,
+                                                          (unsigned long long * const *)peers, rank, world, cap, tag, status, wait_ns);
     return (int)cudaGetLastError();
 }
 
@@ -404,9 +395,10 @@ int launch_tp_staged(int warps, size_t smem, int n, void * x, const void * d, co
 
 }   // namespace
 
-// cam_tp_rms_words: 64-bit words of one rank's exchange buffer for up to cap rows per call (the caller allocates them zeroed)
+// cam_tp_rms_words: 64-bit words of one rank's exchange buffer for up to cap rows per call (the caller allocates them zeroed):
+// [2 parities][world sources][cap rows] and 8 words of the library's own
 extern "C" int cam_tp_rms_words(int cap, int world) {
-    const long w = 2L * world * cap;
+    const long w = 2L * world * cap + 8;             // (+ 8: the word after the exchange words counts a call's started blocks)
     return cap < 1 || world < 1 || world > 32 || w > 0x7fffffffL ? CAM_ERR_ARG : (int)w;
 }
 
@@ -431,23 +423,19 @@ extern "C" int cam_tp_rms_norm_f16(int n, void * x, const void * d, const float 
     cudaStream_t st = (cudaStream_t)stream;
     unsigned long long wait_ns = CAM_TP_WAIT_NS;    // CAMINUS_B200_TP_WAIT_MS: the limit of a wait in milliseconds (1 .. 600000)
     if (const char * e = getenv("CAMINUS_B200_TP_WAIT_MS")) { const long ms = atol(e); if (ms >= 1 && ms <= 600000) wait_ns = (unsigned long long)ms * 1000000ull; }
-    // The lean kernel requests the next rows' loads before it normalises the previous rows (126 registers; on one rank the same 63 us as
-    // without: 65536 rows of 640 columns). Measured around it and not kept: the rows read a second time from the second-level cache instead of parked in
-    // shared memory, one or two rows per lane group and step (67.8 / 72.7 us); the partials' words asked for a phase early (64.4 us);
-    // blocks of 6 or 4 warps (64.4 / 76.4 us).
-    if (world <= 16 && !getenv("CAMINUS_B200_TP_CFG")) {                // the usual shards: the lean kernel (a row on 16 or 32 lanes, chunks counted at compile time)
-#define CAM_TP_LEAN(GV, CHV) return launch_tp_lean<GV, CHV>(n, x, d, nw, eps, h16, Nfull, peers, rank, world, cap, tag, status, wait_ns, st);
+    if (world <= 16 && !getenv("CAMINUS_B200_TP_CFG")) {                // the usual shards: rows in registers (a row on 16 or 32 lanes, chunks counted at compile time)
+#define CAM_TP_DIRECT(GV, CHV) return launch_tp_direct<GV, CHV>(n, x, d, nw, eps, h16, Nfull, peers, rank, world, cap, tag, status, wait_ns, st);
         switch (Ns) {
-            case 512: CAM_TP_LEAN(16, 4) case 640: CAM_TP_LEAN(16, 5) case 1024: CAM_TP_LEAN(32, 4) case 1280: CAM_TP_LEAN(32, 5)
+            case 512: CAM_TP_DIRECT(16, 4) case 640: CAM_TP_DIRECT(16, 5) case 1024: CAM_TP_DIRECT(32, 4) case 1280: CAM_TP_DIRECT(32, 5)
+            case 2048: CAM_TP_DIRECT(32, 8) case 2560: CAM_TP_DIRECT(32, 10)
             default: break;
         }
-#undef CAM_TP_LEAN
+#undef CAM_TP_DIRECT
     }
-    // Rows staged in shared memory. (Tried and not kept: rows converted once and held in fp32 registers, a half-warp per row of a 640-column
-    // shard: 200 instructions per row instead of 575, but 16 warps of 128 registers per multiprocessor hold too few rows in flight to
-    // cover the load and the exchange: 73.5 us against 67.4 us for 65536 rows on one rank.) Measured on B200 (T = 65536, shards of 640 / 1280 / 2560 columns): resident warps matter more than
-    // rows in flight per warp: two slots per warp (one row waiting for its partials while the next is loaded and reduced) where
-    // that still leaves 20 warps per multiprocessor, else one slot. CAMINUS_B200_TP_CFG="slots,warps" overrides (tuning).
+    // Other shard widths: rows staged in shared memory on resident blocks that loop. Measured on B200 (T = 65536, shards of 640 / 1280 / 2560
+    // columns, before the kernel above took those): resident warps matter more than rows in flight per warp: two slots per warp (one row
+    // waiting for its partials while the next is loaded and reduced) where that still leaves 20 warps per multiprocessor, else one slot.
+    // CAMINUS_B200_TP_CFG="slots,warps" overrides (tuning, and it keeps the usual shards on this kernel too).
     {
         const size_t row_bytes = (size_t)(d ? 2 : 1) * ((Ns + 255) >> 8) * 512, budget = 224 * 1024;
         int slots = 2 * 20 * row_bytes <= budget ? 2 : 1, warps = 8;
