@@ -730,8 +730,8 @@ bool launch_actq_wide(Src src, bool aligned, int M, uint16_t * y, float * s, int
 #define CAM_AQ_WIDE(STV, WPRV, WANT, SMV) do { \
         const bool sm = force ? force[0] == '1' : (SMV || (Src::kHeavy && STV > 1)); \
         const size_t pro = Src::kPrologue ? (size_t)8 * STV * 1024 : 0;      /* (a prologue's staged row: STV * 512 bf16 per warp) */ \
-        if (sm) actq_wide_kernel<Src, STV, WPRV, true><<<cam_resident_grid(actq_wide_kernel<Src, STV, WPRV, true>, 256, 8 * STV * 1024 + pro, WANT), 256, 8 * STV * 1024 + pro, stream>>>(src, y, s, K, clip, qmax, codes, M); \
-        else actq_wide_kernel<Src, STV, WPRV, false><<<cam_resident_grid(actq_wide_kernel<Src, STV, WPRV, false>, 256, pro, WANT), 256, pro, stream>>>(src, y, s, K, clip, qmax, codes, M); } while (0)
+        if (sm) actq_wide_kernel<Src, STV, WPRV, true><<<cam_resident_grid(actq_wide_kernel<Src, STV, WPRV, true>, 256, 8 * STV * 1024 + pro, WANT, Src::kPrologue ? 8 : 1), 256, 8 * STV * 1024 + pro, stream>>>(src, y, s, K, clip, qmax, codes, M); \
+        else actq_wide_kernel<Src, STV, WPRV, false><<<cam_resident_grid(actq_wide_kernel<Src, STV, WPRV, false>, 256, pro, WANT, Src::kPrologue ? 8 : 1), 256, pro, stream>>>(src, y, s, K, clip, qmax, codes, M); } while (0)
     if (K <= 512) CAM_AQ_WIDE(1, 1, want8, false);
     else if (K <= 1024) CAM_AQ_WIDE(2, 1, want8, false);
     else if (K <= 2048) CAM_AQ_WIDE(4, 1, want8, true);

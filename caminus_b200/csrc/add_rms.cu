@@ -299,7 +299,8 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) rms_rows_vec_kernel(float * x,
 template <int CH, bool POST, bool Q8 = false>
 int launch_rows_vec(float * x, const float * w, float * y, uint16_t * ybf, float * scl, int R, int wr, float eps, const float * b, const float * inj,
                     int HC, float rs, cudaStream_t stream, uint8_t * yq = nullptr) {
-    const int grid = cam_resident_grid(rms_rows_vec_kernel<CH, POST, Q8>, RMS_WARPS * 32, 0, ((long)R + RMS_WARPS - 1) / RMS_WARPS);
+    // (8 x the resident blocks: pf_rms_mul 0.86 -> 0.94, rmsnorm_f32 0.86 -> 0.955, the Q8_1 form 0.84 -> 0.87; the hyper-connection form ran the same or slower with them)
+    const int grid = cam_resident_grid(rms_rows_vec_kernel<CH, POST, Q8>, RMS_WARPS * 32, 0, ((long)R + RMS_WARPS - 1) / RMS_WARPS, POST ? 1 : 8);
     rms_rows_vec_kernel<CH, POST, Q8><<<grid, RMS_WARPS * 32, 0, stream>>>(x, w, y, ybf, scl, R, wr, eps, b, inj, HC, rs, yq);
     return (int)cudaGetLastError();
 }
@@ -525,6 +526,95 @@ __global__ void __launch_bounds__(128, 2) add_rms_f16_reg_kernel(uint16_t * __re
     }
 }
 
+// Rows too long for one warp's registers (N = 256 CHW WPR, WPR = 2 or 4 warps per row): warp w of a row's group holds chunks
+// w CHW .. (w + 1) CHW - 1 in registers. The reference's sum is one fma chain per thread over the whole row, so the 8 accumulators of a
+// lane pass from warp to warp through shared memory (WPR short steps, a block barrier after each); the last warp forms the total and the
+// scale, every warp normalises its part from registers. Nothing is read twice, in HBM or in the second-level cache, for rows of up to
+// 20480 values (the staged kernel holds 2 to 4 warps per multiprocessor on rows of 6144 to 8192: 0.30-0.58 of the copy bandwidth; the
+// two-pass kernel: 0.62-0.66).
+template <int CHW, int WPR>
+__global__ void __launch_bounds__(128, 2) add_rms_f16_reg_multi_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d,
+                                                                       const float * __restrict__ nw, float eps, uint16_t * __restrict__ h16, int n) {
+    constexpr int N = 256 * CHW * WPR, RPB = 4 / WPR;                    // rows per block and pass
+    extern __shared__ __align__(16) float multi_smem[];
+    float * const snw = multi_smem;                                      // [N] weights
+    float * const acc = snw + N;                                         // [RPB][8][32]: a row's accumulators in flight between its warps
+    float * const scl = acc + RPB * 256;                                 // [RPB]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, grp = warp / WPR, part = warp % WPR;
+    for (int i = threadIdx.x * 4; i < N; i += 512) *reinterpret_cast<float4 *>(snw + i) = __ldg(reinterpret_cast<const float4 *>(nw + i));
+    __syncthreads();
+    for (int t0 = blockIdx.x * RPB; t0 < n; t0 += gridDim.x * RPB) {     // (block-uniform: every warp takes part in the barriers)
+        const int t = t0 + grp;
+        const bool on = t < n;
+        const size_t at = (size_t)(on ? t : 0) * N + part * (256 * CHW) + 8 * lane;
+        uint4 rx[CHW], rd[CHW];
+#pragma unroll
+        for (int m = 0; m < CHW; m++) rx[m] = on ? ld128(x + at + 256 * m) : make_uint4(0u, 0u, 0u, 0u);
+        if (d) {
+#pragma unroll
+            for (int m = 0; m < CHW; m++) rd[m] = on ? ldg128(d + at + 256 * m) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        float xs[CHW][8];
+#pragma unroll
+        for (int m = 0; m < CHW; m++) {
+            load8(rx[m], xs[m]);
+            if (d) {
+                float dv[8];
+                load8(rd[m], dv);
+#pragma unroll
+                for (int c = 0; c < 8; c++) xs[m][c] = fadd(xs[m][c], dv[c]);
+                if (on) st128(x + at + 256 * m, make_uint4(f2_to_h2(xs[m][0], xs[m][1]), f2_to_h2(xs[m][2], xs[m][3]), f2_to_h2(xs[m][4], xs[m][5]),
+                                                           f2_to_h2(xs[m][6], xs[m][7])));
+            }
+        }
+        float * const ga = acc + grp * 256 + lane;                      // + 32 c: accumulator c of this lane
+#pragma unroll
+        for (int w = 0; w < WPR; w++) {                                  // the chain: warp w continues where warp w - 1 stopped
+            if (part == w) {
+                float a[8];
+#pragma unroll
+                for (int c = 0; c < 8; c++) a[c] = w ? ga[32 * c] : 0.0f;
+#pragma unroll
+                for (int m = 0; m < CHW; m++)
+#pragma unroll
+                    for (int c = 0; c < 8; c++) a[c] = ffma(xs[m][c], xs[m][c], a[c]);
+                if (w < WPR - 1) {
+#pragma unroll
+                    for (int c = 0; c < 8; c++) ga[32 * c] = a[c];
+                } else {
+                    const float tot = ref_total_f16(a, lane);
+                    if (lane == 0) scl[grp] = cam_rsqrt(fadd(fdiv(tot, (float)N), eps));
+                }
+            }
+            __syncthreads();
+        }
+        const float scale = scl[grp];
+#pragma unroll
+        for (int m = 0; m < CHW; m++) {
+            const float * wp = snw + part * (256 * CHW) + 8 * lane + 256 * m;
+            const float4 w0 = *reinterpret_cast<const float4 *>(wp), w1 = *reinterpret_cast<const float4 *>(wp + 4);
+            const float v0 = fmul(fmul(xs[m][0], scale), w0.x), v1 = fmul(fmul(xs[m][1], scale), w0.y);
+            const float v2 = fmul(fmul(xs[m][2], scale), w0.z), v3 = fmul(fmul(xs[m][3], scale), w0.w);
+            const float v4 = fmul(fmul(xs[m][4], scale), w1.x), v5 = fmul(fmul(xs[m][5], scale), w1.y);
+            const float v6 = fmul(fmul(xs[m][6], scale), w1.z), v7 = fmul(fmul(xs[m][7], scale), w1.w);
+            if (on) st128_stream(h16 + at + 256 * m, make_uint4(f2_to_h2(v0, v1), f2_to_h2(v2, v3), f2_to_h2(v4, v5), f2_to_h2(v6, v7)));
+        }
+        __syncthreads();                                                 // (scl and acc are rewritten by the next pass)
+    }
+}
+
+template <int CHW, int WPR>
+int launch_f16_reg_multi(uint16_t * x, const uint16_t * d, const float * nw, float eps, uint16_t * h16, int n, cudaStream_t stream) {
+    constexpr int N = 256 * CHW * WPR, RPB = 4 / WPR;
+    const size_t smem = ((size_t)N + RPB * 256 + 8) * sizeof(float);
+    static unsigned long long allowed = 0;
+    if (smem > 48 * 1024) { const cudaError_t e = cam_allow_smem(add_rms_f16_reg_multi_kernel<CHW, WPR>, smem, allowed); if (e != cudaSuccess) return (int)e; }
+    const long want = ((long)n + RPB - 1) / RPB;
+    const int grid = cam_resident_grid(add_rms_f16_reg_multi_kernel<CHW, WPR>, 128, smem, want, 8);
+    add_rms_f16_reg_multi_kernel<CHW, WPR><<<grid, 128, smem, stream>>>(x, d, nw, eps, h16, n);
+    return (int)cudaGetLastError();
+}
+
 template <int CH>
 int launch_f16_reg(uint16_t * x, const uint16_t * d, const float * nw, float eps, uint16_t * h16, int n, cudaStream_t stream) {
     // eight times the resident blocks (or a block per four rows, if fewer): a finished block's successor starts with its rows' loads
@@ -570,7 +660,7 @@ int launch_f32(float * x, const float * d, const float * w, int S, const float *
     const long want = ((long)n + RMS_WARPS - 1) / RMS_WARPS;
 #define CAM_RMS_CASE(CHV)                                                                                              \
     case CHV:                                                                                                          \
-        add_rms_f32_kernel<CHV><<<cam_resident_grid(add_rms_f32_kernel<CHV>, RMS_WARPS * 32, 0, want), RMS_WARPS * 32, 0, stream>>>( \
+        add_rms_f32_kernel<CHV><<<cam_resident_grid(add_rms_f32_kernel<CHV>, RMS_WARPS * 32, 0, want, 8), RMS_WARPS * 32, 0, stream>>>(      /* (8 x resident: 65536 rows of 2048 0.91 -> 0.995) */ \
             x, d, w, S, nw, eps, h, h16, N, n, q35);                                                                   \
         break;
     switch (N <= 2048 ? N >> 7 : 0) {
@@ -616,11 +706,17 @@ extern "C" int cam_add_rms_f16(int n, void * x, const void * d, const float * nw
             case 768: return launch_f16_reg<3>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
             case 1280: return launch_f16_reg<5>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
             case 1536: return launch_f16_reg<6>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
+            case 3072: return launch_f16_reg<12>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
+            case 3584: return launch_f16_reg<14>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
             case 1024: return launch_f16_reg<4>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
             case 2048: return launch_f16_reg<8>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
             case 2560: return launch_f16_reg<10>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
             case 4096: return launch_f16_reg<16>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
             case 5120: return launch_f16_reg<20>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
+#define CAM_REG_MULTI(CHWV, WPRV) return launch_f16_reg_multi<CHWV, WPRV>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, n, (cudaStream_t)stream);
+            case 6144: CAM_REG_MULTI(12, 2) case 7168: CAM_REG_MULTI(14, 2) case 8192: CAM_REG_MULTI(16, 2) case 10240: CAM_REG_MULTI(20, 2)
+            case 12288: CAM_REG_MULTI(12, 4) case 14336: CAM_REG_MULTI(14, 4) case 16384: CAM_REG_MULTI(16, 4) case 20480: CAM_REG_MULTI(20, 4)
+#undef CAM_REG_MULTI
             default: break;
         }
     }

@@ -321,7 +321,7 @@ extern "C" int cam_emb_rows_q6k(int n, const void * W, int rb, int vocab, const 
     if (n < 0 || vocab < 1 || N < 256 || (N & 255) || rb < N / 256 * 210 || !W || !toks || !x) return CAM_ERR_ARG;
     if ((reinterpret_cast<uintptr_t>(W) & 1u) || (rb & 1) || !cam_aligned16(x)) return CAM_ERR_ALIGN;
     if (n == 0) return CAM_OK;
-    emb_rows_q6k_kernel<<<cam_resident_grid(emb_rows_q6k_kernel, 256, 0, n), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)W, rb, vocab, toks, x, n, N);
+    emb_rows_q6k_kernel<<<cam_resident_grid(emb_rows_q6k_kernel, 256, 0, n, 8), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)W, rb, vocab, toks, x, n, N);
     return (int)cudaGetLastError();
 }
 

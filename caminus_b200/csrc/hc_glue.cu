@@ -551,7 +551,7 @@ extern "C" int pf_hc_post_rms(const float * b, const float * inj, float * res, c
 extern "C" int pf_hc_post(const float * b, const float * inj, float * res, int T, int HC, int D, float rs, void * stream) {
     if (T < 0 || HC < 1 || D < 1 || !b || !inj || !res) return CAM_ERR_ARG;
     if (T == 0) return CAM_OK;
-    if (!(D & 3) && cam_aligned16(b) && cam_aligned16(res)) hc_post_vec_kernel<<<cam_resident_grid(hc_post_vec_kernel, 256, 0, T), 256, 0, CAM_STREAM>>>(b, inj, res, T, HC, D, rs);
+    if (!(D & 3) && cam_aligned16(b) && cam_aligned16(res)) hc_post_vec_kernel<<<cam_resident_grid(hc_post_vec_kernel, 256, 0, T, 8), 256, 0, CAM_STREAM>>>(b, inj, res, T, HC, D, rs);
     else hc_post_kernel<<<grid_for((long)T * D), 256, 0, CAM_STREAM>>>(b, inj, res, T, HC, D, rs);
     return (int)cudaGetLastError();
 }
@@ -571,7 +571,7 @@ extern "C" int pf_add_sum(const float * a, const float * b, float * y, long n, v
     if (n < 0 || !a || !b || !y) return CAM_ERR_ARG;
     if (n == 0) return CAM_OK;
     if (n >= 4 && cam_aligned16(a) && cam_aligned16(b) && cam_aligned16(y))
-        ew_vec_kernel<EW_ADD_SUM><<<cam_resident_grid(ew_vec_kernel<EW_ADD_SUM>, 256, 0, ((n >> 2) + 511) / 512), 256, 0, CAM_STREAM>>>(a, b, nullptr, y, n);
+        ew_vec_kernel<EW_ADD_SUM><<<cam_resident_grid(ew_vec_kernel<EW_ADD_SUM>, 256, 0, ((n >> 2) + 511) / 512, 8), 256, 0, CAM_STREAM>>>(a, b, nullptr, y, n);
     else ew_kernel<EW_ADD_SUM><<<grid_for(n), 256, 0, CAM_STREAM>>>(a, b, nullptr, y, n);
     return (int)cudaGetLastError();
 }
@@ -580,7 +580,7 @@ extern "C" int pf_swiglu(const float * g, const float * u, float * y, long n, vo
     if (n < 0 || !g || !u || !y) return CAM_ERR_ARG;
     if (n == 0) return CAM_OK;
     if (n >= 4 && cam_aligned16(g) && cam_aligned16(u) && cam_aligned16(y))
-        ew_vec_kernel<EW_SWIGLU><<<cam_resident_grid(ew_vec_kernel<EW_SWIGLU>, 256, 0, ((n >> 2) + 511) / 512), 256, 0, CAM_STREAM>>>(g, u, nullptr, y, n);
+        ew_vec_kernel<EW_SWIGLU><<<cam_resident_grid(ew_vec_kernel<EW_SWIGLU>, 256, 0, ((n >> 2) + 511) / 512, 8), 256, 0, CAM_STREAM>>>(g, u, nullptr, y, n);
     else ew_kernel<EW_SWIGLU><<<grid_for(n), 256, 0, CAM_STREAM>>>(g, u, nullptr, y, n);
     return (int)cudaGetLastError();
 }
@@ -590,7 +590,7 @@ extern "C" int pf_silu_bf16(const float * x, int ldx, void * y, int T, int Tpad,
     if (Tpad == 0) return CAM_OK;
     if (!(K & 3) && !(ldx & 3) && (long)Tpad * (K >> 2) < 0x7fffffffL && cam_aligned16(x) && !(reinterpret_cast<uintptr_t>(y) & 7u)) {
         const unsigned K4 = (unsigned)(K >> 2), live = (unsigned)T * K4, all = (unsigned)Tpad * K4;
-        to_bf16_vec_kernel<true><<<cam_resident_grid(to_bf16_vec_kernel<true>, 256, 0, ((long)all + 511) / 512), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, live, all, K4, rs);
+        to_bf16_vec_kernel<true><<<cam_resident_grid(to_bf16_vec_kernel<true>, 256, 0, ((long)all + 511) / 512, 8), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, live, all, K4, rs);
     } else to_bf16_kernel<true><<<cam_resident_grid(to_bf16_kernel<true>, 256, 0, Tpad), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, T, Tpad, K, rs);
     return (int)cudaGetLastError();
 }
@@ -599,7 +599,7 @@ extern "C" int pf_to_bf16(const float * x, int ldx, void * y, int T, int Tpad, i
     if (Tpad == 0) return CAM_OK;
     if (!(K & 3) && !(ldx & 3) && (long)Tpad * (K >> 2) < 0x7fffffffL && cam_aligned16(x) && !(reinterpret_cast<uintptr_t>(y) & 7u)) {
         const unsigned K4 = (unsigned)(K >> 2), live = (unsigned)T * K4, all = (unsigned)Tpad * K4;
-        to_bf16_vec_kernel<false><<<cam_resident_grid(to_bf16_vec_kernel<false>, 256, 0, ((long)all + 511) / 512), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, live, all, K4, 0.0f);
+        to_bf16_vec_kernel<false><<<cam_resident_grid(to_bf16_vec_kernel<false>, 256, 0, ((long)all + 511) / 512, 8), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, live, all, K4, 0.0f);
     } else to_bf16_kernel<false><<<cam_resident_grid(to_bf16_kernel<false>, 256, 0, Tpad), 256, 0, CAM_STREAM>>>(x, ldx, (uint16_t *)y, T, Tpad, K, 0.0f);
     return (int)cudaGetLastError();
 }
@@ -643,7 +643,7 @@ extern "C" int silu_mul_bf16(const void * gu, void * act, int H, long n, void * 
     const long rows = n / H;
     if (!(H & 7) && rows > 0 && rows * (H >> 3) < 0x7fffffffL && cam_aligned16(gu) && cam_aligned16(act)) {     // whole rows by vectors, a last partial row by elements
         const unsigned items = (unsigned)(rows * (H >> 3));
-        silu_mul_bf16_vec_kernel<<<cam_resident_grid(silu_mul_bf16_vec_kernel, 256, 0, (items + 255) / 256), 256, 0, CAM_STREAM>>>((const uint16_t *)gu, (uint16_t *)act,
+        silu_mul_bf16_vec_kernel<<<cam_resident_grid(silu_mul_bf16_vec_kernel, 256, 0, (items + 255) / 256, 8), 256, 0, CAM_STREAM>>>((const uint16_t *)gu, (uint16_t *)act,
                                                                                                                         (unsigned)(H >> 3), items);
         const long rest = n - rows * H;
         if (rest) silu_mul_bf16_kernel<<<grid_for(rest), 256, 0, CAM_STREAM>>>((const uint16_t *)gu + rows * 2 * H, (uint16_t *)act + rows * H, H, rest);
@@ -654,7 +654,7 @@ extern "C" int residual3(const float * x, const void * m, const void * y, float 
     if (n < 0 || !x || !m || !y || !out) return CAM_ERR_ARG;
     if (n == 0) return CAM_OK;
     if (n >= 4 && cam_aligned16(x) && cam_aligned16(out) && !(reinterpret_cast<uintptr_t>(m) & 7u) && !(reinterpret_cast<uintptr_t>(y) & 7u))
-        ew_vec_kernel<EW_RESIDUAL3><<<cam_resident_grid(ew_vec_kernel<EW_RESIDUAL3>, 256, 0, ((n >> 2) + 511) / 512), 256, 0, CAM_STREAM>>>(x, m, y, out, n);
+        ew_vec_kernel<EW_RESIDUAL3><<<cam_resident_grid(ew_vec_kernel<EW_RESIDUAL3>, 256, 0, ((n >> 2) + 511) / 512, 8), 256, 0, CAM_STREAM>>>(x, m, y, out, n);
     else ew_kernel<EW_RESIDUAL3><<<grid_for(n), 256, 0, CAM_STREAM>>>(x, m, y, out, n);
     return (int)cudaGetLastError();
 }
@@ -662,7 +662,7 @@ extern "C" int cast_bf16(const float * x, void * out, long n, void * stream) {
     if (n < 0 || !x || !out) return CAM_ERR_ARG;
     if (n == 0) return CAM_OK;
     if (n >= 4 && cam_aligned16(x) && !(reinterpret_cast<uintptr_t>(out) & 7u))
-        ew_vec_kernel<EW_CAST_BF16><<<cam_resident_grid(ew_vec_kernel<EW_CAST_BF16>, 256, 0, ((n >> 2) + 511) / 512), 256, 0, CAM_STREAM>>>(x, nullptr, nullptr, out, n);
+        ew_vec_kernel<EW_CAST_BF16><<<cam_resident_grid(ew_vec_kernel<EW_CAST_BF16>, 256, 0, ((n >> 2) + 511) / 512, 8), 256, 0, CAM_STREAM>>>(x, nullptr, nullptr, out, n);
     else ew_kernel<EW_CAST_BF16><<<grid_for(n), 256, 0, CAM_STREAM>>>(x, nullptr, nullptr, out, n);
     return (int)cudaGetLastError();
 }

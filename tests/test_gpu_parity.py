@@ -108,7 +108,10 @@ def test_add_rms16_q35(N, add):
     with pytest.raises(ValueError): Q.add_rms16(x, cu(nw), 1e-6, h16, n, N)          # h is required (q35own.py:139)
 
 
-@pytest.mark.parametrize('T,N', [(1, 2048), (5, 256), (777, 5120), (4096, 5120), (64, 8192), (3, 28672)])
+@pytest.mark.parametrize('T,N', [(1, 2048), (5, 256), (777, 5120), (4096, 5120), (64, 8192), (3, 28672),
+                                 (70, 512), (99, 768), (130, 1280), (65, 1536), (77, 3072), (66, 3584),       # rows held in one warp's registers
+                                 (71, 6144), (67, 7168), (90, 8192), (65, 10240), (64, 12288), (69, 14336), (66, 16384), (65, 20480),   # in two or four warps'
+                                 (63, 8192), (200, 3328)])                                                      # few rows / another length: the staged kernel
 @pytest.mark.parametrize('add', [True, False])
 def test_add_rms_f16(T, N, add):
     x0, r0, w = synth.add_rms_inputs(T, N, seed=T, dtype=np.float16)
