@@ -617,11 +617,11 @@ int launch_f16_reg_multi(uint16_t * x, const uint16_t * d, const float * nw, flo
 
 template <int CH>
 int launch_f16_reg(uint16_t * x, const uint16_t * d, const float * nw, float eps, uint16_t * h16, int n, cudaStream_t stream) {
-    // eight times the resident blocks (or a block per four rows, if fewer): a finished block's successor starts with its rows' loads
-    // at once, which measured 424 us against 437 us for exactly the resident blocks looping over rows (65536 rows of 5120)
+    // about two passes of four rows per block (at least the resident blocks): a finished block's successor starts with its rows' loads at
+    // once. 65536 rows of 5120: 412 us, against 423 us with 8 x the resident blocks, 426 us with a block per four rows and 437 us with
+    // exactly the resident blocks looping over the rows
     const long want = ((long)n + 3) / 4;
-    const long cap = 8L * cam_resident_grid(add_rms_f16_reg_kernel<CH>, 128, 0, want);
-    const int grid = (int)(want < cap ? want : cap);
+    const int grid = cam_iter_grid(add_rms_f16_reg_kernel<CH>, 128, 0, want, 2);
     add_rms_f16_reg_kernel<CH><<<grid, 128, 0, stream>>>(x, d, nw, eps, h16, n);
     return (int)cudaGetLastError();
 }
@@ -660,7 +660,7 @@ int launch_f32(float * x, const float * d, const float * w, int S, const float *
     const long want = ((long)n + RMS_WARPS - 1) / RMS_WARPS;
 #define CAM_RMS_CASE(CHV)                                                                                              \
     case CHV:                                                                                                          \
-        add_rms_f32_kernel<CHV><<<cam_resident_grid(add_rms_f32_kernel<CHV>, RMS_WARPS * 32, 0, want, 8), RMS_WARPS * 32, 0, stream>>>(      /* (8 x resident: 65536 rows of 2048 0.91 -> 0.995) */ \
+        add_rms_f32_kernel<CHV><<<cam_iter_grid(add_rms_f32_kernel<CHV>, RMS_WARPS * 32, 0, want, 1), RMS_WARPS * 32, 0, stream>>>(      /* (a block per unit: 65536 rows of 2048 408 -> 360 us, 0.91 -> 1.03) */ \
             x, d, w, S, nw, eps, h, h16, N, n, q35);                                                                   \
         break;
     switch (N <= 2048 ? N >> 7 : 0) {

@@ -270,6 +270,17 @@ static inline int cam_resident_grid(K kernel, int threads, size_t smem, long wan
     return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
 }
 
+// A grid of looping blocks sized by the work per block: each block gets about `iters` units (at least the resident blocks, at most
+// one block per unit). The SwiGLU + Q8_1 kernels run fastest at 7 to 8 units per block whatever the batch (65536 x 25600 values:
+// 1229 us, against 1268 us with 8 x the resident blocks, 1289 us with a block per unit and 1309 us with the resident blocks alone).
+template <typename K>
+static inline int cam_iter_grid(K kernel, int threads, size_t smem, long want, int iters) {
+    const long resident = cam_resident_grid(kernel, threads, smem, want);
+    const long by_iters = (want + iters - 1) / iters;
+    const long g = by_iters > resident ? by_iters : resident;
+    return (int)(g > 0x7fffffffL ? 0x7fffffffL : g);
+}
+
 // One-time, per device: a kernel's opt-in to more dynamic shared memory than the default limit. `done` is the caller's static word,
 // one bit per device ordinal: after the first launch on a device the attribute call (a driver call) is skipped.
 template <typename Kn> static inline cudaError_t cam_allow_smem(Kn kernel, size_t bytes, unsigned long long & done) {

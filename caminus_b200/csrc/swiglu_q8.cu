@@ -350,11 +350,11 @@ int launch_q8(const T * g, const T * u, void * y, long n, cudaStream_t stream) {
         const long want = (nb * 4 + Q8_THREADS - 1) / Q8_THREADS;
         if (FAST) {
             const long piece = 1L << 28;                                   // blocks per launch
-            // (8 x the resident thread blocks: 1309 -> 1273 us for 65536 x 25600 values, the all-bytes form 0.83 -> 0.89, the exact-statements form 0.35 -> 0.40)
+            // (about 8 units of 4096 values per thread block: 1309 -> 1229 us for 65536 x 25600 values, the all-bytes form 0.83 -> 0.88)
             for (long b0 = 0; b0 < nb; b0 += piece) {
                 const long m = nb - b0 < piece ? nb - b0 : piece;
                 const long w = (m * 2 + Q8_THREADS - 1) / Q8_THREADS;
-                swiglu_q8_fast_kernel<T, FAST == 2><<<cam_resident_grid(swiglu_q8_fast_kernel<T, FAST == 2>, Q8_THREADS, 0, w, 8), Q8_THREADS, 0, stream>>>(
+                swiglu_q8_fast_kernel<T, FAST == 2><<<cam_iter_grid(swiglu_q8_fast_kernel<T, FAST == 2>, Q8_THREADS, 0, w, 8), Q8_THREADS, 0, stream>>>(
                     g + b0 * 32, u + b0 * 32, (uint8_t *)y + b0 * 36, (int)m);
             }
         } else if (!SWIGLU) {
@@ -380,7 +380,7 @@ int launch_q8_scaled(const float * x, float rs, void * y, long n, cudaStream_t s
     for (long b0 = 0; b0 < nb; b0 += piece) {
         const long m = nb - b0 < piece ? nb - b0 : piece;
         const long w = (m * 2 + Q8_THREADS - 1) / Q8_THREADS;
-        swiglu_q8_fast_kernel<float, SUMS, true><<<cam_resident_grid(swiglu_q8_fast_kernel<float, SUMS, true>, Q8_THREADS, 0, w, 8), Q8_THREADS, 0, stream>>>(
+        swiglu_q8_fast_kernel<float, SUMS, true><<<cam_iter_grid(swiglu_q8_fast_kernel<float, SUMS, true>, Q8_THREADS, 0, w, 8), Q8_THREADS, 0, stream>>>(
             x + b0 * 32, nullptr, (uint8_t *)y + b0 * 36, (int)m, rs);
     }
     if (n & 31) q8_1_tail_kernel<float, false, true><<<1, 32, 0, stream>>>(x, nullptr, (uint8_t *)y, nb << 5, (int)(n & 31), rs);
