@@ -65,7 +65,8 @@ int cam_rms_apply_f16(int n, void * x, const void * d, const float * tot, const 
                       int Nfull, void * stream);
 
 /* The tensor-parallel RMSNorm as one kernel per rank (no reference counterpart; one rank per GPU). Each rank's exchange buffer holds
- * cam_tp_rms_words(cap, world) 64-bit words, zeroed once, and is mapped into every rank's process; peers is a device array of `world`
+ * cam_tp_rms_words(cap, world) 64-bit words (2 * world * cap exchange words and 8 of the library's own: a call's blocks are numbered
+ * there in the order they start), zeroed once, and is mapped into every rank's process; peers is a device array of `world`
  * pointers to them (entry `rank` = the caller's own). A rank writes its per-row partial sums into every buffer by peer stores and
  * normalises a row when all ranks' partials have arrived; tag = the call's sequence number (1, 2, 3, ..: never 0, the same on every
  * rank; a call with n = 0 launches nothing and must not use a tag up). Waits are bounded (2 s, or CAMINUS_B200_TP_WAIT_MS milliseconds):
