@@ -533,13 +533,19 @@ def main():
         # the same norm as one kernel per rank (partials by peer stores over NVLink, no collective call)
         try:
             fused = D.TPRmsNormFused(norm.nw, HIDDEN, T, 1e-6)
-            xc = xs0.clone(); h_f = fused(xc, ds); fused.check()
+
+            def checked():                                            # a wait that ran out on one rank ends the leg on every rank (the ranks' collectives stay matched)
+                err = None
+                try: fused.check()
+                except RuntimeError as e_: err = e_
+                if not all_true(err is None): raise RuntimeError(str(err) if err else 'a wait for another rank ran out on another rank')
+            xc = xs0.clone(); h_f = fused(xc, ds); checked()
             bitwise = all_true(torch.equal(h_f, h_ref) and torch.equal(xc, xa))
-            xc.copy_(xs0); h_f2 = fused(xc, ds); fused.check()           # the next call (the other half of the exchange buffer)
+            xc.copy_(xs0); h_f2 = fused(xc, ds); checked()               # the next call (the other half of the exchange buffer)
             bitwise = all_true(torch.equal(h_f2, h_ref) and torch.equal(xc, xa)) and bitwise
             rel_f = float(((h_f.float() - h_nccl.float()).abs().max() / h_nccl.float().abs().max()).item())
             tf = timed_norm(lambda: fused(xs, ds, hs))
-            fused.check()
+            checked()
             tp['fused'] = {'us_per_step': tf * 1e6, 'tokens_per_s': T / tf, 'hbm_gbs_per_gpu': T * 4 * Ns * 2 / tf / 1e9, 'frac_of_peak': T * 4 * Ns * 2 / tf / 1e9 / peaks()[0],
                            'nvlink_bytes_per_rank': T * 8 * (world - 1), 'parity': 'bitwise' if bitwise else 'MISMATCH',
                            'vs_nccl_form_max_rel': rel_f, 'note': 'one launch per rank: per-row partials stored into every peer, rows normalised as they complete; '

@@ -458,40 +458,6 @@ CAM_DEV bool bf16_word_has_nan(uint32_t w) { return (((w & 0x7fff7fffu) + 0x007f
 // hb = bf16((x rstd) w) into the warp's shared-memory slice and the thin projections ab = bf16(hb . wab[j]); the quantiser's steps then
 // read hb back sixteen values per lane. Sums: thread tid owns tid + 256 j, wave butterflies, 8 wave sums in order (ref_total_f32's
 // statements, the butterfly's additions two accumulators per instruction).
-CAM_DEV float ref_total_f32_pairs(f32x2 (&a2)[4], int lane) {            // a2[c] = accumulators 2 c, 2 c + 1 of ref_total_f32's a[8]
-#pragma unroll
-    for (int o = 4; o > 0; o >>= 1)
-#pragma unroll
-        for (int c = 0; c < 4; c++) a2[c] = add2(a2[c], pk2(__shfl_xor_sync(CAM_FULL, lo2(a2[c]), o), __shfl_xor_sync(CAM_FULL, hi2(a2[c]), o)));
-    const f32x2 t0 = add2(a2[0], a2[1]), t1 = add2(a2[2], a2[3]);        // partner 2: (a0 + a2, a1 + a3), (a4 + a6, a5 + a7)
-    const float P0 = fadd(lo2(t0), hi2(t0)), P1 = fadd(lo2(t1), hi2(t1));   // partner 1
-    float tot = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 8; w++) tot = fadd(tot, __shfl_sync(CAM_FULL, w < 4 ? P0 : P1, 8 * (w & 3)));
-    return tot;
-}
-// two such sums at once, a[] and b[]: in the first butterfly stage a lane keeps one of the two (lanes with bit 2 clear a's, the others b's) and
-// sends the other, so each stage costs one set of shuffles for both; the additions and their order are ref_total_f32's. Returns the
-// total of the lane's own sum (a's where lane & 4 is clear).
-CAM_DEV float ref_total_f32_two(const f32x2 (&a)[4], const f32x2 (&b)[4], int lane) {
-    const bool up = (lane & 4) != 0;
-    f32x2 v[4];
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-        const f32x2 keep = up ? b[c] : a[c], send = up ? a[c] : b[c];
-        v[c] = add2(keep, pk2(__shfl_xor_sync(CAM_FULL, lo2(send), 4), __shfl_xor_sync(CAM_FULL, hi2(send), 4)));
-    }
-#pragma unroll
-    for (int o = 2; o > 0; o >>= 1)
-#pragma unroll
-        for (int c = 0; c < 4; c++) v[c] = add2(v[c], pk2(__shfl_xor_sync(CAM_FULL, lo2(v[c]), o), __shfl_xor_sync(CAM_FULL, hi2(v[c]), o)));
-    const f32x2 t0 = add2(v[0], v[1]), t1 = add2(v[2], v[3]);
-    const float P0 = fadd(lo2(t0), hi2(t0)), P1 = fadd(lo2(t1), hi2(t1));
-    float tot = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 8; w++) tot = fadd(tot, __shfl_sync(CAM_FULL, w < 4 ? P0 : P1, 8 * (w & 3) + (lane & 4)));
-    return tot;
-}
 // NCH: the row's chunks of 128 when known at compile time (0: counted from d, up to 8)
 template <int NCH>
 struct BlockEntrySrc {

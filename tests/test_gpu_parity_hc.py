@@ -91,7 +91,8 @@ def test_bf16_operands_and_swiglu():
     assert same(yy, oracle.pf_swiglu(gg, uu))
 
 
-@pytest.mark.parametrize('rows,heads,D,nrot,stride', [(7, 3, 256, 64, 512), (1, 24, 256, 64, 512), (40, 2, 128, 128, 128), (3, 1, 512, 0, 512)])
+@pytest.mark.parametrize('rows,heads,D,nrot,stride', [(7, 3, 256, 64, 512), (1, 24, 256, 64, 512), (40, 2, 128, 128, 128), (3, 1, 512, 0, 512),
+                                                      (64, 4, 256, 256, 256), (10, 6, 128, 8, 132), (500, 16, 256, 0, 256), (9, 2, 256, 136, 260)])   # pairs of heads: both chunks rotated, a rotated range of 8, none, one that ends inside the second chunk
 def test_qk_nr(rows, heads, D, nrot, stride):
     g = np.random.default_rng(rows + D)
     x = acts(g, (rows * heads, stride), 1.5); w = (g.random(D) + 0.5).astype(np.float32)
