@@ -322,9 +322,11 @@ def single_op_lines(torch, dev, peak, only=(), headline=False):
     Q8 = q3m_ops.Ops(dev, q8=True)
     qkv = [rnd(T * ldq, scale=3.0) for _ in range(2)]; q16 = torch.empty(T, nh, 128, dtype=torch.float16, device=dev)
     cache = torch.zeros(T * rowb, dtype=torch.uint8, device=dev); err = torch.zeros(1, dtype=torch.int32, device=dev)
-    line('qk_rope_q8_f32_T4096', T * (ldq * 4 + nh * 256 + rowb), timed(lambda i: Q8.qk_rope(qkv[i], ldq, nh, nkv, par, 0, q16, cache, T, err=err), rot=2), T, 'tokens_per_s')
+    line('qk_rope_q8_f32_T4096', T * (ldq * 4 + nh * 256 + rowb), timed(lambda i: Q8.qk_rope(qkv[i], ldq, nh, nkv, par, 0, q16, cache, T, err=err), rot=2), T, 'tokens_per_s',
+         graph_fn=lambda i: Q8.qk_rope(qkv[i % 2], ldq, nh, nkv, par, 0, q16, cache, T, err=err))
     F16 = q3m_ops.Ops(dev); c16 = torch.zeros(T * 2 * M, dtype=torch.float16, device=dev)
-    line('qk_rope_f32_cache_T4096', T * (ldq * 4 + nh * 256 + 2 * M * 2), timed(lambda i: F16.qk_rope(qkv[i], ldq, nh, nkv, par, 0, q16, c16, T), rot=2), T, 'tokens_per_s')
+    line('qk_rope_f32_cache_T4096', T * (ldq * 4 + nh * 256 + 2 * M * 2), timed(lambda i: F16.qk_rope(qkv[i], ldq, nh, nkv, par, 0, q16, c16, T), rot=2), T, 'tokens_per_s',
+         graph_fn=lambda i: F16.qk_rope(qkv[i % 2], ldq, nh, nkv, par, 0, q16, c16, T))
     del qkv, cache, c16
     T2 = 32768                                               # the same two forms on a batch that fills the device for longer
     qkv2 = rnd(T2 * ldq, scale=3.0); q16b = torch.empty(T2, nh, 128, dtype=torch.float16, device=dev)
@@ -365,19 +367,23 @@ def single_op_lines(torch, dev, peak, only=(), headline=False):
     tab = torch.randint(0, 256, (vocab, nblk, 136), device=dev, dtype=torch.uint8, generator=g)
     tab[:, :, 0:2] = (torch.randn(vocab, nblk, 1, device=dev, generator=g) * 1e-3).abs().half().view(torch.uint8).view(vocab, nblk, 2)
     tk = torch.randint(0, vocab, (nt,), device=dev, dtype=torch.int32, generator=g); xo = [torch.empty(nt, nblk * 256, device=dev) for _ in range(2)]
-    line('embd_rows_iq4xs_16384x2048', nt * (4 + nblk * 136 + nblk * 1024), timed(lambda i: feed.embd_rows_iq4xs((1,), (256,), tab.view(-1), tk, I(vocab), I(nt), I(nblk), xo[i], er), rot=2), nt, 'rows_per_s')
+    line('embd_rows_iq4xs_16384x2048', nt * (4 + nblk * 136 + nblk * 1024), timed(lambda i: feed.embd_rows_iq4xs((1,), (256,), tab.view(-1), tk, I(vocab), I(nt), I(nblk), xo[i], er), rot=2), nt, 'rows_per_s',
+         graph_fn=lambda i: feed.embd_rows_iq4xs((1,), (256,), tab.view(-1), tk, I(vocab), I(nt), I(nblk), xo[i % 2], er))
     bpr = 64; raw = torch.randint(0, 256, (vocab, bpr, 18), device=dev, dtype=torch.uint8, generator=g)
     raw[:, :, 0:2] = (torch.randn(vocab, bpr, 1, device=dev, generator=g) * 1e-3).abs().half().view(torch.uint8).view(vocab, bpr, 2)
-    line('ple_rows_iq4nl_16384x2048', nt * (4 + bpr * 18 + bpr * 128), timed(lambda i: feed.ple_rows_iq4nl((1,), (256,), raw.view(-1), tk, I(vocab), I(nt), I(bpr), xo[i], er), rot=2), nt, 'rows_per_s')
+    line('ple_rows_iq4nl_16384x2048', nt * (4 + bpr * 18 + bpr * 128), timed(lambda i: feed.ple_rows_iq4nl((1,), (256,), raw.view(-1), tk, I(vocab), I(nt), I(bpr), xo[i], er), rot=2), nt, 'rows_per_s',
+         graph_fn=lambda i: feed.ple_rows_iq4nl((1,), (256,), raw.view(-1), tk, I(vocab), I(nt), I(bpr), xo[i % 2], er))
     tq6 = torch.randint(0, 256, (vocab, nblk, 210), device=dev, dtype=torch.uint8, generator=g)
     tq6[:, :, 208:210] = (torch.randn(vocab, nblk, 1, device=dev, generator=g) * 1e-3).half().view(torch.uint8).view(vocab, nblk, 2)
-    line('emb_rows_q6k_16384x2048', nt * (4 + nblk * 210 + nblk * 1024), timed(lambda i: O.emb_q6k(tq6.view(-1), nblk * 210, vocab, tk, xo[i], nt, nblk * 256), rot=2), nt, 'rows_per_s')
+    line('emb_rows_q6k_16384x2048', nt * (4 + nblk * 210 + nblk * 1024), timed(lambda i: O.emb_q6k(tq6.view(-1), nblk * 210, vocab, tk, xo[i], nt, nblk * 256), rot=2), nt, 'rows_per_s',
+         graph_fn=lambda i: O.emb_q6k(tq6.view(-1), nblk * 210, vocab, tk, xo[i % 2], nt, nblk * 256))
     ti2 = torch.randint(0, 256, (vocab, nblk, 82), device=dev, dtype=torch.uint8, generator=g)
     ti2[:, :, 0:2] = (torch.randn(vocab, nblk, 1, device=dev, generator=g) * 1e-2).half().view(torch.uint8).view(vocab, nblk, 2)
     CU.set_iq2s_grid(np.array([8, 25, 43], np.uint8)[np.random.default_rng(5).integers(0, 3, (1024, 8))])     # a stand-in grid: the timing does not depend on its entries
     from caminus_b200.prefill import q35own
     OT = q35own.Ops(dev, module=q35own.MODULE_TCAP)
-    line('emb_rows_iq2s_16384x2048', nt * (4 + nblk * 82 + nblk * 1024), timed(lambda i: OT.emb_iq2s(ti2.view(-1), nblk * 82, vocab, tk, xo[i], nt, nblk * 256), rot=2), nt, 'rows_per_s')
+    line('emb_rows_iq2s_16384x2048', nt * (4 + nblk * 82 + nblk * 1024), timed(lambda i: OT.emb_iq2s(ti2.view(-1), nblk * 82, vocab, tk, xo[i], nt, nblk * 256), rot=2), nt, 'rows_per_s',
+         graph_fn=lambda i: OT.emb_iq2s(ti2.view(-1), nblk * 82, vocab, tk, xo[i % 2], nt, nblk * 256))
     del tab, raw, xo, tq6, ti2
     from caminus_b200 import lib as LB
     Rq, Kq8 = 32768, 2560

@@ -119,6 +119,25 @@ template <bool NANQ> CAM_DEV uint32_t bf16x2(float lo, float hi) {
     return r;
 }
 
+// cam_expf of two values: the same statements, the fma chain two values per instruction (clamp and exponent insertion stay per value)
+CAM_DEV f32x2 cam_expf2(float a0, float a1) {
+    a0 = fminf(fmaxf(a0, -87.0f), 88.0f); a1 = fminf(fmaxf(a1, -87.0f), 88.0f);
+    const f32x2 a = pk2(a0, a1), magic = pk2(12582912.0f, 12582912.0f);
+    const f32x2 t = fma2(a, pk2(0x1.715476p+0f, 0x1.715476p+0f), magic);
+    const f32x2 n = sub2(t, magic);
+    f32x2 r = fma2(n, pk2(-0x1.62e430p-1f, -0x1.62e430p-1f), a);
+    r = fma2(n, pk2(0x1.05c610p-29f, 0x1.05c610p-29f), r);
+    f32x2 p = pk2(0x1.687b46p-10f, 0x1.687b46p-10f);
+    p = fma2(p, r, pk2(0x1.123bdcp-7f, 0x1.123bdcp-7f));
+    p = fma2(p, r, pk2(0x1.555b5cp-5f, 0x1.555b5cp-5f));
+    p = fma2(p, r, pk2(0x1.55548ep-3f, 0x1.55548ep-3f));
+    p = fma2(p, r, pk2(0x1.fffff8p-2f, 0x1.fffff8p-2f));
+    const f32x2 one = pk2(1.0f, 1.0f);
+    p = fma2(p, r, one);
+    p = fma2(p, r, one);
+    return pk2(__uint_as_float(__float_as_uint(lo2(p)) + (__float_as_uint(lo2(t)) << 23)), __uint_as_float(__float_as_uint(hi2(p)) + (__float_as_uint(hi2(t)) << 23)));
+}
+
 // ---- 128-bit global accesses ------------------------------------------------------------------------------------------
 CAM_DEV uint4 ldg128(const void * p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }          // read-only data
 CAM_DEV uint4 ld128(const void * p) { return *reinterpret_cast<const uint4 *>(p); }                 // data this kernel also writes

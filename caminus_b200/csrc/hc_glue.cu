@@ -24,6 +24,12 @@ CAM_DEV uint16_t bf16_nan(float f) {       // core.hip's f2bf: the same, NaN -> 
 }
 CAM_DEV float bf16_f(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
 CAM_DEV float cam_sigmoid(float v) { return fdiv(1.0f, fadd(1.0f, cam_expf(-v))); }
+// four sigmoids with the exponentials' fma chains packed: sum += x * sigmoid(g), element by element
+CAM_DEV float4 fma_sigmoid4(float4 x, float4 g, float4 sum) {
+    const f32x2 one = pk2(1.0f, 1.0f);
+    const f32x2 d0 = add2(one, cam_expf2(-g.x, -g.y)), d1 = add2(one, cam_expf2(-g.z, -g.w));
+    return make_float4(ffma(x.x, fdiv(1.0f, lo2(d0)), sum.x), ffma(x.y, fdiv(1.0f, hi2(d0)), sum.y), ffma(x.z, fdiv(1.0f, lo2(d1)), sum.z), ffma(x.w, fdiv(1.0f, hi2(d1)), sum.w));
+}
 
 // the block's sum over the threads' partial sums: wave butterfly, eight partials in order (every thread gets the total)
 CAM_DEV float block_total(float ss, float * part) {
@@ -163,8 +169,7 @@ __global__ void __launch_bounds__(256) hc_mean_vec_kernel(const float * __restri
                         const float4 wv = __ldg(reinterpret_cast<const float4 *>(w) + (size_t)h * D4 + i4);
                         xv[h] = make_float4(fmul(fmul(xv[h].x, sc), wv.x), fmul(fmul(xv[h].y, sc), wv.y), fmul(fmul(xv[h].z, sc), wv.z), fmul(fmul(xv[h].w, sc), wv.w));
                     }
-                    sum = make_float4(ffma(xv[h].x, cam_sigmoid(gv[h].x), sum.x), ffma(xv[h].y, cam_sigmoid(gv[h].y), sum.y),
-                                      ffma(xv[h].z, cam_sigmoid(gv[h].z), sum.z), ffma(xv[h].w, cam_sigmoid(gv[h].w), sum.w));
+                    sum = fma_sigmoid4(xv[h], gv[h], sum);
                 }
             } else {
                 for (int h = 0; h < nh; h++) {
@@ -176,8 +181,7 @@ __global__ void __launch_bounds__(256) hc_mean_vec_kernel(const float * __restri
                         const float4 wv = __ldg(reinterpret_cast<const float4 *>(w) + (size_t)h * D4 + i4);
                         xv = make_float4(fmul(fmul(xv.x, sc), wv.x), fmul(fmul(xv.y, sc), wv.y), fmul(fmul(xv.z, sc), wv.z), fmul(fmul(xv.w, sc), wv.w));
                     }
-                    sum = make_float4(ffma(xv.x, cam_sigmoid(gv.x), sum.x), ffma(xv.y, cam_sigmoid(gv.y), sum.y), ffma(xv.z, cam_sigmoid(gv.z), sum.z),
-                                      ffma(xv.w, cam_sigmoid(gv.w), sum.w));
+                    sum = fma_sigmoid4(xv, gv, sum);
                 }
             }
             __stcs(reinterpret_cast<float4 *>(out) + (size_t)tt * D4 + i4, make_float4(fmul(rs, sum.x), fmul(rs, sum.y), fmul(rs, sum.z), fmul(rs, sum.w)));
