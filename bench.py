@@ -31,9 +31,9 @@ import numpy as np   # noqa: E402
 T_PER_GPU, HIDDEN, NH, NKV, INTER = 65536, 5120, 64, 8, 25600
 BYTES_PER_TOKEN = {'add_rms_f16': 4 * HIDDEN * 2, 'qk_rope_f16': (NH + NKV) * 128 * 2 * 2, 'swiglu_q8_1_f16': 2 * INTER * 2 + INTER // 32 * 36}
 # DRAM bytes per token row of the dominant kernel, from one ncu capture of swiglu_q8_fast_kernel at T = 8192, I = 25600
-# (dram__bytes_read.sum + dram__bytes_write.sum = 838.89 + 216.15 MB); the traffic grows in proportion to the rows, so a launch
+# (dram__bytes_read.sum + dram__bytes_write.sum = 838.90 + 215.24 MB); the traffic grows in proportion to the rows, so a launch
 # of T rows is scaled from it
-SWIGLU_DRAM_BYTES_PER_TOKEN = (838_888_448 + 216_150_272) / 8192
+SWIGLU_DRAM_BYTES_PER_TOKEN = (838_904_320 + 215_235_072) / 8192
 METRIC = 'per-layer glue throughput (residual add + RMSNorm -> q/k norm + RoPE -> SwiGLU + Q8_1), tokens/s'
 
 
@@ -263,7 +263,8 @@ def single_op_lines(torch, dev, peak, only=(), headline=False):
         xs = [torch.randn(T, 2048, device=dev, generator=g) for _ in range(rot)]; d = torch.randn(T, 2048, device=dev, generator=g)
         nw = 1 + 0.05 * torch.randn(2048, device=dev, generator=g); h = torch.empty(T, 2048, device=dev); h16 = torch.empty(T, 2048, dtype=torch.float16, device=dev)
         sec = timed(lambda i: O.add_rms16(xs[i], nw, 1e-6, h16, T, 2048, d=d, S=1, h=h), rot=rot, inner=100 if T == 1 else 10)
-        line(f'add_rms16_f32_h2048_T{T}', T * (4 * 8192 + 4096) + 8192, sec, T, 'tokens_per_s')
+        line(f'add_rms16_f32_h2048_T{T}', T * (4 * 8192 + 4096) + 8192, sec, T, 'tokens_per_s',
+             graph_fn=(lambda i: O.add_rms16(xs[i % rot], nw, 1e-6, h16, T, 2048, d=d, S=1, h=h)) if 1 < T <= 4096 else None)
         if T == 1 and f'add_rms16_f32_h2048_T{T}' in out:
             gs = graphed(lambda i: O.add_rms16(xs[i % rot], nw, 1e-6, h16, T, 2048, d=d, S=1, h=h))
             out[f'add_rms16_f32_h2048_T{T}']['us_in_cuda_graph'] = gs * 1e6 if isinstance(gs, float) else gs
