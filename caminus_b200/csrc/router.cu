@@ -62,6 +62,8 @@ __global__ void __launch_bounds__(256) router_few_kernel(const float * __restric
 // loads for 64 pairs instead of two global loads per pair, and no load waits on DRAM. Per pair the statements and their order
 // are the ones stated above router_few_kernel.
 constexpr int RT_TOK = 32, RT_EXP = 16, RT_STAGES = 3, RT_STAGE_FLOATS = (RT_TOK + RT_EXP) * 128;
+constexpr int RT_SUMS_PITCH = RT_TOK * RT_EXP + 1;                        // a lane's 512 partial sums (+ 1: the lanes of a warp on different banks)
+static_assert(32 * RT_SUMS_PITCH <= RT_STAGES * RT_STAGE_FLOATS, "the partial sums reuse the stages");
 
 __global__ void __launch_bounds__(256) router_tile_kernel(const float * __restrict__ h, const float * __restrict__ Wr, int E, int K,
                                                           float * __restrict__ logits, int n) {
@@ -107,15 +109,26 @@ __global__ void __launch_bounds__(256) router_tile_kernel(const float * __restri
             for (int j = 0; j < 8; j++) acc[i][j] = fadd(acc[i][j], dot4(wv[j], xv[i]));
     }
     cp_async_wait<0>();
-    float mine[2] = {0.0f, 0.0f};                                          // lane l stores pairs (token l / 8 and 4 + l / 8, expert l % 8)
+    __syncthreads();                                                       // (the stages become the partial sums [lane][token][expert])
+    // The 32 lanes' partial sums of a pair meet in shared memory and one thread adds them as the xor butterfly 16, 8, 4, 2, 1 does
+    // (lane 0's tree; the additions commute, so every lane's total is that one): 31 additions per pair instead of 160 and no shuffles.
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 8; j++) { const float v = wsum(acc[i][j]); if (lane == (i & 3) * 8 + j) mine[i >> 2] = v; }      // (every lane holds the same total)
+        for (int j = 0; j < 8; j++) rt_smem[lane * RT_SUMS_PITCH + (wt + i) * RT_EXP + we + j] = acc[i][j];
+    __syncthreads();
 #pragma unroll
     for (int hh = 0; hh < 2; hh++) {
-        const int ti = t0 + wt + 4 * hh + (lane >> 3), ej = e0 + we + (lane & 7);
-        if (ti < n && ej < E) logits[(size_t)ti * E + ej] = mine[hh];
+        const int pair = tid + 256 * hh;
+        float p[32];
+#pragma unroll
+        for (int c = 0; c < 32; c++) p[c] = rt_smem[c * RT_SUMS_PITCH + pair];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int c = 0; c < o; c++) p[c] = fadd(p[c], p[c + o]);
+        const int ti = t0 + (pair >> 4), ej = e0 + (pair & 15);
+        if (ti < n && ej < E) logits[(size_t)ti * E + ej] = p[0];
     }
 }
 
