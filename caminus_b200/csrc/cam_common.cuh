@@ -88,6 +88,11 @@ CAM_DEV f32x2 mul2(f32x2 a, f32x2 b) { f32x2 r; asm("mul.rn.f32x2 %0, %1, %2;" :
 CAM_DEV f32x2 sub2(f32x2 a, f32x2 b) { f32x2 r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
 CAM_DEV f32x2 add2(f32x2 a, f32x2 b) { f32x2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
 CAM_DEV f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r; }
+// The rounded product where a packed addition or subtraction consumes it: the assembler contracts mul.rn.f32x2 followed by
+// add / sub.rn.f32x2 into one packed fma (seen on this toolchain: t = v inv = 63.5 exactly, t - 63 came out as 0.49999997, the
+// unrounded product's; a b + (-0) as an fma is simplified to the product and contracted all the same). The scalar mul.rn is never
+// contracted, so the two products are scalar and packed afterwards.
+CAM_DEV f32x2 prod2(f32x2 a, f32x2 b) { return pk2(fmul(lo2(a), lo2(b)), fmul(hi2(a), hi2(b))); }
 
 // ---- fp16 <-> fp32 (the widening is exact; the narrowing rounds to nearest even) --------------------------------------------
 CAM_DEV float2 h2_to_f2(uint32_t v) { return __half22float2(*reinterpret_cast<const __half2 *>(&v)); }

@@ -30,11 +30,20 @@ CAM_DEV void q8_0_store(const float (&v)[4], uint8_t * blk, int l8, int * err, b
     const bool refuse = !finite_f(amax) || (amax != 0.0f && (d == 0.0f || !finite_f(d) || !finite_f(inv) || !finite_f(__half2float(stored))));
     if (!store) return;
     if (refuse) { if (l8 == 0) atomicOr(err, 2); return; }
-    int q[4];
+    // roundf(t), t = v inv, without the special-function unit's rounding and conversion: t + 1.5 2^23 is t rounded to the nearest integer,
+    // ties to even, its two's complement in the sum's low byte (|t| <= 127 (1 + 2^-22) here: every value is a number). roundf differs on
+    // exact ties only, and t - rint(t) is exact: a lane that sees |t - rint(t)| = 0.5 takes roundf.
+    const f32x2 inv2 = pk2(inv, inv), big2 = pk2(12582912.0f, 12582912.0f);
+    const f32x2 ta = prod2(pk2(v[0], v[1]), inv2), tb = prod2(pk2(v[2], v[3]), inv2);      // (prod2: the sums below must see the rounded t)
+    const f32x2 sa = add2(ta, big2), sb = add2(tb, big2);
+    const f32x2 ea = sub2(ta, sub2(sa, big2)), eb = sub2(tb, sub2(sb, big2));
+    uint32_t q[4] = {__float_as_uint(lo2(sa)), __float_as_uint(hi2(sa)), __float_as_uint(lo2(sb)), __float_as_uint(hi2(sb))};
+    if (fmaxf(fmaxf(fabsf(lo2(ea)), fabsf(hi2(ea))), fmaxf(fabsf(lo2(eb)), fabsf(hi2(eb)))) >= 0.5f) {
 #pragma unroll
-    for (int c = 0; c < 4; c++) q[c] = __float2int_rn(roundf(fmul(v[c], inv))) & 0xff;
+        for (int c = 0; c < 4; c++) q[c] = (uint32_t)__float2int_rn(roundf(fmul(v[c], inv)));
+    }
     uint16_t * o = reinterpret_cast<uint16_t *>(blk + 2 + 4 * l8);              // (34-byte blocks: 2-byte alignment)
-    o[0] = (uint16_t)(q[0] | (q[1] << 8)); o[1] = (uint16_t)(q[2] | (q[3] << 8));
+    o[0] = (uint16_t)__byte_perm(q[0], q[1], 0x0040); o[1] = (uint16_t)__byte_perm(q[2], q[3], 0x0040);
     if (l8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(stored);
 }
 

@@ -21,7 +21,19 @@ template <> struct MmqRaw<0> { float4 a[4]; };
 template <> struct MmqRaw<2> { uint2 a[4], b[4]; };
 
 template <int MODE>
-CAM_DEV void mmq_load(MmqRaw<MODE> & raw, const void * __restrict__ xv, const void * __restrict__ uv, int k, size_t row_at, int kvalid) {
+CAM_DEV void mmq_load(MmqRaw<MODE> & raw, const void * __restrict__ xv, const void * __restrict__ uv, int k, size_t row_at, int kvalid, bool wide = false) {
+    if constexpr (MODE == 0) {
+        if (wide && k + 16 <= kvalid) {                                   // (rows 32-byte aligned: a lane's 64 bytes as two whole sectors)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                uint4 a, b;
+                ldg256((const float *)xv + row_at + k + 8 * h, a, b);
+                raw.a[2 * h] = make_float4(__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w));
+                raw.a[2 * h + 1] = make_float4(__uint_as_float(b.x), __uint_as_float(b.y), __uint_as_float(b.z), __uint_as_float(b.w));
+            }
+            return;
+        }
+    }
 #pragma unroll
     for (int s = 0; s < 4; s++) {
         const bool in = k + 4 * s < kvalid;
@@ -76,11 +88,34 @@ CAM_DEV void mmq_quant(const float (&v)[16], uint4 & w, uint32_t & hdr) {
     uint32_t ww[4] = {0u, 0u, 0u, 0u};
     if (amax != 0.0f) {
         const float d_inv = fdiv(127.0f, amax);
+        // roundf(t) without the rounding and conversion instructions (the special-function unit's, a quarter of the fp32 rate):
+        // t + 1.5 2^23 is t rounded to the nearest integer, ties to even, with that integer's two's complement in the sum's low
+        // bits (|t| <= 127 (1 + 2^-23) whenever it is a number). roundf differs on exact ties only, and t - rint(t) is exact, so
+        // a lane whose largest |t - rint(t)| stays below 0.5 has its codes; a tie, a NaN or an infinity among the t (0 t summed
+        // is then a NaN) sends the lane to the reference's statements below.
+        const f32x2 di2 = pk2(d_inv, d_inv), big2 = pk2(12582912.0f, 12582912.0f), zero2 = pk2(0.0f, 0.0f);
+        f32x2 z2 = zero2;
+        float em = 0.0f;
+        uint32_t sb[16];
 #pragma unroll
-        for (int c = 0; c < 16; c++) {
-            const float t = fmul(v[c], d_inv);
-            const int q = fabsf(t) < 127.5f ? __float2int_rn(roundf(t)) : 0;
-            ww[c >> 2] |= (uint32_t)(q & 0xff) << (8 * (c & 3));
+        for (int c = 0; c < 16; c += 2) {
+            const f32x2 t2 = prod2(pk2(v[c], v[c + 1]), di2), s2 = add2(t2, big2), e2 = sub2(t2, sub2(s2, big2));      // (prod2: the sums must see the rounded t)
+            em = fmaxf(fmaxf(em, fabsf(lo2(e2))), fabsf(hi2(e2)));
+            z2 = fma2(t2, zero2, z2);
+            sb[c] = __float_as_uint(lo2(s2)); sb[c + 1] = __float_as_uint(hi2(s2));
+        }
+        const float zs = fadd(lo2(z2), hi2(z2));
+        if (em < 0.5f && zs == zs) {
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                ww[k] = __byte_perm(__byte_perm(sb[4 * k], sb[4 * k + 1], 0x0040), __byte_perm(sb[4 * k + 2], sb[4 * k + 3], 0x0040), 0x5410);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 16; c++) {
+                const float t = fmul(v[c], d_inv);
+                const int q = fabsf(t) < 127.5f ? __float2int_rn(roundf(t)) : 0;
+                ww[c >> 2] |= (uint32_t)(q & 0xff) << (8 * (c & 3));
+            }
         }
         d = fdiv(1.0f, d_inv);
     }
@@ -124,34 +159,43 @@ __global__ void __launch_bounds__(256) mmq_q8_1_rows_kernel(const float * __rest
     }
 }
 
-// grid.x walks the rows, grid.y groups of 32 K-blocks (four per warp): a block reads 16 KB of a row; two rows per pass, both rows'
-// loads issued before either is used. (No index is divided: a 64-bit division per task costs more than the task's arithmetic.)
+// A warp's task is a group of four K-blocks of one row (2 KB of fp32 input); the tasks, row-major, go to the warps of the grid in turn,
+// so a block reads 16 KB of consecutive input whatever the row length (K-blocks per row a multiple of 32 or not: rows of 40 K-blocks
+// left three warps in four idle every second pass when a block owned 32 K-blocks of a row). A warp steps by the grid's warps as
+// (rows, groups) with a carry, so no index is divided in the loop; two tasks per pass, both loads issued before either is used.
 // ids (nullable): column r of y holds row ids[r] of the inputs, clamped to the rows there are
 template <int MODE, int LAYOUT>
 __global__ void __launch_bounds__(256) mmq_q8_1_kernel(const void * __restrict__ xv, const void * __restrict__ uv, uint8_t * __restrict__ y,
                                                        int kvalid, int nkb, long ld, int rows, const int * __restrict__ ids) {
     const int lane = threadIdx.x & 31;
-    for (int kb0 = (blockIdx.y * 8 + (threadIdx.x >> 5)) * 4; kb0 < nkb; kb0 += gridDim.y * 32) {
-        const int kb = kb0 + (lane >> 3), k = kb * 128 + (lane & 7) * 16;
-        const bool kon = kb < nkb;
-        const int kv = kon ? kvalid : 0;
-        for (int r = blockIdx.x; r < rows; r += 2 * gridDim.x) {
-            const int r2 = r + gridDim.x;
-            MmqRaw<MODE> a0, a1;
-            const int s0 = ids ? min(max(__ldg(ids + r), 0), rows - 1) : r, s1 = ids && r2 < rows ? min(max(__ldg(ids + r2), 0), rows - 1) : r2;
-            mmq_load<MODE>(a0, xv, uv, k, (size_t)s0 * ld, kv);
-            if (r2 < rows) mmq_load<MODE>(a1, xv, uv, k, (size_t)s1 * ld, kv);
-            float v[16];
-            uint4 w; uint32_t hdr;
-            mmq_values(a0, v);
+    const int ng = (nkb + 3) >> 2;                                        // groups of four K-blocks per row
+    const bool wide = MODE == 0 && !(ld & 7) && (reinterpret_cast<uintptr_t>(xv) & 31u) == 0;
+    const long first = (long)blockIdx.x * 8 + (threadIdx.x >> 5), nw = (long)gridDim.x * 8;
+    if (first >= (long)rows * ng) return;                                 // (whole warps; no block-wide barrier below)
+    int r = (int)(first / ng), g = (int)(first - (long)r * ng);
+    const int dr = (int)(nw / ng), dg = (int)(nw - (long)dr * ng);
+    while (r < rows) {
+        int r2 = r + dr, g2 = g + dg;
+        if (g2 >= ng) { g2 -= ng; r2++; }
+        const bool two = r2 < rows;
+        const int kb = g * 4 + (lane >> 3), kb2 = g2 * 4 + (lane >> 3);
+        const bool kon = kb < nkb, kon2 = two && kb2 < nkb;
+        MmqRaw<MODE> a0, a1;
+        const int s0 = ids ? min(max(__ldg(ids + r), 0), rows - 1) : r, s1 = ids && two ? min(max(__ldg(ids + r2), 0), rows - 1) : r2;
+        mmq_load<MODE>(a0, xv, uv, kb * 128 + (lane & 7) * 16, (size_t)s0 * ld, kon ? kvalid : 0, wide);
+        if (two) mmq_load<MODE>(a1, xv, uv, kb2 * 128 + (lane & 7) * 16, (size_t)s1 * ld, kon2 ? kvalid : 0, wide);
+        float v[16];
+        uint4 w; uint32_t hdr;
+        mmq_values(a0, v);
+        mmq_quant<LAYOUT>(v, w, hdr);
+        if (kon) mmq_write(y + ((size_t)kb * rows + r) * 144, lane, w, hdr);
+        if (two) {
+            mmq_values(a1, v);
             mmq_quant<LAYOUT>(v, w, hdr);
-            if (kon) mmq_write(y + ((size_t)kb * rows + r) * 144, lane, w, hdr);
-            if (r2 < rows) {
-                mmq_values(a1, v);
-                mmq_quant<LAYOUT>(v, w, hdr);
-                if (kon) mmq_write(y + ((size_t)kb * rows + r2) * 144, lane, w, hdr);
-            }
+            if (kon2) mmq_write(y + ((size_t)kb2 * rows + r2) * 144, lane, w, hdr);
         }
+        r = r2 + dr; g = g2 + dg;
+        if (g >= ng) { g -= ng; r++; }
     }
 }
 
@@ -255,6 +299,7 @@ template <bool IDS> struct MmqTask {
 };
 
 // chunk c (row r0 + c) of a task: a lane's 16 values as two loads of 8
+// (256-bit loads of a lane's 32 or 64 bytes, which help the plain quantiser above, cost this kernel a fifth of its speed)
 template <typename T, bool IDS>
 CAM_DEV void mmq_fetch(const T * __restrict__ g, const T * __restrict__ u, const MmqTask<IDS> & t, long ld, int rows, Raw8<T> (&rg)[2][2], Raw8<T> (&ru)[2][2]) {
 #pragma unroll
@@ -486,9 +531,9 @@ int launch_mmq(const void * x, const void * u, void * y, int kvalid, int Kpad, l
 #undef CAM_MMQ_FAST
         return (int)cudaGetLastError();
     }
-    const long ny = (Kpad / 128 + 31) / 32;
-    if (layout == 0) mmq_q8_1_kernel<MODE, 0><<<mmq_grid(mmq_q8_1_kernel<MODE, 0>, rows, ny), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows, ids);
-    else mmq_q8_1_kernel<MODE, 1><<<mmq_grid(mmq_q8_1_kernel<MODE, 1>, rows, ny), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows, ids);
+    const long want = ((long)rows * ((Kpad / 128 + 3) / 4) + 7) / 8;     // (warp tasks / 8)
+    if (layout == 0) mmq_q8_1_kernel<MODE, 0><<<cam_resident_grid(mmq_q8_1_kernel<MODE, 0>, 256, 0, want, 8), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows, ids);
+    else mmq_q8_1_kernel<MODE, 1><<<cam_resident_grid(mmq_q8_1_kernel<MODE, 1>, 256, 0, want, 8), 256, 0, stream>>>(x, u, (uint8_t *)y, kvalid, Kpad / 128, ld, rows, ids);
     return (int)cudaGetLastError();
 }
 

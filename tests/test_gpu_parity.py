@@ -500,6 +500,8 @@ def test_qk_rope_q8(n, nh, nkv, pos0, yarn):
     g = np.random.default_rng(n + nh); M = nkv * 128; ldq = nh * 128 + 2 * M; rowb = 2 * (M // 32) * 34
     par = synth.rope_par(seed=n, yarn_table=synth.yarn_table() if yarn else None)
     qkv = (g.standard_normal((n, ldq)) * 3).astype(np.float32)
+    tie = ((g.integers(-126, 126, 32) + 0.5) / 4).astype(np.float32); tie[3] = 127 / 4         # a V block whose quotients sit on .5 (scale 1 / 4):
+    qkv[n // 3, nh * 128 + M + 32:nh * 128 + M + 64] = tie                                     # roundf rounds those away from zero
     cache0 = g.integers(0, 256, (pos0 + n + 2) * rowb, dtype=np.uint8)
     R = q3m_ops.Ops(DEV, q8=True, yarn=yarn)
     cache = cu(cache0); q16 = torch.zeros(n, nh, 128, dtype=torch.float16, device=DEV); err = torch.zeros(1, dtype=torch.int32, device=DEV)

@@ -251,6 +251,31 @@ def test_mmq_q8_1(layout, rows, K):
 
 
 @pytest.mark.parametrize('layout', ['D4', 'DS4'])
+@pytest.mark.parametrize('rows,K,pad', [(5, 384, 0), (40, 5120, 0), (7, 640, 4), (6, 300, 0), (9, 1024, 8)])
+def test_mmq_q8_1_ties_and_specials(layout, rows, K, pad):
+    """the plain MMQ quantiser on quotients that sit on .5 (roundf rounds them away from zero, the device's add-a-large-number rounding
+    to even: those lanes take the reference's statements), NaN, infinities, a maximum so small that 127 / amax overflows, zero groups;
+    rows 32-byte aligned (256-bit loads) and not (row stride K + 4)"""
+    from caminus_b200.engine import gguf
+    rng = np.random.default_rng(rows + K + pad); lay = gguf.MMQ_LAYOUTS[layout]; Kp = (K + 127) // 128 * 128
+    full = np.zeros((rows, K + pad), np.float32); x = full[:, :K]
+    x[:] = acts(rng, (rows, K), 0.7)
+    x[0, :32] = np.arange(32, dtype=np.float32) - 15.5; x[0, 0] = 127.0            # amax 127: the quotients are the values, halves are ties
+    x[0, 32:64] = (rng.integers(-126, 126, 32).astype(np.float32) + 0.5) / 8; x[0, 40] = 127.0 / 8
+    x[1, 64:96] = np.round(x[1, 64:96] * 40) / 2; x[1, 70] = 63.5                  # amax 63.5: the quotients are twice the values
+    if rows > 2: x[2, 5] = np.nan; x[2, 40] = np.inf; x[2, 64:96] = 0; x[2, 100] = -np.inf; x[2, 130] = 3e38
+    if rows > 3: x[3, :32] = 1e-42; x[3, 32:64] *= 1e-38; x[3, 64:96] = -0.0
+    got = gguf.quantize_mmq_q8_1(cu(full)[:, :K], layout)
+    want = oracle.mmq_q8_1(np.ascontiguousarray(x), K, Kp, lay)
+    if layout == 'DS4':                                                            # (a NaN sum has the arithmetic unit's payload)
+        gb, wb = bits(got).reshape(-1, 144), bits(want).reshape(-1, 144)
+        gh, wh = gb[:, :16].copy().view(np.uint16), wb[:, :16].copy().view(np.uint16)
+        nan = (wh & 0x7fff) > 0x7c00
+        assert np.array_equal(gb[:, 16:], wb[:, 16:]) and np.array_equal(gh[~nan], wh[~nan]) and ((gh[nan] & 0x7fff) > 0x7c00).all()
+    else: assert same(got, want)
+
+
+@pytest.mark.parametrize('layout', ['D4', 'DS4'])
 @pytest.mark.parametrize('dt', [np.float16, np.float32])
 @pytest.mark.parametrize('rows,K,kvalid', [(1, 128, 128), (3, 384, 384), (6, 640, 592), (13, 1024, 1024), (5, 896, 888), (64, 2560, 2560)])
 def test_swiglu_mmq_hard_inputs(layout, dt, rows, K, kvalid):
