@@ -170,10 +170,10 @@ __global__ void __launch_bounds__(256) mmq_q8_1_kernel(const void * __restrict__
     const int lane = threadIdx.x & 31;
     const int ng = (nkb + 3) >> 2;                                        // groups of four K-blocks per row
     const bool wide = MODE == 0 && !(ld & 7) && (reinterpret_cast<uintptr_t>(xv) & 31u) == 0;
-    const long first = (long)blockIdx.x * 8 + (threadIdx.x >> 5), nw = (long)gridDim.x * 8;
-    if (first >= (long)rows * ng) return;                                 // (whole warps; no block-wide barrier below)
-    int r = (int)(first / ng), g = (int)(first - (long)r * ng);
-    const int dr = (int)(nw / ng), dg = (int)(nw - (long)dr * ng);
+    const unsigned first = blockIdx.x * 8u + (threadIdx.x >> 5), nw = gridDim.x * 8u;       // (the launch keeps the grid's warps within the tasks: 32-bit)
+    if (first >= (unsigned long)rows * ng) return;                        // (whole warps; no block-wide barrier below)
+    int r = (int)(first / (unsigned)ng), g = (int)(first - (unsigned)r * ng);
+    const int dr = (int)(nw / (unsigned)ng), dg = (int)(nw - (unsigned)dr * ng);
     while (r < rows) {
         int r2 = r + dr, g2 = g + dg;
         if (g2 >= ng) { g2 -= ng; r2++; }
