@@ -390,8 +390,8 @@ int launch_tp_direct(int n, void * x, const void * d, const float * nw, float ep
     // second one, from the cache, normalising, so that no block waits with a row in its registers: 79 us against 64 us at shards of 640.)
     // a block per 4 or 8 rows, so more blocks than are resident: 56.0 us against 63.8 us for resident blocks that loop (65536 rows of 640, one rank)
     const int grid = (n + rpb - 1) / rpb;
-    static const char * agg_env = getenv("CAMINUS_B200_TP_AGG");          // (tuning: "0" / "1" overrides the choice)
-    const bool agg = agg_env ? agg_env[0] == '1' : world * rpb <= 128 && world > 2;
+    static const char * agg_env = getenv("CAMINUS_B200_TP_AGG");          // (tuning: "1" = a block's words to a peer as one contiguous store)
+    const bool agg = agg_env && agg_env[0] == '1' && world * rpb <= 128;
     if (agg) tp_rms_direct_kernel<G, CH, true><<<grid, 128, 0, stream>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Nfull, n,
                                                                         (unsigned long long * const *)peers, rank, world, cap, tag, status, wait_ns);
     else tp_rms_direct_kernel<G, CH, false><<<grid, 128, 0, stream>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Nfull, n,
