@@ -289,13 +289,12 @@ CAM_DEV unsigned tp_take_number(unsigned long long * counter, unsigned tag) {
 // block's successor starts with its loads at once, and the blocks' load, arithmetic and store phases drift apart instead of running in
 // step): the shape of add_rms_f16_reg_kernel. 65536 rows of 640 columns on one rank: 57 us (0.89); the pipelined kernels that parked rows
 // in shared memory on resident, looping blocks: 63-68 us, and this kernel itself on resident blocks that loop: 63.8 us.
-template <int G, int CH, bool AGG>
+template <int G, int CH>
 __global__ void __launch_bounds__(128) tp_rms_direct_kernel(uint16_t * __restrict__ x, const uint16_t * __restrict__ d, const float * __restrict__ nw, float eps,
                                                             uint16_t * __restrict__ h16, int Nfull, int n, unsigned long long * const * __restrict__ peers,
                                                             int rank, int world, int cap, unsigned tag, int * status, unsigned long long wait_ns) {
-    constexpr int RPW = 32 / G, RPB = 4 * RPW, Ns = G * 8 * CH;
+    constexpr int RPW = 32 / G, Ns = G * 8 * CH;
     __shared__ unsigned number;
-    __shared__ float sums[RPB];                                          // AGG: the block's partial sums, sent by its first threads
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, h = lane & (G - 1), sub = lane / G;
     if (threadIdx.x == 0) number = tp_take_number(peers[rank] + (size_t)2 * world * cap, tag);      // (the word after this rank's exchange words)
     __syncthreads();
@@ -304,7 +303,7 @@ __global__ void __launch_bounds__(128) tp_rms_direct_kernel(uint16_t * __restric
     const unsigned long long * const from = h < world ? peers[rank] + slot0 + (size_t)h * cap : nullptr;
     {                                                                    // one block = 4 RPW rows (the grid covers n)
         const int first = ((int)number * 4 + warp) * RPW;                // (warp-uniform)
-        if (!AGG && first >= n) return;                                  // (AGG: every warp comes to the barrier below)
+        if (first >= n) return;
         const int t = first + sub;
         const bool on = t < n;
         const size_t at = (size_t)(on ? t : 0) * Ns + 8 * h;
@@ -335,17 +334,7 @@ __global__ void __launch_bounds__(128) tp_rms_direct_kernel(uint16_t * __restric
             for (int c = 0; c < 4; c++) { ag[2 * c] = ffma(lo2(xs[q][c]), lo2(xs[q][c]), ag[2 * c]); ag[2 * c + 1] = ffma(hi2(xs[q][c]), hi2(xs[q][c]), ag[2 * c + 1]); }
         }
         const float own = tp_row_total<G>(a, lane);                      // (the bits of cam_rms_partial_f16)
-        if (!AGG) { if (mine && on) st_sys_u64(mine + t, ((unsigned long long)tag << 32) | __float_as_uint(own)); }
-        else {
-            // the block's RPB words for a peer are consecutive: RPB adjacent lanes store them as one contiguous piece per peer (64 bytes
-            // at 8 rows) instead of one 8- or 16-byte piece per warp and peer
-            if (h == 0) sums[warp * RPW + sub] = own;
-            __syncthreads();
-            const int row0 = (int)number * RPB, pr = threadIdx.x / RPB, r = threadIdx.x % RPB;
-            if (pr < world && row0 + r < n)                       // (this rank's own buffer too: its words are all sources')
-                st_sys_u64(peers[pr] + slot0 + (size_t)rank * cap + row0 + r, ((unsigned long long)tag << 32) | __float_as_uint(sums[r]));
-            if (first >= n) return;
-        }
+        if (mine && on) st_sys_u64(mine + t, ((unsigned long long)tag << 32) | __float_as_uint(own));
         float part = 0.0f;
         bool late = false;
         if (from && on) {
@@ -388,14 +377,12 @@ int launch_tp_direct(int n, void * x, const void * d, const float * nw, float ep
     const int rpb = 4 * (32 / G);
     // (Measured on two GPUs and not kept: the rows in chunks that fit the second-level cache, a first pass over a chunk sending the partials and a
     // second one, from the cache, normalising, so that no block waits with a row in its registers: 79 us against 64 us at shards of 640.)
+    // (Measured on eight GPUs and not kept either: a block's partial sums gathered in shared memory and sent by its first threads, 64 contiguous
+    // bytes per peer instead of a 16-byte piece per warp and peer: 71.9-72.2 us against 71.3 us at shards of 640; on two GPUs 65.0 against 62.9.)
     // a block per 4 or 8 rows, so more blocks than are resident: 56.0 us against 63.8 us for resident blocks that loop (65536 rows of 640, one rank)
     const int grid = (n + rpb - 1) / rpb;
-    static const char * agg_env = getenv("CAMINUS_B200_TP_AGG");          // (tuning: "1" = a block's words to a peer as one contiguous store)
-    const bool agg = agg_env && agg_env[0] == '1' && world * rpb <= 128;
-    if (agg) tp_rms_direct_kernel<G, CH, true><<<grid, 128, 0, stream>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Nfull, n,
-                                                                        (unsigned long long * const *)peers, rank, world, cap, tag, status, wait_ns);
-    else tp_rms_direct_kernel<G, CH, false><<<grid, 128, 0, stream>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Nfull, n,
-                                                                      (unsigned long long * const *)peers, rank, world, cap, tag, status, wait_ns);
+    tp_rms_direct_kernel<G, CH><<<grid, 128, 0, stream>>>((uint16_t *)x, (const uint16_t *)d, nw, eps, (uint16_t *)h16, Nfull, n,
+                                                          (unsigned long long * const *)peers, rank, world, cap, tag, status, wait_ns);
     return (int)cudaGetLastError();
 }
 
