@@ -283,13 +283,7 @@ CAM_DEV void q8_plain_step(const T * __restrict__ x, uint8_t * __restrict__ y, i
     const int pi = base + lane, q = lane & 1;
     const bool on = FULL || pi < npairs;
     float h[16];
-    if (sizeof(T) == 4 && on && (reinterpret_cast<uintptr_t>(x) & 31u) == 0) {      // a lane's 64 bytes as two whole sectors each (256-bit loads)
-        uint4 a, b, c, e;
-        ldg256(x + (size_t)pi * 16, a, b); ldg256(x + (size_t)pi * 16 + 8, c, e);
-        const uint32_t w[16] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w, c.x, c.y, c.z, c.w, e.x, e.y, e.z, e.w};
-#pragma unroll
-        for (int k = 0; k < 16; k++) h[k] = __uint_as_float(w[k]);
-    } else if (on) {
+    if (on) {
         float t[8];
         Load8<T>::get(x + (size_t)pi * 16, t);
 #pragma unroll
