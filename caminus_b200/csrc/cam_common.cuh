@@ -25,6 +25,8 @@ CAM_DEV float fadd(float a, float b) { return __fadd_rn(a, b); }
 CAM_DEV float fsub(float a, float b) { return __fsub_rn(a, b); }
 CAM_DEV float ffma(float a, float b, float c) { return __fmaf_rn(a, b, c); }
 CAM_DEV float fdiv(float a, float b) { return __fdiv_rn(a, b); }
+// 1 / b correctly rounded: the same bits as fdiv(1.0f, b) (both are the IEEE quotient) in fewer instructions
+CAM_DEV float frcp(float b) { return __frcp_rn(b); }
 
 // exp(a), a clamped to [-87, 88]: n = rint(a log2 e) through the 1.5 * 2^23 constant, r = a - n ln 2 in two fma steps,
 // a degree-6 polynomial, n added to the exponent field.
@@ -46,7 +48,7 @@ CAM_DEV float cam_expf(float a) {
 // the reference's gg_silu, x / (1 + expf(-x)) (kernels/k3_gguf_ops.h:53), with an IEEE division
 CAM_DEV float cam_silu(float x) { return fdiv(x, fadd(1.0f, cam_expf(-x))); }
 // 1 / sqrt(v): IEEE square root then IEEE division
-CAM_DEV float cam_rsqrt(float v) { return fdiv(1.0f, __fsqrt_rn(v)); }
+CAM_DEV float cam_rsqrt(float v) { return frcp(__fsqrt_rn(v)); }
 // base^e (integer e >= 0) by binary exponentiation in binary64, rounded once to binary32
 CAM_DEV float cam_powi(float base, int e) {
     double b = (double)base, p = 1.0;

@@ -23,12 +23,12 @@ CAM_DEV uint16_t bf16_nan(float f) {       // core.hip's f2bf: the same, NaN -> 
     return (uint16_t)(u >> 16);
 }
 CAM_DEV float bf16_f(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
-CAM_DEV float cam_sigmoid(float v) { return fdiv(1.0f, fadd(1.0f, cam_expf(-v))); }
+CAM_DEV float cam_sigmoid(float v) { return frcp(fadd(1.0f, cam_expf(-v))); }      // (1 / d: the IEEE reciprocal is that quotient)
 // four sigmoids with the exponentials' fma chains packed: sum += x * sigmoid(g), element by element
 CAM_DEV float4 fma_sigmoid4(float4 x, float4 g, float4 sum) {
     const f32x2 one = pk2(1.0f, 1.0f);
     const f32x2 d0 = add2(one, cam_expf2(-g.x, -g.y)), d1 = add2(one, cam_expf2(-g.z, -g.w));
-    return make_float4(ffma(x.x, fdiv(1.0f, lo2(d0)), sum.x), ffma(x.y, fdiv(1.0f, hi2(d0)), sum.y), ffma(x.z, fdiv(1.0f, lo2(d1)), sum.z), ffma(x.w, fdiv(1.0f, hi2(d1)), sum.w));
+    return make_float4(ffma(x.x, frcp(lo2(d0)), sum.x), ffma(x.y, frcp(hi2(d0)), sum.y), ffma(x.z, frcp(lo2(d1)), sum.z), ffma(x.w, frcp(hi2(d1)), sum.w));
 }
 
 // the block's sum over the threads' partial sums: wave butterfly, eight partials in order (every thread gets the total)
