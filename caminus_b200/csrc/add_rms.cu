@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(RMS_WARPS * 32) rms_rows_vec_kernel(float * x,
         for (int m = 0; m < CH; m++) xv[m] = *reinterpret_cast<const float4 *>(xr + 128 * m);
         if (POST) {
             const float * br = b + (size_t)(t / HC) * K + 4 * lane;
-            const float p = fmul(fdiv(1.0f, fadd(1.0f, cam_expf(-fmul(__ldg(inj + t), rs)))), 2.0f);
+            const float p = fmul(frcp(fadd(1.0f, cam_expf(-fmul(__ldg(inj + t), rs)))), 2.0f);
 #pragma unroll
             for (int m = 0; m < CH; m++) {
                 const float4 bv = __ldg(reinterpret_cast<const float4 *>(br + 128 * m));

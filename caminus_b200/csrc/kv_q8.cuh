@@ -25,7 +25,7 @@ CAM_DEV void q8_0_store(const float (&v)[4], uint8_t * blk, int l8, int * err, b
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(CAM_FULL, amax, o));
     const float d = fdiv(amax, 127.0f);
-    const float inv = d != 0.0f ? fdiv(1.0f, d) : 0.0f;
+    const float inv = d != 0.0f ? frcp(d) : 0.0f;                    // (1.0f / d: the IEEE reciprocal is that quotient)
     const __half stored = __float2half_rn(d);
     const bool refuse = !finite_f(amax) || (amax != 0.0f && (d == 0.0f || !finite_f(d) || !finite_f(inv) || !finite_f(__half2float(stored))));
     if (!store) return;

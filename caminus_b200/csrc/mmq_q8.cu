@@ -117,7 +117,7 @@ CAM_DEV void mmq_quant(const float (&v)[16], uint4 & w, uint32_t & hdr) {
                 ww[c >> 2] |= (uint32_t)(q & 0xff) << (8 * (c & 3));
             }
         }
-        d = fdiv(1.0f, d_inv);
+        d = frcp(d_inv);                                            // (1.0f / d_inv, as the reference writes it: the same bits)
     }
     w = make_uint4(ww[0], ww[1], ww[2], ww[3]);
     hdr = LAYOUT == 0 ? __float_as_uint(d) : f2_to_h2(d, sum);
@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
         float d_inv = 0.0f, d = 0.0f;
         if constexpr (LAYOUT == 0) {
             const float am = fabsf(fmul(cam_silu(eg), eu));
-            d_inv = fdiv(127.0f, am); d = fdiv(1.0f, d_inv);
+            d_inv = fdiv(127.0f, am); d = frcp(d_inv);
         }
         uint32_t hdr2[2] = {0u, 0u};
         uint8_t * const yb = y + ((size_t)t.kb * rows + t.r0) * 144;           // row r0's block of this lane's K-block
@@ -489,7 +489,7 @@ __global__ void __launch_bounds__(256, 2) mmq_swiglu_fast_kernel(const T * __res
             if (a != 0.0f) {
                 const float di = fdiv(127.0f, a), tq = fmul(x, di);
                 code = fabsf(tq) < 127.5f ? __float2int_rn(roundf(tq)) : 0;
-                de = fdiv(1.0f, di);
+                de = frcp(di);
             }
             blk[16 + (j & 3) * 32 + lane] = (uint8_t)code;
             if constexpr (LAYOUT == 0) { if (lane == 0) reinterpret_cast<float *>(blk)[j & 3] = de; }
