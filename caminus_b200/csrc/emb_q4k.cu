@@ -53,7 +53,8 @@ __global__ void __launch_bounds__(EMB_WARPS * 32) emb_q4k_kernel(const uint8_t *
                 // subtracted: exact for 0 .. 15, and two operations instead of shift, mask and convert
                 const uint32_t n0 = (w0[j] >> nib) & 0x0f0f0f0fu, n1 = (w1[j] >> nib) & 0x0f0f0f0fu;
                 const f32x2 d0 = pk2(dl0, dl0), d1 = pk2(dl1, dl1), c0 = pk2(ml0, ml0), c1 = pk2(ml1, ml1);
-                // y = fl(fl(dl q) - ml): the subtraction as the addition of -ml (the same rounding)
+                // y = fl(fl(dl q) - ml): the subtraction as the addition of -ml (the same rounding). dl q is exact (dl = an fp16 times an integer
+                // below 64: 17 bits; q below 16), so a product contracted into the addition by the assembler gives the same bits
                 const f32x2 a0 = add2(mul2(d0, add2(pk2(__uint_as_float(__byte_perm(n0, 0x4b000000u, 0x7440)), __uint_as_float(__byte_perm(n0, 0x4b000000u, 0x7441))), bias)), c0);
                 const f32x2 a1 = add2(mul2(d0, add2(pk2(__uint_as_float(__byte_perm(n0, 0x4b000000u, 0x7442)), __uint_as_float(__byte_perm(n0, 0x4b000000u, 0x7443))), bias)), c0);
                 const f32x2 e0 = add2(mul2(d1, add2(pk2(__uint_as_float(__byte_perm(n1, 0x4b000000u, 0x7440)), __uint_as_float(__byte_perm(n1, 0x4b000000u, 0x7441))), bias)), c1);
