@@ -126,3 +126,16 @@ def test_iq2s_grid_packing():
     assert np.array_equal(hip.pack_iq2s_grid(w), w) and np.array_equal(hip.pack_iq2s_grid(w.view(np.int32)), w)
     with pytest.raises(ValueError): hip.pack_iq2s_grid(np.zeros((1024, 8), np.uint8))
     with pytest.raises(ValueError): hip.pack_iq2s_grid(np.zeros(100, np.uint32))
+
+
+def test_no_packed_product_feeds_a_packed_sum():
+    """the assembler contracts mul.rn.f32x2 into a packed add / sub that consumes it (unlike the scalar forms), so a kernel that needs
+    the rounded product writes prod2(..) or scalar products; the one place that nests them (the Q4_K gather) has an exact product"""
+    csrc = os.path.join(ROOT, 'caminus_b200', 'csrc')
+    hits = []
+    for name in sorted(os.listdir(csrc)):
+        if not name.endswith(('.cu', '.cuh')): continue
+        for no, line in enumerate(open(os.path.join(csrc, name)), 1):
+            code = line.split('//')[0]
+            if re.search(r'\b(add2|sub2)\(\s*mul2\(', code) or re.search(r'\b(add2|sub2)\([^;]*,\s*mul2\(', code): hits.append((name, no))
+    assert all(n == 'emb_q4k.cu' for n, _ in hits) and len(hits) == 4, hits
