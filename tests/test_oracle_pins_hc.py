@@ -194,3 +194,37 @@ def test_group_lists_and_items():
     bad = ids.copy(); bad[5] = -1; bad[6] = E
     xs2, yd2, items2, err2 = oracle.group(bad, k, E)
     assert err2 == 2 and items2[0, 0] == 0 and 5 in yd2[:items2[0, 2]].tolist()
+
+
+@pytest.mark.parametrize('rows,K', [(7, 384), (5, 300), (3, 1280)])
+def test_mmq_q8_1_against_numpy(rows, K):
+    """the MMQ-layout quantiser (kernels/ggml_mmq/quantize_mmq.cuh:41-140) restated independently in numpy: per group of 32,
+    d_inv = 127 / amax, q = roundf(x d_inv) (halves away from zero: exact ties are in the data), d = 1 / d_inv; D4 blocks are
+    4 fp32 d + 128 codes, DS4 blocks 4 (fp16 d, fp16 sum) + 128 codes, the sum within one fp16 step of the float64 sum"""
+    g = np.random.default_rng(rows * K); Kp = (K + 127) // 128 * 128
+    x = acts(g, (rows, K), 0.7)
+    x[0, :32] = np.arange(32, dtype=np.float32) - 15.5; x[0, 0] = 127.0      # amax 127: the quotients are the values, the halves are ties
+    x[1, 32:64] = 0                                                          # a zero group: d = 0, codes 0
+    xp = np.zeros((rows, Kp), np.float32); xp[:, :K] = x
+    grp = xp.reshape(rows, Kp // 32, 32)
+    amax = np.abs(grp).max(-1)
+    with np.errstate(divide='ignore', invalid='ignore'):
+        d_inv = np.where(amax > 0, np.float32(127) / amax, np.float32(0)).astype(np.float32)
+        d = np.where(amax > 0, np.float32(1) / d_inv, np.float32(0)).astype(np.float32)
+    t = (grp * d_inv[..., None]).astype(np.float32).astype(np.float64)
+    q = np.where(np.abs(t) < 127.5, np.trunc(t + np.copysign(0.5, t)), 0).astype(np.int8)
+    assert (np.abs(t - np.rint(t)) == 0.5).sum() >= 16                       # the ties are there
+    for layout in (0, 1):
+        y = oracle.mmq_q8_1(x, K, Kp, layout)                                # [Kp / 128, rows, 144]
+        codes = y[:, :, 16:].view(np.int8).reshape(Kp // 128, rows, 4, 32).transpose(1, 0, 2, 3).reshape(rows, Kp // 32, 32)
+        assert np.array_equal(codes, q)
+        hdr = np.ascontiguousarray(y[:, :, :16]).reshape(Kp // 128, rows, 16)
+        if layout == 0:
+            dd = hdr.view(np.float32).reshape(Kp // 128, rows, 4).transpose(1, 0, 2).reshape(rows, Kp // 32)
+            assert np.array_equal(dd.view(np.uint32), d.view(np.uint32))
+        else:
+            hs = hdr.view(np.float16).reshape(Kp // 128, rows, 4, 2).transpose(1, 0, 2, 3).reshape(rows, Kp // 32, 2)
+            assert np.array_equal(hs[..., 0].view(np.uint16), d.astype(np.float16).view(np.uint16))
+            s64 = grp.astype(np.float64).sum(-1)
+            step = np.maximum(np.abs(s64), np.abs(grp).sum(-1) * 1e-3) * 2.0 ** -10 + 1e-7      # an fp16 step at the sum (looser where terms cancel)
+            assert (np.abs(hs[..., 1].astype(np.float64) - s64) <= step).all()
